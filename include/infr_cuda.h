@@ -1,0 +1,179 @@
+/* infr_cuda.h — C ABI of the B200 (sm_100a) backend for MoE4All's quantized MoE FFN path.
+ *
+ * This is the boundary a `Backend` implementation for the reference's seam
+ * (crates/infr-core/src/backend.rs:630-1088) binds through FFI.  Every entry point takes plain
+ * pointers and sizes, returns an int32 status (0 = ok, negative = error class) and never throws
+ * or aborts; the text of the last error is kept per context (`infr_cuda_last_error`).
+ *
+ * A context is bound to one device and one stream.  Calls on one context must be serialised by
+ * the caller (the reference runs one op loop per backend, backend.rs:891-899); distinct contexts
+ * are independent.  There is no CPU fallback anywhere behind this header: an op, dtype or shape
+ * the CUDA kernels do not cover returns INFR_CUDA_ERR_UNSUPPORTED.
+ *
+ * Weights are uploaded byte-for-byte as GGUF blocks (`Rewrite::Native`,
+ * crates/infr-llama/src/seam/weight_upload.rs:8-14); nothing is repacked or re-quantised.
+ */
+#ifndef INFR_CUDA_H
+#define INFR_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  They map onto infr_core::error::Error (crates/infr-core/src/error.rs:11-50):
+ * INVALID_ARG/OOM/CUDA/NCCL/TIMEOUT → Error::Backend(msg), UNSUPPORTED → Error::Unsupported(msg). */
+#define INFR_CUDA_OK 0
+#define INFR_CUDA_ERR_INVALID_ARG (-1)
+#define INFR_CUDA_ERR_UNSUPPORTED (-2)
+#define INFR_CUDA_ERR_OOM (-3)
+#define INFR_CUDA_ERR_CUDA (-4)
+#define INFR_CUDA_ERR_NCCL (-5)
+#define INFR_CUDA_ERR_TIMEOUT (-6)
+
+/* Element / block types (crates/infr-core/src/tensor.rs:7-57), numbered as in the GGUF file
+ * format so a loader can pass a tensor's type through unchanged. */
+#define INFR_CUDA_DT_F32 0
+#define INFR_CUDA_DT_Q4K 12 /* 256 weights / 144 B, crates/infr-core/src/decode_spec.rs:327 */
+#define INFR_CUDA_DT_Q6K 14 /* 256 weights / 210 B, crates/infr-core/src/decode_spec.rs:331 */
+
+/* MoeGating (crates/infr-core/src/graph.rs:73-85). */
+#define INFR_CUDA_GATING_SOFTMAX 0
+#define INFR_CUDA_GATING_SIGMOID 1
+
+typedef struct infr_cuda_ctx infr_cuda_ctx; /* opaque: device, stream, scratch */
+typedef struct infr_cuda_buf infr_cuda_buf; /* opaque: one device allocation, owned by the caller */
+
+/* ---- context ------------------------------------------------------------------------------- */
+
+/* Backend construction (the reference: `VulkanBackend::new`, crates/infr-vulkan/src/lib.rs).
+ * Fails with INFR_CUDA_ERR_UNSUPPORTED on a device that is not compute capability 10.x. */
+int32_t infr_cuda_create(int32_t device, infr_cuda_ctx** out);
+void infr_cuda_destroy(infr_cuda_ctx* ctx);
+/* Message of the most recent failing call on this context ("" if none).  Valid until the next
+ * call on the context.  `Backend` methods return it inside Error::Backend / Error::Unsupported. */
+const char* infr_cuda_last_error(const infr_cuda_ctx* ctx);
+/* Backend::name (backend.rs:631). */
+const char* infr_cuda_name(void);
+/* Use an existing CUDA stream (a `cudaStream_t` passed as void*) instead of the context's own;
+ * NULL restores the context's stream.  Lets a host that owns streams (PyTorch, NCCL) order the
+ * kernels with its own work.  No counterpart in the reference (Vulkan queues are internal). */
+int32_t infr_cuda_set_stream(infr_cuda_ctx* ctx, void* cuda_stream);
+
+/* ---- buffers: Backend::alloc / alloc_uninit / upload / download / sync ------------------------ */
+
+/* Backend::alloc (backend.rs:652; zero-initialised, the calloc contract of :647-651) when
+ * `zero` != 0, Backend::alloc_uninit (backend.rs:659) otherwise. */
+int32_t infr_cuda_alloc(infr_cuda_ctx* ctx, size_t bytes, int32_t zero, infr_cuda_buf** out);
+/* Wrap device memory the caller already owns (a torch tensor, an NCCL receive buffer) as a
+ * buffer handle; freeing the handle leaves the memory alone.  No reference counterpart. */
+int32_t infr_cuda_wrap(infr_cuda_ctx* ctx, void* device_ptr, size_t bytes, infr_cuda_buf** out);
+void infr_cuda_free(infr_cuda_ctx* ctx, infr_cuda_buf* buf);
+/* Buffer::len_bytes (backend.rs:424-433) and the raw device address. */
+size_t infr_cuda_buf_len(const infr_cuda_buf* buf);
+void* infr_cuda_buf_ptr(const infr_cuda_buf* buf);
+/* Backend::upload / download (backend.rs:759-760): prefix copies at a byte offset; out-of-range
+ * is an error, not a panic (backend.rs:22-33).  Both return after the copy has completed. */
+int32_t infr_cuda_upload(infr_cuda_ctx* ctx, infr_cuda_buf* dst, size_t dst_off, const void* src, size_t n);
+int32_t infr_cuda_download(infr_cuda_ctx* ctx, const infr_cuda_buf* src, size_t src_off, void* dst, size_t n);
+/* Backend::sync (backend.rs:1006). */
+int32_t infr_cuda_sync(infr_cuda_ctx* ctx);
+
+/* ---- Op::MoeFfn ------------------------------------------------------------------------------ */
+
+/* Mirrors Op::MoeFfn (crates/infr-core/src/graph.rs:1259-1352) for the forms on the hot path:
+ * split gate/up banks, SiLU, output-side weighting (`weight_before` = false), no `down_scale`,
+ * no hash-routed `expert_ids`, no SwiGLU clamp.  Banks are `[n_expert, out_f, in_f]` row-major,
+ * expert e = the e-th equal byte slice (graph.rs:1257-1258).
+ *
+ * The shared expert of qwen35moe / DeepSeek (graph builder: crates/infr-llama/src/seam/runner.rs:
+ * 8088-8175) can ride in the same call: when `sh_gate` is non-NULL the result is
+ *   dst = moe + sigmoid(sh_gate_inp · x) * shexp(x)   if sh_gate_inp != NULL  (Op::MoeSharedExpertAdd)
+ *   dst = moe + shexp(x)                              otherwise               (Op::Add)
+ * exactly as the separate Linear / GatedAct / Linear / MoeSharedExpertAdd ops would produce. */
+typedef struct infr_cuda_moe_ffn_desc {
+  const infr_cuda_buf* x;           /* [rows, ne] f32: expert input                                */
+  const infr_cuda_buf* router_x;    /* [rows, ne] f32: router input (often the same buffer as x)   */
+  const infr_cuda_buf* router;      /* [n_expert, ne] router_dtype                                 */
+  const infr_cuda_buf* gate_exps;   /* [n_expert, n_ff_exp, ne] gate_dtype                         */
+  const infr_cuda_buf* up_exps;     /* [n_expert, n_ff_exp, ne] up_dtype                           */
+  const infr_cuda_buf* down_exps;   /* [n_expert, ne, n_ff_exp] down_dtype                         */
+  const infr_cuda_buf* exp_probs_b; /* [n_expert] f32 selection-only bias, or NULL                 */
+  infr_cuda_buf* dst;               /* [rows, ne] f32                                              */
+  infr_cuda_buf* ids_out;           /* [rows, n_used] i32 selected experts, rank order; or NULL    */
+  infr_cuda_buf* wts_out;           /* [rows, n_used] f32 routing weights, rank order; or NULL     */
+  uint32_t rows, ne, n_expert, n_used, n_ff_exp;
+  float scale;
+  int32_t router_dtype, gate_dtype, up_dtype, down_dtype; /* INFR_CUDA_DT_*                        */
+  uint32_t gating;                  /* INFR_CUDA_GATING_*                                          */
+  uint32_t norm_w;                  /* renormalise the selected probabilities to sum 1             */
+  uint32_t n_expert_groups, n_expert_groups_used; /* group-limited routing; 0/1 groups = off       */
+  uint32_t ep_lo, ep_n_local;       /* Op::MoeFfn::ep_band (graph.rs:1309-1319): only experts in
+                                       [ep_lo, ep_lo+ep_n_local) contribute; ep_n_local == 0 = off */
+  /* fused shared expert (all NULL = none) */
+  const infr_cuda_buf* sh_gate;     /* [sh_ff, ne] gate_dtype                                      */
+  const infr_cuda_buf* sh_up;       /* [sh_ff, ne] up_dtype                                        */
+  const infr_cuda_buf* sh_down;     /* [ne, sh_ff] down_dtype                                      */
+  const infr_cuda_buf* sh_gate_inp; /* [ne] f32 gate vector, or NULL for the ungated sum           */
+  uint32_t sh_ff;
+  uint32_t path;                    /* 0 = choose by rows; 1 = force the small-m (decode) kernels;
+                                       2 = force the grouped-GEMM (prefill) kernels                */
+} infr_cuda_moe_ffn_desc;
+
+/* Backend::execute of a graph holding one Op::MoeFfn (backend.rs:908; CPU arm
+ * crates/infr-cpu/src/lib.rs:3584-4304, Vulkan lowering crates/infr-vulkan/src/adapter.rs:
+ * 8884-9652).  Asynchronous on the context's stream; outputs are visible after infr_cuda_sync or
+ * a download. */
+int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* desc);
+
+/* Router logits + gating + top-k only (the `moe_topk` stage, crates/infr-vulkan/src/recorder.rs:
+ * 12893; CPU crates/infr-cpu/src/lib.rs:3684-3863).  Uses the routing fields of the descriptor
+ * (router_x, router, exp_probs_b, ids_out, wts_out, rows, ne, n_expert, n_used, scale, gating,
+ * norm_w, groups); bank and dst fields are ignored.  ids_out and wts_out are required. */
+int32_t infr_cuda_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* desc);
+
+/* ---- the ops around it (shared expert and the 40-layer stack) --------------------------------- */
+
+/* Op::Linear (crates/infr-cpu/src/lib.rs:1275-1328): y[m, out_f] = x[m, in_f] · Wᵀ, W row-major
+ * [out_f, in_f] of `dtype` (F32, Q4_K, Q6_K). */
+int32_t infr_cuda_linear(infr_cuda_ctx* ctx, int32_t dtype, const infr_cuda_buf* w, const infr_cuda_buf* x,
+                         infr_cuda_buf* y, uint32_t m, uint32_t in_f, uint32_t out_f);
+/* Op::GatedAct with Activation::Silu, contiguous operands (crates/infr-cpu/src/lib.rs:2973-3027):
+ * dst = silu(gate) * up, n elements. */
+int32_t infr_cuda_gated_act(infr_cuda_ctx* ctx, const infr_cuda_buf* gate, const infr_cuda_buf* up,
+                            infr_cuda_buf* dst, size_t n);
+/* Op::MoeSharedExpertAdd (crates/infr-core/src/graph.rs:1449-1463; CPU lib.rs:3336-3356):
+ * dst[r, :] = moe[r, :] + sigmoid(gate[r]) * shexp[r, :]. */
+int32_t infr_cuda_moe_shared_add(infr_cuda_ctx* ctx, const infr_cuda_buf* moe, const infr_cuda_buf* shexp,
+                                 const infr_cuda_buf* gate, infr_cuda_buf* dst, uint32_t rows, uint32_t n);
+/* Op::RmsNorm (crates/infr-cpu/src/lib.rs:1046-1069). */
+int32_t infr_cuda_rmsnorm(infr_cuda_ctx* ctx, const infr_cuda_buf* x, const infr_cuda_buf* weight,
+                          infr_cuda_buf* dst, uint32_t rows, uint32_t dim, float eps);
+/* Op::Add (crates/infr-cpu/src/lib.rs:3055-3070). */
+int32_t infr_cuda_add(infr_cuda_ctx* ctx, const infr_cuda_buf* a, const infr_cuda_buf* b, infr_cuda_buf* dst,
+                      size_t n);
+
+/* ---- expert-parallel building blocks (crates/infr-vulkan/src/ep.rs:454-493) ------------------- */
+
+/* Expert FFN over rows that are already grouped by expert: rows [seg_off[e], seg_off[e+1]) of
+ * `x_rows` go through local expert e (gate/up → SwiGLU → down) and land in the same rows of
+ * `y_rows`.  This is what a rank runs between the dispatch and the combine exchange; the banks
+ * hold only the rank's `n_local` experts.  `seg_off` is [n_local+1] i32 on the device.
+ * x_rows / y_rows are f32 [n_rows, ne]. */
+int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_rows, const infr_cuda_buf* seg_off,
+                                  const infr_cuda_buf* gate_exps, const infr_cuda_buf* up_exps,
+                                  const infr_cuda_buf* down_exps, infr_cuda_buf* y_rows, uint32_t n_rows,
+                                  uint32_t n_local, uint32_t ne, uint32_t n_ff_exp, int32_t gate_dtype,
+                                  int32_t up_dtype, int32_t down_dtype);
+
+/* ---- introspection for the test-suite and the benchmark ---------------------------------------- */
+
+/* Number of kernel launches this context has issued since creation (host-side count). */
+uint64_t infr_cuda_launch_count(const infr_cuda_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INFR_CUDA_H */

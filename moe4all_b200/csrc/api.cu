@@ -1,0 +1,444 @@
+// C ABI: context, buffers, descriptor validation and dispatch (see include/infr_cuda.h).
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "kernels.cuh"
+
+namespace infr {
+
+int32_t fail(infr_cuda_ctx* ctx, int32_t code, const std::string& msg) {
+  if (ctx) ctx->last_error = msg;
+  return code;
+}
+
+int32_t check_cuda(infr_cuda_ctx* ctx, cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return INFR_CUDA_OK;
+  const int32_t code = (e == cudaErrorMemoryAllocation) ? INFR_CUDA_ERR_OOM : INFR_CUDA_ERR_CUDA;
+  return fail(ctx, code, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+int32_t ensure_scratch(infr_cuda_ctx* ctx, size_t bytes) {
+  if (bytes <= ctx->scratch_bytes) return INFR_CUDA_OK;
+  // growing is a synchronising operation: earlier launches may still use the old block
+  cudaError_t e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "scratch grow: sync");
+  if (ctx->scratch) cudaFree(ctx->scratch);
+  ctx->scratch = nullptr;
+  ctx->scratch_bytes = 0;
+  const size_t want = align_up(bytes + bytes / 4, 1 << 20);
+  e = cudaMalloc(&ctx->scratch, want);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "scratch grow: cudaMalloc");
+  ctx->scratch_bytes = want;
+  return INFR_CUDA_OK;
+}
+
+namespace {
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (prev >= 0 && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+bool fits(const infr_cuda_buf* b, size_t need) { return b && b->ptr && b->bytes >= need; }
+
+// A bounded wait that ran out inside a kernel is reported here, after the stream has drained.
+int32_t poll_status(infr_cuda_ctx* ctx) {
+  DeviceStatus st;
+  cudaError_t e = cudaMemcpy(&st, ctx->status, sizeof(st), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "status read");
+  if (st.timeout) {
+    cudaMemset(ctx->status, 0, sizeof(DeviceStatus));
+    char msg[96];
+    std::snprintf(msg, sizeof msg, "a bounded device-side wait ran out (kernel tag %d); outputs of that call are invalid",
+                  st.timeout);
+    return fail(ctx, INFR_CUDA_ERR_TIMEOUT, msg);
+  }
+  return INFR_CUDA_OK;
+}
+
+}  // namespace
+}  // namespace infr
+
+using namespace infr;
+
+extern "C" {
+
+const char* infr_cuda_name(void) { return "cuda-sm100a"; }
+
+int32_t infr_cuda_create(int32_t device, infr_cuda_ctx** out) {
+  if (!out) return INFR_CUDA_ERR_INVALID_ARG;
+  *out = nullptr;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || device < 0 || device >= n) return e == cudaSuccess ? INFR_CUDA_ERR_INVALID_ARG : INFR_CUDA_ERR_CUDA;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return INFR_CUDA_ERR_CUDA;
+  if (prop.major != 10) return INFR_CUDA_ERR_UNSUPPORTED;  // the kernels are built for sm_100a only
+  infr_cuda_ctx* ctx = new (std::nothrow) infr_cuda_ctx();
+  if (!ctx) return INFR_CUDA_ERR_OOM;
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  DeviceGuard g(device);
+  if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaMalloc(&ctx->status, sizeof(DeviceStatus)) != cudaSuccess ||
+      cudaMalloc(&ctx->counters, 64 * sizeof(unsigned int)) != cudaSuccess ||
+      cudaMemset(ctx->status, 0, sizeof(DeviceStatus)) != cudaSuccess ||
+      cudaMemset(ctx->counters, 0, 64 * sizeof(unsigned int)) != cudaSuccess) {
+    infr_cuda_destroy(ctx);
+    return INFR_CUDA_ERR_CUDA;
+  }
+  ctx->stream = ctx->own_stream;
+  *out = ctx;
+  return INFR_CUDA_OK;
+}
+
+void infr_cuda_destroy(infr_cuda_ctx* ctx) {
+  if (!ctx) return;
+  DeviceGuard g(ctx->device);
+  if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
+  if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->status) cudaFree(ctx->status);
+  if (ctx->counters) cudaFree(ctx->counters);
+  if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+  delete ctx;
+}
+
+const char* infr_cuda_last_error(const infr_cuda_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+int32_t infr_cuda_set_stream(infr_cuda_ctx* ctx, void* cuda_stream) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  ctx->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
+  return INFR_CUDA_OK;
+}
+
+int32_t infr_cuda_alloc(infr_cuda_ctx* ctx, size_t bytes, int32_t zero, infr_cuda_buf** out) {
+  if (!ctx || !out) return INFR_CUDA_ERR_INVALID_ARG;
+  *out = nullptr;
+  DeviceGuard g(ctx->device);
+  infr_cuda_buf* b = new (std::nothrow) infr_cuda_buf();
+  if (!b) return fail(ctx, INFR_CUDA_ERR_OOM, "alloc: host out of memory");
+  // 16 spare bytes so block decoders may read a word pair at the very end of a bank
+  cudaError_t e = cudaMalloc(&b->ptr, bytes + 16);
+  if (e != cudaSuccess) {
+    delete b;
+    cudaGetLastError();
+    return check_cuda(ctx, e, "alloc");
+  }
+  if (zero) {
+    e = cudaMemsetAsync(b->ptr, 0, bytes + 16, ctx->stream);
+    if (e != cudaSuccess) {
+      cudaFree(b->ptr);
+      delete b;
+      return check_cuda(ctx, e, "alloc: memset");
+    }
+  }
+  b->bytes = bytes;
+  b->owned = true;
+  *out = b;
+  return INFR_CUDA_OK;
+}
+
+int32_t infr_cuda_wrap(infr_cuda_ctx* ctx, void* device_ptr, size_t bytes, infr_cuda_buf** out) {
+  if (!ctx || !out) return INFR_CUDA_ERR_INVALID_ARG;
+  *out = nullptr;
+  if (!device_ptr) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "wrap: null device pointer");
+  if (reinterpret_cast<uintptr_t>(device_ptr) % 16) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "wrap: pointer must be 16-byte aligned");
+  infr_cuda_buf* b = new (std::nothrow) infr_cuda_buf();
+  if (!b) return fail(ctx, INFR_CUDA_ERR_OOM, "wrap: host out of memory");
+  b->ptr = device_ptr;
+  b->bytes = bytes;
+  b->owned = false;
+  *out = b;
+  return INFR_CUDA_OK;
+}
+
+void infr_cuda_free(infr_cuda_ctx* ctx, infr_cuda_buf* buf) {
+  if (!buf) return;
+  if (buf->owned && buf->ptr) {
+    if (ctx) {
+      DeviceGuard g(ctx->device);
+      cudaStreamSynchronize(ctx->stream);
+      cudaFree(buf->ptr);
+    } else {
+      cudaFree(buf->ptr);
+    }
+  }
+  delete buf;
+}
+
+size_t infr_cuda_buf_len(const infr_cuda_buf* buf) { return buf ? buf->bytes : 0; }
+void* infr_cuda_buf_ptr(const infr_cuda_buf* buf) { return buf ? buf->ptr : nullptr; }
+
+int32_t infr_cuda_upload(infr_cuda_ctx* ctx, infr_cuda_buf* dst, size_t dst_off, const void* src, size_t n) {
+  if (!ctx || !dst || (!src && n)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "upload: null argument");
+  if (dst_off > dst->bytes || n > dst->bytes - dst_off) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "upload: range exceeds the buffer");
+  if (!n) return INFR_CUDA_OK;
+  DeviceGuard g(ctx->device);
+  cudaError_t e = cudaMemcpyAsync(static_cast<char*>(dst->ptr) + dst_off, src, n, cudaMemcpyHostToDevice, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  return check_cuda(ctx, e, "upload");
+}
+
+int32_t infr_cuda_download(infr_cuda_ctx* ctx, const infr_cuda_buf* src, size_t src_off, void* dst, size_t n) {
+  if (!ctx || !src || (!dst && n)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "download: null argument");
+  if (src_off > src->bytes || n > src->bytes - src_off) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "download: range exceeds the buffer");
+  DeviceGuard g(ctx->device);
+  cudaError_t e = cudaSuccess;
+  if (n) e = cudaMemcpyAsync(dst, static_cast<const char*>(src->ptr) + src_off, n, cudaMemcpyDeviceToHost, ctx->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "download");
+  return poll_status(ctx);
+}
+
+int32_t infr_cuda_sync(infr_cuda_ctx* ctx) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  DeviceGuard g(ctx->device);
+  cudaError_t e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "sync");
+  return poll_status(ctx);
+}
+
+uint64_t infr_cuda_launch_count(const infr_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// ---- Op::MoeFfn ---------------------------------------------------------------------------------
+
+static int32_t validate_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
+  if (!d) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: null descriptor");
+  if (!d->rows || !d->ne || !d->n_expert || !d->n_used) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: zero dimension");
+  if (d->n_used > d->n_expert) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: n_used exceeds n_expert");
+  if (d->n_used > 32) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: n_used > 32 is not covered");
+  if (d->n_expert > 4096) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: more than 4096 experts is not covered");
+  if (d->ne % 8) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: ne must be a multiple of 8");
+  if (d->router_dtype != INFR_CUDA_DT_F32) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: router dtype must be F32");
+  if (d->gating != INFR_CUDA_GATING_SOFTMAX && d->gating != INFR_CUDA_GATING_SIGMOID)
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: gating must be softmax or sigmoid");
+  if (d->n_expert_groups > 1 && d->n_expert_groups_used > 0) {
+    if (d->n_expert_groups > 32) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: more than 32 expert groups is not covered");
+    if (d->n_expert % d->n_expert_groups) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: n_expert is not a multiple of n_expert_groups");
+  }
+  const size_t xb = (size_t)d->rows * d->ne * 4;
+  if (!fits(d->router_x, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: router_x missing or too small");
+  if (!fits(d->router, (size_t)d->n_expert * d->ne * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: router missing or too small");
+  if (d->exp_probs_b && !fits(d->exp_probs_b, (size_t)d->n_expert * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: exp_probs_b too small");
+  const size_t kb = (size_t)d->rows * d->n_used * 4;
+  if (d->ids_out && !fits(d->ids_out, kb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ids_out too small");
+  if (d->wts_out && !fits(d->wts_out, kb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: wts_out too small");
+  return INFR_CUDA_OK;
+}
+
+static int32_t validate_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
+  int32_t rc = validate_route(ctx, d);
+  if (rc) return rc;
+  if (!d->n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: zero n_ff_exp");
+  if (d->gate_dtype != INFR_CUDA_DT_Q4K || d->up_dtype != INFR_CUDA_DT_Q4K || d->down_dtype != INFR_CUDA_DT_Q6K)
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be gate/up Q4_K and down Q6_K");
+  if (d->ne % 256 || d->n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ne and n_ff_exp must be multiples of the 256-weight block");
+  const size_t xb = (size_t)d->rows * d->ne * 4;
+  if (!fits(d->x, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: x missing or too small");
+  if (!fits(d->dst, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: dst missing or too small");
+  const size_t gb = (size_t)d->n_expert * d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
+  const size_t db = (size_t)d->n_expert * d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
+  if (!fits(d->gate_exps, gb) || !fits(d->up_exps, gb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: gate/up bank missing or too small");
+  if (!fits(d->down_exps, db)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: down bank missing or too small");
+  if (d->ep_n_local && (uint64_t)d->ep_lo + d->ep_n_local > d->n_expert)
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ep band exceeds n_expert");
+  if (d->sh_gate || d->sh_up || d->sh_down) {
+    if (!d->sh_gate || !d->sh_up || !d->sh_down || !d->sh_ff || d->sh_ff % 256)
+      return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: shared expert needs gate, up, down and sh_ff (multiple of 256)");
+    const size_t sgb = (size_t)d->sh_ff * row_bytes(d->gate_dtype, d->ne);
+    const size_t sdb = (size_t)d->ne * row_bytes(d->down_dtype, d->sh_ff);
+    if (!fits(d->sh_gate, sgb) || !fits(d->sh_up, sgb) || !fits(d->sh_down, sdb))
+      return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: shared expert tensor too small");
+    if (d->sh_gate_inp && !fits(d->sh_gate_inp, (size_t)d->ne * 4))
+      return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: sh_gate_inp too small");
+  } else if (d->sh_gate_inp) {
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: sh_gate_inp without a shared expert");
+  }
+  return INFR_CUDA_OK;
+}
+
+namespace {
+// Scratch carve-up for one call.
+struct Scratch {
+  float* logits;
+  float* sh_logit;
+  int32_t* ids;
+  float* wts;
+  float* act;
+  size_t total;
+};
+
+Scratch carve(void* base, const infr_cuda_moe_ffn_desc* d, bool with_act) {
+  Scratch s;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    void* p = base ? static_cast<char*>(base) + off : nullptr;
+    off += align_up(bytes, 256);
+    return p;
+  };
+  s.logits = static_cast<float*>(take((size_t)d->rows * d->n_expert * 4));
+  s.sh_logit = static_cast<float*>(take((size_t)d->rows * 4));
+  s.ids = static_cast<int32_t*>(take((size_t)d->rows * d->n_used * 4));
+  s.wts = static_cast<float*>(take((size_t)d->rows * d->n_used * 4));
+  s.act = with_act ? static_cast<float*>(take(((size_t)d->rows * d->n_used * d->n_ff_exp + (size_t)d->rows * d->sh_ff) * 4)) : nullptr;
+  s.total = off;
+  return s;
+}
+
+RouteParams route_params(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, const Scratch& s, bool with_gate) {
+  RouteParams rp = {};
+  rp.router_x = static_cast<const float*>(d->router_x->ptr);
+  rp.x = d->x ? static_cast<const float*>(d->x->ptr) : rp.router_x;
+  rp.router = static_cast<const float*>(d->router->ptr);
+  rp.sh_gate_inp = (with_gate && d->sh_gate_inp) ? static_cast<const float*>(d->sh_gate_inp->ptr) : nullptr;
+  rp.bias = d->exp_probs_b ? static_cast<const float*>(d->exp_probs_b->ptr) : nullptr;
+  rp.logits = s.logits;
+  rp.sh_logit = s.sh_logit;
+  rp.ids = d->ids_out ? static_cast<int32_t*>(d->ids_out->ptr) : s.ids;
+  rp.wts = d->wts_out ? static_cast<float*>(d->wts_out->ptr) : s.wts;
+  rp.counter = ctx->counters;
+  rp.rows = d->rows;
+  rp.ne = d->ne;
+  rp.n_expert = d->n_expert;
+  rp.n_used = d->n_used;
+  rp.scale = d->scale;
+  rp.gating = d->gating;
+  rp.norm_w = d->norm_w ? 1 : 0;
+  rp.n_groups = d->n_expert_groups;
+  rp.n_groups_used = d->n_expert_groups_used;
+  return rp;
+}
+}  // namespace
+
+int32_t infr_cuda_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  int32_t rc = validate_route(ctx, d);
+  if (rc) return rc;
+  if (!d->ids_out || !d->wts_out) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_route: ids_out and wts_out are required");
+  DeviceGuard g(ctx->device);
+  Scratch sz = carve(nullptr, d, false);
+  if ((rc = ensure_scratch(ctx, sz.total))) return rc;
+  Scratch s = carve(ctx->scratch, d, false);
+  RouteParams rp = route_params(ctx, d, s, false);
+  return launch_route(ctx, rp, false);
+}
+
+int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  int32_t rc = validate_ffn(ctx, d);
+  if (rc) return rc;
+  DeviceGuard g(ctx->device);
+  const bool has_sh = d->sh_gate != nullptr;
+  std::string why;
+  const bool small_ok = decode_ffn_supported(ctx, d->ne, d->n_ff_exp, has_sh ? d->sh_ff : 0, d->n_used, &why);
+  uint32_t path = d->path;
+  if (path == 0) path = (d->rows <= 8 && small_ok) ? 1 : 2;
+  if (path == 1) {
+    if (!small_ok) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, why);
+    Scratch sz = carve(nullptr, d, true);
+    if ((rc = ensure_scratch(ctx, sz.total))) return rc;
+    Scratch s = carve(ctx->scratch, d, true);
+    RouteParams rp = route_params(ctx, d, s, true);
+    if ((rc = launch_route(ctx, rp, false))) return rc;
+    DecodeParams dp = {};
+    dp.x = static_cast<const float*>(d->x->ptr);
+    dp.ids = rp.ids;
+    dp.wts = rp.wts;
+    dp.sh_logit = (has_sh && d->sh_gate_inp) ? s.sh_logit : nullptr;
+    dp.gate = static_cast<const uint8_t*>(d->gate_exps->ptr);
+    dp.up = static_cast<const uint8_t*>(d->up_exps->ptr);
+    dp.down = static_cast<const uint8_t*>(d->down_exps->ptr);
+    dp.sh_gate = has_sh ? static_cast<const uint8_t*>(d->sh_gate->ptr) : nullptr;
+    dp.sh_up = has_sh ? static_cast<const uint8_t*>(d->sh_up->ptr) : nullptr;
+    dp.sh_down = has_sh ? static_cast<const uint8_t*>(d->sh_down->ptr) : nullptr;
+    dp.act = s.act;
+    dp.dst = static_cast<float*>(d->dst->ptr);
+    dp.status = ctx->status;
+    dp.gate_stride = (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
+    dp.up_stride = dp.gate_stride;
+    dp.down_stride = (size_t)d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
+    dp.rows = d->rows;
+    dp.ne = d->ne;
+    dp.n_used = d->n_used;
+    dp.nff = d->n_ff_exp;
+    dp.sh_ff = has_sh ? d->sh_ff : 0;
+    dp.n_expert = d->n_expert;
+    dp.ep_lo = d->ep_lo;
+    dp.ep_n = d->ep_n_local;
+    return launch_decode_ffn(ctx, dp, false);
+  }
+  return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: the grouped-GEMM path is not built yet");
+}
+
+// ---- the ops around it --------------------------------------------------------------------------
+
+int32_t infr_cuda_linear(infr_cuda_ctx* ctx, int32_t dtype, const infr_cuda_buf* w, const infr_cuda_buf* x,
+                         infr_cuda_buf* y, uint32_t m, uint32_t in_f, uint32_t out_f) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  if (!m || !in_f || !out_f) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: zero dimension");
+  const size_t rb = row_bytes(dtype, in_f);
+  if (!rb) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32, Q4_K, Q6_K only)");
+  if (dtype != INFR_CUDA_DT_F32 && in_f % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: in_f must be a multiple of the 256-weight block");
+  if (!fits(w, rb * out_f) || !fits(x, (size_t)m * in_f * 4) || !fits(y, (size_t)m * out_f * 4))
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: buffer missing or too small");
+  DeviceGuard g(ctx->device);
+  return launch_linear(ctx, dtype, static_cast<const uint8_t*>(w->ptr), static_cast<const float*>(x->ptr),
+                       static_cast<float*>(y->ptr), (int)m, (int)in_f, (int)out_f);
+}
+
+int32_t infr_cuda_gated_act(infr_cuda_ctx* ctx, const infr_cuda_buf* gate, const infr_cuda_buf* up, infr_cuda_buf* dst, size_t n) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  if (!fits(gate, n * 4) || !fits(up, n * 4) || !fits(dst, n * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "gated_act: buffer missing or too small");
+  if (!n) return INFR_CUDA_OK;
+  DeviceGuard g(ctx->device);
+  return launch_gated_act(ctx, static_cast<const float*>(gate->ptr), static_cast<const float*>(up->ptr), static_cast<float*>(dst->ptr), n);
+}
+
+int32_t infr_cuda_moe_shared_add(infr_cuda_ctx* ctx, const infr_cuda_buf* moe, const infr_cuda_buf* shexp,
+                                 const infr_cuda_buf* gate, infr_cuda_buf* dst, uint32_t rows, uint32_t n) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  const size_t b = (size_t)rows * n * 4;
+  if (!rows || !n) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_shared_add: zero dimension");
+  if (!fits(moe, b) || !fits(shexp, b) || !fits(dst, b) || !fits(gate, (size_t)rows * 4))
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_shared_add: buffer missing or too small");
+  DeviceGuard g(ctx->device);
+  return launch_shared_add(ctx, static_cast<const float*>(moe->ptr), static_cast<const float*>(shexp->ptr),
+                           static_cast<const float*>(gate->ptr), static_cast<float*>(dst->ptr), (int)rows, (int)n);
+}
+
+int32_t infr_cuda_rmsnorm(infr_cuda_ctx* ctx, const infr_cuda_buf* x, const infr_cuda_buf* weight, infr_cuda_buf* dst,
+                          uint32_t rows, uint32_t dim, float eps) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  if (!rows || !dim) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "rmsnorm: zero dimension");
+  const size_t b = (size_t)rows * dim * 4;
+  if (!fits(x, b) || !fits(dst, b) || !fits(weight, (size_t)dim * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "rmsnorm: buffer missing or too small");
+  DeviceGuard g(ctx->device);
+  return launch_rmsnorm(ctx, static_cast<const float*>(x->ptr), static_cast<const float*>(weight->ptr),
+                        static_cast<float*>(dst->ptr), (int)rows, (int)dim, eps);
+}
+
+int32_t infr_cuda_add(infr_cuda_ctx* ctx, const infr_cuda_buf* a, const infr_cuda_buf* b, infr_cuda_buf* dst, size_t n) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  if (!fits(a, n * 4) || !fits(b, n * 4) || !fits(dst, n * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "add: buffer missing or too small");
+  if (!n) return INFR_CUDA_OK;
+  DeviceGuard g(ctx->device);
+  return launch_add(ctx, static_cast<const float*>(a->ptr), static_cast<const float*>(b->ptr), static_cast<float*>(dst->ptr), n);
+}
+
+int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf*, const infr_cuda_buf*, const infr_cuda_buf*,
+                                  const infr_cuda_buf*, const infr_cuda_buf*, infr_cuda_buf*, uint32_t, uint32_t, uint32_t,
+                                  uint32_t, int32_t, int32_t, int32_t) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: the grouped-GEMM path is not built yet");
+}
+
+}  // extern "C"

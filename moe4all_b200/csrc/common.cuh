@@ -1,0 +1,222 @@
+// Shared device/host helpers of the sm_100a MoE FFN library.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/infr_cuda.h"
+
+namespace infr {
+
+// ---------------------------------------------------------------------------------------------
+// Host-side objects behind the opaque C handles.
+// ---------------------------------------------------------------------------------------------
+
+constexpr uint32_t Q4K_BLOCK_BYTES = 144;  // 256 weights: f16 d, f16 dmin, 12 B scales, 128 B nibbles
+constexpr uint32_t Q6K_BLOCK_BYTES = 210;  // 256 weights: 128 B ql, 64 B qh, 16 i8 scales, f16 d
+constexpr uint32_t QK = 256;
+
+// Device-visible status word written by kernels whose bounded waits ran out.
+struct DeviceStatus {
+  int timeout;      // != 0: a bounded wait gave up (value identifies the kernel)
+  int bad_index;    // != 0: an index was clamped (diagnostic only)
+};
+
+}  // namespace infr
+
+struct infr_cuda_buf {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  bool owned = false;
+};
+
+struct infr_cuda_ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  std::string last_error;
+  uint64_t launches = 0;
+  // scratch grown on demand (never inside a launch sequence that could be captured)
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  infr::DeviceStatus* status = nullptr;       // device memory
+  unsigned int* counters = nullptr;           // device memory: completion counters (zeroed by users)
+};
+
+namespace infr {
+
+int32_t fail(infr_cuda_ctx* ctx, int32_t code, const std::string& msg);
+int32_t check_cuda(infr_cuda_ctx* ctx, cudaError_t e, const char* what);
+int32_t ensure_scratch(infr_cuda_ctx* ctx, size_t bytes);
+
+inline size_t row_bytes(int32_t dtype, size_t n_elem) {
+  switch (dtype) {
+    case INFR_CUDA_DT_F32: return n_elem * 4;
+    case INFR_CUDA_DT_Q4K: return n_elem / QK * Q4K_BLOCK_BYTES;
+    case INFR_CUDA_DT_Q6K: return n_elem / QK * Q6K_BLOCK_BYTES;
+    default: return 0;
+  }
+}
+
+#ifdef __CUDACC__
+#define INFR_HD __host__ __device__
+#else
+#define INFR_HD
+#endif
+INFR_HD inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---------------------------------------------------------------------------------------------
+// Device helpers.
+// ---------------------------------------------------------------------------------------------
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t h) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(h & 0xFFFFu)));
+}
+
+// ---- mbarrier + bulk async copy (TMA, untiled form; never multicast) --------------------------
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+// Bounded wait: returns false when the limit ran out (the caller records the failure in the
+// status word and leaves without touching the data).  The limit is a few seconds of polling.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (1u << 24); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 4096) __nanosleep(64);
+  }
+  return false;
+}
+
+// 1-D bulk copy global → this CTA's shared memory, completion counted in bytes on `bar`.
+// Both addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// L2 prefetch of a byte range (16-byte aligned address, size multiple of 16).
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gmem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes) : "memory");
+}
+
+// ---- programmatic dependent launch ------------------------------------------------------------
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---- warp reductions ----------------------------------------------------------------------------
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+
+// ---- in-register block unpack -------------------------------------------------------------------
+
+// Build the f32 whose top mantissa bits hold byte `B` of `w`:  bits = 0x3F000000 | byte<<16.
+// With byte = 0x80 | (n << 3) this is exactly 1 + n/16  (n a 4-bit code);
+// with byte = 0x80 | (q << 1) this is exactly 1 + q/64  (q a 6-bit code).
+template <int B>
+__device__ __forceinline__ float byte_to_unit_float(uint32_t w) {
+  return __uint_as_float(__byte_perm(w, 0x0000003Fu, 0x4055u | (B << 8)));
+}
+
+// Q4_K: 6-bit (scale, min) pairs of sub-blocks 2j and 2j+1 from the 12 scale bytes held in
+// words s0..s2 (GGUF `get_scale_min_k4` layout).  Returns sc | (sc' << 8) and m | (m' << 8).
+__device__ __forceinline__ void q4k_scale_min_pair(uint32_t s0, uint32_t s1, uint32_t s2, int j, uint32_t& scp,
+                                                   uint32_t& mp) {
+  const int sh = (j & 1) * 16;
+  const uint32_t a = (s0 >> sh) & 0xFFFFu, b = (s1 >> sh) & 0xFFFFu, t = (s2 >> sh) & 0xFFFFu;
+  if (j < 2) {
+    scp = a & 0x3F3Fu;
+    mp = b & 0x3F3Fu;
+  } else {
+    scp = (t & 0x0F0Fu) | ((a >> 2) & 0x3030u);
+    mp = ((t >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
+  }
+}
+
+// Dot product of 64 consecutive weights of a Q4_K block (elements 64j .. 64j+63) with x[0..63].
+//   hdr : the block's first 16 bytes (d, dmin, scales[12]);  q : qs[32j .. 32j+31] as 8 words
+//   xs0 / xs1 : Σ x[0..31], Σ x[32..63]
+// Codes enter the FMA as 1 + n/16 built by byte permutes, so
+//   Σ w·x = 16·d·sc·(A − X) − dmin·m·X   per 32-element sub-block, A = Σ (1 + n/16)·x.
+__device__ __forceinline__ float q4k_dot64(const uint4& hdr, const uint32_t (&q)[8], const float (&x)[64], float xs0,
+                                           float xs1, int j) {
+  float2 alo0 = make_float2(0.f, 0.f), alo1 = alo0, ahi0 = alo0, ahi1 = alo0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t w = q[i];
+    const uint32_t lo = ((w << 3) & 0x78787878u) | 0x80808080u;
+    const uint32_t hi = ((w >> 1) & 0x78787878u) | 0x80808080u;
+    alo0 = __ffma2_rn(make_float2(byte_to_unit_float<0>(lo), byte_to_unit_float<1>(lo)),
+                      make_float2(x[4 * i + 0], x[4 * i + 1]), alo0);
+    alo1 = __ffma2_rn(make_float2(byte_to_unit_float<2>(lo), byte_to_unit_float<3>(lo)),
+                      make_float2(x[4 * i + 2], x[4 * i + 3]), alo1);
+    ahi0 = __ffma2_rn(make_float2(byte_to_unit_float<0>(hi), byte_to_unit_float<1>(hi)),
+                      make_float2(x[32 + 4 * i + 0], x[32 + 4 * i + 1]), ahi0);
+    ahi1 = __ffma2_rn(make_float2(byte_to_unit_float<2>(hi), byte_to_unit_float<3>(hi)),
+                      make_float2(x[32 + 4 * i + 2], x[32 + 4 * i + 3]), ahi1);
+  }
+  const float A0 = (alo0.x + alo0.y) + (alo1.x + alo1.y);
+  const float A1 = (ahi0.x + ahi0.y) + (ahi1.x + ahi1.y);
+  uint32_t scp, mp;
+  q4k_scale_min_pair(hdr.y, hdr.z, hdr.w, j, scp, mp);
+  const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+  const float s0 = d * (float)(scp & 0xFFu), s1 = d * (float)(scp >> 8);
+  const float m0 = dmin * (float)(mp & 0xFFu), m1 = dmin * (float)(mp >> 8);
+  return (16.f * s0) * (A0 - xs0) - m0 * xs0 + (16.f * s1) * (A1 - xs1) - m1 * xs1;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace infr

@@ -1,0 +1,420 @@
+// Small-m (decode) expert FFN: fused dequant-GEMV directly on GGUF Q4_K / Q6_K blocks.
+//
+//   k_decode_gateup : act[p, f] = silu(W_gate[e_p][f,:]·x) * (W_up[e_p][f,:]·x)      (Q4_K banks)
+//   k_decode_down   : dst[r, i] = Σ_slot w_slot · (W_down[e_slot][i,:]·act[slot,:])  (Q6_K bank)
+//                     (+ shared expert as one more slot, sigmoid-gated or plain)
+//
+// Reference: CPU stages B-E, crates/infr-cpu/src/lib.rs:4051-4303 (mat-vec = dequantised row ·
+// activation, crates/infr-cpu/src/moe.rs:142-173; SwiGLU crates/infr-cpu/src/kernels.rs:6666-6683;
+// rank-ordered weighted sum lib.rs:4287-4303; shared expert lib.rs:3336-3356).  Vulkan twins:
+// shaders/native_gemv_id_multi.comp + silu_mul.comp + moe_accumulate_shared.comp, i.e. five
+// dispatches where this file has two kernels.
+//
+// Data movement: only the routed experts' rows are touched, once.  Each CTA pulls its contiguous
+// slab of rows with 1-D bulk async copies (TMA, never multicast) into shared memory, all issued
+// up front so every SM has its whole share in flight, and lanes unpack blocks in registers:
+// a 4-bit (6-bit) code becomes the float 1 + n/16 (1 + q/64) with one byte-permute, products
+// are packed f32x2 fmas, and row sums finish with warp shuffles.
+#include "kernels.cuh"
+
+namespace infr {
+
+namespace {
+
+constexpr int GU_WARPS = 8;
+constexpr int GU_THREADS = GU_WARPS * 32;
+constexpr int GU_MAX_CHUNKS = 4;
+
+constexpr int DN_WARPS = 8;
+constexpr int DN_THREADS = DN_WARPS * 32;
+constexpr int DN_MAX_SLOTS = 33;  // n_used ≤ 32 plus the shared expert
+
+__device__ __forceinline__ bool in_band(const DecodeParams& p, int e) {
+  return p.ep_n == 0 || ((uint32_t)e >= p.ep_lo && (uint32_t)e < p.ep_lo + p.ep_n);
+}
+
+// ---------------------------------------------------------------------------------------------
+// gate/up + SwiGLU
+// ---------------------------------------------------------------------------------------------
+// One CTA = one (token, slot) pair x one tile of TR = 8*n_chunks output features, for both roles.
+// Shared memory: n_chunks x { 8 gate rows | 8 up rows }, one mbarrier per chunk.
+// Lane L owns the 64-element groups g = L, L+32, ... of the input (for ne = 2048 exactly one, so
+// its 64 activations stay in registers for the whole tile).
+template <int NG>
+__global__ void __launch_bounds__(GU_THREADS) k_decode_gateup(DecodeParams p, int n_chunks) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t s_bar[GU_MAX_CHUNKS];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rb = p.ne / 256 * (int)Q4K_BLOCK_BYTES;  // bytes per weight row
+  const int TR = 8 * n_chunks;
+  const int tiles = p.nff / TR, sh_tiles = p.sh_ff / TR;
+  const int n_routed_jobs = p.rows * p.n_used * tiles;
+
+  pdl_wait();  // ids (and x) come from kernels earlier in the stream
+
+  int pair, tile, r;
+  const uint8_t *gsrc, *usrc;
+  float* act_out;
+  if ((int)blockIdx.x < n_routed_jobs) {
+    pair = blockIdx.x / tiles;
+    tile = blockIdx.x % tiles;
+    r = pair / p.n_used;
+    int e = p.ids[pair];
+    if (e < 0 || e >= p.n_expert) {
+      if (tid == 0) p.status->bad_index = 1;
+      e = min(max(e, 0), p.n_expert - 1);
+    }
+    if (!in_band(p, e)) return;
+    gsrc = p.gate + (size_t)e * p.gate_stride + (size_t)tile * TR * rb;
+    usrc = p.up + (size_t)e * p.up_stride + (size_t)tile * TR * rb;
+    act_out = p.act + (size_t)pair * p.nff + tile * TR;
+  } else {
+    const int jb = blockIdx.x - n_routed_jobs;
+    r = jb / sh_tiles;
+    tile = jb % sh_tiles;
+    gsrc = p.sh_gate + (size_t)tile * TR * rb;
+    usrc = p.sh_up + (size_t)tile * TR * rb;
+    act_out = p.act + (size_t)p.rows * p.n_used * p.nff + (size_t)r * p.sh_ff + tile * TR;
+  }
+
+  const uint32_t chunk_bytes = 8u * rb;  // per role
+  if (tid == 0) {
+    for (int c = 0; c < n_chunks; ++c) mbar_init(&s_bar[c], 1);
+    mbar_fence_init();
+    for (int c = 0; c < n_chunks; ++c) {
+      mbar_arrive_expect_tx(&s_bar[c], 2 * chunk_bytes);
+      unsigned char* dstc = smem + (size_t)c * 2 * chunk_bytes;
+      bulk_g2s(dstc, gsrc + (size_t)c * chunk_bytes, chunk_bytes, &s_bar[c]);
+      bulk_g2s(dstc + chunk_bytes, usrc + (size_t)c * chunk_bytes, chunk_bytes, &s_bar[c]);
+    }
+  }
+
+  // this lane's activations
+  const int n_groups = p.ne / 64;
+  const float* xr = p.x + (size_t)r * p.ne;
+  float xv[64];
+  float xs0 = 0.f, xs1 = 0.f;
+  auto load_x = [&](int g) {
+    const float4* src = reinterpret_cast<const float4*>(xr + (size_t)g * 64);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float4 v = __ldg(src + i);
+      xv[4 * i + 0] = v.x; xv[4 * i + 1] = v.y; xv[4 * i + 2] = v.z; xv[4 * i + 3] = v.w;
+    }
+    xs0 = 0.f; xs1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) { xs0 += xv[i]; xs1 += xv[32 + i]; }
+  };
+  if (NG == 1) {
+    if (lane < n_groups) load_x(lane);
+  }
+  __syncthreads();  // barrier init visible to all waiters
+
+  bool ok = true;
+  for (int c = 0; c < n_chunks; ++c) {
+    if (!mbar_wait_bounded(&s_bar[c], 0)) { ok = false; break; }
+    const unsigned char* grow = smem + (size_t)c * 2 * chunk_bytes + (size_t)warp * rb;
+    const unsigned char* urow = grow + chunk_bytes;
+    float gsum = 0.f, usum = 0.f;
+#pragma unroll
+    for (int t = 0; t < NG; ++t) {
+      const int g = lane + 32 * t;
+      if (g < n_groups) {
+        if (NG > 1) load_x(g);
+        const int blk = g >> 2, j = g & 3;
+        const uint4 gh = *reinterpret_cast<const uint4*>(grow + blk * Q4K_BLOCK_BYTES);
+        const uint4 uh = *reinterpret_cast<const uint4*>(urow + blk * Q4K_BLOCK_BYTES);
+        uint32_t gq[8], uq[8];
+        {
+          const uint4 a = *reinterpret_cast<const uint4*>(grow + blk * Q4K_BLOCK_BYTES + 16 + 32 * j);
+          const uint4 b = *reinterpret_cast<const uint4*>(grow + blk * Q4K_BLOCK_BYTES + 32 + 32 * j);
+          gq[0] = a.x; gq[1] = a.y; gq[2] = a.z; gq[3] = a.w; gq[4] = b.x; gq[5] = b.y; gq[6] = b.z; gq[7] = b.w;
+          const uint4 c4 = *reinterpret_cast<const uint4*>(urow + blk * Q4K_BLOCK_BYTES + 16 + 32 * j);
+          const uint4 d4 = *reinterpret_cast<const uint4*>(urow + blk * Q4K_BLOCK_BYTES + 32 + 32 * j);
+          uq[0] = c4.x; uq[1] = c4.y; uq[2] = c4.z; uq[3] = c4.w; uq[4] = d4.x; uq[5] = d4.y; uq[6] = d4.z; uq[7] = d4.w;
+        }
+        gsum += q4k_dot64(gh, gq, xv, xs0, xs1, j);
+        usum += q4k_dot64(uh, uq, xv, xs0, xs1, j);
+      }
+    }
+    gsum = warp_sum(gsum);
+    usum = warp_sum(usum);
+    if (lane == 0) {
+      const float s = gsum / (1.0f + __expf(-gsum));
+      act_out[c * 8 + warp] = s * usum;
+    }
+  }
+  if (!ok) {
+    // a copy never signalled: report and make sure nothing is still landing in this CTA's
+    // shared memory before it is handed to another CTA
+    if (lane == 0) atomicExch(&p.status->timeout, 1);
+    for (int c = 0; c < n_chunks; ++c) (void)mbar_wait_bounded(&s_bar[c], 0);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// down + weighted combine (+ shared expert)
+// ---------------------------------------------------------------------------------------------
+// One CTA = one token x TI consecutive output features x every slot, so the sum over slots never
+// leaves the CTA.  Shared memory: per slot TI rows of the expert's down matrix (one bulk copy and
+// one mbarrier per slot) and the slot's activation vector.
+// Lane mapping inside a row: unit u = (block b, half h, word lw) covers the 16 elements
+// 256b + 128h + 32q + 4lw + i (q, i = 0..3): three 32-bit words of codes, four scales.
+//
+// Q6_K blocks are 210 bytes, so odd blocks start 2 bytes off a word boundary: words are fetched
+// as two aligned loads and a funnel shift.
+__device__ __forceinline__ uint32_t lds_u32_unaligned(const unsigned char* base, uint32_t off) {
+  const uint32_t a = off & ~3u;
+  const uint32_t lo = *reinterpret_cast<const uint32_t*>(base + a);
+  const uint32_t hi = *reinterpret_cast<const uint32_t*>(base + a + 4);
+  return __funnelshift_r(lo, hi, (off & 3u) * 8);
+}
+
+__global__ void __launch_bounds__(DN_THREADS) k_decode_down(DecodeParams p, int TI) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t s_bar[DN_MAX_SLOTS];
+  __shared__ float s_w[DN_MAX_SLOTS];
+  __shared__ int s_on[DN_MAX_SLOTS];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nb = p.nff / 256;                    // blocks per routed row
+  const int drb = nb * (int)Q6K_BLOCK_BYTES;     // bytes per routed row
+  const bool has_sh = p.sh_down != nullptr;
+  const int sh_nb = p.sh_ff / 256, sh_drb = sh_nb * (int)Q6K_BLOCK_BYTES;
+  const int n_slots = p.n_used + (has_sh ? 1 : 0);
+  const int tiles = p.ne / TI;
+  const int r = blockIdx.x / tiles, i0 = (blockIdx.x % tiles) * TI;
+
+  // shared-memory carve-up: weights per slot, then activations per slot
+  const uint32_t slab = (uint32_t)TI * drb, sh_slab = (uint32_t)TI * sh_drb;
+  const uint32_t slab_pad = (uint32_t)align_up(slab + 8, 16), sh_slab_pad = (uint32_t)align_up(sh_slab + 8, 16);
+  unsigned char* s_wt = smem;
+  float* s_act = reinterpret_cast<float*>(smem + (size_t)p.n_used * slab_pad + (has_sh ? sh_slab_pad : 0));
+
+  pdl_wait();
+
+  if (tid < n_slots) {
+    const int s = tid;
+    if (s < p.n_used) {
+      int e = p.ids[r * p.n_used + s];
+      e = min(max(e, 0), p.n_expert - 1);
+      s_on[s] = in_band(p, e) ? e + 1 : 0;
+      s_w[s] = p.wts[r * p.n_used + s];
+    } else {
+      s_on[s] = 1;
+      s_w[s] = p.sh_logit ? 1.0f / (1.0f + __expf(-p.sh_logit[r])) : 1.0f;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    for (int s = 0; s < n_slots; ++s) mbar_init(&s_bar[s], 1);
+    mbar_fence_init();
+    for (int s = 0; s < n_slots; ++s) {
+      if (!s_on[s]) continue;
+      if (s < p.n_used) {
+        mbar_arrive_expect_tx(&s_bar[s], slab);
+        bulk_g2s(s_wt + (size_t)s * slab_pad, p.down + (size_t)(s_on[s] - 1) * p.down_stride + (size_t)i0 * drb, slab,
+                 &s_bar[s]);
+      } else {
+        mbar_arrive_expect_tx(&s_bar[s], sh_slab);
+        bulk_g2s(s_wt + (size_t)p.n_used * slab_pad, p.sh_down + (size_t)i0 * sh_drb, sh_slab, &s_bar[s]);
+      }
+    }
+  }
+  // activations of this token: routed slots then the shared expert
+  {
+    const float* a_src = p.act + (size_t)r * p.n_used * p.nff;
+    const int n4 = p.n_used * p.nff / 4;
+    for (int i = tid; i < n4; i += DN_THREADS)
+      reinterpret_cast<float4*>(s_act)[i] = __ldcg(reinterpret_cast<const float4*>(a_src) + i);
+    if (has_sh) {
+      const float* sh_src = p.act + (size_t)p.rows * p.n_used * p.nff + (size_t)r * p.sh_ff;
+      float4* d = reinterpret_cast<float4*>(s_act + (size_t)p.n_used * p.nff);
+      for (int i = tid; i < p.sh_ff / 4; i += DN_THREADS) d[i] = __ldcg(reinterpret_cast<const float4*>(sh_src) + i);
+    }
+  }
+  __syncthreads();
+
+  constexpr int MAX_ROWS_PER_WARP = 4;
+  float acc[MAX_ROWS_PER_WARP];
+#pragma unroll
+  for (int q = 0; q < MAX_ROWS_PER_WARP; ++q) acc[q] = 0.f;
+
+  bool ok = true;
+  for (int s = 0; s < n_slots && ok; ++s) {
+    if (!s_on[s]) continue;
+    if (!mbar_wait_bounded(&s_bar[s], 0)) { ok = false; break; }
+    const bool shared_slot = s >= p.n_used;
+    const int row_bytes_s = shared_slot ? sh_drb : drb;
+    const int units = (shared_slot ? sh_nb : nb) * 16;
+    const unsigned char* wt = s_wt + (shared_slot ? (size_t)p.n_used * slab_pad : (size_t)s * slab_pad);
+    const float* a = s_act + (shared_slot ? (size_t)p.n_used * p.nff : (size_t)s * p.nff);
+    const float ws = s_w[s];
+    for (int u = lane; u < units; u += 32) {
+      const int b = u >> 4, h = (u >> 3) & 1, lw = u & 7;
+      // activations of the unit and 96 * their per-quadrant sums
+      float av[16], s96[4];
+      const float* ab = a + b * 256 + h * 128 + lw * 4;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float4 v = *reinterpret_cast<const float4*>(ab + 32 * q);
+        av[4 * q + 0] = v.x; av[4 * q + 1] = v.y; av[4 * q + 2] = v.z; av[4 * q + 3] = v.w;
+        s96[q] = 96.f * ((v.x + v.y) + (v.z + v.w));
+      }
+      const uint32_t boff = (uint32_t)b * Q6K_BLOCK_BYTES;
+#pragma unroll
+      for (int q = 0; q < MAX_ROWS_PER_WARP; ++q) {
+        const int row = warp + q * DN_WARPS;
+        if (row < TI) {
+          // offsets are taken from the 16-byte aligned slab base: rows of an odd block count
+          // start 2 bytes off a word boundary too
+          const uint32_t ro = (uint32_t)row * row_bytes_s + boff;
+          const uint32_t A = lds_u32_unaligned(wt, ro + 64 * h + 4 * lw);
+          const uint32_t B = lds_u32_unaligned(wt, ro + 64 * h + 32 + 4 * lw);
+          const uint32_t H = lds_u32_unaligned(wt, ro + 128 + 32 * h + 4 * lw);
+          const uint32_t S0 = lds_u32_unaligned(wt, ro + 192 + 8 * h);
+          const uint32_t S1 = lds_u32_unaligned(wt, ro + 196 + 8 * h);
+          const float d = f16_bits_to_f32(*reinterpret_cast<const unsigned short*>(wt + ro + 208));
+          // codes as bytes 0x80 | (q << 1)
+          const uint32_t c0 = ((A << 1) & 0x1E1E1E1Eu) | ((H << 5) & 0x60606060u) | 0x80808080u;
+          const uint32_t c1 = ((B << 1) & 0x1E1E1E1Eu) | ((H << 3) & 0x60606060u) | 0x80808080u;
+          const uint32_t c2 = ((A >> 3) & 0x1E1E1E1Eu) | ((H << 1) & 0x60606060u) | 0x80808080u;
+          const uint32_t c3 = ((B >> 3) & 0x1E1E1E1Eu) | ((H >> 1) & 0x60606060u) | 0x80808080u;
+          const uint32_t cs[4] = {c0, c1, c2, c3};
+          // scales of the four quadrants: bytes (lw>>2) + 2q of the eight scale bytes of this half
+          const uint32_t sel = (lw >> 2) ? 0x7531u : 0x6420u;
+          const uint32_t sc4 = __byte_perm(S0, S1, sel);
+          float part = 0.f;
+#pragma unroll
+          for (int qd = 0; qd < 4; ++qd) {
+            const uint32_t c = cs[qd];
+            float2 f = __fmul2_rn(make_float2(byte_to_unit_float<0>(c), byte_to_unit_float<1>(c)),
+                                  make_float2(av[4 * qd + 0], av[4 * qd + 1]));
+            f = __ffma2_rn(make_float2(byte_to_unit_float<2>(c), byte_to_unit_float<3>(c)),
+                           make_float2(av[4 * qd + 2], av[4 * qd + 3]), f);
+            const float F = f.x + f.y;
+            const float sc = (float)(int)(signed char)((sc4 >> (8 * qd)) & 0xFFu);
+            // Σ sc·(q-32)·a = sc·(64·F − 96·S)
+            part = fmaf(sc, fmaf(64.f, F, -s96[qd]), part);
+          }
+          acc[q] = fmaf(ws * d, part, acc[q]);
+        }
+      }
+    }
+  }
+  if (!ok) {
+    if (lane == 0) atomicExch(&p.status->timeout, 2);
+    for (int s = 0; s < n_slots; ++s)
+      if (s_on[s]) (void)mbar_wait_bounded(&s_bar[s], 0);
+    return;
+  }
+#pragma unroll
+  for (int q = 0; q < MAX_ROWS_PER_WARP; ++q) {
+    const int row = warp + q * DN_WARPS;
+    const float v = warp_sum(acc[q]);
+    if (row < TI && lane == 0) p.dst[(size_t)r * p.ne + i0 + row] = v;
+  }
+}
+
+size_t gateup_smem(int ne, int n_chunks) { return (size_t)n_chunks * 2 * 8 * (ne / 256 * Q4K_BLOCK_BYTES); }
+
+int pick_chunks(int ne, int nff, int sh_ff) {
+  for (int c = GU_MAX_CHUNKS; c >= 1; c >>= 1) {
+    const int TR = 8 * c;
+    if (nff % TR) continue;
+    if (sh_ff && sh_ff % TR) continue;
+    if (gateup_smem(ne, c) <= 100 * 1024) return c;
+  }
+  return 0;
+}
+
+size_t down_smem(int TI, int nff, int sh_ff, int n_used) {
+  const size_t slab = align_up((size_t)TI * (nff / 256 * Q6K_BLOCK_BYTES) + 8, 16);
+  const size_t sh_slab = sh_ff ? align_up((size_t)TI * (sh_ff / 256 * Q6K_BLOCK_BYTES) + 8, 16) : 0;
+  return (size_t)n_used * slab + sh_slab + ((size_t)n_used * nff + sh_ff) * sizeof(float);
+}
+
+// TI rows per CTA: bulk copies need TI * row_bytes to be a multiple of 16 for both banks.
+int pick_down_tile(int ne, int nff, int sh_ff, int n_used) {
+  const int cands[] = {16, 8, 4};
+  for (int TI : cands) {
+    if (ne % TI) continue;
+    if (((size_t)TI * (nff / 256) * Q6K_BLOCK_BYTES) % 16) continue;
+    if (sh_ff && ((size_t)TI * (sh_ff / 256) * Q6K_BLOCK_BYTES) % 16) continue;
+    if (down_smem(TI, nff, sh_ff, n_used) <= 200 * 1024) return TI;
+  }
+  return 0;
+}
+
+template <typename K, typename... Args>
+cudaError_t launch_ex(K kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+}  // namespace
+
+bool decode_ffn_supported(const infr_cuda_ctx*, int ne, int nff, int sh_ff, int n_used, std::string* why) {
+  if (ne % 256 || nff % 256 || (sh_ff % 256)) {
+    if (why) *why = "small-m path: ne, n_ff_exp and sh_ff must be multiples of 256";
+    return false;
+  }
+  if (ne / 64 > 32 * 4) {
+    if (why) *why = "small-m path: ne larger than 8192 is not covered";
+    return false;
+  }
+  if (n_used + 1 > DN_MAX_SLOTS) {
+    if (why) *why = "small-m path: n_used larger than 32 is not covered";
+    return false;
+  }
+  if (!pick_chunks(ne, nff, sh_ff) || !pick_down_tile(ne, nff, sh_ff, n_used)) {
+    if (why) *why = "small-m path: tile does not fit shared memory for these dims";
+    return false;
+  }
+  return true;
+}
+
+int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl) {
+  const bool has_sh = p.sh_gate != nullptr;
+  const int sh_ff = has_sh ? p.sh_ff : 0;
+  const int n_chunks = pick_chunks(p.ne, p.nff, sh_ff);
+  const int TI = pick_down_tile(p.ne, p.nff, sh_ff, p.n_used);
+  if (!n_chunks || !TI) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "small-m path: tile does not fit shared memory");
+  const int TR = 8 * n_chunks;
+  const int jobs = p.rows * p.n_used * (p.nff / TR) + (has_sh ? p.rows * (sh_ff / TR) : 0);
+  const size_t smem_gu = gateup_smem(p.ne, n_chunks);
+  const int ng = (p.ne / 64 + 31) / 32;
+  cudaError_t e;
+  auto run_gu = [&](auto kern) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gu);
+    if (e != cudaSuccess) return e;
+    return launch_ex(kern, dim3(jobs), dim3(GU_THREADS), smem_gu, ctx->stream, pdl, p, n_chunks);
+  };
+  if (ng == 1)
+    e = run_gu(k_decode_gateup<1>);
+  else if (ng == 2)
+    e = run_gu(k_decode_gateup<2>);
+  else
+    e = run_gu(k_decode_gateup<4>);
+  ctx->launches += 1;
+  if (e != cudaSuccess) return check_cuda(ctx, e, "k_decode_gateup launch");
+
+  const size_t smem_dn = down_smem(TI, p.nff, sh_ff, p.n_used);
+  e = cudaFuncSetAttribute(k_decode_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dn);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "k_decode_down smem attribute");
+  e = launch_ex(k_decode_down, dim3(p.rows * (p.ne / TI)), dim3(DN_THREADS), smem_dn, ctx->stream, pdl, p, TI);
+  ctx->launches += 1;
+  return check_cuda(ctx, e, "k_decode_down launch");
+}
+
+}  // namespace infr

@@ -1,0 +1,55 @@
+// Kernel parameter blocks and host-side launchers (one translation unit per kernel family).
+#pragma once
+#include "common.cuh"
+
+namespace infr {
+
+// Calls with at most this many rows run the whole-row router kernel with the fused top-k.
+constexpr int ROUTE_SMALL_MAX_ROWS = 8;
+
+struct RouteParams {
+  const float* router_x;     // [rows, ne]
+  const float* x;            // [rows, ne] (shared-expert gate input)
+  const float* router;       // [n_expert, ne] f32
+  const float* sh_gate_inp;  // [ne] or null
+  const float* bias;         // [n_expert] or null
+  float* logits;             // [rows, n_expert] scratch
+  float* sh_logit;           // [rows] scratch
+  int32_t* ids;              // [rows, n_used]
+  float* wts;                // [rows, n_used]
+  unsigned int* counter;     // zero on entry, zero on exit
+  int rows, ne, n_expert, n_used;
+  float scale;
+  int gating, norm_w, n_groups, n_groups_used;
+};
+
+struct DecodeParams {
+  const float* x;        // [rows, ne]
+  const int32_t* ids;    // [rows, n_used]
+  const float* wts;      // [rows, n_used]
+  const float* sh_logit; // [rows] or null (ungated shared expert)
+  const uint8_t *gate, *up, *down;           // routed banks
+  const uint8_t *sh_gate, *sh_up, *sh_down;  // shared expert or null
+  float* act;            // [rows*n_used, nff] then [rows, sh_ff]
+  float* dst;            // [rows, ne]
+  DeviceStatus* status;
+  size_t gate_stride, up_stride, down_stride;  // bytes per expert
+  int rows, ne, n_used, nff, sh_ff, n_expert;
+  uint32_t ep_lo, ep_n;  // band (ep_n == 0: off)
+};
+
+int32_t launch_route(infr_cuda_ctx* ctx, const RouteParams& p, bool pdl);
+int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl);
+// Whether the small-m kernels cover this shape (dims, shared-memory budget).
+bool decode_ffn_supported(const infr_cuda_ctx* ctx, int ne, int nff, int sh_ff, int n_used, std::string* why);
+
+// y[m, out_f] = x[m, in_f] · Wᵀ for W of dtype F32 / Q4_K / Q6_K.
+int32_t launch_linear(infr_cuda_ctx* ctx, int32_t dtype, const uint8_t* w, const float* x, float* y, int m, int in_f,
+                      int out_f);
+int32_t launch_gated_act(infr_cuda_ctx* ctx, const float* gate, const float* up, float* dst, size_t n);
+int32_t launch_shared_add(infr_cuda_ctx* ctx, const float* moe, const float* shexp, const float* gate, float* dst,
+                          int rows, int n);
+int32_t launch_rmsnorm(infr_cuda_ctx* ctx, const float* x, const float* w, float* dst, int rows, int dim, float eps);
+int32_t launch_add(infr_cuda_ctx* ctx, const float* a, const float* b, float* dst, size_t n);
+
+}  // namespace infr

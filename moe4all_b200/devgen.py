@@ -1,0 +1,63 @@
+"""Synthetic layer weights generated directly in device memory (torch is used for the random
+streams and the allocation only).  Same distributions as synth.make_layer: random block payload,
+f16 scales ~ U[1e-4, 1e-3], router ~ N(0, 0.02)."""
+from __future__ import annotations
+
+import torch
+
+
+def _scales(n, gen, device):
+    return (torch.rand(n, generator=gen, device=device) * 9e-4 + 1e-4).to(torch.float16).view(torch.uint8).reshape(n, 2)
+
+
+def q4k_bank(n_blocks: int, gen, device) -> torch.Tensor:
+    t = torch.randint(0, 256, (n_blocks, 144), dtype=torch.uint8, generator=gen, device=device)
+    t[:, 0:2] = _scales(n_blocks, gen, device)
+    t[:, 2:4] = _scales(n_blocks, gen, device)
+    return t.reshape(-1)
+
+
+def q6k_bank(n_blocks: int, gen, device) -> torch.Tensor:
+    t = torch.randint(0, 256, (n_blocks, 210), dtype=torch.uint8, generator=gen, device=device)
+    t[:, 208:210] = _scales(n_blocks, gen, device)
+    return t.reshape(-1)
+
+
+class DeviceLayer:
+    """One MoE layer's tensors as torch CUDA tensors plus Buffer handles on them."""
+
+    def __init__(self, be, seed, ne, n_expert, n_ff, sh_ff=0, gated_shared=True, device="cuda:0", router_std=0.02):
+        gen = torch.Generator(device=device)
+        gen.manual_seed(seed)
+        self.ne, self.n_expert, self.n_ff, self.sh_ff = ne, n_expert, n_ff, sh_ff
+        self.t = {}
+        self.t["router"] = torch.randn(n_expert, ne, generator=gen, device=device) * router_std
+        self.t["gate"] = q4k_bank(n_expert * n_ff * ne // 256, gen, device)
+        self.t["up"] = q4k_bank(n_expert * n_ff * ne // 256, gen, device)
+        self.t["down"] = q6k_bank(n_expert * ne * n_ff // 256, gen, device)
+        if sh_ff:
+            self.t["sh_gate"] = q4k_bank(sh_ff * ne // 256, gen, device)
+            self.t["sh_up"] = q4k_bank(sh_ff * ne // 256, gen, device)
+            self.t["sh_down"] = q6k_bank(ne * sh_ff // 256, gen, device)
+            if gated_shared:
+                self.t["sh_gate_inp"] = torch.randn(ne, generator=gen, device=device) * router_std
+        # 16 spare bytes after each bank: block decoders may read a word pair at the very end
+        for k in list(self.t):
+            v = self.t[k]
+            padded = torch.empty(v.numel() * v.element_size() + 16, dtype=torch.uint8, device=device)
+            padded[: v.numel() * v.element_size()] = v.reshape(-1).view(torch.uint8)
+            self.t[k] = padded
+        self.b = {k: be.wrap(v.data_ptr(), v.numel() - 16) for k, v in self.t.items()}
+
+    def host(self):
+        """synth.LayerWeights with the same bytes (for the CPU oracle)."""
+        from .synth import LayerWeights
+        import numpy as np
+        L = LayerWeights(self.ne, self.n_expert, self.n_ff, self.sh_ff, "sh_gate_inp" in self.t)
+        get = lambda k: self.t[k][:-16].cpu().numpy() if k in self.t else None
+        L.router = get("router").view(np.float32).reshape(self.n_expert, self.ne)
+        L.gate, L.up, L.down = get("gate"), get("up"), get("down")
+        L.sh_gate, L.sh_up, L.sh_down = get("sh_gate"), get("sh_up"), get("sh_down")
+        gi = get("sh_gate_inp")
+        L.sh_gate_inp = gi.view(np.float32) if gi is not None else None
+        return L

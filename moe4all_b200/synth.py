@@ -1,0 +1,104 @@
+"""Seeded synthetic inputs in the shapes and value distributions of the benchmark configs.
+
+Block generators write valid GGUF Q4_K / Q6_K super-blocks: every payload bit pattern decodes to
+a finite value, only the f16 scale slots need sane magnitudes.  Two families:
+  * `random_q4k` / `random_q6k`: random payload, f16 d (and dmin) drawn from U[1e-4, 1e-3]
+    (the benchmark configs);
+  * `testkit_weight`: the reference's own synthesis recipe, an LCG byte stream per block with the
+    scale slots overwritten (crates/infr-testkit/src/lib.rs:49-56, 70-123).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+Q4K_BYTES, Q6K_BYTES, QK = 144, 210, 256
+
+
+def _f16_bytes(vals: np.ndarray) -> np.ndarray:
+    return vals.astype(np.float16).view(np.uint8).reshape(-1, 2)
+
+
+def random_q4k(rng: np.random.Generator, n_blocks: int, lo: float = 1e-4, hi: float = 1e-3) -> np.ndarray:
+    """[n_blocks, 144] u8: f16 d, f16 dmin ~ U[lo, hi]; 12 random scale bytes; 128 random nibble bytes."""
+    blk = rng.integers(0, 256, size=(n_blocks, Q4K_BYTES), dtype=np.uint8)
+    blk[:, 0:2] = _f16_bytes(rng.uniform(lo, hi, n_blocks))
+    blk[:, 2:4] = _f16_bytes(rng.uniform(lo, hi, n_blocks))
+    return blk
+
+
+def random_q6k(rng: np.random.Generator, n_blocks: int, lo: float = 1e-4, hi: float = 1e-3) -> np.ndarray:
+    """[n_blocks, 210] u8: random ql/qh/int8 scales; f16 d ~ U[lo, hi] at byte 208."""
+    blk = rng.integers(0, 256, size=(n_blocks, Q6K_BYTES), dtype=np.uint8)
+    blk[:, 208:210] = _f16_bytes(rng.uniform(lo, hi, n_blocks))
+    return blk
+
+
+def lcg_bytes(seed: int, n: int) -> np.ndarray:
+    """crates/infr-testkit/src/lib.rs:49-56: seed = seed*1664525 + 1013904223 (mod 2^32); byte = seed >> 16."""
+    out = np.empty(n, dtype=np.uint8)
+    s = seed & 0xFFFFFFFF
+    for i in range(n):
+        s = (s * 1664525 + 1013904223) & 0xFFFFFFFF
+        out[i] = (s >> 16) & 0xFF
+    return out
+
+
+def gen_f32(n: int, salt: int) -> np.ndarray:
+    """crates/infr-testkit/src/lib.rs:60-64 (and seam_op_parity.rs:257-261): (((i*13+salt) % 29) - 14) * 0.05."""
+    i = np.arange(n, dtype=np.int64)
+    return ((((i * 13 + salt) % 29).astype(np.float32) - np.float32(14.0)) * np.float32(0.05)).astype(np.float32)
+
+
+def testkit_weight(dtype_name: str, n_elem: int, seed: int) -> np.ndarray:
+    """crates/infr-testkit/src/lib.rs:106-123 for Q4_K (d 0.05, dmin 0.10) and Q6_K (d 0.03)."""
+    assert n_elem % QK == 0
+    nblk = n_elem // QK
+    if dtype_name == "Q4K":
+        out = np.empty((nblk, Q4K_BYTES), np.uint8)
+        for b in range(nblk):
+            out[b] = lcg_bytes(seed ^ b, Q4K_BYTES)
+        out[:, 0:2] = _f16_bytes(np.full(nblk, 0.05))
+        out[:, 2:4] = _f16_bytes(np.full(nblk, 0.10))
+    elif dtype_name == "Q6K":
+        out = np.empty((nblk, Q6K_BYTES), np.uint8)
+        for b in range(nblk):
+            out[b] = lcg_bytes(seed ^ b, Q6K_BYTES)
+        out[:, 208:210] = _f16_bytes(np.full(nblk, 0.03))
+    else:
+        raise ValueError(dtype_name)
+    return out
+
+
+class LayerWeights:
+    """Host copies of one MoE layer's tensors (raw GGUF bytes + f32 router)."""
+
+    def __init__(self, ne, n_expert, n_ff, sh_ff=0, gated_shared=True):
+        self.ne, self.n_expert, self.n_ff, self.sh_ff, self.gated_shared = ne, n_expert, n_ff, sh_ff, gated_shared
+        self.router = self.gate = self.up = self.down = None
+        self.sh_gate = self.sh_up = self.sh_down = self.sh_gate_inp = None
+        self.bias = None
+
+
+def make_layer(seed: int, ne: int, n_expert: int, n_ff: int, sh_ff: int = 0, gated_shared: bool = True,
+               router_std: float = 0.02, bias_std: float = 0.0) -> LayerWeights:
+    """One layer in the benchmark configs' distributions: router f32 N(0, 0.02); gate/up Q4_K and
+    down Q6_K with random payload and U[1e-4, 1e-3] scales; optional shared expert."""
+    rng = np.random.default_rng(seed)
+    L = LayerWeights(ne, n_expert, n_ff, sh_ff, gated_shared)
+    L.router = rng.normal(0.0, router_std, size=(n_expert, ne)).astype(np.float32)
+    L.gate = random_q4k(rng, n_expert * n_ff * ne // QK).reshape(-1)
+    L.up = random_q4k(rng, n_expert * n_ff * ne // QK).reshape(-1)
+    L.down = random_q6k(rng, n_expert * ne * n_ff // QK).reshape(-1)
+    if sh_ff:
+        L.sh_gate = random_q4k(rng, sh_ff * ne // QK).reshape(-1)
+        L.sh_up = random_q4k(rng, sh_ff * ne // QK).reshape(-1)
+        L.sh_down = random_q6k(rng, ne * sh_ff // QK).reshape(-1)
+        if gated_shared:
+            L.sh_gate_inp = rng.normal(0.0, router_std, size=ne).astype(np.float32)
+    if bias_std > 0:
+        L.bias = rng.normal(0.0, bias_std, size=n_expert).astype(np.float32)
+    return L
+
+
+def activations(seed: int, rows: int, ne: int) -> np.ndarray:
+    return np.random.default_rng(seed).normal(0.0, 1.0, size=(rows, ne)).astype(np.float32)

@@ -1,0 +1,517 @@
+// CPU oracle for the quantized mixture-of-experts FFN hot path.
+//
+// TEST INFRASTRUCTURE ONLY.  This file restates, in plain C++, the f32 "reference mode"
+// arithmetic of MoE4All's CPU interpreter (crates/infr-cpu) so that the CUDA library can be
+// checked against it and so that the CPU path can be timed beside the GPU one.  Nothing in the
+// product library links, loads or calls it; only the test-suite, the smoke check and the
+// benchmark's CPU-baseline leg do.
+//
+// Parity is pinned by the reference's own known-answer material (see tests/test_oracle_*.py):
+// the patterned Q4_K / Q6_K blocks of crates/infr-gguf/src/dequant.rs:1174-1202, the routing
+// vectors of crates/infr-llama/tests/seam_op_parity.rs:2352-2554 and the hand-written layer
+// reference `moe_ref` at :2245-2343, all re-created from their formulas.
+//
+// Arithmetic rules the reference follows and this file keeps (Rust never contracts a*b+c):
+//   * fused multiply-add ONLY where the reference calls `mul_add` (inside `dot`);
+//   * every other a*b+c is a rounded multiply followed by a rounded add  → build with
+//     -ffp-contract=off;
+//   * `iter().sum::<f32>()` is a left-to-right fold starting at 0; `sort_by` is stable;
+//   * expf / logf / sqrtf are libm's.
+//
+// Build: see oracle/Makefile (g++ -O2 -mavx2 -mfma -ffp-contract=off -shared -fPIC).
+
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <functional>
+#include <limits>
+#include <numeric>
+#include <thread>
+#include <vector>
+
+#if defined(__AVX2__) && defined(__FMA__)
+#include <immintrin.h>
+#define ORC_AVX2 1
+#endif
+
+namespace {
+
+// dtype ids follow the public GGUF/ggml numbering.
+enum : int { DT_F32 = 0, DT_Q4K = 12, DT_Q6K = 14 };
+
+// IEEE binary16 → binary32, exact (what `half::f16::to_f32` does; dequant.rs:72-74).
+inline float f16_to_f32(uint16_t h) {
+  uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1Fu;
+  uint32_t man = h & 0x3FFu;
+  uint32_t bits;
+  if (exp == 0) {
+    if (man == 0) {
+      bits = sign;
+    } else {  // subnormal: renormalise
+      int e = -1;
+      do {
+        man <<= 1;
+        ++e;
+      } while ((man & 0x400u) == 0);
+      man &= 0x3FFu;
+      bits = sign | ((uint32_t)(127 - 15 - e) << 23) | (man << 13);
+    }
+  } else if (exp == 31) {
+    bits = sign | 0x7F800000u | (man << 13);
+  } else {
+    bits = sign | ((exp + 127 - 15) << 23) | (man << 13);
+  }
+  float f;
+  std::memcpy(&f, &bits, 4);
+  return f;
+}
+
+inline uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+
+// 6-bit (scale, min) of sub-block j of a Q4_K block (dequant.rs:77-87).
+inline void k4(int j, const uint8_t* q, uint32_t& sc, uint32_t& m) {
+  if (j < 4) {
+    sc = q[j] & 63u;
+    m = q[j + 4] & 63u;
+  } else {
+    sc = (uint32_t)((q[j + 4] & 0x0F) | ((q[j - 4] >> 6) << 4));
+    m = (uint32_t)((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+  }
+}
+
+// One Q4_K super-block (144 B → 256 f32).  Factored form dequant.rs:315-335, expansion
+// dequant.rs:35-51: per 16-element group  sc = f32(d)*scm ; mn = f32(dmin)*(-m) ;
+// out = sc*code + mn  (multiply, then add; no fma).
+void dequant_q4k_block(const uint8_t* blk, float* out) {
+  const float d = f16_to_f32(rd16(blk));
+  const float dmin = f16_to_f32(rd16(blk + 2));
+  const uint8_t* scales = blk + 4;
+  const uint8_t* qs = blk + 16;
+  for (int j = 0; j < 4; ++j) {
+    uint32_t sc1, m1, sc2, m2;
+    k4(2 * j, scales, sc1, m1);
+    k4(2 * j + 1, scales, sc2, m2);
+    const float s1 = d * (float)(int16_t)sc1;
+    const float n1 = dmin * (float)(int16_t)(-(int)m1);
+    const float s2 = d * (float)(int16_t)sc2;
+    const float n2 = dmin * (float)(int16_t)(-(int)m2);
+    for (int l = 0; l < 32; ++l) {
+      const uint8_t v = qs[j * 32 + l];
+      out[j * 64 + l] = s1 * (float)(v & 0xF) + n1;
+      out[j * 64 + 32 + l] = s2 * (float)(v >> 4) + n2;
+    }
+  }
+}
+
+// One Q6_K super-block (210 B → 256 f32).  dequant.rs:365-389: per 16-element group
+// sc = f32(d)*s ; mn = f32(d)*(-32*s) ; out = sc*code + mn.
+void dequant_q6k_block(const uint8_t* blk, float* out) {
+  const uint8_t* ql = blk;
+  const uint8_t* qh = blk + 128;
+  const int8_t* scales = (const int8_t*)(blk + 192);
+  const float d = f16_to_f32(rd16(blk + 208));
+  float sc[16], mn[16];
+  for (int g = 0; g < 16; ++g) {
+    const int16_t s = (int16_t)scales[g];
+    sc[g] = d * (float)s;
+    mn[g] = d * (float)(int16_t)(-32 * s);
+  }
+  for (int half = 0; half < 2; ++half) {
+    const int qlo = half * 64, qho = half * 32, base = half * 128;
+    for (int l = 0; l < 32; ++l) {
+      const uint8_t c0 = (uint8_t)((ql[qlo + l] & 0xF) | ((qh[qho + l] & 3) << 4));
+      const uint8_t c1 = (uint8_t)((ql[qlo + l + 32] & 0xF) | (((qh[qho + l] >> 2) & 3) << 4));
+      const uint8_t c2 = (uint8_t)((ql[qlo + l] >> 4) | (((qh[qho + l] >> 4) & 3) << 4));
+      const uint8_t c3 = (uint8_t)((ql[qlo + l + 32] >> 4) | (((qh[qho + l] >> 6) & 3) << 4));
+      const int e0 = base + l, e1 = base + l + 32, e2 = base + l + 64, e3 = base + l + 96;
+      out[e0] = sc[e0 / 16] * (float)c0 + mn[e0 / 16];
+      out[e1] = sc[e1 / 16] * (float)c1 + mn[e1 / 16];
+      out[e2] = sc[e2 / 16] * (float)c2 + mn[e2 / 16];
+      out[e3] = sc[e3 / 16] * (float)c3 + mn[e3 / 16];
+    }
+  }
+}
+
+size_t row_bytes(int dtype, size_t n_elem) {
+  switch (dtype) {
+    case DT_F32: return n_elem * 4;
+    case DT_Q4K: return n_elem / 256 * 144;
+    case DT_Q6K: return n_elem / 256 * 210;
+    default: return 0;
+  }
+}
+
+// `bytes_to_f32(row, dt)` of the reference (infr-cpu/src/lib.rs:513-527): a weight row → f32.
+bool dequant_row(int dtype, const uint8_t* bytes, size_t n_elem, float* out) {
+  switch (dtype) {
+    case DT_F32:
+      std::memcpy(out, bytes, n_elem * 4);
+      return true;
+    case DT_Q4K:
+      if (n_elem % 256) return false;
+      for (size_t b = 0; b < n_elem / 256; ++b) dequant_q4k_block(bytes + b * 144, out + b * 256);
+      return true;
+    case DT_Q6K:
+      if (n_elem % 256) return false;
+      for (size_t b = 0; b < n_elem / 256; ++b) dequant_q6k_block(bytes + b * 210, out + b * 256);
+      return true;
+    default:
+      return false;
+  }
+}
+
+// `dot` of the reference, scalar form (infr-cpu/src/kernels.rs:6568-6583): eight accumulation
+// lanes, lane j takes elements 8c+j by fma; lanes summed left to right; tail by fma.
+float dot_scalar(const float* a, const float* b, size_t n) {
+  const size_t chunks = n / 8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (size_t c = 0; c < chunks; ++c)
+    for (int j = 0; j < 8; ++j) acc[j] = std::fmaf(a[c * 8 + j], b[c * 8 + j], acc[j]);
+  float s = 0.0f;
+  for (int j = 0; j < 8; ++j) s = s + acc[j];
+  for (size_t i = chunks * 8; i < n; ++i) s = std::fmaf(a[i], b[i], s);
+  return s;
+}
+
+#ifdef ORC_AVX2
+// AVX2 form (kernels.rs:6587-6608): one 8-wide fmadd per chunk, same lanes, same final order.
+float dot_avx2(const float* a, const float* b, size_t n) {
+  __m256 sum = _mm256_setzero_ps();
+  size_t i = 0;
+  for (; i + 8 <= n; i += 8)
+    sum = _mm256_fmadd_ps(_mm256_loadu_ps(a + i), _mm256_loadu_ps(b + i), sum);
+  float lanes[8];
+  _mm256_storeu_ps(lanes, sum);
+  float s = 0.0f;
+  for (int j = 0; j < 8; ++j) s = s + lanes[j];
+  for (; i < n; ++i) s = std::fmaf(a[i], b[i], s);
+  return s;
+}
+inline float dot(const float* a, const float* b, size_t n) { return dot_avx2(a, b, n); }
+#else
+inline float dot(const float* a, const float* b, size_t n) { return dot_scalar(a, b, n); }
+#endif
+
+inline float silu(float g) { return g / (1.0f + std::exp(-g)); }       // kernels.rs:6666
+inline float sigmoidf(float v) { return 1.0f / (1.0f + std::exp(-v)); }  // kernels.rs:6670
+
+// Run fn(i) for i in [0,n) on `threads` host threads, items claimed dynamically (the reference
+// claims 64-row chunks from a shared counter the same way, infr-cpu/src/lib.rs:3992-4003).
+void parallel_for(size_t n, int threads, const std::function<void(size_t)>& fn) {
+  if (threads <= 1 || n <= 1) {
+    for (size_t i = 0; i < n; ++i) fn(i);
+    return;
+  }
+  std::atomic<size_t> next{0};
+  auto work = [&]() {
+    for (;;) {
+      size_t i = next.fetch_add(1);
+      if (i >= n) break;
+      fn(i);
+    }
+  };
+  std::vector<std::thread> pool;
+  int nt = (int)std::min<size_t>((size_t)threads, n);
+  for (int t = 1; t < nt; ++t) pool.emplace_back(work);
+  work();
+  for (auto& t : pool) t.join();
+}
+
+}  // namespace
+
+extern "C" {
+
+// Descriptor of one Op::MoeFfn call (crates/infr-core/src/graph.rs:1259-1352), restricted to the
+// forms on the hot path: split gate/up, SiLU, output-side weighting, no down_scale, no hash ids.
+struct orc_moe_desc {
+  const float* x;         // [rows, ne]
+  const float* router_x;  // [rows, ne]
+  const uint8_t* router;  // [n_expert, ne] router_dtype
+  const uint8_t* gate_exps;  // [n_expert, n_ff_exp, ne]
+  const uint8_t* up_exps;    // [n_expert, n_ff_exp, ne]
+  const uint8_t* down_exps;  // [n_expert, ne, n_ff_exp]
+  const float* exp_probs_b;  // [n_expert] or null
+  float* dst;                // [rows, ne]
+  int32_t* ids_out;          // [rows, n_used] or null
+  float* wts_out;            // [rows, n_used] or null
+  float* logits_out;         // [rows, n_expert] or null
+  float* sel_out;            // [rows, n_expert] or null: the selection scores after bias/groups
+  uint32_t rows, ne, n_expert, n_used, n_ff_exp;
+  float scale;
+  int32_t router_dtype, gate_dtype, up_dtype, down_dtype;
+  uint32_t gating;  // 0 softmax, 1 sigmoid, 2 sqrt-softplus
+  uint32_t norm_w;
+  uint32_t n_expert_groups, n_expert_groups_used;
+  uint32_t ep_lo, ep_n_local;  // band [ep_lo, ep_lo+ep_n_local); ep_n_local == 0 → no band
+  int32_t threads;
+};
+
+int orc_has_avx2(void) {
+#ifdef ORC_AVX2
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+int orc_hw_threads(void) {
+  unsigned n = std::thread::hardware_concurrency();
+  return n ? (int)n : 1;
+}
+
+size_t orc_row_bytes(int dtype, size_t n_elem) { return row_bytes(dtype, n_elem); }
+
+int orc_dequant(int dtype, const uint8_t* bytes, size_t n_elem, float* out) {
+  return dequant_row(dtype, bytes, n_elem, out) ? 0 : -1;
+}
+
+float orc_dot(const float* a, const float* b, size_t n) { return dot(a, b, n); }
+float orc_dot_scalar(const float* a, const float* b, size_t n) { return dot_scalar(a, b, n); }
+
+// Routing of one row (infr-cpu/src/lib.rs:3741-3863).  logits → probs → selection copy (+bias,
+// group mask) → stable descending sort → first n_used; weights from the UNBIASED probs.
+static void route_row(const orc_moe_desc* d, const float* logits, int32_t* idx_out, float* w_out,
+                      float* sel_out) {
+  const uint32_t E = d->n_expert, k = d->n_used;
+  std::vector<float> probs(E);
+  if (d->gating == 0) {
+    float maxl = -std::numeric_limits<float>::infinity();
+    for (uint32_t e = 0; e < E; ++e) maxl = std::max(maxl, logits[e]);  // f32::max fold
+    for (uint32_t e = 0; e < E; ++e) probs[e] = std::exp(logits[e] - maxl);
+    float psum = 0.0f;
+    for (uint32_t e = 0; e < E; ++e) psum = psum + probs[e];
+    for (uint32_t e = 0; e < E; ++e) probs[e] = probs[e] / psum;
+  } else if (d->gating == 1) {
+    for (uint32_t e = 0; e < E; ++e) probs[e] = 1.0f / (1.0f + std::exp(-logits[e]));
+  } else {
+    for (uint32_t e = 0; e < E; ++e) {
+      const float v = logits[e];
+      const float sp = v > 20.0f ? v : std::log(1.0f + std::exp(v));
+      probs[e] = std::sqrt(sp);
+    }
+  }
+  std::vector<float> sel(probs);
+  if (d->exp_probs_b)
+    for (uint32_t e = 0; e < E; ++e) sel[e] = probs[e] + d->exp_probs_b[e];
+  if (d->n_expert_groups > 1 && d->n_expert_groups_used > 0) {
+    const uint32_t ng = d->n_expert_groups, per = E / ng, used = d->n_expert_groups_used;
+    const float ninf = -std::numeric_limits<float>::infinity();
+    std::vector<float> gs(ng, ninf);
+    for (uint32_t g = 0; g < ng; ++g) {
+      float best0 = ninf, best1 = ninf;
+      for (uint32_t i = 0; i < per; ++i) {
+        const float s = sel[g * per + i];
+        if (s > best0) {
+          best1 = best0;
+          best0 = s;
+        } else if (s > best1) {
+          best1 = s;
+        }
+      }
+      gs[g] = best0 + best1;
+    }
+    std::vector<uint32_t> gidx(ng);
+    std::iota(gidx.begin(), gidx.end(), 0u);
+    std::stable_sort(gidx.begin(), gidx.end(), [&](uint32_t a, uint32_t b) { return gs[a] > gs[b]; });
+    std::vector<char> chosen(ng, 0);
+    for (uint32_t i = 0; i < std::min(used, ng); ++i) chosen[gidx[i]] = 1;
+    for (uint32_t g = 0; g < ng; ++g)
+      if (!chosen[g])
+        for (uint32_t i = 0; i < per; ++i) sel[g * per + i] = ninf;
+  }
+  std::vector<uint32_t> idx(E);
+  std::iota(idx.begin(), idx.end(), 0u);
+  std::stable_sort(idx.begin(), idx.end(), [&](uint32_t a, uint32_t b) { return sel[a] > sel[b]; });
+  if (d->norm_w) {
+    float ws = 0.0f;
+    for (uint32_t s = 0; s < k; ++s) ws = ws + probs[idx[s]];
+    ws = std::max(ws, 1e-20f);
+    for (uint32_t s = 0; s < k; ++s) w_out[s] = probs[idx[s]] / ws * d->scale;
+  } else {
+    for (uint32_t s = 0; s < k; ++s) w_out[s] = probs[idx[s]] * d->scale;
+  }
+  for (uint32_t s = 0; s < k; ++s) idx_out[s] = (int32_t)idx[s];
+  if (sel_out) std::memcpy(sel_out, sel.data(), E * sizeof(float));
+}
+
+// Op::MoeFfn in reference mode (infr-cpu/src/lib.rs:3584-4304 with every bank on the f32
+// activation path, :3675-3679; expert mat-vec = dequantised row + `dot`, moe.rs:142-173).
+// Work is bucketed by expert like stages A-E of the reference; bucketing only reorders work, each
+// output element sees the same operations in the same order as the per-row form.
+int orc_moe_ffn(const orc_moe_desc* d) {
+  const size_t R = d->rows, ne = d->ne, E = d->n_expert, k = d->n_used, nff = d->n_ff_exp;
+  if (!R || !ne || !E || !k || !nff || k > E) return -1;
+  const size_t rrb = row_bytes(d->router_dtype, ne), grb = row_bytes(d->gate_dtype, ne),
+               urb = row_bytes(d->up_dtype, ne), drb = row_bytes(d->down_dtype, nff);
+  if (!rrb || !grb || !urb || !drb) return -2;
+  const int T = d->threads > 0 ? d->threads : orc_hw_threads();
+
+  // Router logits: logits[r,e] = dot(router_row_e, router_x[r])  (lib.rs:3684-3716).
+  std::vector<float> logits(R * E);
+  parallel_for(E, T, [&](size_t e) {
+    std::vector<float> wf(ne);
+    dequant_row(d->router_dtype, d->router + e * rrb, ne, wf.data());
+    for (size_t r = 0; r < R; ++r) logits[r * E + e] = dot(wf.data(), d->router_x + r * ne, ne);
+  });
+  if (d->logits_out) std::memcpy(d->logits_out, logits.data(), R * E * sizeof(float));
+
+  std::vector<int32_t> ids(R * k);
+  std::vector<float> wts(R * k);
+  parallel_for(R, T, [&](size_t r) {
+    route_row(d, &logits[r * E], &ids[r * k], &wts[r * k], d->sel_out ? d->sel_out + r * E : nullptr);
+  });
+  if (d->ids_out) std::memcpy(d->ids_out, ids.data(), R * k * sizeof(int32_t));
+  if (d->wts_out) std::memcpy(d->wts_out, wts.data(), R * k * sizeof(float));
+
+  // Bucket the (row, rank) pairs by expert (lib.rs:3873-3907).  An expert outside the EP band
+  // contributes nothing (graph.rs:1309-1319: out-of-band ids are remapped to weight 0).
+  std::vector<std::vector<uint32_t>> bucket(E);
+  const bool band = d->ep_n_local != 0;
+  for (size_t p = 0; p < R * k; ++p) {
+    const uint32_t e = (uint32_t)ids[p];
+    if (band && (e < d->ep_lo || e >= d->ep_lo + d->ep_n_local)) continue;
+    bucket[e].push_back((uint32_t)p);
+  }
+  std::vector<uint32_t> active;
+  for (uint32_t e = 0; e < E; ++e)
+    if (!bucket[e].empty()) active.push_back(e);
+
+  const size_t gst = grb * nff, ust = urb * nff, dst_stride = drb * ne;  // bytes per expert
+  std::vector<float> act(R * k * nff, 0.0f), y(R * k * ne, 0.0f);
+
+  // Stages B + C: gate/up mat-vec then act = silu(g)*u  (lib.rs:4051-4212).
+  struct Task { uint32_t e; uint32_t o0; };
+  std::vector<Task> tasks;
+  for (uint32_t e : active)
+    for (uint32_t o0 = 0; o0 < nff; o0 += 64) tasks.push_back({e, o0});
+  parallel_for(tasks.size(), T, [&](size_t ti) {
+    const Task t = tasks[ti];
+    std::vector<float> wg(ne), wu(ne);
+    const size_t o1 = std::min<size_t>(t.o0 + 64, nff);
+    for (size_t o = t.o0; o < o1; ++o) {
+      dequant_row(d->gate_dtype, d->gate_exps + t.e * gst + o * grb, ne, wg.data());
+      dequant_row(d->up_dtype, d->up_exps + t.e * ust + o * urb, ne, wu.data());
+      for (uint32_t p : bucket[t.e]) {
+        const float* xr = d->x + (size_t)(p / k) * ne;
+        const float g = dot(wg.data(), xr, ne);
+        const float u = dot(wu.data(), xr, ne);
+        act[(size_t)p * nff + o] = silu(g) * u;
+      }
+    }
+  });
+
+  // Stage D: down mat-vec (lib.rs:4214-4266).
+  tasks.clear();
+  for (uint32_t e : active)
+    for (uint32_t o0 = 0; o0 < ne; o0 += 64) tasks.push_back({e, o0});
+  parallel_for(tasks.size(), T, [&](size_t ti) {
+    const Task t = tasks[ti];
+    std::vector<float> wd(nff);
+    const size_t o1 = std::min<size_t>(t.o0 + 64, ne);
+    for (size_t o = t.o0; o < o1; ++o) {
+      dequant_row(d->down_dtype, d->down_exps + t.e * dst_stride + o * drb, nff, wd.data());
+      for (uint32_t p : bucket[t.e]) y[(size_t)p * ne + o] = dot(wd.data(), &act[(size_t)p * nff], nff);
+    }
+  });
+
+  // Stage E: out += w*y in rank order, multiply then add (lib.rs:4287-4303).
+  parallel_for(R, T, [&](size_t r) {
+    float* o = d->dst + r * ne;
+    for (size_t i = 0; i < ne; ++i) o[i] = 0.0f;
+    for (size_t rank = 0; rank < k; ++rank) {
+      const size_t p = r * k + rank;
+      const uint32_t e = (uint32_t)ids[p];
+      if (band && (e < d->ep_lo || e >= d->ep_lo + d->ep_n_local)) continue;
+      const float w = wts[p];
+      const float* yr = &y[p * ne];
+      for (size_t i = 0; i < ne; ++i) o[i] = o[i] + w * yr[i];
+    }
+  });
+  return 0;
+}
+
+// Op::Linear, reference branch (infr-cpu/src/lib.rs:1312-1328; F32 weights :1459, :1752-1754):
+// y[r,o] = dot(dequant(W row o), x[r]).
+int orc_linear(int dtype, const uint8_t* w, const float* x, uint32_t m, uint32_t in_f,
+               uint32_t out_f, float* y, int32_t threads) {
+  const size_t rb = row_bytes(dtype, in_f);
+  if (!rb) return -2;
+  const int T = threads > 0 ? threads : orc_hw_threads();
+  const size_t chunks = (out_f + 63) / 64;
+  parallel_for(chunks, T, [&](size_t c) {
+    std::vector<float> wf(in_f);
+    const size_t o1 = std::min<size_t>((c + 1) * 64, out_f);
+    for (size_t o = c * 64; o < o1; ++o) {
+      dequant_row(dtype, w + o * rb, in_f, wf.data());
+      for (size_t r = 0; r < m; ++r) y[r * out_f + o] = dot(wf.data(), x + r * in_f, in_f);
+    }
+  });
+  return 0;
+}
+
+// Op::GatedAct with SiLU, contiguous operands (lib.rs:2973-3027; kernels.rs:6678-6683).
+void orc_gated_act_silu(const float* gate, const float* up, float* dst, size_t n) {
+  for (size_t i = 0; i < n; ++i) dst[i] = silu(gate[i]) * up[i];
+}
+
+// Op::MoeSharedExpertAdd (lib.rs:3336-3356): dst = moe + sigmoid(gate[r]) * shexp.
+void orc_moe_shared_add(const float* moe, const float* shexp, const float* gate, float* dst,
+                        uint32_t rows, uint32_t n) {
+  for (uint32_t r = 0; r < rows; ++r) {
+    const float g = sigmoidf(gate[r]);
+    for (uint32_t c = 0; c < n; ++c) dst[(size_t)r * n + c] = moe[(size_t)r * n + c] + g * shexp[(size_t)r * n + c];
+  }
+}
+
+// Op::RmsNorm (lib.rs:1046-1069): ss = (Σ→ x²)/dim ; s = 1/sqrt(ss+eps) ; o = x*s*w.
+void orc_rmsnorm(const float* x, const float* w, float* dst, uint32_t rows, uint32_t dim, float eps) {
+  for (uint32_t r = 0; r < rows; ++r) {
+    const float* xr = x + (size_t)r * dim;
+    float ss = 0.0f;
+    for (uint32_t i = 0; i < dim; ++i) ss = ss + xr[i] * xr[i];
+    ss = ss / (float)dim;
+    const float s = 1.0f / std::sqrt(ss + eps);
+    for (uint32_t i = 0; i < dim; ++i) dst[(size_t)r * dim + i] = xr[i] * s * w[i];
+  }
+}
+
+// Op::Add (lib.rs:3055-3070).
+void orc_add(const float* a, const float* b, float* dst, size_t n) {
+  for (size_t i = 0; i < n; ++i) dst[i] = a[i] + b[i];
+}
+
+// The whole qwen35moe / DeepSeek FFN sub-layer as the graph builder emits it
+// (crates/infr-llama/src/seam/runner.rs:7999-8176): MoeFfn, then the shared expert as
+// Linear(gate) / Linear(up) / GatedAct / Linear(down) and MoeSharedExpertAdd (gated) or Add.
+//   sh_gate_inp == null → plain sum (DeepSeek, llama4); else sigmoid-gated (qwen35moe).
+int orc_moe_layer(const orc_moe_desc* d, const uint8_t* sh_gate, const uint8_t* sh_up,
+                  const uint8_t* sh_down, const float* sh_gate_inp, uint32_t sh_ff, float* dst) {
+  const size_t R = d->rows, ne = d->ne;
+  std::vector<float> moe(R * ne);
+  orc_moe_desc dd = *d;
+  dd.dst = moe.data();
+  int rc = orc_moe_ffn(&dd);
+  if (rc) return rc;
+  if (!sh_gate) {
+    std::memcpy(dst, moe.data(), R * ne * sizeof(float));
+    return 0;
+  }
+  std::vector<float> g(R * sh_ff), u(R * sh_ff), a(R * sh_ff), ds(R * ne);
+  if ((rc = orc_linear(d->gate_dtype, sh_gate, d->x, d->rows, d->ne, sh_ff, g.data(), d->threads))) return rc;
+  if ((rc = orc_linear(d->up_dtype, sh_up, d->x, d->rows, d->ne, sh_ff, u.data(), d->threads))) return rc;
+  orc_gated_act_silu(g.data(), u.data(), a.data(), R * sh_ff);
+  if ((rc = orc_linear(d->down_dtype, sh_down, a.data(), d->rows, sh_ff, d->ne, ds.data(), d->threads))) return rc;
+  if (sh_gate_inp) {
+    std::vector<float> gl(R);
+    orc_linear(DT_F32, (const uint8_t*)sh_gate_inp, d->x, d->rows, d->ne, 1, gl.data(), 1);
+    orc_moe_shared_add(moe.data(), ds.data(), gl.data(), dst, d->rows, d->ne);
+  } else {
+    orc_add(moe.data(), ds.data(), dst, R * ne);
+  }
+  return 0;
+}
+
+}  // extern "C"
