@@ -168,10 +168,31 @@ int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_row
                                   uint32_t n_local, uint32_t ne, uint32_t n_ff_exp, int32_t gate_dtype,
                                   int32_t up_dtype, int32_t down_dtype);
 
+/* ---- record once, replay (Backend::compile + the decode replay of the Vulkan backend) ----------- */
+
+/* The reference records a decode step's dispatches once and replays the command buffer per token
+ * (`Capabilities::decode_replay`, crates/infr-core/src/backend.rs:45-236; graph built per forward in
+ * crates/infr-llama/src/seam/runner.rs:12574-12796).  Here the calls issued between begin and end
+ * are captured into a CUDA graph instead of being executed; `infr_cuda_graph_launch` replays them
+ * on the context's stream.  Buffers named by the recorded calls must stay alive and keep their
+ * addresses; new inputs are written into the same buffers before each replay.  Calls that need
+ * to grow the context's scratch memory fail with INVALID_ARG while recording: run the same calls
+ * once un-recorded first. */
+typedef struct infr_cuda_graph infr_cuda_graph;
+int32_t infr_cuda_graph_begin(infr_cuda_ctx* ctx);
+int32_t infr_cuda_graph_end(infr_cuda_ctx* ctx, infr_cuda_graph** out);
+int32_t infr_cuda_graph_launch(infr_cuda_ctx* ctx, infr_cuda_graph* graph);
+void infr_cuda_graph_free(infr_cuda_ctx* ctx, infr_cuda_graph* graph);
+
 /* ---- introspection for the test-suite and the benchmark ---------------------------------------- */
 
 /* Number of kernel launches this context has issued since creation (host-side count). */
 uint64_t infr_cuda_launch_count(const infr_cuda_ctx* ctx);
+/* Attach (or with NULL detach) a 4096-byte device buffer into which the decode kernels write
+ * phase time stamps: pairs of u64 (global timer in ns, SM cycle counter), 16 pairs per kernel in
+ * the order router, gate/up, down.  A profiling aid for latency work; the reference's analogue is
+ * the per-op `[prof-moe]` breakdown of crates/infr-cpu/src/lib.rs:4267-4285. */
+int32_t infr_cuda_set_trace(infr_cuda_ctx* ctx, infr_cuda_buf* buf);
 
 #ifdef __cplusplus
 }

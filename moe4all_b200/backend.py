@@ -28,6 +28,7 @@ EXPORTS = [
     "infr_cuda_sync", "infr_cuda_moe_ffn", "infr_cuda_moe_route", "infr_cuda_linear",
     "infr_cuda_gated_act", "infr_cuda_moe_shared_add", "infr_cuda_rmsnorm", "infr_cuda_add",
     "infr_cuda_moe_expert_rows", "infr_cuda_launch_count",
+    "infr_cuda_graph_begin", "infr_cuda_graph_end", "infr_cuda_graph_launch", "infr_cuda_graph_free", "infr_cuda_set_trace",
 ]
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
@@ -125,6 +126,12 @@ def load_library(path: Optional[str] = None):
     L.infr_cuda_rmsnorm.argtypes = [vp, vp, vp, vp, u32, u32, C.c_float]
     L.infr_cuda_add.argtypes = [vp, vp, vp, vp, sz]
     L.infr_cuda_moe_expert_rows.argtypes = [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, i32, i32, i32]
+    L.infr_cuda_graph_begin.argtypes = [vp]
+    L.infr_cuda_graph_end.argtypes = [vp, C.POINTER(vp)]
+    L.infr_cuda_graph_launch.argtypes = [vp, vp]
+    L.infr_cuda_graph_free.argtypes = [vp, vp]
+    L.infr_cuda_graph_free.restype = None
+    L.infr_cuda_set_trace.argtypes = [vp, vp]
     L.infr_cuda_launch_count.argtypes = [vp]
     L.infr_cuda_launch_count.restype = C.c_uint64
     for name in EXPORTS:
@@ -156,6 +163,24 @@ class Buffer:
     def free(self) -> None:
         if self._h:
             self._be._lib.infr_cuda_free(self._be._ctx, self._h)
+            self._h = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Plan:
+    """`trait Plan` (backend.rs:468-482): a recorded sequence of ops, replayed by `execute`."""
+
+    def __init__(self, backend: "CudaBackend", handle: int):
+        self._be, self._h = backend, handle
+
+    def free(self) -> None:
+        if self._h:
+            self._be._lib.infr_cuda_graph_free(self._be._ctx, self._h)
             self._h = 0
 
     def __del__(self):
@@ -314,8 +339,24 @@ class CudaBackend:
         self.upload(b, a)
         return b
 
+    def set_trace(self, buf: Optional[Buffer]) -> None:
+        self._check(self._lib.infr_cuda_set_trace(self._ctx, _h(buf)))
+
     def launch_count(self) -> int:
         return int(self._lib.infr_cuda_launch_count(self._ctx))
+
+    # -- record once, replay (Backend::compile + decode replay) ----------------------------------
+    def graph_begin(self) -> None:
+        self._check(self._lib.infr_cuda_graph_begin(self._ctx))
+
+    def graph_end(self) -> "Plan":
+        h = C.c_void_p()
+        self._check(self._lib.infr_cuda_graph_end(self._ctx, C.byref(h)))
+        return Plan(self, h.value)
+
+    def execute(self, plan: "Plan") -> None:
+        """`Backend::execute(plan, bindings)` for a recorded plan (backend.rs:908)."""
+        self._check(self._lib.infr_cuda_graph_launch(self._ctx, plan._h))
 
     # -- ops (Backend::execute of a one-op graph) ----------------------------------------------------
     def moe_ffn(self, op: MoeFfn) -> None:

@@ -1,6 +1,8 @@
 // C ABI: context, buffers, descriptor validation and dispatch (see include/infr_cuda.h).
 #include <cstdio>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <new>
 
 #include "kernels.cuh"
@@ -20,6 +22,8 @@ int32_t check_cuda(infr_cuda_ctx* ctx, cudaError_t e, const char* what) {
 
 int32_t ensure_scratch(infr_cuda_ctx* ctx, size_t bytes) {
   if (bytes <= ctx->scratch_bytes) return INFR_CUDA_OK;
+  if (ctx->capturing)
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "scratch would have to grow while recording: run the call once un-recorded first");
   // growing is a synchronising operation: earlier launches may still use the old block
   cudaError_t e = cudaStreamSynchronize(ctx->stream);
   if (e != cudaSuccess) return check_cuda(ctx, e, "scratch grow: sync");
@@ -31,6 +35,20 @@ int32_t ensure_scratch(infr_cuda_ctx* ctx, size_t bytes) {
   if (e != cudaSuccess) return check_cuda(ctx, e, "scratch grow: cudaMalloc");
   ctx->scratch_bytes = want;
   return INFR_CUDA_OK;
+}
+
+cudaError_t ensure_smem(const void* kernel, size_t bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<int, const void*>, size_t> granted;
+  if (bytes <= 48 * 1024) return cudaSuccess;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  size_t& g = granted[{dev, kernel}];
+  if (bytes <= g) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) g = bytes;
+  return e;
 }
 
 namespace {
@@ -209,6 +227,72 @@ int32_t infr_cuda_sync(infr_cuda_ctx* ctx) {
 
 uint64_t infr_cuda_launch_count(const infr_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
+int32_t infr_cuda_set_trace(infr_cuda_ctx* ctx, infr_cuda_buf* buf) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  if (buf && buf->bytes < 4096) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_trace: the buffer must hold 4096 bytes");
+  ctx->trace = buf ? static_cast<unsigned long long*>(buf->ptr) : nullptr;
+  return INFR_CUDA_OK;
+}
+
+int32_t infr_cuda_graph_begin(infr_cuda_ctx* ctx) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  if (ctx->capturing) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "graph_begin: already recording");
+  DeviceGuard g(ctx->device);
+  cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "graph_begin");
+  ctx->capturing = true;
+  ctx->capture_launches = ctx->launches;
+  return INFR_CUDA_OK;
+}
+
+int32_t infr_cuda_graph_end(infr_cuda_ctx* ctx, infr_cuda_graph** out) {
+  if (!ctx || !out) return INFR_CUDA_ERR_INVALID_ARG;
+  *out = nullptr;
+  if (!ctx->capturing) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "graph_end: not recording");
+  DeviceGuard g(ctx->device);
+  ctx->capturing = false;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+  if (e != cudaSuccess || !graph) return check_cuda(ctx, e == cudaSuccess ? cudaErrorUnknown : e, "graph_end");
+  cudaGraphExec_t exec = nullptr;
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  if (e != cudaSuccess) {
+    cudaGraphDestroy(graph);
+    return check_cuda(ctx, e, "graph instantiate");
+  }
+  infr_cuda_graph* gr = new (std::nothrow) infr_cuda_graph();
+  if (!gr) {
+    cudaGraphExecDestroy(exec);
+    cudaGraphDestroy(graph);
+    return fail(ctx, INFR_CUDA_ERR_OOM, "graph_end: host out of memory");
+  }
+  gr->graph = graph;
+  gr->exec = exec;
+  gr->kernels = ctx->launches - ctx->capture_launches;
+  ctx->launches = ctx->capture_launches;  // recorded launches have not run
+  *out = gr;
+  return INFR_CUDA_OK;
+}
+
+int32_t infr_cuda_graph_launch(infr_cuda_ctx* ctx, infr_cuda_graph* graph) {
+  if (!ctx || !graph || !graph->exec) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "graph_launch: null graph");
+  DeviceGuard g(ctx->device);
+  cudaError_t e = cudaGraphLaunch(graph->exec, ctx->stream);
+  if (e == cudaSuccess) ctx->launches += graph->kernels;
+  return check_cuda(ctx, e, "graph_launch");
+}
+
+void infr_cuda_graph_free(infr_cuda_ctx* ctx, infr_cuda_graph* graph) {
+  if (!graph) return;
+  if (ctx) {
+    DeviceGuard g(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+  }
+  if (graph->exec) cudaGraphExecDestroy(graph->exec);
+  if (graph->graph) cudaGraphDestroy(graph->graph);
+  delete graph;
+}
+
 // ---- Op::MoeFfn ---------------------------------------------------------------------------------
 
 static int32_t validate_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
@@ -216,8 +300,8 @@ static int32_t validate_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* 
   if (!d->rows || !d->ne || !d->n_expert || !d->n_used) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: zero dimension");
   if (d->n_used > d->n_expert) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: n_used exceeds n_expert");
   if (d->n_used > 32) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: n_used > 32 is not covered");
-  if (d->n_expert > 4096) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: more than 4096 experts is not covered");
-  if (d->ne % 8) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: ne must be a multiple of 8");
+  if (d->n_expert > 1024) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: more than 1024 experts is not covered");
+  if (d->ne % 64) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: ne must be a multiple of 64");
   if (d->router_dtype != INFR_CUDA_DT_F32) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: router dtype must be F32");
   if (d->gating != INFR_CUDA_GATING_SOFTMAX && d->gating != INFR_CUDA_GATING_SIGMOID)
     return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: gating must be softmax or sigmoid");
@@ -306,6 +390,7 @@ RouteParams route_params(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, co
   rp.ids = d->ids_out ? static_cast<int32_t*>(d->ids_out->ptr) : s.ids;
   rp.wts = d->wts_out ? static_cast<float*>(d->wts_out->ptr) : s.wts;
   rp.counter = ctx->counters;
+  rp.trace = ctx->trace;
   rp.rows = d->rows;
   rp.ne = d->ne;
   rp.n_expert = d->n_expert;
@@ -348,7 +433,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     if ((rc = ensure_scratch(ctx, sz.total))) return rc;
     Scratch s = carve(ctx->scratch, d, true);
     RouteParams rp = route_params(ctx, d, s, true);
-    if ((rc = launch_route(ctx, rp, false))) return rc;
+    if ((rc = launch_route(ctx, rp, true))) return rc;
     DecodeParams dp = {};
     dp.x = static_cast<const float*>(d->x->ptr);
     dp.ids = rp.ids;
@@ -363,6 +448,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.act = s.act;
     dp.dst = static_cast<float*>(d->dst->ptr);
     dp.status = ctx->status;
+    dp.trace = ctx->trace;
     dp.gate_stride = (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
     dp.up_stride = dp.gate_stride;
     dp.down_stride = (size_t)d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
@@ -374,7 +460,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.n_expert = d->n_expert;
     dp.ep_lo = d->ep_lo;
     dp.ep_n = d->ep_n_local;
-    return launch_decode_ffn(ctx, dp, false);
+    return launch_decode_ffn(ctx, dp, true);
   }
   return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: the grouped-GEMM path is not built yet");
 }

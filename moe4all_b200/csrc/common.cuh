@@ -35,6 +35,12 @@ struct infr_cuda_buf {
   bool owned = false;
 };
 
+struct infr_cuda_graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  uint64_t kernels = 0;  // kernel launches one replay stands for
+};
+
 struct infr_cuda_ctx {
   int device = 0;
   int sm_count = 0;
@@ -42,11 +48,14 @@ struct infr_cuda_ctx {
   cudaStream_t stream = nullptr;
   std::string last_error;
   uint64_t launches = 0;
+  bool capturing = false;
+  uint64_t capture_launches = 0;  // launches recorded since graph_begin
   // scratch grown on demand (never inside a launch sequence that could be captured)
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   infr::DeviceStatus* status = nullptr;       // device memory
   unsigned int* counters = nullptr;           // device memory: completion counters (zeroed by users)
+  unsigned long long* trace = nullptr;        // optional phase stamps (see trace_stamp)
 };
 
 namespace infr {
@@ -54,6 +63,9 @@ namespace infr {
 int32_t fail(infr_cuda_ctx* ctx, int32_t code, const std::string& msg);
 int32_t check_cuda(infr_cuda_ctx* ctx, cudaError_t e, const char* what);
 int32_t ensure_scratch(infr_cuda_ctx* ctx, size_t bytes);
+
+// Raise a kernel's dynamic shared-memory limit once per (device, kernel) instead of on every launch.
+cudaError_t ensure_smem(const void* kernel, size_t bytes);
 
 inline size_t row_bytes(int32_t dtype, size_t n_elem) {
   switch (dtype) {
@@ -145,6 +157,18 @@ __device__ __forceinline__ void bulk_prefetch_l2(const void* gmem_src, uint32_t 
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---- optional phase stamps (latency analysis) ---------------------------------------------------
+// When a trace buffer is attached to the context, thread 0 of selected CTAs records
+// (globaltimer ns, SM clock) pairs at phase boundaries.  Null pointer = no stores.
+__device__ __forceinline__ void trace_stamp(unsigned long long* tr, int slot) {
+  if (tr != nullptr && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    tr[2 * slot] = g;
+    tr[2 * slot + 1] = (unsigned long long)clock64();
+  }
+}
 
 // ---- warp reductions ----------------------------------------------------------------------------
 

@@ -21,12 +21,12 @@ namespace infr {
 
 namespace {
 
-constexpr int GU_WARPS = 8;
+constexpr int GU_WARPS = 16;  // rows per chunk and role: one per warp
 constexpr int GU_THREADS = GU_WARPS * 32;
 constexpr int GU_MAX_CHUNKS = 4;
+constexpr int GU_XPITCH = 68;  // floats per 64-element group of x in shared memory (bank spread)
 
-constexpr int DN_WARPS = 8;
-constexpr int DN_THREADS = DN_WARPS * 32;
+constexpr int DN_MAX_WARPS = 24;
 constexpr int DN_MAX_SLOTS = 33;  // n_used ≤ 32 plus the shared expert
 
 __device__ __forceinline__ bool in_band(const DecodeParams& p, int e) {
@@ -36,84 +36,108 @@ __device__ __forceinline__ bool in_band(const DecodeParams& p, int e) {
 // ---------------------------------------------------------------------------------------------
 // gate/up + SwiGLU
 // ---------------------------------------------------------------------------------------------
-// One CTA = one (token, slot) pair x one tile of TR = 8*n_chunks output features, for both roles.
-// Shared memory: n_chunks x { 8 gate rows | 8 up rows }, one mbarrier per chunk.
+// One CTA = one (token, slot) pair x one tile of TR = 16*n_chunks output features, for both roles.
+// Shared memory: n_chunks x { 16 gate rows | 16 up rows }, one mbarrier per chunk, then the
+// token's activations.  Sixteen warps keep four resident per scheduler: the unpack is a chain of
+// dependent integer ops and only other warps hide its latency.
 // Lane L owns the 64-element groups g = L, L+32, ... of the input (for ne = 2048 exactly one, so
 // its 64 activations stay in registers for the whole tile).
 template <int NG>
-__global__ void __launch_bounds__(GU_THREADS) k_decode_gateup(DecodeParams p, int n_chunks) {
+__global__ void __launch_bounds__(GU_THREADS, 1) k_decode_gateup(DecodeParams p, int n_chunks) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_bar[GU_MAX_CHUNKS];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rb = p.ne / 256 * (int)Q4K_BLOCK_BYTES;  // bytes per weight row
-  const int TR = 8 * n_chunks;
+  const int TR = GU_WARPS * n_chunks;
   const int tiles = p.nff / TR, sh_tiles = p.sh_ff / TR;
   const int n_routed_jobs = p.rows * p.n_used * tiles;
 
-  pdl_wait();  // ids (and x) come from kernels earlier in the stream
+  const uint32_t chunk_bytes = (uint32_t)GU_WARPS * rb;  // per role
+  auto issue_copies = [&](const uint8_t* gs, const uint8_t* us) {
+    for (int c = 0; c < n_chunks; ++c) {
+      mbar_arrive_expect_tx(&s_bar[c], 2 * chunk_bytes);
+      unsigned char* dstc = smem + (size_t)c * 2 * chunk_bytes;
+      bulk_g2s(dstc, gs + (size_t)c * chunk_bytes, chunk_bytes, &s_bar[c]);
+      bulk_g2s(dstc + chunk_bytes, us + (size_t)c * chunk_bytes, chunk_bytes, &s_bar[c]);
+    }
+  };
+  if (tid == 0) {
+    for (int c = 0; c < n_chunks; ++c) mbar_init(&s_bar[c], 1);
+    mbar_fence_init();
+  }
 
-  int pair, tile, r;
-  const uint8_t *gsrc, *usrc;
+  const bool routed = (int)blockIdx.x < n_routed_jobs;
+  int pair = 0, tile, r;
   float* act_out;
-  if ((int)blockIdx.x < n_routed_jobs) {
+  if (!routed) {
+    // the shared expert's rows do not depend on routing: start fetching before the router is done
+    const int jb = blockIdx.x - n_routed_jobs;
+    r = jb / sh_tiles;
+    tile = jb % sh_tiles;
+    act_out = p.act + (size_t)p.rows * p.n_used * p.nff + (size_t)r * p.sh_ff + tile * TR;
+    if (tid == 0) issue_copies(p.sh_gate + (size_t)tile * TR * rb, p.sh_up + (size_t)tile * TR * rb);
+  } else {
     pair = blockIdx.x / tiles;
     tile = blockIdx.x % tiles;
     r = pair / p.n_used;
-    int e = p.ids[pair];
+    act_out = p.act + (size_t)pair * p.nff + tile * TR;
+  }
+
+  unsigned long long* tr = (blockIdx.x == 0) ? p.trace : nullptr;
+  trace_stamp(tr, 16);
+  pdl_wait();     // ids and x come from kernels earlier in the stream
+  trace_stamp(tr, 17);
+  pdl_trigger();  // only now: the next kernel reads ids as soon as it starts
+
+  int e_sel = routed ? __ldcg(p.ids + pair) : 0;  // L2 read: written by an overlapping earlier kernel
+  // the token's activations: coalesced into shared memory, then each lane keeps its group(s).
+  // Requested before the routing result so that both reads are in flight together.
+  const int n_groups = p.ne / 64;
+  float* s_x = reinterpret_cast<float*>(smem + (size_t)n_chunks * 2 * chunk_bytes);
+  {
+    const float4* xr4 = reinterpret_cast<const float4*>(p.x + (size_t)r * p.ne);
+    for (int i = tid; i < p.ne / 4; i += GU_THREADS) {
+      const float4 v = __ldcg(xr4 + i);
+      *reinterpret_cast<float4*>(s_x + (i >> 4) * GU_XPITCH + (i & 15) * 4) = v;
+    }
+  }
+  if (routed) {
+    int e = e_sel;
     if (e < 0 || e >= p.n_expert) {
       if (tid == 0) p.status->bad_index = 1;
       e = min(max(e, 0), p.n_expert - 1);
     }
     if (!in_band(p, e)) return;
-    gsrc = p.gate + (size_t)e * p.gate_stride + (size_t)tile * TR * rb;
-    usrc = p.up + (size_t)e * p.up_stride + (size_t)tile * TR * rb;
-    act_out = p.act + (size_t)pair * p.nff + tile * TR;
-  } else {
-    const int jb = blockIdx.x - n_routed_jobs;
-    r = jb / sh_tiles;
-    tile = jb % sh_tiles;
-    gsrc = p.sh_gate + (size_t)tile * TR * rb;
-    usrc = p.sh_up + (size_t)tile * TR * rb;
-    act_out = p.act + (size_t)p.rows * p.n_used * p.nff + (size_t)r * p.sh_ff + tile * TR;
+    if (tid == 0)
+      issue_copies(p.gate + (size_t)e * p.gate_stride + (size_t)tile * TR * rb,
+                   p.up + (size_t)e * p.up_stride + (size_t)tile * TR * rb);
   }
 
-  const uint32_t chunk_bytes = 8u * rb;  // per role
-  if (tid == 0) {
-    for (int c = 0; c < n_chunks; ++c) mbar_init(&s_bar[c], 1);
-    mbar_fence_init();
-    for (int c = 0; c < n_chunks; ++c) {
-      mbar_arrive_expect_tx(&s_bar[c], 2 * chunk_bytes);
-      unsigned char* dstc = smem + (size_t)c * 2 * chunk_bytes;
-      bulk_g2s(dstc, gsrc + (size_t)c * chunk_bytes, chunk_bytes, &s_bar[c]);
-      bulk_g2s(dstc + chunk_bytes, usrc + (size_t)c * chunk_bytes, chunk_bytes, &s_bar[c]);
-    }
-  }
-
-  // this lane's activations
-  const int n_groups = p.ne / 64;
-  const float* xr = p.x + (size_t)r * p.ne;
+  __syncthreads();  // x staged, barrier init visible to all waiters
+  trace_stamp(tr, 18);
   float xv[64];
   float xs0 = 0.f, xs1 = 0.f;
   auto load_x = [&](int g) {
-    const float4* src = reinterpret_cast<const float4*>(xr + (size_t)g * 64);
+    const float4* src = reinterpret_cast<const float4*>(s_x + g * GU_XPITCH);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float4 v = __ldg(src + i);
+      const float4 v = src[i];
       xv[4 * i + 0] = v.x; xv[4 * i + 1] = v.y; xv[4 * i + 2] = v.z; xv[4 * i + 3] = v.w;
     }
-    xs0 = 0.f; xs1 = 0.f;
+    float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) { xs0 += xv[i]; xs1 += xv[32 + i]; }
+    for (int i = 0; i < 16; ++i) { a0 += xv[2 * i]; a1 += xv[2 * i + 1]; b0 += xv[32 + 2 * i]; b1 += xv[33 + 2 * i]; }
+    xs0 = a0 + a1; xs1 = b0 + b1;
   };
   if (NG == 1) {
     if (lane < n_groups) load_x(lane);
   }
-  __syncthreads();  // barrier init visible to all waiters
 
   bool ok = true;
   for (int c = 0; c < n_chunks; ++c) {
     if (!mbar_wait_bounded(&s_bar[c], 0)) { ok = false; break; }
+    trace_stamp(tr, 19 + c);
     const unsigned char* grow = smem + (size_t)c * 2 * chunk_bytes + (size_t)warp * rb;
     const unsigned char* urow = grow + chunk_bytes;
     float gsum = 0.f, usum = 0.f;
@@ -142,9 +166,10 @@ __global__ void __launch_bounds__(GU_THREADS) k_decode_gateup(DecodeParams p, in
     usum = warp_sum(usum);
     if (lane == 0) {
       const float s = gsum / (1.0f + __expf(-gsum));
-      act_out[c * 8 + warp] = s * usum;
+      act_out[c * GU_WARPS + warp] = s * usum;
     }
   }
+  trace_stamp(tr, 23);
   if (!ok) {
     // a copy never signalled: report and make sure nothing is still landing in this CTA's
     // shared memory before it is handed to another CTA
@@ -171,13 +196,13 @@ __device__ __forceinline__ uint32_t lds_u32_unaligned(const unsigned char* base,
   return __funnelshift_r(lo, hi, (off & 3u) * 8);
 }
 
-__global__ void __launch_bounds__(DN_THREADS) k_decode_down(DecodeParams p, int TI) {
+__global__ void __launch_bounds__(DN_MAX_WARPS * 32, 1) k_decode_down(DecodeParams p, int TI) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_bar[DN_MAX_SLOTS];
   __shared__ float s_w[DN_MAX_SLOTS];
   __shared__ int s_on[DN_MAX_SLOTS];
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x, nwarps = nthreads >> 5;
   const int nb = p.nff / 256;                    // blocks per routed row
   const int drb = nb * (int)Q6K_BLOCK_BYTES;     // bytes per routed row
   const bool has_sh = p.sh_down != nullptr;
@@ -186,32 +211,34 @@ __global__ void __launch_bounds__(DN_THREADS) k_decode_down(DecodeParams p, int 
   const int tiles = p.ne / TI;
   const int r = blockIdx.x / tiles, i0 = (blockIdx.x % tiles) * TI;
 
-  // shared-memory carve-up: weights per slot, then activations per slot
+  // shared-memory carve-up: weights per slot, activations per slot, weighted partial outputs
   const uint32_t slab = (uint32_t)TI * drb, sh_slab = (uint32_t)TI * sh_drb;
   const uint32_t slab_pad = (uint32_t)align_up(slab + 8, 16), sh_slab_pad = (uint32_t)align_up(sh_slab + 8, 16);
   unsigned char* s_wt = smem;
   float* s_act = reinterpret_cast<float*>(smem + (size_t)p.n_used * slab_pad + (has_sh ? sh_slab_pad : 0));
+  float* s_part = s_act + (size_t)p.n_used * p.nff + (has_sh ? p.sh_ff : 0);  // [n_slots][TI]
 
-  pdl_wait();
-
+  // The routing result was complete before this kernel could start (the gate/up kernel releases
+  // its dependents only after it has itself waited for the router), so the weight slabs are
+  // requested right away and stream in while the gate/up kernel is still running.
+  unsigned long long* tr = (blockIdx.x == 0) ? p.trace : nullptr;
+  trace_stamp(tr, 32);
+  pdl_trigger();
   if (tid < n_slots) {
     const int s = tid;
     if (s < p.n_used) {
-      int e = p.ids[r * p.n_used + s];
+      int e = __ldcg(p.ids + r * p.n_used + s);
       e = min(max(e, 0), p.n_expert - 1);
       s_on[s] = in_band(p, e) ? e + 1 : 0;
-      s_w[s] = p.wts[r * p.n_used + s];
+      s_w[s] = __ldcg(p.wts + r * p.n_used + s);
     } else {
       s_on[s] = 1;
-      s_w[s] = p.sh_logit ? 1.0f / (1.0f + __expf(-p.sh_logit[r])) : 1.0f;
+      s_w[s] = p.sh_logit ? 1.0f / (1.0f + __expf(-__ldcg(p.sh_logit + r))) : 1.0f;
     }
-  }
-  __syncthreads();
-  if (tid == 0) {
-    for (int s = 0; s < n_slots; ++s) mbar_init(&s_bar[s], 1);
+    // each slot's barrier and copy are set up by the slot's own thread
+    mbar_init(&s_bar[s], 1);
     mbar_fence_init();
-    for (int s = 0; s < n_slots; ++s) {
-      if (!s_on[s]) continue;
+    if (s_on[s]) {
       if (s < p.n_used) {
         mbar_arrive_expect_tx(&s_bar[s], slab);
         bulk_g2s(s_wt + (size_t)s * slab_pad, p.down + (size_t)(s_on[s] - 1) * p.down_stride + (size_t)i0 * drb, slab,
@@ -222,109 +249,139 @@ __global__ void __launch_bounds__(DN_THREADS) k_decode_down(DecodeParams p, int 
       }
     }
   }
+  trace_stamp(tr, 33);
+  pdl_wait();  // the activations come from the gate/up kernel
+  trace_stamp(tr, 34);
   // activations of this token: routed slots then the shared expert
   {
     const float* a_src = p.act + (size_t)r * p.n_used * p.nff;
     const int n4 = p.n_used * p.nff / 4;
-    for (int i = tid; i < n4; i += DN_THREADS)
+    for (int i = tid; i < n4; i += nthreads)
       reinterpret_cast<float4*>(s_act)[i] = __ldcg(reinterpret_cast<const float4*>(a_src) + i);
     if (has_sh) {
       const float* sh_src = p.act + (size_t)p.rows * p.n_used * p.nff + (size_t)r * p.sh_ff;
       float4* d = reinterpret_cast<float4*>(s_act + (size_t)p.n_used * p.nff);
-      for (int i = tid; i < p.sh_ff / 4; i += DN_THREADS) d[i] = __ldcg(reinterpret_cast<const float4*>(sh_src) + i);
+      for (int i = tid; i < p.sh_ff / 4; i += nthreads) d[i] = __ldcg(reinterpret_cast<const float4*>(sh_src) + i);
     }
   }
   __syncthreads();
+  trace_stamp(tr, 35);
 
-  constexpr int MAX_ROWS_PER_WARP = 4;
-  float acc[MAX_ROWS_PER_WARP];
-#pragma unroll
-  for (int q = 0; q < MAX_ROWS_PER_WARP; ++q) acc[q] = 0.f;
-
+  // A warp task = one slot x one group of RPG rows: the slot's activations stay in registers
+  // while the rows of the group stream past them.
+  const int RPG = TI < 8 ? TI : 8, RG = TI / RPG;
+  const int n_tasks = n_slots * RG;
   bool ok = true;
-  for (int s = 0; s < n_slots && ok; ++s) {
-    if (!s_on[s]) continue;
-    if (!mbar_wait_bounded(&s_bar[s], 0)) { ok = false; break; }
-    const bool shared_slot = s >= p.n_used;
-    const int row_bytes_s = shared_slot ? sh_drb : drb;
-    const int units = (shared_slot ? sh_nb : nb) * 16;
-    const unsigned char* wt = s_wt + (shared_slot ? (size_t)p.n_used * slab_pad : (size_t)s * slab_pad);
-    const float* a = s_act + (shared_slot ? (size_t)p.n_used * p.nff : (size_t)s * p.nff);
-    const float ws = s_w[s];
-    for (int u = lane; u < units; u += 32) {
-      const int b = u >> 4, h = (u >> 3) & 1, lw = u & 7;
-      // activations of the unit and 96 * their per-quadrant sums
-      float av[16], s96[4];
-      const float* ab = a + b * 256 + h * 128 + lw * 4;
+  for (int task = warp; task < n_tasks && ok; task += nwarps) {
+    const int s = task / RG, row0 = (task % RG) * RPG;
+    float acc[8];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float4 v = *reinterpret_cast<const float4*>(ab + 32 * q);
-        av[4 * q + 0] = v.x; av[4 * q + 1] = v.y; av[4 * q + 2] = v.z; av[4 * q + 3] = v.w;
-        s96[q] = 96.f * ((v.x + v.y) + (v.z + v.w));
-      }
-      const uint32_t boff = (uint32_t)b * Q6K_BLOCK_BYTES;
+    for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+    if (s_on[s]) {
+      if (!mbar_wait_bounded(&s_bar[s], 0)) { ok = false; break; }
+      const bool shared_slot = s >= p.n_used;
+      const int row_bytes_s = shared_slot ? sh_drb : drb;
+      const int units = (shared_slot ? sh_nb : nb) * 16;
+      const unsigned char* wt = s_wt + (shared_slot ? (size_t)p.n_used * slab_pad : (size_t)s * slab_pad);
+      const float* a = s_act + (shared_slot ? (size_t)p.n_used * p.nff : (size_t)s * p.nff);
+      for (int u = lane; u < units; u += 32) {
+        const int b = u >> 4, h = (u >> 3) & 1, lw = u & 7;
+        // activations of the unit and 96 * their per-quadrant sums
+        float av[16], s96[4];
+        const float* ab = a + b * 256 + h * 128 + lw * 4;
 #pragma unroll
-      for (int q = 0; q < MAX_ROWS_PER_WARP; ++q) {
-        const int row = warp + q * DN_WARPS;
-        if (row < TI) {
-          // offsets are taken from the 16-byte aligned slab base: rows of an odd block count
-          // start 2 bytes off a word boundary too
-          const uint32_t ro = (uint32_t)row * row_bytes_s + boff;
-          const uint32_t A = lds_u32_unaligned(wt, ro + 64 * h + 4 * lw);
-          const uint32_t B = lds_u32_unaligned(wt, ro + 64 * h + 32 + 4 * lw);
-          const uint32_t H = lds_u32_unaligned(wt, ro + 128 + 32 * h + 4 * lw);
-          const uint32_t S0 = lds_u32_unaligned(wt, ro + 192 + 8 * h);
-          const uint32_t S1 = lds_u32_unaligned(wt, ro + 196 + 8 * h);
-          const float d = f16_bits_to_f32(*reinterpret_cast<const unsigned short*>(wt + ro + 208));
-          // codes as bytes 0x80 | (q << 1)
-          const uint32_t c0 = ((A << 1) & 0x1E1E1E1Eu) | ((H << 5) & 0x60606060u) | 0x80808080u;
-          const uint32_t c1 = ((B << 1) & 0x1E1E1E1Eu) | ((H << 3) & 0x60606060u) | 0x80808080u;
-          const uint32_t c2 = ((A >> 3) & 0x1E1E1E1Eu) | ((H << 1) & 0x60606060u) | 0x80808080u;
-          const uint32_t c3 = ((B >> 3) & 0x1E1E1E1Eu) | ((H >> 1) & 0x60606060u) | 0x80808080u;
-          const uint32_t cs[4] = {c0, c1, c2, c3};
-          // scales of the four quadrants: bytes (lw>>2) + 2q of the eight scale bytes of this half
-          const uint32_t sel = (lw >> 2) ? 0x7531u : 0x6420u;
-          const uint32_t sc4 = __byte_perm(S0, S1, sel);
-          float part = 0.f;
+        for (int q = 0; q < 4; ++q) {
+          const float4 v = *reinterpret_cast<const float4*>(ab + 32 * q);
+          av[4 * q + 0] = v.x; av[4 * q + 1] = v.y; av[4 * q + 2] = v.z; av[4 * q + 3] = v.w;
+          s96[q] = 96.f * ((v.x + v.y) + (v.z + v.w));
+        }
+        const uint32_t boff = (uint32_t)b * Q6K_BLOCK_BYTES;
+        const uint32_t sel = (lw >> 2) ? 0x7531u : 0x6420u;
 #pragma unroll
-          for (int qd = 0; qd < 4; ++qd) {
-            const uint32_t c = cs[qd];
-            float2 f = __fmul2_rn(make_float2(byte_to_unit_float<0>(c), byte_to_unit_float<1>(c)),
-                                  make_float2(av[4 * qd + 0], av[4 * qd + 1]));
-            f = __ffma2_rn(make_float2(byte_to_unit_float<2>(c), byte_to_unit_float<3>(c)),
-                           make_float2(av[4 * qd + 2], av[4 * qd + 3]), f);
-            const float F = f.x + f.y;
-            const float sc = (float)(int)(signed char)((sc4 >> (8 * qd)) & 0xFFu);
-            // Σ sc·(q-32)·a = sc·(64·F − 96·S)
-            part = fmaf(sc, fmaf(64.f, F, -s96[qd]), part);
+        for (int q = 0; q < 8; ++q) {
+          if (q < RPG) {
+            // offsets are taken from the 16-byte aligned slab base: rows of an odd block count
+            // start 2 bytes off a word boundary too
+            const uint32_t ro = (uint32_t)(row0 + q) * row_bytes_s + boff;
+            const uint32_t A = lds_u32_unaligned(wt, ro + 64 * h + 4 * lw);
+            const uint32_t B = lds_u32_unaligned(wt, ro + 64 * h + 32 + 4 * lw);
+            const uint32_t H = lds_u32_unaligned(wt, ro + 128 + 32 * h + 4 * lw);
+            const uint32_t S0 = lds_u32_unaligned(wt, ro + 192 + 8 * h);
+            const uint32_t S1 = lds_u32_unaligned(wt, ro + 196 + 8 * h);
+            const float d = f16_bits_to_f32(*reinterpret_cast<const unsigned short*>(wt + ro + 208));
+            // codes as bytes 0x80 | (q << 1)
+            const uint32_t cs[4] = {((A << 1) & 0x1E1E1E1Eu) | ((H << 5) & 0x60606060u) | 0x80808080u,
+                                    ((B << 1) & 0x1E1E1E1Eu) | ((H << 3) & 0x60606060u) | 0x80808080u,
+                                    ((A >> 3) & 0x1E1E1E1Eu) | ((H << 1) & 0x60606060u) | 0x80808080u,
+                                    ((B >> 3) & 0x1E1E1E1Eu) | ((H >> 1) & 0x60606060u) | 0x80808080u};
+            // scales of the four quadrants: bytes (lw>>2) + 2q of the eight scale bytes of this half
+            const uint32_t sc4 = __byte_perm(S0, S1, sel);
+            float part = 0.f;
+#pragma unroll
+            for (int qd = 0; qd < 4; ++qd) {
+              const uint32_t c = cs[qd];
+              float2 f = __fmul2_rn(make_float2(byte_to_unit_float<0>(c), byte_to_unit_float<1>(c)),
+                                    make_float2(av[4 * qd + 0], av[4 * qd + 1]));
+              f = __ffma2_rn(make_float2(byte_to_unit_float<2>(c), byte_to_unit_float<3>(c)),
+                             make_float2(av[4 * qd + 2], av[4 * qd + 3]), f);
+              const float F = f.x + f.y;
+              const float sc = (float)(int)(signed char)((sc4 >> (8 * qd)) & 0xFFu);
+              // Σ sc·(q-32)·a = sc·(64·F − 96·S)
+              part = fmaf(sc, fmaf(64.f, F, -s96[qd]), part);
+            }
+            acc[q] = fmaf(d, part, acc[q]);
           }
-          acc[q] = fmaf(ws * d, part, acc[q]);
         }
       }
     }
+    // eight row sums across 32 lanes with nine shuffles: halve the value set at every step
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float send = (lane & 16) ? acc[i] : acc[i + 4];
+      const float keep = (lane & 16) ? acc[i + 4] : acc[i];
+      acc[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float send = (lane & 8) ? acc[i] : acc[i + 2];
+      const float keep = (lane & 8) ? acc[i + 2] : acc[i];
+      acc[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, 8);
+    }
+    {
+      const float send = (lane & 4) ? acc[0] : acc[1];
+      const float keep = (lane & 4) ? acc[1] : acc[0];
+      acc[0] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, 4);
+    }
+    acc[0] += __shfl_xor_sync(0xFFFFFFFFu, acc[0], 2);
+    acc[0] += __shfl_xor_sync(0xFFFFFFFFu, acc[0], 1);
+    const int q_mine = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    if ((lane & 3) == 0 && q_mine < RPG) s_part[s * TI + row0 + q_mine] = s_w[s] * acc[0];
   }
   if (!ok) {
     if (lane == 0) atomicExch(&p.status->timeout, 2);
     for (int s = 0; s < n_slots; ++s)
       if (s_on[s]) (void)mbar_wait_bounded(&s_bar[s], 0);
-    return;
   }
-#pragma unroll
-  for (int q = 0; q < MAX_ROWS_PER_WARP; ++q) {
-    const int row = warp + q * DN_WARPS;
-    const float v = warp_sum(acc[q]);
-    if (row < TI && lane == 0) p.dst[(size_t)r * p.ne + i0 + row] = v;
+  __syncthreads();
+  trace_stamp(tr, 36);
+  // weighted sum over slots in rank order, the shared expert last (the CPU's order)
+  if (tid < TI) {
+    float o = 0.f;
+    for (int s = 0; s < n_slots; ++s) o += s_part[s * TI + tid];
+    p.dst[(size_t)r * p.ne + i0 + tid] = o;
   }
 }
 
-size_t gateup_smem(int ne, int n_chunks) { return (size_t)n_chunks * 2 * 8 * (ne / 256 * Q4K_BLOCK_BYTES); }
+size_t gateup_smem(int ne, int n_chunks) {
+  return (size_t)n_chunks * 2 * GU_WARPS * (ne / 256 * Q4K_BLOCK_BYTES) + (size_t)(ne / 64) * GU_XPITCH * sizeof(float);
+}
 
 int pick_chunks(int ne, int nff, int sh_ff) {
-  for (int c = GU_MAX_CHUNKS; c >= 1; c >>= 1) {
-    const int TR = 8 * c;
+  for (int c = 2; c >= 1; c >>= 1) {
+    const int TR = GU_WARPS * c;
     if (nff % TR) continue;
     if (sh_ff && sh_ff % TR) continue;
-    if (gateup_smem(ne, c) <= 100 * 1024) return c;
+    if (gateup_smem(ne, c) <= 200 * 1024) return c;
   }
   return 0;
 }
@@ -332,7 +389,8 @@ int pick_chunks(int ne, int nff, int sh_ff) {
 size_t down_smem(int TI, int nff, int sh_ff, int n_used) {
   const size_t slab = align_up((size_t)TI * (nff / 256 * Q6K_BLOCK_BYTES) + 8, 16);
   const size_t sh_slab = sh_ff ? align_up((size_t)TI * (sh_ff / 256 * Q6K_BLOCK_BYTES) + 8, 16) : 0;
-  return (size_t)n_used * slab + sh_slab + ((size_t)n_used * nff + sh_ff) * sizeof(float);
+  return (size_t)n_used * slab + sh_slab + ((size_t)n_used * nff + sh_ff) * sizeof(float) +
+         (size_t)(n_used + 1) * TI * sizeof(float);
 }
 
 // TI rows per CTA: bulk copies need TI * row_bytes to be a multiple of 16 for both banks.
@@ -390,13 +448,13 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl) {
   const int n_chunks = pick_chunks(p.ne, p.nff, sh_ff);
   const int TI = pick_down_tile(p.ne, p.nff, sh_ff, p.n_used);
   if (!n_chunks || !TI) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "small-m path: tile does not fit shared memory");
-  const int TR = 8 * n_chunks;
+  const int TR = GU_WARPS * n_chunks;
   const int jobs = p.rows * p.n_used * (p.nff / TR) + (has_sh ? p.rows * (sh_ff / TR) : 0);
   const size_t smem_gu = gateup_smem(p.ne, n_chunks);
   const int ng = (p.ne / 64 + 31) / 32;
   cudaError_t e;
   auto run_gu = [&](auto kern) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_gu);
+    e = ensure_smem(reinterpret_cast<const void*>(kern), smem_gu);
     if (e != cudaSuccess) return e;
     return launch_ex(kern, dim3(jobs), dim3(GU_THREADS), smem_gu, ctx->stream, pdl, p, n_chunks);
   };
@@ -410,9 +468,15 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl) {
   if (e != cudaSuccess) return check_cuda(ctx, e, "k_decode_gateup launch");
 
   const size_t smem_dn = down_smem(TI, p.nff, sh_ff, p.n_used);
-  e = cudaFuncSetAttribute(k_decode_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dn);
+  e = ensure_smem(reinterpret_cast<const void*>(k_decode_down), smem_dn);
   if (e != cudaSuccess) return check_cuda(ctx, e, "k_decode_down smem attribute");
-  e = launch_ex(k_decode_down, dim3(p.rows * (p.ne / TI)), dim3(DN_THREADS), smem_dn, ctx->stream, pdl, p, TI);
+  // one warp per (slot, group of up to 8 rows) when that fits, else the largest divisor
+  const int n_tasks = (p.n_used + (has_sh ? 1 : 0)) * (TI > 8 ? TI / 8 : 1);
+  int nw = 16;
+  for (int c = DN_MAX_WARPS; c >= 8; --c)
+    if (n_tasks % c == 0) { nw = c; break; }
+  if (n_tasks < 8) nw = n_tasks < 4 ? 4 : n_tasks;
+  e = launch_ex(k_decode_down, dim3(p.rows * (p.ne / TI)), dim3(nw * 32), smem_dn, ctx->stream, pdl, p, TI);
   ctx->launches += 1;
   return check_cuda(ctx, e, "k_decode_down launch");
 }

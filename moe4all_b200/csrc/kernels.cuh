@@ -18,6 +18,7 @@ struct RouteParams {
   int32_t* ids;              // [rows, n_used]
   float* wts;                // [rows, n_used]
   unsigned int* counter;     // zero on entry, zero on exit
+  unsigned long long* trace; // optional phase stamps
   int rows, ne, n_expert, n_used;
   float scale;
   int gating, norm_w, n_groups, n_groups_used;
@@ -33,6 +34,7 @@ struct DecodeParams {
   float* act;            // [rows*n_used, nff] then [rows, sh_ff]
   float* dst;            // [rows, ne]
   DeviceStatus* status;
+  unsigned long long* trace;  // optional phase stamps
   size_t gate_stride, up_stride, down_stride;  // bytes per expert
   int rows, ne, n_used, nff, sh_ff, n_expert;
   uint32_t ep_lo, ep_n;  // band (ep_n == 0: off)
