@@ -120,6 +120,10 @@ typedef struct infr_cuda_moe_ffn_desc {
   uint32_t sh_ff;
   uint32_t path;                    /* 0 = choose by rows; 1 = force the small-m (decode) kernels;
                                        2 = force the grouped-GEMM (prefill) kernels                */
+  uint32_t stages;                  /* 0 = the whole op.  Otherwise a mask of the kernels to launch,
+                                       for timing one of them alone: 1 router + top-k, 2 gate/up,
+                                       4 down + combine.  Later stages read what an earlier full
+                                       call left in ids_out / wts_out and the context's scratch.   */
 } infr_cuda_moe_ffn_desc;
 
 /* Backend::execute of a graph holding one Op::MoeFfn (backend.rs:908; CPU arm

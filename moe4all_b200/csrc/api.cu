@@ -433,7 +433,8 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     if ((rc = ensure_scratch(ctx, sz.total))) return rc;
     Scratch s = carve(ctx->scratch, d, true);
     RouteParams rp = route_params(ctx, d, s, true);
-    if ((rc = launch_route(ctx, rp, true))) return rc;
+    const uint32_t stages = d->stages ? d->stages : 7u;
+    if ((stages & 1u) && (rc = launch_route(ctx, rp, true))) return rc;
     DecodeParams dp = {};
     dp.x = static_cast<const float*>(d->x->ptr);
     dp.ids = rp.ids;
@@ -460,7 +461,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.n_expert = d->n_expert;
     dp.ep_lo = d->ep_lo;
     dp.ep_n = d->ep_n_local;
-    return launch_decode_ffn(ctx, dp, true);
+    return launch_decode_ffn(ctx, dp, true, stages);
   }
   return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: the grouped-GEMM path is not built yet");
 }

@@ -442,7 +442,7 @@ bool decode_ffn_supported(const infr_cuda_ctx*, int ne, int nff, int sh_ff, int 
   return true;
 }
 
-int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl) {
+int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages) {
   const bool has_sh = p.sh_gate != nullptr;
   const int sh_ff = has_sh ? p.sh_ff : 0;
   const int n_chunks = pick_chunks(p.ne, p.nff, sh_ff);
@@ -452,20 +452,23 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl) {
   const int jobs = p.rows * p.n_used * (p.nff / TR) + (has_sh ? p.rows * (sh_ff / TR) : 0);
   const size_t smem_gu = gateup_smem(p.ne, n_chunks);
   const int ng = (p.ne / 64 + 31) / 32;
-  cudaError_t e;
+  cudaError_t e = cudaSuccess;
   auto run_gu = [&](auto kern) {
     e = ensure_smem(reinterpret_cast<const void*>(kern), smem_gu);
     if (e != cudaSuccess) return e;
     return launch_ex(kern, dim3(jobs), dim3(GU_THREADS), smem_gu, ctx->stream, pdl, p, n_chunks);
   };
-  if (ng == 1)
-    e = run_gu(k_decode_gateup<1>);
-  else if (ng == 2)
-    e = run_gu(k_decode_gateup<2>);
-  else
-    e = run_gu(k_decode_gateup<4>);
-  ctx->launches += 1;
-  if (e != cudaSuccess) return check_cuda(ctx, e, "k_decode_gateup launch");
+  if (stages & 2u) {
+    if (ng == 1)
+      e = run_gu(k_decode_gateup<1>);
+    else if (ng == 2)
+      e = run_gu(k_decode_gateup<2>);
+    else
+      e = run_gu(k_decode_gateup<4>);
+    ctx->launches += 1;
+    if (e != cudaSuccess) return check_cuda(ctx, e, "k_decode_gateup launch");
+  }
+  if (!(stages & 4u)) return INFR_CUDA_OK;
 
   const size_t smem_dn = down_smem(TI, p.nff, sh_ff, p.n_used);
   e = ensure_smem(reinterpret_cast<const void*>(k_decode_down), smem_dn);

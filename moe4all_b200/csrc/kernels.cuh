@@ -41,7 +41,7 @@ struct DecodeParams {
 };
 
 int32_t launch_route(infr_cuda_ctx* ctx, const RouteParams& p, bool pdl);
-int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl);
+int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages);
 // Whether the small-m kernels cover this shape (dims, shared-memory budget).
 bool decode_ffn_supported(const infr_cuda_ctx* ctx, int ne, int nff, int sh_ff, int n_used, std::string* why);
 

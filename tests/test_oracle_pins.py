@@ -1,0 +1,328 @@
+"""Pins the CPU oracle to the reference's own known-answer material (CPU only).
+
+Every vector here is re-created from the formula the reference's tests use; the files and lines
+are cited per test.  Independent decoders are written in numpy from the block layout, not from the
+oracle's C++.
+"""
+import numpy as np
+import pytest
+
+from moe4all_b200 import synth
+from oracle import oracle as orc
+
+F32 = np.float32
+
+
+# ---- independent numpy decoders -----------------------------------------------------------------
+
+def f16(b0, b1):
+    return np.array([b0 | (b1 << 8)], dtype=np.uint16).view(np.float16).astype(F32)[0]
+
+
+def np_q4k(raw):
+    """Factored form (crates/infr-gguf/src/dequant.rs:35-51, 315-335): (f32(d)*sc)*q + (f32(dmin)*(-m))."""
+    raw = np.asarray(raw, np.uint8).reshape(-1, 144)
+    out = np.empty((raw.shape[0], 256), F32)
+    for bi, blk in enumerate(raw):
+        d, dmin = f16(int(blk[0]), int(blk[1])), f16(int(blk[2]), int(blk[3]))
+        sc_b, qs = blk[4:16].astype(np.int64), blk[16:144]
+        for s in range(8):
+            if s < 4:
+                sc, m = sc_b[s] & 63, sc_b[s + 4] & 63
+            else:
+                sc = (sc_b[s + 4] & 0xF) | ((sc_b[s - 4] >> 6) << 4)
+                m = (sc_b[s + 4] >> 4) | ((sc_b[s] >> 6) << 4)
+            S = F32(d * F32(sc))
+            M = F32(dmin * F32(-m))
+            byts = qs[32 * (s // 2): 32 * (s // 2) + 32]
+            q = (byts & 0xF) if s % 2 == 0 else (byts >> 4)
+            out[bi, 32 * s: 32 * s + 32] = (S * q.astype(F32)).astype(F32) + M
+    return out.reshape(-1)
+
+
+def np_q6k_codes(blk):
+    ql, qh = blk[0:128].astype(np.int64), blk[128:192].astype(np.int64)
+    q = np.empty(256, np.int64)
+    for half in range(2):
+        for l in range(32):
+            a, b, h = ql[64 * half + l], ql[64 * half + 32 + l], qh[32 * half + l]
+            base = 128 * half + l
+            q[base] = (a & 0xF) | ((h & 3) << 4)
+            q[base + 32] = (b & 0xF) | (((h >> 2) & 3) << 4)
+            q[base + 64] = (a >> 4) | (((h >> 4) & 3) << 4)
+            q[base + 96] = (b >> 4) | (((h >> 6) & 3) << 4)
+    return q
+
+
+def np_q6k(raw, glsl_form=False):
+    """Factored form (dequant.rs:365-389): (f32(d)*sc)*q + f32(d)*(-32*sc); or the shader's
+    d*sc*(q-32) (crates/infr-vulkan/shaders/native_decode.glsl:581)."""
+    raw = np.asarray(raw, np.uint8).reshape(-1, 210)
+    out = np.empty((raw.shape[0], 256), F32)
+    for bi, blk in enumerate(raw):
+        d = f16(int(blk[208]), int(blk[209]))
+        sc = blk[192:208].view(np.int8).astype(np.int64)
+        q = np_q6k_codes(blk)
+        scale = np.repeat(sc, 16)
+        if glsl_form:
+            out[bi] = (F32(d) * scale.astype(F32)).astype(F32) * (q - 32).astype(F32)
+        else:
+            S = (F32(d) * scale.astype(F32)).astype(F32)
+            M = (F32(d) * (-32 * scale).astype(F32)).astype(F32)
+            out[bi] = (S * q.astype(F32)).astype(F32) + M
+    return out.reshape(-1)
+
+
+def pattern_q4k():
+    # crates/infr-gguf/src/dequant.rs:1174-1187: bytes ((i*37+11)&0xFF), d = 0.375, dmin = -0.125
+    b = ((np.arange(288) * 37 + 11) & 0xFF).astype(np.uint8)
+    for blk in range(2):
+        b[blk * 144: blk * 144 + 2] = np.array([0.375], np.float16).view(np.uint8)
+        b[blk * 144 + 2: blk * 144 + 4] = np.array([-0.125], np.float16).view(np.uint8)
+    return b
+
+
+def pattern_q6k():
+    # crates/infr-gguf/src/dequant.rs:1190-1202: bytes ((i*53+7)&0xFF), d = 0.05 at byte 208
+    b = ((np.arange(420) * 53 + 7) & 0xFF).astype(np.uint8)
+    for blk in range(2):
+        b[blk * 210 + 208: blk * 210 + 210] = np.array([0.05], np.float16).view(np.uint8)
+    return b
+
+
+# ---- block decode --------------------------------------------------------------------------------
+
+def test_q4k_pattern_bit_identical():
+    raw = pattern_q4k()
+    got = orc.dequant(orc.DT_Q4K, raw, 512)
+    assert np.array_equal(got.view(np.uint32), np_q4k(raw).view(np.uint32))
+    # element 0 by hand: sub-block 0, sc = scales[0] & 63, m = scales[4] & 63, q = qs[0] & 0xF
+    sc, m, q = int(raw[4]) & 63, int(raw[8]) & 63, int(raw[16]) & 0xF
+    want0 = F32(F32(0.375) * F32(sc)) * F32(q) + F32(F32(-0.125) * F32(-m))
+    assert got[0] == want0
+    assert np.all(np.isfinite(got)) and np.ptp(got) > 0
+
+
+def test_q6k_pattern_bit_identical():
+    raw = pattern_q6k()
+    got = orc.dequant(orc.DT_Q6K, raw, 512)
+    assert np.array_equal(got.view(np.uint32), np_q6k(raw).view(np.uint32))
+    # the shader's form d*sc*(q-32) rounds differently by at most an ulp or two of the scale term
+    alt = np_q6k(raw, glsl_form=True)
+    assert np.max(np.abs(got - alt)) <= 4e-6 * np.max(np.abs(alt))
+    assert np.ptp(got) > 0
+
+
+@pytest.mark.parametrize("dt,name,nbytes", [(orc.DT_Q4K, "Q4K", 144), (orc.DT_Q6K, "Q6K", 210)])
+def test_testkit_synth_blocks(dt, name, nbytes):
+    # crates/infr-testkit/src/lib.rs:106-123: LCG payload per block (seed ^ block), scale slots overwritten
+    raw = synth.testkit_weight(name, 4 * 256, seed=0x1234)
+    assert raw.shape == (4, nbytes)
+    got = orc.dequant(dt, raw, 1024)
+    want = np_q4k(raw) if name == "Q4K" else np_q6k(raw)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # LCG: first byte of block 0 is ((seed*1664525 + 1013904223) mod 2^32) >> 16 & 0xFF
+    s = (0x1234 * 1664525 + 1013904223) & 0xFFFFFFFF
+    assert synth.lcg_bytes(0x1234, 1)[0] == (s >> 16) & 0xFF
+
+
+def test_random_blocks_match_numpy_decoder():
+    rng = np.random.default_rng(5)
+    q4, q6 = synth.random_q4k(rng, 16), synth.random_q6k(rng, 16)
+    assert np.array_equal(orc.dequant(orc.DT_Q4K, q4, 4096).view(np.uint32), np_q4k(q4).view(np.uint32))
+    assert np.array_equal(orc.dequant(orc.DT_Q6K, q6, 4096).view(np.uint32), np_q6k(q6).view(np.uint32))
+
+
+def test_ragged_block_count_rejected():
+    with pytest.raises(ValueError):
+        orc.dequant(orc.DT_Q4K, np.zeros(144, np.uint8), 100)
+
+
+# ---- dot ------------------------------------------------------------------------------------------
+
+def dot_8lane_longdouble(a, b):
+    """crates/infr-cpu/src/kernels.rs:6568-6583 with each fma evaluated in extended precision and
+    rounded once to f32."""
+    ld = np.longdouble
+    acc = [F32(0)] * 8
+    n = len(a)
+    for c in range(n // 8):
+        for j in range(8):
+            acc[j] = F32(ld(a[8 * c + j]) * ld(b[8 * c + j]) + ld(acc[j]))
+    s = F32(0)
+    for j in range(8):
+        s = F32(s + acc[j])
+    for i in range(n // 8 * 8, n):
+        s = F32(ld(a[i]) * ld(b[i]) + ld(s))
+    return s
+
+
+@pytest.mark.parametrize("n", [8, 64, 67, 256])
+def test_dot_lane_order(n):
+    rng = np.random.default_rng(n)
+    a = rng.normal(size=n).astype(F32) * F32(1e3)
+    b = rng.normal(size=n).astype(F32)
+    want = dot_8lane_longdouble(a, b)
+    assert orc.dot(a, b) == want
+    assert orc.dot(a, b, scalar=True) == want  # AVX2 form == scalar form (kernels.rs:6697-6719)
+
+
+def test_dot_order_is_not_a_plain_sum():
+    # the 8-lane order differs from a left-to-right sum on cancellation-heavy data: the oracle must
+    # follow the former
+    rng = np.random.default_rng(1)
+    a = (rng.normal(size=512) * 1e4).astype(F32)
+    b = rng.normal(size=512).astype(F32)
+    seq = F32(0)
+    for x, y in zip(a, b):
+        seq = F32(seq + F32(x * y))
+    assert orc.dot(a, b) == dot_8lane_longdouble(a, b)
+    assert orc.dot(a, b) != seq
+
+
+# ---- routing vectors --------------------------------------------------------------------------------
+
+def gen(n, salt):
+    return synth.gen_f32(n, salt)
+
+
+def moe_ref_numpy(x, router, gate, up, down, ne, n_expert, n_used, nff, scale, gating, bias, groups, groups_used):
+    """`moe_ref` of crates/infr-llama/tests/seam_op_parity.rs:2245-2343 (plain sequential f32 dots)."""
+    def dot(a, b):
+        s = F32(0)
+        for u, v in zip(a, b):
+            s = F32(s + F32(u * v))
+        return s
+    logits = np.array([dot(router[e * ne:(e + 1) * ne], x) for e in range(n_expert)], F32)
+    if gating == "softmax":
+        p = np.exp(logits - logits.max(), dtype=F32)
+        ps = F32(0)
+        for v in p:
+            ps = F32(ps + v)
+        probs = (p / ps).astype(F32)
+    elif gating == "sigmoid":
+        probs = (F32(1) / (F32(1) + np.exp(-logits, dtype=F32))).astype(F32)
+    else:
+        sp = np.where(logits > 20, logits, np.log(F32(1) + np.exp(logits, dtype=F32), dtype=F32))
+        probs = np.sqrt(sp, dtype=F32)
+    sel = probs.copy() if bias is None else (probs + bias).astype(F32)
+    if groups > 1 and groups_used > 0:
+        per = n_expert // groups
+        gs = [float(np.sort(sel[g * per:(g + 1) * per])[-2:].sum()) for g in range(groups)]
+        keep = sorted(range(groups), key=lambda g: -gs[g])[:groups_used]
+        for g in range(groups):
+            if g not in keep:
+                sel[g * per:(g + 1) * per] = -np.inf
+    idx = sorted(range(n_expert), key=lambda e: -sel[e])[:n_used]
+    wsum = F32(0)
+    for e in idx:
+        wsum = F32(wsum + probs[e])
+    out = np.zeros(ne, F32)
+    silu = lambda z: F32(z / (F32(1) + np.exp(-z, dtype=F32)))
+    for e in idx:
+        gs_, ds_ = e * nff * ne, e * ne * nff
+        act = np.array([silu(dot(gate[gs_ + j * ne: gs_ + (j + 1) * ne], x)) * dot(up[gs_ + j * ne: gs_ + (j + 1) * ne], x)
+                        for j in range(nff)], F32)
+        w_e = F32(F32(probs[e] / wsum) * F32(scale))
+        for i in range(ne):
+            out[i] = F32(out[i] + F32(w_e * dot(down[ds_ + i * nff: ds_ + (i + 1) * nff], act)))
+    return out, idx
+
+
+def run_f32_case(lead, salts, gating, gname, bias=None, groups=0, groups_used=0, n_used=2):
+    ne = nff = 32
+    n_expert = len(lead)
+    x = np.ones((1, ne), F32)
+    router = np.zeros(n_expert * ne, F32)
+    router[::ne] = lead
+    gate, up, down = gen(n_expert * nff * ne, salts[0]), gen(n_expert * nff * ne, salts[1]), gen(n_expert * ne * nff, salts[2])
+    res = orc.moe_ffn(x, router, gate, up, down, n_expert=n_expert, n_used=n_used, n_ff_exp=nff, scale=1.0,
+                      gate_dtype=orc.DT_F32, up_dtype=orc.DT_F32, down_dtype=orc.DT_F32, gating=gating,
+                      bias=bias, groups=groups, groups_used=groups_used, threads=2)
+    want, idx = moe_ref_numpy(x[0], router, gate, up, down, ne, n_expert, n_used, nff, 1.0, gname, bias, groups, groups_used)
+    return res, want, idx
+
+
+def test_sqrt_softplus_vector():
+    # crates/infr-llama/tests/seam_op_parity.rs:2352-2443: leads [24, 1, .75, .5, -1.5, -1] -> experts 0, 1
+    res, want, idx = run_f32_case(np.array([24.0, 1.0, 0.75, 0.5, -1.5, -1.0], F32), (12, 13, 14),
+                                  orc.GATING_SQRT_SOFTPLUS, "sqrt_softplus")
+    assert res.ids[0].tolist() == [0, 1] == idx
+    assert np.max(np.abs(res.dst[0] - want)) < 1e-4  # the reference's own bound (:2430-2436)
+    assert np.abs(want).max() > 0
+
+
+def test_groups_bias_vector():
+    # seam_op_parity.rs:2453-2554: sigmoid gating, 2 groups / 1 used, +0.6 bias on experts 4..7:
+    # biased probabilities pick group 1 and experts 4, 5; unbiased probabilities drive the weights
+    lead = np.array([3.0, 2.5, 2.0, 1.5, 1.0, 0.9, 0.8, 0.7], F32)
+    bias = np.array([0, 0, 0, 0, 0.6, 0.6, 0.6, 0.6], F32)
+    res, want, idx = run_f32_case(lead, (15, 16, 17), orc.GATING_SIGMOID, "sigmoid", bias=bias, groups=2, groups_used=1)
+    assert res.ids[0].tolist() == [4, 5] == idx
+    assert np.max(np.abs(res.dst[0] - want)) < 1e-4
+    p4, p5 = 1 / (1 + np.exp(-1.0)), 1 / (1 + np.exp(-0.9))
+    np.testing.assert_allclose(res.wts[0], [p4 / (p4 + p5), p5 / (p4 + p5)], rtol=1e-6)
+    # without the bias group 0 wins (experts 0, 1): the bias semantics are what flips it
+    res2, _, _ = run_f32_case(lead, (15, 16, 17), orc.GATING_SIGMOID, "sigmoid", bias=None, groups=2, groups_used=1)
+    assert res2.ids[0].tolist() == [0, 1]
+
+
+def test_tie_goes_to_lower_index():
+    # stable descending sort (crates/infr-cpu/src/lib.rs:3847-3850): equal scores keep index order
+    lead = np.array([0.5, 2.0, 2.0, 0.5, 2.0, -1.0], F32)
+    res, _, _ = run_f32_case(lead, (1, 2, 3), orc.GATING_SOFTMAX, "softmax")
+    assert res.ids[0].tolist() == [1, 2]
+
+
+@pytest.mark.parametrize("rows", [1, 4])
+def test_tiny_sinusoid_layer(rows):
+    # crates/infr-vulkan/src/adapter.rs:27365-27413: ne = nff = 32, 4 experts, top-2, scale 1.3,
+    # sinusoidal fillers; f32 banks here (the reference quantises them to Q8_0 first)
+    ne = nff = 32
+    n_expert, n_used, scale = 4, 2, 1.3
+    f = lambda i, s: (np.sin(i.astype(F32) * F32(s)) * F32(0.5)).astype(F32)
+    i_r, i_g, i_d = np.arange(n_expert * ne), np.arange(n_expert * nff * ne), np.arange(n_expert * ne * nff)
+    router = (f(i_r, 0.037) + (i_r // ne).astype(F32) * F32(0.15)).astype(F32)
+    gate, up, down = f(i_g, 0.017), f(i_g, 0.023), f(i_d, 0.029)
+    x = (f(np.arange(rows * ne), 0.11) + F32(0.05)).astype(F32).reshape(rows, ne)
+    res = orc.moe_ffn(x, router, gate, up, down, n_expert=n_expert, n_used=n_used, n_ff_exp=nff, scale=scale,
+                      gate_dtype=orc.DT_F32, up_dtype=orc.DT_F32, down_dtype=orc.DT_F32, threads=1)
+    # float64 reference
+    R, G, U, D = (router.reshape(n_expert, ne).astype(np.float64), gate.reshape(n_expert, nff, ne).astype(np.float64),
+                  up.reshape(n_expert, nff, ne).astype(np.float64), down.reshape(n_expert, ne, nff).astype(np.float64))
+    for t in range(rows):
+        xt = x[t].astype(np.float64)
+        lg = R @ xt
+        p = np.exp(lg - lg.max())
+        p /= p.sum()
+        idx = np.argsort(-p, kind="stable")[:n_used]
+        out = np.zeros(ne)
+        for e in idx:
+            g, u = G[e] @ xt, U[e] @ xt
+            out += p[e] / p[idx].sum() * scale * (D[e] @ (g / (1 + np.exp(-g)) * u))
+        assert res.ids[t].tolist() == idx.tolist()
+        assert np.max(np.abs(res.dst[t] - out)) < 1e-4
+
+
+def test_ep_bands_sum_to_full():
+    # Op::MoeFfn::ep_band (crates/infr-core/src/graph.rs:1309-1319): band partials add up
+    L = synth.make_layer(3, 256, 8, 256, router_std=0.05)
+    x = synth.activations(4, 3, 256)
+    kw = dict(n_expert=8, n_used=2, n_ff_exp=256)
+    full = orc.moe_ffn(x, L.router, L.gate, L.up, L.down, **kw)
+    parts = [orc.moe_ffn(x, L.router, L.gate, L.up, L.down, ep_band=(lo, 4), **kw) for lo in (0, 4)]
+    assert np.array_equal(parts[0].ids, full.ids)
+    np.testing.assert_allclose(parts[0].dst + parts[1].dst, full.dst, rtol=1e-5, atol=1e-7)
+
+
+def test_elementwise_ops():
+    rng = np.random.default_rng(0)
+    x, w = rng.normal(size=(3, 64)).astype(F32), rng.normal(size=64).astype(F32)
+    got = orc.rmsnorm(x, w, 1e-6)
+    want = x / np.sqrt((x.astype(np.float64) ** 2).mean(1, keepdims=True) + 1e-6) * w
+    np.testing.assert_allclose(got, want, rtol=2e-6)
+    g = rng.normal(size=(3, 64)).astype(F32)
+    np.testing.assert_allclose(orc.gated_act_silu(g, x), g / (1 + np.exp(-g)) * x, rtol=2e-6)
+    gate = rng.normal(size=3).astype(F32)
+    np.testing.assert_allclose(orc.moe_shared_add(x, g, gate), x + (1 / (1 + np.exp(-gate)))[:, None] * g, rtol=2e-6, atol=1e-7)
+    assert np.array_equal(orc.add(x, g), x + g)
