@@ -138,6 +138,31 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* desc
  * norm_w, groups); bank and dst fields are ignored.  ids_out and wts_out are required. */
 int32_t infr_cuda_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* desc);
 
+/* Routing for callers that must not allocate.  It has no counterpart in the reference.
+ *
+ * Some hosts cannot let a library call cudaMalloc: a serving process that has handed all device
+ * memory to its own pool (a late cudaMalloc there simply fails), or a latency-critical loop that
+ * cannot afford the device-wide synchronisation an allocation implies.  `infr_cuda_moe_route`
+ * grows per-context scratch on demand; this variant does the same computation (router logits in
+ * the CPU's accumulation order, gating, top-k, routing weights) with its scratch in a fixed array
+ * inside the library image: 8 rows x 1024 experts of f32 logits plus a counter, 33 KB, held by
+ * every GPU that loads the library until the process exits.  Larger calls are rejected with
+ * INFR_CUDA_ERR_INVALID_ARG and a message; nothing here calls cudaMalloc, cudaFree or any
+ * allocating routine.  All arguments are plain device pointers (inputs and outputs stay the
+ * caller's); `cuda_stream` is a cudaStream_t (NULL = the legacy default stream); `err`/`err_cap`
+ * optionally receive the error text.
+ *
+ * The first call on a device looks up the device address of the array (cudaGetSymbolAddress) with
+ * that device current, so make that first call before starting any stream capture.  Every call
+ * shares the one array: it keeps the previous call's logits (each call overwrites the part it
+ * uses and clears its counter first), and two calls that overlap on the GPU race on it - keep
+ * calls on one device ordered on one stream. */
+int32_t infr_cuda_moe_route_noalloc(int32_t device, void* cuda_stream, const float* router_x, const float* router,
+                                    const float* exp_probs_b, int32_t* ids_out, float* wts_out, uint32_t rows,
+                                    uint32_t ne, uint32_t n_expert, uint32_t n_used, float scale, uint32_t gating,
+                                    uint32_t norm_w, uint32_t n_expert_groups, uint32_t n_expert_groups_used,
+                                    char* err, size_t err_cap);
+
 /* ---- the ops around it (shared expert and the 40-layer stack) --------------------------------- */
 
 /* Op::Linear (crates/infr-cpu/src/lib.rs:1275-1328): y[m, out_f] = x[m, in_f] · Wᵀ, W row-major
