@@ -371,6 +371,15 @@ class CudaBackend:
         d = op.to_desc()
         self._check(self._lib.infr_cuda_moe_route(self._ctx, C.byref(d)))
 
+    def moe_expert_rows(self, x_rows: Buffer, seg_off: Buffer, gate_exps: Buffer, up_exps: Buffer, down_exps: Buffer,
+                        y_rows: Buffer, n_rows: int, n_local: int, ne: int, n_ff_exp: int,
+                        gate_dtype: DType = DType.Q4K, up_dtype: DType = DType.Q4K, down_dtype: DType = DType.Q6K) -> None:
+        """Expert FFN over rows already grouped by local expert (what an expert-parallel rank runs
+        between the dispatch and the combine exchange, crates/infr-vulkan/src/ep.rs:454-493)."""
+        self._check(self._lib.infr_cuda_moe_expert_rows(self._ctx, x_rows.handle, seg_off.handle, gate_exps.handle,
+                                                        up_exps.handle, down_exps.handle, y_rows.handle, n_rows, n_local,
+                                                        ne, n_ff_exp, int(gate_dtype), int(up_dtype), int(down_dtype)))
+
     def linear(self, dtype: DType, w: Buffer, x: Buffer, y: Buffer, m: int, in_f: int, out_f: int) -> None:
         self._check(self._lib.infr_cuda_linear(self._ctx, int(dtype), w.handle, x.handle, y.handle, m, in_f, out_f))
 

@@ -463,7 +463,51 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.ep_n = d->ep_n_local;
     return launch_decode_ffn(ctx, dp, true, stages);
   }
-  return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: the grouped-GEMM path is not built yet");
+  // batched path: router GEMM + top-k, permute, grouped GEMMs, un-permute combine
+  if (d->ne % 64 || d->n_ff_exp % 64) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: batched path needs ne and n_ff_exp multiples of 64");
+  if (has_sh && d->sh_ff != d->n_ff_exp)
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: batched path needs the shared expert as wide as the routed experts");
+  if ((uint64_t)d->rows * d->n_used > (1u << 24)) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: more than 2^24 (token, expert) pairs per call");
+  {
+    const int n_pairs = (int)(d->rows * d->n_used);
+    const int shared_rows = has_sh ? (int)d->rows : 0;
+    const int rows_bound = n_pairs + shared_rows;
+    Scratch sz = carve(nullptr, d, false);
+    const size_t gbytes = grouped_scratch_bytes(rows_bound, n_pairs, (int)d->n_expert + 1, (int)d->ne, (int)d->n_ff_exp);
+    if ((rc = ensure_scratch(ctx, sz.total + gbytes))) return rc;
+    Scratch s = carve(ctx->scratch, d, false);
+    RouteParams rp = route_params(ctx, d, s, true);
+    const uint32_t stages = d->stages ? d->stages : 7u;
+    if ((stages & 1u) && (rc = launch_route(ctx, rp, false))) return rc;
+    if (!(stages & 6u)) return INFR_CUDA_OK;
+    GroupedCall c = {};
+    c.scratch = static_cast<char*>(ctx->scratch) + sz.total;
+    c.x = static_cast<const float*>(d->x->ptr);
+    c.ids = rp.ids;
+    c.wts = rp.wts;
+    c.sh_logit = (has_sh && d->sh_gate_inp) ? s.sh_logit : nullptr;
+    c.dst = static_cast<float*>(d->dst->ptr);
+    c.gate = static_cast<const uint8_t*>(d->gate_exps->ptr);
+    c.up = static_cast<const uint8_t*>(d->up_exps->ptr);
+    c.down = static_cast<const uint8_t*>(d->down_exps->ptr);
+    c.sh_gate = has_sh ? static_cast<const uint8_t*>(d->sh_gate->ptr) : nullptr;
+    c.sh_up = has_sh ? static_cast<const uint8_t*>(d->sh_up->ptr) : nullptr;
+    c.sh_down = has_sh ? static_cast<const uint8_t*>(d->sh_down->ptr) : nullptr;
+    c.gate_stride = (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
+    c.up_stride = c.gate_stride;
+    c.down_stride = (size_t)d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
+    c.rows = (int)d->rows;
+    c.n_used = (int)d->n_used;
+    c.n_pairs = n_pairs;
+    c.ne = (int)d->ne;
+    c.nff = (int)d->n_ff_exp;
+    c.n_expert = (int)d->n_expert;
+    c.shared_rows = shared_rows;
+    c.rows_bound = rows_bound;
+    c.ep_lo = d->ep_lo;
+    c.ep_n = d->ep_n_local;
+    return launch_grouped_ffn(ctx, c);
+  }
 }
 
 // ---- the ops around it --------------------------------------------------------------------------
@@ -521,11 +565,44 @@ int32_t infr_cuda_add(infr_cuda_ctx* ctx, const infr_cuda_buf* a, const infr_cud
   return launch_add(ctx, static_cast<const float*>(a->ptr), static_cast<const float*>(b->ptr), static_cast<float*>(dst->ptr), n);
 }
 
-int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf*, const infr_cuda_buf*, const infr_cuda_buf*,
-                                  const infr_cuda_buf*, const infr_cuda_buf*, infr_cuda_buf*, uint32_t, uint32_t, uint32_t,
-                                  uint32_t, int32_t, int32_t, int32_t) {
+int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_rows, const infr_cuda_buf* seg_off,
+                                  const infr_cuda_buf* gate_exps, const infr_cuda_buf* up_exps, const infr_cuda_buf* down_exps,
+                                  infr_cuda_buf* y_rows, uint32_t n_rows, uint32_t n_local, uint32_t ne, uint32_t n_ff_exp,
+                                  int32_t gate_dtype, int32_t up_dtype, int32_t down_dtype) {
   if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
-  return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: the grouped-GEMM path is not built yet");
+  if (!n_local || !ne || !n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: zero dimension");
+  if (n_local > 1024) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: more than 1024 local experts");
+  if (gate_dtype != INFR_CUDA_DT_Q4K || up_dtype != INFR_CUDA_DT_Q4K || down_dtype != INFR_CUDA_DT_Q6K)
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be gate/up Q4_K and down Q6_K");
+  if (ne % 256 || n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: ne and n_ff_exp must be multiples of 256");
+  if (!n_rows) return INFR_CUDA_OK;
+  const size_t gb = (size_t)n_local * n_ff_exp * row_bytes(gate_dtype, ne), db = (size_t)n_local * ne * row_bytes(down_dtype, n_ff_exp);
+  if (!fits(x_rows, (size_t)n_rows * ne * 4) || !fits(y_rows, (size_t)n_rows * ne * 4) || !fits(seg_off, (size_t)(n_local + 1) * 4) ||
+      !fits(gate_exps, gb) || !fits(up_exps, gb) || !fits(down_exps, db))
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: buffer missing or too small");
+  DeviceGuard g(ctx->device);
+  const size_t gbytes = grouped_scratch_bytes((int)n_rows, 1, (int)n_local + 1, (int)ne, (int)n_ff_exp);
+  int32_t rc = ensure_scratch(ctx, gbytes);
+  if (rc) return rc;
+  GroupedCall c = {};
+  c.scratch = ctx->scratch;
+  c.x = static_cast<const float*>(x_rows->ptr);
+  c.seg_off_in = static_cast<const int*>(seg_off->ptr);
+  c.y_out = static_cast<float*>(y_rows->ptr);
+  c.gate = static_cast<const uint8_t*>(gate_exps->ptr);
+  c.up = static_cast<const uint8_t*>(up_exps->ptr);
+  c.down = static_cast<const uint8_t*>(down_exps->ptr);
+  c.gate_stride = (size_t)n_ff_exp * row_bytes(gate_dtype, ne);
+  c.up_stride = c.gate_stride;
+  c.down_stride = (size_t)ne * row_bytes(down_dtype, n_ff_exp);
+  c.rows = (int)n_rows;
+  c.n_used = 1;
+  c.n_pairs = 1;
+  c.ne = (int)ne;
+  c.nff = (int)n_ff_exp;
+  c.n_expert = (int)n_local;
+  c.rows_bound = (int)n_rows;
+  return launch_grouped_ffn(ctx, c);
 }
 
 }  // extern "C"

@@ -40,6 +40,39 @@ struct DecodeParams {
   uint32_t ep_lo, ep_n;  // band (ep_n == 0: off)
 };
 
+// Device-side view of one grouped-GEMM launch (see grouped_ffn.cu).
+struct GroupedParams {
+  const int *tile_expert, *tile_row0, *tile_rows, *n_tiles;  // tile table built on the device
+  const __half* xg;  // [rows, ne]  token rows grouped by expert, f16, K order 0,2,1,3 per four
+  __half* act;       // [rows, nff] same grouping and K order
+  float* y;          // [rows, ne]
+  const uint8_t *gate, *up, *down;
+  const uint8_t *sh_gate, *sh_up, *sh_down;  // segment index n_expert = the shared expert
+  size_t gate_stride, up_stride, down_stride;
+  int ne, nff, n_expert;
+};
+
+// Host-side description of one batched expert-FFN call.
+struct GroupedCall {
+  void* scratch;           // grouped_scratch_bytes(...) bytes
+  const float* x;          // [rows, ne] f32 tokens (routed call) or rows grouped by expert
+  const int32_t* ids;      // [rows, n_used] or null when the rows are already grouped
+  const float* wts;        // [rows, n_used]
+  const float* sh_logit;   // [rows] or null
+  const int* seg_off_in;   // [n_expert + 1] device offsets (grouped-rows form)
+  float* dst;              // [rows, ne] combined output, or null (grouped-rows form)
+  float* y_out;            // grouped-rows form: per-row outputs [rows, ne]; null = scratch
+  const uint8_t *gate, *up, *down, *sh_gate, *sh_up, *sh_down;
+  size_t gate_stride, up_stride, down_stride;
+  int rows, n_used, n_pairs, ne, nff, n_expert;
+  int shared_rows;         // rows of the shared-expert segment (rows or 0)
+  int rows_bound;          // upper bound on grouped rows including the shared segment
+  uint32_t ep_lo, ep_n;
+};
+
+size_t grouped_scratch_bytes(int rows_total, int n_pairs, int n_seg, int ne, int nff);
+int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c);
+
 int32_t launch_route(infr_cuda_ctx* ctx, const RouteParams& p, bool pdl);
 int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages);
 // Whether the small-m kernels cover this shape (dims, shared-memory budget).
