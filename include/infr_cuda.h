@@ -197,6 +197,16 @@ int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_row
                                   uint32_t n_local, uint32_t ne, uint32_t n_ff_exp, int32_t gate_dtype,
                                   int32_t up_dtype, int32_t down_dtype);
 
+/* The combine a rank runs after the return exchange (the reference sums band partials with an
+ * all-reduce, crates/infr-vulkan/src/ep.rs:483-490; the fixed-order weighted sum is
+ * shaders/moe_scatter_reduce.comp):  dst[t, :] = sum over ranks s (in rank order) of
+ * wts[t, s] * y_rows[pos_of_pair[t*n_used + s], :]  (pairs with pos < 0 contribute nothing), then
+ * + sigmoid(sh_logit[t]) * sh_rows[t, :]  (or + sh_rows[t, :] when sh_logit is NULL) when sh_rows
+ * is given.  y_rows holds n_y_rows rows of ne f32; pos_of_pair is i32. */
+int32_t infr_cuda_moe_combine(infr_cuda_ctx* ctx, const infr_cuda_buf* y_rows, const infr_cuda_buf* pos_of_pair,
+                              const infr_cuda_buf* wts, const infr_cuda_buf* sh_rows, const infr_cuda_buf* sh_logit,
+                              infr_cuda_buf* dst, uint32_t rows, uint32_t n_used, uint32_t ne, uint32_t n_y_rows);
+
 /* ---- record once, replay (Backend::compile + the decode replay of the Vulkan backend) ----------- */
 
 /* The reference records a decode step's dispatches once and replays the command buffer per token

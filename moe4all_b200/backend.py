@@ -28,7 +28,7 @@ EXPORTS = [
     "infr_cuda_sync", "infr_cuda_moe_ffn", "infr_cuda_moe_route", "infr_cuda_linear",
     "infr_cuda_gated_act", "infr_cuda_moe_shared_add", "infr_cuda_rmsnorm", "infr_cuda_add",
     "infr_cuda_moe_expert_rows", "infr_cuda_launch_count",
-    "infr_cuda_graph_begin", "infr_cuda_graph_end", "infr_cuda_graph_launch", "infr_cuda_graph_free", "infr_cuda_set_trace", "infr_cuda_moe_route_noalloc",
+    "infr_cuda_graph_begin", "infr_cuda_graph_end", "infr_cuda_graph_launch", "infr_cuda_graph_free", "infr_cuda_set_trace", "infr_cuda_moe_route_noalloc", "infr_cuda_moe_combine",
 ]
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
@@ -133,6 +133,7 @@ def load_library(path: Optional[str] = None):
     L.infr_cuda_graph_free.argtypes = [vp, vp]
     L.infr_cuda_graph_free.restype = None
     L.infr_cuda_set_trace.argtypes = [vp, vp]
+    L.infr_cuda_moe_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32]
     L.infr_cuda_moe_route_noalloc.argtypes = [i32, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, C.c_float, u32, u32, u32, u32,
                                               C.c_char_p, sz]
     L.infr_cuda_launch_count.argtypes = [vp]
@@ -379,6 +380,12 @@ class CudaBackend:
         self._check(self._lib.infr_cuda_moe_expert_rows(self._ctx, x_rows.handle, seg_off.handle, gate_exps.handle,
                                                         up_exps.handle, down_exps.handle, y_rows.handle, n_rows, n_local,
                                                         ne, n_ff_exp, int(gate_dtype), int(up_dtype), int(down_dtype)))
+
+    def moe_combine(self, y_rows: Buffer, pos_of_pair: Buffer, wts: Buffer, dst: Buffer, rows: int, n_used: int, ne: int,
+                    n_y_rows: int, sh_rows: Optional[Buffer] = None, sh_logit: Optional[Buffer] = None) -> None:
+        """Rank-ordered weighted sum of per-pair expert outputs plus the shared expert."""
+        self._check(self._lib.infr_cuda_moe_combine(self._ctx, y_rows.handle, pos_of_pair.handle, wts.handle, _h(sh_rows),
+                                                    _h(sh_logit), dst.handle, rows, n_used, ne, n_y_rows))
 
     def linear(self, dtype: DType, w: Buffer, x: Buffer, y: Buffer, m: int, in_f: int, out_f: int) -> None:
         self._check(self._lib.infr_cuda_linear(self._ctx, int(dtype), w.handle, x.handle, y.handle, m, in_f, out_f))

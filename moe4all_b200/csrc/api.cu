@@ -605,4 +605,22 @@ int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_row
   return launch_grouped_ffn(ctx, c);
 }
 
+int32_t infr_cuda_moe_combine(infr_cuda_ctx* ctx, const infr_cuda_buf* y_rows, const infr_cuda_buf* pos_of_pair,
+                              const infr_cuda_buf* wts, const infr_cuda_buf* sh_rows, const infr_cuda_buf* sh_logit,
+                              infr_cuda_buf* dst, uint32_t rows, uint32_t n_used, uint32_t ne, uint32_t n_y_rows) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  if (!rows || !n_used || !ne || ne % 4) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_combine: bad dimensions");
+  if (rows > 65535) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_combine: more than 65535 rows per call");
+  if (!fits(y_rows, (size_t)n_y_rows * ne * 4) || !fits(pos_of_pair, (size_t)rows * n_used * 4) ||
+      !fits(wts, (size_t)rows * n_used * 4) || !fits(dst, (size_t)rows * ne * 4))
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_combine: buffer missing or too small");
+  if (sh_rows && !fits(sh_rows, (size_t)rows * ne * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_combine: sh_rows too small");
+  if (sh_logit && (!sh_rows || !fits(sh_logit, (size_t)rows * 4))) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_combine: sh_logit needs sh_rows");
+  DeviceGuard g(ctx->device);
+  return launch_combine(ctx, static_cast<const float*>(y_rows->ptr), static_cast<const int*>(pos_of_pair->ptr),
+                        static_cast<const float*>(wts->ptr), sh_logit ? static_cast<const float*>(sh_logit->ptr) : nullptr,
+                        sh_rows ? static_cast<const float*>(sh_rows->ptr) : nullptr, (int)rows, (int)n_used, (int)ne,
+                        static_cast<float*>(dst->ptr));
+}
+
 }  // extern "C"

@@ -366,11 +366,36 @@ __global__ void __launch_bounds__(GG_THREADS) k_grouped_down(GroupedParams p) {
 
 // ---- un-permute + combine -----------------------------------------------------------------------------
 
-// dst[t, :] = sum over ranks (in rank order) of w * y[pos(t, rank), :], then the shared expert.
+// dst[t, :] = sum over ranks (in rank order) of w * y[pos(t, rank), :], then the shared expert
+// (sh_y = the shared expert's output rows in token order, or null).
 __global__ void __launch_bounds__(256) k_unpermute_combine(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
                                                            const float* __restrict__ wts, const float* __restrict__ sh_logit,
-                                                           const int* __restrict__ seg_off, int n_seg_routed, int has_shared,
-                                                           int rows, int n_used, int ne, float* __restrict__ dst) {
+                                                           const float* __restrict__ sh_y, int rows, int n_used, int ne,
+                                                           float* __restrict__ dst) {
+  const int t = blockIdx.y;
+  const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
+  if (c >= ne) return;
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < n_used; ++s) {
+    const int pos = pos_of_pair[t * n_used + s];
+    if (pos < 0) continue;
+    const float w = wts[t * n_used + s];
+    const float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * ne + c);
+    o.x += w * v.x; o.y += w * v.y; o.z += w * v.z; o.w += w * v.w;
+  }
+  if (sh_y) {
+    const float gsh = sh_logit ? 1.0f / (1.0f + __expf(-sh_logit[t])) : 1.0f;
+    const float4 v = *reinterpret_cast<const float4*>(sh_y + (size_t)t * ne + c);
+    o.x += gsh * v.x; o.y += gsh * v.y; o.z += gsh * v.z; o.w += gsh * v.w;
+  }
+  *reinterpret_cast<float4*>(dst + (size_t)t * ne + c) = o;
+}
+
+// The shared segment starts right after the routed rows: its address is only known on the device.
+__global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
+                                                               const float* __restrict__ wts, const float* __restrict__ sh_logit,
+                                                               const int* __restrict__ seg_off, int n_seg_routed, int has_shared,
+                                                               int rows, int n_used, int ne, float* __restrict__ dst) {
   const int t = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
   if (c >= ne) return;
@@ -504,11 +529,18 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   k_grouped_down<<<dim3(c.ne / TM, max_tiles), GG_THREADS, 0, st>>>(p);
   ctx->launches += 2;
   if (c.dst) {
-    k_unpermute_combine<<<dim3((c.ne / 4 + 255) / 256, c.rows), 256, 0, st>>>(y, pos_of_pair, c.wts, c.sh_logit, seg_off, n_seg_routed,
-                                                                               c.shared_rows > 0 ? 1 : 0, c.rows, c.n_used, c.ne, c.dst);
+    k_unpermute_combine_seg<<<dim3((c.ne / 4 + 255) / 256, c.rows), 256, 0, st>>>(y, pos_of_pair, c.wts, c.sh_logit, seg_off, n_seg_routed,
+                                                                                   c.shared_rows > 0 ? 1 : 0, c.rows, c.n_used, c.ne, c.dst);
     ctx->launches += 1;
   }
   return check_cuda(ctx, cudaGetLastError(), "grouped ffn launch");
+}
+
+int32_t launch_combine(infr_cuda_ctx* ctx, const float* y, const int* pos_of_pair, const float* wts, const float* sh_logit,
+                       const float* sh_y, int rows, int n_used, int ne, float* dst) {
+  k_unpermute_combine<<<dim3((ne / 4 + 255) / 256, rows), 256, 0, ctx->stream>>>(y, pos_of_pair, wts, sh_logit, sh_y, rows, n_used, ne, dst);
+  ctx->launches += 1;
+  return check_cuda(ctx, cudaGetLastError(), "combine launch");
 }
 
 }  // namespace infr

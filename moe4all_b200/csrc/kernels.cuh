@@ -72,6 +72,8 @@ struct GroupedCall {
 
 size_t grouped_scratch_bytes(int rows_total, int n_pairs, int n_seg, int ne, int nff);
 int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c);
+int32_t launch_combine(infr_cuda_ctx* ctx, const float* y, const int* pos_of_pair, const float* wts, const float* sh_logit,
+                       const float* sh_y, int rows, int n_used, int ne, float* dst);
 
 int32_t launch_route(infr_cuda_ctx* ctx, const RouteParams& p, bool pdl);
 int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages);

@@ -26,7 +26,10 @@ def q6k_bank(n_blocks: int, gen, device) -> torch.Tensor:
 class DeviceLayer:
     """One MoE layer's tensors as torch CUDA tensors plus Buffer handles on them."""
 
-    def __init__(self, be, seed, ne, n_expert, n_ff, sh_ff=0, gated_shared=True, device="cuda:0", router_std=0.02):
+    def __init__(self, be, seed, ne, n_expert, n_ff, sh_ff=0, gated_shared=True, device="cuda:0", router_std=0.02,
+                 band=None):
+        """band = (lo, n_local): keep only that slice of the expert banks (an expert-parallel rank);
+        the bytes equal the same slice of the un-banded layer with the same seed."""
         gen = torch.Generator(device=device)
         gen.manual_seed(seed)
         self.ne, self.n_expert, self.n_ff, self.sh_ff = ne, n_expert, n_ff, sh_ff
@@ -41,6 +44,10 @@ class DeviceLayer:
             self.t["sh_down"] = q6k_bank(ne * sh_ff // 256, gen, device)
             if gated_shared:
                 self.t["sh_gate_inp"] = torch.randn(ne, generator=gen, device=device) * router_std
+        if band is not None:
+            lo, n_local = band
+            for k, per in (("gate", n_ff * ne // 256 * 144), ("up", n_ff * ne // 256 * 144), ("down", ne * n_ff // 256 * 210)):
+                self.t[k] = self.t[k][lo * per:(lo + n_local) * per].clone()
         # 16 spare bytes after each bank: block decoders may read a word pair at the very end
         for k in list(self.t):
             v = self.t[k]
