@@ -225,6 +225,11 @@ void infr_cuda_graph_free(infr_cuda_ctx* ctx, infr_cuda_graph* graph);
 
 /* ---- introspection for the test-suite and the benchmark ---------------------------------------- */
 
+/* Checks the tensor-core building blocks of the grouped GEMM in isolation:
+ * c[128, n] (f32) = a[128, 64] (f16) x b[n, 64]^T (f16) through 128-byte-swizzled shared-memory
+ * tiles, tcgen05.mma and tensor memory; n a multiple of 16 in [16, 256].  Test aid, no reference
+ * counterpart. */
+int32_t infr_cuda_umma_selftest(infr_cuda_ctx* ctx, const infr_cuda_buf* a, const infr_cuda_buf* b, infr_cuda_buf* c, uint32_t n);
 /* Number of kernel launches this context has issued since creation (host-side count). */
 uint64_t infr_cuda_launch_count(const infr_cuda_ctx* ctx);
 /* Attach (or with NULL detach) a 4096-byte device buffer into which the decode kernels write

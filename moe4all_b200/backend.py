@@ -28,7 +28,7 @@ EXPORTS = [
     "infr_cuda_sync", "infr_cuda_moe_ffn", "infr_cuda_moe_route", "infr_cuda_linear",
     "infr_cuda_gated_act", "infr_cuda_moe_shared_add", "infr_cuda_rmsnorm", "infr_cuda_add",
     "infr_cuda_moe_expert_rows", "infr_cuda_launch_count",
-    "infr_cuda_graph_begin", "infr_cuda_graph_end", "infr_cuda_graph_launch", "infr_cuda_graph_free", "infr_cuda_set_trace", "infr_cuda_moe_route_noalloc", "infr_cuda_moe_combine",
+    "infr_cuda_graph_begin", "infr_cuda_graph_end", "infr_cuda_graph_launch", "infr_cuda_graph_free", "infr_cuda_set_trace", "infr_cuda_moe_route_noalloc", "infr_cuda_moe_combine", "infr_cuda_umma_selftest",
 ]
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
@@ -133,6 +133,7 @@ def load_library(path: Optional[str] = None):
     L.infr_cuda_graph_free.argtypes = [vp, vp]
     L.infr_cuda_graph_free.restype = None
     L.infr_cuda_set_trace.argtypes = [vp, vp]
+    L.infr_cuda_umma_selftest.argtypes = [vp, vp, vp, vp, u32]
     L.infr_cuda_moe_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32]
     L.infr_cuda_moe_route_noalloc.argtypes = [i32, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, C.c_float, u32, u32, u32, u32,
                                               C.c_char_p, sz]

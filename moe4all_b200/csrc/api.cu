@@ -623,4 +623,14 @@ int32_t infr_cuda_moe_combine(infr_cuda_ctx* ctx, const infr_cuda_buf* y_rows, c
                         static_cast<float*>(dst->ptr));
 }
 
+int32_t infr_cuda_umma_selftest(infr_cuda_ctx* ctx, const infr_cuda_buf* a, const infr_cuda_buf* b, infr_cuda_buf* c, uint32_t n) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  if (n < 16 || n > 256 || n % 16) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "umma_selftest: n must be a multiple of 16 in [16, 256]");
+  if (!fits(a, 128 * 64 * 2) || !fits(b, (size_t)n * 64 * 2) || !fits(c, (size_t)128 * n * 4))
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "umma_selftest: buffer missing or too small");
+  DeviceGuard g(ctx->device);
+  return launch_umma_selftest(ctx, static_cast<const __half*>(a->ptr), static_cast<const __half*>(b->ptr),
+                              static_cast<float*>(c->ptr), (int)n);
+}
+
 }  // extern "C"

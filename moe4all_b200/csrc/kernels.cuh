@@ -75,6 +75,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c);
 int32_t launch_combine(infr_cuda_ctx* ctx, const float* y, const int* pos_of_pair, const float* wts, const float* sh_logit,
                        const float* sh_y, int rows, int n_used, int ne, float* dst);
 
+int32_t launch_umma_selftest(infr_cuda_ctx* ctx, const __half* a, const __half* b, float* c, int n);
 int32_t launch_route(infr_cuda_ctx* ctx, const RouteParams& p, bool pdl);
 int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages);
 // Whether the small-m kernels cover this shape (dims, shared-memory budget).
