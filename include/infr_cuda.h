@@ -119,7 +119,8 @@ typedef struct infr_cuda_moe_ffn_desc {
   const infr_cuda_buf* sh_gate_inp; /* [ne] f32 gate vector, or NULL for the ungated sum           */
   uint32_t sh_ff;
   uint32_t path;                    /* 0 = choose by rows; 1 = force the small-m (decode) kernels;
-                                       2 = force the grouped-GEMM (prefill) kernels                */
+                                       2 = force the grouped-GEMM (prefill) kernels; 3 = same with
+                                       the legacy mma.sync tiles instead of tcgen05               */
   uint32_t stages;                  /* 0 = the whole op.  Otherwise a mask of the kernels to launch,
                                        for timing one of them alone: 1 router + top-k, 2 gate/up,
                                        4 down + combine.  Later stages read what an earlier full

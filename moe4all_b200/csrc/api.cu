@@ -506,6 +506,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     c.rows_bound = rows_bound;
     c.ep_lo = d->ep_lo;
     c.ep_n = d->ep_n_local;
+    c.legacy = (path == 3) ? 1 : 0;
     return launch_grouped_ffn(ctx, c);
   }
 }

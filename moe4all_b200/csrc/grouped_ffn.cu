@@ -56,7 +56,7 @@ __global__ void k_pair_count(const int32_t* __restrict__ ids, int n_pairs, int n
 
 // One CTA: exclusive scan of the per-expert counts, the tile table (one entry per 64 rows of a
 // segment, the shared expert's rows appended as segment n_expert), and the fill cursors reset.
-__global__ void __launch_bounds__(1024) k_segment_scan(const int* __restrict__ counts, int n_expert, int shared_rows,
+__global__ void __launch_bounds__(1024) k_segment_scan(const int* __restrict__ counts, int n_expert, int shared_rows, int tn,
                                                        int* __restrict__ seg_off, int* __restrict__ fill,
                                                        int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                                        int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(1024) k_segment_scan(const int* __restrict__ c
       s_off[e] = off;
       s_toff[e] = toff;
       off += s_cnt[e];
-      toff += (s_cnt[e] + TN - 1) / TN;
+      toff += (s_cnt[e] + tn - 1) / tn;
     }
     s_off[n_seg] = off;
     s_toff[n_seg] = toff;
@@ -82,11 +82,11 @@ __global__ void __launch_bounds__(1024) k_segment_scan(const int* __restrict__ c
   for (int e = tid; e <= n_seg; e += 1024) seg_off[e] = s_off[e];
   for (int e = tid; e < n_expert; e += 1024) fill[e] = 0;
   for (int e = tid; e < n_seg; e += 1024) {
-    const int nt = (s_cnt[e] + TN - 1) / TN;
+    const int nt = (s_cnt[e] + tn - 1) / tn;
     for (int t = 0; t < nt; ++t) {
       tile_expert[s_toff[e] + t] = e;
-      tile_row0[s_toff[e] + t] = s_off[e] + t * TN;
-      tile_rows[s_toff[e] + t] = min(TN, s_cnt[e] - t * TN);
+      tile_row0[s_toff[e] + t] = s_off[e] + t * tn;
+      tile_rows[s_toff[e] + t] = min(tn, s_cnt[e] - t * tn);
     }
   }
 }
@@ -416,7 +416,7 @@ __global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __re
 }
 
 // Tile table straight from caller-provided segment offsets (rows already grouped by expert).
-__global__ void __launch_bounds__(1024) k_tiles_from_offsets(const int* __restrict__ seg_off, int n_seg,
+__global__ void __launch_bounds__(1024) k_tiles_from_offsets(const int* __restrict__ seg_off, int n_seg, int tn,
                                                              int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                                              int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
   __shared__ int s_toff[1026];
@@ -425,18 +425,18 @@ __global__ void __launch_bounds__(1024) k_tiles_from_offsets(const int* __restri
     int toff = 0;
     for (int e = 0; e < n_seg; ++e) {
       s_toff[e] = toff;
-      toff += (seg_off[e + 1] - seg_off[e] + TN - 1) / TN;
+      toff += (seg_off[e + 1] - seg_off[e] + tn - 1) / tn;
     }
     *n_tiles = toff;
   }
   __syncthreads();
   for (int e = tid; e < n_seg; e += 1024) {
     const int cnt = seg_off[e + 1] - seg_off[e];
-    const int nt = (cnt + TN - 1) / TN;
+    const int nt = (cnt + tn - 1) / tn;
     for (int t = 0; t < nt; ++t) {
       tile_expert[s_toff[e] + t] = e;
-      tile_row0[s_toff[e] + t] = seg_off[e] + t * TN;
-      tile_rows[s_toff[e] + t] = min(TN, cnt - t * TN);
+      tile_row0[s_toff[e] + t] = seg_off[e] + t * tn;
+      tile_rows[s_toff[e] + t] = min(tn, cnt - t * tn);
     }
   }
 }
@@ -444,7 +444,7 @@ __global__ void __launch_bounds__(1024) k_tiles_from_offsets(const int* __restri
 }  // namespace
 
 size_t grouped_scratch_bytes(int rows_total, int n_pairs, int n_seg, int ne, int nff) {
-  const size_t rows_pad = (size_t)rows_total + TN;
+  const size_t rows_pad = (size_t)rows_total + 256;
   size_t b = 0;
   b += align_up((size_t)(n_seg + 2) * 4, 256) * 3;                 // counts, seg_off, fill
   b += align_up((size_t)(rows_total / TN + n_seg + 2) * 4, 256) * 3 + 256;  // tile table + n_tiles
@@ -467,19 +467,22 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   const int n_seg_routed = c.n_expert;
   const int n_seg = c.n_expert + (c.shared_rows > 0 ? 1 : 0);
   const int rows_total = c.rows_bound;  // upper bound on sorted rows + shared rows
-  const int max_tiles = rows_total / TN + n_seg + 1;
+  const bool use_umma = !c.legacy && umma_grouped_supported(c.ne, c.nff);
+  const int tn = use_umma ? umma_tile_rows() : TN;
+  const int max_tiles = rows_total / tn + n_seg + 1;
+  const int max_tiles_alloc = rows_total / TN + n_seg + 1;
   int* counts = reinterpret_cast<int*>(take((size_t)(n_seg + 2) * 4));
   int* seg_off = reinterpret_cast<int*>(take((size_t)(n_seg + 2) * 4));
   int* fill = reinterpret_cast<int*>(take((size_t)(n_seg + 2) * 4));
-  int* tile_expert = reinterpret_cast<int*>(take((size_t)(max_tiles + 1) * 4));
-  int* tile_row0 = reinterpret_cast<int*>(take((size_t)(max_tiles + 1) * 4));
-  int* tile_rows = reinterpret_cast<int*>(take((size_t)(max_tiles + 1) * 4));
+  int* tile_expert = reinterpret_cast<int*>(take((size_t)(max_tiles_alloc + 1) * 4));
+  int* tile_row0 = reinterpret_cast<int*>(take((size_t)(max_tiles_alloc + 1) * 4));
+  int* tile_rows = reinterpret_cast<int*>(take((size_t)(max_tiles_alloc + 1) * 4));
   int* n_tiles = reinterpret_cast<int*>(take(256));
   int* pos_of_pair = reinterpret_cast<int*>(take((size_t)(c.n_pairs + 1) * 4));
   int* pair_of_pos = reinterpret_cast<int*>(take((size_t)(c.n_pairs + 1) * 4));
-  __half* xg = reinterpret_cast<__half*>(take(((size_t)rows_total + TN) * c.ne * 2));
-  __half* act = reinterpret_cast<__half*>(take(((size_t)rows_total + TN) * c.nff * 2));
-  float* y = c.y_out ? c.y_out : reinterpret_cast<float*>(take(((size_t)rows_total + TN) * c.ne * 4));
+  __half* xg = reinterpret_cast<__half*>(take(((size_t)rows_total + 256) * c.ne * 2));
+  __half* act = reinterpret_cast<__half*>(take(((size_t)rows_total + 256) * c.nff * 2));
+  float* y = c.y_out ? c.y_out : reinterpret_cast<float*>(take(((size_t)rows_total + 256) * c.ne * 4));
   cudaStream_t st = ctx->stream;
 
   if (c.ids) {
@@ -487,7 +490,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
     cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)(n_seg + 2) * 4, st);
     if (e != cudaSuccess) return check_cuda(ctx, e, "grouped: memset");
     k_pair_count<<<(c.n_pairs + 255) / 256, 256, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, counts);
-    k_segment_scan<<<1, 1024, 0, st>>>(counts, c.n_expert, c.shared_rows, seg_off, fill, tile_expert, tile_row0, tile_rows, n_tiles);
+    k_segment_scan<<<1, 1024, 0, st>>>(counts, c.n_expert, c.shared_rows, tn, seg_off, fill, tile_expert, tile_row0, tile_rows, n_tiles);
     k_pair_scatter<<<(c.n_pairs + 255) / 256, 256, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, seg_off, fill,
                                                              pos_of_pair, pair_of_pos);
     ctx->launches += 3;
@@ -495,7 +498,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
     ctx->launches += 1;
   } else {
     // rows already grouped: offsets come from the caller (n_expert segments, no shared segment)
-    k_tiles_from_offsets<<<1, 1024, 0, st>>>(c.seg_off_in, c.n_expert, tile_expert, tile_row0, tile_rows, n_tiles);
+    k_tiles_from_offsets<<<1, 1024, 0, st>>>(c.seg_off_in, c.n_expert, tn, tile_expert, tile_row0, tile_rows, n_tiles);
     // gather with identity order: seg_off_in[n_expert] rows; reuse the same kernel with a
     // two-entry offset view (sorted rows = all rows, shared rows = none)
     cudaError_t e = cudaMemcpyAsync(seg_off, c.seg_off_in + c.n_expert, 4, cudaMemcpyDeviceToDevice, st);
@@ -525,9 +528,15 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   p.ne = c.ne;
   p.nff = c.nff;
   p.n_expert = c.n_expert;
-  k_grouped_gateup<<<dim3(c.nff / TM, max_tiles), GG_THREADS, 0, st>>>(p);
-  k_grouped_down<<<dim3(c.ne / TM, max_tiles), GG_THREADS, 0, st>>>(p);
-  ctx->launches += 2;
+  p.status = ctx->status;
+  if (use_umma) {
+    const int32_t rc = launch_umma_grouped(ctx, p, max_tiles);
+    if (rc) return rc;
+  } else {
+    k_grouped_gateup<<<dim3(c.nff / TM, max_tiles), GG_THREADS, 0, st>>>(p);
+    k_grouped_down<<<dim3(c.ne / TM, max_tiles), GG_THREADS, 0, st>>>(p);
+    ctx->launches += 2;
+  }
   if (c.dst) {
     k_unpermute_combine_seg<<<dim3((c.ne / 4 + 255) / 256, c.rows), 256, 0, st>>>(y, pos_of_pair, c.wts, c.sh_logit, seg_off, n_seg_routed,
                                                                                    c.shared_rows > 0 ? 1 : 0, c.rows, c.n_used, c.ne, c.dst);

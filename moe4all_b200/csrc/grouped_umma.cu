@@ -1,0 +1,356 @@
+// Grouped expert GEMMs on the 5th-generation tensor cores (tcgen05, accumulators in tensor memory).
+//
+// Same contract as the legacy-MMA kernels of grouped_ffn.cu (reference: CPU stages B-D
+// crates/infr-cpu/src/lib.rs:4051-4266; Vulkan native_gemm_mmq_q4k/q6k.comp): per expert segment
+//   act = silu(Wg x) * (Wu x)      (k_umma_gateup, Q4_K weights)
+//   y   = Wd act                   (k_umma_down,   Q6_K weights)
+// with the weights as the M operand (128 output features per CTA) and up to 256 token rows as the
+// N operand, so every weight block is unpacked once per 256 tokens.
+//
+// Warp roles (9 warps): warps 0-7 are producers - each thread owns one weight row of the tile,
+// unpacks its 64 weights of the K step to f16 straight into the 128-byte-swizzled operand tile,
+// and copies one token row's 128 bytes with cp.async; warp 8 issues the MMAs (one thread) and
+// releases each pipeline stage with tcgen05.commit.  After the K loop the producers drain the
+// accumulators with tcgen05.ld and write the result.  Stages are handed over through mbarriers;
+// every wait is bounded.
+#include "kernels.cuh"
+#include "umma.cuh"
+
+namespace infr {
+namespace {
+
+constexpr int UM = 128;           // weight rows per role and CTA
+constexpr int UN = 256;           // max token rows per CTA
+constexpr int UK = 64;            // K elements per stage
+constexpr int U_PRODUCERS = 256;  // producer threads
+constexpr int U_THREADS = U_PRODUCERS + 32;
+constexpr float W_PRESCALE = 256.0f;
+constexpr float W_POSTSCALE = 1.0f / 256.0f;
+constexpr uint32_t A_TILE_BYTES = UM * 128;  // 16 KB
+constexpr uint32_t B_TILE_BYTES = UN * 128;  // 32 KB
+
+__device__ __forceinline__ int kperm(int k) {
+  const int r = k & 3;
+  return (k & ~3) | (r == 1 ? 2 : (r == 2 ? 1 : r));
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+__device__ __forceinline__ void q4_word_to_h2(uint32_t w, __half2 s, __half2 m, uint32_t& out02, uint32_t& out13) {
+  const __half2 k1024 = __float2half2_rn(1024.f);
+  const __half2 a = __hsub2(u32_as_h2((w & 0x000F000Fu) | 0x64006400u), k1024);
+  const __half2 b = __hsub2(u32_as_h2(((w >> 8) & 0x000F000Fu) | 0x64006400u), k1024);
+  out02 = h2_as_u32(__hfma2(a, s, m));
+  out13 = h2_as_u32(__hfma2(b, s, m));
+}
+
+__device__ __forceinline__ void q6_word_to_h2(uint32_t c, __half2 s, uint32_t& out02, uint32_t& out13) {
+  const __half2 k1056 = __float2half2_rn(1056.f);
+  const __half2 a = __hsub2(u32_as_h2((c & 0x00FF00FFu) | 0x64006400u), k1056);
+  const __half2 b = __hsub2(u32_as_h2(((c >> 8) & 0x00FF00FFu) | 0x64006400u), k1056);
+  out02 = h2_as_u32(__hmul2(a, s));
+  out13 = h2_as_u32(__hmul2(b, s));
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// One token row's 64 K elements (128 B) into the swizzled B tile.
+__device__ __forceinline__ void copy_token_row(unsigned char* tB, int row, const __half* src) {
+#pragma unroll
+  for (int c = 0; c < 8; ++c) cp_async16(tB + umma::swz128_offset(row, c), src + c * 8);
+}
+
+struct PipeBars {
+  uint64_t full[4];
+  uint64_t empty[4];
+  uint64_t done;
+};
+
+// Shared pipeline skeleton.  `unpack(stage_ptr, step)` is run by every producer thread;
+// `issue(stage_ptr, step)` by the MMA thread.
+template <int STAGES, typename Unpack, typename Issue>
+__device__ __forceinline__ bool run_pipeline(PipeBars& bars, unsigned char* stages, uint32_t stage_bytes, int n_steps,
+                                             Unpack unpack, Issue issue) {
+  const int tid = threadIdx.x;
+  bool ok = true;
+  if (tid < U_PRODUCERS) {
+    for (int step = 0; step < n_steps && ok; ++step) {
+      const int s = step % STAGES, use = step / STAGES;
+      if (!mbar_wait_bounded(&bars.empty[s], (use & 1) ^ 1)) { ok = false; break; }
+      unpack(stages + (size_t)s * stage_bytes, step);
+      cp_async_wait_all();
+      umma::fence_proxy_async();
+      mbar_arrive(&bars.full[s]);
+    }
+  } else if (tid == U_PRODUCERS) {
+    for (int step = 0; step < n_steps && ok; ++step) {
+      const int s = step % STAGES, use = step / STAGES;
+      if (!mbar_wait_bounded(&bars.full[s], use & 1)) { ok = false; break; }
+      umma::fence_after_sync();
+      issue(stages + (size_t)s * stage_bytes, step);
+      umma::commit(&bars.empty[s]);
+    }
+    umma::commit(&bars.done);
+  }
+  return ok;
+}
+
+// ---- gate/up + SwiGLU ---------------------------------------------------------------------------
+
+constexpr int GU_STAGES = 3;
+constexpr uint32_t GU_STAGE_BYTES = 2 * A_TILE_BYTES + B_TILE_BYTES;  // 64 KB
+
+__global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) PipeBars bars;
+  __shared__ uint32_t s_tmem;
+  const int tile = blockIdx.y;
+  if (tile >= *p.n_tiles) return;
+  unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int e = p.tile_expert[tile], row0 = p.tile_row0[tile], rows_valid = p.tile_rows[tile];
+  const int n_eff = (rows_valid + 15) & ~15;
+  const int f0 = blockIdx.x * UM;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rb = p.ne / 256 * (int)Q4K_BLOCK_BYTES;
+  const bool shared_seg = e >= p.n_expert;
+
+  if (tid == 0) {
+    for (int s = 0; s < GU_STAGES; ++s) {
+      mbar_init(&bars.full[s], U_PRODUCERS);
+      mbar_init(&bars.empty[s], 1);
+    }
+    mbar_init(&bars.done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 8) umma::tmem_alloc(&s_tmem, 512);
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = s_tmem;
+
+  // producer identity: role 0 = gate rows, role 1 = up rows; every producer also owns a token row
+  const int role = (tid >> 7) & 1, wrow = tid & 127;
+  const uint8_t* wbase = role == 0 ? (shared_seg ? p.sh_gate : p.gate + (size_t)e * p.gate_stride)
+                                   : (shared_seg ? p.sh_up : p.up + (size_t)e * p.up_stride);
+  const uint8_t* wrow_ptr = wbase + (size_t)(f0 + wrow) * rb;
+  const __half* tok_ptr = p.xg + (size_t)(row0 + tid) * p.ne;
+  const bool tok_on = tid < rows_valid;
+  const uint32_t idesc = umma::idesc_f16_f32(UM, n_eff);
+
+  // raw weight words of the next step are fetched while the current step is unpacked
+  uint4 hdr = __ldg(reinterpret_cast<const uint4*>(wrow_ptr));
+  uint4 q0 = __ldg(reinterpret_cast<const uint4*>(wrow_ptr + 16)), q1 = __ldg(reinterpret_cast<const uint4*>(wrow_ptr + 32));
+
+  auto unpack = [&](unsigned char* st, int step) {
+    unsigned char* tA = st + (size_t)role * A_TILE_BYTES;
+    unsigned char* tB = st + 2 * A_TILE_BYTES;
+    if (tok_on) copy_token_row(tB, tid, tok_ptr + (size_t)step * UK);
+    const int j = step & 3;
+    const uint4 ch = hdr, c0 = q0, c1 = q1;
+    if (step + 1 < p.ne / UK) {  // prefetch the next 64-group of this row
+      const int nb = (step + 1) >> 2, nj = (step + 1) & 3;
+      const uint8_t* bp = wrow_ptr + (size_t)nb * Q4K_BLOCK_BYTES;
+      if (nj == 0) hdr = __ldg(reinterpret_cast<const uint4*>(bp));
+      q0 = __ldg(reinterpret_cast<const uint4*>(bp + 16 + 32 * nj));
+      q1 = __ldg(reinterpret_cast<const uint4*>(bp + 32 + 32 * nj));
+    }
+    uint32_t scp, mp;
+    q4k_scale_min_pair(ch.y, ch.z, ch.w, j, scp, mp);
+    const float d = f16_bits_to_f32(ch.x) * W_PRESCALE, dmin = f16_bits_to_f32(ch.x >> 16) * W_PRESCALE;
+    const __half2 s_lo = __float2half2_rn(d * (float)(scp & 0xFFu)), s_hi = __float2half2_rn(d * (float)(scp >> 8));
+    const __half2 m_lo = __float2half2_rn(-dmin * (float)(mp & 0xFFu)), m_hi = __float2half2_rn(-dmin * (float)(mp >> 8));
+    const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // chunk c: K positions 8c..8c+7 (low nibbles), 32+8c.. (high nibbles)
+      uint4 lo, hi;
+      q4_word_to_h2(w[2 * c], s_lo, m_lo, lo.x, lo.y);
+      q4_word_to_h2(w[2 * c + 1], s_lo, m_lo, lo.z, lo.w);
+      q4_word_to_h2(w[2 * c] >> 4, s_hi, m_hi, hi.x, hi.y);
+      q4_word_to_h2(w[2 * c + 1] >> 4, s_hi, m_hi, hi.z, hi.w);
+      *reinterpret_cast<uint4*>(tA + umma::swz128_offset(wrow, c)) = lo;
+      *reinterpret_cast<uint4*>(tA + umma::swz128_offset(wrow, 4 + c)) = hi;
+    }
+  };
+  auto issue = [&](unsigned char* st, int step) {
+    unsigned char* tB = st + 2 * A_TILE_BYTES;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint64_t bd = umma::smem_desc_k_major_swz128(tB, k);
+      umma::mma_f16(tmem, umma::smem_desc_k_major_swz128(st, k), bd, idesc, step > 0 || k > 0);
+      umma::mma_f16(tmem + 256, umma::smem_desc_k_major_swz128(st + A_TILE_BYTES, k), bd, idesc, step > 0 || k > 0);
+    }
+  };
+  bool ok = run_pipeline<GU_STAGES>(bars, stages, GU_STAGE_BYTES, p.ne / UK, unpack, issue);
+
+  // epilogue: producers drain the two accumulators
+  if (tid < U_PRODUCERS) {
+    if (ok) ok = mbar_wait_bounded(&bars.done, 0);
+    umma::fence_after_sync();
+    if (ok) {
+      const int lane_grp = warp & 3, col_half = warp >> 2;
+      const int f = f0 + lane_grp * 32 + lane;
+      const int fpos = kperm(f);
+      for (int c0 = col_half * 128; c0 < min(n_eff, col_half * 128 + 128); c0 += 32) {
+        float g[32], u[32];
+        const uint32_t ta = tmem + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)c0;
+        umma::ld_32x32(ta, g);
+        umma::ld_32x32(ta + 256, u);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int n = c0 + i;
+          if (n < rows_valid) {
+            const float gv = g[i] * W_POSTSCALE, uv = u[i] * W_POSTSCALE;
+            const float a = (gv / (1.0f + __expf(-gv))) * uv;
+            p.act[(size_t)(row0 + n) * p.nff + fpos] = __float2half_rn(fminf(fmaxf(a, -65504.f), 65504.f));
+          }
+        }
+      }
+    }
+  }
+  if (!ok && lane == 0) atomicExch(&p.status->timeout, 5);
+  umma::fence_before_sync();
+  __syncthreads();
+  if (warp == 8) umma::tmem_dealloc(tmem, 512);
+}
+
+// ---- down ---------------------------------------------------------------------------------------------
+
+constexpr int DN_STAGES = 4;
+constexpr uint32_t DN_STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;  // 48 KB
+
+__device__ __forceinline__ uint32_t ldg_u32_unaligned(const uint8_t* base, size_t off) {
+  const size_t a = off & ~(size_t)3;
+  const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(base + a));
+  const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(base + a + 4));
+  return __funnelshift_r(lo, hi, (uint32_t)(off & 3) * 8);
+}
+
+__global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) PipeBars bars;
+  __shared__ uint32_t s_tmem;
+  const int tile = blockIdx.y;
+  if (tile >= *p.n_tiles) return;
+  unsigned char* stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int e = p.tile_expert[tile], row0 = p.tile_row0[tile], rows_valid = p.tile_rows[tile];
+  const int n_eff = (rows_valid + 15) & ~15;
+  const int i0 = blockIdx.x * UM;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int drb = p.nff / 256 * (int)Q6K_BLOCK_BYTES;
+  const bool shared_seg = e >= p.n_expert;
+
+  if (tid == 0) {
+    for (int s = 0; s < DN_STAGES; ++s) {
+      mbar_init(&bars.full[s], U_PRODUCERS);
+      mbar_init(&bars.empty[s], 1);
+    }
+    mbar_init(&bars.done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 8) umma::tmem_alloc(&s_tmem, 256);
+  umma::fence_before_sync();
+  __syncthreads();
+  umma::fence_after_sync();
+  const uint32_t tmem = s_tmem;
+
+  // producer identity: weight row and which of the step's two 32-element quadrants it unpacks
+  const int wrow = tid & 127, part = (tid >> 7) & 1;
+  const uint8_t* wbase = shared_seg ? p.sh_down : p.down + (size_t)e * p.down_stride;  // 16-byte aligned
+  const size_t row_off = (size_t)(i0 + wrow) * drb;
+  const __half* tok_ptr = p.act + (size_t)(row0 + tid) * p.nff;
+  const bool tok_on = tid < rows_valid;
+  const uint32_t idesc = umma::idesc_f16_f32(UM, n_eff);
+
+  // raw words of a step: eight ql words, eight qh words, the two scales, d
+  uint32_t rL[8], rH[8], rS, rD;
+  auto fetch = [&](int step) {
+    const int blk = step >> 2, c = step & 3, h = c >> 1, qd = 2 * (c & 1) + part;
+    const size_t bo = row_off + (size_t)blk * Q6K_BLOCK_BYTES;
+    rD = __ldg(reinterpret_cast<const unsigned short*>(wbase + bo + 208));
+    rS = ldg_u32_unaligned(wbase, bo + 192 + 8 * h + 2 * qd);  // scales of l < 16 and l >= 16
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      rL[w] = ldg_u32_unaligned(wbase, bo + 64 * h + 32 * part + 4 * w);
+      rH[w] = ldg_u32_unaligned(wbase, bo + 128 + 32 * h + 4 * w);
+    }
+  };
+  if (tid < U_PRODUCERS) fetch(0);
+
+  auto unpack = [&](unsigned char* st, int step) {
+    unsigned char* tA = st;
+    unsigned char* tB = st + A_TILE_BYTES;
+    if (tok_on) copy_token_row(tB, tid, tok_ptr + (size_t)step * UK);
+    // step covers elements [64c, 64c+64) of half h of block blk: quadrants 2*(c&1) and 2*(c&1)+1
+    const int hi_nib = step & 1;
+    const int qd = 2 * hi_nib + part;
+    uint32_t cL[8], cH[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { cL[w] = rL[w]; cH[w] = rH[w]; }
+    const uint32_t sc2 = rS;
+    const float d = f16_bits_to_f32(rD) * W_PRESCALE;
+    if (step + 1 < p.nff / UK) fetch(step + 1);  // in flight while this step is unpacked
+    const __half2 s_a = __float2half2_rn(d * (float)(int)(signed char)(sc2 & 0xFFu));
+    const __half2 s_b = __float2half2_rn(d * (float)(int)(signed char)((sc2 >> 8) & 0xFFu));
+    const int qh_shift = 2 * qd;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {  // eight words of four l each
+      const uint32_t nib = hi_nib ? (cL[w] >> 4) : cL[w];
+      const uint32_t code = (nib & 0x0F0F0F0Fu) | (((cH[w] >> qh_shift) << 4) & 0x30303030u);
+      uint32_t o02, o13;
+      q6_word_to_h2(code, w < 4 ? s_a : s_b, o02, o13);
+      // K position inside the step: 32*part + 4w .. +3  ->  chunk 4*part + w/2, half-chunk w&1
+      *reinterpret_cast<uint2*>(tA + umma::swz128_offset(wrow, 4 * part + (w >> 1)) + (w & 1) * 8) = make_uint2(o02, o13);
+    }
+  };
+  auto issue = [&](unsigned char* st, int step) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      umma::mma_f16(tmem, umma::smem_desc_k_major_swz128(st, k), umma::smem_desc_k_major_swz128(st + A_TILE_BYTES, k), idesc,
+                    step > 0 || k > 0);
+  };
+  bool ok = run_pipeline<DN_STAGES>(bars, stages, DN_STAGE_BYTES, p.nff / UK, unpack, issue);
+
+  if (tid < U_PRODUCERS) {
+    if (ok) ok = mbar_wait_bounded(&bars.done, 0);
+    umma::fence_after_sync();
+    if (ok) {
+      const int lane_grp = warp & 3, col_half = warp >> 2;
+      const int i = i0 + lane_grp * 32 + lane;
+      for (int c0 = col_half * 128; c0 < min(n_eff, col_half * 128 + 128); c0 += 32) {
+        float v[32];
+        umma::ld_32x32(tmem + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+        for (int t = 0; t < 32; ++t)
+          if (c0 + t < rows_valid) p.y[(size_t)(row0 + c0 + t) * p.ne + i] = v[t] * W_POSTSCALE;
+      }
+    }
+  }
+  if (!ok && lane == 0) atomicExch(&p.status->timeout, 6);
+  umma::fence_before_sync();
+  __syncthreads();
+  if (warp == 8) umma::tmem_dealloc(tmem, 256);
+}
+
+}  // namespace
+
+bool umma_grouped_supported(int ne, int nff) { return ne % 256 == 0 && nff % 256 == 0 && ne % UM == 0 && nff % UM == 0; }
+
+int umma_tile_rows() { return UN; }
+
+int32_t launch_umma_grouped(infr_cuda_ctx* ctx, const GroupedParams& p, int max_tiles) {
+  const size_t smem_gu = 1024 + (size_t)GU_STAGES * GU_STAGE_BYTES;
+  const size_t smem_dn = 1024 + (size_t)DN_STAGES * DN_STAGE_BYTES;
+  cudaError_t e = ensure_smem(reinterpret_cast<const void*>(k_umma_gateup), smem_gu);
+  if (e == cudaSuccess) e = ensure_smem(reinterpret_cast<const void*>(k_umma_down), smem_dn);
+  if (e != cudaSuccess) return check_cuda(ctx, e, "umma grouped smem attribute");
+  k_umma_gateup<<<dim3(p.nff / UM, max_tiles), U_THREADS, smem_gu, ctx->stream>>>(p);
+  k_umma_down<<<dim3(p.ne / UM, max_tiles), U_THREADS, smem_dn, ctx->stream>>>(p);
+  ctx->launches += 2;
+  return check_cuda(ctx, cudaGetLastError(), "umma grouped launch");
+}
+
+}  // namespace infr

@@ -49,6 +49,7 @@ struct GroupedParams {
   const uint8_t *gate, *up, *down;
   const uint8_t *sh_gate, *sh_up, *sh_down;  // segment index n_expert = the shared expert
   size_t gate_stride, up_stride, down_stride;
+  DeviceStatus* status;
   int ne, nff, n_expert;
 };
 
@@ -68,8 +69,12 @@ struct GroupedCall {
   int shared_rows;         // rows of the shared-expert segment (rows or 0)
   int rows_bound;          // upper bound on grouped rows including the shared segment
   uint32_t ep_lo, ep_n;
+  int legacy;              // 1: use the mma.sync tiles even where the tcgen05 kernels apply
 };
 
+bool umma_grouped_supported(int ne, int nff);
+int umma_tile_rows();
+int32_t launch_umma_grouped(infr_cuda_ctx* ctx, const GroupedParams& p, int max_tiles);
 size_t grouped_scratch_bytes(int rows_total, int n_pairs, int n_seg, int ne, int nff);
 int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c);
 int32_t launch_combine(infr_cuda_ctx* ctx, const float* y, const int* pos_of_pair, const float* wts, const float* sh_logit,

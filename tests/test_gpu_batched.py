@@ -18,11 +18,13 @@ def ids_match(ids, ref, n_used):
     return ties
 
 
-@pytest.mark.parametrize("rows", [1, 5, 64, 200])
-def test_batched_small_layer(backend, rows):
+# path 2 = tcgen05 tiles where the shape allows, path 3 = the legacy mma.sync tiles
+@pytest.mark.parametrize("path", [2, 3])
+@pytest.mark.parametrize("rows", [1, 5, 64, 200, 700])
+def test_batched_small_layer(backend, rows, path):
     L = synth.make_layer(41, 512, 16, 256, sh_ff=256, router_std=0.05)
     x = synth.activations(rows, rows, 512)
-    out, ids, wts = GpuLayer(backend, L).run(x, 4, path=2)
+    out, ids, wts = GpuLayer(backend, L).run(x, 4, path=path)
     ref = oracle_layer(L, x, 4)
     ties = ids_match(ids, ref, 4)
     keep = [r for r in range(rows) if r not in ties]
@@ -42,7 +44,8 @@ def test_auto_path_switches_above_eight_rows(backend):
     assert_close(out, ref.dst)
 
 
-def test_skewed_load_and_empty_experts(backend):
+@pytest.mark.parametrize("path", [2, 3])
+def test_skewed_load_and_empty_experts(backend, path):
     # a router bias column (router_x differs from x, crates/infr-core/src/graph.rs:1261-1266) gives a
     # Zipf(1.1)-like load: a few experts get hundreds of rows, many get none
     ne, E, rows = 512, 64, 600
@@ -52,7 +55,7 @@ def test_skewed_load_and_empty_experts(backend):
     x = synth.activations(7, rows, ne)
     rx = x.copy()
     rx[:, ne - 1] = 1.0
-    out, ids, wts = GpuLayer(backend, L).run(x, 4, router_x=rx, path=2)
+    out, ids, wts = GpuLayer(backend, L).run(x, 4, router_x=rx, path=path)
     ref = oracle_layer(L, x, 4, router_x=rx)
     counts = np.bincount(ref.ids.reshape(-1), minlength=E)
     assert counts.max() > 300 and (counts == 0).sum() > 0, "the case must have a hot and an empty expert"
