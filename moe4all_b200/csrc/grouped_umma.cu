@@ -56,12 +56,21 @@ __device__ __forceinline__ void q6_word_to_h2(uint32_t c, __half2 s, uint32_t& o
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-// One token row's 64 K elements (128 B) into the swizzled B tile.
-__device__ __forceinline__ void copy_token_row(unsigned char* tB, int row, const __half* src) {
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// The K step's slice (64 halfs = 128 B) of up to 256 token rows into the swizzled B tile.  Eight
+// consecutive lanes copy the eight 16-byte pieces of one row, so a warp request covers four whole
+// 128-byte lines.
+__device__ __forceinline__ void copy_token_tile(unsigned char* tB, const __half* src, int ld, int rows_valid, int tid) {
+  const int chunk = tid & 7;
 #pragma unroll
-  for (int c = 0; c < 8; ++c) cp_async16(tB + umma::swz128_offset(row, c), src + c * 8);
+  for (int pass = 0; pass < 8; ++pass) {
+    const int row = pass * 32 + (tid >> 3);
+    if (row < rows_valid) cp_async16(tB + umma::swz128_offset(row, chunk), src + (size_t)row * ld + chunk * 8);
+  }
 }
 
 struct PipeBars {
@@ -70,22 +79,38 @@ struct PipeBars {
   uint64_t done;
 };
 
-// Shared pipeline skeleton.  `unpack(stage_ptr, step)` is run by every producer thread;
-// `issue(stage_ptr, step)` by the MMA thread.
-template <int STAGES, typename Unpack, typename Issue>
+// Shared pipeline skeleton.  Producers: `copy_b(stage_ptr, step)` starts the asynchronous token-tile
+// copy of a step STAGES-2 steps ahead of its use, `unpack(stage_ptr, step)` writes the weight
+// tile(s); MMA thread: `issue(stage_ptr, step)`.
+template <int STAGES, typename CopyB, typename Unpack, typename Issue>
 __device__ __forceinline__ bool run_pipeline(PipeBars& bars, unsigned char* stages, uint32_t stage_bytes, int n_steps,
-                                             Unpack unpack, Issue issue) {
+                                             CopyB copy_b, Unpack unpack, Issue issue) {
+  constexpr int AHEAD = STAGES - 2;
   const int tid = threadIdx.x;
   bool ok = true;
   if (tid < U_PRODUCERS) {
-    for (int step = 0; step < n_steps && ok; ++step) {
+    // stages are claimed in step order; a claim waits for the MMAs that last read the stage
+    auto claim = [&](int step) {
       const int s = step % STAGES, use = step / STAGES;
-      if (!mbar_wait_bounded(&bars.empty[s], (use & 1) ^ 1)) { ok = false; break; }
+      if (!mbar_wait_bounded(&bars.empty[s], (use & 1) ^ 1)) return false;
+      copy_b(stages + (size_t)s * stage_bytes, step);
+      return true;
+    };
+    for (int step = 0; step < AHEAD && step < n_steps && ok; ++step) {
+      ok = claim(step);
+      cp_async_commit();
+    }
+    for (int step = 0; step < n_steps && ok; ++step) {
+      if (step + AHEAD < n_steps) ok = claim(step + AHEAD);
+      cp_async_commit();  // one group per step, empty or not, keeps the group count uniform
+      if (!ok) break;
+      const int s = step % STAGES;
       unpack(stages + (size_t)s * stage_bytes, step);
-      cp_async_wait_all();
+      cp_async_wait_group<AHEAD>();  // the token tile of `step` has landed
       umma::fence_proxy_async();
       mbar_arrive(&bars.full[s]);
     }
+    cp_async_wait_group<0>();
   } else if (tid == U_PRODUCERS) {
     for (int step = 0; step < n_steps && ok; ++step) {
       const int s = step % STAGES, use = step / STAGES;
@@ -137,8 +162,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p) {
   const uint8_t* wbase = role == 0 ? (shared_seg ? p.sh_gate : p.gate + (size_t)e * p.gate_stride)
                                    : (shared_seg ? p.sh_up : p.up + (size_t)e * p.up_stride);
   const uint8_t* wrow_ptr = wbase + (size_t)(f0 + wrow) * rb;
-  const __half* tok_ptr = p.xg + (size_t)(row0 + tid) * p.ne;
-  const bool tok_on = tid < rows_valid;
+  const __half* tok_tile = p.xg + (size_t)row0 * p.ne;
   const uint32_t idesc = umma::idesc_f16_f32(UM, n_eff);
 
   // raw weight words of the next step are fetched while the current step is unpacked
@@ -147,8 +171,6 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p) {
 
   auto unpack = [&](unsigned char* st, int step) {
     unsigned char* tA = st + (size_t)role * A_TILE_BYTES;
-    unsigned char* tB = st + 2 * A_TILE_BYTES;
-    if (tok_on) copy_token_row(tB, tid, tok_ptr + (size_t)step * UK);
     const int j = step & 3;
     const uint4 ch = hdr, c0 = q0, c1 = q1;
     if (step + 1 < p.ne / UK) {  // prefetch the next 64-group of this row
@@ -184,7 +206,10 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p) {
       umma::mma_f16(tmem + 256, umma::smem_desc_k_major_swz128(st + A_TILE_BYTES, k), bd, idesc, step > 0 || k > 0);
     }
   };
-  bool ok = run_pipeline<GU_STAGES>(bars, stages, GU_STAGE_BYTES, p.ne / UK, unpack, issue);
+  auto copy_b = [&](unsigned char* st, int step) {
+    copy_token_tile(st + 2 * A_TILE_BYTES, tok_tile + (size_t)step * UK, p.ne, rows_valid, tid);
+  };
+  bool ok = run_pipeline<GU_STAGES>(bars, stages, GU_STAGE_BYTES, p.ne / UK, copy_b, unpack, issue);
 
   // epilogue: producers drain the two accumulators
   if (tid < U_PRODUCERS) {
@@ -257,53 +282,62 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
   umma::fence_after_sync();
   const uint32_t tmem = s_tmem;
 
-  // producer identity: weight row and which of the step's two 32-element quadrants it unpacks
-  const int wrow = tid & 127, part = (tid >> 7) & 1;
+  // producer identity: eight consecutive lanes share a weight row (lane w takes the four l values
+  // 4w..4w+3 of every quadrant), so a warp request covers whole 32-byte runs of four rows; the 128
+  // rows of the tile take four passes.
+  const int g8 = tid >> 3, w = tid & 7;
   const uint8_t* wbase = shared_seg ? p.sh_down : p.down + (size_t)e * p.down_stride;  // 16-byte aligned
-  const size_t row_off = (size_t)(i0 + wrow) * drb;
-  const __half* tok_ptr = p.act + (size_t)(row0 + tid) * p.nff;
-  const bool tok_on = tid < rows_valid;
+  const __half* tok_tile = p.act + (size_t)row0 * p.nff;
   const uint32_t idesc = umma::idesc_f16_f32(UM, n_eff);
 
-  // raw words of a step: eight ql words, eight qh words, the two scales, d
-  uint32_t rL[8], rH[8], rS, rD;
-  auto fetch = [&](int step) {
-    const int blk = step >> 2, c = step & 3, h = c >> 1, qd = 2 * (c & 1) + part;
-    const size_t bo = row_off + (size_t)blk * Q6K_BLOCK_BYTES;
-    rD = __ldg(reinterpret_cast<const unsigned short*>(wbase + bo + 208));
-    rS = ldg_u32_unaligned(wbase, bo + 192 + 8 * h + 2 * qd);  // scales of l < 16 and l >= 16
+  // Raw words of one half-block (128 elements = two K steps: low nibbles first, high nibbles
+  // second) per pass: ql words of quadrants 0|2 and 1|3, the qh word, the eight scales, d.
+  // The next half-block is fetched while the current one is unpacked.
+  uint32_t nxt[4][6], cur[4][6];
+  const int n_pairs = p.nff / 128;
+  auto fetch_pair = [&](int pair) {
+    const int blk = pair >> 1, h = pair & 1;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      rL[w] = ldg_u32_unaligned(wbase, bo + 64 * h + 32 * part + 4 * w);
-      rH[w] = ldg_u32_unaligned(wbase, bo + 128 + 32 * h + 4 * w);
+    for (int ps = 0; ps < 4; ++ps) {
+      const size_t bo = (size_t)(i0 + ps * 32 + g8) * drb + (size_t)blk * Q6K_BLOCK_BYTES;
+      nxt[ps][0] = ldg_u32_unaligned(wbase, bo + 64 * h + 4 * w);
+      nxt[ps][1] = ldg_u32_unaligned(wbase, bo + 64 * h + 32 + 4 * w);
+      nxt[ps][2] = ldg_u32_unaligned(wbase, bo + 128 + 32 * h + 4 * w);
+      nxt[ps][3] = ldg_u32_unaligned(wbase, bo + 192 + 8 * h);
+      nxt[ps][4] = ldg_u32_unaligned(wbase, bo + 196 + 8 * h);
+      nxt[ps][5] = __ldg(reinterpret_cast<const unsigned short*>(wbase + bo + 208));
     }
   };
-  if (tid < U_PRODUCERS) fetch(0);
+  if (tid < U_PRODUCERS) fetch_pair(0);
 
   auto unpack = [&](unsigned char* st, int step) {
     unsigned char* tA = st;
-    unsigned char* tB = st + A_TILE_BYTES;
-    if (tok_on) copy_token_row(tB, tid, tok_ptr + (size_t)step * UK);
-    // step covers elements [64c, 64c+64) of half h of block blk: quadrants 2*(c&1) and 2*(c&1)+1
     const int hi_nib = step & 1;
-    const int qd = 2 * hi_nib + part;
-    uint32_t cL[8], cH[8];
+    if (hi_nib == 0) {
 #pragma unroll
-    for (int w = 0; w < 8; ++w) { cL[w] = rL[w]; cH[w] = rH[w]; }
-    const uint32_t sc2 = rS;
-    const float d = f16_bits_to_f32(rD) * W_PRESCALE;
-    if (step + 1 < p.nff / UK) fetch(step + 1);  // in flight while this step is unpacked
-    const __half2 s_a = __float2half2_rn(d * (float)(int)(signed char)(sc2 & 0xFFu));
-    const __half2 s_b = __float2half2_rn(d * (float)(int)(signed char)((sc2 >> 8) & 0xFFu));
-    const int qh_shift = 2 * qd;
+      for (int ps = 0; ps < 4; ++ps)
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {  // eight words of four l each
-      const uint32_t nib = hi_nib ? (cL[w] >> 4) : cL[w];
-      const uint32_t code = (nib & 0x0F0F0F0Fu) | (((cH[w] >> qh_shift) << 4) & 0x30303030u);
-      uint32_t o02, o13;
-      q6_word_to_h2(code, w < 4 ? s_a : s_b, o02, o13);
-      // K position inside the step: 32*part + 4w .. +3  ->  chunk 4*part + w/2, half-chunk w&1
-      *reinterpret_cast<uint2*>(tA + umma::swz128_offset(wrow, 4 * part + (w >> 1)) + (w & 1) * 8) = make_uint2(o02, o13);
+        for (int i = 0; i < 6; ++i) cur[ps][i] = nxt[ps][i];
+      if ((step >> 1) + 1 < n_pairs) fetch_pair((step >> 1) + 1);
+    }
+#pragma unroll
+    for (int ps = 0; ps < 4; ++ps) {
+      const int row = ps * 32 + g8;
+      const float d = f16_bits_to_f32(cur[ps][5]) * W_PRESCALE;
+      // scale of quadrant qd for these l: byte 2*qd + (w >> 2) of the half's eight scale bytes
+      const uint32_t sc4 = __byte_perm(cur[ps][3], cur[ps][4], (w >> 2) ? 0x7531u : 0x6420u);
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        const int qd = 2 * hi_nib + part;
+        const uint32_t L = cur[ps][part];
+        const uint32_t nib = hi_nib ? (L >> 4) : L;
+        const uint32_t code = (nib & 0x0F0F0F0Fu) | (((cur[ps][2] >> (2 * qd)) << 4) & 0x30303030u);
+        const float sc = (float)(int)(signed char)((sc4 >> (8 * qd)) & 0xFFu);
+        uint32_t o02, o13;
+        q6_word_to_h2(code, __float2half2_rn(d * sc), o02, o13);
+        // K position inside the step: 32*part + 4w .. +3  ->  chunk 4*part + w/2, half-chunk w&1
+        *reinterpret_cast<uint2*>(tA + umma::swz128_offset(row, 4 * part + (w >> 1)) + (w & 1) * 8) = make_uint2(o02, o13);
+      }
     }
   };
   auto issue = [&](unsigned char* st, int step) {
@@ -312,7 +346,10 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
       umma::mma_f16(tmem, umma::smem_desc_k_major_swz128(st, k), umma::smem_desc_k_major_swz128(st + A_TILE_BYTES, k), idesc,
                     step > 0 || k > 0);
   };
-  bool ok = run_pipeline<DN_STAGES>(bars, stages, DN_STAGE_BYTES, p.nff / UK, unpack, issue);
+  auto copy_b = [&](unsigned char* st, int step) {
+    copy_token_tile(st + A_TILE_BYTES, tok_tile + (size_t)step * UK, p.nff, rows_valid, tid);
+  };
+  bool ok = run_pipeline<DN_STAGES>(bars, stages, DN_STAGE_BYTES, p.nff / UK, copy_b, unpack, issue);
 
   if (tid < U_PRODUCERS) {
     if (ok) ok = mbar_wait_bounded(&bars.done, 0);
