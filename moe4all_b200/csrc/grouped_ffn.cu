@@ -529,6 +529,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   p.nff = c.nff;
   p.n_expert = c.n_expert;
   p.status = ctx->status;
+  p.trace = ctx->trace;
   if (use_umma) {
     const int32_t rc = launch_umma_grouped(ctx, p, max_tiles);
     if (rc) return rc;

@@ -13,6 +13,8 @@
 // releases each pipeline stage with tcgen05.commit.  After the K loop the producers drain the
 // accumulators with tcgen05.ld and write the result.  Stages are handed over through mbarriers;
 // every wait is bounded.
+#include <type_traits>
+
 #include "kernels.cuh"
 #include "umma.cuh"
 
@@ -84,7 +86,7 @@ struct PipeBars {
 // tile(s); MMA thread: `issue(stage_ptr, step)`.
 template <int STAGES, typename CopyB, typename Unpack, typename Issue>
 __device__ __forceinline__ bool run_pipeline(PipeBars& bars, unsigned char* stages, uint32_t stage_bytes, int n_steps,
-                                             CopyB copy_b, Unpack unpack, Issue issue) {
+                                             CopyB copy_b, Unpack unpack, Issue issue, unsigned long long* tr) {
   constexpr int AHEAD = STAGES - 2;
   const int tid = threadIdx.x;
   bool ok = true;
@@ -100,15 +102,29 @@ __device__ __forceinline__ bool run_pipeline(PipeBars& bars, unsigned char* stag
       ok = claim(step);
       cp_async_commit();
     }
-    for (int step = 0; step < n_steps && ok; ++step) {
+    // `jc` carries step % 4 as a compile-time constant (n_steps is a multiple of four): the
+    // producers index their register-resident prefetch buffers with it
+    auto body = [&](int step, auto jc) {
+      if (!ok) return;
+      if (step < 8) trace_stamp(tr, 64 + 4 * step);
       if (step + AHEAD < n_steps) ok = claim(step + AHEAD);
       cp_async_commit();  // one group per step, empty or not, keeps the group count uniform
-      if (!ok) break;
+      if (!ok) return;
+      if (step < 8) trace_stamp(tr, 65 + 4 * step);
       const int s = step % STAGES;
-      unpack(stages + (size_t)s * stage_bytes, step);
+      unpack(stages + (size_t)s * stage_bytes, step, jc);
+      if (step < 8) trace_stamp(tr, 66 + 4 * step);
       cp_async_wait_group<AHEAD>();  // the token tile of `step` has landed
+      if (step < 8) trace_stamp(tr, 67 + 4 * step);
       umma::fence_proxy_async();
-      mbar_arrive(&bars.full[s]);
+      __syncwarp();
+      if ((tid & 31) == 0) mbar_arrive(&bars.full[s]);  // one arrival per producer warp
+    };
+    for (int base = 0; base < n_steps && ok; base += 4) {
+      body(base, std::integral_constant<int, 0>{});
+      body(base + 1, std::integral_constant<int, 1>{});
+      body(base + 2, std::integral_constant<int, 2>{});
+      body(base + 3, std::integral_constant<int, 3>{});
     }
     cp_async_wait_group<0>();
   } else if (tid == U_PRODUCERS) {
@@ -116,8 +132,10 @@ __device__ __forceinline__ bool run_pipeline(PipeBars& bars, unsigned char* stag
       const int s = step % STAGES, use = step / STAGES;
       if (!mbar_wait_bounded(&bars.full[s], use & 1)) { ok = false; break; }
       umma::fence_after_sync();
+      if (tr != nullptr && step < 8) { tr[2 * (100 + 2 * step)] = 0; tr[2 * (100 + 2 * step) + 1] = (unsigned long long)clock64(); }
       issue(stages + (size_t)s * stage_bytes, step);
       umma::commit(&bars.empty[s]);
+      if (tr != nullptr && step < 8) { tr[2 * (101 + 2 * step)] = 0; tr[2 * (101 + 2 * step) + 1] = (unsigned long long)clock64(); }
     }
     umma::commit(&bars.done);
   }
@@ -145,7 +163,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p) {
 
   if (tid == 0) {
     for (int s = 0; s < GU_STAGES; ++s) {
-      mbar_init(&bars.full[s], U_PRODUCERS);
+      mbar_init(&bars.full[s], U_PRODUCERS / 32);
       mbar_init(&bars.empty[s], 1);
     }
     mbar_init(&bars.done, 1);
@@ -165,21 +183,28 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p) {
   const __half* tok_tile = p.xg + (size_t)row0 * p.ne;
   const uint32_t idesc = umma::idesc_f16_f32(UM, n_eff);
 
-  // raw weight words of the next step are fetched while the current step is unpacked
-  uint4 hdr = __ldg(reinterpret_cast<const uint4*>(wrow_ptr));
-  uint4 q0 = __ldg(reinterpret_cast<const uint4*>(wrow_ptr + 16)), q1 = __ldg(reinterpret_cast<const uint4*>(wrow_ptr + 32));
+  // Raw bytes of one whole 256-weight block of this row (header + 128 code bytes) are fetched a
+  // block ahead, i.e. four K steps before they are unpacked: the rows of a tile are 1152 bytes
+  // apart, every fetch is its own sector and takes a full memory latency.
+  uint4 nxt_h, cur_h, nxt_q[8], cur_q[8];
+  auto fetch_block = [&](int blk) {
+    const uint8_t* bp = wrow_ptr + (size_t)blk * Q4K_BLOCK_BYTES;
+    nxt_h = __ldg(reinterpret_cast<const uint4*>(bp));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) nxt_q[i] = __ldg(reinterpret_cast<const uint4*>(bp + 16 + 16 * i));
+  };
+  fetch_block(0);
 
-  auto unpack = [&](unsigned char* st, int step) {
+  auto unpack = [&](unsigned char* st, int step, auto jc) {
+    constexpr int j = decltype(jc)::value;
     unsigned char* tA = st + (size_t)role * A_TILE_BYTES;
-    const int j = step & 3;
-    const uint4 ch = hdr, c0 = q0, c1 = q1;
-    if (step + 1 < p.ne / UK) {  // prefetch the next 64-group of this row
-      const int nb = (step + 1) >> 2, nj = (step + 1) & 3;
-      const uint8_t* bp = wrow_ptr + (size_t)nb * Q4K_BLOCK_BYTES;
-      if (nj == 0) hdr = __ldg(reinterpret_cast<const uint4*>(bp));
-      q0 = __ldg(reinterpret_cast<const uint4*>(bp + 16 + 32 * nj));
-      q1 = __ldg(reinterpret_cast<const uint4*>(bp + 32 + 32 * nj));
+    if (j == 0) {
+      cur_h = nxt_h;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) cur_q[i] = nxt_q[i];
+      if ((step >> 2) + 1 < p.ne / 256) fetch_block((step >> 2) + 1);
     }
+    const uint4 ch = cur_h, c0 = cur_q[2 * j], c1 = cur_q[2 * j + 1];
     uint32_t scp, mp;
     q4k_scale_min_pair(ch.y, ch.z, ch.w, j, scp, mp);
     const float d = f16_bits_to_f32(ch.x) * W_PRESCALE, dmin = f16_bits_to_f32(ch.x >> 16) * W_PRESCALE;
@@ -209,7 +234,8 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p) {
   auto copy_b = [&](unsigned char* st, int step) {
     copy_token_tile(st + 2 * A_TILE_BYTES, tok_tile + (size_t)step * UK, p.ne, rows_valid, tid);
   };
-  bool ok = run_pipeline<GU_STAGES>(bars, stages, GU_STAGE_BYTES, p.ne / UK, copy_b, unpack, issue);
+  bool ok = run_pipeline<GU_STAGES>(bars, stages, GU_STAGE_BYTES, p.ne / UK, copy_b, unpack, issue,
+                                    (blockIdx.x == 0 && blockIdx.y == 0) ? p.trace : nullptr);
 
   // epilogue: producers drain the two accumulators
   if (tid < U_PRODUCERS) {
@@ -270,7 +296,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
 
   if (tid == 0) {
     for (int s = 0; s < DN_STAGES; ++s) {
-      mbar_init(&bars.full[s], U_PRODUCERS);
+      mbar_init(&bars.full[s], U_PRODUCERS / 32);
       mbar_init(&bars.empty[s], 1);
     }
     mbar_init(&bars.done, 1);
@@ -310,7 +336,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
   };
   if (tid < U_PRODUCERS) fetch_pair(0);
 
-  auto unpack = [&](unsigned char* st, int step) {
+  auto unpack = [&](unsigned char* st, int step, auto) {
     unsigned char* tA = st;
     const int hi_nib = step & 1;
     if (hi_nib == 0) {
@@ -349,7 +375,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
   auto copy_b = [&](unsigned char* st, int step) {
     copy_token_tile(st + A_TILE_BYTES, tok_tile + (size_t)step * UK, p.nff, rows_valid, tid);
   };
-  bool ok = run_pipeline<DN_STAGES>(bars, stages, DN_STAGE_BYTES, p.nff / UK, copy_b, unpack, issue);
+  bool ok = run_pipeline<DN_STAGES>(bars, stages, DN_STAGE_BYTES, p.nff / UK, copy_b, unpack, issue, nullptr);
 
   if (tid < U_PRODUCERS) {
     if (ok) ok = mbar_wait_bounded(&bars.done, 0);

@@ -50,6 +50,7 @@ struct GroupedParams {
   const uint8_t *sh_gate, *sh_up, *sh_down;  // segment index n_expert = the shared expert
   size_t gate_stride, up_stride, down_stride;
   DeviceStatus* status;
+  unsigned long long* trace;  // optional phase stamps
   int ne, nff, n_expert;
 };
 
