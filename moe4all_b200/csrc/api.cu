@@ -353,6 +353,8 @@ static int32_t validate_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d)
 namespace {
 // Scratch carve-up for one call.
 struct Scratch {
+  int8_t *xq_lo, *xq_hi;
+  float* xscale;
   float* logits;
   float* sh_logit;
   int32_t* ids;
@@ -374,6 +376,9 @@ Scratch carve(void* base, const infr_cuda_moe_ffn_desc* d, bool with_act) {
   s.ids = static_cast<int32_t*>(take((size_t)d->rows * d->n_used * 4));
   s.wts = static_cast<float*>(take((size_t)d->rows * d->n_used * 4));
   s.act = with_act ? static_cast<float*>(take(((size_t)d->rows * d->n_used * d->n_ff_exp + (size_t)d->rows * d->sh_ff) * 4)) : nullptr;
+  s.xq_lo = with_act ? static_cast<int8_t*>(take((size_t)d->rows * d->ne)) : nullptr;
+  s.xq_hi = with_act ? static_cast<int8_t*>(take((size_t)d->rows * d->ne)) : nullptr;
+  s.xscale = with_act ? static_cast<float*>(take((size_t)d->rows * 4)) : nullptr;
   s.total = off;
   return s;
 }
@@ -433,9 +438,15 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     if ((rc = ensure_scratch(ctx, sz.total))) return rc;
     Scratch s = carve(ctx->scratch, d, true);
     RouteParams rp = route_params(ctx, d, s, true);
+    rp.xq_lo = s.xq_lo;
+    rp.xq_hi = s.xq_hi;
+    rp.xscale = s.xscale;
     const uint32_t stages = d->stages ? d->stages : 7u;
     if ((stages & 1u) && (rc = launch_route(ctx, rp, true))) return rc;
     DecodeParams dp = {};
+    dp.xq_lo = s.xq_lo;
+    dp.xq_hi = s.xq_hi;
+    dp.xscale = s.xscale;
     dp.x = static_cast<const float*>(d->x->ptr);
     dp.ids = rp.ids;
     dp.wts = rp.wts;

@@ -241,6 +241,29 @@ __device__ __forceinline__ float q4k_dot64(const uint4& hdr, const uint32_t (&q)
   return (16.f * s0) * (A0 - xs0) - m0 * xs0 + (16.f * s1) * (A1 - xs1) - m1 * xs1;
 }
 
+// Same dot product with the activations in 16-bit fixed point, split into two signed 8-bit limbs
+// (X = 256*hi + lo per element, four elements per word): the nibbles of a code word are masked in
+// place and multiplied with integer dot-product instructions, which keeps the unpack off the
+// (half-rate) logic pipe.  xl/xh: limbs of the 64 elements, sx0/sx1: integer sums of X over the two
+// 32-element sub-blocks.  Returns sum(w * X); the caller multiplies by the fixed-point scale.
+__device__ __forceinline__ float q4k_dot64_i8(const uint4& hdr, const uint32_t (&q)[8], const int (&xl)[16], const int (&xh)[16],
+                                              float sx0, float sx1, int j) {
+  int a_ll = 0, a_lh = 0, a_hl = 0, a_hh = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int lo4 = (int)(q[i] & 0x0F0F0F0Fu), hi4 = (int)((q[i] >> 4) & 0x0F0F0F0Fu);
+    a_ll = __dp4a(lo4, xl[i], a_ll);
+    a_lh = __dp4a(lo4, xh[i], a_lh);
+    a_hl = __dp4a(hi4, xl[8 + i], a_hl);
+    a_hh = __dp4a(hi4, xh[8 + i], a_hh);
+  }
+  const float v0 = (float)(a_lh * 256 + a_ll), v1 = (float)(a_hh * 256 + a_hl);
+  uint32_t scp, mp;
+  q4k_scale_min_pair(hdr.y, hdr.z, hdr.w, j, scp, mp);
+  const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+  return d * ((float)(scp & 0xFFu) * v0 + (float)(scp >> 8) * v1) - dmin * ((float)(mp & 0xFFu) * sx0 + (float)(mp >> 8) * sx1);
+}
+
 #endif  // __CUDACC__
 
 }  // namespace infr

@@ -24,7 +24,7 @@ namespace {
 constexpr int GU_WARPS = 16;  // rows per chunk and role: one per warp
 constexpr int GU_THREADS = GU_WARPS * 32;
 constexpr int GU_MAX_CHUNKS = 4;
-constexpr int GU_XPITCH = 68;  // floats per 64-element group of x in shared memory (bank spread)
+constexpr int GU_XQPITCH = 144;  // bytes per 64-element group of fixed-point x: 64 low limbs, 64 high limbs, pad
 
 constexpr int DN_MAX_WARPS = 24;
 constexpr int DN_MAX_SLOTS = 33;  // n_used ≤ 32 plus the shared expert
@@ -43,7 +43,7 @@ __device__ __forceinline__ bool in_band(const DecodeParams& p, int e) {
 // Lane L owns the 64-element groups g = L, L+32, ... of the input (for ne = 2048 exactly one, so
 // its 64 activations stay in registers for the whole tile).
 template <int NG>
-__global__ void __launch_bounds__(GU_THREADS, 1) k_decode_gateup(DecodeParams p, int n_chunks) {
+__global__ void __launch_bounds__(GU_THREADS, 2) k_decode_gateup(DecodeParams p, int n_chunks) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_bar[GU_MAX_CHUNKS];
 
@@ -91,17 +91,18 @@ __global__ void __launch_bounds__(GU_THREADS, 1) k_decode_gateup(DecodeParams p,
   pdl_trigger();  // only now: the next kernel reads ids as soon as it starts
 
   int e_sel = routed ? __ldcg(p.ids + pair) : 0;  // L2 read: written by an overlapping earlier kernel
-  // the token's activations: coalesced into shared memory, then each lane keeps its group(s).
-  // Requested before the routing result so that both reads are in flight together.
+  // The token's activations arrive as 16-bit fixed point (two signed 8-bit limbs per element,
+  // made by the router kernel): 64 low limbs then 64 high limbs per 64-element group.  Requested
+  // before the routing result is used so that both reads are in flight together.
   const int n_groups = p.ne / 64;
-  float* s_x = reinterpret_cast<float*>(smem + (size_t)n_chunks * 2 * chunk_bytes);
-  {
-    const float4* xr4 = reinterpret_cast<const float4*>(p.x + (size_t)r * p.ne);
-    for (int i = tid; i < p.ne / 4; i += GU_THREADS) {
-      const float4 v = __ldcg(xr4 + i);
-      *reinterpret_cast<float4*>(s_x + (i >> 4) * GU_XPITCH + (i & 15) * 4) = v;
-    }
+  unsigned char* s_xq = smem + (size_t)n_chunks * 2 * chunk_bytes;  // [group][144]
+  const bool stage_on = tid < p.ne / 16;  // ne <= 8192: one 16-byte piece of each limb array per thread
+  uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
+  if (stage_on) {
+    xa = __ldcg(reinterpret_cast<const uint4*>(p.xq_lo + (size_t)r * p.ne) + tid);
+    xb = __ldcg(reinterpret_cast<const uint4*>(p.xq_hi + (size_t)r * p.ne) + tid);
   }
+  const float q_scale = __ldcg(p.xscale + r);
   if (routed) {
     int e = e_sel;
     if (e < 0 || e >= p.n_expert) {
@@ -113,22 +114,32 @@ __global__ void __launch_bounds__(GU_THREADS, 1) k_decode_gateup(DecodeParams p,
       issue_copies(p.gate + (size_t)e * p.gate_stride + (size_t)tile * TR * rb,
                    p.up + (size_t)e * p.up_stride + (size_t)tile * TR * rb);
   }
+  if (stage_on) {
+    unsigned char* g = s_xq + (size_t)(tid >> 2) * GU_XQPITCH + (tid & 3) * 16;
+    *reinterpret_cast<uint4*>(g) = xa;
+    *reinterpret_cast<uint4*>(g + 64) = xb;
+  }
 
-  __syncthreads();  // x staged, barrier init visible to all waiters
+  __syncthreads();  // limbs staged, barrier init visible to all waiters
   trace_stamp(tr, 18);
-  float xv[64];
-  float xs0 = 0.f, xs1 = 0.f;
+  int xl[16], xh[16];
+  float sx0 = 0.f, sx1 = 0.f;
   auto load_x = [&](int g) {
-    const float4* src = reinterpret_cast<const float4*>(s_x + g * GU_XPITCH);
+    const uint4* src = reinterpret_cast<const uint4*>(s_xq + (size_t)g * GU_XQPITCH);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float4 v = src[i];
-      xv[4 * i + 0] = v.x; xv[4 * i + 1] = v.y; xv[4 * i + 2] = v.z; xv[4 * i + 3] = v.w;
+    for (int i = 0; i < 4; ++i) {
+      const uint4 a = src[i], b = src[4 + i];
+      xl[4 * i + 0] = (int)a.x; xl[4 * i + 1] = (int)a.y; xl[4 * i + 2] = (int)a.z; xl[4 * i + 3] = (int)a.w;
+      xh[4 * i + 0] = (int)b.x; xh[4 * i + 1] = (int)b.y; xh[4 * i + 2] = (int)b.z; xh[4 * i + 3] = (int)b.w;
     }
-    float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+    int l0 = 0, h0 = 0, l1 = 0, h1 = 0;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) { a0 += xv[2 * i]; a1 += xv[2 * i + 1]; b0 += xv[32 + 2 * i]; b1 += xv[33 + 2 * i]; }
-    xs0 = a0 + a1; xs1 = b0 + b1;
+    for (int i = 0; i < 8; ++i) {
+      l0 = __dp4a(0x01010101, xl[i], l0); h0 = __dp4a(0x01010101, xh[i], h0);
+      l1 = __dp4a(0x01010101, xl[8 + i], l1); h1 = __dp4a(0x01010101, xh[8 + i], h1);
+    }
+    sx0 = (float)(h0 * 256 + l0);
+    sx1 = (float)(h1 * 256 + l1);
   };
   if (NG == 1) {
     if (lane < n_groups) load_x(lane);
@@ -158,12 +169,12 @@ __global__ void __launch_bounds__(GU_THREADS, 1) k_decode_gateup(DecodeParams p,
           const uint4 d4 = *reinterpret_cast<const uint4*>(urow + blk * Q4K_BLOCK_BYTES + 32 + 32 * j);
           uq[0] = c4.x; uq[1] = c4.y; uq[2] = c4.z; uq[3] = c4.w; uq[4] = d4.x; uq[5] = d4.y; uq[6] = d4.z; uq[7] = d4.w;
         }
-        gsum += q4k_dot64(gh, gq, xv, xs0, xs1, j);
-        usum += q4k_dot64(uh, uq, xv, xs0, xs1, j);
+        gsum += q4k_dot64_i8(gh, gq, xl, xh, sx0, sx1, j);
+        usum += q4k_dot64_i8(uh, uq, xl, xh, sx0, sx1, j);
       }
     }
-    gsum = warp_sum(gsum);
-    usum = warp_sum(usum);
+    gsum = warp_sum(gsum) * q_scale;
+    usum = warp_sum(usum) * q_scale;
     if (lane == 0) {
       const float s = gsum / (1.0f + __expf(-gsum));
       act_out[c * GU_WARPS + warp] = s * usum;
@@ -252,16 +263,25 @@ __global__ void __launch_bounds__(DN_MAX_WARPS * 32, 1) k_decode_down(DecodePara
   trace_stamp(tr, 33);
   pdl_wait();  // the activations come from the gate/up kernel
   trace_stamp(tr, 34);
-  // activations of this token: routed slots then the shared expert
+  // activations of this token: routed slots then the shared expert; loads are issued four deep
+  // before the first store so that their L2 latencies overlap
   {
-    const float* a_src = p.act + (size_t)r * p.n_used * p.nff;
-    const int n4 = p.n_used * p.nff / 4;
-    for (int i = tid; i < n4; i += nthreads)
-      reinterpret_cast<float4*>(s_act)[i] = __ldcg(reinterpret_cast<const float4*>(a_src) + i);
-    if (has_sh) {
-      const float* sh_src = p.act + (size_t)p.rows * p.n_used * p.nff + (size_t)r * p.sh_ff;
-      float4* d = reinterpret_cast<float4*>(s_act + (size_t)p.n_used * p.nff);
-      for (int i = tid; i < p.sh_ff / 4; i += nthreads) d[i] = __ldcg(reinterpret_cast<const float4*>(sh_src) + i);
+    const float4* a_src = reinterpret_cast<const float4*>(p.act + (size_t)r * p.n_used * p.nff);
+    const float4* sh_src = reinterpret_cast<const float4*>(p.act + (size_t)p.rows * p.n_used * p.nff + (size_t)r * p.sh_ff);
+    const int n4 = p.n_used * p.nff / 4, tot4 = n4 + (has_sh ? p.sh_ff / 4 : 0);
+    float4* d4 = reinterpret_cast<float4*>(s_act);
+    for (int base = tid; base < tot4; base += 4 * nthreads) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = base + u * nthreads;
+        if (i < tot4) v[u] = __ldcg(i < n4 ? a_src + i : sh_src + (i - n4));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = base + u * nthreads;
+        if (i < tot4) d4[i] = v[u];
+      }
     }
   }
   __syncthreads();
@@ -373,7 +393,7 @@ __global__ void __launch_bounds__(DN_MAX_WARPS * 32, 1) k_decode_down(DecodePara
 }
 
 size_t gateup_smem(int ne, int n_chunks) {
-  return (size_t)n_chunks * 2 * GU_WARPS * (ne / 256 * Q4K_BLOCK_BYTES) + (size_t)(ne / 64) * GU_XPITCH * sizeof(float);
+  return (size_t)n_chunks * 2 * GU_WARPS * (ne / 256 * Q4K_BLOCK_BYTES) + (size_t)(ne / 64) * GU_XQPITCH;
 }
 
 int pick_chunks(int ne, int nff, int sh_ff) {

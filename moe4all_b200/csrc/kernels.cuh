@@ -18,6 +18,8 @@ struct RouteParams {
   int32_t* ids;              // [rows, n_used]
   float* wts;                // [rows, n_used]
   unsigned int* counter;     // zero on entry, zero on exit
+  int8_t *xq_lo, *xq_hi;     // [rows, ne] fixed-point limbs of x for the small-m expert kernels, or null
+  float* xscale;             // [rows] value of one fixed-point unit
   unsigned long long* trace; // optional phase stamps
   int rows, ne, n_expert, n_used;
   float scale;
@@ -29,6 +31,8 @@ struct DecodeParams {
   const int32_t* ids;    // [rows, n_used]
   const float* wts;      // [rows, n_used]
   const float* sh_logit; // [rows] or null (ungated shared expert)
+  const int8_t *xq_lo, *xq_hi;  // [rows, ne] fixed-point limbs of x (X = 256*hi + lo)
+  const float* xscale;   // [rows]
   const uint8_t *gate, *up, *down;           // routed banks
   const uint8_t *sh_gate, *sh_up, *sh_down;  // shared expert or null
   float* act;            // [rows*n_used, nff] then [rows, sh_ff]

@@ -82,7 +82,7 @@ def test_unfused_shared_expert_matches_fused(backend):
     be.linear(DType.Q6K, g.sh_down, act, sd, 3, 256, 512)
     be.moe_shared_expert_add(be.from_host(moe), sd, gl, dst, 3, 512)
     unfused = be.download(dst).reshape(3, 512)
-    assert_close(unfused, fused, tol=1e-5)
+    assert_close(unfused, fused, tol=1e-4)  # the fused kernels take x in 16-bit fixed point
     assert_close(unfused, oracle_layer(L, x, 4).dst)
 
 
