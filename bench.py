@@ -48,6 +48,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--streams", type=int, default=1, help="concurrent decode streams (rows per step)")
+    ap.add_argument("--workload", default="layer", choices=["layer", "stack", "prefill"],
+                    help="layer: one MoE layer per step (the headline); stack: 40 such layers with RmsNorm and residual "
+                         "add per step; prefill: one 4096-token chunk through one layer per step")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -345,10 +348,160 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def setup_dist():
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    torch.cuda.set_device(local)
+    return world, rank, local
+
+
+def timed(torch, dist, world, fn, steps):
+    """K calls of fn between barriers, CUDA events on the current stream, max over ranks (ms)."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(steps):
+        fn(s)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def run_stack(args):
+    """Config 3: 40 MoE sub-layers (RmsNorm eps 1e-6, MoE + shared expert, residual add), steady-state
+    decode; one step = one token row per stream through all 40 layers, replayed from a recording."""
+    import torch
+    import torch.distributed as dist
+    from moe4all_b200 import CudaBackend, build
+    from moe4all_b200.devgen import DeviceLayer
+    from moe4all_b200.stack import MoeStack
+
+    world, rank, local = setup_dist()
+    build.build()
+    be = CudaBackend(local)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    be.set_stream(stream.cuda_stream)
+    R, K, W, NL = args.streams, args.steps, max(args.warmup, 3), 40
+    dev = f"cuda:{local}"
+    layers = [DeviceLayer(be, 5000 * (rank + 1) + i, NE, N_EXPERT, N_FF, sh_ff=SH_FF, device=dev) for i in range(NL)]
+    nws = [torch.ones(NE, device=dev) for _ in range(NL)]
+    st = MoeStack(be, layers, nws, R, NE, N_EXPERT, N_USED, N_FF, sh_ff=SH_FF)
+    st.hidden.normal_()
+    st.record()
+    for _ in range(W):
+        st.replay()
+    be.sync()
+    u = sum(len(torch.unique(st.ids[li])) for li in range(NL))
+    sampler = ClockSampler(local)
+    l0 = be.launch_count()
+    ms = timed(torch, dist, world, lambda s: st.replay(), K)
+    launches = be.launch_count() - l0
+    clocks = sampler.stop()
+    if rank == 0:
+        peaks, kind = measured_peaks()
+        active = (u + NL) * EXPERT_BYTES
+        us = ms * 1e3 / K
+        print(json.dumps({
+            "metric": "moe_stack_decode_tok_per_s", "value": world * R * K / (ms * 1e-3), "unit": "tok/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"40 Qwen3.6-35B-A3B-shaped MoE FFN layers with RmsNorm and residual add, decode, {R} stream(s)",
+                       "streams": R, "l2": "40 independent weight sets, 21 GB resident (inputs larger than L2)"},
+            "active_expert_gbs": world * active / (us * 1e-6) / 1e9,
+            "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": active / (us * 1e-6) / 1e9, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": active / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], "peak_kind": kind, "traffic": None},
+            "gpu_launches": launches, "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_prefill(args):
+    """Config 2: one 4096-token chunk through the layer, router biased Zipf(1.1) over experts.
+    N = 1: the batched path of one device.  N > 1: tokens and experts sharded over the ranks,
+    NCCL all-to-all dispatch and combine."""
+    import torch
+    import torch.distributed as dist
+    from moe4all_b200 import CudaBackend, MoeFfn, build
+    from moe4all_b200.devgen import DeviceLayer
+    from moe4all_b200.ep import CudaExpertParallelLayer
+
+    world, rank, local = setup_dist()
+    build.build()
+    be = CudaBackend(local)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    be.set_stream(stream.cuda_stream)
+    dev = f"cuda:{local}"
+    T, K, W = 4096, args.steps, max(args.warmup, 3)
+    rows = T // world
+    band = None if world == 1 else (rank * (N_EXPERT // world), N_EXPERT // world)
+    L = DeviceLayer(be, 77, NE, N_EXPERT, N_FF, sh_ff=SH_FF, device=dev, band=band)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(9)
+    zipf = -1.1 * torch.log((torch.randperm(N_EXPERT, generator=gen, device=dev) + 1).float())
+    L.t["router"][:-16].view(torch.float32).view(N_EXPERT, NE)[:, NE - 1] = zipf
+    gen.manual_seed(100 + rank)
+    x = torch.randn(rows, NE, generator=gen, device=dev)
+    dst = torch.empty_like(x)
+    b = L.b
+    if world == 1:
+        rx = x.clone()
+        rx[:, NE - 1] = 1.0  # the bias column is read by the router only (separate router_x handle)
+        op = MoeFfn(x=be.wrap_tensor(x), router_x=be.wrap_tensor(rx), router=b["router"], gate_exps=b["gate"], up_exps=b["up"],
+                    down_exps=b["down"], dst=be.wrap_tensor(dst), rows=rows, ne=NE, n_expert=N_EXPERT, n_used=N_USED,
+                    n_ff_exp=N_FF, sh_gate=b["sh_gate"], sh_up=b["sh_up"], sh_down=b["sh_down"], sh_gate_inp=b["sh_gate_inp"],
+                    sh_ff=SH_FF, path=2)
+        step = lambda s: be.moe_ffn(op)
+    else:
+        x[:, NE - 1] = 1.0  # expert-parallel layer routes on x itself
+        layer = CudaExpertParallelLayer(be, L, N_EXPERT, N_USED, N_FF, NE)
+        step = lambda s: layer.forward(x)
+    for s in range(W):
+        step(s)
+    sampler = ClockSampler(local)
+    l0 = be.launch_count()
+    ms = timed(torch, dist, world, step, K)
+    launches = be.launch_count() - l0
+    clocks = sampler.stop()
+    if rank == 0:
+        peaks, kind = measured_peaks()
+        flops = 3 * 2 * T * N_USED * NE * N_FF  # routed experts only (2*pairs*K*N per GEMM)
+        tfl = flops / (ms / K * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "moe_prefill_routed_tflops", "value": tfl, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "tokens_per_s": T * K / (ms * 1e-3),
+            "config": {"workload": "4096-token prefill chunk through one Qwen3.6-35B-A3B-shaped MoE layer, Zipf(1.1) router bias",
+                       "parallelism": f"ep{world}" if world > 1 else "single", "l2": "522 MB expert banks (inputs larger than L2)"},
+            "roofline": {"bound": "tensor", "kernel": "whole step (router + permute + grouped GEMMs + combine)", "achieved": tfl,
+                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tfl / peaks["bf16_tflops"], "peak_kind": kind,
+                         "traffic": None},
+            "gpu_launches": launches, "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "stack":
+        run_stack(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_ours(args)
 

@@ -16,14 +16,15 @@ __device__ __forceinline__ uint32_t ld_u32_unaligned(const unsigned char* base, 
   return __funnelshift_r(lo, hi, (uint32_t)(off & 3) * 8);
 }
 
-// One warp per output feature, looping over the m input rows.
+// One warp per (input row, output feature): grid.y walks the m input rows.
 template <int DT>
 __global__ void __launch_bounds__(256) k_linear(const unsigned char* __restrict__ w, const float* __restrict__ x,
                                                 float* __restrict__ y, int m, int in_f, int out_f, size_t w_bytes) {
   const int o = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (o >= out_f) return;
-  for (int r = 0; r < m; ++r) {
+  {
+    const int r = blockIdx.y;
     const float* xr = x + (size_t)r * in_f;
     float acc = 0.f;
     if (DT == INFR_CUDA_DT_F32) {
@@ -158,7 +159,8 @@ __global__ void k_add(const float* __restrict__ a, const float* __restrict__ b, 
 
 int32_t launch_linear(infr_cuda_ctx* ctx, int32_t dtype, const uint8_t* w, const float* x, float* y, int m, int in_f,
                       int out_f) {
-  const dim3 grid((out_f + 7) / 8), block(256);
+  if (m > 65535) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: more than 65535 input rows per call");
+  const dim3 grid((out_f + 7) / 8, m), block(256);
   const size_t wb = row_bytes(dtype, in_f) * (size_t)out_f;
   switch (dtype) {
     case INFR_CUDA_DT_F32: k_linear<INFR_CUDA_DT_F32><<<grid, block, 0, ctx->stream>>>(w, x, y, m, in_f, out_f, wb); break;
