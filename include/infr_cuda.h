@@ -121,6 +121,14 @@ typedef struct infr_cuda_moe_ffn_desc {
   uint32_t path;                    /* 0 = choose by rows; 1 = force the small-m (decode) kernels;
                                        2 = force the grouped-GEMM (prefill) kernels; 3 = same with
                                        the legacy mma.sync tiles instead of tcgen05               */
+  /* optional fusions the reference's graph rewriter applies around the op
+   * (crates/infr-core/src/fusion.rs:17-25, 53-82); both need router_x == x */
+  const infr_cuda_buf* norm_weight; /* RmsNorm -> MoeFfn: x is the un-normed row, the op first computes
+                                       RmsNorm(x, norm_weight, norm_eps) and feeds that to the router,
+                                       the experts and the shared expert; NULL = off                */
+  const infr_cuda_buf* residual;    /* MoeFfn -> Add: [rows, ne] f32 added to the result; may be the
+                                       same buffer as dst (in-place hidden update); NULL = off      */
+  float norm_eps;
   uint32_t stages;                  /* 0 = the whole op.  Otherwise a mask of the kernels to launch,
                                        for timing one of them alone: 1 router + top-k, 2 gate/up,
                                        4 down + combine.  Later stages read what an earlier full

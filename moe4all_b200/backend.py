@@ -80,6 +80,7 @@ class _Desc(C.Structure):
         ("ep_lo", C.c_uint32), ("ep_n_local", C.c_uint32),
         ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p),
         ("sh_gate_inp", C.c_void_p), ("sh_ff", C.c_uint32), ("path", C.c_uint32),
+        ("norm_weight", C.c_void_p), ("residual", C.c_void_p), ("norm_eps", C.c_float),
         ("stages", C.c_uint32),
     ]
 
@@ -236,6 +237,9 @@ class MoeFfn:
     sh_ff: int = 0
     path: int = 0  # 0 auto, 1 small-m kernels, 2 grouped-GEMM kernels
     stages: int = 0  # 0 whole op; mask 1 router+top-k, 2 gate/up, 4 down (timing one kernel alone)
+    norm_weight: Optional[Buffer] = None  # RmsNorm -> MoeFfn fusion (fusion.rs:17-25): x is the un-normed row
+    norm_eps: float = 1e-6
+    residual: Optional[Buffer] = None     # MoeFfn -> Add fusion: added to the result, may be dst itself
     _keep: list = field(default_factory=list, repr=False)
 
     def to_desc(self) -> _Desc:
@@ -252,6 +256,7 @@ class MoeFfn:
         d.ep_lo, d.ep_n_local = self.ep_band if self.ep_band else (0, 0)
         d.sh_gate, d.sh_up, d.sh_down, d.sh_gate_inp = _h(self.sh_gate), _h(self.sh_up), _h(self.sh_down), _h(self.sh_gate_inp)
         d.sh_ff, d.path, d.stages = self.sh_ff, self.path, self.stages
+        d.norm_weight, d.residual, d.norm_eps = _h(self.norm_weight), _h(self.residual), self.norm_eps
         return d
 
 

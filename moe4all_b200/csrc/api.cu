@@ -333,6 +333,12 @@ static int32_t validate_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d)
   const size_t db = (size_t)d->n_expert * d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
   if (!fits(d->gate_exps, gb) || !fits(d->up_exps, gb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: gate/up bank missing or too small");
   if (!fits(d->down_exps, db)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: down bank missing or too small");
+  if (d->norm_weight) {
+    if (!fits(d->norm_weight, (size_t)d->ne * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: norm_weight too small");
+    if (d->router_x->ptr != d->x->ptr) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: the RmsNorm fusion needs router_x == x");
+    if (d->ne > 8192) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: the RmsNorm fusion covers ne <= 8192");
+  }
+  if (d->residual && !fits(d->residual, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: residual too small");
   if (d->ep_n_local && (uint64_t)d->ep_lo + d->ep_n_local > d->n_expert)
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ep band exceeds n_expert");
   if (d->sh_gate || d->sh_up || d->sh_down) {
@@ -441,6 +447,8 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     rp.xq_lo = s.xq_lo;
     rp.xq_hi = s.xq_hi;
     rp.xscale = s.xscale;
+    rp.rms_w = d->norm_weight ? static_cast<const float*>(d->norm_weight->ptr) : nullptr;
+    rp.rms_eps = d->norm_eps;
     const uint32_t stages = d->stages ? d->stages : 7u;
     if ((stages & 1u) && (rc = launch_route(ctx, rp, true))) return rc;
     DecodeParams dp = {};
@@ -459,6 +467,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.sh_down = has_sh ? static_cast<const uint8_t*>(d->sh_down->ptr) : nullptr;
     dp.act = s.act;
     dp.dst = static_cast<float*>(d->dst->ptr);
+    dp.residual = d->residual ? static_cast<const float*>(d->residual->ptr) : nullptr;
     dp.status = ctx->status;
     dp.trace = ctx->trace;
     dp.gate_stride = (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
@@ -485,15 +494,26 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     const int rows_bound = n_pairs + shared_rows;
     Scratch sz = carve(nullptr, d, false);
     const size_t gbytes = grouped_scratch_bytes(rows_bound, n_pairs, (int)d->n_expert + 1, (int)d->ne, (int)d->n_ff_exp);
-    if ((rc = ensure_scratch(ctx, sz.total + gbytes))) return rc;
+    const size_t hn_bytes = d->norm_weight ? align_up((size_t)d->rows * d->ne * 4, 256) : 0;
+    if ((rc = ensure_scratch(ctx, sz.total + gbytes + hn_bytes))) return rc;
     Scratch s = carve(ctx->scratch, d, false);
     RouteParams rp = route_params(ctx, d, s, true);
+    const float* x_eff = static_cast<const float*>(d->x->ptr);
+    if (d->norm_weight) {
+      // RmsNorm -> MoeFfn: the batched kernels read the normed rows from scratch
+      float* hn = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + sz.total + gbytes);
+      if ((rc = launch_rmsnorm(ctx, x_eff, static_cast<const float*>(d->norm_weight->ptr), hn, (int)d->rows, (int)d->ne, d->norm_eps))) return rc;
+      x_eff = hn;
+      rp.router_x = hn;
+      rp.x = hn;
+    }
     const uint32_t stages = d->stages ? d->stages : 7u;
     if ((stages & 1u) && (rc = launch_route(ctx, rp, false))) return rc;
     if (!(stages & 6u)) return INFR_CUDA_OK;
     GroupedCall c = {};
     c.scratch = static_cast<char*>(ctx->scratch) + sz.total;
-    c.x = static_cast<const float*>(d->x->ptr);
+    c.x = x_eff;
+    c.residual = d->residual ? static_cast<const float*>(d->residual->ptr) : nullptr;
     c.ids = rp.ids;
     c.wts = rp.wts;
     c.sh_logit = (has_sh && d->sh_gate_inp) ? s.sh_logit : nullptr;

@@ -388,6 +388,7 @@ __global__ void __launch_bounds__(DN_MAX_WARPS * 32, 1) k_decode_down(DecodePara
   if (tid < TI) {
     float o = 0.f;
     for (int s = 0; s < n_slots; ++s) o += s_part[s * TI + tid];
+    if (p.residual != nullptr) o += __ldcg(p.residual + (size_t)r * p.ne + i0 + tid);  // MoeFfn -> Add
     p.dst[(size_t)r * p.ne + i0 + tid] = o;
   }
 }

@@ -395,7 +395,8 @@ __global__ void __launch_bounds__(256) k_unpermute_combine(const float* __restri
 __global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
                                                                const float* __restrict__ wts, const float* __restrict__ sh_logit,
                                                                const int* __restrict__ seg_off, int n_seg_routed, int has_shared,
-                                                               int rows, int n_used, int ne, float* __restrict__ dst) {
+                                                               int rows, int n_used, int ne, const float* residual,
+                                                               float* dst) {
   const int t = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
   if (c >= ne) return;
@@ -411,6 +412,10 @@ __global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __re
     const float gsh = sh_logit ? 1.0f / (1.0f + __expf(-sh_logit[t])) : 1.0f;
     const float4 v = *reinterpret_cast<const float4*>(y + (size_t)(seg_off[n_seg_routed] + t) * ne + c);
     o.x += gsh * v.x; o.y += gsh * v.y; o.z += gsh * v.z; o.w += gsh * v.w;
+  }
+  if (residual != nullptr) {  // MoeFfn -> Add; may alias dst: each element is read, then written, by this thread
+    const float4 h = *reinterpret_cast<const float4*>(residual + (size_t)t * ne + c);
+    o.x += h.x; o.y += h.y; o.z += h.z; o.w += h.w;
   }
   *reinterpret_cast<float4*>(dst + (size_t)t * ne + c) = o;
 }
@@ -540,7 +545,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   }
   if (c.dst) {
     k_unpermute_combine_seg<<<dim3((c.ne / 4 + 255) / 256, c.rows), 256, 0, st>>>(y, pos_of_pair, c.wts, c.sh_logit, seg_off, n_seg_routed,
-                                                                                   c.shared_rows > 0 ? 1 : 0, c.rows, c.n_used, c.ne, c.dst);
+                                                                                   c.shared_rows > 0 ? 1 : 0, c.rows, c.n_used, c.ne, c.residual, c.dst);
     ctx->launches += 1;
   }
   return check_cuda(ctx, cudaGetLastError(), "grouped ffn launch");

@@ -13,6 +13,8 @@ struct RouteParams {
   const float* router;       // [n_expert, ne] f32
   const float* sh_gate_inp;  // [ne] or null
   const float* bias;         // [n_expert] or null
+  const float* rms_w;        // [ne] RmsNorm weight applied to x before everything else, or null
+  float rms_eps;
   float* logits;             // [rows, n_expert] scratch
   float* sh_logit;           // [rows] scratch
   int32_t* ids;              // [rows, n_used]
@@ -37,6 +39,7 @@ struct DecodeParams {
   const uint8_t *sh_gate, *sh_up, *sh_down;  // shared expert or null
   float* act;            // [rows*n_used, nff] then [rows, sh_ff]
   float* dst;            // [rows, ne]
+  const float* residual; // [rows, ne] added to the result (may be dst itself), or null
   DeviceStatus* status;
   unsigned long long* trace;  // optional phase stamps
   size_t gate_stride, up_stride, down_stride;  // bytes per expert
@@ -67,6 +70,7 @@ struct GroupedCall {
   const float* sh_logit;   // [rows] or null
   const int* seg_off_in;   // [n_expert + 1] device offsets (grouped-rows form)
   float* dst;              // [rows, ne] combined output, or null (grouped-rows form)
+  const float* residual;   // [rows, ne] added to dst (may alias it), or null
   float* y_out;            // grouped-rows form: per-row outputs [rows, ne]; null = scratch
   const uint8_t *gate, *up, *down, *sh_gate, *sh_up, *sh_down;
   size_t gate_stride, up_stride, down_stride;

@@ -24,7 +24,8 @@ def oracle_sublayer(h, nw, L):
     return orc.add(h, res.dst), res
 
 
-def test_stack_teacher_forced_and_replay(backend):
+@pytest.mark.parametrize("fused", [False, True])
+def test_stack_teacher_forced_and_replay(backend, fused):
     be = backend
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
@@ -34,7 +35,7 @@ def test_stack_teacher_forced_and_replay(backend):
             gen = torch.Generator(device="cuda")
             gen.manual_seed(1)
             nws = [1.0 + 0.1 * torch.randn(NE, generator=gen, device="cuda") for _ in range(NL)]
-            st = MoeStack(be, layers, nws, ROWS, NE, E, K, NFF, sh_ff=NFF)
+            st = MoeStack(be, layers, nws, ROWS, NE, E, K, NFF, sh_ff=NFF, fused=fused)
             hosts = [L.host() for L in layers]
             h0 = np.random.default_rng(2).normal(size=(ROWS, NE)).astype(np.float32)
             # teacher-forced: every layer starts from the oracle's hidden state
@@ -64,3 +65,27 @@ def test_stack_teacher_forced_and_replay(backend):
         finally:
             be.sync()
             be.set_stream(None)
+
+
+@pytest.mark.parametrize("rows,path", [(2, 1), (40, 2)])
+def test_fused_norm_and_residual_one_op(backend, rows, path):
+    # RmsNorm -> MoeFfn -> Add folded into one call, in place on the hidden state, both paths
+    from moe4all_b200 import MoeFfn, synth
+    be = backend
+    L = synth.make_layer(71, NE, E, NFF, sh_ff=NFF, router_std=0.05)
+    rng = np.random.default_rng(3)
+    h = rng.normal(size=(rows, NE)).astype(np.float32)
+    nw = (1.0 + 0.1 * rng.normal(size=NE)).astype(np.float32)
+    b = {k: be.from_host(getattr(L, k)) for k in ("router", "gate", "up", "down", "sh_gate", "sh_up", "sh_down", "sh_gate_inp")}
+    hb, nwb = be.from_host(h), be.from_host(nw)
+    ids = be.alloc(rows * K * 4)
+    be.moe_ffn(MoeFfn(x=hb, dst=hb, residual=hb, norm_weight=nwb, norm_eps=1e-6, router=b["router"], gate_exps=b["gate"],
+                      up_exps=b["up"], down_exps=b["down"], rows=rows, ne=NE, n_expert=E, n_used=K, n_ff_exp=NFF,
+                      sh_gate=b["sh_gate"], sh_up=b["sh_up"], sh_down=b["sh_down"], sh_gate_inp=b["sh_gate_inp"], sh_ff=NFF,
+                      ids_out=ids, path=path))
+    got = be.download(hb, np.float32).reshape(rows, NE)
+    want, res = oracle_sublayer(h, nw, L)
+    ties = set(near_tie_rows(res, K).tolist())
+    keep = [r for r in range(rows) if r not in ties]
+    assert np.array_equal(be.download(ids, np.int32).reshape(rows, K)[keep], res.ids[keep])
+    assert_close(got[keep], want[keep])
