@@ -306,14 +306,33 @@ __global__ void __launch_bounds__(DN_MAX_WARPS * 32, 1) k_decode_down(DecodePara
       const float* a = s_act + (shared_slot ? (size_t)p.n_used * p.nff : (size_t)s * p.nff);
       for (int u = lane; u < units; u += 32) {
         const int b = u >> 4, h = (u >> 3) & 1, lw = u & 7;
-        // activations of the unit and 96 * their per-quadrant sums
-        float av[16], s96[4];
+        // The unit's 16 activations in 16-bit fixed point with the unit's own scale (X = 256 hi + lo,
+        // signed 8-bit limbs, four elements per word like the code words): products with the 6-bit
+        // codes are exact integer dot products, and the unpack stays off the half-rate logic pipe.
         const float* ab = a + b * 256 + h * 128 + lw * 4;
+        float4 av[4];
+        float amax = 0.f;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const float4 v = *reinterpret_cast<const float4*>(ab + 32 * q);
-          av[4 * q + 0] = v.x; av[4 * q + 1] = v.y; av[4 * q + 2] = v.z; av[4 * q + 3] = v.w;
-          s96[q] = 96.f * ((v.x + v.y) + (v.z + v.w));
+          av[q] = *reinterpret_cast<const float4*>(ab + 32 * q);
+          amax = fmaxf(fmaxf(fabsf(av[q].x), fabsf(av[q].y)), fmaxf(amax, fmaxf(fabsf(av[q].z), fabsf(av[q].w))));
+        }
+        const float a_inv = amax > 0.f ? 32639.f / amax : 0.f, a_scale = amax / 32639.f;
+        int xl[4], xh[4], s32[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int X[4] = {__float2int_rn(av[q].x * a_inv), __float2int_rn(av[q].y * a_inv), __float2int_rn(av[q].z * a_inv),
+                            __float2int_rn(av[q].w * a_inv)};
+          uint32_t lo = 0, hi = 0;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const int hh = (X[t] + 128) >> 8, ll = X[t] - (hh << 8);
+            lo |= (uint32_t)(ll & 0xFF) << (8 * t);
+            hi |= (uint32_t)(hh & 0xFF) << (8 * t);
+          }
+          xl[q] = (int)lo;
+          xh[q] = (int)hi;
+          s32[q] = 32 * ((X[0] + X[1]) + (X[2] + X[3]));
         }
         const uint32_t boff = (uint32_t)b * Q6K_BLOCK_BYTES;
         const uint32_t sel = (lw >> 2) ? 0x7531u : 0x6420u;
@@ -329,27 +348,19 @@ __global__ void __launch_bounds__(DN_MAX_WARPS * 32, 1) k_decode_down(DecodePara
             const uint32_t S0 = lds_u32_unaligned(wt, ro + 192 + 8 * h);
             const uint32_t S1 = lds_u32_unaligned(wt, ro + 196 + 8 * h);
             const float d = f16_bits_to_f32(*reinterpret_cast<const unsigned short*>(wt + ro + 208));
-            // codes as bytes 0x80 | (q << 1)
-            const uint32_t cs[4] = {((A << 1) & 0x1E1E1E1Eu) | ((H << 5) & 0x60606060u) | 0x80808080u,
-                                    ((B << 1) & 0x1E1E1E1Eu) | ((H << 3) & 0x60606060u) | 0x80808080u,
-                                    ((A >> 3) & 0x1E1E1E1Eu) | ((H << 1) & 0x60606060u) | 0x80808080u,
-                                    ((B >> 3) & 0x1E1E1E1Eu) | ((H >> 1) & 0x60606060u) | 0x80808080u};
+            // 6-bit codes of the four quadrants, one per byte
+            const uint32_t cs[4] = {(A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u), (B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u),
+                                    ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u), ((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u)};
             // scales of the four quadrants: bytes (lw>>2) + 2q of the eight scale bytes of this half
             const uint32_t sc4 = __byte_perm(S0, S1, sel);
-            float part = 0.f;
+            long long part = 0;
 #pragma unroll
             for (int qd = 0; qd < 4; ++qd) {
-              const uint32_t c = cs[qd];
-              float2 f = __fmul2_rn(make_float2(byte_to_unit_float<0>(c), byte_to_unit_float<1>(c)),
-                                    make_float2(av[4 * qd + 0], av[4 * qd + 1]));
-              f = __ffma2_rn(make_float2(byte_to_unit_float<2>(c), byte_to_unit_float<3>(c)),
-                             make_float2(av[4 * qd + 2], av[4 * qd + 3]), f);
-              const float F = f.x + f.y;
-              const float sc = (float)(int)(signed char)((sc4 >> (8 * qd)) & 0xFFu);
-              // Σ sc·(q-32)·a = sc·(64·F − 96·S)
-              part = fmaf(sc, fmaf(64.f, F, -s96[qd]), part);
+              // sum (q - 32) X = 256 * dot(codes, hi) + dot(codes, lo) - 32 * sum X   (|.| < 2^24)
+              const int t = __dp4a((int)cs[qd], xh[qd], 0) * 256 + __dp4a((int)cs[qd], xl[qd], 0) - s32[qd];
+              part += (long long)(int)(signed char)((sc4 >> (8 * qd)) & 0xFFu) * t;
             }
-            acc[q] = fmaf(d, part, acc[q]);
+            acc[q] = fmaf(d * a_scale, (float)part, acc[q]);
           }
         }
       }
