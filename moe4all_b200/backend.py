@@ -25,6 +25,7 @@ EXPORTS = [
     "infr_cuda_create", "infr_cuda_destroy", "infr_cuda_last_error", "infr_cuda_name",
     "infr_cuda_set_stream", "infr_cuda_alloc", "infr_cuda_wrap", "infr_cuda_free",
     "infr_cuda_buf_len", "infr_cuda_buf_ptr", "infr_cuda_upload", "infr_cuda_download",
+    "infr_cuda_upload_async", "infr_cuda_download_async",
     "infr_cuda_sync", "infr_cuda_moe_ffn", "infr_cuda_moe_route", "infr_cuda_linear",
     "infr_cuda_gated_act", "infr_cuda_moe_shared_add", "infr_cuda_rmsnorm", "infr_cuda_add",
     "infr_cuda_moe_expert_rows", "infr_cuda_launch_count",
@@ -119,6 +120,8 @@ def load_library(path: Optional[str] = None):
     L.infr_cuda_buf_ptr.restype = vp
     L.infr_cuda_upload.argtypes = [vp, vp, sz, vp, sz]
     L.infr_cuda_download.argtypes = [vp, vp, sz, vp, sz]
+    L.infr_cuda_upload_async.argtypes = [vp, vp, sz, vp, sz]
+    L.infr_cuda_download_async.argtypes = [vp, vp, sz, vp, sz]
     L.infr_cuda_sync.argtypes = [vp]
     L.infr_cuda_moe_ffn.argtypes = [vp, C.POINTER(_Desc)]
     L.infr_cuda_moe_route.argtypes = [vp, C.POINTER(_Desc)]
@@ -329,6 +332,14 @@ class CudaBackend:
 
     def upload_ptr(self, dst: Buffer, host_ptr: int, nbytes: int, offset: int = 0) -> None:
         self._check(self._lib.infr_cuda_upload(self._ctx, dst.handle, offset, host_ptr, nbytes))
+
+    def upload_ptr_async(self, dst: Buffer, host_ptr: int, nbytes: int, offset: int = 0) -> None:
+        """Queued copy: the host range must stay untouched until `sync()`."""
+        self._check(self._lib.infr_cuda_upload_async(self._ctx, dst.handle, offset, host_ptr, nbytes))
+
+    def download_ptr_async(self, src: Buffer, host_ptr: int, nbytes: int, offset: int = 0) -> None:
+        """Queued copy: the host range holds the data after `sync()`."""
+        self._check(self._lib.infr_cuda_download_async(self._ctx, src.handle, offset, host_ptr, nbytes))
 
     def download(self, src: Buffer, dtype=np.float32, count: Optional[int] = None, offset: int = 0) -> np.ndarray:
         itemsize = np.dtype(dtype).itemsize

@@ -40,14 +40,19 @@ int32_t ensure_scratch(infr_cuda_ctx* ctx, size_t bytes) {
 cudaError_t ensure_smem(const void* kernel, size_t bytes) {
   static std::mutex mu;
   static std::map<std::pair<int, const void*>, size_t> granted;
-  if (bytes <= 48 * 1024) return cudaSuccess;
   int dev = 0;
   cudaGetDevice(&dev);
   std::lock_guard<std::mutex> lock(mu);
   size_t& g = granted[{dev, kernel}];
-  if (bytes <= g) return cudaSuccess;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-  if (e == cudaSuccess) g = bytes;
+  if (g != 0 && bytes <= g) return cudaSuccess;
+  cudaError_t e = cudaSuccess;
+  // Ask for the largest shared-memory split on every kernel of the chain: an SM changes its
+  // split only when idle, so kernels that prefer different splits cannot share one, and a
+  // dependent kernel's CTAs could not start beside those of its predecessor.
+  if (g == 0) e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (e == cudaSuccess && bytes > 48 * 1024)
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) g = bytes > 48 * 1024 ? bytes : 48 * 1024;
   return e;
 }
 
@@ -68,16 +73,23 @@ struct DeviceGuard {
 
 bool fits(const infr_cuda_buf* b, size_t need) { return b && b->ptr && b->bytes >= need; }
 
-// A bounded wait that ran out inside a kernel is reported here, after the stream has drained.
-int32_t poll_status(infr_cuda_ctx* ctx) {
-  DeviceStatus st;
-  cudaError_t e = cudaMemcpy(&st, ctx->status, sizeof(st), cudaMemcpyDeviceToHost);
-  if (e != cudaSuccess) return check_cuda(ctx, e, "status read");
-  if (st.timeout) {
-    cudaMemset(ctx->status, 0, sizeof(DeviceStatus));
+// Drains the context's stream and reports a bounded wait that ran out inside a kernel.  The status
+// words travel to a pinned host mirror on the same stream, so the caller pays for one wait.
+int32_t drain_and_poll(infr_cuda_ctx* ctx, const char* what) {
+  // A recorded plan ends with this copy, so nothing is queued here when only plans ran since.
+  cudaError_t e = cudaSuccess;
+  if (ctx->launches != ctx->launches_at_status) {
+    e = cudaMemcpyAsync(ctx->status_host, ctx->status, sizeof(DeviceStatus), cudaMemcpyDeviceToHost, ctx->stream);
+    ctx->launches_at_status = ctx->launches;
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) return check_cuda(ctx, e, what);
+  const int tag = ctx->status_host->timeout;
+  if (tag) {
+    cudaMemsetAsync(ctx->status, 0, sizeof(DeviceStatus), ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
     char msg[96];
-    std::snprintf(msg, sizeof msg, "a bounded device-side wait ran out (kernel tag %d); outputs of that call are invalid",
-                  st.timeout);
+    std::snprintf(msg, sizeof msg, "a bounded device-side wait ran out (kernel tag %d); outputs of that call are invalid", tag);
     return fail(ctx, INFR_CUDA_ERR_TIMEOUT, msg);
   }
   return INFR_CUDA_OK;
@@ -108,6 +120,7 @@ int32_t infr_cuda_create(int32_t device, infr_cuda_ctx** out) {
   DeviceGuard g(device);
   if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaMalloc(&ctx->status, sizeof(DeviceStatus)) != cudaSuccess ||
+      cudaMallocHost(&ctx->status_host, sizeof(DeviceStatus)) != cudaSuccess ||
       cudaMalloc(&ctx->counters, 64 * sizeof(unsigned int)) != cudaSuccess ||
       cudaMemset(ctx->status, 0, sizeof(DeviceStatus)) != cudaSuccess ||
       cudaMemset(ctx->counters, 0, 64 * sizeof(unsigned int)) != cudaSuccess) {
@@ -125,6 +138,7 @@ void infr_cuda_destroy(infr_cuda_ctx* ctx) {
   if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->status) cudaFree(ctx->status);
+  if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->counters) cudaFree(ctx->counters);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
@@ -212,17 +226,32 @@ int32_t infr_cuda_download(infr_cuda_ctx* ctx, const infr_cuda_buf* src, size_t 
   DeviceGuard g(ctx->device);
   cudaError_t e = cudaSuccess;
   if (n) e = cudaMemcpyAsync(dst, static_cast<const char*>(src->ptr) + src_off, n, cudaMemcpyDeviceToHost, ctx->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
   if (e != cudaSuccess) return check_cuda(ctx, e, "download");
-  return poll_status(ctx);
+  return drain_and_poll(ctx, "download");
+}
+
+int32_t infr_cuda_upload_async(infr_cuda_ctx* ctx, infr_cuda_buf* dst, size_t dst_off, const void* src, size_t n) {
+  if (!ctx || !dst || (!src && n)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "upload: null argument");
+  if (dst_off > dst->bytes || n > dst->bytes - dst_off) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "upload: range exceeds the buffer");
+  if (!n) return INFR_CUDA_OK;
+  DeviceGuard g(ctx->device);
+  return check_cuda(ctx, cudaMemcpyAsync(static_cast<char*>(dst->ptr) + dst_off, src, n, cudaMemcpyHostToDevice, ctx->stream),
+                    "upload (queued)");
+}
+
+int32_t infr_cuda_download_async(infr_cuda_ctx* ctx, const infr_cuda_buf* src, size_t src_off, void* dst, size_t n) {
+  if (!ctx || !src || (!dst && n)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "download: null argument");
+  if (src_off > src->bytes || n > src->bytes - src_off) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "download: range exceeds the buffer");
+  if (!n) return INFR_CUDA_OK;
+  DeviceGuard g(ctx->device);
+  return check_cuda(ctx, cudaMemcpyAsync(dst, static_cast<const char*>(src->ptr) + src_off, n, cudaMemcpyDeviceToHost, ctx->stream),
+                    "download (queued)");
 }
 
 int32_t infr_cuda_sync(infr_cuda_ctx* ctx) {
   if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
   DeviceGuard g(ctx->device);
-  cudaError_t e = cudaStreamSynchronize(ctx->stream);
-  if (e != cudaSuccess) return check_cuda(ctx, e, "sync");
-  return poll_status(ctx);
+  return drain_and_poll(ctx, "sync");
 }
 
 uint64_t infr_cuda_launch_count(const infr_cuda_ctx* ctx) { return ctx ? ctx->launches : 0; }
@@ -252,7 +281,10 @@ int32_t infr_cuda_graph_end(infr_cuda_ctx* ctx, infr_cuda_graph** out) {
   DeviceGuard g(ctx->device);
   ctx->capturing = false;
   cudaGraph_t graph = nullptr;
+  // last node: the status words travel to their host mirror with every replay
+  cudaError_t e0 = cudaMemcpyAsync(ctx->status_host, ctx->status, sizeof(DeviceStatus), cudaMemcpyDeviceToHost, ctx->stream);
   cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+  if (e == cudaSuccess && e0 != cudaSuccess) e = e0;
   if (e != cudaSuccess || !graph) return check_cuda(ctx, e == cudaSuccess ? cudaErrorUnknown : e, "graph_end");
   cudaGraphExec_t exec = nullptr;
   e = cudaGraphInstantiate(&exec, graph, 0);
@@ -278,7 +310,10 @@ int32_t infr_cuda_graph_launch(infr_cuda_ctx* ctx, infr_cuda_graph* graph) {
   if (!ctx || !graph || !graph->exec) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "graph_launch: null graph");
   DeviceGuard g(ctx->device);
   cudaError_t e = cudaGraphLaunch(graph->exec, ctx->stream);
-  if (e == cudaSuccess) ctx->launches += graph->kernels;
+  if (e == cudaSuccess) {
+    ctx->launches += graph->kernels;
+    ctx->launches_at_status = ctx->launches;  // the plan's last node refreshes the mirror after all earlier work
+  }
   return check_cuda(ctx, e, "graph_launch");
 }
 

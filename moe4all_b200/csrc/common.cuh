@@ -54,6 +54,8 @@ struct infr_cuda_ctx {
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   infr::DeviceStatus* status = nullptr;       // device memory
+  infr::DeviceStatus* status_host = nullptr;  // pinned host mirror, filled when the stream is drained
+  uint64_t launches_at_status = ~0ull;        // value of `launches` when the mirror was last queued for refresh
   unsigned int* counters = nullptr;           // device memory: completion counters (zeroed by users)
   unsigned long long* trace = nullptr;        // optional phase stamps (see trace_stamp)
 };
@@ -167,6 +169,27 @@ __device__ __forceinline__ void trace_stamp(unsigned long long* tr, int slot) {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
     tr[2 * slot] = g;
     tr[2 * slot + 1] = (unsigned long long)clock64();
+  }
+}
+
+// Grid-wide extremes for the same buffer: earliest / latest time any CTA passed a point.
+__device__ __forceinline__ void trace_extreme(unsigned long long* tr, int slot, bool latest) {
+  if (tr != nullptr && threadIdx.x == 0) {
+    unsigned long long g;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    if (latest) atomicMax(&tr[2 * slot], g);
+    else atomicMin(&tr[2 * slot], g);
+  }
+}
+
+// Per-CTA stamps for the first 128 CTAs: low 40 bits of the global timer, SM id in the low byte.
+__device__ __forceinline__ void trace_cta(unsigned long long* tr, int k) {
+  if (tr != nullptr && threadIdx.x == 0 && blockIdx.x < 128) {
+    unsigned long long g;
+    unsigned int sm;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    tr[128 + 3 * blockIdx.x + k] = ((g & 0xFFFFFFFFFFull) << 8) | sm;
   }
 }
 

@@ -27,6 +27,7 @@ constexpr int GU_MAX_CHUNKS = 4;
 constexpr int GU_XQPITCH = 144;  // bytes per 64-element group of fixed-point x: 64 low limbs, 64 high limbs, pad
 
 constexpr int DN_MAX_WARPS = 24;
+constexpr int DN_XPITCH = 36;     // words per 128-activation chunk and limb: four neighbouring chunks start in four 16-byte bank groups
 constexpr int DN_MAX_SLOTS = 33;  // n_used ≤ 32 plus the shared expert
 
 __device__ __forceinline__ bool in_band(const DecodeParams& p, int e) {
@@ -43,7 +44,7 @@ __device__ __forceinline__ bool in_band(const DecodeParams& p, int e) {
 // Lane L owns the 64-element groups g = L, L+32, ... of the input (for ne = 2048 exactly one, so
 // its 64 activations stay in registers for the whole tile).
 template <int NG>
-__global__ void __launch_bounds__(GU_THREADS, 2) k_decode_gateup(DecodeParams p, int n_chunks) {
+__global__ void __maxnreg__(56) k_decode_gateup(DecodeParams p, int n_chunks) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_bar[GU_MAX_CHUNKS];
 
@@ -86,6 +87,8 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_decode_gateup(DecodeParams p,
 
   unsigned long long* tr = (blockIdx.x == 0) ? p.trace : nullptr;
   trace_stamp(tr, 16);
+  trace_extreme(p.trace, 40, false);
+  trace_extreme(p.trace, 41, true);
   pdl_wait();     // ids and x come from kernels earlier in the stream
   trace_stamp(tr, 17);
   pdl_trigger();  // only now: the next kernel reads ids as soon as it starts
@@ -181,6 +184,7 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_decode_gateup(DecodeParams p,
     }
   }
   trace_stamp(tr, 23);
+  trace_extreme(p.trace, 42, true);
   if (!ok) {
     // a copy never signalled: report and make sure nothing is still landing in this CTA's
     // shared memory before it is handed to another CTA
@@ -200,18 +204,13 @@ __global__ void __launch_bounds__(GU_THREADS, 2) k_decode_gateup(DecodeParams p,
 //
 // Q6_K blocks are 210 bytes, so odd blocks start 2 bytes off a word boundary: words are fetched
 // as two aligned loads and a funnel shift.
-__device__ __forceinline__ uint32_t lds_u32_unaligned(const unsigned char* base, uint32_t off) {
-  const uint32_t a = off & ~3u;
-  const uint32_t lo = *reinterpret_cast<const uint32_t*>(base + a);
-  const uint32_t hi = *reinterpret_cast<const uint32_t*>(base + a + 4);
-  return __funnelshift_r(lo, hi, (off & 3u) * 8);
-}
 
-__global__ void __launch_bounds__(DN_MAX_WARPS * 32, 1) k_decode_down(DecodeParams p, int TI) {
+__global__ void __maxnreg__(56) k_decode_down(DecodeParams p, int TI) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_bar[DN_MAX_SLOTS];
   __shared__ float s_w[DN_MAX_SLOTS];
   __shared__ int s_on[DN_MAX_SLOTS];
+  __shared__ uint32_t s_off[DN_MAX_SLOTS];  // slab start inside its shared-memory slot
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x, nwarps = nthreads >> 5;
   const int nb = p.nff / 256;                    // blocks per routed row
@@ -224,16 +223,25 @@ __global__ void __launch_bounds__(DN_MAX_WARPS * 32, 1) k_decode_down(DecodePara
 
   // shared-memory carve-up: weights per slot, activations per slot, weighted partial outputs
   const uint32_t slab = (uint32_t)TI * drb, sh_slab = (uint32_t)TI * sh_drb;
-  const uint32_t slab_pad = (uint32_t)align_up(slab + 8, 16), sh_slab_pad = (uint32_t)align_up(sh_slab + 8, 16);
-  unsigned char* s_wt = smem;
-  float* s_act = reinterpret_cast<float*>(smem + (size_t)p.n_used * slab_pad + (has_sh ? sh_slab_pad : 0));
-  float* s_part = s_act + (size_t)p.n_used * p.nff + (has_sh ? p.sh_ff : 0);  // [n_slots][TI]
+  // A slab lands at the same offset inside a 128-byte line as its source has in global memory:
+  // bulk copies whose two sides disagree modulo 128 run several times slower.
+  const uint32_t slab_pad = (uint32_t)align_up(slab + 8, 128) + 128, sh_slab_pad = (uint32_t)align_up(sh_slab + 8, 128) + 128;
+  unsigned char* s_wt = smem + ((128u - (smem_u32(smem) & 127u)) & 127u);
+  // activations as 16-bit fixed point, one scale per 128-element chunk (= half a Q6_K block):
+  // low limbs, high limbs (4 elements per word), chunk scales, integer sums per 16 elements
+  const int n_act = p.n_used * p.nff + (has_sh ? p.sh_ff : 0), n_chunk = n_act / 128;
+  uint32_t* s_xlo = reinterpret_cast<uint32_t*>(s_wt + (size_t)p.n_used * slab_pad + (has_sh ? sh_slab_pad : 0));  // [n_chunk][DN_XPITCH]
+  uint32_t* s_xhi = s_xlo + n_chunk * DN_XPITCH;
+  float* s_xsc = reinterpret_cast<float*>(s_xhi + n_chunk * DN_XPITCH);  // [n_chunk]
+  int* s_s16 = reinterpret_cast<int*>(s_xsc + n_chunk);          // [n_chunk][8]
+  float* s_part = reinterpret_cast<float*>(s_s16 + n_chunk * 8);  // [n_slots][TI]
 
   // The routing result was complete before this kernel could start (the gate/up kernel releases
   // its dependents only after it has itself waited for the router), so the weight slabs are
   // requested right away and stream in while the gate/up kernel is still running.
   unsigned long long* tr = (blockIdx.x == 0) ? p.trace : nullptr;
   trace_stamp(tr, 32);
+  trace_extreme(p.trace, 43, true);
   pdl_trigger();
   if (tid < n_slots) {
     const int s = tid;
@@ -249,144 +257,140 @@ __global__ void __launch_bounds__(DN_MAX_WARPS * 32, 1) k_decode_down(DecodePara
     // each slot's barrier and copy are set up by the slot's own thread
     mbar_init(&s_bar[s], 1);
     mbar_fence_init();
+    s_off[s] = 0;
     if (s_on[s]) {
       if (s < p.n_used) {
+        const uint8_t* src = p.down + (size_t)(s_on[s] - 1) * p.down_stride + (size_t)i0 * drb;
+        s_off[s] = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 127u);
         mbar_arrive_expect_tx(&s_bar[s], slab);
-        bulk_g2s(s_wt + (size_t)s * slab_pad, p.down + (size_t)(s_on[s] - 1) * p.down_stride + (size_t)i0 * drb, slab,
-                 &s_bar[s]);
+        bulk_g2s(s_wt + (size_t)s * slab_pad + s_off[s], src, slab, &s_bar[s]);
       } else {
+        const uint8_t* src = p.sh_down + (size_t)i0 * sh_drb;
+        s_off[s] = (uint32_t)(reinterpret_cast<uintptr_t>(src) & 127u);
         mbar_arrive_expect_tx(&s_bar[s], sh_slab);
-        bulk_g2s(s_wt + (size_t)p.n_used * slab_pad, p.sh_down + (size_t)i0 * sh_drb, sh_slab, &s_bar[s]);
+        bulk_g2s(s_wt + (size_t)p.n_used * slab_pad + s_off[s], src, sh_slab, &s_bar[s]);
       }
     }
   }
   trace_stamp(tr, 33);
+  trace_cta(p.trace, 0);
   pdl_wait();  // the activations come from the gate/up kernel
   trace_stamp(tr, 34);
-  // activations of this token: routed slots then the shared expert; loads are issued four deep
-  // before the first store so that their L2 latencies overlap
+  trace_extreme(p.trace, 44, false);
+  // activations of this token (routed slots, then the shared expert) -> fixed point.  One warp
+  // per 128-element chunk: X = round(a * 32639 / max|a|), X = 256 hi + lo with signed 8-bit limbs.
   {
-    const float4* a_src = reinterpret_cast<const float4*>(p.act + (size_t)r * p.n_used * p.nff);
-    const float4* sh_src = reinterpret_cast<const float4*>(p.act + (size_t)p.rows * p.n_used * p.nff + (size_t)r * p.sh_ff);
-    const int n4 = p.n_used * p.nff / 4, tot4 = n4 + (has_sh ? p.sh_ff / 4 : 0);
-    float4* d4 = reinterpret_cast<float4*>(s_act);
-    for (int base = tid; base < tot4; base += 4 * nthreads) {
-      float4 v[4];
+    const float* a_src = p.act + (size_t)r * p.n_used * p.nff;
+    const float* sh_src = p.act + (size_t)p.rows * p.n_used * p.nff + (size_t)r * p.sh_ff;
+    const int n_routed_chunk = p.n_used * p.nff / 128;
+    for (int c0 = warp; c0 < n_chunk; c0 += 2 * nwarps) {
+      // two chunks per pass so that their loads overlap
+      const int c1 = c0 + nwarps;
+      const float4 v0 = __ldcg(reinterpret_cast<const float4*>(c0 < n_routed_chunk ? a_src + (size_t)c0 * 128 : sh_src + (size_t)(c0 - n_routed_chunk) * 128) + lane);
+      float4 v1 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c1 < n_chunk)
+        v1 = __ldcg(reinterpret_cast<const float4*>(c1 < n_routed_chunk ? a_src + (size_t)c1 * 128 : sh_src + (size_t)(c1 - n_routed_chunk) * 128) + lane);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = base + u * nthreads;
-        if (i < tot4) v[u] = __ldcg(i < n4 ? a_src + i : sh_src + (i - n4));
-      }
+      for (int k = 0; k < 2; ++k) {
+        const int c = k ? c1 : c0;
+        if (c >= n_chunk) break;
+        const float4 v = k ? v1 : v0;
+        const float m = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        const float inv = m > 0.f ? 32639.f / m : 0.f;
+        const int X[4] = {__float2int_rn(v.x * inv), __float2int_rn(v.y * inv), __float2int_rn(v.z * inv), __float2int_rn(v.w * inv)};
+        uint32_t lo = 0, hi = 0;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i = base + u * nthreads;
-        if (i < tot4) d4[i] = v[u];
+        for (int t = 0; t < 4; ++t) {
+          const int hh = (X[t] + 128) >> 8, ll = X[t] - (hh << 8);
+          lo |= (uint32_t)(ll & 0xFF) << (8 * t);
+          hi |= (uint32_t)(hh & 0xFF) << (8 * t);
+        }
+        s_xlo[c * DN_XPITCH + lane] = lo;
+        s_xhi[c * DN_XPITCH + lane] = hi;
+        int sx = (X[0] + X[1]) + (X[2] + X[3]);  // sum over the 16 elements held by four lanes
+        sx += __shfl_xor_sync(0xFFFFFFFFu, sx, 1);
+        sx += __shfl_xor_sync(0xFFFFFFFFu, sx, 2);
+        if ((lane & 3) == 0) s_s16[c * 8 + (lane >> 2)] = sx;
+        if (lane == 0) s_xsc[c] = m / 32639.f;
       }
     }
   }
   __syncthreads();
   trace_stamp(tr, 35);
+  trace_cta(p.trace, 1);
 
-  // A warp task = one slot x one group of RPG rows: the slot's activations stay in registers
-  // while the rows of the group stream past them.
+  // A warp task = one slot x one group of up to 8 rows.  Lane = (row q = lane / 4, quarter u4 =
+  // lane % 4): a lane walks whole half-blocks (128 weights: 64 B of low bits, 32 B of high bits,
+  // 8 scales) of its row, four half-blocks of the row side by side across the quarter lanes.
+  // Blocks are 210 bytes, so a row's bytes start 0 or 2 bytes off a word boundary: the lane reads
+  // aligned words and funnel-shifts neighbouring pairs.
   const int RPG = TI < 8 ? TI : 8, RG = TI / RPG;
   const int n_tasks = n_slots * RG;
+  const int q = lane >> 2, u4 = lane & 3;
   bool ok = true;
   for (int task = warp; task < n_tasks && ok; task += nwarps) {
     const int s = task / RG, row0 = (task % RG) * RPG;
-    float acc[8];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+    float acc = 0.f;
     if (s_on[s]) {
       if (!mbar_wait_bounded(&s_bar[s], 0)) { ok = false; break; }
+      trace_stamp(tr, 37);
+      trace_cta(p.trace, 2);
+      trace_extreme(p.trace, 45, true);
       const bool shared_slot = s >= p.n_used;
       const int row_bytes_s = shared_slot ? sh_drb : drb;
-      const int units = (shared_slot ? sh_nb : nb) * 16;
-      const unsigned char* wt = s_wt + (shared_slot ? (size_t)p.n_used * slab_pad : (size_t)s * slab_pad);
-      const float* a = s_act + (shared_slot ? (size_t)p.n_used * p.nff : (size_t)s * p.nff);
-      for (int u = lane; u < units; u += 32) {
-        const int b = u >> 4, h = (u >> 3) & 1, lw = u & 7;
-        // The unit's 16 activations in 16-bit fixed point with the unit's own scale (X = 256 hi + lo,
-        // signed 8-bit limbs, four elements per word like the code words): products with the 6-bit
-        // codes are exact integer dot products, and the unpack stays off the half-rate logic pipe.
-        const float* ab = a + b * 256 + h * 128 + lw * 4;
-        float4 av[4];
-        float amax = 0.f;
+      const int n_hb = (shared_slot ? sh_nb : nb) * 2;  // half-blocks per row
+      const unsigned char* wt = s_wt + (shared_slot ? (size_t)p.n_used * slab_pad : (size_t)s * slab_pad) + s_off[s];
+      const int chunk0 = shared_slot ? p.n_used * p.nff / 128 : s * (p.nff / 128);
+      if (q < RPG) {
+        for (int hb = u4; hb < n_hb; hb += 4) {
+          const int b = hb >> 1, h = hb & 1, chunk = chunk0 + hb;
+          const uint32_t ro = (uint32_t)(row0 + q) * row_bytes_s + (uint32_t)b * Q6K_BLOCK_BYTES;
+          const uint32_t sh = (ro & 3u) * 8;                 // 0 or 16
+          const uint32_t* wq = reinterpret_cast<const uint32_t*>(wt + (ro & ~3u));  // aligned view of the block
+          // aligned word j of the view covers block bytes 4j - (ro & 3) ..; block byte o starts in word o / 4
+          auto word = [&](int o4) { return __funnelshift_r(wq[o4], wq[o4 + 1], sh); };  // bytes 4*o4 .. 4*o4+3 of the block
+          const float d = f16_bits_to_f32(*reinterpret_cast<const unsigned short*>(wt + ro + 208));
+          const uint32_t S0 = word(48 + 2 * h), S1 = word(49 + 2 * h);  // the half's eight int8 scales
+          const uint4* xl = reinterpret_cast<const uint4*>(s_xlo + chunk * DN_XPITCH);
+          const uint4* xh = reinterpret_cast<const uint4*>(s_xhi + chunk * DN_XPITCH);
+          const int* s16 = s_s16 + chunk * 8;
+          float part = 0.f;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          av[q] = *reinterpret_cast<const float4*>(ab + 32 * q);
-          amax = fmaxf(fmaxf(fabsf(av[q].x), fabsf(av[q].y)), fmaxf(amax, fmaxf(fabsf(av[q].z), fabsf(av[q].w))));
-        }
-        const float a_inv = amax > 0.f ? 32639.f / amax : 0.f, a_scale = amax / 32639.f;
-        int xl[4], xh[4], s32[4];
+          for (int hf = 0; hf < 2; ++hf) {  // l = 16 hf .. 16 hf + 15
+            uint32_t c[4][4];               // codes [quadrant][word of four l values]
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int X[4] = {__float2int_rn(av[q].x * a_inv), __float2int_rn(av[q].y * a_inv), __float2int_rn(av[q].z * a_inv),
-                            __float2int_rn(av[q].w * a_inv)};
-          uint32_t lo = 0, hi = 0;
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const int hh = (X[t] + 128) >> 8, ll = X[t] - (hh << 8);
-            lo |= (uint32_t)(ll & 0xFF) << (8 * t);
-            hi |= (uint32_t)(hh & 0xFF) << (8 * t);
-          }
-          xl[q] = (int)lo;
-          xh[q] = (int)hi;
-          s32[q] = 32 * ((X[0] + X[1]) + (X[2] + X[3]));
-        }
-        const uint32_t boff = (uint32_t)b * Q6K_BLOCK_BYTES;
-        const uint32_t sel = (lw >> 2) ? 0x7531u : 0x6420u;
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          if (q < RPG) {
-            // offsets are taken from the 16-byte aligned slab base: rows of an odd block count
-            // start 2 bytes off a word boundary too
-            const uint32_t ro = (uint32_t)(row0 + q) * row_bytes_s + boff;
-            const uint32_t A = lds_u32_unaligned(wt, ro + 64 * h + 4 * lw);
-            const uint32_t B = lds_u32_unaligned(wt, ro + 64 * h + 32 + 4 * lw);
-            const uint32_t H = lds_u32_unaligned(wt, ro + 128 + 32 * h + 4 * lw);
-            const uint32_t S0 = lds_u32_unaligned(wt, ro + 192 + 8 * h);
-            const uint32_t S1 = lds_u32_unaligned(wt, ro + 196 + 8 * h);
-            const float d = f16_bits_to_f32(*reinterpret_cast<const unsigned short*>(wt + ro + 208));
-            // 6-bit codes of the four quadrants, one per byte
-            const uint32_t cs[4] = {(A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u), (B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u),
-                                    ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u), ((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u)};
-            // scales of the four quadrants: bytes (lw>>2) + 2q of the eight scale bytes of this half
-            const uint32_t sc4 = __byte_perm(S0, S1, sel);
-            long long part = 0;
+            for (int i4 = 0; i4 < 4; ++i4) {
+              const int i = 4 * hf + i4;
+              const uint32_t A = word(16 * h + i), B = word(16 * h + 8 + i), H = word(32 + 8 * h + i);
+              c[0][i4] = (A & 0x0F0F0F0Fu) | ((H << 4) & 0x30303030u);
+              c[1][i4] = (B & 0x0F0F0F0Fu) | ((H << 2) & 0x30303030u);
+              c[2][i4] = ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u);
+              c[3][i4] = ((B >> 4) & 0x0F0F0F0Fu) | ((H >> 2) & 0x30303030u);
+            }
 #pragma unroll
             for (int qd = 0; qd < 4; ++qd) {
-              // sum (q - 32) X = 256 * dot(codes, hi) + dot(codes, lo) - 32 * sum X   (|.| < 2^24)
-              const int t = __dp4a((int)cs[qd], xh[qd], 0) * 256 + __dp4a((int)cs[qd], xl[qd], 0) - s32[qd];
-              part += (long long)(int)(signed char)((sc4 >> (8 * qd)) & 0xFFu) * t;
+              // the quadrant's 16 activations of this half: one 16-byte read per limb
+              const uint4 l4 = xl[2 * qd + hf], h4 = xh[2 * qd + hf];
+              int dlo = __dp4a((int)c[qd][0], (int)l4.x, 0), dhi = __dp4a((int)c[qd][0], (int)h4.x, 0);
+              dlo = __dp4a((int)c[qd][1], (int)l4.y, dlo); dhi = __dp4a((int)c[qd][1], (int)h4.y, dhi);
+              dlo = __dp4a((int)c[qd][2], (int)l4.z, dlo); dhi = __dp4a((int)c[qd][2], (int)h4.z, dhi);
+              dlo = __dp4a((int)c[qd][3], (int)l4.w, dlo); dhi = __dp4a((int)c[qd][3], (int)h4.w, dhi);
+              // scale group 2 qd + hf of the half: sum (code - 32) X = 256 dhi + dlo - 32 sum X
+              const int g = 2 * qd + hf;
+              const int t = dhi * 256 + dlo - 32 * s16[g];
+              const uint32_t sw = g < 4 ? S0 : S1;
+              const float sc = (float)(int)(signed char)((sw >> (8 * (g & 3))) & 0xFFu);
+              part = fmaf(sc, (float)t, part);
             }
-            acc[q] = fmaf(d * a_scale, (float)part, acc[q]);
           }
+          acc = fmaf(d * s_xsc[chunk], part, acc);
         }
       }
     }
-    // eight row sums across 32 lanes with nine shuffles: halve the value set at every step
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float send = (lane & 16) ? acc[i] : acc[i + 4];
-      const float keep = (lane & 16) ? acc[i + 4] : acc[i];
-      acc[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, 16);
-    }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const float send = (lane & 8) ? acc[i] : acc[i + 2];
-      const float keep = (lane & 8) ? acc[i + 2] : acc[i];
-      acc[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, 8);
-    }
-    {
-      const float send = (lane & 4) ? acc[0] : acc[1];
-      const float keep = (lane & 4) ? acc[1] : acc[0];
-      acc[0] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, 4);
-    }
-    acc[0] += __shfl_xor_sync(0xFFFFFFFFu, acc[0], 2);
-    acc[0] += __shfl_xor_sync(0xFFFFFFFFu, acc[0], 1);
-    const int q_mine = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-    if ((lane & 3) == 0 && q_mine < RPG) s_part[s * TI + row0 + q_mine] = s_w[s] * acc[0];
+    // the four quarter lanes of a row
+    acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+    acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 2);
+    if (u4 == 0 && q < RPG) s_part[s * TI + row0 + q] = s_w[s] * acc;
   }
   if (!ok) {
     if (lane == 0) atomicExch(&p.status->timeout, 2);
@@ -395,6 +399,7 @@ __global__ void __launch_bounds__(DN_MAX_WARPS * 32, 1) k_decode_down(DecodePara
   }
   __syncthreads();
   trace_stamp(tr, 36);
+  trace_extreme(p.trace, 46, true);
   // weighted sum over slots in rank order, the shared expert last (the CPU's order)
   if (tid < TI) {
     float o = 0.f;
@@ -419,10 +424,10 @@ int pick_chunks(int ne, int nff, int sh_ff) {
 }
 
 size_t down_smem(int TI, int nff, int sh_ff, int n_used) {
-  const size_t slab = align_up((size_t)TI * (nff / 256 * Q6K_BLOCK_BYTES) + 8, 16);
-  const size_t sh_slab = sh_ff ? align_up((size_t)TI * (sh_ff / 256 * Q6K_BLOCK_BYTES) + 8, 16) : 0;
-  return (size_t)n_used * slab + sh_slab + ((size_t)n_used * nff + sh_ff) * sizeof(float) +
-         (size_t)(n_used + 1) * TI * sizeof(float);
+  const size_t slab = align_up((size_t)TI * (nff / 256 * Q6K_BLOCK_BYTES) + 8, 128) + 128;
+  const size_t sh_slab = sh_ff ? align_up((size_t)TI * (sh_ff / 256 * Q6K_BLOCK_BYTES) + 8, 128) + 128 : 0;
+  const size_t n_act = (size_t)n_used * nff + sh_ff;
+  return 128 + (size_t)n_used * slab + sh_slab + (n_act / 128) * (2 * DN_XPITCH * 4 + 4 + 32) + (size_t)(n_used + 1) * TI * sizeof(float);
 }
 
 // TI rows per CTA: bulk copies need TI * row_bytes to be a multiple of 16 for both banks.
@@ -482,7 +487,12 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, u
   if (!n_chunks || !TI) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "small-m path: tile does not fit shared memory");
   const int TR = GU_WARPS * n_chunks;
   const int jobs = p.rows * p.n_used * (p.nff / TR) + (has_sh ? p.rows * (sh_ff / TR) : 0);
-  const size_t smem_gu = gateup_smem(p.ne, n_chunks);
+  size_t smem_gu = gateup_smem(p.ne, n_chunks);
+  // A grid that fits the device one CTA per SM is spread that way: gate/up CTAs start while the
+  // router's CTAs still hold some SMs and would otherwise pair up on the free ones, halving their
+  // copy bandwidth and leaving no room for the down kernel's CTAs to start beside them.  A request
+  // above half of an SM's shared memory keeps two off one SM; a down CTA still fits beside one.
+  if (jobs <= ctx->sm_count && smem_gu < 114 * 1024) smem_gu = 114 * 1024;
   const int ng = (p.ne / 64 + 31) / 32;
   cudaError_t e = cudaSuccess;
   auto run_gu = [&](auto kern) {
@@ -511,6 +521,10 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, u
   for (int c = DN_MAX_WARPS; c >= 8; --c)
     if (n_tasks % c == 0) { nw = c; break; }
   if (n_tasks < 8) nw = n_tasks < 4 ? 4 : n_tasks;
+  // One CTA per SM when the grid fits the device that way: with a whole number of warps per SM
+  // sub-partition, one of these CTAs shares the register file with a gate/up CTA but not with a
+  // second CTA of its own kind (which would only get going once the first has finished).
+  if (p.rows * (p.ne / TI) <= ctx->sm_count && nw > 16 && nw % 4) nw = std::min((int)DN_MAX_WARPS, (nw + 3) & ~3);
   e = launch_ex(k_decode_down, dim3(p.rows * (p.ne / TI)), dim3(nw * 32), smem_dn, ctx->stream, pdl, p, TI);
   ctx->launches += 1;
   return check_cuda(ctx, e, "k_decode_down launch");
