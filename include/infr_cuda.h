@@ -124,7 +124,9 @@ typedef struct infr_cuda_moe_ffn_desc {
   const infr_cuda_buf* sh_down;     /* [ne, sh_ff] down_dtype                                      */
   const infr_cuda_buf* sh_gate_inp; /* [ne] f32 gate vector, or NULL for the ungated sum           */
   uint32_t sh_ff;
-  uint32_t path;                    /* 0 = choose by rows; 1 = force the small-m (decode) kernels;
+  uint32_t path;                    /* 0 = choose by rows (small-m while an expert sees fewer than
+                                       about three tokens of the call on average);
+                                       1 = force the small-m (decode) kernels;
                                        2 = force the grouped-GEMM (prefill) kernels; 3 = same with
                                        the legacy mma.sync tiles instead of tcgen05               */
   /* optional fusions the reference's graph rewriter applies around the op

@@ -472,20 +472,43 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   std::string why;
   const bool small_ok = decode_ffn_supported(ctx, d->ne, d->n_ff_exp, has_sh ? d->sh_ff : 0, d->n_used, &why);
   uint32_t path = d->path;
-  if (path == 0) path = (d->rows <= 8 && small_ok) ? 1 : 2;
+  // Per (token, expert) pair the small-m kernels are cheaper than a grouped-GEMM tile until an
+  // expert sees several tokens of the call on average; measured cross-over near 120 rows for
+  // 256 experts, top-8.
+  if (path == 0) {
+    const bool few_per_expert = (uint64_t)d->rows * d->n_used * 8 <= (uint64_t)d->n_expert * 24;  // <= 3 tokens per expert
+    path = (small_ok && (d->rows <= 8 || few_per_expert)) ? 1 : 2;
+  }
   if (path == 1) {
     if (!small_ok) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, why);
+    // Up to ROUTE_SMALL_MAX_ROWS rows the router kernel also normalises x and makes its
+    // fixed-point copy; above that the batched router runs and two small kernels do those jobs.
+    const bool few = d->rows <= (uint32_t)ROUTE_SMALL_MAX_ROWS;
     Scratch sz = carve(nullptr, d, true);
-    if ((rc = ensure_scratch(ctx, sz.total))) return rc;
+    const size_t hn_bytes = (!few && d->norm_weight) ? align_up((size_t)d->rows * d->ne * 4, 256) : 0;
+    if ((rc = ensure_scratch(ctx, sz.total + hn_bytes))) return rc;
     Scratch s = carve(ctx->scratch, d, true);
     RouteParams rp = route_params(ctx, d, s, true);
-    rp.xq_lo = s.xq_lo;
-    rp.xq_hi = s.xq_hi;
-    rp.xscale = s.xscale;
-    rp.rms_w = d->norm_weight ? static_cast<const float*>(d->norm_weight->ptr) : nullptr;
-    rp.rms_eps = d->norm_eps;
     const uint32_t stages = d->stages ? d->stages : 7u;
-    if ((stages & 1u) && (rc = launch_route(ctx, rp, true))) return rc;
+    if (few) {
+      rp.xq_lo = s.xq_lo;
+      rp.xq_hi = s.xq_hi;
+      rp.xscale = s.xscale;
+      rp.rms_w = d->norm_weight ? static_cast<const float*>(d->norm_weight->ptr) : nullptr;
+      rp.rms_eps = d->norm_eps;
+      if ((stages & 1u) && (rc = launch_route(ctx, rp, true))) return rc;
+    } else if (stages & 1u) {
+      const float* x_eff = static_cast<const float*>(d->x->ptr);
+      if (d->norm_weight) {
+        float* hn = reinterpret_cast<float*>(static_cast<char*>(ctx->scratch) + sz.total);
+        if ((rc = launch_rmsnorm(ctx, x_eff, static_cast<const float*>(d->norm_weight->ptr), hn, (int)d->rows, (int)d->ne, d->norm_eps))) return rc;
+        x_eff = hn;
+        rp.router_x = hn;
+        rp.x = hn;
+      }
+      if ((rc = launch_route(ctx, rp, false))) return rc;
+      if ((rc = launch_quantize_rows(ctx, x_eff, s.xq_lo, s.xq_hi, s.xscale, (int)d->rows, (int)d->ne))) return rc;
+    }
     DecodeParams dp = {};
     dp.xq_lo = s.xq_lo;
     dp.xq_hi = s.xq_hi;

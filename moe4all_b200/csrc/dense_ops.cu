@@ -150,6 +150,44 @@ __global__ void __launch_bounds__(256) k_rmsnorm(const float* __restrict__ x, co
   for (int i = threadIdx.x; i < dim; i += 256) dr[i] = xr[i] * s * w[i];
 }
 
+// Rows of x in 16-bit fixed point for the small-m expert kernels: X = round(x * 32639 / max|x|)
+// per row, stored as two signed 8-bit limbs (X = 256*hi + lo).  One CTA per row.
+__global__ void __launch_bounds__(256) k_quantize_rows(const float* __restrict__ x, int8_t* __restrict__ lo_out,
+                                                       int8_t* __restrict__ hi_out, float* __restrict__ scale, int dim) {
+  __shared__ float s_max[8];
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * dim);
+  const int n4 = dim / 4;
+  float m = 0.f;
+  for (int i = threadIdx.x; i < n4; i += 256) {
+    const float4 v = xr[i];
+    m = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(m, fmaxf(fabsf(v.z), fabsf(v.w))));
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) m = fmaxf(m, s_max[i]);
+  const float q_inv = m > 0.f ? 32639.f / m : 0.f;
+  if (threadIdx.x == 0) scale[blockIdx.x] = m / 32639.f;
+  uint32_t* lo_row = reinterpret_cast<uint32_t*>(lo_out + (size_t)blockIdx.x * dim);
+  uint32_t* hi_row = reinterpret_cast<uint32_t*>(hi_out + (size_t)blockIdx.x * dim);
+  for (int i = threadIdx.x; i < n4; i += 256) {
+    const float4 v = xr[i];
+    const int X[4] = {__float2int_rn(v.x * q_inv), __float2int_rn(v.y * q_inv), __float2int_rn(v.z * q_inv),
+                      __float2int_rn(v.w * q_inv)};
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int h = (X[t] + 128) >> 8, l = X[t] - (h << 8);
+      lo |= (uint32_t)(l & 0xFF) << (8 * t);
+      hi |= (uint32_t)(h & 0xFF) << (8 * t);
+    }
+    lo_row[i] = lo;
+    hi_row[i] = hi;
+  }
+}
+
 __global__ void k_add(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ dst, size_t n) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[i] = a[i] + b[i];
@@ -190,6 +228,12 @@ int32_t launch_rmsnorm(infr_cuda_ctx* ctx, const float* x, const float* w, float
   k_rmsnorm<<<rows, 256, 0, ctx->stream>>>(x, w, dst, dim, eps);
   ctx->launches += 1;
   return check_cuda(ctx, cudaGetLastError(), "k_rmsnorm launch");
+}
+
+int32_t launch_quantize_rows(infr_cuda_ctx* ctx, const float* x, int8_t* lo, int8_t* hi, float* scale, int rows, int dim) {
+  k_quantize_rows<<<rows, 256, 0, ctx->stream>>>(x, lo, hi, scale, dim);
+  ctx->launches += 1;
+  return check_cuda(ctx, cudaGetLastError(), "k_quantize_rows launch");
 }
 
 int32_t launch_add(infr_cuda_ctx* ctx, const float* a, const float* b, float* dst, size_t n) {

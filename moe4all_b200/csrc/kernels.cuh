@@ -102,6 +102,7 @@ int32_t launch_gated_act(infr_cuda_ctx* ctx, const float* gate, const float* up,
 int32_t launch_shared_add(infr_cuda_ctx* ctx, const float* moe, const float* shexp, const float* gate, float* dst,
                           int rows, int n);
 int32_t launch_rmsnorm(infr_cuda_ctx* ctx, const float* x, const float* w, float* dst, int rows, int dim, float eps);
+int32_t launch_quantize_rows(infr_cuda_ctx* ctx, const float* x, int8_t* lo, int8_t* hi, float* scale, int rows, int dim);
 int32_t launch_add(infr_cuda_ctx* ctx, const float* a, const float* b, float* dst, size_t n);
 
 }  // namespace infr

@@ -58,6 +58,20 @@ def test_config1_layer(backend, rows):
     assert_close(out2, oracle_layer(L, x, 8, shared=False).dst)
 
 
+@pytest.mark.parametrize("rows", [12, 40])
+def test_config1_layer_more_rows(backend, rows):
+    # above eight rows the small-m expert kernels run behind the batched router
+    L = synth.make_layer(1, 2048, 256, 512, sh_ff=512)
+    x = synth.activations(17, rows, 2048)
+    g = GpuLayer(backend, L)
+    out, ids, wts = g.run(x, 8, path=1)
+    ref = oracle_layer(L, x, 8)
+    check_ids(ids, wts, ref, 8)
+    assert_close(out, ref.dst)
+    out_auto, ids_auto, _ = g.run(x, 8)
+    assert np.array_equal(out_auto, out) and np.array_equal(ids_auto, ids)
+
+
 def test_determinism(backend):
     L = synth.make_layer(3, 2048, 64, 512, sh_ff=512)
     x = synth.activations(9, 4, 2048)
