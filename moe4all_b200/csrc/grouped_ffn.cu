@@ -23,6 +23,9 @@
 // act) are written in the same order.
 #include <mma.h>
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "kernels.cuh"
 
 namespace infr {
@@ -130,6 +133,41 @@ __global__ void __launch_bounds__(256) k_gather_rows(const float* __restrict__ x
     const float4 v = __ldg(src + i);
     dst[2 * i] = __floats2half2_rn(v.x, v.z);      // positions 0,1 <- elements 0,2
     dst[2 * i + 1] = __floats2half2_rn(v.y, v.w);  // positions 2,3 <- elements 1,3
+  }
+}
+
+// The same rows as operand tiles for the tcgen05 kernels: [tile][K step of 64][256 rows][128 B],
+// every 128-byte line already in the 128-byte-swizzled order of its shared-memory image (16-byte
+// chunk c of row n at chunk position c ^ (n & 7)), so that a CTA fetches a step's whole token
+// operand with one bulk copy.  One warp per row of a tile.
+__global__ void __launch_bounds__(256) k_gather_tiles(const float* __restrict__ x, const int* __restrict__ pair_of_pos,
+                                                      const int* __restrict__ seg_off, int n_seg_routed, int n_used,
+                                                      const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+                                                      const int* __restrict__ n_tiles, int tn, int ne,
+                                                      unsigned char* __restrict__ xt) {
+  const int tile = blockIdx.y;
+  if (tile >= *n_tiles) return;
+  const int n = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (n >= tile_rows[tile]) return;
+  const int row = tile_row0[tile] + n;
+  const int n_sorted = seg_off[n_seg_routed];
+  int tok;
+  if (row < n_sorted)
+    tok = pair_of_pos ? pair_of_pos[row] / n_used : row;
+  else
+    tok = row - n_sorted;  // shared-expert segment: token order
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)tok * ne);
+  const size_t step_bytes = (size_t)tn * 128;
+  unsigned char* line0 = xt + (size_t)tile * (ne / 64) * step_bytes + (size_t)n * 128;
+  for (int i = lane; i < ne / 4; i += 32) {
+    const float4 v = __ldg(src + i);
+    const __half2 h02 = __floats2half2_rn(v.x, v.z), h13 = __floats2half2_rn(v.y, v.w);  // K order 0,2,1,3
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&h02);
+    o.y = *reinterpret_cast<const uint32_t*>(&h13);
+    const int step = i >> 4, chunk = (i & 15) >> 1;
+    *reinterpret_cast<uint2*>(line0 + (size_t)step * step_bytes + ((chunk ^ (n & 7)) << 4) + (i & 1) * 8) = o;
   }
 }
 
@@ -424,13 +462,15 @@ __global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __re
 __global__ void __launch_bounds__(1024) k_tiles_from_offsets(const int* __restrict__ seg_off, int n_seg, int tn,
                                                              int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                                              int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
-  __shared__ int s_toff[1026];
+  __shared__ int s_toff[1026], s_so[1026];
   const int tid = threadIdx.x;
+  for (int e = tid; e <= n_seg; e += 1024) s_so[e] = seg_off[e];
+  __syncthreads();
   if (tid == 0) {
     int toff = 0;
     for (int e = 0; e < n_seg; ++e) {
       s_toff[e] = toff;
-      toff += (seg_off[e + 1] - seg_off[e] + tn - 1) / tn;
+      toff += (s_so[e + 1] - s_so[e] + tn - 1) / tn;
     }
     *n_tiles = toff;
   }
@@ -454,8 +494,11 @@ size_t grouped_scratch_bytes(int rows_total, int n_pairs, int n_seg, int ne, int
   b += align_up((size_t)(n_seg + 2) * 4, 256) * 3;                 // counts, seg_off, fill
   b += align_up((size_t)(rows_total / TN + n_seg + 2) * 4, 256) * 3 + 256;  // tile table + n_tiles
   b += align_up((size_t)(n_pairs + 1) * 4, 256) * 2;               // pos_of_pair, pair_of_pos
-  b += align_up(rows_pad * ne * 2, 256);                           // xg
-  b += align_up(rows_pad * nff * 2, 256);                          // act
+  // token arrays: rows grouped by expert (legacy tiles) or padded to whole 256-row tiles (tcgen05)
+  const size_t tile_rows_pad = ((size_t)rows_total / 256 + n_seg + 1) * 256;
+  const size_t tok_rows = tile_rows_pad > rows_pad ? tile_rows_pad : rows_pad;
+  b += align_up(tok_rows * ne * 2, 256);                           // xg
+  b += align_up(tok_rows * nff * 2, 256);                          // act
   b += align_up(rows_pad * ne * 4, 256);                           // y
   return b;
 }
@@ -485,8 +528,10 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   int* n_tiles = reinterpret_cast<int*>(take(256));
   int* pos_of_pair = reinterpret_cast<int*>(take((size_t)(c.n_pairs + 1) * 4));
   int* pair_of_pos = reinterpret_cast<int*>(take((size_t)(c.n_pairs + 1) * 4));
-  __half* xg = reinterpret_cast<__half*>(take(((size_t)rows_total + 256) * c.ne * 2));
-  __half* act = reinterpret_cast<__half*>(take(((size_t)rows_total + 256) * c.nff * 2));
+  const size_t tile_rows_pad = ((size_t)rows_total / 256 + n_seg + 1) * 256;
+  const size_t tok_rows = std::max(tile_rows_pad, (size_t)rows_total + 256);
+  __half* xg = reinterpret_cast<__half*>(take(tok_rows * c.ne * 2));
+  __half* act = reinterpret_cast<__half*>(take(tok_rows * c.nff * 2));
   float* y = c.y_out ? c.y_out : reinterpret_cast<float*>(take(((size_t)rows_total + 256) * c.ne * 4));
   cudaStream_t st = ctx->stream;
 
@@ -499,7 +544,11 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
     k_pair_scatter<<<(c.n_pairs + 255) / 256, 256, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, seg_off, fill,
                                                              pos_of_pair, pair_of_pos);
     ctx->launches += 3;
-    k_gather_rows<<<(rows_total + 7) / 8, 256, 0, st>>>(c.x, pair_of_pos, seg_off, n_seg_routed, c.n_used, rows_total, c.ne, xg);
+    if (use_umma)
+      k_gather_tiles<<<dim3(tn / 8, max_tiles), 256, 0, st>>>(c.x, pair_of_pos, seg_off, n_seg_routed, c.n_used, tile_row0, tile_rows,
+                                                             n_tiles, tn, c.ne, reinterpret_cast<unsigned char*>(xg));
+    else
+      k_gather_rows<<<(rows_total + 7) / 8, 256, 0, st>>>(c.x, pair_of_pos, seg_off, n_seg_routed, c.n_used, rows_total, c.ne, xg);
     ctx->launches += 1;
   } else {
     // rows already grouped: offsets come from the caller (n_expert segments, no shared segment)
@@ -509,7 +558,11 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
     cudaError_t e = cudaMemcpyAsync(seg_off, c.seg_off_in + c.n_expert, 4, cudaMemcpyDeviceToDevice, st);
     if (e == cudaSuccess) e = cudaMemcpyAsync(seg_off + 1, c.seg_off_in + c.n_expert, 4, cudaMemcpyDeviceToDevice, st);
     if (e != cudaSuccess) return check_cuda(ctx, e, "grouped: offsets copy");
-    k_gather_rows<<<(rows_total + 7) / 8, 256, 0, st>>>(c.x, nullptr, seg_off, 0, 1, rows_total, c.ne, xg);
+    if (use_umma)
+      k_gather_tiles<<<dim3(tn / 8, max_tiles), 256, 0, st>>>(c.x, nullptr, seg_off, 0, 1, tile_row0, tile_rows, n_tiles, tn, c.ne,
+                                                             reinterpret_cast<unsigned char*>(xg));
+    else
+      k_gather_rows<<<(rows_total + 7) / 8, 256, 0, st>>>(c.x, nullptr, seg_off, 0, 1, rows_total, c.ne, xg);
     ctx->launches += 2;
   }
 
@@ -535,6 +588,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   p.n_expert = c.n_expert;
   p.status = ctx->status;
   p.trace = ctx->trace;
+  p.trace_tile = getenv("INFR_TRACE_TILE") ? atoi(getenv("INFR_TRACE_TILE")) : 0;
   if (use_umma) {
     const int32_t rc = launch_umma_grouped(ctx, p, max_tiles);
     if (rc) return rc;

@@ -50,14 +50,17 @@ struct DecodeParams {
 // Device-side view of one grouped-GEMM launch (see grouped_ffn.cu).
 struct GroupedParams {
   const int *tile_expert, *tile_row0, *tile_rows, *n_tiles;  // tile table built on the device
-  const __half* xg;  // [rows, ne]  token rows grouped by expert, f16, K order 0,2,1,3 per four
-  __half* act;       // [rows, nff] same grouping and K order
+  // token rows grouped by expert, f16, K order 0,2,1,3 per four.  Legacy tiles: [rows, ne] and
+  // [rows, nff] row-major.  tcgen05 tiles: [tile][K step][256 rows][64] with swizzled 128-byte lines.
+  const __half* xg;
+  __half* act;
   float* y;          // [rows, ne]
   const uint8_t *gate, *up, *down;
   const uint8_t *sh_gate, *sh_up, *sh_down;  // segment index n_expert = the shared expert
   size_t gate_stride, up_stride, down_stride;
   DeviceStatus* status;
   unsigned long long* trace;  // optional phase stamps
+  int trace_tile;             // tile whose first CTA writes them
   int ne, nff, n_expert;
 };
 

@@ -95,5 +95,18 @@ __device__ __forceinline__ void ld_32x32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Two such loads in flight, one wait: 32 columns at `ta` into a, 32 columns at `tb` into b.  One
+// asm statement, so that no use of the outputs can be scheduled ahead of the wait.
+__device__ __forceinline__ void ld_32x32_pair(uint32_t ta, uint32_t tb, float (&a)[32], float (&b)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%64];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%65];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=f"(a[0]), "=f"(a[1]), "=f"(a[2]), "=f"(a[3]), "=f"(a[4]), "=f"(a[5]), "=f"(a[6]), "=f"(a[7]), "=f"(a[8]), "=f"(a[9]), "=f"(a[10]), "=f"(a[11]), "=f"(a[12]), "=f"(a[13]), "=f"(a[14]), "=f"(a[15]), "=f"(a[16]), "=f"(a[17]), "=f"(a[18]), "=f"(a[19]), "=f"(a[20]), "=f"(a[21]), "=f"(a[22]), "=f"(a[23]), "=f"(a[24]), "=f"(a[25]), "=f"(a[26]), "=f"(a[27]), "=f"(a[28]), "=f"(a[29]), "=f"(a[30]), "=f"(a[31]),
+        "=f"(b[0]), "=f"(b[1]), "=f"(b[2]), "=f"(b[3]), "=f"(b[4]), "=f"(b[5]), "=f"(b[6]), "=f"(b[7]), "=f"(b[8]), "=f"(b[9]), "=f"(b[10]), "=f"(b[11]), "=f"(b[12]), "=f"(b[13]), "=f"(b[14]), "=f"(b[15]), "=f"(b[16]), "=f"(b[17]), "=f"(b[18]), "=f"(b[19]), "=f"(b[20]), "=f"(b[21]), "=f"(b[22]), "=f"(b[23]), "=f"(b[24]), "=f"(b[25]), "=f"(b[26]), "=f"(b[27]), "=f"(b[28]), "=f"(b[29]), "=f"(b[30]), "=f"(b[31])
+      : "r"(ta), "r"(tb)
+      : "memory");
+}
+
 }  // namespace umma
 }  // namespace infr
