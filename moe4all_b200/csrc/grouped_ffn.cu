@@ -57,29 +57,80 @@ __global__ void k_pair_count(const int32_t* __restrict__ ids, int n_pairs, int n
   atomicAdd(&counts[e], 1);
 }
 
+// Exclusive prefix sums of (a, b) over the 1024 threads of the CTA; totals returned through
+// `ta`, `tb`.  s_ws: 2 x 32 ints of scratch.
+__device__ __forceinline__ void block_scan2(int& a, int& b, int& ta, int& tb, int* s_ws) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int ia = a, ib = b;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int ua = __shfl_up_sync(0xFFFFFFFFu, ia, o), ub = __shfl_up_sync(0xFFFFFFFFu, ib, o);
+    if (lane >= o) {
+      ia += ua;
+      ib += ub;
+    }
+  }
+  if (lane == 31) {
+    s_ws[warp] = ia;
+    s_ws[32 + warp] = ib;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int wa = s_ws[lane], wb = s_ws[32 + lane];
+    const int oa = wa, ob = wb;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int ua = __shfl_up_sync(0xFFFFFFFFu, wa, o), ub = __shfl_up_sync(0xFFFFFFFFu, wb, o);
+      if (lane >= o) {
+        wa += ua;
+        wb += ub;
+      }
+    }
+    s_ws[lane] = wa - oa;  // exclusive warp offsets
+    s_ws[32 + lane] = wb - ob;
+    if (lane == 31) {
+      s_ws[64] = wa;
+      s_ws[65] = wb;
+    }
+  }
+  __syncthreads();
+  a = ia - a + s_ws[warp];
+  b = ib - b + s_ws[32 + warp];
+  ta = s_ws[64];
+  tb = s_ws[65];
+}
+
 // One CTA: exclusive scan of the per-expert counts, the tile table (one entry per 64 rows of a
 // segment, the shared expert's rows appended as segment n_expert), and the fill cursors reset.
 __global__ void __launch_bounds__(1024) k_segment_scan(const int* __restrict__ counts, int n_expert, int shared_rows, int tn,
                                                        int* __restrict__ seg_off, int* __restrict__ fill,
                                                        int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                                        int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
-  __shared__ int s_cnt[1025], s_off[1026], s_toff[1026];
+  __shared__ int s_cnt[1025], s_off[1026], s_toff[1026], s_ws[66];
   const int tid = threadIdx.x;
   const int n_seg = n_expert + (shared_rows > 0 ? 1 : 0);
-  for (int e = tid; e < n_seg; e += 1024) s_cnt[e] = e < n_expert ? counts[e] : shared_rows;
-  __syncthreads();
+  // thread e scans segment e; segment 1024 (only with 1024 experts and a shared segment) is
+  // appended by thread 0 afterwards
+  const int cnt = tid < n_seg ? (tid < n_expert ? counts[tid] : shared_rows) : 0;
+  int off = cnt, toff = (cnt + tn - 1) / tn, total = 0, total_t = 0;
+  block_scan2(off, toff, total, total_t, s_ws);
+  if (tid < n_seg) {
+    s_cnt[tid] = cnt;
+    s_off[tid] = off;
+    s_toff[tid] = toff;
+  }
   if (tid == 0) {
-    int off = 0, toff = 0;
-    for (int e = 0; e < n_seg; ++e) {
-      s_off[e] = off;
-      s_toff[e] = toff;
-      off += s_cnt[e];
-      toff += (s_cnt[e] + tn - 1) / tn;
+    if (n_seg > 1024) {
+      s_cnt[1024] = shared_rows;
+      s_off[1024] = total;
+      s_toff[1024] = total_t;
+      total += shared_rows;
+      total_t += (shared_rows + tn - 1) / tn;
     }
-    s_off[n_seg] = off;
-    s_toff[n_seg] = toff;
-    *n_tiles = toff;
-    seg_off[n_expert + 1] = off;  // total grouped rows, with or without a shared segment
+    s_off[n_seg] = total;
+    s_toff[n_seg] = total_t;
+    *n_tiles = total_t;
+    seg_off[n_expert + 1] = total;  // total grouped rows, with or without a shared segment
   }
   __syncthreads();
   for (int e = tid; e <= n_seg; e += 1024) seg_off[e] = s_off[e];

@@ -4,12 +4,15 @@
 // crates/infr-cpu/src/lib.rs:4051-4266; Vulkan native_gemm_mmq_q4k/q6k.comp): per expert segment
 //   act = silu(Wg x) * (Wu x)      (k_umma_gateup, Q4_K weights)
 //   y   = Wd act                   (k_umma_down,   Q6_K weights)
-// with the weights as the M operand (128 output features per CTA) and up to 256 token rows as the
-// N operand, so every weight block is unpacked once per 256 tokens.
+// with the tokens as the M operand (one or two halves of 128 rows per tile of up to 256 tokens)
+// and 256 weight rows as the N operand (gate/up: 128 gate rows and their 128 up rows; down: 256
+// output features), so every weight block is unpacked once per 256 tokens, a tile with few tokens
+// costs half the MMA instructions of a full one, and in the accumulators a thread's row is a
+// token: its results are contiguous in the output.
 //
-// Warp roles (10 warps): warps 0-7 are producers - each thread owns one weight row of the tile and
-// unpacks its 64 weights of the K step to f16 straight into the 128-byte-swizzled operand tile;
-// warp 8 issues the MMAs (one thread) and releases pipeline stages with tcgen05.commit; warp 9
+// Warp roles (18 warps): warps 0-15 are producers - two (gate/up) or eight (down) threads share a
+// weight row of the tile and unpack its 64 weights of the K step to f16 straight into the 128-byte-swizzled operand tile;
+// warp 16 issues the MMAs (one thread) and releases pipeline stages with tcgen05.commit; warp 17
 // fetches the token operand: the gather kernel (and the gate/up epilogue) store token rows per
 // (tile, K step) as 128-byte lines already in swizzled order, so one bulk copy brings a step's
 // whole operand and runs several steps ahead of the MMAs.  After the K loop the producers drain
@@ -28,17 +31,12 @@ namespace {
 constexpr int UM = 128;           // weight rows per role and CTA
 constexpr int UN = 256;           // max token rows per CTA
 constexpr int UK = 64;            // K elements per stage
-constexpr int U_PRODUCERS = 256;  // producer threads
+constexpr int U_PRODUCERS = 512;  // producer threads: two per weight row of a gate/up tile pair, four per row of a down tile
 constexpr int U_THREADS = U_PRODUCERS + 64;  // + MMA warp + token-copy warp
 constexpr float W_PRESCALE = 256.0f;
 constexpr float W_POSTSCALE = 1.0f / 256.0f;
 constexpr uint32_t A_TILE_BYTES = UM * 128;  // 16 KB
 constexpr uint32_t B_TILE_BYTES = UN * 128;  // 32 KB
-
-__device__ __forceinline__ int kperm(int k) {
-  const int r = k & 3;
-  return (k & ~3) | (r == 1 ? 2 : (r == 2 ? 1 : r));
-}
 
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
@@ -111,15 +109,16 @@ __device__ __forceinline__ bool run_pipeline(PipeBars& bars, unsigned char* a_st
     auto body = [&](int step, auto jc) {
       if (!ok) return;
       const int s = step % SA, use = step / SA;
-      if ((step & 3) == 0 && step < 32) trace_stamp(tr, 64 + step);
+      if (step >= 8 && step < 16) trace_stamp(tr, 64 + 4 * (step - 8));
       // a stage is free again when the MMAs that last read it have completed
       if (!mbar_wait_bounded(&bars.empty_a[s], (use & 1) ^ 1)) { ok = false; return; }
-      if ((step & 3) == 0 && step < 32) trace_stamp(tr, 65 + step);
+      if (step >= 8 && step < 16) trace_stamp(tr, 65 + 4 * (step - 8));
       if (!unpack(a_stages + (size_t)s * a_stage_bytes, step, jc)) { ok = false; return; }
-      if ((step & 3) == 0 && step < 32) trace_stamp(tr, 66 + step);
+      if (step >= 8 && step < 16) trace_stamp(tr, 66 + 4 * (step - 8));
       umma::fence_proxy_async();
       __syncwarp();
       if ((tid & 31) == 0) mbar_arrive(&bars.full_a[s]);  // one arrival per producer warp
+      if (step >= 8 && step < 16) trace_stamp(tr, 67 + 4 * (step - 8));
     };
     for (int base = 0; base < n_steps && ok; base += 4) {
       body(base, std::integral_constant<int, 0>{});
@@ -135,11 +134,11 @@ __device__ __forceinline__ bool run_pipeline(PipeBars& bars, unsigned char* a_st
         break;
       }
       umma::fence_after_sync();
-      if (tr != nullptr && (step & 3) == 0 && step < 32) { tr[2 * (100 + step / 2)] = 0; tr[2 * (100 + step / 2) + 1] = (unsigned long long)clock64(); }
+      if (tr != nullptr && step >= 8 && step < 16) { tr[2 * (100 + 2 * (step - 8))] = 0; tr[2 * (100 + 2 * (step - 8)) + 1] = (unsigned long long)clock64(); }
       issue(a_stages + (size_t)sa * a_stage_bytes, b_stages + (size_t)sb * B_TILE_BYTES, step);
       umma::commit(&bars.empty_a[sa]);
       umma::commit(&bars.empty_b[sb]);
-      if (tr != nullptr && (step & 3) == 0 && step < 32) { tr[2 * (101 + step / 2)] = 0; tr[2 * (101 + step / 2) + 1] = (unsigned long long)clock64(); }
+      if (tr != nullptr && step >= 8 && step < 16) { tr[2 * (101 + 2 * (step - 8))] = 0; tr[2 * (101 + 2 * (step - 8)) + 1] = (unsigned long long)clock64(); }
     }
     umma::commit(&bars.done);
   } else if (tid == U_PRODUCERS + 32) {
@@ -151,6 +150,27 @@ __device__ __forceinline__ bool run_pipeline(PipeBars& bars, unsigned char* a_st
     }
   }
   return ok;
+}
+
+// Epilogue helper.  Every lane holds NP consecutive 16-byte pieces of its own row (a token); rows
+// are far apart in global memory, so the warp first parks them in its private shared-memory
+// patch (row pitch NP*16 + 16 bytes: conflict-free both ways) and then writes them out with
+// 32 / NP whole rows per store instruction.  `dst(row, piece)` gives the global address of a piece.
+template <int NP, typename Dst>
+__device__ __forceinline__ void warp_store_rows(unsigned char* patch, const uint4 (&v)[NP], int lane, int rows_ok, Dst dst) {
+  constexpr int PITCH = NP * 16 + 16;
+#pragma unroll
+  for (int c = 0; c < NP; ++c) *reinterpret_cast<uint4*>(patch + lane * PITCH + c * 16) = v[c];
+  __syncwarp();
+  constexpr int RPI = 32 / NP;  // rows per instruction
+  const int piece = lane % NP, sub = lane / NP;
+#pragma unroll
+  for (int it = 0; it < NP; ++it) {
+    const int row = it * RPI + sub;
+    const uint4 x = *reinterpret_cast<const uint4*>(patch + row * PITCH + piece * 16);
+    if (row < rows_ok) *reinterpret_cast<uint4*>(dst(row, piece)) = x;
+  }
+  __syncwarp();
 }
 
 // ---- gate/up + SwiGLU ---------------------------------------------------------------------------
@@ -181,15 +201,18 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
     mbar_init(&s_raw_full, 1);
     init_bars<GU_SA, GU_SB>(bars);
   }
-  if (warp == 8) umma::tmem_alloc(&s_tmem, 512);
+  if (warp == U_PRODUCERS / 32) umma::tmem_alloc(&s_tmem, 512);
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t tmem = s_tmem;
 
-  // producer identity: role 0 = gate rows, role 1 = up rows; every producer also owns a token row
-  const int role = (tid >> 7) & 1, wrow = tid & 127;
-  const uint32_t idesc = umma::idesc_f16_f32(UM, n_eff);
+  // producer identity: role 0 = gate rows, role 1 = up rows; two threads share a weight row, thread
+  // `hh` taking code words 4 hh .. 4 hh + 3 of every 32-byte run (K positions 16 hh .. 16 hh + 15
+  // from the low nibbles, 32 + 16 hh .. from the high ones)
+  const int role = (tid >> 7) & 1, wrow = tid & 127, hh = (tid >> 8) & 1;
+  const uint32_t idesc = umma::idesc_f16_f32(128, 2 * UM);  // 128 tokens x (128 gate + 128 up) rows
+  const int n_m = (rows_valid + 127) >> 7;                   // token halves in use
 
   // Raw bytes of the tile's rows, one 256-weight block (144 B) per row at a time, come in through
   // the copy engine as two tiled copies (128 rows x 144 B out of rows 1152 B apart, gate and up)
@@ -197,19 +220,19 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
   // vector loads every warp request would touch 32 different lines and the load/store pipe, which
   // the unpacked tiles also go through, would be the bottleneck.
   unsigned char* raw = b_stages + GU_SB * B_TILE_BYTES;
-  const unsigned char* my_raw = raw + (size_t)tid * Q4K_BLOCK_BYTES;
+  const unsigned char* my_raw = raw + (size_t)(tid & 255) * Q4K_BLOCK_BYTES;
   const CUtensorMap* tmg = shared_seg ? &tm_sh_gate : &tm_gate;
   const CUtensorMap* tmu = shared_seg ? &tm_sh_up : &tm_up;
   const int bank_row0 = (shared_seg ? 0 : e * p.nff) + f0;
   auto request_block = [&](int blk) {
     if (tid == 0) {
-      mbar_arrive_expect_tx(&s_raw_full, U_PRODUCERS * (uint32_t)Q4K_BLOCK_BYTES);
+      mbar_arrive_expect_tx(&s_raw_full, 2 * UM * (uint32_t)Q4K_BLOCK_BYTES);
       tma_load_2d(raw, tmg, blk * (int)Q4K_BLOCK_BYTES, bank_row0, &s_raw_full);
       tma_load_2d(raw + UM * Q4K_BLOCK_BYTES, tmu, blk * (int)Q4K_BLOCK_BYTES, bank_row0, &s_raw_full);
     }
   };
   if (tid < U_PRODUCERS) request_block(0);
-  uint4 cur_h, cur_q[8];
+  uint4 cur_h, cur_q[4];
 
   auto unpack = [&](unsigned char* st, int step, auto jc) -> bool {
     constexpr int j = decltype(jc)::value;
@@ -219,36 +242,42 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
       if (!mbar_wait_bounded(&s_raw_full, blk & 1)) return false;
       cur_h = *reinterpret_cast<const uint4*>(my_raw);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) cur_q[i] = *reinterpret_cast<const uint4*>(my_raw + 16 + 16 * i);
+      for (int i = 0; i < 4; ++i) cur_q[i] = *reinterpret_cast<const uint4*>(my_raw + 16 + 32 * i + 16 * hh);
       // every producer has taken its row: the staging area can be refilled
       asm volatile("bar.sync 1, %0;" ::"n"(U_PRODUCERS) : "memory");
       if (blk + 1 < p.ne / 256) request_block(blk + 1);
     }
-    const uint4 ch = cur_h, c0 = cur_q[2 * j], c1 = cur_q[2 * j + 1];
+    const uint4 ch = cur_h, cq = cur_q[j];
     uint32_t scp, mp;
     q4k_scale_min_pair(ch.y, ch.z, ch.w, j, scp, mp);
     const float d = f16_bits_to_f32(ch.x) * W_PRESCALE, dmin = f16_bits_to_f32(ch.x >> 16) * W_PRESCALE;
     const __half2 s_lo = __float2half2_rn(d * (float)(scp & 0xFFu)), s_hi = __float2half2_rn(d * (float)(scp >> 8));
     const __half2 m_lo = __float2half2_rn(-dmin * (float)(mp & 0xFFu)), m_hi = __float2half2_rn(-dmin * (float)(mp >> 8));
-    const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const uint32_t w[4] = {cq.x, cq.y, cq.z, cq.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {  // chunk c: K positions 8c..8c+7 (low nibbles), 32+8c.. (high nibbles)
+    for (int cc = 0; cc < 2; ++cc) {  // chunk c: K positions 8c..8c+7 (low nibbles), 32+8c.. (high nibbles)
+      const int c = 2 * hh + cc;
       uint4 lo, hi;
-      q4_word_to_h2(w[2 * c], s_lo, m_lo, lo.x, lo.y);
-      q4_word_to_h2(w[2 * c + 1], s_lo, m_lo, lo.z, lo.w);
-      q4_word_to_h2(w[2 * c] >> 4, s_hi, m_hi, hi.x, hi.y);
-      q4_word_to_h2(w[2 * c + 1] >> 4, s_hi, m_hi, hi.z, hi.w);
+      q4_word_to_h2(w[2 * cc], s_lo, m_lo, lo.x, lo.y);
+      q4_word_to_h2(w[2 * cc + 1], s_lo, m_lo, lo.z, lo.w);
+      q4_word_to_h2(w[2 * cc] >> 4, s_hi, m_hi, hi.x, hi.y);
+      q4_word_to_h2(w[2 * cc + 1] >> 4, s_hi, m_hi, hi.z, hi.w);
       *reinterpret_cast<uint4*>(tA + umma::swz128_offset(wrow, c)) = lo;
       *reinterpret_cast<uint4*>(tA + umma::swz128_offset(wrow, 4 + c)) = hi;
     }
     return true;
   };
+  // One thread issues everything, so its instruction count per step is the pipeline's floor for
+  // small tiles: the three descriptors are built once per step, a K slice is +32 bytes = +2 in
+  // the address field.
   auto issue = [&](unsigned char* st, unsigned char* tB, int step) {
+    const uint64_t dw = umma::smem_desc_k_major_swz128(st, 0);  // gate tile and up tile back to back: 256 rows
+    const uint64_t dt = umma::smem_desc_k_major_swz128(tB, 0);
+    for (int m = 0; m < n_m; ++m) {
+      const uint64_t dtm = dt + (uint64_t)m * (128 * 128 / 16);  // token rows 128 m ..
+      umma::mma_f16(tmem + m * 256, dtm, dw, idesc, step > 0);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint64_t bd = umma::smem_desc_k_major_swz128(tB, k);
-      umma::mma_f16(tmem, umma::smem_desc_k_major_swz128(st, k), bd, idesc, step > 0 || k > 0);
-      umma::mma_f16(tmem + 256, umma::smem_desc_k_major_swz128(st + A_TILE_BYTES, k), bd, idesc, step > 0 || k > 0);
+      for (int k = 1; k < 4; ++k) umma::mma_f16_acc(tmem + m * 256, dtm + 2 * k, dw + 2 * k, idesc);
     }
   };
   const int k_steps = p.ne / UK;
@@ -260,36 +289,43 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
                                        trc);
   trace_stamp(trc, 42);
 
-  // epilogue: producers drain the two accumulators.  The CTA's 128 features are two whole 128-byte
-  // lines (K steps f0/64 and f0/64 + 1) of every token row of the down kernel's operand
-  // ([tile][K step][row][128 B], swizzled like its shared-memory image); the values go through
-  // shared memory (the weight stages are idle by now) so that each line is written whole.
+  // epilogue: a thread's accumulator row is a token; its 64 gate and 64 up values per feature half
+  // give 64 activations = one whole 128-byte line of the down kernel's operand
+  // ([tile][K step][row][128 B], swizzled like its shared-memory image).
   if (tid < U_PRODUCERS) {
     if (ok) ok = mbar_wait_bounded(&bars.done, 0);
     umma::fence_after_sync();
-    unsigned char* stg = a_stages;  // [256 rows][256 B]
-    if (ok) {
-      const int lane_grp = warp & 3, col_half = warp >> 2;
-      const int lpos = kperm(lane_grp * 32 + lane);  // position of this thread's feature inside the CTA's 128
-      for (int c0 = col_half * 128; c0 < min(n_eff, col_half * 128 + 128); c0 += 32) {
-        float g[32], u[32];
-        const uint32_t ta = tmem + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)c0;
-        umma::ld_32x32_pair(ta, ta + 256, g, u);
+    const int lq = warp & 3, m = warp >> 3, fh = (warp >> 2) & 1;  // TMEM lane quarter, token half, feature half
+    if (ok && m < n_m) {
+      const int n0 = m * 128 + lq * 32;  // first token row of this warp
+      const uint32_t trow = tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(m * 256 + fh * 64);
+      unsigned char* lines = reinterpret_cast<unsigned char*>(p.act) + tile_step_offset(tile, p.nff / UK, (f0 >> 6) + fh) + (size_t)n0 * 128;
+      unsigned char* patch = a_stages + (size_t)warp * (32 * 80);  // the weight stages are idle by now
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float gv = g[i] * W_POSTSCALE, uv = u[i] * W_POSTSCALE;
-          const float a = __fdividef(gv, 1.0f + __expf(-gv)) * uv;
-          *reinterpret_cast<__half*>(stg + (size_t)(c0 + i) * 256 + lpos * 2) = __float2half_rn(fminf(fmaxf(a, -65504.f), 65504.f));
+      for (int hf = 0; hf < 2; ++hf) {
+        float g[32], u[32];
+        umma::ld_32x32_pair(trow + hf * 32, trow + 128 + hf * 32, g, u);
+        uint4 o[4];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {  // four features -> positions 0,2,1,3
+          float a[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float gv = g[4 * q + t] * W_POSTSCALE, uv = u[4 * q + t] * W_POSTSCALE;
+            a[t] = fminf(fmaxf(__fdividef(gv, 1.0f + __expf(-gv)) * uv, -65504.f), 65504.f);
+          }
+          const uint32_t w0 = h2_as_u32(__floats2half2_rn(a[0], a[2])), w1 = h2_as_u32(__floats2half2_rn(a[1], a[3]));
+          if (q & 1) {
+            o[q >> 1].z = w0;
+            o[q >> 1].w = w1;
+          } else {
+            o[q >> 1].x = w0;
+            o[q >> 1].y = w1;
+          }
         }
-      }
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(U_PRODUCERS) : "memory");
-    if (ok) {
-      unsigned char* act_tile = reinterpret_cast<unsigned char*>(p.act) + tile_step_offset(tile, p.nff / UK, f0 >> 6);
-      for (int idx = tid; idx < rows_valid * 16; idx += U_PRODUCERS) {
-        const int n = idx >> 4, q = idx & 15;
-        const uint4 v = *reinterpret_cast<const uint4*>(stg + (size_t)n * 256 + q * 16);
-        *reinterpret_cast<uint4*>(act_tile + ((size_t)(q >> 3) * UN + n) * 128 + (((q & 7) ^ (n & 7)) << 4)) = v;
+        warp_store_rows<4>(patch, o, lane, rows_valid - n0, [&](int row, int piece) {
+          return lines + (size_t)row * 128 + (((4 * hf + piece) ^ ((n0 + row) & 7)) << 4);
+        });
       }
     }
   }
@@ -297,12 +333,14 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
   if (!ok && lane == 0) atomicExch(&p.status->timeout, 5);
   umma::fence_before_sync();
   __syncthreads();
-  if (warp == 8) umma::tmem_dealloc(tmem, 512);
+  if (warp == U_PRODUCERS / 32) umma::tmem_dealloc(tmem, 512);
 }
 
 // ---- down ---------------------------------------------------------------------------------------------
 
-constexpr int DN_SA = 4, DN_SB = 4;
+constexpr int DN_SA = 3, DN_SB = 3;
+constexpr int DM = 256;                                   // output features per CTA
+constexpr uint32_t DN_W_STAGE_BYTES = DM * 128;           // 32 KB
 
 __device__ __forceinline__ uint32_t ldg_u32_unaligned(const uint8_t* base, size_t off) {
   const size_t a = off & ~(size_t)3;
@@ -319,16 +357,16 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
   if (tile >= *p.n_tiles) return;
   trace_stamp((blockIdx.x == 0 && blockIdx.y == p.trace_tile) ? p.trace : nullptr, 44);
   unsigned char* a_stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char* b_stages = a_stages + DN_SA * A_TILE_BYTES;
+  unsigned char* b_stages = a_stages + DN_SA * DN_W_STAGE_BYTES;
   const int e = p.tile_expert[tile], row0 = p.tile_row0[tile], rows_valid = p.tile_rows[tile];
   const int n_eff = (rows_valid + 15) & ~15;
-  const int i0 = blockIdx.x * UM;
+  const int i0 = blockIdx.x * DM;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int drb = p.nff / 256 * (int)Q6K_BLOCK_BYTES;
   const bool shared_seg = e >= p.n_expert;
 
   if (tid == 0) init_bars<DN_SA, DN_SB>(bars);
-  if (warp == 8) umma::tmem_alloc(&s_tmem, 256);
+  if (warp == U_PRODUCERS / 32) umma::tmem_alloc(&s_tmem, 512);
   umma::fence_before_sync();
   __syncthreads();
   umma::fence_after_sync();
@@ -339,18 +377,20 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
   // rows of the tile take four passes.
   const int g8 = tid >> 3, w = tid & 7;
   const uint8_t* wbase = shared_seg ? p.sh_down : p.down + (size_t)e * p.down_stride;  // 16-byte aligned
-  const uint32_t idesc = umma::idesc_f16_f32(UM, n_eff);
+  const uint32_t idesc = umma::idesc_f16_f32(128, DM);  // 128 tokens x 256 output features
+  const int n_m = (rows_valid + 127) >> 7;
 
   // Raw words of one half-block (128 elements = two K steps: low nibbles first, high nibbles
   // second) per pass: ql words of quadrants 0|2 and 1|3, the qh word, the eight scales, d.
   // The next half-block is fetched while the current one is unpacked.
-  uint32_t nxt[4][6], cur[4][6];
+  constexpr int PS = DM * 8 / U_PRODUCERS;  // passes over the tile's rows
+  uint32_t nxt[PS][6], cur[PS][6];
   const int n_pairs = p.nff / 128;
   auto fetch_pair = [&](int pair) {
     const int blk = pair >> 1, h = pair & 1;
 #pragma unroll
-    for (int ps = 0; ps < 4; ++ps) {
-      const size_t bo = (size_t)(i0 + ps * 32 + g8) * drb + (size_t)blk * Q6K_BLOCK_BYTES;
+    for (int ps = 0; ps < PS; ++ps) {
+      const size_t bo = (size_t)(i0 + ps * (U_PRODUCERS / 8) + g8) * drb + (size_t)blk * Q6K_BLOCK_BYTES;
       nxt[ps][0] = ldg_u32_unaligned(wbase, bo + 64 * h + 4 * w);
       nxt[ps][1] = ldg_u32_unaligned(wbase, bo + 64 * h + 32 + 4 * w);
       nxt[ps][2] = ldg_u32_unaligned(wbase, bo + 128 + 32 * h + 4 * w);
@@ -366,14 +406,14 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
     const int hi_nib = step & 1;
     if (hi_nib == 0) {
 #pragma unroll
-      for (int ps = 0; ps < 4; ++ps)
+      for (int ps = 0; ps < PS; ++ps)
 #pragma unroll
         for (int i = 0; i < 6; ++i) cur[ps][i] = nxt[ps][i];
       if ((step >> 1) + 1 < n_pairs) fetch_pair((step >> 1) + 1);
     }
 #pragma unroll
-    for (int ps = 0; ps < 4; ++ps) {
-      const int row = ps * 32 + g8;
+    for (int ps = 0; ps < PS; ++ps) {
+      const int row = ps * (U_PRODUCERS / 8) + g8;
       const float d = f16_bits_to_f32(cur[ps][5]) * W_PRESCALE;
       // scale of quadrant qd for these l: byte 2*qd + (w >> 2) of the half's eight scale bytes
       const uint32_t sc4 = __byte_perm(cur[ps][3], cur[ps][4], (w >> 2) ? 0x7531u : 0x6420u);
@@ -393,30 +433,46 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
     return true;
   };
   auto issue = [&](unsigned char* st, unsigned char* tB, int step) {
+    const uint64_t dw = umma::smem_desc_k_major_swz128(st, 0), dt = umma::smem_desc_k_major_swz128(tB, 0);
+    for (int m = 0; m < n_m; ++m) {
+      const uint64_t dtm = dt + (uint64_t)m * (128 * 128 / 16);
+      umma::mma_f16(tmem + m * 256, dtm, dw, idesc, step > 0);
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
-      umma::mma_f16(tmem, umma::smem_desc_k_major_swz128(st, k), umma::smem_desc_k_major_swz128(tB, k), idesc, step > 0 || k > 0);
+      for (int k = 1; k < 4; ++k) umma::mma_f16_acc(tmem + m * 256, dtm + 2 * k, dw + 2 * k, idesc);
+    }
   };
   const int k_steps = p.nff / UK;
   unsigned long long* trc = (blockIdx.x == 0 && blockIdx.y == p.trace_tile) ? p.trace : nullptr;
   trace_stamp(trc, 45);
-  bool ok = run_pipeline<DN_SA, DN_SB>(bars, a_stages, A_TILE_BYTES, b_stages,
+  bool ok = run_pipeline<DN_SA, DN_SB>(bars, a_stages, DN_W_STAGE_BYTES, b_stages,
                                        reinterpret_cast<const unsigned char*>(p.act) + tile_step_offset(tile, k_steps, 0),
                                        (size_t)UN * 128, (uint32_t)n_eff * 128u, k_steps, unpack, issue, nullptr);
   trace_stamp(trc, 46);
 
+  // epilogue: a thread's accumulator row is a token, its 128 columns of this warp's feature half
+  // are 512 contiguous bytes of the token's output row
   if (tid < U_PRODUCERS) {
     if (ok) ok = mbar_wait_bounded(&bars.done, 0);
     umma::fence_after_sync();
-    if (ok) {
-      const int lane_grp = warp & 3, col_half = warp >> 2;
-      const int i = i0 + lane_grp * 32 + lane;
-      for (int c0 = col_half * 128; c0 < min(n_eff, col_half * 128 + 128); c0 += 32) {
-        float v[32];
-        umma::ld_32x32(tmem + ((uint32_t)(lane_grp * 32) << 16) + (uint32_t)c0, v);
+    const int lq = warp & 3, m = warp >> 3, ch = (warp >> 2) & 1;
+    if (ok && m < n_m) {
+      const int n0 = m * 128 + lq * 32;
+      const uint32_t trow = tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(m * 256 + ch * 128);
+      unsigned char* out = reinterpret_cast<unsigned char*>(p.y + (size_t)(row0 + n0) * p.ne + i0 + ch * 128);
+      const size_t out_pitch = (size_t)p.ne * 4;
+      unsigned char* patch = a_stages + (size_t)warp * (32 * 144);  // the weight stages are idle by now
 #pragma unroll
-        for (int t = 0; t < 32; ++t)
-          if (c0 + t < rows_valid) p.y[(size_t)(row0 + c0 + t) * p.ne + i] = v[t] * W_POSTSCALE;
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        umma::ld_32x32(trow + c * 32, v);
+        uint4 o[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+          o[t] = make_uint4(__float_as_uint(v[4 * t] * W_POSTSCALE), __float_as_uint(v[4 * t + 1] * W_POSTSCALE),
+                            __float_as_uint(v[4 * t + 2] * W_POSTSCALE), __float_as_uint(v[4 * t + 3] * W_POSTSCALE));
+        warp_store_rows<8>(patch, o, lane, rows_valid - n0, [&](int row, int piece) {
+          return out + (size_t)row * out_pitch + (size_t)c * 128 + piece * 16;
+        });
       }
     }
   }
@@ -424,12 +480,12 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
   if (!ok && lane == 0) atomicExch(&p.status->timeout, 6);
   umma::fence_before_sync();
   __syncthreads();
-  if (warp == 8) umma::tmem_dealloc(tmem, 256);
+  if (warp == U_PRODUCERS / 32) umma::tmem_dealloc(tmem, 512);
 }
 
 }  // namespace
 
-bool umma_grouped_supported(int ne, int nff) { return ne % 256 == 0 && nff % 256 == 0 && ne % UM == 0 && nff % UM == 0; }
+bool umma_grouped_supported(int ne, int nff) { return ne % 256 == 0 && nff % 256 == 0 && ne % DM == 0 && nff % UM == 0; }
 
 int umma_tile_rows() { return UN; }
 
@@ -465,8 +521,8 @@ bool q4k_rows_map(CUtensorMap* tm, const uint8_t* base, size_t n_rows, size_t ro
 }  // namespace
 
 int32_t launch_umma_grouped(infr_cuda_ctx* ctx, const GroupedParams& p, int max_tiles) {
-  const size_t smem_gu = 1024 + (size_t)GU_SA * GU_A_STAGE_BYTES + (size_t)GU_SB * B_TILE_BYTES + (size_t)U_PRODUCERS * Q4K_BLOCK_BYTES;
-  const size_t smem_dn = 1024 + (size_t)DN_SA * A_TILE_BYTES + (size_t)DN_SB * B_TILE_BYTES;
+  const size_t smem_gu = 1024 + (size_t)GU_SA * GU_A_STAGE_BYTES + (size_t)GU_SB * B_TILE_BYTES + (size_t)2 * UM * Q4K_BLOCK_BYTES;
+  const size_t smem_dn = 1024 + (size_t)DN_SA * DN_W_STAGE_BYTES + (size_t)DN_SB * B_TILE_BYTES;
   cudaError_t e = ensure_smem(reinterpret_cast<const void*>(k_umma_gateup), smem_gu);
   if (e == cudaSuccess) e = ensure_smem(reinterpret_cast<const void*>(k_umma_down), smem_dn);
   if (e != cudaSuccess) return check_cuda(ctx, e, "umma grouped smem attribute");
@@ -480,7 +536,7 @@ int32_t launch_umma_grouped(infr_cuda_ctx* ctx, const GroupedParams& p, int max_
     tm_sh_up = tm_up;
   }
   k_umma_gateup<<<dim3(p.nff / UM, max_tiles), U_THREADS, smem_gu, ctx->stream>>>(p, tm_gate, tm_up, tm_sh_gate, tm_sh_up);
-  k_umma_down<<<dim3(p.ne / UM, max_tiles), U_THREADS, smem_dn, ctx->stream>>>(p);
+  k_umma_down<<<dim3(p.ne / DM, max_tiles), U_THREADS, smem_dn, ctx->stream>>>(p);
   ctx->launches += 2;
   return check_cuda(ctx, cudaGetLastError(), "umma grouped launch");
 }
