@@ -39,8 +39,8 @@ Q4K_ROW = NE // 256 * 144      # bytes of one gate/up row
 Q6K_ROW = N_FF // 256 * 210    # bytes of one down row
 EXPERT_BYTES = 2 * N_FF * Q4K_ROW + NE * Q6K_ROW  # 2 039 808
 # DRAM bytes of one gate/up launch at 1 stream from the ncu capture summarised in
-# profiles/decode_gateup_c1_r1.md (dram__bytes_read.sum + dram__bytes_write.sum)
-GATEUP_TRAFFIC_R1 = 10_657_024
+# profiles/decode_c1_r1.md (dram__bytes_read.sum + dram__bytes_write.sum)
+GATEUP_TRAFFIC_R1 = 10_651_392
 
 
 def parse_args():
@@ -52,6 +52,7 @@ def parse_args():
     ap.add_argument("--workload", default="layer", choices=["layer", "stack", "prefill"],
                     help="layer: one MoE layer per step (the headline); stack: 40 such layers with RmsNorm and residual "
                          "add per step; prefill: one 4096-token chunk through one layer per step")
+    ap.add_argument("--tokens", type=int, default=4096, help="tokens of the prefill chunk (a smaller chunk is for profiler captures)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -462,7 +463,7 @@ def run_prefill(args):
     torch.cuda.set_stream(stream)
     be.set_stream(stream.cuda_stream)
     dev = f"cuda:{local}"
-    T, K, W = 4096, args.steps, max(args.warmup, 3)
+    T, K, W = args.tokens, args.steps, max(args.warmup, 3)
     rows = T // world
     band = None if world == 1 else (rank * (N_EXPERT // world), N_EXPERT // world)
     L = DeviceLayer(be, 77, NE, N_EXPERT, N_FF, sh_ff=SH_FF, device=dev, band=band)
@@ -501,7 +502,7 @@ def run_prefill(args):
             "metric": "moe_prefill_routed_tflops", "value": tfl, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic", "tokens_per_s": T * K / (ms * 1e-3),
-            "config": {"workload": "4096-token prefill chunk through one Qwen3.6-35B-A3B-shaped MoE layer, Zipf(1.1) router bias",
+            "config": {"workload": f"{T}-token prefill chunk through one Qwen3.6-35B-A3B-shaped MoE layer, Zipf(1.1) router bias",
                        "parallelism": f"ep{world}" if world > 1 else "single", "l2": "522 MB expert banks (inputs larger than L2)"},
             "roofline": {"bound": "tensor", "kernel": "whole step (router + permute + grouped GEMMs + combine)", "achieved": tfl,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tfl / peaks["bf16_tflops"], "peak_kind": kind,
