@@ -170,8 +170,7 @@ int32_t infr_cuda_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* de
  * optionally receive the error text.
  *
  * The first call on a device looks up the device address of the array (cudaGetSymbolAddress) with
- * that device current, so make that first call before starting any stream capture.  Every call
- * shares the one array: it keeps the previous call's logits (each call overwrites the part it
+ * that device current.  Every call shares the one array: it keeps the previous call's logits (each call overwrites the part it
  * uses and clears its counter first), and two calls that overlap on the GPU race on it - keep
  * calls on one device ordered on one stream. */
 int32_t infr_cuda_moe_route_noalloc(int32_t device, void* cuda_stream, const float* router_x, const float* router,
