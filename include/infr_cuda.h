@@ -67,8 +67,10 @@ int32_t infr_cuda_set_stream(infr_cuda_ctx* ctx, void* cuda_stream);
 /* Backend::alloc (backend.rs:652; zero-initialised, the calloc contract of :647-651) when
  * `zero` != 0, Backend::alloc_uninit (backend.rs:659) otherwise. */
 int32_t infr_cuda_alloc(infr_cuda_ctx* ctx, size_t bytes, int32_t zero, infr_cuda_buf** out);
-/* Wrap device memory the caller already owns (a torch tensor, an NCCL receive buffer) as a
- * buffer handle; freeing the handle leaves the memory alone.  No reference counterpart. */
+/* Wrap memory the caller already owns (a torch tensor, an NCCL receive buffer) as a buffer
+ * handle; freeing the handle leaves the memory alone.  Any address the device can access will do:
+ * device memory, or pinned host memory under unified addressing (a one-row `dst` there saves the
+ * copy back).  No reference counterpart. */
 int32_t infr_cuda_wrap(infr_cuda_ctx* ctx, void* device_ptr, size_t bytes, infr_cuda_buf** out);
 void infr_cuda_free(infr_cuda_ctx* ctx, infr_cuda_buf* buf);
 /* Buffer::len_bytes (backend.rs:424-433) and the raw device address. */
