@@ -227,6 +227,33 @@ int32_t infr_cuda_moe_combine(infr_cuda_ctx* ctx, const infr_cuda_buf* y_rows, c
 
 /* ---- record once, replay (Backend::compile + the decode replay of the Vulkan backend) ----------- */
 
+/* ---- GGUF ingest ------------------------------------------------------------------------------
+ * The tensors of the path come out of a model file byte for byte, as the reference loads them
+ * (parser crates/infr-gguf/src/lib.rs:745-870; tensor names crates/infr-llama/src/seam/runner.rs:
+ * 2560-2595: blk.N.ffn_gate_inp.weight (router), ffn_gate_exps / ffn_up_exps / ffn_down_exps,
+ * exp_probs_b.bias, ffn_gate_shexp / ffn_up_shexp / ffn_down_shexp, ffn_gate_inp_shexp).  GGUF
+ * dimensions list the fastest axis first: an expert bank reads {in_f, out_f, n_expert}, which is
+ * the [n_expert, out_f, in_f] row-major bank of the descriptor.  Versions 2 and 3, one file
+ * (no split sets).  A malformed file is refused with a message in `err`. */
+typedef struct infr_cuda_gguf infr_cuda_gguf; /* opaque: a mapped, parsed file */
+typedef struct infr_cuda_gguf_tensor {
+  int32_t dtype;     /* ggml type number (= INFR_CUDA_DT_* for the types the kernels take) */
+  uint32_t n_dims;
+  uint64_t dims[4];  /* ne[0] fastest; unused dimensions are 1 */
+  uint64_t offset;   /* absolute byte offset in the file */
+  uint64_t nbytes;   /* 0 when the type's block layout is not known to the reader */
+} infr_cuda_gguf_tensor;
+int32_t infr_cuda_gguf_open(const char* path, infr_cuda_gguf** out, char* err, size_t err_cap);
+void infr_cuda_gguf_close(infr_cuda_gguf* g);
+uint64_t infr_cuda_gguf_tensor_count(const infr_cuda_gguf* g);
+/* INFR_CUDA_ERR_INVALID_ARG when there is no such tensor / key (or the key has another type). */
+int32_t infr_cuda_gguf_find(const infr_cuda_gguf* g, const char* name, infr_cuda_gguf_tensor* out);
+int32_t infr_cuda_gguf_meta_u64(const infr_cuda_gguf* g, const char* key, uint64_t* out);
+int32_t infr_cuda_gguf_meta_f64(const infr_cuda_gguf* g, const char* key, double* out);
+int32_t infr_cuda_gguf_meta_str(const infr_cuda_gguf* g, const char* key, char* out, size_t cap);
+/* A new device buffer holding the tensor's bytes as stored (plus 16 spare bytes at the end). */
+int32_t infr_cuda_gguf_upload(infr_cuda_ctx* ctx, const infr_cuda_gguf* g, const char* name, infr_cuda_buf** out);
+
 /* The reference records a decode step's dispatches once and replays the command buffer per token
  * (`Capabilities::decode_replay`, crates/infr-core/src/backend.rs:45-236; graph built per forward in
  * crates/infr-llama/src/seam/runner.rs:12574-12796).  Here the calls issued between begin and end

@@ -11,7 +11,8 @@ CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_lib")
 LIB = os.path.join(OUT_DIR, "libinfr_cuda.so")
 
-SOURCES = ["api.cu", "router_topk.cu", "decode_ffn.cu", "dense_ops.cu", "grouped_ffn.cu", "grouped_umma.cu", "umma_selftest.cu"]
+SOURCES = ["api.cu", "router_topk.cu", "decode_ffn.cu", "dense_ops.cu", "grouped_ffn.cu", "grouped_umma.cu", "umma_selftest.cu",
+           "gguf_ingest.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
