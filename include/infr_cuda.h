@@ -139,10 +139,15 @@ typedef struct infr_cuda_moe_ffn_desc {
   const infr_cuda_buf* residual;    /* MoeFfn -> Add: [rows, ne] f32 added to the result; may be the
                                        same buffer as dst (in-place hidden update); NULL = off      */
   float norm_eps;
-  uint32_t stages;                  /* 0 = the whole op.  Otherwise a mask of the kernels to launch,
-                                       for timing one of them alone: 1 router + top-k, 2 gate/up,
-                                       4 down + combine.  Later stages read what an earlier full
-                                       call left in ids_out / wts_out and the context's scratch.   */
+  uint32_t stages;                  /* 0 = the whole op.  Otherwise a mask of the kernels to launch:
+                                       1 router + top-k, 2 gate/up, 4 down + combine, 8 the
+                                       fixed-point copy of x the small-m expert kernels read
+                                       (made by stage 1 otherwise).  Later
+                                       stages read ids_out / wts_out (what an earlier call left
+                                       there, or routing done elsewhere: an expert-parallel rank
+                                       passes the ids it received with stages = 14) and the
+                                       context's scratch.  A negative id marks a pair that is not
+                                       this call's to serve; it contributes nothing.               */
 } infr_cuda_moe_ffn_desc;
 
 /* Backend::execute of a graph holding one Op::MoeFfn (backend.rs:908; CPU arm

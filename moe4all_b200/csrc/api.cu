@@ -508,6 +508,10 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
       }
       if ((rc = launch_route(ctx, rp, false))) return rc;
       if ((rc = launch_quantize_rows(ctx, x_eff, s.xq_lo, s.xq_hi, s.xscale, (int)d->rows, (int)d->ne))) return rc;
+    } else if (stages & 8u) {
+      // routing came from elsewhere (ids_out / wts_out are inputs): only the fixed-point copy of x is made here
+      if (d->norm_weight) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: stages without the router cannot apply norm_weight");
+      if ((rc = launch_quantize_rows(ctx, static_cast<const float*>(d->x->ptr), s.xq_lo, s.xq_hi, s.xscale, (int)d->rows, (int)d->ne))) return rc;
     }
     DecodeParams dp = {};
     dp.xq_lo = s.xq_lo;

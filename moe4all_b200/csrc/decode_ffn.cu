@@ -108,9 +108,10 @@ __global__ void __maxnreg__(56) k_decode_gateup(DecodeParams p, int n_chunks) {
   const float q_scale = __ldcg(p.xscale + r);
   if (routed) {
     int e = e_sel;
-    if (e < 0 || e >= p.n_expert) {
+    if (e < 0) return;  // a negative id marks a pair another rank serves
+    if (e >= p.n_expert) {
       if (tid == 0) p.status->bad_index = 1;
-      e = min(max(e, 0), p.n_expert - 1);
+      e = p.n_expert - 1;
     }
     if (!in_band(p, e)) return;
     if (tid == 0)
@@ -247,8 +248,9 @@ __global__ void __maxnreg__(56) k_decode_down(DecodeParams p, int TI) {
     const int s = tid;
     if (s < p.n_used) {
       int e = __ldcg(p.ids + r * p.n_used + s);
+      const bool mine = e >= 0;  // a negative id marks a pair another rank serves
       e = min(max(e, 0), p.n_expert - 1);
-      s_on[s] = in_band(p, e) ? e + 1 : 0;
+      s_on[s] = (mine && in_band(p, e)) ? e + 1 : 0;
       s_w[s] = __ldcg(p.wts + r * p.n_used + s);
     } else {
       s_on[s] = 1;

@@ -52,7 +52,8 @@ __global__ void k_pair_count(const int32_t* __restrict__ ids, int n_pairs, int n
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= n_pairs) return;
   int e = ids[p];
-  e = min(max(e, 0), n_expert - 1);
+  if (e < 0) return;  // a negative id marks a pair another rank serves
+  e = min(e, n_expert - 1);
   if (ep_n && ((uint32_t)e < ep_lo || (uint32_t)e >= ep_lo + ep_n)) return;
   atomicAdd(&counts[e], 1);
 }
@@ -151,8 +152,9 @@ __global__ void k_pair_scatter(const int32_t* __restrict__ ids, int n_pairs, int
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= n_pairs) return;
   int e = ids[p];
+  const bool other = e < 0;
   e = min(max(e, 0), n_expert - 1);
-  if (ep_n && ((uint32_t)e < ep_lo || (uint32_t)e >= ep_lo + ep_n)) {
+  if (other || (ep_n && ((uint32_t)e < ep_lo || (uint32_t)e >= ep_lo + ep_n))) {
     pos_of_pair[p] = -1;
     return;
   }

@@ -1,5 +1,5 @@
 """Expert-parallel dispatch/combine bookkeeping on CPU: world size 2 over gloo, with a stand-in
-expert function (no GPU, no oracle): y = x * (global expert id + 1)."""
+expert function (no GPU, no oracle): expert e maps x to x * (e + 1)."""
 import os
 import socket
 
@@ -22,20 +22,19 @@ def fake_route(x):
     return ids, wts
 
 
-def make_expert_fn(rank, e_local):
-    def fn(xg, seg_off):
-        y = torch.empty_like(xg)
-        for e in range(e_local):
-            a, b = int(seg_off[e]), int(seg_off[e + 1])
-            y[a:b] = xg[a:b] * float(rank * e_local + e + 1)
-        return y
+def make_band_fn(rank, e_local):
+    lo = rank * e_local
+
+    def fn(x_rows, ids, wts):
+        ids = ids.to(torch.int64)
+        mine = ((ids >= lo) & (ids < lo + e_local)).to(torch.float32)
+        coef = ((ids.to(torch.float32) + 1) * wts * mine).sum(1, keepdim=True)
+        return x_rows * coef
     return fn
 
 
-def combine(y_sorted, pos_of_pair, wts, x):
-    R = x.shape[0]
-    y = y_sorted[pos_of_pair.long()].reshape(R, K, x.shape[1])
-    return (y * wts[..., None]).sum(1)
+def finish(moe, x):
+    return moe
 
 
 def expected(x):
@@ -49,10 +48,10 @@ def worker(rank, world, port, rows_per_rank, fail_rank, ret):
     try:
         torch.manual_seed(100 + rank)
         x = torch.randn(rows_per_rank[rank], NE)
-        ep = ExpertParallel(E, K, fake_route, make_expert_fn(rank, E // world), combine)
+        ep = ExpertParallel(E, K, fake_route, make_band_fn(rank, E // world), finish)
         if fail_rank == rank:
             # a rank whose expert function returns the wrong number of rows must raise, not hang
-            ep.expert_fn = lambda xg, seg: xg[:-1] if xg.shape[0] else xg
+            ep.band_fn = lambda xr, i, w: xr[:-1] if xr.shape[0] else xr.new_zeros(1, xr.shape[1])
         try:
             out = ep.forward(x)
             ok = torch.allclose(out, expected(x), rtol=1e-5, atol=1e-6)
@@ -88,7 +87,7 @@ def test_ep_world1_identity():
     # world 1 is the identity lowering (crates/infr-vulkan/src/adapter.rs:27494-27701)
     torch.manual_seed(3)
     x = torch.randn(11, NE)
-    ep = ExpertParallel(E, K, fake_route, make_expert_fn(0, E), combine)
+    ep = ExpertParallel(E, K, fake_route, make_band_fn(0, E), finish)
     assert torch.allclose(ep.forward(x), expected(x), rtol=1e-5, atol=1e-6)
 
 
@@ -98,7 +97,7 @@ def test_expert_count_must_divide(monkeypatch):
     monkeypatch.setattr(dist, "get_world_size", lambda group=None: 2)
     monkeypatch.setattr(dist, "get_rank", lambda group=None: 0)
     with pytest.raises(ValueError):
-        ExpertParallel(7, 2, fake_route, make_expert_fn(0, 3), combine)
+        ExpertParallel(7, 2, fake_route, make_band_fn(0, 3), finish)
 
 
 def test_bad_expert_fn_raises_on_the_host():

@@ -85,6 +85,27 @@ def test_batched_ep_bands_sum_to_full(backend):
     assert_close(parts[1], oracle_layer(L, x, 4, ep_band=(8, 8)).dst)
 
 
+@pytest.mark.parametrize("rows,path", [(4, 1), (20, 1), (100, 2)])
+def test_routing_from_outside_with_foreign_pairs(backend, rows, path):
+    # what an expert-parallel rank runs: ids and weights are inputs (stages 2 + 4 + 8), pairs of
+    # other ranks carry a negative id and contribute nothing
+    from moe4all_b200 import MoeFfn
+    L = synth.make_layer(47, 512, 32, 256, router_std=0.05)
+    x = synth.activations(6, rows, 512)
+    g = GpuLayer(backend, L)
+    want, ids, wts = g.run(x, 4, path=path, ep_band=(8, 16))
+    local = np.where((ids >= 8) & (ids < 24), ids, -1).astype(np.int32)
+    be = backend
+    dst = be.alloc(rows * 512 * 4)
+    op = MoeFfn(x=be.from_host(x), router=g.router, gate_exps=g.gate, up_exps=g.up, down_exps=g.down, dst=dst, rows=rows, ne=512,
+                n_expert=32, n_used=4, n_ff_exp=256, ids_out=be.from_host(local), wts_out=be.from_host(wts), stages=14, path=path)
+    be.moe_ffn(op)
+    be.sync()
+    got = be.download(dst, np.float32).reshape(rows, 512)
+    assert np.array_equal(got, want)
+    assert_close(got, oracle_layer(L, x, 4, ep_band=(8, 16)).dst)
+
+
 def test_config1_shape_512_rows(backend):
     # the Qwen3.6-35B-A3B layer shape with a 512-token chunk
     L = synth.make_layer(46, 2048, 256, 512, sh_ff=512)
