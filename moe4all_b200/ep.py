@@ -35,10 +35,10 @@ class ExpertParallel:
     """route_fn(x) -> (ids [R,k] int32, wts [R,k] f32)
     band_fn(x_rows [n, ne], ids [n,k] int32 global ids, wts [n,k]) -> [n, ne]: for every row the
         weighted sum over its pairs whose expert lies in THIS rank's band (others contribute 0)
-    finish_fn(moe [R, ne], x [R, ne]) -> out [R, ne]   (adds what is replicated: the shared expert)"""
+    finish_fn(moe [R, ne], x [R, ne][, prepared]) -> out [R, ne]   (adds what is replicated: the shared expert)"""
 
     def __init__(self, n_expert: int, n_used: int, route_fn: Callable, band_fn: Callable, finish_fn: Callable,
-                 group: Optional[dist.ProcessGroup] = None):
+                 group: Optional[dist.ProcessGroup] = None, prepare_fn: Optional[Callable] = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -46,6 +46,9 @@ class ExpertParallel:
             raise ValueError(f"n_expert {n_expert} is not a multiple of the world size {self.world}")  # ep.rs:171-176
         self.n_expert, self.n_used, self.e_local = n_expert, n_used, n_expert // self.world
         self.route_fn, self.band_fn, self.finish_fn = route_fn, band_fn, finish_fn
+        # optional: work on x that needs no exchange (the shared expert), queued before the plan's
+        # host synchronisation so that the device is busy meanwhile; its result goes to finish_fn
+        self.prepare_fn = prepare_fn
         self.check_ids = False
 
     @property
@@ -80,6 +83,7 @@ class ExpertParallel:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """x: this rank's token rows [R, ne] (f32).  Returns the MoE FFN output for those rows."""
         ids, wts = self.route_fn(x)
+        prepared = self.prepare_fn(x) if self.prepare_fn is not None else None
         pl = self.plan(ids)
         ne, k = x.shape[1], self.n_used
         # dispatch: the row, its ids (bit-cast) and its weights, once per destination rank
@@ -104,7 +108,7 @@ class ExpertParallel:
             if n:
                 moe.index_add_(0, pl.tok[o:o + n], back[o:o + n])
             o += n
-        return self.finish_fn(moe, x)
+        return self.finish_fn(moe, x) if self.prepare_fn is None else self.finish_fn(moe, x, prepared)
 
 
 # -------------------------------------------------------------------------------------------------
@@ -127,8 +131,9 @@ class CudaExpertParallelLayer:
         # the index plumbing runs as torch ops: put the library's kernels on the same stream
         s = torch.cuda.current_stream().cuda_stream
         be.set_stream(s if s != 0 else 1)  # 1 = the legacy default stream handle (0 would mean "own stream")
-        self.ep = ExpertParallel(n_expert, n_used, self._route, self._band, self._finish)
         self.has_shared = "sh_gate" in layer.b
+        self.ep = ExpertParallel(n_expert, n_used, self._route, self._band, self._finish, prepare_fn=self._shared)
+        self._keep = []  # tensors the queued kernels still read; released at the start of the next forward
 
     def _route(self, x):
         be, b = self.be, self.L.b
@@ -156,29 +161,44 @@ class CudaExpertParallelLayer:
         be.moe_ffn(self._MoeFfn(x=be.wrap_tensor(x_rows), router=b["router"], gate_exps=b["gate"], up_exps=b["up"], down_exps=b["down"],
                                 dst=be.wrap_tensor(out), rows=n, ne=self.ne, n_expert=n_local, n_used=self.n_used, n_ff_exp=self.n_ff,
                                 ids_out=be.wrap_tensor(local), wts_out=be.wrap_tensor(wts), stages=14))
-        be.sync()  # `local` must outlive the kernels that read it
+        self._keep += [x_rows, local, wts, out]
         return out
 
-    def _finish(self, moe, x):
+    def _shared(self, x):
+        """Queues the replicated shared expert over this rank's own tokens: (rows, gate logits)."""
         if not self.has_shared:
-            return moe
+            return None
         be, b = self.be, self.L.b
         R = x.shape[0]
-        # the shared expert is replicated: every rank runs it over its own tokens
         sh = torch.empty_like(x)
         seg = torch.tensor([0, R], dtype=torch.int32, device=x.device)
         xb = be.wrap_tensor(x)
         be.moe_expert_rows(xb, be.wrap_tensor(seg), b["sh_gate"], b["sh_up"], b["sh_down"], be.wrap_tensor(sh), R, 1, self.ne, self.n_ff)
-        out = torch.empty_like(x)
+        gl = None
         if "sh_gate_inp" in b:
             gl = torch.empty(R, dtype=torch.float32, device=x.device)
-            glb = be.wrap_tensor(gl)
-            be.linear(self._DType.F32, b["sh_gate_inp"], xb, glb, R, self.ne, 1)
-            be.moe_shared_expert_add(be.wrap_tensor(moe), be.wrap_tensor(sh), glb, be.wrap_tensor(out), R, self.ne)
+            be.linear(self._DType.F32, b["sh_gate_inp"], xb, be.wrap_tensor(gl), R, self.ne, 1)
+        self._keep += [sh, seg, gl]
+        return sh, gl
+
+    def _finish(self, moe, x, prepared):
+        if prepared is None:
+            return moe
+        be = self.be
+        sh, gl = prepared
+        R = x.shape[0]
+        out = torch.empty_like(x)
+        if gl is not None:
+            be.moe_shared_expert_add(be.wrap_tensor(moe), be.wrap_tensor(sh), be.wrap_tensor(gl), be.wrap_tensor(out), R, self.ne)
         else:
             be.add(be.wrap_tensor(moe), be.wrap_tensor(sh), be.wrap_tensor(out), R * self.ne)
-        be.sync()  # the temporaries above must outlive the kernels that read them
+        self._keep += [moe, out]
         return out
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.ep.forward(x)
+        # everything queued by the previous call has been ordered before this call's work on the
+        # same stream; the plan's host synchronisation below makes releasing its tensors safe
+        keep, self._keep = self._keep, []
+        out = self.ep.forward(x)
+        del keep
+        return out
