@@ -53,7 +53,11 @@ def parse_args():
     ap.add_argument("--workload", default="layer", choices=["layer", "stack", "prefill"],
                     help="layer: one MoE layer per step (the headline); stack: 40 such layers with RmsNorm and residual "
                          "add per step; prefill: one 4096-token chunk through one layer per step")
-    ap.add_argument("--tokens", type=int, default=4096, help="tokens of the prefill chunk (a smaller chunk is for profiler captures)")
+    ap.add_argument("--tokens", type=int, default=0, help="tokens of the prefill chunk (default 4096, or 8192 for --shape deepseek; "
+                    "64 is the largest configuration's decode batch; a smaller chunk also suits profiler captures)")
+    ap.add_argument("--shape", default="qwen", choices=["qwen", "deepseek"],
+                    help="prefill workload only: the 256-expert Qwen3.6-35B-A3B layer, or the DeepSeek-V3-shaped one "
+                         "(hidden 7168, intermediate 2048, sigmoid gating in 8 groups / 4 used, ungated shared expert)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -471,29 +475,35 @@ def run_prefill(args):
     torch.cuda.set_stream(stream)
     be.set_stream(stream.cuda_stream)
     dev = f"cuda:{local}"
-    T, K, W = args.tokens, args.steps, max(args.warmup, 3)
+    deepseek = args.shape == "deepseek"
+    ne, n_expert, n_used, n_ff, sh_ff = (7168, 256, 8, 2048, 2048) if deepseek else (NE, N_EXPERT, N_USED, N_FF, SH_FF)
+    route_kw = dict(scale=2.5, gating=1, n_expert_groups=8, n_expert_groups_used=4) if deepseek else {}
+    T, K, W = args.tokens or (8192 if deepseek else 4096), args.steps, max(args.warmup, 3)
     rows = T // world
-    band = None if world == 1 else (rank * (N_EXPERT // world), N_EXPERT // world)
-    L = DeviceLayer(be, 77, NE, N_EXPERT, N_FF, sh_ff=SH_FF, device=dev, band=band)
+    band = None if world == 1 else (rank * (n_expert // world), n_expert // world)
+    L = DeviceLayer(be, 77, ne, n_expert, n_ff, sh_ff=sh_ff, gated_shared=not deepseek, device=dev, band=band)
     gen = torch.Generator(device=dev)
-    gen.manual_seed(9)
-    zipf = -1.1 * torch.log((torch.randperm(N_EXPERT, generator=gen, device=dev) + 1).float())
-    L.t["router"][:-16].view(torch.float32).view(N_EXPERT, NE)[:, NE - 1] = zipf
+    if not deepseek:
+        gen.manual_seed(9)
+        zipf = -1.1 * torch.log((torch.randperm(n_expert, generator=gen, device=dev) + 1).float())
+        L.t["router"][:-16].view(torch.float32).view(n_expert, ne)[:, ne - 1] = zipf
     gen.manual_seed(100 + rank)
-    x = torch.randn(rows, NE, generator=gen, device=dev)
+    x = torch.randn(rows, ne, generator=gen, device=dev)
     dst = torch.empty_like(x)
     b = L.b
     if world == 1:
         rx = x.clone()
-        rx[:, NE - 1] = 1.0  # the bias column is read by the router only (separate router_x handle)
+        if not deepseek:
+            rx[:, ne - 1] = 1.0  # the bias column is read by the router only (separate router_x handle)
         op = MoeFfn(x=be.wrap_tensor(x), router_x=be.wrap_tensor(rx), router=b["router"], gate_exps=b["gate"], up_exps=b["up"],
-                    down_exps=b["down"], dst=be.wrap_tensor(dst), rows=rows, ne=NE, n_expert=N_EXPERT, n_used=N_USED,
-                    n_ff_exp=N_FF, sh_gate=b["sh_gate"], sh_up=b["sh_up"], sh_down=b["sh_down"], sh_gate_inp=b["sh_gate_inp"],
-                    sh_ff=SH_FF, path=2)
+                    down_exps=b["down"], dst=be.wrap_tensor(dst), rows=rows, ne=ne, n_expert=n_expert, n_used=n_used,
+                    n_ff_exp=n_ff, sh_gate=b["sh_gate"], sh_up=b["sh_up"], sh_down=b["sh_down"], sh_gate_inp=b.get("sh_gate_inp"),
+                    sh_ff=sh_ff, path=0 if T < 512 else 2, **route_kw)
         step = lambda s: be.moe_ffn(op)
     else:
-        x[:, NE - 1] = 1.0  # expert-parallel layer routes on x itself
-        layer = CudaExpertParallelLayer(be, L, N_EXPERT, N_USED, N_FF, NE)
+        if not deepseek:
+            x[:, ne - 1] = 1.0  # expert-parallel layer routes on x itself
+        layer = CudaExpertParallelLayer(be, L, n_expert, n_used, n_ff, ne, **{("n_groups" if k == "n_expert_groups" else "n_groups_used" if k == "n_expert_groups_used" else k): v for k, v in route_kw.items()})
         step = lambda s: layer.forward(x)
     for s in range(W):
         step(s)
@@ -504,14 +514,17 @@ def run_prefill(args):
     clocks = sampler.stop()
     if rank == 0:
         peaks, kind = measured_peaks()
-        flops = 3 * 2 * T * N_USED * NE * N_FF  # routed experts only (2*pairs*K*N per GEMM)
+        flops = 3 * 2 * T * n_used * ne * n_ff  # routed experts only (2*pairs*K*N per GEMM)
         tfl = flops / (ms / K * 1e-3) / 1e12
         print(json.dumps({
             "metric": "moe_prefill_routed_tflops", "value": tfl, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic", "tokens_per_s": T * K / (ms * 1e-3),
-            "config": {"workload": f"{T}-token prefill chunk through one Qwen3.6-35B-A3B-shaped MoE layer, Zipf(1.1) router bias",
-                       "parallelism": f"ep{world}" if world > 1 else "single", "l2": "522 MB expert banks (inputs larger than L2)"},
+            "config": {"workload": (f"{T} tokens through one DeepSeek-V3-shaped MoE layer (hidden 7168, 256 experts top-8 in 8 groups / 4 used, "
+                                    f"intermediate 2048, shared expert)" if deepseek else
+                                    f"{T}-token prefill chunk through one Qwen3.6-35B-A3B-shaped MoE layer, Zipf(1.1) router bias"),
+                       "parallelism": f"ep{world}" if world > 1 else "single",
+                       "l2": f"{n_expert * (2 * n_ff * (ne // 256 * 144) + ne * (n_ff // 256 * 210)) >> 20} MiB expert banks (inputs larger than L2)"},
             "roofline": {"bound": "tensor", "kernel": "whole step (router + permute + grouped GEMMs + combine)", "achieved": tfl,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tfl / peaks["bf16_tflops"], "peak_kind": kind,
                          "traffic": None},

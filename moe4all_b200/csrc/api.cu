@@ -477,7 +477,10 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   // 256 experts, top-8.
   if (path == 0) {
     const bool few_per_expert = (uint64_t)d->rows * d->n_used * 8 <= (uint64_t)d->n_expert * 24;  // <= 3 tokens per expert
-    path = (small_ok && (d->rows <= 8 || few_per_expert)) ? 1 : 2;
+    // experts of tens of megabytes (hidden 7168 x intermediate 2048): the small-m kernels hold one
+    // chunk of rows per CTA there and the grouped GEMMs are ahead from eight rows on
+    const bool big = (uint64_t)d->ne * d->n_ff_exp >= (1ull << 23);
+    path = (small_ok && (big ? d->rows < 8 : (d->rows <= 8 || few_per_expert))) ? 1 : 2;
   }
   if (path == 1) {
     if (!small_ok) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, why);

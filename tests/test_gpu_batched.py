@@ -85,6 +85,22 @@ def test_batched_ep_bands_sum_to_full(backend):
     assert_close(parts[1], oracle_layer(L, x, 4, ep_band=(8, 8)).dst)
 
 
+@pytest.mark.parametrize("path", [1, 2])
+def test_deepseek_v3_dims(backend, path):
+    # hidden 7168, expert intermediate 2048, sigmoid gating with 8 groups / 4 used, scale 2.5,
+    # ungated shared expert; 16 experts keep the oracle quick.  64 rows is the decode batch of the
+    # largest configuration, served by the small-m kernels (path 1) or the grouped GEMMs (path 2).
+    L = synth.make_layer(51, 7168, 16, 2048, sh_ff=2048, gated_shared=False, bias_std=0.02)
+    x = synth.activations(8, 64, 7168)
+    kw = dict(scale=2.5, gating=MoeGating.Sigmoid, groups=8, groups_used=4)
+    out, ids, wts = GpuLayer(backend, L).run(x, 4, path=path, **kw)
+    ref = oracle_layer(L, x, 4, **kw)
+    ties = ids_match(ids, ref, 4)
+    keep = [r for r in range(64) if r not in ties]
+    assert len(keep) > 56
+    assert_close(out[keep], ref.dst[keep])
+
+
 @pytest.mark.parametrize("rows,path", [(4, 1), (20, 1), (100, 2)])
 def test_routing_from_outside_with_foreign_pairs(backend, rows, path):
     # what an expert-parallel rank runs: ids and weights are inputs (stages 2 + 4 + 8), pairs of
