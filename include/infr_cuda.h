@@ -107,7 +107,7 @@ typedef struct infr_cuda_moe_ffn_desc {
   const infr_cuda_buf* router;      /* [n_expert, ne] router_dtype                                 */
   const infr_cuda_buf* gate_exps;   /* [n_expert, n_ff_exp, ne] gate_dtype                         */
   const infr_cuda_buf* up_exps;     /* [n_expert, n_ff_exp, ne] up_dtype                           */
-  const infr_cuda_buf* down_exps;   /* [n_expert, ne, n_ff_exp] down_dtype                         */
+  const infr_cuda_buf* down_exps;   /* [n_expert, ne, n_ff_exp] down_dtype (Q6_K or Q4_K)          */
   const infr_cuda_buf* exp_probs_b; /* [n_expert] f32 selection-only bias, or NULL                 */
   infr_cuda_buf* dst;               /* [rows, ne] f32                                              */
   infr_cuda_buf* ids_out;           /* [rows, n_used] i32 selected experts, rank order; or NULL    */

@@ -358,8 +358,9 @@ static int32_t validate_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d)
   int32_t rc = validate_route(ctx, d);
   if (rc) return rc;
   if (!d->n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: zero n_ff_exp");
-  if (d->gate_dtype != INFR_CUDA_DT_Q4K || d->up_dtype != INFR_CUDA_DT_Q4K || d->down_dtype != INFR_CUDA_DT_Q6K)
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be gate/up Q4_K and down Q6_K");
+  if (d->gate_dtype != INFR_CUDA_DT_Q4K || d->up_dtype != INFR_CUDA_DT_Q4K ||
+      (d->down_dtype != INFR_CUDA_DT_Q6K && d->down_dtype != INFR_CUDA_DT_Q4K))
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be gate/up Q4_K and down Q6_K or Q4_K");
   if (d->ne % 256 || d->n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ne and n_ff_exp must be multiples of the 256-weight block");
   const size_t xb = (size_t)d->rows * d->ne * 4;
   if (!fits(d->x, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: x missing or too small");
@@ -470,7 +471,8 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   DeviceGuard g(ctx->device);
   const bool has_sh = d->sh_gate != nullptr;
   std::string why;
-  const bool small_ok = decode_ffn_supported(ctx, d->ne, d->n_ff_exp, has_sh ? d->sh_ff : 0, d->n_used, &why);
+  const bool down_q4k = d->down_dtype == INFR_CUDA_DT_Q4K;
+  const bool small_ok = decode_ffn_supported(ctx, d->ne, d->n_ff_exp, has_sh ? d->sh_ff : 0, d->n_used, down_q4k, &why);
   uint32_t path = d->path;
   // Per (token, expert) pair the small-m kernels are cheaper than a grouped-GEMM tile until an
   // expert sees several tokens of the call on average; measured cross-over near 120 rows for
@@ -546,6 +548,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.n_expert = d->n_expert;
     dp.ep_lo = d->ep_lo;
     dp.ep_n = d->ep_n_local;
+    dp.down_q4k = down_q4k ? 1 : 0;
     return launch_decode_ffn(ctx, dp, true, stages);
   }
   // batched path: router GEMM + top-k, permute, grouped GEMMs, un-permute combine
@@ -603,6 +606,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     c.ep_lo = d->ep_lo;
     c.ep_n = d->ep_n_local;
     c.legacy = (path == 3) ? 1 : 0;
+    c.down_q4k = down_q4k ? 1 : 0;
     return launch_grouped_ffn(ctx, c);
   }
 }
@@ -669,8 +673,8 @@ int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_row
   if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
   if (!n_local || !ne || !n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: zero dimension");
   if (n_local > 1024) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: more than 1024 local experts");
-  if (gate_dtype != INFR_CUDA_DT_Q4K || up_dtype != INFR_CUDA_DT_Q4K || down_dtype != INFR_CUDA_DT_Q6K)
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be gate/up Q4_K and down Q6_K");
+  if (gate_dtype != INFR_CUDA_DT_Q4K || up_dtype != INFR_CUDA_DT_Q4K || (down_dtype != INFR_CUDA_DT_Q6K && down_dtype != INFR_CUDA_DT_Q4K))
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be gate/up Q4_K and down Q6_K or Q4_K");
   if (ne % 256 || n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: ne and n_ff_exp must be multiples of 256");
   if (!n_rows) return INFR_CUDA_OK;
   const size_t gb = (size_t)n_local * n_ff_exp * row_bytes(gate_dtype, ne), db = (size_t)n_local * ne * row_bytes(down_dtype, n_ff_exp);
@@ -699,6 +703,7 @@ int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_row
   c.nff = (int)n_ff_exp;
   c.n_expert = (int)n_local;
   c.rows_bound = (int)n_rows;
+  c.down_q4k = down_dtype == INFR_CUDA_DT_Q4K ? 1 : 0;
   return launch_grouped_ffn(ctx, c);
 }
 

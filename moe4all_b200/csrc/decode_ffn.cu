@@ -215,9 +215,10 @@ __global__ void __maxnreg__(56) k_decode_down(DecodeParams p, int TI) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthreads = blockDim.x, nwarps = nthreads >> 5;
   const int nb = p.nff / 256;                    // blocks per routed row
-  const int drb = nb * (int)Q6K_BLOCK_BYTES;     // bytes per routed row
+  const int dbb = p.down_q4k ? (int)Q4K_BLOCK_BYTES : (int)Q6K_BLOCK_BYTES;  // bytes per 256-weight block of the down banks
+  const int drb = nb * dbb;                      // bytes per routed row
   const bool has_sh = p.sh_down != nullptr;
-  const int sh_nb = p.sh_ff / 256, sh_drb = sh_nb * (int)Q6K_BLOCK_BYTES;
+  const int sh_nb = p.sh_ff / 256, sh_drb = sh_nb * dbb;
   const int n_slots = p.n_used + (has_sh ? 1 : 0);
   const int tiles = p.ne / TI;
   const int r = blockIdx.x / tiles, i0 = (blockIdx.x % tiles) * TI;
@@ -343,7 +344,44 @@ __global__ void __maxnreg__(56) k_decode_down(DecodeParams p, int TI) {
       const int n_hb = (shared_slot ? sh_nb : nb) * 2;  // half-blocks per row
       const unsigned char* wt = s_wt + (shared_slot ? (size_t)p.n_used * slab_pad : (size_t)s * slab_pad) + s_off[s];
       const int chunk0 = shared_slot ? p.n_used * p.nff / 128 : s * (p.nff / 128);
-      if (q < RPG) {
+      if (q < RPG && p.down_q4k) {
+        // Q4_K rows (16-byte aligned): a lane walks 64-element groups (32 code bytes: low nibbles
+        // = 32 elements, high nibbles = the next 32), four groups side by side across the quarter lanes
+        const unsigned char* wrow = wt + (size_t)(row0 + q) * row_bytes_s;
+        for (int g = u4; g < n_hb * 2; g += 4) {
+          const int b = g >> 2, j = g & 3, chunk = chunk0 + (g >> 1);
+          const uint4 hdr = *reinterpret_cast<const uint4*>(wrow + b * Q4K_BLOCK_BYTES);
+          const uint4 qa = *reinterpret_cast<const uint4*>(wrow + b * Q4K_BLOCK_BYTES + 16 + 32 * j);
+          const uint4 qb = *reinterpret_cast<const uint4*>(wrow + b * Q4K_BLOCK_BYTES + 32 + 32 * j);
+          const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+          const uint4* xl = reinterpret_cast<const uint4*>(s_xlo + chunk * DN_XPITCH + (g & 1) * 16);
+          const uint4* xh = reinterpret_cast<const uint4*>(s_xhi + chunk * DN_XPITCH + (g & 1) * 16);
+          const int* s16 = s_s16 + chunk * 8 + (g & 1) * 4;
+          int v[2];
+#pragma unroll
+          for (int hn = 0; hn < 2; ++hn) {  // low nibbles, then high nibbles
+            int al = 0, ah = 0;
+#pragma unroll
+            for (int i4 = 0; i4 < 2; ++i4) {
+              const uint4 l4 = xl[2 * hn + i4], h4 = xh[2 * hn + i4];
+              const int c0 = (int)((qw[4 * i4 + 0] >> (4 * hn)) & 0x0F0F0F0Fu), c1 = (int)((qw[4 * i4 + 1] >> (4 * hn)) & 0x0F0F0F0Fu),
+                        c2 = (int)((qw[4 * i4 + 2] >> (4 * hn)) & 0x0F0F0F0Fu), c3 = (int)((qw[4 * i4 + 3] >> (4 * hn)) & 0x0F0F0F0Fu);
+              al = __dp4a(c0, (int)l4.x, al); ah = __dp4a(c0, (int)h4.x, ah);
+              al = __dp4a(c1, (int)l4.y, al); ah = __dp4a(c1, (int)h4.y, ah);
+              al = __dp4a(c2, (int)l4.z, al); ah = __dp4a(c2, (int)h4.z, ah);
+              al = __dp4a(c3, (int)l4.w, al); ah = __dp4a(c3, (int)h4.w, ah);
+            }
+            v[hn] = ah * 256 + al;
+          }
+          uint32_t scp, mp;
+          q4k_scale_min_pair(hdr.y, hdr.z, hdr.w, j, scp, mp);
+          const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
+          const float sx0 = (float)(s16[0] + s16[1]), sx1 = (float)(s16[2] + s16[3]);
+          const float part = d * ((float)(scp & 0xFFu) * (float)v[0] + (float)(scp >> 8) * (float)v[1]) -
+                             dmin * ((float)(mp & 0xFFu) * sx0 + (float)(mp >> 8) * sx1);
+          acc = fmaf(s_xsc[chunk], part, acc);
+        }
+      } else if (q < RPG) {
         for (int hb = u4; hb < n_hb; hb += 4) {
           const int b = hb >> 1, h = hb & 1, chunk = chunk0 + hb;
           const uint32_t ro = (uint32_t)(row0 + q) * row_bytes_s + (uint32_t)b * Q6K_BLOCK_BYTES;
@@ -425,21 +463,21 @@ int pick_chunks(int ne, int nff, int sh_ff) {
   return 0;
 }
 
-size_t down_smem(int TI, int nff, int sh_ff, int n_used) {
-  const size_t slab = align_up((size_t)TI * (nff / 256 * Q6K_BLOCK_BYTES) + 8, 128) + 128;
-  const size_t sh_slab = sh_ff ? align_up((size_t)TI * (sh_ff / 256 * Q6K_BLOCK_BYTES) + 8, 128) + 128 : 0;
+size_t down_smem(int TI, int nff, int sh_ff, int n_used, size_t dbb) {
+  const size_t slab = align_up((size_t)TI * (nff / 256 * dbb) + 8, 128) + 128;
+  const size_t sh_slab = sh_ff ? align_up((size_t)TI * (sh_ff / 256 * dbb) + 8, 128) + 128 : 0;
   const size_t n_act = (size_t)n_used * nff + sh_ff;
   return 128 + (size_t)n_used * slab + sh_slab + (n_act / 128) * (2 * DN_XPITCH * 4 + 4 + 32) + (size_t)(n_used + 1) * TI * sizeof(float);
 }
 
 // TI rows per CTA: bulk copies need TI * row_bytes to be a multiple of 16 for both banks.
-int pick_down_tile(int ne, int nff, int sh_ff, int n_used) {
+int pick_down_tile(int ne, int nff, int sh_ff, int n_used, size_t dbb) {
   const int cands[] = {16, 8, 4};
   for (int TI : cands) {
     if (ne % TI) continue;
-    if (((size_t)TI * (nff / 256) * Q6K_BLOCK_BYTES) % 16) continue;
-    if (sh_ff && ((size_t)TI * (sh_ff / 256) * Q6K_BLOCK_BYTES) % 16) continue;
-    if (down_smem(TI, nff, sh_ff, n_used) <= 200 * 1024) return TI;
+    if (((size_t)TI * (nff / 256) * dbb) % 16) continue;
+    if (sh_ff && ((size_t)TI * (sh_ff / 256) * dbb) % 16) continue;
+    if (down_smem(TI, nff, sh_ff, n_used, dbb) <= 200 * 1024) return TI;
   }
   return 0;
 }
@@ -461,7 +499,7 @@ cudaError_t launch_ex(K kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t
 
 }  // namespace
 
-bool decode_ffn_supported(const infr_cuda_ctx*, int ne, int nff, int sh_ff, int n_used, std::string* why) {
+bool decode_ffn_supported(const infr_cuda_ctx*, int ne, int nff, int sh_ff, int n_used, bool down_q4k, std::string* why) {
   if (ne % 256 || nff % 256 || (sh_ff % 256)) {
     if (why) *why = "small-m path: ne, n_ff_exp and sh_ff must be multiples of 256";
     return false;
@@ -474,7 +512,7 @@ bool decode_ffn_supported(const infr_cuda_ctx*, int ne, int nff, int sh_ff, int 
     if (why) *why = "small-m path: n_used larger than 32 is not covered";
     return false;
   }
-  if (!pick_chunks(ne, nff, sh_ff) || !pick_down_tile(ne, nff, sh_ff, n_used)) {
+  if (!pick_chunks(ne, nff, sh_ff) || !pick_down_tile(ne, nff, sh_ff, n_used, down_q4k ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES)) {
     if (why) *why = "small-m path: tile does not fit shared memory for these dims";
     return false;
   }
@@ -485,7 +523,8 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, u
   const bool has_sh = p.sh_gate != nullptr;
   const int sh_ff = has_sh ? p.sh_ff : 0;
   const int n_chunks = pick_chunks(p.ne, p.nff, sh_ff);
-  const int TI = pick_down_tile(p.ne, p.nff, sh_ff, p.n_used);
+  const size_t dbb = p.down_q4k ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES;
+  const int TI = pick_down_tile(p.ne, p.nff, sh_ff, p.n_used, dbb);
   if (!n_chunks || !TI) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "small-m path: tile does not fit shared memory");
   const int TR = GU_WARPS * n_chunks;
   const int jobs = p.rows * p.n_used * (p.nff / TR) + (has_sh ? p.rows * (sh_ff / TR) : 0);
@@ -514,7 +553,7 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, u
   }
   if (!(stages & 4u)) return INFR_CUDA_OK;
 
-  const size_t smem_dn = down_smem(TI, p.nff, sh_ff, p.n_used);
+  const size_t smem_dn = down_smem(TI, p.nff, sh_ff, p.n_used, dbb);
   e = ensure_smem(reinterpret_cast<const void*>(k_decode_down), smem_dn);
   if (e != cudaSuccess) return check_cuda(ctx, e, "k_decode_down smem attribute");
   // one warp per (slot, group of up to 8 rows) when that fits, else the largest divisor

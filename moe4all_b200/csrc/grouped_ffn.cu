@@ -569,6 +569,8 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   const int n_seg = c.n_expert + (c.shared_rows > 0 ? 1 : 0);
   const int rows_total = c.rows_bound;  // upper bound on sorted rows + shared rows
   const bool use_umma = !c.legacy && umma_grouped_supported(c.ne, c.nff);
+  if (c.down_q4k && !use_umma)
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "grouped GEMM: Q4_K down banks need the tcgen05 tiles (ne, n_ff_exp multiples of 256, not path 3)");
   const int tn = use_umma ? umma_tile_rows() : TN;
   const int max_tiles = rows_total / tn + n_seg + 1;
   const int max_tiles_alloc = rows_total / TN + n_seg + 1;
@@ -639,6 +641,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   p.ne = c.ne;
   p.nff = c.nff;
   p.n_expert = c.n_expert;
+  p.down_q4k = c.down_q4k;
   p.status = ctx->status;
   p.trace = ctx->trace;
   p.trace_tile = getenv("INFR_TRACE_TILE") ? atoi(getenv("INFR_TRACE_TILE")) : 0;

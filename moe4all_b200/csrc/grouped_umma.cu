@@ -349,9 +349,14 @@ __device__ __forceinline__ uint32_t ldg_u32_unaligned(const uint8_t* base, size_
   return __funnelshift_r(lo, hi, (uint32_t)(off & 3) * 8);
 }
 
-__global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
+// Q4: the down banks are Q4_K (raw blocks by tiled TMA copies, as in the gate/up kernel) instead of Q6_K.
+template <bool Q4>
+__global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p, const __grid_constant__ CUtensorMap tm_down,
+                                                           const __grid_constant__ CUtensorMap tm_sh_down) {
+  constexpr int SB = Q4 ? 2 : DN_SB;  // the Q4_K form gives one token stage to its raw-block staging area
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) PipeBars bars;
+  __shared__ __align__(8) uint64_t s_raw_full;
   __shared__ uint32_t s_tmem;
   const int tile = blockIdx.y;
   if (tile >= *p.n_tiles) return;
@@ -362,10 +367,13 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
   const int n_eff = (rows_valid + 15) & ~15;
   const int i0 = blockIdx.x * DM;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int drb = p.nff / 256 * (int)Q6K_BLOCK_BYTES;
+  const int drb = p.nff / 256 * (int)(Q4 ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES);
   const bool shared_seg = e >= p.n_expert;
 
-  if (tid == 0) init_bars<DN_SA, DN_SB>(bars);
+  if (tid == 0) {
+    mbar_init(&s_raw_full, 1);
+    init_bars<DN_SA, SB>(bars);
+  }
   if (warp == U_PRODUCERS / 32) umma::tmem_alloc(&s_tmem, 512);
   umma::fence_before_sync();
   __syncthreads();
@@ -380,58 +388,6 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
   const uint32_t idesc = umma::idesc_f16_f32(128, DM);  // 128 tokens x 256 output features
   const int n_m = (rows_valid + 127) >> 7;
 
-  // Raw words of one half-block (128 elements = two K steps: low nibbles first, high nibbles
-  // second) per pass: ql words of quadrants 0|2 and 1|3, the qh word, the eight scales, d.
-  // The next half-block is fetched while the current one is unpacked.
-  constexpr int PS = DM * 8 / U_PRODUCERS;  // passes over the tile's rows
-  uint32_t nxt[PS][6], cur[PS][6];
-  const int n_pairs = p.nff / 128;
-  auto fetch_pair = [&](int pair) {
-    const int blk = pair >> 1, h = pair & 1;
-#pragma unroll
-    for (int ps = 0; ps < PS; ++ps) {
-      const size_t bo = (size_t)(i0 + ps * (U_PRODUCERS / 8) + g8) * drb + (size_t)blk * Q6K_BLOCK_BYTES;
-      nxt[ps][0] = ldg_u32_unaligned(wbase, bo + 64 * h + 4 * w);
-      nxt[ps][1] = ldg_u32_unaligned(wbase, bo + 64 * h + 32 + 4 * w);
-      nxt[ps][2] = ldg_u32_unaligned(wbase, bo + 128 + 32 * h + 4 * w);
-      nxt[ps][3] = ldg_u32_unaligned(wbase, bo + 192 + 8 * h);
-      nxt[ps][4] = ldg_u32_unaligned(wbase, bo + 196 + 8 * h);
-      nxt[ps][5] = __ldg(reinterpret_cast<const unsigned short*>(wbase + bo + 208));
-    }
-  };
-  if (tid < U_PRODUCERS) fetch_pair(0);
-
-  auto unpack = [&](unsigned char* st, int step, auto) -> bool {
-    unsigned char* tA = st;
-    const int hi_nib = step & 1;
-    if (hi_nib == 0) {
-#pragma unroll
-      for (int ps = 0; ps < PS; ++ps)
-#pragma unroll
-        for (int i = 0; i < 6; ++i) cur[ps][i] = nxt[ps][i];
-      if ((step >> 1) + 1 < n_pairs) fetch_pair((step >> 1) + 1);
-    }
-#pragma unroll
-    for (int ps = 0; ps < PS; ++ps) {
-      const int row = ps * (U_PRODUCERS / 8) + g8;
-      const float d = f16_bits_to_f32(cur[ps][5]) * W_PRESCALE;
-      // scale of quadrant qd for these l: byte 2*qd + (w >> 2) of the half's eight scale bytes
-      const uint32_t sc4 = __byte_perm(cur[ps][3], cur[ps][4], (w >> 2) ? 0x7531u : 0x6420u);
-#pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        const int qd = 2 * hi_nib + part;
-        const uint32_t L = cur[ps][part];
-        const uint32_t nib = hi_nib ? (L >> 4) : L;
-        const uint32_t code = (nib & 0x0F0F0F0Fu) | (((cur[ps][2] >> (2 * qd)) << 4) & 0x30303030u);
-        const float sc = (float)(int)(signed char)((sc4 >> (8 * qd)) & 0xFFu);
-        uint32_t o02, o13;
-        q6_word_to_h2(code, __float2half2_rn(d * sc), o02, o13);
-        // K position inside the step: 32*part + 4w .. +3  ->  chunk 4*part + w/2, half-chunk w&1
-        *reinterpret_cast<uint2*>(tA + umma::swz128_offset(row, 4 * part + (w >> 1)) + (w & 1) * 8) = make_uint2(o02, o13);
-      }
-    }
-    return true;
-  };
   auto issue = [&](unsigned char* st, unsigned char* tB, int step) {
     const uint64_t dw = umma::smem_desc_k_major_swz128(st, 0), dt = umma::smem_desc_k_major_swz128(tB, 0);
     for (int m = 0; m < n_m; ++m) {
@@ -444,9 +400,113 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p) {
   const int k_steps = p.nff / UK;
   unsigned long long* trc = (blockIdx.x == 0 && blockIdx.y == p.trace_tile) ? p.trace : nullptr;
   trace_stamp(trc, 45);
-  bool ok = run_pipeline<DN_SA, DN_SB>(bars, a_stages, DN_W_STAGE_BYTES, b_stages,
-                                       reinterpret_cast<const unsigned char*>(p.act) + tile_step_offset(tile, k_steps, 0),
-                                       (size_t)UN * 128, (uint32_t)n_eff * 128u, k_steps, unpack, issue, nullptr);
+  bool ok;
+  const unsigned char* tok_src = reinterpret_cast<const unsigned char*>(p.act) + tile_step_offset(tile, k_steps, 0);
+  if constexpr (Q4) {
+    // two threads share a weight row; thread `hh` takes code words 4 hh .. 4 hh + 3 of every 32-byte
+    // run.  Raw blocks (144 B of each of the 256 rows) arrive by one tiled copy, a block ahead.
+    const int wrow = tid & 255, hh = (tid >> 8) & 1;
+    unsigned char* raw = b_stages + SB * B_TILE_BYTES;
+    const unsigned char* my_raw = raw + (size_t)wrow * Q4K_BLOCK_BYTES;
+    const CUtensorMap* tmd = shared_seg ? &tm_sh_down : &tm_down;
+    const int bank_row0 = (shared_seg ? 0 : e * p.ne) + i0;
+    auto request_block = [&](int blk) {
+      if (tid == 0) {
+        mbar_arrive_expect_tx(&s_raw_full, DM * (uint32_t)Q4K_BLOCK_BYTES);
+        tma_load_2d(raw, tmd, blk * (int)Q4K_BLOCK_BYTES, bank_row0, &s_raw_full);
+      }
+    };
+    if (tid < U_PRODUCERS) request_block(0);
+    uint4 cur_h, cur_q[4];
+    auto unpack = [&](unsigned char* tA, int step, auto jc) -> bool {
+      constexpr int j = decltype(jc)::value;
+      if (j == 0) {
+        const int blk = step >> 2;
+        if (!mbar_wait_bounded(&s_raw_full, blk & 1)) return false;
+        cur_h = *reinterpret_cast<const uint4*>(my_raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cur_q[i] = *reinterpret_cast<const uint4*>(my_raw + 16 + 32 * i + 16 * hh);
+        asm volatile("bar.sync 1, %0;" ::"n"(U_PRODUCERS) : "memory");  // every producer has taken its row
+        if (blk + 1 < p.nff / 256) request_block(blk + 1);
+      }
+      const uint4 ch = cur_h, cq = cur_q[j];
+      uint32_t scp, mp;
+      q4k_scale_min_pair(ch.y, ch.z, ch.w, j, scp, mp);
+      const float d = f16_bits_to_f32(ch.x) * W_PRESCALE, dmin = f16_bits_to_f32(ch.x >> 16) * W_PRESCALE;
+      const __half2 s_lo = __float2half2_rn(d * (float)(scp & 0xFFu)), s_hi = __float2half2_rn(d * (float)(scp >> 8));
+      const __half2 m_lo = __float2half2_rn(-dmin * (float)(mp & 0xFFu)), m_hi = __float2half2_rn(-dmin * (float)(mp >> 8));
+      const uint32_t w4[4] = {cq.x, cq.y, cq.z, cq.w};
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * hh + cc;
+        uint4 lo, hi;
+        q4_word_to_h2(w4[2 * cc], s_lo, m_lo, lo.x, lo.y);
+        q4_word_to_h2(w4[2 * cc + 1], s_lo, m_lo, lo.z, lo.w);
+        q4_word_to_h2(w4[2 * cc] >> 4, s_hi, m_hi, hi.x, hi.y);
+        q4_word_to_h2(w4[2 * cc + 1] >> 4, s_hi, m_hi, hi.z, hi.w);
+        *reinterpret_cast<uint4*>(tA + umma::swz128_offset(wrow, c)) = lo;
+        *reinterpret_cast<uint4*>(tA + umma::swz128_offset(wrow, 4 + c)) = hi;
+      }
+      return true;
+    };
+    ok = run_pipeline<DN_SA, SB>(bars, a_stages, DN_W_STAGE_BYTES, b_stages, tok_src, (size_t)UN * 128, (uint32_t)n_eff * 128u, k_steps,
+                                 unpack, issue, nullptr);
+  } else {
+    // Raw words of one half-block (128 elements = two K steps: low nibbles first, high nibbles
+    // second) per pass: ql words of quadrants 0|2 and 1|3, the qh word, the eight scales, d.
+    // The next half-block is fetched while the current one is unpacked.
+    constexpr int PS = DM * 8 / U_PRODUCERS;  // passes over the tile's rows
+    uint32_t nxt[PS][6], cur[PS][6];
+    const int n_pairs = p.nff / 128;
+    auto fetch_pair = [&](int pair) {
+      const int blk = pair >> 1, h = pair & 1;
+  #pragma unroll
+      for (int ps = 0; ps < PS; ++ps) {
+        const size_t bo = (size_t)(i0 + ps * (U_PRODUCERS / 8) + g8) * drb + (size_t)blk * Q6K_BLOCK_BYTES;
+        nxt[ps][0] = ldg_u32_unaligned(wbase, bo + 64 * h + 4 * w);
+        nxt[ps][1] = ldg_u32_unaligned(wbase, bo + 64 * h + 32 + 4 * w);
+        nxt[ps][2] = ldg_u32_unaligned(wbase, bo + 128 + 32 * h + 4 * w);
+        nxt[ps][3] = ldg_u32_unaligned(wbase, bo + 192 + 8 * h);
+        nxt[ps][4] = ldg_u32_unaligned(wbase, bo + 196 + 8 * h);
+        nxt[ps][5] = __ldg(reinterpret_cast<const unsigned short*>(wbase + bo + 208));
+      }
+    };
+    if (tid < U_PRODUCERS) fetch_pair(0);
+
+    auto unpack = [&](unsigned char* st, int step, auto) -> bool {
+      unsigned char* tA = st;
+      const int hi_nib = step & 1;
+      if (hi_nib == 0) {
+  #pragma unroll
+        for (int ps = 0; ps < PS; ++ps)
+  #pragma unroll
+          for (int i = 0; i < 6; ++i) cur[ps][i] = nxt[ps][i];
+        if ((step >> 1) + 1 < n_pairs) fetch_pair((step >> 1) + 1);
+      }
+  #pragma unroll
+      for (int ps = 0; ps < PS; ++ps) {
+        const int row = ps * (U_PRODUCERS / 8) + g8;
+        const float d = f16_bits_to_f32(cur[ps][5]) * W_PRESCALE;
+        // scale of quadrant qd for these l: byte 2*qd + (w >> 2) of the half's eight scale bytes
+        const uint32_t sc4 = __byte_perm(cur[ps][3], cur[ps][4], (w >> 2) ? 0x7531u : 0x6420u);
+  #pragma unroll
+        for (int part = 0; part < 2; ++part) {
+          const int qd = 2 * hi_nib + part;
+          const uint32_t L = cur[ps][part];
+          const uint32_t nib = hi_nib ? (L >> 4) : L;
+          const uint32_t code = (nib & 0x0F0F0F0Fu) | (((cur[ps][2] >> (2 * qd)) << 4) & 0x30303030u);
+          const float sc = (float)(int)(signed char)((sc4 >> (8 * qd)) & 0xFFu);
+          uint32_t o02, o13;
+          q6_word_to_h2(code, __float2half2_rn(d * sc), o02, o13);
+          // K position inside the step: 32*part + 4w .. +3  ->  chunk 4*part + w/2, half-chunk w&1
+          *reinterpret_cast<uint2*>(tA + umma::swz128_offset(row, 4 * part + (w >> 1)) + (w & 1) * 8) = make_uint2(o02, o13);
+        }
+      }
+      return true;
+    };
+    ok = run_pipeline<DN_SA, SB>(bars, a_stages, DN_W_STAGE_BYTES, b_stages, tok_src, (size_t)UN * 128, (uint32_t)n_eff * 128u, k_steps,
+                                 unpack, issue, nullptr);
+  }
   trace_stamp(trc, 46);
 
   // epilogue: a thread's accumulator row is a token, its 128 columns of this warp's feature half
@@ -506,13 +566,13 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// A Q4_K bank as a 2-D byte tensor [rows][row_bytes]; box = one block (144 B) of 128 rows.
-bool q4k_rows_map(CUtensorMap* tm, const uint8_t* base, size_t n_rows, size_t row_bytes) {
+// A Q4_K bank as a 2-D byte tensor [rows][row_bytes]; box = one block (144 B) of `box_rows` rows.
+bool q4k_rows_map(CUtensorMap* tm, const uint8_t* base, size_t n_rows, size_t row_bytes, int box_rows) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_rows};
   const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-  const cuuint32_t box[2] = {(cuuint32_t)Q4K_BLOCK_BYTES, (cuuint32_t)UM};
+  const cuuint32_t box[2] = {(cuuint32_t)Q4K_BLOCK_BYTES, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   return enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -522,21 +582,35 @@ bool q4k_rows_map(CUtensorMap* tm, const uint8_t* base, size_t n_rows, size_t ro
 
 int32_t launch_umma_grouped(infr_cuda_ctx* ctx, const GroupedParams& p, int max_tiles) {
   const size_t smem_gu = 1024 + (size_t)GU_SA * GU_A_STAGE_BYTES + (size_t)GU_SB * B_TILE_BYTES + (size_t)2 * UM * Q4K_BLOCK_BYTES;
-  const size_t smem_dn = 1024 + (size_t)DN_SA * DN_W_STAGE_BYTES + (size_t)DN_SB * B_TILE_BYTES;
+  const size_t smem_dn = 1024 + (size_t)DN_SA * DN_W_STAGE_BYTES +
+                         (p.down_q4k ? (size_t)2 * B_TILE_BYTES + (size_t)DM * Q4K_BLOCK_BYTES : (size_t)DN_SB * B_TILE_BYTES);
   cudaError_t e = ensure_smem(reinterpret_cast<const void*>(k_umma_gateup), smem_gu);
-  if (e == cudaSuccess) e = ensure_smem(reinterpret_cast<const void*>(k_umma_down), smem_dn);
+  if (e == cudaSuccess)
+    e = p.down_q4k ? ensure_smem(reinterpret_cast<const void*>(k_umma_down<true>), smem_dn)
+                   : ensure_smem(reinterpret_cast<const void*>(k_umma_down<false>), smem_dn);
   if (e != cudaSuccess) return check_cuda(ctx, e, "umma grouped smem attribute");
   const size_t rb = (size_t)p.ne / 256 * Q4K_BLOCK_BYTES;
-  CUtensorMap tm_gate, tm_up, tm_sh_gate, tm_sh_up;
-  bool ok = q4k_rows_map(&tm_gate, p.gate, (size_t)p.n_expert * p.nff, rb) && q4k_rows_map(&tm_up, p.up, (size_t)p.n_expert * p.nff, rb);
-  if (ok && p.sh_gate) ok = q4k_rows_map(&tm_sh_gate, p.sh_gate, (size_t)p.nff, rb) && q4k_rows_map(&tm_sh_up, p.sh_up, (size_t)p.nff, rb);
-  if (!ok) return fail(ctx, INFR_CUDA_ERR_CUDA, "grouped GEMM: the driver refused a tensor map for the expert banks");
+  CUtensorMap tm_gate, tm_up, tm_sh_gate, tm_sh_up, tm_down, tm_sh_down;
+  bool ok = q4k_rows_map(&tm_gate, p.gate, (size_t)p.n_expert * p.nff, rb, UM) && q4k_rows_map(&tm_up, p.up, (size_t)p.n_expert * p.nff, rb, UM);
+  if (ok && p.sh_gate) ok = q4k_rows_map(&tm_sh_gate, p.sh_gate, (size_t)p.nff, rb, UM) && q4k_rows_map(&tm_sh_up, p.sh_up, (size_t)p.nff, rb, UM);
   if (!p.sh_gate) {
     tm_sh_gate = tm_gate;
     tm_sh_up = tm_up;
   }
+  tm_down = tm_gate;  // placeholders when the down banks are Q6_K (that kernel reads them with plain loads)
+  tm_sh_down = tm_gate;
+  if (ok && p.down_q4k) {
+    const size_t drb = (size_t)p.nff / 256 * Q4K_BLOCK_BYTES;
+    ok = q4k_rows_map(&tm_down, p.down, (size_t)p.n_expert * p.ne, drb, DM);
+    tm_sh_down = tm_down;
+    if (ok && p.sh_down) ok = q4k_rows_map(&tm_sh_down, p.sh_down, (size_t)p.ne, drb, DM);
+  }
+  if (!ok) return fail(ctx, INFR_CUDA_ERR_CUDA, "grouped GEMM: the driver refused a tensor map for the expert banks");
   k_umma_gateup<<<dim3(p.nff / UM, max_tiles), U_THREADS, smem_gu, ctx->stream>>>(p, tm_gate, tm_up, tm_sh_gate, tm_sh_up);
-  k_umma_down<<<dim3(p.ne / DM, max_tiles), U_THREADS, smem_dn, ctx->stream>>>(p);
+  if (p.down_q4k)
+    k_umma_down<true><<<dim3(p.ne / DM, max_tiles), U_THREADS, smem_dn, ctx->stream>>>(p, tm_down, tm_sh_down);
+  else
+    k_umma_down<false><<<dim3(p.ne / DM, max_tiles), U_THREADS, smem_dn, ctx->stream>>>(p, tm_down, tm_sh_down);
   ctx->launches += 2;
   return check_cuda(ctx, cudaGetLastError(), "umma grouped launch");
 }

@@ -45,6 +45,7 @@ struct DecodeParams {
   size_t gate_stride, up_stride, down_stride;  // bytes per expert
   int rows, ne, n_used, nff, sh_ff, n_expert;
   uint32_t ep_lo, ep_n;  // band (ep_n == 0: off)
+  int down_q4k;          // the down banks (routed and shared) are Q4_K instead of Q6_K
 };
 
 // Device-side view of one grouped-GEMM launch (see grouped_ffn.cu).
@@ -62,6 +63,7 @@ struct GroupedParams {
   unsigned long long* trace;  // optional phase stamps
   int trace_tile;             // tile whose first CTA writes them
   int ne, nff, n_expert;
+  int down_q4k;               // the down banks are Q4_K instead of Q6_K (tcgen05 kernels only)
 };
 
 // Host-side description of one batched expert-FFN call.
@@ -82,6 +84,7 @@ struct GroupedCall {
   int rows_bound;          // upper bound on grouped rows including the shared segment
   uint32_t ep_lo, ep_n;
   int legacy;              // 1: use the mma.sync tiles even where the tcgen05 kernels apply
+  int down_q4k;            // the down banks are Q4_K instead of Q6_K
 };
 
 bool umma_grouped_supported(int ne, int nff);
@@ -96,7 +99,7 @@ int32_t launch_umma_selftest(infr_cuda_ctx* ctx, const __half* a, const __half* 
 int32_t launch_route(infr_cuda_ctx* ctx, const RouteParams& p, bool pdl);
 int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages);
 // Whether the small-m kernels cover this shape (dims, shared-memory budget).
-bool decode_ffn_supported(const infr_cuda_ctx* ctx, int ne, int nff, int sh_ff, int n_used, std::string* why);
+bool decode_ffn_supported(const infr_cuda_ctx* ctx, int ne, int nff, int sh_ff, int n_used, bool down_q4k, std::string* why);
 
 // y[m, out_f] = x[m, in_f] · Wᵀ for W of dtype F32 / Q4_K / Q6_K.
 int32_t launch_linear(infr_cuda_ctx* ctx, int32_t dtype, const uint8_t* w, const float* x, float* y, int m, int in_f,

@@ -77,10 +77,11 @@ class LayerWeights:
         self.router = self.gate = self.up = self.down = None
         self.sh_gate = self.sh_up = self.sh_down = self.sh_gate_inp = None
         self.bias = None
+        self.down_dtype = 14
 
 
 def make_layer(seed: int, ne: int, n_expert: int, n_ff: int, sh_ff: int = 0, gated_shared: bool = True,
-               router_std: float = 0.02, bias_std: float = 0.0) -> LayerWeights:
+               router_std: float = 0.02, bias_std: float = 0.0, down_q4k: bool = False) -> LayerWeights:
     """One layer in the benchmark configs' distributions: router f32 N(0, 0.02); gate/up Q4_K and
     down Q6_K with random payload and U[1e-4, 1e-3] scales; optional shared expert."""
     rng = np.random.default_rng(seed)
@@ -88,11 +89,12 @@ def make_layer(seed: int, ne: int, n_expert: int, n_ff: int, sh_ff: int = 0, gat
     L.router = rng.normal(0.0, router_std, size=(n_expert, ne)).astype(np.float32)
     L.gate = random_q4k(rng, n_expert * n_ff * ne // QK).reshape(-1)
     L.up = random_q4k(rng, n_expert * n_ff * ne // QK).reshape(-1)
-    L.down = random_q6k(rng, n_expert * ne * n_ff // QK).reshape(-1)
+    L.down_dtype = 12 if down_q4k else 14  # GGUF type numbers: Q4_K, Q6_K (a Q4_K_M file mixes both over its layers)
+    L.down = (random_q4k if down_q4k else random_q6k)(rng, n_expert * ne * n_ff // QK).reshape(-1)
     if sh_ff:
         L.sh_gate = random_q4k(rng, sh_ff * ne // QK).reshape(-1)
         L.sh_up = random_q4k(rng, sh_ff * ne // QK).reshape(-1)
-        L.sh_down = random_q6k(rng, ne * sh_ff // QK).reshape(-1)
+        L.sh_down = (random_q4k if down_q4k else random_q6k)(rng, ne * sh_ff // QK).reshape(-1)
         if gated_shared:
             L.sh_gate_inp = rng.normal(0.0, router_std, size=ne).astype(np.float32)
     if bias_std > 0:

@@ -58,11 +58,11 @@ def layer_to_gguf(path, L, layer=0, arch="qwen35moe", n_used=8, alignment=32, ex
          (p + "ffn_gate_inp.weight", (L.ne, L.n_expert), 0, np.ascontiguousarray(L.router, np.float32).tobytes()),
          (p + "ffn_gate_exps.weight", (L.ne, L.n_ff, L.n_expert), 12, L.gate.tobytes()),
          (p + "ffn_up_exps.weight", (L.ne, L.n_ff, L.n_expert), 12, L.up.tobytes()),
-         (p + "ffn_down_exps.weight", (L.n_ff, L.ne, L.n_expert), 14, L.down.tobytes())]
+         (p + "ffn_down_exps.weight", (L.n_ff, L.ne, L.n_expert), getattr(L, "down_dtype", 14), L.down.tobytes())]
     if L.sh_gate is not None:
         t += [(p + "ffn_gate_shexp.weight", (L.ne, L.sh_ff), 12, L.sh_gate.tobytes()),
               (p + "ffn_up_shexp.weight", (L.ne, L.sh_ff), 12, L.sh_up.tobytes()),
-              (p + "ffn_down_shexp.weight", (L.sh_ff, L.ne), 14, L.sh_down.tobytes())]
+              (p + "ffn_down_shexp.weight", (L.sh_ff, L.ne), getattr(L, "down_dtype", 14), L.sh_down.tobytes())]
         if L.sh_gate_inp is not None:
             t.append((p + "ffn_gate_inp_shexp.weight", (L.ne,), 0, np.ascontiguousarray(L.sh_gate_inp, np.float32).tobytes()))
     if L.bias is not None:

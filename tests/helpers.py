@@ -61,7 +61,7 @@ class GpuLayer:
                     sh_gate=self.sh_gate if use_sh else None, sh_up=self.sh_up if use_sh else None,
                     sh_down=self.sh_down if use_sh else None,
                     sh_gate_inp=self.sh_gate_inp if use_sh else None,
-                    sh_ff=L.sh_ff if use_sh else 0, path=path)
+                    sh_ff=L.sh_ff if use_sh else 0, path=path, down_dtype=DType(getattr(L, "down_dtype", 14)))
         be.moe_ffn(op)
         be.sync()
         out = be.download(dst, np.float32).reshape(rows, L.ne)
@@ -72,7 +72,7 @@ def oracle_layer(L, x, n_used, *, router_x=None, scale=1.0, gating=0, norm_w=Tru
                  groups_used=0, ep_band=None, shared=True, threads=0):
     kw = dict(n_expert=L.n_expert, n_used=n_used, n_ff_exp=L.n_ff, scale=scale, gating=int(gating),
               norm_w=norm_w, bias=L.bias, groups=groups, groups_used=groups_used, ep_band=ep_band,
-              threads=threads, router_x=router_x)
+              threads=threads, router_x=router_x, down_dtype=getattr(L, "down_dtype", 14))
     if shared and L.sh_gate is not None:
         return orc.moe_layer(x, L.router, L.gate, L.up, L.down, L.sh_gate, L.sh_up, L.sh_down,
                              L.sh_gate_inp, L.sh_ff, **kw)

@@ -85,6 +85,18 @@ def test_batched_ep_bands_sum_to_full(backend):
     assert_close(parts[1], oracle_layer(L, x, 4, ep_band=(8, 8)).dst)
 
 
+def test_q4k_down_banks_batched(backend):
+    L = synth.make_layer(62, 1024, 16, 512, sh_ff=512, down_q4k=True, router_std=0.05)
+    x = synth.activations(23, 300, 1024)
+    out, ids, wts = GpuLayer(backend, L).run(x, 4, path=2)
+    ref = oracle_layer(L, x, 4)
+    ties = ids_match(ids, ref, 4)
+    keep = [r for r in range(300) if r not in ties]
+    assert_close(out[keep], ref.dst[keep])
+    with pytest.raises(Exception):
+        GpuLayer(backend, L).run(x, 4, path=3)  # the legacy tiles have no Q4_K down kernel
+
+
 @pytest.mark.parametrize("path", [1, 2])
 def test_deepseek_v3_dims(backend, path):
     # hidden 7168, expert intermediate 2048, sigmoid gating with 8 groups / 4 used, scale 2.5,

@@ -72,6 +72,18 @@ def test_config1_layer_more_rows(backend, rows):
     assert np.array_equal(out_auto, out) and np.array_equal(ids_auto, ids)
 
 
+@pytest.mark.parametrize("rows", [1, 4, 20])
+def test_q4k_down_banks(backend, rows):
+    # a Q4_K_M model file stores most layers' down banks in Q4_K (the rest in Q6_K)
+    L = synth.make_layer(61, 2048, 32, 512, sh_ff=512, down_q4k=True)
+    x = synth.activations(19, rows, 2048)
+    g = GpuLayer(backend, L)
+    out, ids, wts = g.run(x, 8, path=1)
+    ref = oracle_layer(L, x, 8)
+    check_ids(ids, wts, ref, 8)
+    assert_close(out, ref.dst)
+
+
 def test_determinism(backend):
     L = synth.make_layer(3, 2048, 64, 512, sh_ff=512)
     x = synth.activations(9, 4, 2048)
