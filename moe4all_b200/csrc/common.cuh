@@ -264,27 +264,39 @@ __device__ __forceinline__ float q4k_dot64(const uint4& hdr, const uint32_t (&q)
   return (16.f * s0) * (A0 - xs0) - m0 * xs0 + (16.f * s1) * (A1 - xs1) - m1 * xs1;
 }
 
+// Four unsigned bytes of `a` times four signed bytes of `b`, accumulated onto c.
+__device__ __forceinline__ int dp4a_us(unsigned a, int b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
 // Same dot product with the activations in 16-bit fixed point, split into two signed 8-bit limbs
 // (X = 256*hi + lo per element, four elements per word): the nibbles of a code word are masked in
 // place and multiplied with integer dot-product instructions, which keeps the unpack off the
 // (half-rate) logic pipe.  xl/xh: limbs of the 64 elements, sx0/sx1: integer sums of X over the two
 // 32-element sub-blocks.  Returns sum(w * X); the caller multiplies by the fixed-point scale.
 __device__ __forceinline__ float q4k_dot64_i8(const uint4& hdr, const uint32_t (&q)[8], const int (&xl)[16], const int (&xh)[16],
-                                              float sx0, float sx1, int j) {
+                                              int sx0, int sx1, int j) {
   int a_ll = 0, a_lh = 0, a_hl = 0, a_hh = 0;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const int lo4 = (int)(q[i] & 0x0F0F0F0Fu), hi4 = (int)((q[i] >> 4) & 0x0F0F0F0Fu);
-    a_ll = __dp4a(lo4, xl[i], a_ll);
-    a_lh = __dp4a(lo4, xh[i], a_lh);
-    a_hl = __dp4a(hi4, xl[8 + i], a_hl);
-    a_hh = __dp4a(hi4, xh[8 + i], a_hh);
+    // the high nibbles stay in place: as unsigned bytes they are 16 x the code, and the exact
+    // integer sums are divided by 16 afterwards (one mask per word instead of a shift and a mask)
+    const unsigned lo4 = q[i] & 0x0F0F0F0Fu, hi4 = q[i] & 0xF0F0F0F0u;
+    a_ll = dp4a_us(lo4, xl[i], a_ll);
+    a_lh = dp4a_us(lo4, xh[i], a_lh);
+    a_hl = dp4a_us(hi4, xl[8 + i], a_hl);
+    a_hh = dp4a_us(hi4, xh[8 + i], a_hh);
   }
-  const float v0 = (float)(a_lh * 256 + a_ll), v1 = (float)(a_hh * 256 + a_hl);
+  // |v| <= 32 * 15 * 32639 < 2^24 and the 6-bit scales keep the two weighted sums inside int32
+  const int v0 = a_lh * 256 + a_ll, v1 = (a_hh * 256 + a_hl) >> 4;
   uint32_t scp, mp;
   q4k_scale_min_pair(hdr.y, hdr.z, hdr.w, j, scp, mp);
+  const int sv = (int)(scp & 0xFFu) * v0 + (int)(scp >> 8) * v1;
+  const int mv = (int)(mp & 0xFFu) * sx0 + (int)(mp >> 8) * sx1;
   const float d = f16_bits_to_f32(hdr.x), dmin = f16_bits_to_f32(hdr.x >> 16);
-  return d * ((float)(scp & 0xFFu) * v0 + (float)(scp >> 8) * v1) - dmin * ((float)(mp & 0xFFu) * sx0 + (float)(mp >> 8) * sx1);
+  return d * (float)sv - dmin * (float)mv;
 }
 
 #endif  // __CUDACC__

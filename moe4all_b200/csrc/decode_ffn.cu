@@ -127,7 +127,7 @@ __global__ void __maxnreg__(56) k_decode_gateup(DecodeParams p, int n_chunks) {
   __syncthreads();  // limbs staged, barrier init visible to all waiters
   trace_stamp(tr, 18);
   int xl[16], xh[16];
-  float sx0 = 0.f, sx1 = 0.f;
+  int sx0 = 0, sx1 = 0;
   auto load_x = [&](int g) {
     const uint4* src = reinterpret_cast<const uint4*>(s_xq + (size_t)g * GU_XQPITCH);
 #pragma unroll
@@ -142,8 +142,8 @@ __global__ void __maxnreg__(56) k_decode_gateup(DecodeParams p, int n_chunks) {
       l0 = __dp4a(0x01010101, xl[i], l0); h0 = __dp4a(0x01010101, xh[i], h0);
       l1 = __dp4a(0x01010101, xl[8 + i], l1); h1 = __dp4a(0x01010101, xh[8 + i], h1);
     }
-    sx0 = (float)(h0 * 256 + l0);
-    sx1 = (float)(h1 * 256 + l1);
+    sx0 = h0 * 256 + l0;
+    sx1 = h1 * 256 + l1;
   };
   if (NG == 1) {
     if (lane < n_groups) load_x(lane);
