@@ -504,7 +504,7 @@ def run_prefill(args):
         if not deepseek:
             x[:, ne - 1] = 1.0  # expert-parallel layer routes on x itself
         layer = CudaExpertParallelLayer(be, L, n_expert, n_used, n_ff, ne, **{("n_groups" if k == "n_expert_groups" else "n_groups_used" if k == "n_expert_groups_used" else k): v for k, v in route_kw.items()})
-        step = lambda s: layer.forward(x)
+        step = lambda s: layer.forward(x, rows_equal=True)  # small calls take the fixed-shape exchange
     for s in range(W):
         step(s)
     sampler = ClockSampler(local)

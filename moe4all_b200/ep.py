@@ -80,8 +80,43 @@ class ExpertParallel:
         tok = (order[:sum(both[0])] % ids.shape[0]).contiguous()
         return DispatchPlan(tok, both[0], both[1])
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x: this rank's token rows [R, ne] (f32).  Returns the MoE FFN output for those rows."""
+    # every rank must take the same branch: the choice depends on sizes all ranks share
+    static_limit_bytes = 48 << 20
+
+    def forward_static(self, x: torch.Tensor) -> torch.Tensor:
+        """The exchange with fixed shapes, for calls whose rows are few enough to send every row to
+        every rank: no counts, no host synchronisation, nothing whose size depends on the routing.
+        A rank that owns none of a row's experts sees that row with all ids negative and returns
+        zeros for it.  Needs the same number of rows on every rank."""
+        W, k = self.world, self.n_used
+        R, ne = x.shape
+        ids, wts = self.route_fn(x)
+        prepared = self.prepare_fn(x) if self.prepare_fn is not None else None
+        dest = torch.div(ids.clamp(0, self.n_expert - 1), self.e_local, rounding_mode="floor")                # [R, k]
+        ranks = torch.arange(W, device=x.device, dtype=dest.dtype).view(W, 1, 1)
+        ids_w = torch.where(dest.unsqueeze(0) == ranks, ids.unsqueeze(0), torch.full_like(ids, -1).unsqueeze(0))  # [W, R, k]
+        send_m = torch.cat([ids_w.contiguous().view(torch.float32), wts.unsqueeze(0).expand(W, R, k)], 2).reshape(W * R, 2 * k)
+        send_x = x.unsqueeze(0).expand(W, R, ne).reshape(W * R, ne)
+        recv_x = torch.empty_like(send_x)
+        recv_m = torch.empty_like(send_m)
+        self._a2a(recv_x, send_x)
+        self._a2a(recv_m, send_m)
+        part = self.band_fn(recv_x, recv_m[:, :k].contiguous().view(torch.int32), recv_m[:, k:].contiguous())
+        if part.shape != recv_x.shape:
+            raise RuntimeError(f"band_fn returned {tuple(part.shape)} for rows {tuple(recv_x.shape)}")
+        back = torch.empty_like(part)
+        self._a2a(back, part)
+        moe = back.view(W, R, ne)[0].clone()
+        for r in range(1, W):  # rank order
+            moe += back.view(W, R, ne)[r]
+        return self.finish_fn(moe, x) if self.prepare_fn is None else self.finish_fn(moe, x, prepared)
+
+    def forward(self, x: torch.Tensor, rows_equal: bool = False) -> torch.Tensor:
+        """x: this rank's token rows [R, ne] (f32).  Returns the MoE FFN output for those rows.
+        `rows_equal`: the caller vouches that every rank passes the same number of rows, which
+        allows the fixed-shape exchange when it is small enough."""
+        if rows_equal and self.world > 1 and self.world * x.shape[0] * x.shape[1] * 4 <= self.static_limit_bytes:
+            return self.forward_static(x)
         ids, wts = self.route_fn(x)
         prepared = self.prepare_fn(x) if self.prepare_fn is not None else None
         pl = self.plan(ids)
@@ -195,10 +230,10 @@ class CudaExpertParallelLayer:
         self._keep += [moe, out]
         return out
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        # everything queued by the previous call has been ordered before this call's work on the
-        # same stream; the plan's host synchronisation below makes releasing its tensors safe
+    def forward(self, x: torch.Tensor, rows_equal: bool = False) -> torch.Tensor:
+        # tensors of the previous call are released here: the caching allocator hands their
+        # memory out again in stream order, and everything runs on one stream
         keep, self._keep = self._keep, []
-        out = self.ep.forward(x)
+        out = self.ep.forward(x, rows_equal=rows_equal)
         del keep
         return out

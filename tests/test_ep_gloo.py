@@ -42,7 +42,7 @@ def expected(x):
     return (x[:, None, :] * (ids.to(torch.float32) + 1)[..., None] * wts[..., None]).sum(1)
 
 
-def worker(rank, world, port, rows_per_rank, fail_rank, ret):
+def worker(rank, world, port, rows_per_rank, fail_rank, ret, static=False):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -53,7 +53,7 @@ def worker(rank, world, port, rows_per_rank, fail_rank, ret):
             # a rank whose expert function returns the wrong number of rows must raise, not hang
             ep.band_fn = lambda xr, i, w: xr[:-1] if xr.shape[0] else xr.new_zeros(1, xr.shape[1])
         try:
-            out = ep.forward(x)
+            out = ep.forward(x, rows_equal=static)
             ok = torch.allclose(out, expected(x), rtol=1e-5, atol=1e-6)
             ret[rank] = "ok" if ok else "mismatch"
         except RuntimeError as e:
@@ -68,14 +68,19 @@ def free_port():
         return s.getsockname()[1]
 
 
-def run(world, rows_per_rank, fail_rank=-1):
+def run(world, rows_per_rank, fail_rank=-1, static=False):
     ret = mp.Manager().dict()
-    mp.spawn(worker, args=(world, free_port(), rows_per_rank, fail_rank, ret), nprocs=world, join=True)
+    mp.spawn(worker, args=(world, free_port(), rows_per_rank, fail_rank, ret, static), nprocs=world, join=True)
     return dict(ret)
 
 
 def test_ep_world2_matches_direct_sum():
     assert run(2, [37, 5]) == {0: "ok", 1: "ok"}
+
+
+def test_ep_world2_fixed_shape_exchange():
+    # equal rows on every rank: every row goes to every rank, foreign pairs carry negative ids
+    assert run(2, [19, 19], static=True) == {0: "ok", 1: "ok"}
 
 
 def test_ep_world2_with_an_empty_rank():

@@ -38,6 +38,7 @@ def worker(rank, world, port, ret):
             x = x_all[rank * ROWS:(rank + 1) * ROWS].contiguous()
             layer = CudaExpertParallelLayer(be, banded, E, K, NFF, NE)
             out = layer.forward(x)
+            out_static = layer.forward(x, rows_equal=True)  # fixed-shape exchange (world > 1), same sums
             # single-device result for the same rows
             dst = torch.empty_like(x)
             b = full.b
@@ -49,6 +50,7 @@ def worker(rank, world, port, ret):
             ref = dst.cpu().numpy()
             got = out.cpu().numpy()
             rel = float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-3))
+            rel = max(rel, float(np.abs(out_static.cpu().numpy() - ref).max() / max(np.abs(ref).max(), 1e-3)))
             ret[rank] = (rel, float(np.abs(ref).max()))
     finally:
         if world > 1:
