@@ -379,6 +379,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p, con
   __syncthreads();
   umma::fence_after_sync();
   const uint32_t tmem = s_tmem;
+  trace_stamp((blockIdx.x == 0 && blockIdx.y == p.trace_tile) ? p.trace : nullptr, 48);
 
   // producer identity: eight consecutive lanes share a weight row (lane w takes the four l values
   // 4w..4w+3 of every quadrant), so a warp request covers whole 32-byte runs of four rows; the 128
@@ -472,6 +473,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p, con
       }
     };
     if (tid < U_PRODUCERS) fetch_pair(0);
+    trace_stamp(trc, 49);
 
     auto unpack = [&](unsigned char* st, int step, auto) -> bool {
       unsigned char* tA = st;
