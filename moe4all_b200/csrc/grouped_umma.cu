@@ -342,13 +342,6 @@ constexpr int DN_SA = 3, DN_SB = 3;
 constexpr int DM = 256;                                   // output features per CTA
 constexpr uint32_t DN_W_STAGE_BYTES = DM * 128;           // 32 KB
 
-__device__ __forceinline__ uint32_t ldg_u32_unaligned(const uint8_t* base, size_t off) {
-  const size_t a = off & ~(size_t)3;
-  const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(base + a));
-  const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(base + a + 4));
-  return __funnelshift_r(lo, hi, (uint32_t)(off & 3) * 8);
-}
-
 // Q4: the down banks are Q4_K (raw blocks by tiled TMA copies, as in the gate/up kernel) instead of Q6_K.
 template <bool Q4>
 __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p, const __grid_constant__ CUtensorMap tm_down,
@@ -454,24 +447,36 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p, con
                                  unpack, issue, nullptr);
   } else {
     // Raw words of one half-block (128 elements = two K steps: low nibbles first, high nibbles
-    // second) per pass: ql words of quadrants 0|2 and 1|3, the qh word, the eight scales, d.
-    // The next half-block is fetched while the current one is unpacked.
+    // second) per pass, fetched while the previous half-block is unpacked.  Q6_K blocks are only
+    // 2-byte aligned, so the words a lane needs straddle two aligned words; the loads stay plain
+    // aligned loads with nothing computed on them (so nothing waits for them at issue time), and
+    // the realignment happens at unpack time: the upper word comes from the neighbouring lane of
+    // the row's eight (shuffle), the words beyond the eighth and the scales / d from six spare
+    // loads spread over lanes 0-5.  Four loads per lane and pass instead of eleven.
     constexpr int PS = DM * 8 / U_PRODUCERS;  // passes over the tile's rows
-    uint32_t nxt[PS][6], cur[PS][6];
+    uint32_t nxt[PS][4], cur[PS][6];
     const int n_pairs = p.nff / 128;
     auto fetch_pair = [&](int pair) {
       const int blk = pair >> 1, h = pair & 1;
+      // lane's spare word: scales (3 words), d, ql word 16 of this half, qh word 8 of this half
+      const int spare = w == 0 ? 192 + 8 * h : w == 1 ? 196 + 8 * h : w == 2 ? 200 + 8 * h : w == 3 ? 208 : w == 4 ? 64 * h + 64 : 160 + 32 * h;
   #pragma unroll
       for (int ps = 0; ps < PS; ++ps) {
         const size_t bo = (size_t)(i0 + ps * (U_PRODUCERS / 8) + g8) * drb + (size_t)blk * Q6K_BLOCK_BYTES;
-        nxt[ps][0] = ldg_u32_unaligned(wbase, bo + 64 * h + 4 * w);
-        nxt[ps][1] = ldg_u32_unaligned(wbase, bo + 64 * h + 32 + 4 * w);
-        nxt[ps][2] = ldg_u32_unaligned(wbase, bo + 128 + 32 * h + 4 * w);
-        nxt[ps][3] = ldg_u32_unaligned(wbase, bo + 192 + 8 * h);
-        nxt[ps][4] = ldg_u32_unaligned(wbase, bo + 196 + 8 * h);
-        nxt[ps][5] = __ldg(reinterpret_cast<const unsigned short*>(wbase + bo + 208));
+        const uint8_t* ab = wbase + (bo & ~(size_t)3);
+        nxt[ps][0] = __ldg(reinterpret_cast<const uint32_t*>(ab + 64 * h + 4 * w));
+        nxt[ps][1] = __ldg(reinterpret_cast<const uint32_t*>(ab + 64 * h + 32 + 4 * w));
+        nxt[ps][2] = __ldg(reinterpret_cast<const uint32_t*>(ab + 128 + 32 * h + 4 * w));
+        nxt[ps][3] = w < 6 ? __ldg(reinterpret_cast<const uint32_t*>(ab + spare)) : 0u;
       }
     };
+    // the CTA's 256 weight rows are one contiguous range: ask for it in L2 up front, so that the
+    // small per-lane loads below find it there instead of each waiting for DRAM
+    if (tid == U_PRODUCERS + 32) {
+      const uint8_t* slab = wbase + (size_t)i0 * drb;
+      const size_t total = (size_t)DM * drb;  // a multiple of 16: DM = 256 rows of 210-byte blocks
+      for (size_t off = 0; off < total; off += 32768) bulk_prefetch_l2(slab + off, (uint32_t)(total - off < 32768 ? total - off : 32768));
+    }
     if (tid < U_PRODUCERS) fetch_pair(0);
     trace_stamp(trc, 49);
 
@@ -479,10 +484,25 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p, con
       unsigned char* tA = st;
       const int hi_nib = step & 1;
       if (hi_nib == 0) {
+        const int blk = step >> 2;
   #pragma unroll
-        for (int ps = 0; ps < PS; ++ps)
-  #pragma unroll
-          for (int i = 0; i < 6; ++i) cur[ps][i] = nxt[ps][i];
+        for (int ps = 0; ps < PS; ++ps) {
+          const uint32_t sh = (uint32_t)((((size_t)(i0 + ps * (U_PRODUCERS / 8) + g8) * drb + (size_t)blk * Q6K_BLOCK_BYTES) & 3) * 8);
+          const uint32_t a0 = nxt[ps][0], b0 = nxt[ps][1], h0 = nxt[ps][2], sp = nxt[ps][3];
+          // the next aligned word: from the lane to the right; for the eighth lane ql's second run
+          // starts where the first ends, the other two continue in spare words
+          const uint32_t a_r = __shfl_down_sync(0xFFFFFFFFu, a0, 1, 8), b_r = __shfl_down_sync(0xFFFFFFFFu, b0, 1, 8),
+                         h_r = __shfl_down_sync(0xFFFFFFFFu, h0, 1, 8);
+          const uint32_t b_first = __shfl_sync(0xFFFFFFFFu, b0, 0, 8);
+          const uint32_t s0 = __shfl_sync(0xFFFFFFFFu, sp, 0, 8), s1 = __shfl_sync(0xFFFFFFFFu, sp, 1, 8), s2 = __shfl_sync(0xFFFFFFFFu, sp, 2, 8),
+                         dw = __shfl_sync(0xFFFFFFFFu, sp, 3, 8), b_8 = __shfl_sync(0xFFFFFFFFu, sp, 4, 8), h_8 = __shfl_sync(0xFFFFFFFFu, sp, 5, 8);
+          cur[ps][0] = __funnelshift_r(a0, w == 7 ? b_first : a_r, sh);
+          cur[ps][1] = __funnelshift_r(b0, w == 7 ? b_8 : b_r, sh);
+          cur[ps][2] = __funnelshift_r(h0, w == 7 ? h_8 : h_r, sh);
+          cur[ps][3] = __funnelshift_r(s0, s1, sh);
+          cur[ps][4] = __funnelshift_r(s1, s2, sh);
+          cur[ps][5] = (dw >> sh) & 0xFFFFu;
+        }
         if ((step >> 1) + 1 < n_pairs) fetch_pair((step >> 1) + 1);
       }
   #pragma unroll
