@@ -427,6 +427,7 @@ Scratch carve(void* base, const infr_cuda_moe_ffn_desc* d, bool with_act) {
 
 RouteParams route_params(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, const Scratch& s, bool with_gate) {
   RouteParams rp = {};
+  rp.status = ctx->status;
   rp.router_x = static_cast<const float*>(d->router_x->ptr);
   rp.x = d->x ? static_cast<const float*>(d->x->ptr) : rp.router_x;
   rp.router = static_cast<const float*>(d->router->ptr);

@@ -20,6 +20,7 @@ struct RouteParams {
   int32_t* ids;              // [rows, n_used]
   float* wts;                // [rows, n_used]
   unsigned int* counter;     // zero on entry, zero on exit
+  DeviceStatus* status;      // bounded waits that ran out are recorded here
   int8_t *xq_lo, *xq_hi;     // [rows, ne] fixed-point limbs of x for the small-m expert kernels, or null
   float* xscale;             // [rows] value of one fixed-point unit
   unsigned long long* trace; // optional phase stamps

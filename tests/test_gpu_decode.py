@@ -106,6 +106,23 @@ def test_grouped_sigmoid_bias_routing(backend):
     assert_close(out, ref.dst)
 
 
+@pytest.mark.parametrize("rows", [1, 8])
+def test_wide_logit_range(backend, rows):
+    # logits spread over hundreds of units: most softmax terms are denormal or zero, which takes the
+    # selection off its fast division and onto the full-range one
+    L = synth.make_layer(31, 256, 64, 256, router_std=2.0)
+    x = synth.activations(33, rows, 256)
+    g = GpuLayer(backend, L)
+    out, ids, wts = g.run(x, 4)
+    ref = oracle_layer(L, x, 4)
+    lg = x @ L.router.reshape(64, 256).T
+    assert (lg.max(1) - lg.min(1)).min() > 110, "the case does not reach the denormal range"
+    for r in range(rows):
+        assert ids[r].tolist() == ref.ids[r].tolist()
+        np.testing.assert_allclose(wts[r], ref.wts[r], rtol=2e-6, atol=1e-12)
+    assert_close(out, ref.dst)
+
+
 def test_ep_band_partials_sum_to_full(backend):
     # Op::MoeFfn::ep_band: the per-band partial outputs add up to the unbanded output
     L = synth.make_layer(8, 1024, 32, 256)
