@@ -42,6 +42,9 @@ extern "C" {
 /* MoeGating (crates/infr-core/src/graph.rs:73-85). */
 #define INFR_CUDA_GATING_SOFTMAX 0
 #define INFR_CUDA_GATING_SIGMOID 1
+#define INFR_CUDA_ACT_SILU 0 /* g / (1 + exp(-g)) */
+#define INFR_CUDA_ACT_GELU 1 /* 0.5 g (1 + tanh(0.7978846 (g + 0.044715 g^3))), kernels.rs:6664-6669 */
+#define INFR_CUDA_GATING_SQRT_SOFTPLUS 2 /* sqrt(ln(1 + exp(v))), v itself above 20 (infr-cpu lib.rs:3760-3774) */
 
 typedef struct infr_cuda_ctx infr_cuda_ctx; /* opaque: device, stream, scratch */
 typedef struct infr_cuda_buf infr_cuda_buf; /* opaque: one device allocation, owned by the caller */
@@ -148,6 +151,23 @@ typedef struct infr_cuda_moe_ffn_desc {
                                        passes the ids it received with stages = 14) and the
                                        context's scratch.  A negative id marks a pair that is not
                                        this call's to serve; it contributes nothing.               */
+  const infr_cuda_buf* expert_ids;  /* Op::MoeFfn::expert_ids (graph.rs:1320-1351, hash-routed layers):
+                                       [rows, n_used] i32 experts chosen by the caller.  Only the
+                                       selection is bypassed: the router and the gating function
+                                       still run and the weights are the router's own probabilities
+                                       at these experts (then norm_w and scale).  Refused together
+                                       with exp_probs_b or expert groups.  An id outside
+                                       [0, n_expert) is reported through infr_cuda_status
+                                       (bad_index) and served as expert 0.  NULL = top-k routing.  */
+  const infr_cuda_buf* down_scale;  /* Op::MoeFfn::down_scale (graph.rs:1273-1276): [n_expert] f32 on the
+                                       selected expert's down output before the weighted sum
+                                       (y = raw * scale[e], then w * y); NULL = none                */
+  uint32_t act;                     /* INFR_CUDA_ACT_*: activation of the routed and shared experts */
+  uint32_t weight_before;           /* routing weight applied to gate and up before the activation
+                                       instead of to the expert's output (llama4, graph.rs:1298-1303) */
+  float swiglu_clamp;               /* > 0: routed experts compute act(min(gate, l)) * clamp(up, -l, l)
+                                       (graph.rs:1283-1290, kernels.rs:6671-6683); 0 = off; refused
+                                       together with weight_before, as in the reference            */
 } infr_cuda_moe_ffn_desc;
 
 /* Backend::execute of a graph holding one Op::MoeFfn (backend.rs:908; CPU arm

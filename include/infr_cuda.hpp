@@ -41,7 +41,12 @@ struct Result {
 // crates/infr-core/src/tensor.rs:7-57, numbered as in the GGUF file format.
 enum class DType : int32_t { F32 = INFR_CUDA_DT_F32, Q4K = INFR_CUDA_DT_Q4K, Q6K = INFR_CUDA_DT_Q6K };
 // crates/infr-core/src/graph.rs:73-85
-enum class MoeGating : uint32_t { Softmax = INFR_CUDA_GATING_SOFTMAX, Sigmoid = INFR_CUDA_GATING_SIGMOID };
+enum class MoeGating : uint32_t {
+  Softmax = INFR_CUDA_GATING_SOFTMAX,
+  Sigmoid = INFR_CUDA_GATING_SIGMOID,
+  SqrtSoftplus = INFR_CUDA_GATING_SQRT_SOFTPLUS
+};
+enum class Activation : uint32_t { Silu = INFR_CUDA_ACT_SILU, Gelu = INFR_CUDA_ACT_GELU };
 
 // What a MoE-only backend reports (backend.rs:45-236): everything off except in-place graph inputs.
 struct Capabilities {
@@ -147,6 +152,11 @@ struct MoeFfn {
   const Buffer* norm_weight = nullptr;
   float norm_eps = 1e-6f;
   const Buffer* residual = nullptr;
+  const Buffer* expert_ids = nullptr;  // graph.rs:1320-1351: the caller's selection, [rows, n_used] i32
+  const Buffer* down_scale = nullptr;  // graph.rs:1273-1276: [n_expert] f32
+  Activation act = Activation::Silu;
+  bool weight_before = false;          // graph.rs:1298-1303
+  float swiglu_clamp = 0.f;            // graph.rs:1283-1290; 0 = none
 
   infr_cuda_moe_ffn_desc to_desc() const {
     infr_cuda_moe_ffn_desc d;
@@ -186,6 +196,11 @@ struct MoeFfn {
     d.norm_weight = h(norm_weight);
     d.norm_eps = norm_eps;
     d.residual = h(residual);
+    d.expert_ids = h(expert_ids);
+    d.down_scale = h(down_scale);
+    d.act = static_cast<uint32_t>(act);
+    d.weight_before = weight_before ? 1u : 0u;
+    d.swiglu_clamp = swiglu_clamp;
     return d;
   }
 };

@@ -67,6 +67,13 @@ class MoeGating(enum.IntEnum):
     """crates/infr-core/src/graph.rs:73-85."""
     Softmax = 0
     Sigmoid = 1
+    SqrtSoftplus = 2
+
+
+class Activation(enum.IntEnum):
+    """crates/infr-core/src/graph.rs Activation; the gated forms of crates/infr-cpu/src/kernels.rs:6662-6683."""
+    Silu = 0
+    Gelu = 1
 
 
 class _Desc(C.Structure):
@@ -84,7 +91,8 @@ class _Desc(C.Structure):
         ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p),
         ("sh_gate_inp", C.c_void_p), ("sh_ff", C.c_uint32), ("path", C.c_uint32),
         ("norm_weight", C.c_void_p), ("residual", C.c_void_p), ("norm_eps", C.c_float),
-        ("stages", C.c_uint32),
+        ("stages", C.c_uint32), ("expert_ids", C.c_void_p), ("down_scale", C.c_void_p),
+        ("act", C.c_uint32), ("weight_before", C.c_uint32), ("swiglu_clamp", C.c_float),
     ]
 
 
@@ -245,6 +253,11 @@ class MoeFfn:
     norm_weight: Optional[Buffer] = None  # RmsNorm -> MoeFfn fusion (fusion.rs:17-25): x is the un-normed row
     norm_eps: float = 1e-6
     residual: Optional[Buffer] = None     # MoeFfn -> Add fusion: added to the result, may be dst itself
+    expert_ids: Optional[Buffer] = None   # [rows, n_used] i32 selection made by the caller (graph.rs:1320-1351)
+    down_scale: Optional[Buffer] = None   # [n_expert] f32 on the expert's down output (graph.rs:1273-1276)
+    act: int = 0                          # Activation
+    weight_before: bool = False           # routing weight before the activation (graph.rs:1298-1303)
+    swiglu_clamp: float = 0.0             # > 0: clamp gate from above and up on both sides (graph.rs:1283-1290)
     _keep: list = field(default_factory=list, repr=False)
 
     def to_desc(self) -> _Desc:
@@ -262,6 +275,9 @@ class MoeFfn:
         d.sh_gate, d.sh_up, d.sh_down, d.sh_gate_inp = _h(self.sh_gate), _h(self.sh_up), _h(self.sh_down), _h(self.sh_gate_inp)
         d.sh_ff, d.path, d.stages = self.sh_ff, self.path, self.stages
         d.norm_weight, d.residual, d.norm_eps = _h(self.norm_weight), _h(self.residual), self.norm_eps
+        d.expert_ids = _h(self.expert_ids)
+        d.down_scale, d.act = _h(self.down_scale), int(self.act)
+        d.weight_before, d.swiglu_clamp = int(bool(self.weight_before)), float(self.swiglu_clamp)
         return d
 
 

@@ -338,8 +338,8 @@ static int32_t validate_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* 
   if (d->n_expert > 1024) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: more than 1024 experts is not covered");
   if (d->ne % 64) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: ne must be a multiple of 64");
   if (d->router_dtype != INFR_CUDA_DT_F32) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: router dtype must be F32");
-  if (d->gating != INFR_CUDA_GATING_SOFTMAX && d->gating != INFR_CUDA_GATING_SIGMOID)
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: gating must be softmax or sigmoid");
+  if (d->gating > INFR_CUDA_GATING_SQRT_SOFTPLUS)
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: gating must be softmax, sigmoid or sqrt-softplus");
   if (d->n_expert_groups > 1 && d->n_expert_groups_used > 0) {
     if (d->n_expert_groups > 32) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: more than 32 expert groups is not covered");
     if (d->n_expert % d->n_expert_groups) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: n_expert is not a multiple of n_expert_groups");
@@ -348,6 +348,12 @@ static int32_t validate_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* 
   if (!fits(d->router_x, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: router_x missing or too small");
   if (!fits(d->router, (size_t)d->n_expert * d->ne * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: router missing or too small");
   if (d->exp_probs_b && !fits(d->exp_probs_b, (size_t)d->n_expert * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: exp_probs_b too small");
+  if (d->expert_ids) {
+    // there is no selection to bias or to limit to groups (graph.rs:1304-1308, 1344-1347)
+    if (d->exp_probs_b || d->n_expert_groups > 1)
+      return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: expert_ids excludes exp_probs_b and expert groups");
+    if (!fits(d->expert_ids, (size_t)d->rows * d->n_used * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: expert_ids too small");
+  }
   const size_t kb = (size_t)d->rows * d->n_used * 4;
   if (d->ids_out && !fits(d->ids_out, kb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ids_out too small");
   if (d->wts_out && !fits(d->wts_out, kb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: wts_out too small");
@@ -375,6 +381,11 @@ static int32_t validate_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d)
     if (d->ne > 8192) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: the RmsNorm fusion covers ne <= 8192");
   }
   if (d->residual && !fits(d->residual, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: residual too small");
+  if (d->act != INFR_CUDA_ACT_SILU && d->act != INFR_CUDA_ACT_GELU) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: act must be SiLU or GELU");
+  if (!(d->swiglu_clamp >= 0.0f)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: swiglu_clamp must be positive, or 0 for none");
+  // the reference defines the clamp for the output-weighted forms only (crates/infr-cpu/src/lib.rs:3613-3619)
+  if (d->swiglu_clamp > 0.0f && d->weight_before) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: swiglu_clamp excludes weight_before");
+  if (d->down_scale && !fits(d->down_scale, (size_t)d->n_expert * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: down_scale too small");
   if (d->ep_n_local && (uint64_t)d->ep_lo + d->ep_n_local > d->n_expert)
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ep band exceeds n_expert");
   if (d->sh_gate || d->sh_up || d->sh_down) {
@@ -433,6 +444,7 @@ RouteParams route_params(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, co
   rp.router = static_cast<const float*>(d->router->ptr);
   rp.sh_gate_inp = (with_gate && d->sh_gate_inp) ? static_cast<const float*>(d->sh_gate_inp->ptr) : nullptr;
   rp.bias = d->exp_probs_b ? static_cast<const float*>(d->exp_probs_b->ptr) : nullptr;
+  rp.given_ids = d->expert_ids ? static_cast<const int32_t*>(d->expert_ids->ptr) : nullptr;
   rp.logits = s.logits;
   rp.sh_logit = s.sh_logit;
   rp.ids = d->ids_out ? static_cast<int32_t*>(d->ids_out->ptr) : s.ids;
@@ -487,9 +499,9 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   }
   if (path == 1) {
     if (!small_ok) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, why);
-    // Up to ROUTE_SMALL_MAX_ROWS rows the router kernel also normalises x and makes its
-    // fixed-point copy; above that the batched router runs and two small kernels do those jobs.
-    const bool few = d->rows <= (uint32_t)ROUTE_SMALL_MAX_ROWS;
+    // Where the whole-row router kernel covers the call it also normalises x and makes its
+    // fixed-point copy; otherwise the batched router runs and two small kernels do those jobs.
+    const bool few = route_small_group(ctx, (int)d->rows, (int)d->ne, (int)d->n_expert) > 0;
     Scratch sz = carve(nullptr, d, true);
     const size_t hn_bytes = (!few && d->norm_weight) ? align_up((size_t)d->rows * d->ne * 4, 256) : 0;
     if ((rc = ensure_scratch(ctx, sz.total + hn_bytes))) return rc;
@@ -550,6 +562,10 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.ep_lo = d->ep_lo;
     dp.ep_n = d->ep_n_local;
     dp.down_q4k = down_q4k ? 1 : 0;
+    dp.down_scale = d->down_scale ? static_cast<const float*>(d->down_scale->ptr) : nullptr;
+    dp.act_kind = (int)d->act;
+    dp.weight_before = d->weight_before ? 1 : 0;
+    dp.clamp = d->swiglu_clamp;
     return launch_decode_ffn(ctx, dp, true, stages);
   }
   // batched path: router GEMM + top-k, permute, grouped GEMMs, un-permute combine
@@ -608,6 +624,10 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     c.ep_n = d->ep_n_local;
     c.legacy = (path == 3) ? 1 : 0;
     c.down_q4k = down_q4k ? 1 : 0;
+    c.act_kind = (int)d->act;
+    c.clamp = d->swiglu_clamp;
+    c.weight_before = d->weight_before ? 1 : 0;
+    c.down_scale = d->down_scale ? static_cast<const float*>(d->down_scale->ptr) : nullptr;
     return launch_grouped_ffn(ctx, c);
   }
 }

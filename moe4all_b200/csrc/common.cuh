@@ -207,6 +207,19 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// One gated-FFN output element (crates/infr-cpu/src/kernels.rs:6662-6683): act(gate) * up, with the
+// optional clamp applied first (gate from above only, up on both sides).
+template <bool FAST_DIV = false>
+__device__ __forceinline__ float gated_act(int act, float clamp, float g, float u) {
+  if (clamp > 0.f) {
+    g = fminf(g, clamp);
+    u = fminf(fmaxf(u, -clamp), clamp);
+  }
+  const float a = act == INFR_CUDA_ACT_GELU ? 0.5f * g * (1.0f + tanhf(0.7978846f * (g + 0.044715f * g * g * g)))
+                                            : (FAST_DIV ? __fdividef(g, 1.0f + __expf(-g)) : g / (1.0f + __expf(-g)));
+  return a * u;
+}
+
 // ---- in-register block unpack -------------------------------------------------------------------
 
 // Build the f32 whose top mantissa bits hold byte `B` of `w`:  bits = 0x3F000000 | byte<<16.

@@ -180,8 +180,9 @@ __global__ void __maxnreg__(56) k_decode_gateup(DecodeParams p, int n_chunks) {
     gsum = warp_sum(gsum) * q_scale;
     usum = warp_sum(usum) * q_scale;
     if (lane == 0) {
-      const float s = gsum / (1.0f + __expf(-gsum));
-      act_out[c * GU_WARPS + warp] = s * usum;
+      // routed pairs: optional clamp, and with weight_before the pair's routing weight on both
+      const float wp = (routed && p.weight_before) ? __ldcg(p.wts + pair) : 1.0f;
+      act_out[c * GU_WARPS + warp] = gated_act(p.act_kind, routed ? p.clamp : 0.f, wp * gsum, wp * usum);
     }
   }
   trace_stamp(tr, 23);
@@ -210,6 +211,7 @@ __global__ void __maxnreg__(56) k_decode_down(DecodeParams p, int TI) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_bar[DN_MAX_SLOTS];
   __shared__ float s_w[DN_MAX_SLOTS];
+  __shared__ float s_ds[DN_MAX_SLOTS];  // per-slot scale of the raw down output (Op::MoeFfn::down_scale)
   __shared__ int s_on[DN_MAX_SLOTS];
   __shared__ uint32_t s_off[DN_MAX_SLOTS];  // slab start inside its shared-memory slot
 
@@ -252,8 +254,10 @@ __global__ void __maxnreg__(56) k_decode_down(DecodeParams p, int TI) {
       const bool mine = e >= 0;  // a negative id marks a pair another rank serves
       e = min(max(e, 0), p.n_expert - 1);
       s_on[s] = (mine && in_band(p, e)) ? e + 1 : 0;
-      s_w[s] = __ldcg(p.wts + r * p.n_used + s);
+      s_w[s] = p.weight_before ? 1.0f : __ldcg(p.wts + r * p.n_used + s);
+      s_ds[s] = p.down_scale ? __ldg(p.down_scale + e) : 1.0f;
     } else {
+      s_ds[s] = 1.0f;
       s_on[s] = 1;
       s_w[s] = p.sh_logit ? 1.0f / (1.0f + __expf(-__ldcg(p.sh_logit + r))) : 1.0f;
     }
@@ -430,7 +434,7 @@ __global__ void __maxnreg__(56) k_decode_down(DecodeParams p, int TI) {
     // the four quarter lanes of a row
     acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
     acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 2);
-    if (u4 == 0 && q < RPG) s_part[s * TI + row0 + q] = s_w[s] * acc;
+    if (u4 == 0 && q < RPG) s_part[s * TI + row0 + q] = s_w[s] * (acc * s_ds[s]);  // s_ds = 1 (exact) without a down_scale
   }
   if (!ok) {
     if (lane == 0) atomicExch(&p.status->timeout, 2);

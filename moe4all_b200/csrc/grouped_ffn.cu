@@ -167,23 +167,28 @@ __global__ void k_pair_scatter(const int32_t* __restrict__ ids, int n_pairs, int
 //   pair_of_pos == nullptr: identity (rows already grouped);  rows >= n_sorted are the shared
 //   expert's copy of every token in natural order.
 __global__ void __launch_bounds__(256) k_gather_rows(const float* __restrict__ x, const int* __restrict__ pair_of_pos,
-                                                     const int* __restrict__ seg_off, int n_seg_routed, int n_used,
-                                                     int total_rows_bound, int ne, __half* __restrict__ xg) {
+                                                     const float* __restrict__ row_w, const int* __restrict__ seg_off,
+                                                     int n_seg_routed, int n_used, int total_rows_bound, int ne,
+                                                     __half* __restrict__ xg) {
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= total_rows_bound) return;
   const int n_sorted = seg_off[n_seg_routed];
   int tok;
-  if (row < n_sorted)
+  float w = 1.0f;  // weight_before: the pair's routing weight on the expert's input row
+  if (row < n_sorted) {
     tok = pair_of_pos ? pair_of_pos[row] / n_used : row;
-  else
+    if (row_w != nullptr && pair_of_pos != nullptr) w = row_w[pair_of_pos[row]];
+  } else {
     tok = row - n_sorted;  // shared-expert segment: token order
+  }
   const int n_total = seg_off[n_seg_routed + 1];
   if (row >= n_total) return;
   const float4* src = reinterpret_cast<const float4*>(x + (size_t)tok * ne);
   __half2* dst = reinterpret_cast<__half2*>(xg + (size_t)row * ne);
   for (int i = lane; i < ne / 4; i += 32) {
-    const float4 v = __ldg(src + i);
+    float4 v = __ldg(src + i);
+    v.x *= w; v.y *= w; v.z *= w; v.w *= w;
     dst[2 * i] = __floats2half2_rn(v.x, v.z);      // positions 0,1 <- elements 0,2
     dst[2 * i + 1] = __floats2half2_rn(v.y, v.w);  // positions 2,3 <- elements 1,3
   }
@@ -194,7 +199,8 @@ __global__ void __launch_bounds__(256) k_gather_rows(const float* __restrict__ x
 // chunk c of row n at chunk position c ^ (n & 7)), so that a CTA fetches a step's whole token
 // operand with one bulk copy.  One warp per row of a tile.
 __global__ void __launch_bounds__(256) k_gather_tiles(const float* __restrict__ x, const int* __restrict__ pair_of_pos,
-                                                      const int* __restrict__ seg_off, int n_seg_routed, int n_used,
+                                                      const float* __restrict__ row_w, const int* __restrict__ seg_off,
+                                                      int n_seg_routed, int n_used,
                                                       const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
                                                       const int* __restrict__ n_tiles, int tn, int ne,
                                                       unsigned char* __restrict__ xt) {
@@ -206,15 +212,19 @@ __global__ void __launch_bounds__(256) k_gather_tiles(const float* __restrict__ 
   const int row = tile_row0[tile] + n;
   const int n_sorted = seg_off[n_seg_routed];
   int tok;
-  if (row < n_sorted)
+  float w = 1.0f;  // weight_before: the pair's routing weight on the expert's input row
+  if (row < n_sorted) {
     tok = pair_of_pos ? pair_of_pos[row] / n_used : row;
-  else
+    if (row_w != nullptr && pair_of_pos != nullptr) w = row_w[pair_of_pos[row]];
+  } else {
     tok = row - n_sorted;  // shared-expert segment: token order
+  }
   const float4* src = reinterpret_cast<const float4*>(x + (size_t)tok * ne);
   const size_t step_bytes = (size_t)tn * 128;
   unsigned char* line0 = xt + (size_t)tile * (ne / 64) * step_bytes + (size_t)n * 128;
   for (int i = lane; i < ne / 4; i += 32) {
-    const float4 v = __ldg(src + i);
+    float4 v = __ldg(src + i);
+    v.x *= w; v.y *= w; v.z *= w; v.w *= w;
     const __half2 h02 = __floats2half2_rn(v.x, v.z), h13 = __floats2half2_rn(v.y, v.w);  // K order 0,2,1,3
     uint2 o;
     o.x = *reinterpret_cast<const uint32_t*>(&h02);
@@ -351,7 +361,7 @@ __global__ void __launch_bounds__(GG_THREADS) k_grouped_gateup(GroupedParams p) 
       const int f = warp_m * 16 + g + (i >> 1) * 8;
       const int n = warp_n * 32 + nt * 8 + 2 * t + (i & 1);
       const float gv = acc[0][nt][i] * W_POSTSCALE, uv = acc[1][nt][i] * W_POSTSCALE;
-      const float a = (gv / (1.0f + __expf(-gv))) * uv;
+      const float a = gated_act(p.act_kind, e < p.n_expert ? p.clamp : 0.f, gv, uv);
       T[n * PITCH + kperm(f)] = __float2half_rn(fminf(fmaxf(a, -65504.f), 65504.f));
     }
   __syncthreads();
@@ -487,7 +497,8 @@ __global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __re
                                                                const float* __restrict__ wts, const float* __restrict__ sh_logit,
                                                                const int* __restrict__ seg_off, int n_seg_routed, int has_shared,
                                                                int rows, int n_used, int ne, const float* residual,
-                                                               float* dst) {
+                                                               const int32_t* __restrict__ ids, const float* __restrict__ down_scale,
+                                                               int weight_before, float* dst) {
   const int t = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
   if (c >= ne) return;
@@ -495,8 +506,12 @@ __global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __re
   for (int s = 0; s < n_used; ++s) {
     const int pos = pos_of_pair[t * n_used + s];
     if (pos < 0) continue;
-    const float w = wts[t * n_used + s];
-    const float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * ne + c);
+    const float w = weight_before ? 1.0f : wts[t * n_used + s];
+    float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * ne + c);
+    if (down_scale != nullptr) {  // y = raw * scale[e], then the weighted sum (Op::MoeFfn::down_scale)
+      const float sc = down_scale[ids[t * n_used + s]];
+      v.x *= sc; v.y *= sc; v.z *= sc; v.w *= sc;
+    }
     o.x += w * v.x; o.y += w * v.y; o.z += w * v.z; o.w += w * v.w;
   }
   if (has_shared) {
@@ -590,6 +605,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   float* y = c.y_out ? c.y_out : reinterpret_cast<float*>(take(((size_t)rows_total + 256) * c.ne * 4));
   cudaStream_t st = ctx->stream;
 
+  const float* row_w = c.weight_before ? c.wts : nullptr;
   if (c.ids) {
     // routed call: bucket the pairs
     cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)(n_seg + 2) * 4, st);
@@ -600,10 +616,10 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
                                                              pos_of_pair, pair_of_pos);
     ctx->launches += 3;
     if (use_umma)
-      k_gather_tiles<<<dim3(tn / 8, max_tiles), 256, 0, st>>>(c.x, pair_of_pos, seg_off, n_seg_routed, c.n_used, tile_row0, tile_rows,
+      k_gather_tiles<<<dim3(tn / 8, max_tiles), 256, 0, st>>>(c.x, pair_of_pos, row_w, seg_off, n_seg_routed, c.n_used, tile_row0, tile_rows,
                                                              n_tiles, tn, c.ne, reinterpret_cast<unsigned char*>(xg));
     else
-      k_gather_rows<<<(rows_total + 7) / 8, 256, 0, st>>>(c.x, pair_of_pos, seg_off, n_seg_routed, c.n_used, rows_total, c.ne, xg);
+      k_gather_rows<<<(rows_total + 7) / 8, 256, 0, st>>>(c.x, pair_of_pos, row_w, seg_off, n_seg_routed, c.n_used, rows_total, c.ne, xg);
     ctx->launches += 1;
   } else {
     // rows already grouped: offsets come from the caller (n_expert segments, no shared segment)
@@ -614,10 +630,10 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
     if (e == cudaSuccess) e = cudaMemcpyAsync(seg_off + 1, c.seg_off_in + c.n_expert, 4, cudaMemcpyDeviceToDevice, st);
     if (e != cudaSuccess) return check_cuda(ctx, e, "grouped: offsets copy");
     if (use_umma)
-      k_gather_tiles<<<dim3(tn / 8, max_tiles), 256, 0, st>>>(c.x, nullptr, seg_off, 0, 1, tile_row0, tile_rows, n_tiles, tn, c.ne,
+      k_gather_tiles<<<dim3(tn / 8, max_tiles), 256, 0, st>>>(c.x, nullptr, nullptr, seg_off, 0, 1, tile_row0, tile_rows, n_tiles, tn, c.ne,
                                                              reinterpret_cast<unsigned char*>(xg));
     else
-      k_gather_rows<<<(rows_total + 7) / 8, 256, 0, st>>>(c.x, nullptr, seg_off, 0, 1, rows_total, c.ne, xg);
+      k_gather_rows<<<(rows_total + 7) / 8, 256, 0, st>>>(c.x, nullptr, nullptr, seg_off, 0, 1, rows_total, c.ne, xg);
     ctx->launches += 2;
   }
 
@@ -642,6 +658,8 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   p.nff = c.nff;
   p.n_expert = c.n_expert;
   p.down_q4k = c.down_q4k;
+  p.act_kind = c.act_kind;
+  p.clamp = c.clamp;
   p.status = ctx->status;
   p.trace = ctx->trace;
   p.trace_tile = getenv("INFR_TRACE_TILE") ? atoi(getenv("INFR_TRACE_TILE")) : 0;
@@ -655,7 +673,8 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   }
   if (c.dst) {
     k_unpermute_combine_seg<<<dim3((c.ne / 4 + 255) / 256, c.rows), 256, 0, st>>>(y, pos_of_pair, c.wts, c.sh_logit, seg_off, n_seg_routed,
-                                                                                   c.shared_rows > 0 ? 1 : 0, c.rows, c.n_used, c.ne, c.residual, c.dst);
+                                                                                   c.shared_rows > 0 ? 1 : 0, c.rows, c.n_used, c.ne, c.residual, c.ids, c.down_scale,
+                                                                                   c.weight_before, c.dst);
     ctx->launches += 1;
   }
   return check_cuda(ctx, cudaGetLastError(), "grouped ffn launch");

@@ -297,6 +297,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
     umma::fence_after_sync();
     const int lq = warp & 3, m = warp >> 3, fh = (warp >> 2) & 1;  // TMEM lane quarter, token half, feature half
     if (ok && m < n_m) {
+      const float clamp = e < p.n_expert ? p.clamp : 0.f;  // the shared expert's segment is not clamped
       const int n0 = m * 128 + lq * 32;  // first token row of this warp
       const uint32_t trow = tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(m * 256 + fh * 64);
       unsigned char* lines = reinterpret_cast<unsigned char*>(p.act) + tile_step_offset(tile, p.nff / UK, (f0 >> 6) + fh) + (size_t)n0 * 128;
@@ -312,7 +313,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             const float gv = g[4 * q + t] * W_POSTSCALE, uv = u[4 * q + t] * W_POSTSCALE;
-            a[t] = fminf(fmaxf(__fdividef(gv, 1.0f + __expf(-gv)) * uv, -65504.f), 65504.f);
+            a[t] = fminf(fmaxf(gated_act<true>(p.act_kind, clamp, gv, uv), -65504.f), 65504.f);
           }
           const uint32_t w0 = h2_as_u32(__floats2half2_rn(a[0], a[2])), w1 = h2_as_u32(__floats2half2_rn(a[1], a[3]));
           if (q & 1) {

@@ -4,8 +4,12 @@
 
 namespace infr {
 
-// Calls with at most this many rows run the whole-row router kernel with the fused top-k.
+// The whole-row router kernel (fused norm, fixed-point copy and top-k) takes up to this many rows per
+// CTA group, up to ROUTE_SMALL_MAX_GROUPS groups (one completion counter each) and
+// ROUTE_SMALL_LIMIT rows per call.
 constexpr int ROUTE_SMALL_MAX_ROWS = 8;
+constexpr int ROUTE_SMALL_MAX_GROUPS = 64;
+constexpr int ROUTE_SMALL_LIMIT = 64;
 
 struct RouteParams {
   const float* router_x;     // [rows, ne]
@@ -13,6 +17,7 @@ struct RouteParams {
   const float* router;       // [n_expert, ne] f32
   const float* sh_gate_inp;  // [ne] or null
   const float* bias;         // [n_expert] or null
+  const int32_t* given_ids;  // [rows, n_used] selection made by the caller, or null (top-k)
   const float* rms_w;        // [ne] RmsNorm weight applied to x before everything else, or null
   float rms_eps;
   float* logits;             // [rows, n_expert] scratch
@@ -47,6 +52,10 @@ struct DecodeParams {
   int rows, ne, n_used, nff, sh_ff, n_expert;
   uint32_t ep_lo, ep_n;  // band (ep_n == 0: off)
   int down_q4k;          // the down banks (routed and shared) are Q4_K instead of Q6_K
+  const float* down_scale;  // [n_expert] scale on a routed expert's down output, or null
+  int act_kind;          // INFR_CUDA_ACT_*
+  int weight_before;     // routing weight on gate and up before the activation, none on the output
+  float clamp;           // > 0: routed experts clamp gate (one-sided) and up (both sides) first
 };
 
 // Device-side view of one grouped-GEMM launch (see grouped_ffn.cu).
@@ -65,6 +74,8 @@ struct GroupedParams {
   int trace_tile;             // tile whose first CTA writes them
   int ne, nff, n_expert;
   int down_q4k;               // the down banks are Q4_K instead of Q6_K (tcgen05 kernels only)
+  int act_kind;               // INFR_CUDA_ACT_*
+  float clamp;                // > 0: routed tiles clamp gate (from above) and up (both sides) first
 };
 
 // Host-side description of one batched expert-FFN call.
@@ -86,6 +97,10 @@ struct GroupedCall {
   uint32_t ep_lo, ep_n;
   int legacy;              // 1: use the mma.sync tiles even where the tcgen05 kernels apply
   int down_q4k;            // the down banks are Q4_K instead of Q6_K
+  int act_kind;            // INFR_CUDA_ACT_*
+  float clamp;             // Op::MoeFfn::swiglu_clamp, 0 = none
+  int weight_before;       // routing weight on the expert's input rows, none on its output
+  const float* down_scale; // [n_expert] or null
 };
 
 bool umma_grouped_supported(int ne, int nff);
@@ -98,6 +113,8 @@ int32_t launch_combine(infr_cuda_ctx* ctx, const float* y, const int* pos_of_pai
 
 int32_t launch_umma_selftest(infr_cuda_ctx* ctx, const __half* a, const __half* b, float* c, int n);
 int32_t launch_route(infr_cuda_ctx* ctx, const RouteParams& p, bool pdl);
+// Rows per group the whole-row router kernel would use for this shape; 0 = the call takes the batched router.
+int route_small_group(const infr_cuda_ctx* ctx, int rows, int ne, int n_expert);
 int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages);
 // Whether the small-m kernels cover this shape (dims, shared-memory budget).
 bool decode_ffn_supported(const infr_cuda_ctx* ctx, int ne, int nff, int sh_ff, int n_used, bool down_q4k, std::string* why);

@@ -225,7 +225,7 @@ void parallel_for(size_t n, int threads, const std::function<void(size_t)>& fn) 
 extern "C" {
 
 // Descriptor of one Op::MoeFfn call (crates/infr-core/src/graph.rs:1259-1352), restricted to the
-// forms on the hot path: split gate/up, SiLU, output-side weighting, no down_scale, no hash ids.
+// split gate/up form.
 struct orc_moe_desc {
   const float* x;         // [rows, ne]
   const float* router_x;  // [rows, ne]
@@ -247,6 +247,11 @@ struct orc_moe_desc {
   uint32_t n_expert_groups, n_expert_groups_used;
   uint32_t ep_lo, ep_n_local;  // band [ep_lo, ep_lo+ep_n_local); ep_n_local == 0 → no band
   int32_t threads;
+  const int32_t* expert_ids;  // [rows, n_used] selection made by the caller (hash-routed layers), or null
+  const float* down_scale;    // [n_expert] scale on an expert's down output before the weighted sum, or null
+  uint32_t act;               // 0 SiLU, 1 GELU (tanh form)
+  uint32_t weight_before;     // routing weight applied to gate and up before the activation
+  float swiglu_clamp;         // > 0: act(min(gate, l)) * clamp(up, -l, l)
 };
 
 int orc_has_avx2(void) {
@@ -273,7 +278,7 @@ float orc_dot_scalar(const float* a, const float* b, size_t n) { return dot_scal
 
 // Routing of one row (infr-cpu/src/lib.rs:3741-3863).  logits → probs → selection copy (+bias,
 // group mask) → stable descending sort → first n_used; weights from the UNBIASED probs.
-static void route_row(const orc_moe_desc* d, const float* logits, int32_t* idx_out, float* w_out,
+static void route_row(const orc_moe_desc* d, const float* logits, const int32_t* given, int32_t* idx_out, float* w_out,
                       float* sel_out) {
   const uint32_t E = d->n_expert, k = d->n_used;
   std::vector<float> probs(E);
@@ -293,7 +298,12 @@ static void route_row(const orc_moe_desc* d, const float* logits, int32_t* idx_o
       probs[e] = std::sqrt(sp);
     }
   }
+  std::vector<uint32_t> idx(E);
   std::vector<float> sel(probs);
+  if (given) {
+    // hash-routed layer (lib.rs:3776-3792): the given experts are the selection, nothing is ranked
+    for (uint32_t s = 0; s < k; ++s) idx[s] = (uint32_t)given[s];
+  } else {
   if (d->exp_probs_b)
     for (uint32_t e = 0; e < E; ++e) sel[e] = probs[e] + d->exp_probs_b[e];
   if (d->n_expert_groups > 1 && d->n_expert_groups_used > 0) {
@@ -322,9 +332,9 @@ static void route_row(const orc_moe_desc* d, const float* logits, int32_t* idx_o
       if (!chosen[g])
         for (uint32_t i = 0; i < per; ++i) sel[g * per + i] = ninf;
   }
-  std::vector<uint32_t> idx(E);
   std::iota(idx.begin(), idx.end(), 0u);
   std::stable_sort(idx.begin(), idx.end(), [&](uint32_t a, uint32_t b) { return sel[a] > sel[b]; });
+  }
   if (d->norm_w) {
     float ws = 0.0f;
     for (uint32_t s = 0; s < k; ++s) ws = ws + probs[idx[s]];
@@ -335,6 +345,16 @@ static void route_row(const orc_moe_desc* d, const float* logits, int32_t* idx_o
   }
   for (uint32_t s = 0; s < k; ++s) idx_out[s] = (int32_t)idx[s];
   if (sel_out) std::memcpy(sel_out, sel.data(), E * sizeof(float));
+}
+
+// act_fn / gated_act_fn (crates/infr-cpu/src/kernels.rs:6662-6683).
+static inline float act_value(uint32_t act, float g) {
+  if (act == 1) return 0.5f * g * (1.0f + std::tanh(0.7978846f * (g + 0.044715f * g * g * g)));
+  return silu(g);
+}
+static inline float gated_act_value(uint32_t act, float clamp, float gate, float up) {
+  if (clamp > 0.0f) return act_value(act, std::min(gate, clamp)) * std::min(std::max(up, -clamp), clamp);
+  return act_value(act, gate) * up;
 }
 
 // Op::MoeFfn in reference mode (infr-cpu/src/lib.rs:3584-4304 with every bank on the f32
@@ -348,6 +368,15 @@ int orc_moe_ffn(const orc_moe_desc* d) {
                urb = row_bytes(d->up_dtype, ne), drb = row_bytes(d->down_dtype, nff);
   if (!rrb || !grb || !urb || !drb) return -2;
   const int T = d->threads > 0 ? d->threads : orc_hw_threads();
+  // the clamp is defined for the gated SiLU / GELU forms without weight_before (lib.rs:3613-3619)
+  if (d->act > 1 || (d->swiglu_clamp > 0.0f && d->weight_before)) return -3;
+  if (d->expert_ids) {
+    // the reference refuses a bias or groups beside given ids (graph.rs:1304-1308) and panics on an
+    // id past n_expert (lib.rs:3782-3788)
+    if (d->exp_probs_b || d->n_expert_groups > 1) return -3;
+    for (size_t i = 0; i < R * k; ++i)
+      if (d->expert_ids[i] < 0 || (size_t)d->expert_ids[i] >= E) return -3;
+  }
 
   // Router logits: logits[r,e] = dot(router_row_e, router_x[r])  (lib.rs:3684-3716).
   std::vector<float> logits(R * E);
@@ -361,7 +390,8 @@ int orc_moe_ffn(const orc_moe_desc* d) {
   std::vector<int32_t> ids(R * k);
   std::vector<float> wts(R * k);
   parallel_for(R, T, [&](size_t r) {
-    route_row(d, &logits[r * E], &ids[r * k], &wts[r * k], d->sel_out ? d->sel_out + r * E : nullptr);
+    route_row(d, &logits[r * E], d->expert_ids ? d->expert_ids + r * k : nullptr, &ids[r * k], &wts[r * k],
+              d->sel_out ? d->sel_out + r * E : nullptr);
   });
   if (d->ids_out) std::memcpy(d->ids_out, ids.data(), R * k * sizeof(int32_t));
   if (d->wts_out) std::memcpy(d->wts_out, wts.data(), R * k * sizeof(float));
@@ -398,7 +428,9 @@ int orc_moe_ffn(const orc_moe_desc* d) {
         const float* xr = d->x + (size_t)(p / k) * ne;
         const float g = dot(wg.data(), xr, ne);
         const float u = dot(wu.data(), xr, ne);
-        act[(size_t)p * nff + o] = silu(g) * u;
+        // llama4's weight_before: the pair's routing weight on gate and up, before the activation
+        const float wp = d->weight_before ? wts[p] : 1.0f;
+        act[(size_t)p * nff + o] = gated_act_value(d->act, d->swiglu_clamp, wp * g, wp * u);
       }
     }
   });
@@ -413,7 +445,10 @@ int orc_moe_ffn(const orc_moe_desc* d) {
     const size_t o1 = std::min<size_t>(t.o0 + 64, ne);
     for (size_t o = t.o0; o < o1; ++o) {
       dequant_row(d->down_dtype, d->down_exps + t.e * dst_stride + o * drb, nff, wd.data());
-      for (uint32_t p : bucket[t.e]) y[(size_t)p * ne + o] = dot(wd.data(), &act[(size_t)p * nff], nff);
+      for (uint32_t p : bucket[t.e]) {
+        const float raw = dot(wd.data(), &act[(size_t)p * nff], nff);
+        y[(size_t)p * ne + o] = d->down_scale ? raw * d->down_scale[t.e] : raw;  // lib.rs:4252-4258
+      }
     }
   });
 
@@ -425,7 +460,7 @@ int orc_moe_ffn(const orc_moe_desc* d) {
       const size_t p = r * k + rank;
       const uint32_t e = (uint32_t)ids[p];
       if (band && (e < d->ep_lo || e >= d->ep_lo + d->ep_n_local)) continue;
-      const float w = wts[p];
+      const float w = d->weight_before ? 1.0f : wts[p];  // lib.rs:4295-4296
       const float* yr = &y[p * ne];
       for (size_t i = 0; i < ne; ++i) o[i] = o[i] + w * yr[i];
     }
@@ -502,7 +537,8 @@ int orc_moe_layer(const orc_moe_desc* d, const uint8_t* sh_gate, const uint8_t* 
   std::vector<float> g(R * sh_ff), u(R * sh_ff), a(R * sh_ff), ds(R * ne);
   if ((rc = orc_linear(d->gate_dtype, sh_gate, d->x, d->rows, d->ne, sh_ff, g.data(), d->threads))) return rc;
   if ((rc = orc_linear(d->up_dtype, sh_up, d->x, d->rows, d->ne, sh_ff, u.data(), d->threads))) return rc;
-  orc_gated_act_silu(g.data(), u.data(), a.data(), R * sh_ff);
+  // Op::GatedAct with the model's activation, no clamp on the shared expert here
+  for (size_t i = 0; i < R * sh_ff; ++i) a[i] = gated_act_value(d->act, 0.0f, g[i], u[i]);
   if ((rc = orc_linear(d->down_dtype, sh_down, a.data(), d->rows, sh_ff, d->ne, ds.data(), d->threads))) return rc;
   if (sh_gate_inp) {
     std::vector<float> gl(R);

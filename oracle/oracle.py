@@ -39,6 +39,8 @@ class _Desc(C.Structure):
         ("down_dtype", C.c_int32), ("gating", C.c_uint32), ("norm_w", C.c_uint32),
         ("n_expert_groups", C.c_uint32), ("n_expert_groups_used", C.c_uint32),
         ("ep_lo", C.c_uint32), ("ep_n_local", C.c_uint32), ("threads", C.c_int32),
+        ("expert_ids", C.c_void_p), ("down_scale", C.c_void_p), ("act", C.c_uint32),
+        ("weight_before", C.c_uint32), ("swiglu_clamp", C.c_float),
     ]
 
 
@@ -120,12 +122,15 @@ class MoeResult:
 def _desc(x, router_x, router, gate, up, down, *, n_expert, n_used, n_ff_exp, scale=1.0,
           router_dtype=DT_F32, gate_dtype=DT_Q4K, up_dtype=DT_Q4K, down_dtype=DT_Q6K,
           gating=GATING_SOFTMAX, norm_w=True, bias=None, groups=0, groups_used=0,
-          ep_band=None, threads=0):
+          ep_band=None, threads=0, expert_ids=None, down_scale=None, act=0, weight_before=False,
+          swiglu_clamp=0.0):
     x = _f32(x)
     rows, ne = x.shape
     router_x = x if router_x is None else _f32(router_x)
     keep = dict(x=x, router_x=router_x, router=_u8(router), gate=_u8(gate), up=_u8(up),
                 down=_u8(down), bias=None if bias is None else _f32(bias),
+                dscale=None if down_scale is None else _f32(down_scale),
+                given=None if expert_ids is None else np.ascontiguousarray(expert_ids, np.int32).reshape(rows, n_used),
                 dst=np.zeros((rows, ne), np.float32), ids=np.zeros((rows, n_used), np.int32),
                 wts=np.zeros((rows, n_used), np.float32),
                 logits=np.zeros((rows, n_expert), np.float32),
@@ -143,6 +148,8 @@ def _desc(x, router_x, router, gate, up, down, *, n_expert, n_used, n_ff_exp, sc
     d.n_expert_groups, d.n_expert_groups_used = groups, groups_used
     d.ep_lo, d.ep_n_local = (ep_band if ep_band else (0, 0))
     d.threads = threads
+    d.expert_ids = _p(keep["given"])
+    d.down_scale, d.act, d.weight_before, d.swiglu_clamp = _p(keep["dscale"]), int(act), int(bool(weight_before)), float(swiglu_clamp)
     return d, keep
 
 

@@ -43,7 +43,8 @@ class GpuLayer:
         self.bias = be.from_host(L.bias) if L.bias is not None else None
 
     def run(self, x, n_used, *, router_x=None, scale=1.0, gating=MoeGating.Softmax, norm_w=True,
-            groups=0, groups_used=0, ep_band=None, shared=True, path=0):
+            groups=0, groups_used=0, ep_band=None, shared=True, path=0, expert_ids=None, down_scale=None,
+            act=0, weight_before=False, swiglu_clamp=0.0):
         be, L = self.be, self.L
         x = np.ascontiguousarray(x, np.float32)
         rows = x.shape[0]
@@ -53,6 +54,8 @@ class GpuLayer:
         ids = be.alloc(rows * n_used * 4)
         wts = be.alloc(rows * n_used * 4)
         use_sh = shared and self.sh_gate is not None
+        given = be.from_host(np.ascontiguousarray(expert_ids, np.int32)) if expert_ids is not None else None
+        dsc = be.from_host(np.ascontiguousarray(down_scale, np.float32)) if down_scale is not None else None
         op = MoeFfn(x=xb, router_x=rxb, router=self.router, gate_exps=self.gate, up_exps=self.up,
                     down_exps=self.down, dst=dst, rows=rows, ne=L.ne, n_expert=L.n_expert,
                     n_used=n_used, n_ff_exp=L.n_ff, scale=scale, gating=gating, norm_w=norm_w,
@@ -61,7 +64,8 @@ class GpuLayer:
                     sh_gate=self.sh_gate if use_sh else None, sh_up=self.sh_up if use_sh else None,
                     sh_down=self.sh_down if use_sh else None,
                     sh_gate_inp=self.sh_gate_inp if use_sh else None,
-                    sh_ff=L.sh_ff if use_sh else 0, path=path, down_dtype=DType(getattr(L, "down_dtype", 14)))
+                    sh_ff=L.sh_ff if use_sh else 0, path=path, down_dtype=DType(getattr(L, "down_dtype", 14)),
+                    expert_ids=given, down_scale=dsc, act=act, weight_before=weight_before, swiglu_clamp=swiglu_clamp)
         be.moe_ffn(op)
         be.sync()
         out = be.download(dst, np.float32).reshape(rows, L.ne)
@@ -69,10 +73,12 @@ class GpuLayer:
 
 
 def oracle_layer(L, x, n_used, *, router_x=None, scale=1.0, gating=0, norm_w=True, groups=0,
-                 groups_used=0, ep_band=None, shared=True, threads=0):
+                 groups_used=0, ep_band=None, shared=True, threads=0, expert_ids=None, down_scale=None, act=0,
+                 weight_before=False, swiglu_clamp=0.0):
     kw = dict(n_expert=L.n_expert, n_used=n_used, n_ff_exp=L.n_ff, scale=scale, gating=int(gating),
               norm_w=norm_w, bias=L.bias, groups=groups, groups_used=groups_used, ep_band=ep_band,
-              threads=threads, router_x=router_x, down_dtype=getattr(L, "down_dtype", 14))
+              threads=threads, router_x=router_x, down_dtype=getattr(L, "down_dtype", 14), expert_ids=expert_ids,
+              down_scale=down_scale, act=int(act), weight_before=weight_before, swiglu_clamp=swiglu_clamp)
     if shared and L.sh_gate is not None:
         return orc.moe_layer(x, L.router, L.gate, L.up, L.down, L.sh_gate, L.sh_up, L.sh_down,
                              L.sh_gate_inp, L.sh_ff, **kw)

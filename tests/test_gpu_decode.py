@@ -4,7 +4,7 @@ import pytest
 
 from moe4all_b200 import MoeGating, synth
 
-from helpers import GpuLayer, assert_close, near_tie_rows, oracle_layer
+from helpers import GpuLayer, assert_close, near_tie_rows, oracle_layer, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -123,6 +123,48 @@ def test_wide_logit_range(backend, rows):
     assert_close(out, ref.dst)
 
 
+@pytest.mark.parametrize("rows", [1, 8, 40])
+def test_sqrt_softplus_gating(backend, rows):
+    # DeepSeek-V4 gating: sqrt(ln(1 + exp(v))), the logit itself above 20; router scaled so that both
+    # branches occur
+    L = synth.make_layer(41, 512, 32, 256, router_std=0.6)
+    x = synth.activations(43, rows, 512)
+    lg = x @ L.router.reshape(32, 512).T
+    assert (lg > 20).any() and (lg < 20).any()
+    g = GpuLayer(backend, L)
+    kw = dict(gating=MoeGating.SqrtSoftplus, scale=1.5)
+    out, ids, wts = g.run(x, 4, **kw)
+    ref = oracle_layer(L, x, 4, **kw)
+    check_ids(ids, wts, ref, 4)
+    assert_close(out, ref.dst)
+
+
+@pytest.mark.parametrize("rows,gating", [(1, MoeGating.Softmax), (6, MoeGating.SqrtSoftplus), (40, MoeGating.Softmax)])
+def test_caller_selected_experts(backend, rows, gating):
+    # hash-routed layers: the experts come from a table; the weights are still the router's own
+    # probabilities at those experts
+    L = synth.make_layer(45, 512, 32, 256, router_std=0.05)
+    x = synth.activations(47, rows, 512)
+    rng = np.random.default_rng(5)
+    given = np.stack([rng.permutation(32)[:4] for _ in range(rows)]).astype(np.int32)
+    g = GpuLayer(backend, L)
+    kw = dict(gating=gating, expert_ids=given)
+    out, ids, wts = g.run(x, 4, **kw)
+    ref = oracle_layer(L, x, 4, **kw)
+    assert (ids == given).all() and (ref.ids == given).all()
+    np.testing.assert_allclose(wts, ref.wts, rtol=2e-6, atol=1e-9)
+    assert_close(out, ref.dst)
+
+
+def test_caller_selected_experts_refusals(backend):
+    L = synth.make_layer(45, 512, 32, 256, bias_std=0.05)
+    g = GpuLayer(backend, L)
+    x = synth.activations(47, 2, 512)
+    given = np.zeros((2, 4), np.int32)
+    with pytest.raises(Exception, match="expert_ids excludes"):
+        g.run(x, 4, expert_ids=given)
+
+
 def test_ep_band_partials_sum_to_full(backend):
     # Op::MoeFfn::ep_band: the per-band partial outputs add up to the unbanded output
     L = synth.make_layer(8, 1024, 32, 256)
@@ -144,3 +186,52 @@ def test_wide_hidden(backend):
     ref = oracle_layer(L, x, 4, gating=1, scale=2.5)
     check_ids(ids, wts, ref, 4)
     assert_close(out, ref.dst)
+
+
+@pytest.mark.parametrize("rows,ne", [(6, 7168), (16, 2048), (33, 1024), (64, 512)])
+def test_router_row_groups(backend, rows, ne):
+    # calls of more rows than one router CTA holds run as groups of tokens (one selecting CTA and
+    # one counter each); at hidden 7168 a group is four rows.  Small-m kernels forced.
+    L = synth.make_layer(51, ne, 64, 256, sh_ff=256, router_std=0.05)
+    x = synth.activations(53, rows, ne)
+    g = GpuLayer(backend, L)
+    out, ids, wts = g.run(x, 4, path=1)
+    ref = oracle_layer(L, x, 4)
+    check_ids(ids, wts, ref, 4)
+    assert_close(out, ref.dst)
+
+
+VARIANTS = {
+    "gelu": dict(act=1),
+    "clamp": dict(swiglu_clamp=0.05),
+    "weight_before": dict(weight_before=True, gating=MoeGating.Sigmoid, norm_w=False),
+    "down_scale": dict(down_scale=np.linspace(0.5, 1.5, 32).astype(np.float32)),
+    "gelu_clamp_scale": dict(act=1, swiglu_clamp=0.08, down_scale=np.linspace(1.5, 0.25, 32).astype(np.float32)),
+}
+
+
+@pytest.mark.parametrize("rows,path", [(1, 1), (5, 1), (24, 1), (70, 2), (70, 3)])
+@pytest.mark.parametrize("variant", sorted(VARIANTS))
+def test_op_variants(backend, rows, path, variant):
+    # the remaining Op::MoeFfn forms (GELU, SwiGLU clamp, llama4's weight_before, per-expert down
+    # scale) through the small-m kernels, the tcgen05 tiles and the mma.sync tiles
+    L = synth.make_layer(61, 512, 32, 256, sh_ff=256, router_std=0.05)
+    x = synth.activations(63, rows, 512)
+    kw = VARIANTS[variant]
+    g = GpuLayer(backend, L)
+    out, ids, wts = g.run(x, 4, path=path, **kw)
+    ref = oracle_layer(L, x, 4, **kw)
+    base = oracle_layer(L, x, 4, **{k: v for k, v in kw.items() if k in ("gating", "norm_w")})
+    assert rel_err(ref.dst, base.dst)[0] > 1e-2, "the variant does not change the result: the case tests nothing"
+    check_ids(ids, wts, ref, 4)
+    assert_close(out, ref.dst)
+
+
+def test_op_variant_refusals(backend):
+    L = synth.make_layer(61, 512, 32, 256)
+    g = GpuLayer(backend, L)
+    x = synth.activations(63, 2, 512)
+    with pytest.raises(Exception, match="swiglu_clamp excludes weight_before"):
+        g.run(x, 4, swiglu_clamp=1.0, weight_before=True)
+    with pytest.raises(Exception, match="act must be"):
+        g.run(x, 4, act=2)

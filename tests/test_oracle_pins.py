@@ -186,7 +186,8 @@ def gen(n, salt):
     return synth.gen_f32(n, salt)
 
 
-def moe_ref_numpy(x, router, gate, up, down, ne, n_expert, n_used, nff, scale, gating, bias, groups, groups_used):
+def moe_ref_numpy(x, router, gate, up, down, ne, n_expert, n_used, nff, scale, gating, bias, groups, groups_used, given=None,
+                  act="silu", clamp=None, weight_before=False, down_scale=None):
     """`moe_ref` of crates/infr-llama/tests/seam_op_parity.rs:2245-2343 (plain sequential f32 dots)."""
     def dot(a, b):
         s = F32(0)
@@ -213,23 +214,35 @@ def moe_ref_numpy(x, router, gate, up, down, ne, n_expert, n_used, nff, scale, g
         for g in range(groups):
             if g not in keep:
                 sel[g * per:(g + 1) * per] = -np.inf
-    idx = sorted(range(n_expert), key=lambda e: -sel[e])[:n_used]
+    idx = sorted(range(n_expert), key=lambda e: -sel[e])[:n_used] if given is None else [int(e) for e in given]
     wsum = F32(0)
     for e in idx:
         wsum = F32(wsum + probs[e])
     out = np.zeros(ne, F32)
     silu = lambda z: F32(z / (F32(1) + np.exp(-z, dtype=F32)))
+    gelu = lambda z: F32(F32(0.5) * z * (F32(1) + np.tanh(F32(0.7978846) * (z + F32(0.044715) * z * z * z), dtype=F32)))
+    fn = silu if act == "silu" else gelu
+
+    def gated(g, u):  # gated_act_fn, crates/infr-cpu/src/kernels.rs:6671-6683
+        if clamp is not None:
+            g, u = min(g, F32(clamp)), min(max(u, F32(-clamp)), F32(clamp))
+        return F32(fn(g) * u)
     for e in idx:
         gs_, ds_ = e * nff * ne, e * ne * nff
-        act = np.array([silu(dot(gate[gs_ + j * ne: gs_ + (j + 1) * ne], x)) * dot(up[gs_ + j * ne: gs_ + (j + 1) * ne], x)
-                        for j in range(nff)], F32)
         w_e = F32(F32(probs[e] / wsum) * F32(scale))
+        wp = w_e if weight_before else F32(1)
+        a = np.array([gated(F32(wp * dot(gate[gs_ + j * ne: gs_ + (j + 1) * ne], x)), F32(wp * dot(up[gs_ + j * ne: gs_ + (j + 1) * ne], x)))
+                      for j in range(nff)], F32)
+        w_out = F32(1) if weight_before else w_e
         for i in range(ne):
-            out[i] = F32(out[i] + F32(w_e * dot(down[ds_ + i * nff: ds_ + (i + 1) * nff], act)))
+            y = dot(down[ds_ + i * nff: ds_ + (i + 1) * nff], a)
+            if down_scale is not None:
+                y = F32(y * down_scale[e])
+            out[i] = F32(out[i] + F32(w_out * y))
     return out, idx
 
 
-def run_f32_case(lead, salts, gating, gname, bias=None, groups=0, groups_used=0, n_used=2):
+def run_f32_case(lead, salts, gating, gname, bias=None, groups=0, groups_used=0, n_used=2, given=None, **variant):
     ne = nff = 32
     n_expert = len(lead)
     x = np.ones((1, ne), F32)
@@ -238,8 +251,12 @@ def run_f32_case(lead, salts, gating, gname, bias=None, groups=0, groups_used=0,
     gate, up, down = gen(n_expert * nff * ne, salts[0]), gen(n_expert * nff * ne, salts[1]), gen(n_expert * ne * nff, salts[2])
     res = orc.moe_ffn(x, router, gate, up, down, n_expert=n_expert, n_used=n_used, n_ff_exp=nff, scale=1.0,
                       gate_dtype=orc.DT_F32, up_dtype=orc.DT_F32, down_dtype=orc.DT_F32, gating=gating,
-                      bias=bias, groups=groups, groups_used=groups_used, threads=2)
-    want, idx = moe_ref_numpy(x[0], router, gate, up, down, ne, n_expert, n_used, nff, 1.0, gname, bias, groups, groups_used)
+                      bias=bias, groups=groups, groups_used=groups_used, threads=2,
+                      expert_ids=None if given is None else np.asarray(given, np.int32).reshape(1, n_used),
+                      act=1 if variant.get("act") == "gelu" else 0, swiglu_clamp=variant.get("clamp") or 0.0,
+                      weight_before=variant.get("weight_before", False), down_scale=variant.get("down_scale"))
+    want, idx = moe_ref_numpy(x[0], router, gate, up, down, ne, n_expert, n_used, nff, 1.0, gname, bias, groups, groups_used, given,
+                              **variant)
     return res, want, idx
 
 
@@ -265,6 +282,44 @@ def test_groups_bias_vector():
     # without the bias group 0 wins (experts 0, 1): the bias semantics are what flips it
     res2, _, _ = run_f32_case(lead, (15, 16, 17), orc.GATING_SIGMOID, "sigmoid", bias=None, groups=2, groups_used=1)
     assert res2.ids[0].tolist() == [0, 1]
+
+
+def test_hash_routing_vector():
+    # Op::MoeFfn::expert_ids (crates/infr-core/src/graph.rs:1320-1351; CPU crates/infr-cpu/src/lib.rs:
+    # 3776-3792; test crates/infr-llama/tests/seam_op_parity.rs:5700-5897): the given experts replace
+    # the selection only; the weights are the router's probabilities at those experts, not uniform
+    lead = np.array([2.0, 1.0, 0.75, 0.5, -1.5, -1.0], F32)
+    res, want, idx = run_f32_case(lead, (12, 13, 14), orc.GATING_SOFTMAX, "softmax", given=[4, 1])
+    assert res.ids[0].tolist() == [4, 1] == idx
+    assert np.max(np.abs(res.dst[0] - want)) < 1e-4
+    p = np.exp(lead - lead.max())
+    np.testing.assert_allclose(res.wts[0], [p[4] / (p[4] + p[1]), p[1] / (p[4] + p[1])], rtol=1e-6)
+    assert abs(res.wts[0][0] - 0.5) > 0.3
+    # ids past n_expert, a bias or groups beside the ids: refused (graph.rs:1304-1308; lib.rs:3782-3788)
+    with pytest.raises(ValueError):
+        run_f32_case(lead, (12, 13, 14), orc.GATING_SOFTMAX, "softmax", given=[6, 1])
+    with pytest.raises(ValueError):
+        run_f32_case(lead, (12, 13, 14), orc.GATING_SOFTMAX, "softmax", given=[4, 1], bias=np.zeros(6, F32))
+
+
+@pytest.mark.parametrize("variant", [
+    dict(act="gelu"),
+    dict(clamp=0.02),                 # DeepSeek-V4 swiglu_clamp: act(min(g, l)) * clamp(u, -l, l)
+    dict(weight_before=True),         # llama4: routing weight on gate and up before the activation
+    dict(down_scale=np.array([0.5, 2.0, 1.5, 1.0, 0.25, 3.0], F32)),  # diffusion-gemma ffn_down_exps.scale
+    dict(act="gelu", clamp=0.03, down_scale=np.array([2.0, 0.5, 1.5, 1.0, 0.25, 3.0], F32)),
+], ids=["gelu", "clamp", "weight_before", "down_scale", "gelu_clamp_scale"])
+def test_op_variant_vectors(variant):
+    # the remaining Op::MoeFfn forms against a from-definition restatement (crates/infr-cpu/src/lib.rs:
+    # 4144-4181 gate/up with weight_before and the clamp, :4246-4258 down_scale, :4287-4303 the sum;
+    # activations crates/infr-cpu/src/kernels.rs:6662-6683)
+    lead = np.array([2.0, 1.0, 0.75, 0.5, -1.5, -1.0], F32)
+    res, want, idx = run_f32_case(lead, (12, 13, 14), orc.GATING_SOFTMAX, "softmax", **variant)
+    plain, _, _ = run_f32_case(lead, (12, 13, 14), orc.GATING_SOFTMAX, "softmax")
+    assert res.ids[0].tolist() == [0, 1] == idx
+    scale = np.abs(want).max()
+    assert np.max(np.abs(res.dst[0] - want)) < 1e-4 * max(scale, 1.0)
+    assert np.max(np.abs(res.dst[0] - plain.dst[0])) > 1e-2 * scale  # the variant is not a no-op here
 
 
 def test_tie_goes_to_lower_index():
