@@ -168,6 +168,9 @@ typedef struct infr_cuda_moe_ffn_desc {
   float swiglu_clamp;               /* > 0: routed experts compute act(min(gate, l)) * clamp(up, -l, l)
                                        (graph.rs:1283-1290, kernels.rs:6671-6683); 0 = off; refused
                                        together with weight_before, as in the reference            */
+  uint32_t fused_gate_up;           /* Op::MoeFfn::fused_gate_up (graph.rs:1277-1282): gate_exps holds
+                                       [n_expert, 2 * n_ff_exp, ne], an expert's gate rows first and
+                                       its up rows second; up_exps is not read                      */
 } infr_cuda_moe_ffn_desc;
 
 /* Backend::execute of a graph holding one Op::MoeFfn (backend.rs:908; CPU arm

@@ -157,6 +157,7 @@ struct MoeFfn {
   Activation act = Activation::Silu;
   bool weight_before = false;          // graph.rs:1298-1303
   float swiglu_clamp = 0.f;            // graph.rs:1283-1290; 0 = none
+  bool fused_gate_up = false;          // graph.rs:1277-1282: gate_exps = [n_expert, 2*n_ff_exp, ne]
 
   infr_cuda_moe_ffn_desc to_desc() const {
     infr_cuda_moe_ffn_desc d;
@@ -201,6 +202,7 @@ struct MoeFfn {
     d.act = static_cast<uint32_t>(act);
     d.weight_before = weight_before ? 1u : 0u;
     d.swiglu_clamp = swiglu_clamp;
+    d.fused_gate_up = fused_gate_up ? 1u : 0u;
     return d;
   }
 };

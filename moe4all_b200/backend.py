@@ -93,6 +93,7 @@ class _Desc(C.Structure):
         ("norm_weight", C.c_void_p), ("residual", C.c_void_p), ("norm_eps", C.c_float),
         ("stages", C.c_uint32), ("expert_ids", C.c_void_p), ("down_scale", C.c_void_p),
         ("act", C.c_uint32), ("weight_before", C.c_uint32), ("swiglu_clamp", C.c_float),
+        ("fused_gate_up", C.c_uint32),
     ]
 
 
@@ -258,6 +259,7 @@ class MoeFfn:
     act: int = 0                          # Activation
     weight_before: bool = False           # routing weight before the activation (graph.rs:1298-1303)
     swiglu_clamp: float = 0.0             # > 0: clamp gate from above and up on both sides (graph.rs:1283-1290)
+    fused_gate_up: bool = False           # gate_exps is [n_expert, 2*n_ff_exp, ne]; up_exps unused (graph.rs:1277-1282)
     _keep: list = field(default_factory=list, repr=False)
 
     def to_desc(self) -> _Desc:
@@ -278,6 +280,7 @@ class MoeFfn:
         d.expert_ids = _h(self.expert_ids)
         d.down_scale, d.act = _h(self.down_scale), int(self.act)
         d.weight_before, d.swiglu_clamp = int(bool(self.weight_before)), float(self.swiglu_clamp)
+        d.fused_gate_up = int(bool(self.fused_gate_up))
         return d
 
 

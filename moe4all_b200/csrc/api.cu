@@ -373,7 +373,8 @@ static int32_t validate_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d)
   if (!fits(d->dst, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: dst missing or too small");
   const size_t gb = (size_t)d->n_expert * d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
   const size_t db = (size_t)d->n_expert * d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
-  if (!fits(d->gate_exps, gb) || !fits(d->up_exps, gb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: gate/up bank missing or too small");
+  if (d->fused_gate_up ? !fits(d->gate_exps, 2 * gb) : (!fits(d->gate_exps, gb) || !fits(d->up_exps, gb)))
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: gate/up bank missing or too small");
   if (!fits(d->down_exps, db)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: down bank missing or too small");
   if (d->norm_weight) {
     if (!fits(d->norm_weight, (size_t)d->ne * 4)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: norm_weight too small");
@@ -540,7 +541,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.wts = rp.wts;
     dp.sh_logit = (has_sh && d->sh_gate_inp) ? s.sh_logit : nullptr;
     dp.gate = static_cast<const uint8_t*>(d->gate_exps->ptr);
-    dp.up = static_cast<const uint8_t*>(d->up_exps->ptr);
+    dp.up = d->fused_gate_up ? dp.gate + (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne) : static_cast<const uint8_t*>(d->up_exps->ptr);
     dp.down = static_cast<const uint8_t*>(d->down_exps->ptr);
     dp.sh_gate = has_sh ? static_cast<const uint8_t*>(d->sh_gate->ptr) : nullptr;
     dp.sh_up = has_sh ? static_cast<const uint8_t*>(d->sh_up->ptr) : nullptr;
@@ -550,7 +551,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.residual = d->residual ? static_cast<const float*>(d->residual->ptr) : nullptr;
     dp.status = ctx->status;
     dp.trace = ctx->trace;
-    dp.gate_stride = (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
+    dp.gate_stride = (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne) * (d->fused_gate_up ? 2 : 1);
     dp.up_stride = dp.gate_stride;
     dp.down_stride = (size_t)d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
     dp.rows = d->rows;
@@ -604,12 +605,12 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     c.sh_logit = (has_sh && d->sh_gate_inp) ? s.sh_logit : nullptr;
     c.dst = static_cast<float*>(d->dst->ptr);
     c.gate = static_cast<const uint8_t*>(d->gate_exps->ptr);
-    c.up = static_cast<const uint8_t*>(d->up_exps->ptr);
+    c.up = d->fused_gate_up ? c.gate + (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne) : static_cast<const uint8_t*>(d->up_exps->ptr);
     c.down = static_cast<const uint8_t*>(d->down_exps->ptr);
     c.sh_gate = has_sh ? static_cast<const uint8_t*>(d->sh_gate->ptr) : nullptr;
     c.sh_up = has_sh ? static_cast<const uint8_t*>(d->sh_up->ptr) : nullptr;
     c.sh_down = has_sh ? static_cast<const uint8_t*>(d->sh_down->ptr) : nullptr;
-    c.gate_stride = (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
+    c.gate_stride = (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne) * (d->fused_gate_up ? 2 : 1);
     c.up_stride = c.gate_stride;
     c.down_stride = (size_t)d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
     c.rows = (int)d->rows;

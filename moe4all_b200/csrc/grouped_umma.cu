@@ -223,7 +223,8 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
   const unsigned char* my_raw = raw + (size_t)(tid & 255) * Q4K_BLOCK_BYTES;
   const CUtensorMap* tmg = shared_seg ? &tm_sh_gate : &tm_gate;
   const CUtensorMap* tmu = shared_seg ? &tm_sh_up : &tm_up;
-  const int bank_row0 = (shared_seg ? 0 : e * p.nff) + f0;
+  // rows of one expert in the bank: nff, or 2 nff where gate and up share a bank (the up map then starts nff rows in)
+  const int bank_row0 = (shared_seg ? 0 : e * (int)(p.gate_stride / ((size_t)p.ne / 256 * Q4K_BLOCK_BYTES))) + f0;
   auto request_block = [&](int blk) {
     if (tid == 0) {
       mbar_arrive_expect_tx(&s_raw_full, 2 * UM * (uint32_t)Q4K_BLOCK_BYTES);
@@ -614,7 +615,12 @@ int32_t launch_umma_grouped(infr_cuda_ctx* ctx, const GroupedParams& p, int max_
   if (e != cudaSuccess) return check_cuda(ctx, e, "umma grouped smem attribute");
   const size_t rb = (size_t)p.ne / 256 * Q4K_BLOCK_BYTES;
   CUtensorMap tm_gate, tm_up, tm_sh_gate, tm_sh_up, tm_down, tm_sh_down;
-  bool ok = q4k_rows_map(&tm_gate, p.gate, (size_t)p.n_expert * p.nff, rb, UM) && q4k_rows_map(&tm_up, p.up, (size_t)p.n_expert * p.nff, rb, UM);
+  // a bank's rows as one 2-D tensor; with gate and up in one bank an expert has 2 nff rows and the
+  // up map starts nff rows in (and ends with the bank)
+  const size_t rows_per_expert = p.gate_stride / rb;
+  const size_t bank_rows = (size_t)p.n_expert * rows_per_expert;
+  bool ok = q4k_rows_map(&tm_gate, p.gate, bank_rows, rb, UM) &&
+            q4k_rows_map(&tm_up, p.up, bank_rows - (rows_per_expert - (size_t)p.nff), rb, UM);
   if (ok && p.sh_gate) ok = q4k_rows_map(&tm_sh_gate, p.sh_gate, (size_t)p.nff, rb, UM) && q4k_rows_map(&tm_sh_up, p.sh_up, (size_t)p.nff, rb, UM);
   if (!p.sh_gate) {
     tm_sh_gate = tm_gate;

@@ -252,6 +252,7 @@ struct orc_moe_desc {
   uint32_t act;               // 0 SiLU, 1 GELU (tanh form)
   uint32_t weight_before;     // routing weight applied to gate and up before the activation
   float swiglu_clamp;         // > 0: act(min(gate, l)) * clamp(up, -l, l)
+  uint32_t fused_gate_up;     // gate_exps holds [n_expert, 2*n_ff_exp, ne]: gate rows then up rows; up_exps unused
 };
 
 int orc_has_avx2(void) {
@@ -409,7 +410,10 @@ int orc_moe_ffn(const orc_moe_desc* d) {
   for (uint32_t e = 0; e < E; ++e)
     if (!bucket[e].empty()) active.push_back(e);
 
-  const size_t gst = grb * nff, ust = urb * nff, dst_stride = drb * ne;  // bytes per expert
+  // bytes per expert; a fused bank (graph.rs:1277-1282) holds an expert's gate rows, then its up rows
+  const bool fused = d->fused_gate_up != 0;
+  const size_t gst = grb * nff * (fused ? 2 : 1), ust = fused ? gst : urb * nff, dst_stride = drb * ne;
+  const uint8_t* up_base = fused ? d->gate_exps + grb * nff : d->up_exps;
   std::vector<float> act(R * k * nff, 0.0f), y(R * k * ne, 0.0f);
 
   // Stages B + C: gate/up mat-vec then act = silu(g)*u  (lib.rs:4051-4212).
@@ -423,7 +427,7 @@ int orc_moe_ffn(const orc_moe_desc* d) {
     const size_t o1 = std::min<size_t>(t.o0 + 64, nff);
     for (size_t o = t.o0; o < o1; ++o) {
       dequant_row(d->gate_dtype, d->gate_exps + t.e * gst + o * grb, ne, wg.data());
-      dequant_row(d->up_dtype, d->up_exps + t.e * ust + o * urb, ne, wu.data());
+      dequant_row(fused ? d->gate_dtype : d->up_dtype, up_base + t.e * ust + o * (fused ? grb : urb), ne, wu.data());
       for (uint32_t p : bucket[t.e]) {
         const float* xr = d->x + (size_t)(p / k) * ne;
         const float g = dot(wg.data(), xr, ne);

@@ -40,7 +40,7 @@ class _Desc(C.Structure):
         ("n_expert_groups", C.c_uint32), ("n_expert_groups_used", C.c_uint32),
         ("ep_lo", C.c_uint32), ("ep_n_local", C.c_uint32), ("threads", C.c_int32),
         ("expert_ids", C.c_void_p), ("down_scale", C.c_void_p), ("act", C.c_uint32),
-        ("weight_before", C.c_uint32), ("swiglu_clamp", C.c_float),
+        ("weight_before", C.c_uint32), ("swiglu_clamp", C.c_float), ("fused_gate_up", C.c_uint32),
     ]
 
 
@@ -123,7 +123,7 @@ def _desc(x, router_x, router, gate, up, down, *, n_expert, n_used, n_ff_exp, sc
           router_dtype=DT_F32, gate_dtype=DT_Q4K, up_dtype=DT_Q4K, down_dtype=DT_Q6K,
           gating=GATING_SOFTMAX, norm_w=True, bias=None, groups=0, groups_used=0,
           ep_band=None, threads=0, expert_ids=None, down_scale=None, act=0, weight_before=False,
-          swiglu_clamp=0.0):
+          swiglu_clamp=0.0, fused_gate_up=False):
     x = _f32(x)
     rows, ne = x.shape
     router_x = x if router_x is None else _f32(router_x)
@@ -149,6 +149,7 @@ def _desc(x, router_x, router, gate, up, down, *, n_expert, n_used, n_ff_exp, sc
     d.ep_lo, d.ep_n_local = (ep_band if ep_band else (0, 0))
     d.threads = threads
     d.expert_ids = _p(keep["given"])
+    d.fused_gate_up = int(bool(fused_gate_up))
     d.down_scale, d.act, d.weight_before, d.swiglu_clamp = _p(keep["dscale"]), int(act), int(bool(weight_before)), float(swiglu_clamp)
     return d, keep
 

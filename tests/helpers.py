@@ -29,6 +29,13 @@ def assert_close(got, want, tol=TOL_REL, what="output"):
     return rel
 
 
+def fused_bank(L):
+    """gate and up banks as one [n_expert, 2*n_ff, row bytes] bank: an expert's gate rows, then its up rows."""
+    g = np.asarray(L.gate, np.uint8).reshape(L.n_expert, -1)
+    u = np.asarray(L.up, np.uint8).reshape(L.n_expert, -1)
+    return np.ascontiguousarray(np.concatenate([g, u], axis=1)).reshape(-1)
+
+
 class GpuLayer:
     """Device copies of a synth.LayerWeights."""
 
@@ -44,7 +51,7 @@ class GpuLayer:
 
     def run(self, x, n_used, *, router_x=None, scale=1.0, gating=MoeGating.Softmax, norm_w=True,
             groups=0, groups_used=0, ep_band=None, shared=True, path=0, expert_ids=None, down_scale=None,
-            act=0, weight_before=False, swiglu_clamp=0.0):
+            act=0, weight_before=False, swiglu_clamp=0.0, fused_gate_up=False):
         be, L = self.be, self.L
         x = np.ascontiguousarray(x, np.float32)
         rows = x.shape[0]
@@ -56,7 +63,10 @@ class GpuLayer:
         use_sh = shared and self.sh_gate is not None
         given = be.from_host(np.ascontiguousarray(expert_ids, np.int32)) if expert_ids is not None else None
         dsc = be.from_host(np.ascontiguousarray(down_scale, np.float32)) if down_scale is not None else None
-        op = MoeFfn(x=xb, router_x=rxb, router=self.router, gate_exps=self.gate, up_exps=self.up,
+        gate_b, up_b = self.gate, self.up
+        if fused_gate_up:  # one bank, an expert's gate rows then its up rows; up_exps gets the same handle and is not read
+            gate_b = up_b = be.from_host(fused_bank(L))
+        op = MoeFfn(x=xb, router_x=rxb, router=self.router, gate_exps=gate_b, up_exps=up_b,
                     down_exps=self.down, dst=dst, rows=rows, ne=L.ne, n_expert=L.n_expert,
                     n_used=n_used, n_ff_exp=L.n_ff, scale=scale, gating=gating, norm_w=norm_w,
                     exp_probs_b=self.bias, n_expert_groups=groups, n_expert_groups_used=groups_used,
@@ -65,7 +75,8 @@ class GpuLayer:
                     sh_down=self.sh_down if use_sh else None,
                     sh_gate_inp=self.sh_gate_inp if use_sh else None,
                     sh_ff=L.sh_ff if use_sh else 0, path=path, down_dtype=DType(getattr(L, "down_dtype", 14)),
-                    expert_ids=given, down_scale=dsc, act=act, weight_before=weight_before, swiglu_clamp=swiglu_clamp)
+                    expert_ids=given, down_scale=dsc, act=act, weight_before=weight_before, swiglu_clamp=swiglu_clamp,
+                    fused_gate_up=fused_gate_up)
         be.moe_ffn(op)
         be.sync()
         out = be.download(dst, np.float32).reshape(rows, L.ne)
@@ -74,15 +85,17 @@ class GpuLayer:
 
 def oracle_layer(L, x, n_used, *, router_x=None, scale=1.0, gating=0, norm_w=True, groups=0,
                  groups_used=0, ep_band=None, shared=True, threads=0, expert_ids=None, down_scale=None, act=0,
-                 weight_before=False, swiglu_clamp=0.0):
+                 weight_before=False, swiglu_clamp=0.0, fused_gate_up=False):
     kw = dict(n_expert=L.n_expert, n_used=n_used, n_ff_exp=L.n_ff, scale=scale, gating=int(gating),
               norm_w=norm_w, bias=L.bias, groups=groups, groups_used=groups_used, ep_band=ep_band,
               threads=threads, router_x=router_x, down_dtype=getattr(L, "down_dtype", 14), expert_ids=expert_ids,
-              down_scale=down_scale, act=int(act), weight_before=weight_before, swiglu_clamp=swiglu_clamp)
+              down_scale=down_scale, act=int(act), weight_before=weight_before, swiglu_clamp=swiglu_clamp,
+              fused_gate_up=fused_gate_up)
+    gate = fused_bank(L) if fused_gate_up else L.gate
     if shared and L.sh_gate is not None:
-        return orc.moe_layer(x, L.router, L.gate, L.up, L.down, L.sh_gate, L.sh_up, L.sh_down,
+        return orc.moe_layer(x, L.router, gate, L.up, L.down, L.sh_gate, L.sh_up, L.sh_down,
                              L.sh_gate_inp, L.sh_ff, **kw)
-    return orc.moe_ffn(x, L.router, L.gate, L.up, L.down, **kw)
+    return orc.moe_ffn(x, L.router, gate, L.up, L.down, **kw)
 
 
 def near_tie_rows(res, n_used, ulps=8):

@@ -207,6 +207,7 @@ VARIANTS = {
     "weight_before": dict(weight_before=True, gating=MoeGating.Sigmoid, norm_w=False),
     "down_scale": dict(down_scale=np.linspace(0.5, 1.5, 32).astype(np.float32)),
     "gelu_clamp_scale": dict(act=1, swiglu_clamp=0.08, down_scale=np.linspace(1.5, 0.25, 32).astype(np.float32)),
+    "fused_gate_up": dict(fused_gate_up=True, act=1),
 }
 
 
@@ -214,7 +215,7 @@ VARIANTS = {
 @pytest.mark.parametrize("variant", sorted(VARIANTS))
 def test_op_variants(backend, rows, path, variant):
     # the remaining Op::MoeFfn forms (GELU, SwiGLU clamp, llama4's weight_before, per-expert down
-    # scale) through the small-m kernels, the tcgen05 tiles and the mma.sync tiles
+    # scale, gate and up in one bank) through the small-m kernels, the tcgen05 tiles and the mma.sync tiles
     L = synth.make_layer(61, 512, 32, 256, sh_ff=256, router_std=0.05)
     x = synth.activations(63, rows, 512)
     kw = VARIANTS[variant]
