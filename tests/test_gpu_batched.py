@@ -32,9 +32,10 @@ def test_batched_small_layer(backend, rows, path):
     assert_close(out[keep], ref.dst[keep])
 
 
-def test_auto_path_switches_above_eight_rows(backend):
+def test_auto_path_switches_to_grouped_gemm(backend):
+    # 40 tokens x 4 over 16 experts = 10 tokens per expert: past the small-m kernels' range
     L = synth.make_layer(42, 512, 16, 256, router_std=0.05)
-    x = synth.activations(1, 9, 512)
+    x = synth.activations(1, 40, 512)
     g = GpuLayer(backend, L)
     n0 = backend.launch_count()
     out, ids, _ = g.run(x, 4)
