@@ -22,7 +22,6 @@ namespace infr {
 namespace {
 
 constexpr int GU_WARPS = 16;  // rows per chunk and role: one per warp
-constexpr int GU_THREADS = GU_WARPS * 32;
 constexpr int GU_MAX_CHUNKS = 4;
 constexpr int GU_XQPITCH = 144;  // bytes per 64-element group of fixed-point x: 64 low limbs, 64 high limbs, pad
 
@@ -50,11 +49,12 @@ __global__ void __maxnreg__(56) k_decode_gateup(DecodeParams p, int n_chunks) {
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rb = p.ne / 256 * (int)Q4K_BLOCK_BYTES;  // bytes per weight row
-  const int TR = GU_WARPS * n_chunks;
+  const int GW = blockDim.x >> 5;  // warps = weight rows per chunk and role
+  const int TR = GW * n_chunks;
   const int tiles = p.nff / TR, sh_tiles = p.sh_ff / TR;
   const int n_routed_jobs = p.rows * p.n_used * tiles;
 
-  const uint32_t chunk_bytes = (uint32_t)GU_WARPS * rb;  // per role
+  const uint32_t chunk_bytes = (uint32_t)GW * rb;  // per role
   auto issue_copies = [&](const uint8_t* gs, const uint8_t* us) {
     for (int c = 0; c < n_chunks; ++c) {
       mbar_arrive_expect_tx(&s_bar[c], 2 * chunk_bytes);
@@ -182,7 +182,7 @@ __global__ void __maxnreg__(56) k_decode_gateup(DecodeParams p, int n_chunks) {
     if (lane == 0) {
       // routed pairs: optional clamp, and with weight_before the pair's routing weight on both
       const float wp = (routed && p.weight_before) ? __ldcg(p.wts + pair) : 1.0f;
-      act_out[c * GU_WARPS + warp] = gated_act(p.act_kind, routed ? p.clamp : 0.f, wp * gsum, wp * usum);
+      act_out[c * GW + warp] = gated_act(p.act_kind, routed ? p.clamp : 0.f, wp * gsum, wp * usum);
     }
   }
   trace_stamp(tr, 23);
@@ -453,8 +453,8 @@ __global__ void __maxnreg__(56) k_decode_down(DecodeParams p, int TI) {
   }
 }
 
-size_t gateup_smem(int ne, int n_chunks) {
-  return (size_t)n_chunks * 2 * GU_WARPS * (ne / 256 * Q4K_BLOCK_BYTES) + (size_t)(ne / 64) * GU_XQPITCH;
+size_t gateup_smem(int ne, int n_chunks, int gw = GU_WARPS) {
+  return (size_t)n_chunks * 2 * gw * (ne / 256 * Q4K_BLOCK_BYTES) + (size_t)(ne / 64) * GU_XQPITCH;
 }
 
 int pick_chunks(int ne, int nff, int sh_ff) {
@@ -530,9 +530,25 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, u
   const size_t dbb = p.down_q4k ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES;
   const int TI = pick_down_tile(p.ne, p.nff, sh_ff, p.n_used, dbb);
   if (!n_chunks || !TI) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "small-m path: tile does not fit shared memory");
-  const int TR = GU_WARPS * n_chunks;
-  const int jobs = p.rows * p.n_used * (p.nff / TR) + (has_sh ? p.rows * (sh_ff / TR) : 0);
-  size_t smem_gu = gateup_smem(p.ne, n_chunks);
+  int gw = GU_WARPS;
+  int TR = gw * n_chunks;
+  int jobs = p.rows * p.n_used * (p.nff / TR) + (has_sh ? p.rows * (sh_ff / TR) : 0);
+  int n_chunks_gu = n_chunks;
+  {
+    // Grids of more than four waves: four warps taking four chunks of four rows each (same tile per role
+    // as 16 x 1, half the default tile).  The smaller CTAs put more independent chains of
+    // (ids -> copies -> unpack) on an SM: 69 us against 78 us for 32 tokens.
+    static const int ew = getenv("INFR_GU_WARPS") ? atoi(getenv("INFR_GU_WARPS")) : 4;
+    static const int ec = getenv("INFR_GU_CHUNKS") ? atoi(getenv("INFR_GU_CHUNKS")) : 4;
+    if (ew > 0 && ec > 0 && ec <= GU_MAX_CHUNKS && jobs > 4 * ctx->sm_count && p.ne / 16 <= ew * 32 && p.nff % (ew * ec) == 0 &&
+        (!has_sh || sh_ff % (ew * ec) == 0)) {
+      gw = ew;
+      n_chunks_gu = ec;
+      TR = gw * n_chunks_gu;
+      jobs = p.rows * p.n_used * (p.nff / TR) + (has_sh ? p.rows * (sh_ff / TR) : 0);
+    }
+  }
+  size_t smem_gu = gateup_smem(p.ne, n_chunks_gu, gw);
   // A grid that fits the device one CTA per SM is spread that way: gate/up CTAs start while the
   // router's CTAs still hold some SMs and would otherwise pair up on the free ones, halving their
   // copy bandwidth and leaving no room for the down kernel's CTAs to start beside them.  A request
@@ -543,7 +559,7 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, u
   auto run_gu = [&](auto kern) {
     e = ensure_smem(reinterpret_cast<const void*>(kern), smem_gu);
     if (e != cudaSuccess) return e;
-    return launch_ex(kern, dim3(jobs), dim3(GU_THREADS), smem_gu, ctx->stream, pdl, p, n_chunks);
+    return launch_ex(kern, dim3(jobs), dim3(gw * 32), smem_gu, ctx->stream, pdl, p, n_chunks_gu);
   };
   if (stages & 2u) {
     if (ng == 1)
@@ -570,6 +586,14 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, u
   // sub-partition, one of these CTAs shares the register file with a gate/up CTA but not with a
   // second CTA of its own kind (which would only get going once the first has finished).
   if (p.rows * (p.ne / TI) <= ctx->sm_count && nw > 16 && nw % 4) nw = std::min((int)DN_MAX_WARPS, (nw + 3) & ~3);
+  {
+    // Grids of more than four waves: at most 12 warps, so that three CTAs share an SM's registers and
+    // their latency chains overlap (83 us against 98 us for 32 tokens).
+    static const int cap = getenv("INFR_DN_WARPS") ? atoi(getenv("INFR_DN_WARPS")) : 12;
+    if (cap > 0 && p.rows * (p.ne / TI) > 4 * ctx->sm_count)
+      for (int c = cap; c >= 1; --c)
+        if (n_tasks % c == 0) { nw = c; break; }
+  }
   e = launch_ex(k_decode_down, dim3(p.rows * (p.ne / TI)), dim3(nw * 32), smem_dn, ctx->stream, pdl, p, TI);
   ctx->launches += 1;
   return check_cuda(ctx, e, "k_decode_down launch");
