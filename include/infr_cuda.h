@@ -157,8 +157,9 @@ typedef struct infr_cuda_moe_ffn_desc {
                                        still run and the weights are the router's own probabilities
                                        at these experts (then norm_w and scale).  Refused together
                                        with exp_probs_b or expert groups.  An id outside
-                                       [0, n_expert) is reported through infr_cuda_status
-                                       (bad_index) and served as expert 0.  NULL = top-k routing.  */
+                                       [0, n_expert) is served as expert 0 and the next
+                                       infr_cuda_sync / download fails with INVALID_ARG (the CPU
+                                       panics there, lib.rs:3782-3788).  NULL = top-k routing.     */
   const infr_cuda_buf* down_scale;  /* Op::MoeFfn::down_scale (graph.rs:1273-1276): [n_expert] f32 on the
                                        selected expert's down output before the weighted sum
                                        (y = raw * scale[e], then w * y); NULL = none                */

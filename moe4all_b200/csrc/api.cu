@@ -73,24 +73,24 @@ struct DeviceGuard {
 
 bool fits(const infr_cuda_buf* b, size_t need) { return b && b->ptr && b->bytes >= need; }
 
-// Drains the context's stream and reports a bounded wait that ran out inside a kernel.  The status
-// words travel to a pinned host mirror on the same stream, so the caller pays for one wait.
+// Drains the context's stream and reports what kernels flagged: a bounded wait that ran out, or an
+// expert id outside [0, n_expert).  The status words live in pinned host memory that the device
+// writes directly (and only in those cases), so polling them costs nothing beyond the one wait.
 int32_t drain_and_poll(infr_cuda_ctx* ctx, const char* what) {
-  // A recorded plan ends with this copy, so nothing is queued here when only plans ran since.
-  cudaError_t e = cudaSuccess;
-  if (ctx->launches != ctx->launches_at_status) {
-    e = cudaMemcpyAsync(ctx->status_host, ctx->status, sizeof(DeviceStatus), cudaMemcpyDeviceToHost, ctx->stream);
-    ctx->launches_at_status = ctx->launches;
-  }
-  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+  const cudaError_t e = cudaStreamSynchronize(ctx->stream);
   if (e != cudaSuccess) return check_cuda(ctx, e, what);
-  const int tag = ctx->status_host->timeout;
-  if (tag) {
-    cudaMemsetAsync(ctx->status, 0, sizeof(DeviceStatus), ctx->stream);
-    cudaStreamSynchronize(ctx->stream);
-    char msg[96];
-    std::snprintf(msg, sizeof msg, "a bounded device-side wait ran out (kernel tag %d); outputs of that call are invalid", tag);
-    return fail(ctx, INFR_CUDA_ERR_TIMEOUT, msg);
+  volatile DeviceStatus* st = ctx->status_host;
+  const int tag = st->timeout, bad = st->bad_index;
+  if (tag || bad) {
+    st->timeout = 0;
+    st->bad_index = 0;
+    if (tag) {
+      char msg[96];
+      std::snprintf(msg, sizeof msg, "a bounded device-side wait ran out (kernel tag %d); outputs of that call are invalid", tag);
+      return fail(ctx, INFR_CUDA_ERR_TIMEOUT, msg);
+    }
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG,
+                "an expert id outside [0, n_expert) reached a kernel and was served as another expert; outputs of that call are invalid");
   }
   return INFR_CUDA_OK;
 }
@@ -119,14 +119,14 @@ int32_t infr_cuda_create(int32_t device, infr_cuda_ctx** out) {
   ctx->sm_count = prop.multiProcessorCount;
   DeviceGuard g(device);
   if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
-      cudaMalloc(&ctx->status, sizeof(DeviceStatus)) != cudaSuccess ||
-      cudaMallocHost(&ctx->status_host, sizeof(DeviceStatus)) != cudaSuccess ||
+      cudaHostAlloc(reinterpret_cast<void**>(&ctx->status_host), sizeof(DeviceStatus), cudaHostAllocMapped) != cudaSuccess ||
+      cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->status), ctx->status_host, 0) != cudaSuccess ||
       cudaMalloc(&ctx->counters, 64 * sizeof(unsigned int)) != cudaSuccess ||
-      cudaMemset(ctx->status, 0, sizeof(DeviceStatus)) != cudaSuccess ||
       cudaMemset(ctx->counters, 0, 64 * sizeof(unsigned int)) != cudaSuccess) {
     infr_cuda_destroy(ctx);
     return INFR_CUDA_ERR_CUDA;
   }
+  std::memset(ctx->status_host, 0, sizeof(DeviceStatus));
   ctx->stream = ctx->own_stream;
   *out = ctx;
   return INFR_CUDA_OK;
@@ -137,7 +137,6 @@ void infr_cuda_destroy(infr_cuda_ctx* ctx) {
   DeviceGuard g(ctx->device);
   if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
-  if (ctx->status) cudaFree(ctx->status);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->counters) cudaFree(ctx->counters);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
@@ -281,10 +280,7 @@ int32_t infr_cuda_graph_end(infr_cuda_ctx* ctx, infr_cuda_graph** out) {
   DeviceGuard g(ctx->device);
   ctx->capturing = false;
   cudaGraph_t graph = nullptr;
-  // last node: the status words travel to their host mirror with every replay
-  cudaError_t e0 = cudaMemcpyAsync(ctx->status_host, ctx->status, sizeof(DeviceStatus), cudaMemcpyDeviceToHost, ctx->stream);
   cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
-  if (e == cudaSuccess && e0 != cudaSuccess) e = e0;
   if (e != cudaSuccess || !graph) return check_cuda(ctx, e == cudaSuccess ? cudaErrorUnknown : e, "graph_end");
   cudaGraphExec_t exec = nullptr;
   e = cudaGraphInstantiate(&exec, graph, 0);
@@ -310,10 +306,7 @@ int32_t infr_cuda_graph_launch(infr_cuda_ctx* ctx, infr_cuda_graph* graph) {
   if (!ctx || !graph || !graph->exec) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "graph_launch: null graph");
   DeviceGuard g(ctx->device);
   cudaError_t e = cudaGraphLaunch(graph->exec, ctx->stream);
-  if (e == cudaSuccess) {
-    ctx->launches += graph->kernels;
-    ctx->launches_at_status = ctx->launches;  // the plan's last node refreshes the mirror after all earlier work
-  }
+  if (e == cudaSuccess) ctx->launches += graph->kernels;
   return check_cuda(ctx, e, "graph_launch");
 }
 

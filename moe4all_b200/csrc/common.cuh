@@ -24,7 +24,7 @@ constexpr uint32_t QK = 256;
 // Device-visible status word written by kernels whose bounded waits ran out.
 struct DeviceStatus {
   int timeout;      // != 0: a bounded wait gave up (value identifies the kernel)
-  int bad_index;    // != 0: an index was clamped (diagnostic only)
+  int bad_index;    // != 0: an expert id outside [0, n_expert) was clamped
 };
 
 }  // namespace infr
@@ -53,9 +53,8 @@ struct infr_cuda_ctx {
   // scratch grown on demand (never inside a launch sequence that could be captured)
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
-  infr::DeviceStatus* status = nullptr;       // device memory
-  infr::DeviceStatus* status_host = nullptr;  // pinned host mirror, filled when the stream is drained
-  uint64_t launches_at_status = ~0ull;        // value of `launches` when the mirror was last queued for refresh
+  infr::DeviceStatus* status = nullptr;       // the device's address of the status words below
+  infr::DeviceStatus* status_host = nullptr;  // pinned, mapped host memory: kernels write it directly when they flag something
   unsigned int* counters = nullptr;           // device memory: completion counters (zeroed by users)
   unsigned long long* trace = nullptr;        // optional phase stamps (see trace_stamp)
 };

@@ -163,6 +163,14 @@ def test_caller_selected_experts_refusals(backend):
     given = np.zeros((2, 4), np.int32)
     with pytest.raises(Exception, match="expert_ids excludes"):
         g.run(x, 4, expert_ids=given)
+    # an id past n_expert: the CPU panics (crates/infr-cpu/src/lib.rs:3782-3788); here the wait that
+    # follows the call fails, and the context stays usable
+    L2 = synth.make_layer(45, 512, 32, 256)
+    g2 = GpuLayer(backend, L2)
+    with pytest.raises(Exception, match="outside"):
+        g2.run(x, 4, expert_ids=np.full((2, 4), 40, np.int32))
+    out, ids, _ = g2.run(x, 4)
+    assert_close(out, oracle_layer(L2, x, 4).dst)
 
 
 def test_ep_band_partials_sum_to_full(backend):
