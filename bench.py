@@ -301,40 +301,29 @@ def run_ours(args):
     # device buffer and a queued copy are faster.
     host_dst = be.wrap(out_host.data_ptr(), nbytes) if R <= 8 else None
     x_ptrs = [x_host[i].data_ptr() for i in range(X_POOL)]
-    if R <= 2:
-        # compile once, execute per step: one recorded plan per weight set holding the host-to-device
-        # copy of the step's input from a pinned staging row and the layer (Backend::compile /
-        # Backend::execute, crates/infr-core/src/backend.rs:907-908).  One launch per step is what
-        # counts when the device work is this short.
-        stage_in = torch.empty(R, NE).pin_memory()
-        plans = []
-        for i in range(LAYER_SETS):
-            be.graph_begin()
-            be.upload_ptr_async(x_in, stage_in.data_ptr(), nbytes)
+    # compile once, execute per step: one recorded plan per weight set holding the host-to-device
+    # copy of the step's input from a pinned staging buffer, the layer, and (past eight rows) the
+    # device-to-host copy of the result (Backend::compile / Backend::execute,
+    # crates/infr-core/src/backend.rs:907-908): one launch and one host wait per step
+    stage_in = torch.empty(R, NE).pin_memory()
+    plans = []
+    for i in range(LAYER_SETS):
+        be.graph_begin()
+        be.upload_ptr_async(x_in, stage_in.data_ptr(), nbytes)
+        if host_dst is not None:
             be.moe_ffn(dataclasses.replace(op_for(i, xbuf=x_in), dst=host_dst))
-            plans.append(be.graph_end())
-        stage_ptr = stage_in.data_ptr()
-        memmove = ctypes.memmove
+        else:
+            be.moe_ffn(op_for(i, xbuf=x_in))
+            be.download_ptr_async(dst, out_host.data_ptr(), nbytes)
+        plans.append(be.graph_end())
+    stage_ptr = stage_in.data_ptr()
+    memmove = ctypes.memmove
 
-        def e2e_step(s):
-            # the step's result is in host memory when sync() returns: one host wait per step
-            memmove(stage_ptr, x_ptrs[s % X_POOL], nbytes)
-            be.execute(plans[s % LAYER_SETS])
-            be.sync()
-    else:
-        # Backend::upload / execute of a one-op graph / sync, call by call: with more device work per
-        # step the first kernel is already running while the later ones are still being launched,
-        # which a recorded plan's single, longer launch does not give.
-        e2e_ops = [op_for(i, xbuf=x_in) if host_dst is None else dataclasses.replace(op_for(i, xbuf=x_in), dst=host_dst)
-                   for i in range(LAYER_SETS)]
-        out_ptr = out_host.data_ptr()
-
-        def e2e_step(s):
-            be.upload_ptr_async(x_in, x_ptrs[s % X_POOL], nbytes)
-            be.moe_ffn(e2e_ops[s % LAYER_SETS])
-            if host_dst is None:
-                be.download_ptr_async(dst, out_ptr, nbytes)
-            be.sync()
+    def e2e_step(s):
+        # the step's result is in host memory when sync() returns
+        memmove(stage_ptr, x_ptrs[s % X_POOL], nbytes)
+        be.execute(plans[s % LAYER_SETS])
+        be.sync()
 
     for s in range(W):
         e2e_step(s)

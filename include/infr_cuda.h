@@ -86,7 +86,10 @@ int32_t infr_cuda_download(infr_cuda_ctx* ctx, const infr_cuda_buf* src, size_t 
 /* The same copies queued on the context's stream without waiting for them: the host range must
  * stay valid and unmodified (upload) or unread (download) until infr_cuda_sync returns.  No
  * counterpart in the reference's trait, whose copies are blocking; a decode step that uploads its
- * input, replays a recorded plan and downloads the result pays for one wait instead of three. */
+ * input, replays a recorded plan and downloads the result pays for one wait instead of three.
+ * A copy of up to 256 KB from or to pinned host memory (16-byte aligned) is done by a small kernel
+ * instead of the copy engine, so that the kernels queued around it can overlap their own start
+ * and a recorded plan holds kernel nodes only. */
 int32_t infr_cuda_upload_async(infr_cuda_ctx* ctx, infr_cuda_buf* dst, size_t dst_off, const void* src, size_t n);
 int32_t infr_cuda_download_async(infr_cuda_ctx* ctx, const infr_cuda_buf* src, size_t src_off, void* dst, size_t n);
 /* Backend::sync (backend.rs:1006). */

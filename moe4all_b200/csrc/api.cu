@@ -234,8 +234,16 @@ int32_t infr_cuda_upload_async(infr_cuda_ctx* ctx, infr_cuda_buf* dst, size_t ds
   if (dst_off > dst->bytes || n > dst->bytes - dst_off) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "upload: range exceeds the buffer");
   if (!n) return INFR_CUDA_OK;
   DeviceGuard g(ctx->device);
-  return check_cuda(ctx, cudaMemcpyAsync(static_cast<char*>(dst->ptr) + dst_off, src, n, cudaMemcpyHostToDevice, ctx->stream),
-                    "upload (queued)");
+  char* d = static_cast<char*>(dst->ptr) + dst_off;
+  // a few rows from pinned memory: fetched by a kernel, which the next kernel can overlap
+  static const bool by_kernel = !(getenv("INFR_UPLOAD_BY_COPY") && atoi(getenv("INFR_UPLOAD_BY_COPY")));
+  if (by_kernel && n <= (256u << 10) && n % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(d) % 16 == 0) {
+    cudaPointerAttributes at = {};
+    if (cudaPointerGetAttributes(&at, src) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer != nullptr)
+      return launch_fetch_host(ctx, at.devicePointer, d, n);
+    (void)cudaGetLastError();  // pageable memory: not an error, the copy engine takes it
+  }
+  return check_cuda(ctx, cudaMemcpyAsync(d, src, n, cudaMemcpyHostToDevice, ctx->stream), "upload (queued)");
 }
 
 int32_t infr_cuda_download_async(infr_cuda_ctx* ctx, const infr_cuda_buf* src, size_t src_off, void* dst, size_t n) {
@@ -243,8 +251,15 @@ int32_t infr_cuda_download_async(infr_cuda_ctx* ctx, const infr_cuda_buf* src, s
   if (src_off > src->bytes || n > src->bytes - src_off) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "download: range exceeds the buffer");
   if (!n) return INFR_CUDA_OK;
   DeviceGuard g(ctx->device);
-  return check_cuda(ctx, cudaMemcpyAsync(dst, static_cast<const char*>(src->ptr) + src_off, n, cudaMemcpyDeviceToHost, ctx->stream),
-                    "download (queued)");
+  const char* sp = static_cast<const char*>(src->ptr) + src_off;
+  static const bool by_kernel = !(getenv("INFR_UPLOAD_BY_COPY") && atoi(getenv("INFR_UPLOAD_BY_COPY")));
+  if (by_kernel && n <= (256u << 10) && n % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 && reinterpret_cast<uintptr_t>(sp) % 16 == 0) {
+    cudaPointerAttributes at = {};
+    if (cudaPointerGetAttributes(&at, dst) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer != nullptr)
+      return launch_store_host(ctx, sp, at.devicePointer, n);
+    (void)cudaGetLastError();
+  }
+  return check_cuda(ctx, cudaMemcpyAsync(dst, sp, n, cudaMemcpyDeviceToHost, ctx->stream), "download (queued)");
 }
 
 int32_t infr_cuda_sync(infr_cuda_ctx* ctx) {

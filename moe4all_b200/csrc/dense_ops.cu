@@ -236,6 +236,33 @@ int32_t launch_quantize_rows(infr_cuda_ctx* ctx, const float* x, int8_t* lo, int
   return check_cuda(ctx, cudaGetLastError(), "k_quantize_rows launch");
 }
 
+// Small host-to-device copies done by the SMs: pinned host memory is mapped into the device's
+// address space, so a few threads can fetch it directly.  Unlike a copy-engine transfer this is an
+// ordinary kernel in the stream: the kernel after it can be released early (programmatic dependent
+// launch) and run its own prologue, e.g. the router staging its weights, while the rows cross PCIe.
+namespace {
+__global__ void __launch_bounds__(256) k_fetch_host(const uint4* __restrict__ src, uint4* __restrict__ dst, int n16) {
+  pdl_trigger();
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n16) dst[i] = __ldcv(src + i);  // never a cached copy of host memory
+}
+}  // namespace
+
+int32_t launch_store_host(infr_cuda_ctx* ctx, const void* src, void* dst_dev_view, size_t bytes) {
+  // the same kernel the other way round: device rows written into mapped pinned host memory
+  const int n16 = (int)(bytes / 16);
+  k_fetch_host<<<(n16 + 255) / 256, 256, 0, ctx->stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst_dev_view), n16);
+  ctx->launches += 1;
+  return check_cuda(ctx, cudaGetLastError(), "k_fetch_host (store) launch");
+}
+
+int32_t launch_fetch_host(infr_cuda_ctx* ctx, const void* src_dev_view, void* dst, size_t bytes) {
+  const int n16 = (int)(bytes / 16);
+  k_fetch_host<<<(n16 + 255) / 256, 256, 0, ctx->stream>>>(static_cast<const uint4*>(src_dev_view), static_cast<uint4*>(dst), n16);
+  ctx->launches += 1;
+  return check_cuda(ctx, cudaGetLastError(), "k_fetch_host launch");
+}
+
 int32_t launch_add(infr_cuda_ctx* ctx, const float* a, const float* b, float* dst, size_t n) {
   k_add<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(a, b, dst, n);
   ctx->launches += 1;

@@ -128,5 +128,8 @@ int32_t launch_shared_add(infr_cuda_ctx* ctx, const float* moe, const float* she
 int32_t launch_rmsnorm(infr_cuda_ctx* ctx, const float* x, const float* w, float* dst, int rows, int dim, float eps);
 int32_t launch_quantize_rows(infr_cuda_ctx* ctx, const float* x, int8_t* lo, int8_t* hi, float* scale, int rows, int dim);
 int32_t launch_add(infr_cuda_ctx* ctx, const float* a, const float* b, float* dst, size_t n);
+// dst[0, bytes) = the pinned host range whose device view is src_dev_view (16-byte aligned, bytes % 16 == 0).
+int32_t launch_fetch_host(infr_cuda_ctx* ctx, const void* src_dev_view, void* dst, size_t bytes);
+int32_t launch_store_host(infr_cuda_ctx* ctx, const void* src, void* dst_dev_view, size_t bytes);
 
 }  // namespace infr
