@@ -659,6 +659,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   p.n_expert = c.n_expert;
   p.down_q4k = c.down_q4k;
   p.act_kind = c.act_kind;
+  p.gu_rows = (int)(c.gate_stride / ((size_t)c.ne / 256 * Q4K_BLOCK_BYTES));
   p.clamp = c.clamp;
   p.status = ctx->status;
   p.trace = ctx->trace;

@@ -178,6 +178,8 @@ __device__ __forceinline__ void warp_store_rows(unsigned char* patch, const uint
 constexpr int GU_SA = 3, GU_SB = 2;                          // weight stages, token stages
 constexpr uint32_t GU_A_STAGE_BYTES = 2 * A_TILE_BYTES;      // gate tile + up tile, 32 KB
 
+// GENERAL = false is the common form (SiLU, no clamp): its epilogue has no other arm.
+template <bool GENERAL>
 __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, const __grid_constant__ CUtensorMap tm_gate,
                                                              const __grid_constant__ CUtensorMap tm_up,
                                                              const __grid_constant__ CUtensorMap tm_sh_gate,
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
   const CUtensorMap* tmg = shared_seg ? &tm_sh_gate : &tm_gate;
   const CUtensorMap* tmu = shared_seg ? &tm_sh_up : &tm_up;
   // rows of one expert in the bank: nff, or 2 nff where gate and up share a bank (the up map then starts nff rows in)
-  const int bank_row0 = (shared_seg ? 0 : e * (int)(p.gate_stride / ((size_t)p.ne / 256 * Q4K_BLOCK_BYTES))) + f0;
+  const int bank_row0 = (shared_seg ? 0 : e * p.gu_rows) + f0;
   auto request_block = [&](int blk) {
     if (tid == 0) {
       mbar_arrive_expect_tx(&s_raw_full, 2 * UM * (uint32_t)Q4K_BLOCK_BYTES);
@@ -314,7 +316,8 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             const float gv = g[4 * q + t] * W_POSTSCALE, uv = u[4 * q + t] * W_POSTSCALE;
-            a[t] = fminf(fmaxf(gated_act<true>(p.act_kind, clamp, gv, uv), -65504.f), 65504.f);
+            const float av = GENERAL ? gated_act<true>(p.act_kind, clamp, gv, uv) : __fdividef(gv, 1.0f + __expf(-gv)) * uv;
+            a[t] = fminf(fmaxf(av, -65504.f), 65504.f);
           }
           const uint32_t w0 = h2_as_u32(__floats2half2_rn(a[0], a[2])), w1 = h2_as_u32(__floats2half2_rn(a[1], a[3]));
           if (q & 1) {
@@ -608,7 +611,9 @@ int32_t launch_umma_grouped(infr_cuda_ctx* ctx, const GroupedParams& p, int max_
   const size_t smem_gu = 1024 + (size_t)GU_SA * GU_A_STAGE_BYTES + (size_t)GU_SB * B_TILE_BYTES + (size_t)2 * UM * Q4K_BLOCK_BYTES;
   const size_t smem_dn = 1024 + (size_t)DN_SA * DN_W_STAGE_BYTES +
                          (p.down_q4k ? (size_t)2 * B_TILE_BYTES + (size_t)DM * Q4K_BLOCK_BYTES : (size_t)DN_SB * B_TILE_BYTES);
-  cudaError_t e = ensure_smem(reinterpret_cast<const void*>(k_umma_gateup), smem_gu);
+  const bool general = p.act_kind != INFR_CUDA_ACT_SILU || p.clamp > 0.f;
+  cudaError_t e = general ? ensure_smem(reinterpret_cast<const void*>(k_umma_gateup<true>), smem_gu)
+                          : ensure_smem(reinterpret_cast<const void*>(k_umma_gateup<false>), smem_gu);
   if (e == cudaSuccess)
     e = p.down_q4k ? ensure_smem(reinterpret_cast<const void*>(k_umma_down<true>), smem_dn)
                    : ensure_smem(reinterpret_cast<const void*>(k_umma_down<false>), smem_dn);
@@ -635,7 +640,10 @@ int32_t launch_umma_grouped(infr_cuda_ctx* ctx, const GroupedParams& p, int max_
     if (ok && p.sh_down) ok = q4k_rows_map(&tm_sh_down, p.sh_down, (size_t)p.ne, drb, DM);
   }
   if (!ok) return fail(ctx, INFR_CUDA_ERR_CUDA, "grouped GEMM: the driver refused a tensor map for the expert banks");
-  k_umma_gateup<<<dim3(p.nff / UM, max_tiles), U_THREADS, smem_gu, ctx->stream>>>(p, tm_gate, tm_up, tm_sh_gate, tm_sh_up);
+  if (general)
+    k_umma_gateup<true><<<dim3(p.nff / UM, max_tiles), U_THREADS, smem_gu, ctx->stream>>>(p, tm_gate, tm_up, tm_sh_gate, tm_sh_up);
+  else
+    k_umma_gateup<false><<<dim3(p.nff / UM, max_tiles), U_THREADS, smem_gu, ctx->stream>>>(p, tm_gate, tm_up, tm_sh_gate, tm_sh_up);
   if (p.down_q4k)
     k_umma_down<true><<<dim3(p.ne / DM, max_tiles), U_THREADS, smem_dn, ctx->stream>>>(p, tm_down, tm_sh_down);
   else

@@ -75,6 +75,7 @@ struct GroupedParams {
   int ne, nff, n_expert;
   int down_q4k;               // the down banks are Q4_K instead of Q6_K (tcgen05 kernels only)
   int act_kind;               // INFR_CUDA_ACT_*
+  int gu_rows;                // rows of one expert in the gate bank: nff, or 2 nff where gate and up share a bank
   float clamp;                // > 0: routed tiles clamp gate (from above) and up (both sides) first
 };
 
