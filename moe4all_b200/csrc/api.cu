@@ -497,10 +497,10 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   const bool small_ok = decode_ffn_supported(ctx, d->ne, d->n_ff_exp, has_sh ? d->sh_ff : 0, d->n_used, down_q4k, &why);
   uint32_t path = d->path;
   // Per (token, expert) pair the small-m kernels are cheaper than a grouped-GEMM tile until an
-  // expert sees several tokens of the call on average; measured cross-over near 120 rows for
+  // expert sees several tokens of the call on average; measured cross-over near 90 rows for
   // 256 experts, top-8.
   if (path == 0) {
-    const bool few_per_expert = (uint64_t)d->rows * d->n_used * 8 <= (uint64_t)d->n_expert * 24;  // <= 3 tokens per expert
+    const bool few_per_expert = (uint64_t)d->rows * d->n_used * 8 <= (uint64_t)d->n_expert * 22;  // <= 2.75 tokens per expert
     // experts of tens of megabytes (hidden 7168 x intermediate 2048): the small-m kernels hold one
     // chunk of rows per CTA there and the grouped GEMMs are ahead from eight rows on
     const bool big = (uint64_t)d->ne * d->n_ff_exp >= (1ull << 23);
