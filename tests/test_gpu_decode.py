@@ -244,3 +244,16 @@ def test_op_variant_refusals(backend):
         g.run(x, 4, swiglu_clamp=1.0, weight_before=True)
     with pytest.raises(Exception, match="act must be"):
         g.run(x, 4, act=2)
+
+
+@pytest.mark.parametrize("rows,n_expert", [(3, 1024), (12, 600)])
+def test_many_experts(backend, rows, n_expert):
+    # more router CTAs than SMs (the selecting CTA waits while the rest take turns), 32 experts per
+    # lane in the top-k, and with 12 rows two token groups
+    L = synth.make_layer(71, 256, n_expert, 256, router_std=0.05)
+    x = synth.activations(73, rows, 256)
+    g = GpuLayer(backend, L)
+    out, ids, wts = g.run(x, 8, path=1)
+    ref = oracle_layer(L, x, 8)
+    check_ids(ids, wts, ref, 8)
+    assert_close(out, ref.dst)
