@@ -486,21 +486,6 @@ int pick_down_tile(int ne, int nff, int sh_ff, int n_used, size_t dbb) {
   return 0;
 }
 
-template <typename K, typename... Args>
-cudaError_t launch_ex(K kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kernel, args...);
-}
-
 }  // namespace
 
 bool decode_ffn_supported(const infr_cuda_ctx*, int ne, int nff, int sh_ff, int n_used, bool down_q4k, std::string* why) {

@@ -101,18 +101,15 @@ __device__ __forceinline__ void block_scan2(int& a, int& b, int& ta, int& tb, in
   tb = s_ws[65];
 }
 
-// One CTA: exclusive scan of the per-expert counts, the tile table (one entry per 64 rows of a
-// segment, the shared expert's rows appended as segment n_expert), and the fill cursors reset.
-__global__ void __launch_bounds__(1024) k_segment_scan(const int* __restrict__ counts, int n_expert, int shared_rows, int tn,
-                                                       int* __restrict__ seg_off, int* __restrict__ fill,
-                                                       int* __restrict__ tile_expert, int* __restrict__ tile_row0,
-                                                       int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
-  __shared__ int s_cnt[1025], s_off[1026], s_toff[1026], s_ws[66];
+// Exclusive scan of the per-expert counts (thread e holds the count of segment e), the tile table
+// (one entry per `tn` rows of a segment, the shared expert's rows appended as segment n_expert) and
+// the segment offsets, by the 1024 threads of one CTA.  Offsets stay in s_off for the caller.
+__device__ __forceinline__ void segment_tables(int cnt, int n_expert, int shared_rows, int tn, int* __restrict__ seg_off,
+                                               int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                               int* __restrict__ tile_rows, int* __restrict__ n_tiles, int* s_cnt, int* s_off,
+                                               int* s_toff, int* s_ws) {
   const int tid = threadIdx.x;
   const int n_seg = n_expert + (shared_rows > 0 ? 1 : 0);
-  // thread e scans segment e; segment 1024 (only with 1024 experts and a shared segment) is
-  // appended by thread 0 afterwards
-  const int cnt = tid < n_seg ? (tid < n_expert ? counts[tid] : shared_rows) : 0;
   int off = cnt, toff = (cnt + tn - 1) / tn, total = 0, total_t = 0;
   block_scan2(off, toff, total, total_t, s_ws);
   if (tid < n_seg) {
@@ -121,6 +118,7 @@ __global__ void __launch_bounds__(1024) k_segment_scan(const int* __restrict__ c
     s_toff[tid] = toff;
   }
   if (tid == 0) {
+    // segment 1024 (only with 1024 experts and a shared segment) is appended here
     if (n_seg > 1024) {
       s_cnt[1024] = shared_rows;
       s_off[1024] = total;
@@ -135,13 +133,65 @@ __global__ void __launch_bounds__(1024) k_segment_scan(const int* __restrict__ c
   }
   __syncthreads();
   for (int e = tid; e <= n_seg; e += 1024) seg_off[e] = s_off[e];
-  for (int e = tid; e < n_expert; e += 1024) fill[e] = 0;
   for (int e = tid; e < n_seg; e += 1024) {
     const int nt = (s_cnt[e] + tn - 1) / tn;
     for (int t = 0; t < nt; ++t) {
       tile_expert[s_toff[e] + t] = e;
       tile_row0[s_toff[e] + t] = s_off[e] + t * tn;
       tile_rows[s_toff[e] + t] = min(tn, s_cnt[e] - t * tn);
+    }
+  }
+}
+
+// One CTA: the tables above from counts made by k_pair_count, and the fill cursors reset.
+__global__ void __launch_bounds__(1024) k_segment_scan(const int* __restrict__ counts, int n_expert, int shared_rows, int tn,
+                                                       int* __restrict__ seg_off, int* __restrict__ fill,
+                                                       int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                                       int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
+  __shared__ int s_cnt[1025], s_off[1026], s_toff[1026], s_ws[66];
+  const int tid = threadIdx.x;
+  const int n_seg = n_expert + (shared_rows > 0 ? 1 : 0);
+  const int cnt = tid < n_seg ? (tid < n_expert ? counts[tid] : shared_rows) : 0;
+  segment_tables(cnt, n_expert, shared_rows, tn, seg_off, tile_expert, tile_row0, tile_rows, n_tiles, s_cnt, s_off, s_toff, s_ws);
+  for (int e = tid; e < n_expert; e += 1024) fill[e] = 0;
+}
+
+// Calls of up to a few hundred thousand pairs: count, scan and scatter by one CTA with the
+// histogram and the cursors in shared memory - one launch instead of a memset and three kernels.
+__device__ __forceinline__ int bucket_of(int e, int n_expert, uint32_t ep_lo, uint32_t ep_n) {
+  if (e < 0) return -1;  // a negative id marks a pair another rank serves
+  e = min(e, n_expert - 1);
+  if (ep_n && ((uint32_t)e < ep_lo || (uint32_t)e >= ep_lo + ep_n)) return -1;
+  return e;
+}
+__global__ void __launch_bounds__(1024) k_bucket_fused(const int32_t* __restrict__ ids, int n_pairs, int n_expert, uint32_t ep_lo,
+                                                       uint32_t ep_n, int shared_rows, int tn, int* __restrict__ seg_off,
+                                                       int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                                       int* __restrict__ tile_rows, int* __restrict__ n_tiles,
+                                                       int* __restrict__ pos_of_pair, int* __restrict__ pair_of_pos) {
+  __shared__ int s_cnt[1025], s_off[1026], s_toff[1026], s_ws[66], s_hist[1024];
+  const int tid = threadIdx.x;
+  s_hist[tid] = 0;
+  __syncthreads();
+  for (int p = tid; p < n_pairs; p += 1024) {
+    const int e = bucket_of(ids[p], n_expert, ep_lo, ep_n);
+    if (e >= 0) atomicAdd(&s_hist[e], 1);
+  }
+  __syncthreads();
+  const int n_seg = n_expert + (shared_rows > 0 ? 1 : 0);
+  const int cnt = tid < n_seg ? (tid < n_expert ? s_hist[tid] : shared_rows) : 0;
+  __syncthreads();
+  s_hist[tid] = 0;  // now the fill cursors
+  segment_tables(cnt, n_expert, shared_rows, tn, seg_off, tile_expert, tile_row0, tile_rows, n_tiles, s_cnt, s_off, s_toff, s_ws);
+  __syncthreads();
+  for (int p = tid; p < n_pairs; p += 1024) {
+    const int e = bucket_of(ids[p], n_expert, ep_lo, ep_n);
+    if (e < 0) {
+      pos_of_pair[p] = -1;
+    } else {
+      const int pos = s_off[e] + atomicAdd(&s_hist[e], 1);
+      pos_of_pair[p] = pos;
+      pair_of_pos[pos] = p;
     }
   }
 }
@@ -608,13 +658,19 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   const float* row_w = c.weight_before ? c.wts : nullptr;
   if (c.ids) {
     // routed call: bucket the pairs
-    cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)(n_seg + 2) * 4, st);
-    if (e != cudaSuccess) return check_cuda(ctx, e, "grouped: memset");
-    k_pair_count<<<(c.n_pairs + 255) / 256, 256, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, counts);
-    k_segment_scan<<<1, 1024, 0, st>>>(counts, c.n_expert, c.shared_rows, tn, seg_off, fill, tile_expert, tile_row0, tile_rows, n_tiles);
-    k_pair_scatter<<<(c.n_pairs + 255) / 256, 256, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, seg_off, fill,
-                                                             pos_of_pair, pair_of_pos);
-    ctx->launches += 3;
+    if (c.n_pairs <= (1 << 16)) {
+      k_bucket_fused<<<1, 1024, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, c.shared_rows, tn, seg_off, tile_expert, tile_row0,
+                                         tile_rows, n_tiles, pos_of_pair, pair_of_pos);
+      ctx->launches += 1;
+    } else {
+      cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)(n_seg + 2) * 4, st);
+      if (e != cudaSuccess) return check_cuda(ctx, e, "grouped: memset");
+      k_pair_count<<<(c.n_pairs + 255) / 256, 256, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, counts);
+      k_segment_scan<<<1, 1024, 0, st>>>(counts, c.n_expert, c.shared_rows, tn, seg_off, fill, tile_expert, tile_row0, tile_rows, n_tiles);
+      k_pair_scatter<<<(c.n_pairs + 255) / 256, 256, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, seg_off, fill,
+                                                               pos_of_pair, pair_of_pos);
+      ctx->launches += 3;
+    }
     if (use_umma)
       k_gather_tiles<<<dim3(tn / 8, max_tiles), 256, 0, st>>>(c.x, pair_of_pos, row_w, seg_off, n_seg_routed, c.n_used, tile_row0, tile_rows,
                                                              n_tiles, tn, c.ne, reinterpret_cast<unsigned char*>(xg));

@@ -184,3 +184,16 @@ def test_expert_rows_building_block(backend):
         u_ = orc.linear(orc.DT_Q4K, L.up[e * gb:(e + 1) * gb], x[a:b], nff)
         want[a:b] = orc.linear(orc.DT_Q6K, L.down[e * db:(e + 1) * db], orc.gated_act_silu(g_, u_), ne)
     assert_close(got, want)
+
+
+def test_many_pairs(backend):
+    # past 65536 (token, expert) pairs the bucketing runs as count / scan / scatter kernels instead of
+    # the single-CTA form
+    L = synth.make_layer(43, 256, 16, 256, router_std=0.05)
+    rows = 8300
+    x = synth.activations(5, rows, 256)
+    out, ids, wts = GpuLayer(backend, L).run(x, 8, path=2)
+    ref = oracle_layer(L, x, 8)
+    ties = ids_match(ids, ref, 8)
+    keep = [r for r in range(rows) if r not in ties]
+    assert_close(out[keep], ref.dst[keep])
