@@ -173,9 +173,16 @@ __global__ void __launch_bounds__(1024) k_bucket_fused(const int32_t* __restrict
   const int tid = threadIdx.x;
   s_hist[tid] = 0;
   __syncthreads();
-  for (int p = tid; p < n_pairs; p += 1024) {
-    const int e = bucket_of(ids[p], n_expert, ep_lo, ep_n);
-    if (e >= 0) atomicAdd(&s_hist[e], 1);
+  // eight ids per thread in flight: the loop is a chain of global-memory latencies otherwise
+  for (int p0 = tid; p0 < n_pairs; p0 += 8 * 1024) {
+    int idv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) idv[u] = p0 + u * 1024 < n_pairs ? ids[p0 + u * 1024] : -1;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int e = bucket_of(idv[u], n_expert, ep_lo, ep_n);
+      if (e >= 0) atomicAdd(&s_hist[e], 1);
+    }
   }
   __syncthreads();
   const int n_seg = n_expert + (shared_rows > 0 ? 1 : 0);
@@ -184,14 +191,22 @@ __global__ void __launch_bounds__(1024) k_bucket_fused(const int32_t* __restrict
   s_hist[tid] = 0;  // now the fill cursors
   segment_tables(cnt, n_expert, shared_rows, tn, seg_off, tile_expert, tile_row0, tile_rows, n_tiles, s_cnt, s_off, s_toff, s_ws);
   __syncthreads();
-  for (int p = tid; p < n_pairs; p += 1024) {
-    const int e = bucket_of(ids[p], n_expert, ep_lo, ep_n);
-    if (e < 0) {
-      pos_of_pair[p] = -1;
-    } else {
-      const int pos = s_off[e] + atomicAdd(&s_hist[e], 1);
-      pos_of_pair[p] = pos;
-      pair_of_pos[pos] = p;
+  for (int p0 = tid; p0 < n_pairs; p0 += 8 * 1024) {
+    int idv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) idv[u] = p0 + u * 1024 < n_pairs ? ids[p0 + u * 1024] : -1;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int p = p0 + u * 1024;
+      if (p >= n_pairs) break;
+      const int e = bucket_of(idv[u], n_expert, ep_lo, ep_n);
+      if (e < 0) {
+        pos_of_pair[p] = -1;
+      } else {
+        const int pos = s_off[e] + atomicAdd(&s_hist[e], 1);
+        pos_of_pair[p] = pos;
+        pair_of_pos[pos] = p;
+      }
     }
   }
 }
