@@ -513,13 +513,7 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, u
   const int sh_ff = has_sh ? p.sh_ff : 0;
   const int n_chunks = pick_chunks(p.ne, p.nff, sh_ff);
   const size_t dbb = p.down_q4k ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES;
-  int TI = pick_down_tile(p.ne, p.nff, sh_ff, p.n_used, dbb);
-  {
-    static const int ti_big = getenv("INFR_DN_TILE") ? atoi(getenv("INFR_DN_TILE")) : 0;
-    if (ti_big > 0 && TI > ti_big && p.rows * (p.ne / TI) > 4 * ctx->sm_count && p.ne % ti_big == 0 &&
-        ((size_t)ti_big * (p.nff / 256) * dbb) % 16 == 0 && (!sh_ff || ((size_t)ti_big * (sh_ff / 256) * dbb) % 16 == 0))
-      TI = ti_big;
-  }
+  const int TI = pick_down_tile(p.ne, p.nff, sh_ff, p.n_used, dbb);
   if (!n_chunks || !TI) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "small-m path: tile does not fit shared memory");
   int gw = GU_WARPS;
   int TR = gw * n_chunks;
