@@ -44,6 +44,7 @@ extern "C" {
 #define INFR_CUDA_GATING_SIGMOID 1
 #define INFR_CUDA_ACT_SILU 0 /* g / (1 + exp(-g)) */
 #define INFR_CUDA_ACT_GELU 1 /* 0.5 g (1 + tanh(0.7978846 (g + 0.044715 g^3))), kernels.rs:6664-6669 */
+#define INFR_CUDA_ACT_SIGMOID 2 /* 1 / (1 + exp(-g)); no clamp with it, as in the reference (lib.rs:3613-3619) */
 #define INFR_CUDA_GATING_SQRT_SOFTPLUS 2 /* sqrt(ln(1 + exp(v))), v itself above 20 (infr-cpu lib.rs:3760-3774) */
 
 typedef struct infr_cuda_ctx infr_cuda_ctx; /* opaque: device, stream, scratch */

@@ -46,7 +46,7 @@ enum class MoeGating : uint32_t {
   Sigmoid = INFR_CUDA_GATING_SIGMOID,
   SqrtSoftplus = INFR_CUDA_GATING_SQRT_SOFTPLUS
 };
-enum class Activation : uint32_t { Silu = INFR_CUDA_ACT_SILU, Gelu = INFR_CUDA_ACT_GELU };
+enum class Activation : uint32_t { Silu = INFR_CUDA_ACT_SILU, Gelu = INFR_CUDA_ACT_GELU, Sigmoid = INFR_CUDA_ACT_SIGMOID };
 
 // What a MoE-only backend reports (backend.rs:45-236): everything off except in-place graph inputs.
 struct Capabilities {

@@ -74,6 +74,7 @@ class Activation(enum.IntEnum):
     """crates/infr-core/src/graph.rs Activation; the gated forms of crates/infr-cpu/src/kernels.rs:6662-6683."""
     Silu = 0
     Gelu = 1
+    Sigmoid = 2
 
 
 class _Desc(C.Structure):

@@ -390,7 +390,8 @@ static int32_t validate_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d)
     if (d->ne > 8192) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: the RmsNorm fusion covers ne <= 8192");
   }
   if (d->residual && !fits(d->residual, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: residual too small");
-  if (d->act != INFR_CUDA_ACT_SILU && d->act != INFR_CUDA_ACT_GELU) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: act must be SiLU or GELU");
+  if (d->act > INFR_CUDA_ACT_SIGMOID) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: act must be SiLU, GELU or Sigmoid");
+  if (d->act == INFR_CUDA_ACT_SIGMOID && d->swiglu_clamp > 0.0f) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: swiglu_clamp excludes the Sigmoid activation");
   if (!(d->swiglu_clamp >= 0.0f)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: swiglu_clamp must be positive, or 0 for none");
   // the reference defines the clamp for the output-weighted forms only (crates/infr-cpu/src/lib.rs:3613-3619)
   if (d->swiglu_clamp > 0.0f && d->weight_before) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: swiglu_clamp excludes weight_before");

@@ -232,8 +232,13 @@ __device__ __forceinline__ float gated_act(int act, float clamp, float g, float 
     g = fminf(g, clamp);
     u = fminf(fmaxf(u, -clamp), clamp);
   }
-  const float a = act == INFR_CUDA_ACT_GELU ? 0.5f * g * (1.0f + tanhf(0.7978846f * (g + 0.044715f * g * g * g)))
-                                            : (FAST_DIV ? __fdividef(g, 1.0f + __expf(-g)) : g / (1.0f + __expf(-g)));
+  float a;
+  if (act == INFR_CUDA_ACT_GELU)
+    a = 0.5f * g * (1.0f + tanhf(0.7978846f * (g + 0.044715f * g * g * g)));
+  else if (act == INFR_CUDA_ACT_SIGMOID)
+    a = 1.0f / (1.0f + __expf(-g));
+  else
+    a = FAST_DIV ? __fdividef(g, 1.0f + __expf(-g)) : g / (1.0f + __expf(-g));
   return a * u;
 }
 

@@ -249,7 +249,7 @@ struct orc_moe_desc {
   int32_t threads;
   const int32_t* expert_ids;  // [rows, n_used] selection made by the caller (hash-routed layers), or null
   const float* down_scale;    // [n_expert] scale on an expert's down output before the weighted sum, or null
-  uint32_t act;               // 0 SiLU, 1 GELU (tanh form)
+  uint32_t act;               // 0 SiLU, 1 GELU (tanh form), 2 Sigmoid
   uint32_t weight_before;     // routing weight applied to gate and up before the activation
   float swiglu_clamp;         // > 0: act(min(gate, l)) * clamp(up, -l, l)
   uint32_t fused_gate_up;     // gate_exps holds [n_expert, 2*n_ff_exp, ne]: gate rows then up rows; up_exps unused
@@ -351,6 +351,7 @@ static void route_row(const orc_moe_desc* d, const float* logits, const int32_t*
 // act_fn / gated_act_fn (crates/infr-cpu/src/kernels.rs:6662-6683).
 static inline float act_value(uint32_t act, float g) {
   if (act == 1) return 0.5f * g * (1.0f + std::tanh(0.7978846f * (g + 0.044715f * g * g * g)));
+  if (act == 2) return 1.0f / (1.0f + std::exp(-g));
   return silu(g);
 }
 static inline float gated_act_value(uint32_t act, float clamp, float gate, float up) {
@@ -370,7 +371,7 @@ int orc_moe_ffn(const orc_moe_desc* d) {
   if (!rrb || !grb || !urb || !drb) return -2;
   const int T = d->threads > 0 ? d->threads : orc_hw_threads();
   // the clamp is defined for the gated SiLU / GELU forms without weight_before (lib.rs:3613-3619)
-  if (d->act > 1 || (d->swiglu_clamp > 0.0f && d->weight_before)) return -3;
+  if (d->act > 2 || (d->swiglu_clamp > 0.0f && (d->weight_before || d->act == 2))) return -3;
   if (d->expert_ids) {
     // the reference refuses a bias or groups beside given ids (graph.rs:1304-1308) and panics on an
     // id past n_expert (lib.rs:3782-3788)

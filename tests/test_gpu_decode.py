@@ -216,6 +216,7 @@ VARIANTS = {
     "down_scale": dict(down_scale=np.linspace(0.5, 1.5, 32).astype(np.float32)),
     "gelu_clamp_scale": dict(act=1, swiglu_clamp=0.08, down_scale=np.linspace(1.5, 0.25, 32).astype(np.float32)),
     "fused_gate_up": dict(fused_gate_up=True, act=1),
+    "sigmoid_act": dict(act=2),
 }
 
 
@@ -243,7 +244,7 @@ def test_op_variant_refusals(backend):
     with pytest.raises(Exception, match="swiglu_clamp excludes weight_before"):
         g.run(x, 4, swiglu_clamp=1.0, weight_before=True)
     with pytest.raises(Exception, match="act must be"):
-        g.run(x, 4, act=2)
+        g.run(x, 4, act=3)
 
 
 @pytest.mark.parametrize("rows,n_expert", [(3, 1024), (12, 600)])

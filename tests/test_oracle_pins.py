@@ -221,7 +221,8 @@ def moe_ref_numpy(x, router, gate, up, down, ne, n_expert, n_used, nff, scale, g
     out = np.zeros(ne, F32)
     silu = lambda z: F32(z / (F32(1) + np.exp(-z, dtype=F32)))
     gelu = lambda z: F32(F32(0.5) * z * (F32(1) + np.tanh(F32(0.7978846) * (z + F32(0.044715) * z * z * z), dtype=F32)))
-    fn = silu if act == "silu" else gelu
+    sigm = lambda z: F32(F32(1) / (F32(1) + np.exp(-z, dtype=F32)))
+    fn = {"silu": silu, "gelu": gelu, "sigmoid": sigm}[act]
 
     def gated(g, u):  # gated_act_fn, crates/infr-cpu/src/kernels.rs:6671-6683
         if clamp is not None:
@@ -253,7 +254,7 @@ def run_f32_case(lead, salts, gating, gname, bias=None, groups=0, groups_used=0,
                       gate_dtype=orc.DT_F32, up_dtype=orc.DT_F32, down_dtype=orc.DT_F32, gating=gating,
                       bias=bias, groups=groups, groups_used=groups_used, threads=2,
                       expert_ids=None if given is None else np.asarray(given, np.int32).reshape(1, n_used),
-                      act=1 if variant.get("act") == "gelu" else 0, swiglu_clamp=variant.get("clamp") or 0.0,
+                      act={None: 0, "gelu": 1, "sigmoid": 2}[variant.get("act")], swiglu_clamp=variant.get("clamp") or 0.0,
                       weight_before=variant.get("weight_before", False), down_scale=variant.get("down_scale"))
     want, idx = moe_ref_numpy(x[0], router, gate, up, down, ne, n_expert, n_used, nff, 1.0, gname, bias, groups, groups_used, given,
                               **variant)
@@ -304,11 +305,12 @@ def test_hash_routing_vector():
 
 @pytest.mark.parametrize("variant", [
     dict(act="gelu"),
+    dict(act="sigmoid"),
     dict(clamp=0.02),                 # DeepSeek-V4 swiglu_clamp: act(min(g, l)) * clamp(u, -l, l)
     dict(weight_before=True),         # llama4: routing weight on gate and up before the activation
     dict(down_scale=np.array([0.5, 2.0, 1.5, 1.0, 0.25, 3.0], F32)),  # diffusion-gemma ffn_down_exps.scale
     dict(act="gelu", clamp=0.03, down_scale=np.array([2.0, 0.5, 1.5, 1.0, 0.25, 3.0], F32)),
-], ids=["gelu", "clamp", "weight_before", "down_scale", "gelu_clamp_scale"])
+], ids=["gelu", "sigmoid", "clamp", "weight_before", "down_scale", "gelu_clamp_scale"])
 def test_op_variant_vectors(variant):
     # the remaining Op::MoeFfn forms against a from-definition restatement (crates/infr-cpu/src/lib.rs:
     # 4144-4181 gate/up with weight_before and the clamp, :4246-4258 down_scale, :4287-4303 the sum;
