@@ -84,6 +84,8 @@ int32_t drain_and_poll(infr_cuda_ctx* ctx, const char* what) {
   if (tag || bad) {
     st->timeout = 0;
     st->bad_index = 0;
+    // a router launch that gave up may have left logits behind: every word back to "not written yet"
+    if (tag && ctx->route_logits) cudaMemset(ctx->route_logits, 0xFF, ROUTE_LOGIT_BYTES);
     if (tag) {
       char msg[96];
       std::snprintf(msg, sizeof msg, "a bounded device-side wait ran out (kernel tag %d); outputs of that call are invalid", tag);
@@ -122,7 +124,9 @@ int32_t infr_cuda_create(int32_t device, infr_cuda_ctx** out) {
       cudaHostAlloc(reinterpret_cast<void**>(&ctx->status_host), sizeof(DeviceStatus), cudaHostAllocMapped) != cudaSuccess ||
       cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->status), ctx->status_host, 0) != cudaSuccess ||
       cudaMalloc(&ctx->counters, 64 * sizeof(unsigned int)) != cudaSuccess ||
-      cudaMemset(ctx->counters, 0, 64 * sizeof(unsigned int)) != cudaSuccess) {
+      cudaMemset(ctx->counters, 0, 64 * sizeof(unsigned int)) != cudaSuccess ||
+      cudaMalloc(&ctx->route_logits, ROUTE_LOGIT_BYTES) != cudaSuccess ||
+      cudaMemset(ctx->route_logits, 0xFF, ROUTE_LOGIT_BYTES) != cudaSuccess) {
     infr_cuda_destroy(ctx);
     return INFR_CUDA_ERR_CUDA;
   }
@@ -139,6 +143,7 @@ void infr_cuda_destroy(infr_cuda_ctx* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->counters) cudaFree(ctx->counters);
+  if (ctx->route_logits) cudaFree(ctx->route_logits);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
 }

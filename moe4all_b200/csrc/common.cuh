@@ -56,6 +56,8 @@ struct infr_cuda_ctx {
   infr::DeviceStatus* status = nullptr;       // the device's address of the status words below
   infr::DeviceStatus* status_host = nullptr;  // pinned, mapped host memory: kernels write it directly when they flag something
   unsigned int* counters = nullptr;           // device memory: completion counters (zeroed by users)
+  float* route_logits = nullptr;              // device memory: the whole-row router kernel's logit buffer, all words
+                                              // "not written yet" between launches (see ROUTE_LOGIT_EMPTY)
   unsigned long long* trace = nullptr;        // optional phase stamps (see trace_stamp)
 };
 

@@ -10,6 +10,10 @@ namespace infr {
 constexpr int ROUTE_SMALL_MAX_ROWS = 8;
 constexpr int ROUTE_SMALL_MAX_GROUPS = 64;
 constexpr int ROUTE_SMALL_LIMIT = 64;
+// Marker of a logit that has not been written yet: a NaN pattern no arithmetic result has (the
+// hardware's NaN results are 0x7FFFFFFF).  The whole-row kernel's logit buffer holds it between launches.
+constexpr uint32_t ROUTE_LOGIT_EMPTY = 0xFFFFFFFFu;
+constexpr size_t ROUTE_LOGIT_BYTES = (size_t)ROUTE_SMALL_LIMIT * 1024 * sizeof(float);  // rows x experts (at most 1024)
 
 struct RouteParams {
   const float* router_x;     // [rows, ne]
@@ -20,7 +24,7 @@ struct RouteParams {
   const int32_t* given_ids;  // [rows, n_used] selection made by the caller, or null (top-k)
   const float* rms_w;        // [ne] RmsNorm weight applied to x before everything else, or null
   float rms_eps;
-  float* logits;             // [rows, n_expert] scratch
+  float* logits;             // [rows, n_expert] scratch (whole-row kernel: every word ROUTE_LOGIT_EMPTY on entry and on exit)
   float* sh_logit;           // [rows] scratch
   int32_t* ids;              // [rows, n_used]
   float* wts;                // [rows, n_used]
