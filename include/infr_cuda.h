@@ -205,8 +205,8 @@ int32_t infr_cuda_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* de
  * optionally receive the error text.
  *
  * The first call on a device looks up the device address of the array (cudaGetSymbolAddress) with
- * that device current.  Every call shares the one array: it keeps the previous call's logits (each call overwrites the part it
- * uses and clears its counter first), and two calls that overlap on the GPU race on it - keep
+ * that device current.  Every call shares the one array (each call first resets the part it uses,
+ * two small memsets queued on the stream), and two calls that overlap on the GPU race on it - keep
  * calls on one device ordered on one stream. */
 int32_t infr_cuda_moe_route_noalloc(int32_t device, void* cuda_stream, const float* router_x, const float* router,
                                     const float* exp_probs_b, int32_t* ids_out, float* wts_out, uint32_t rows,
