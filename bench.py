@@ -441,6 +441,32 @@ def run_stack(args):
     ms = timed(torch, dist, world, lambda s: st.replay(), K)
     launches = be.launch_count() - l0
     clocks = sampler.stop()
+    # end to end: the step's hidden rows come from pinned host memory and go back there, one wait per step
+    nbytes = R * NE * 4
+    x_host = torch.randn(8, R, NE).pin_memory()
+    out_host = torch.empty(R, NE).pin_memory()
+    hid = st.b_hidden
+    e2e_steps = min(K, 200)
+
+    def e2e_step(s):
+        be.upload_ptr_async(hid, x_host[s % 8].data_ptr(), nbytes)
+        st.replay()
+        be.download_ptr_async(hid, out_host.data_ptr(), nbytes)
+        be.sync()
+
+    for s in range(3):
+        e2e_step(s)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for s in range(e2e_steps):
+        e2e_step(s)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t[0])
     if rank == 0:
         peaks, kind = measured_peaks()
         active = (u + NL) * EXPERT_BYTES
@@ -454,6 +480,8 @@ def run_stack(args):
             "active_expert_gbs": world * active / (us * 1e-6) / 1e9,
             "roofline": {"bound": "hbm", "kernel": "whole step", "achieved": active / (us * 1e-6) / 1e9, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": active / (us * 1e-6) / 1e9 / peaks["hbm_gbs"], "peak_kind": kind, "traffic": None},
+            "e2e": {"value": world * R * e2e_steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": nbytes,
+                    "d2h_bytes_per_step": nbytes, "steps": e2e_steps},
             "gpu_launches": launches, "clocks": clocks}))
     if world > 1:
         dist.destroy_process_group()
