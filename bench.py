@@ -541,6 +541,33 @@ def run_prefill(args):
     ms = timed(torch, dist, world, step, K)
     launches = be.launch_count() - l0
     clocks = sampler.stop()
+    # end to end: this rank's token rows come from pinned host memory and the results go back there
+    # (copy-engine transfers at this size), one host wait per step
+    nbytes = rows * ne * 4
+    x_pin = x.cpu().pin_memory()
+    out_pin = torch.empty(rows, ne).pin_memory()
+    xb, db = be.wrap_tensor(x), be.wrap_tensor(dst)
+    e2e_steps = min(K, 20)
+
+    def e2e_step(s):
+        be.upload_ptr_async(xb, x_pin.data_ptr(), nbytes)
+        out = step(s)
+        be.download_ptr_async(db if world == 1 else be.wrap_tensor(out), out_pin.data_ptr(), nbytes)
+        be.sync()
+
+    for s in range(2):
+        e2e_step(s)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for s in range(e2e_steps):
+        e2e_step(s)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        tt = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_s = float(tt[0])
     if rank == 0:
         peaks, kind = measured_peaks()
         flops = 3 * 2 * T * n_used * ne * n_ff  # routed experts only (2*pairs*K*N per GEMM)
@@ -557,6 +584,8 @@ def run_prefill(args):
             "roofline": {"bound": "tensor", "kernel": "whole step (router + permute + grouped GEMMs + combine)", "achieved": tfl,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tfl / peaks["bf16_tflops"], "peak_kind": kind,
                          "traffic": None},
+            "e2e": {"value": flops * e2e_steps / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": nbytes,
+                    "d2h_bytes_per_step": nbytes, "steps": e2e_steps},
             "gpu_launches": launches, "clocks": clocks}))
     if world > 1:
         dist.destroy_process_group()
