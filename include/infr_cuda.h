@@ -66,6 +66,35 @@ const char* infr_cuda_name(void);
  * kernels with its own work.  No counterpart in the reference (Vulkan queues are internal). */
 int32_t infr_cuda_set_stream(infr_cuda_ctx* ctx, void* cuda_stream);
 
+/* Tuning switches of a context, a plain struct read and written as a whole (the reference folds its
+ * kernel knobs into one typed `Config`, crates/infr-core/src/config/mod.rs:1-29; its path choice is
+ * `kernels.vulkan.moe_small_m`, crates/infr-vulkan/src/adapter.rs:253-287).  Nothing in the library
+ * reads the environment.  `infr_cuda_get_config` returns the defaults on a fresh context; every
+ * field has a working default and none changes results beyond the stated tolerances. */
+typedef struct infr_cuda_config {
+  uint32_t gu_warps, gu_chunks;  /* per-pair gate/up kernel on grids of more than four waves: warps per CTA
+                                    and row chunks per CTA (default 4 x 4); 0 = keep the one-wave shape   */
+  uint32_t dn_warps;             /* per-pair down kernel on grids of more than four waves: warp cap
+                                    (default 12); 0 = no cap                                              */
+  uint32_t upload_by_copy;       /* 1: small pinned-memory copies of the *_async calls go through the copy
+                                    engine instead of a fetch kernel (default 0)                          */
+  uint32_t trace_tile;           /* tile whose CTAs write phase stamps in the tcgen05 kernels (default 0)  */
+  uint32_t expert_major;         /* small-m path, who owns a CTA: 0 = choose by rows (default), 1 = always
+                                    one (token, expert) pair per CTA, 2 = always one expert with all of
+                                    its tokens per CTA (int8 tensor-core tiles)                           */
+  uint32_t topk_cta;             /* whole-row router: 0 = choose (default), 1 = one warp per token does the
+                                    top-k, 2 = all warps of the selecting CTA share one token's top-k    */
+  uint32_t dense_min_tiles;      /* batched path: experts with at least this many 256-token tiles are
+                                    unpacked to f16 once per call and fed to the tensor cores by tiled
+                                    copies; 0 = never (default 2)                                         */
+  uint32_t sync_timeout_ms;      /* expert-parallel contexts: how long infr_cuda_sync waits for the stream
+                                    before it aborts the communicator and returns INFR_CUDA_ERR_NCCL
+                                    (default 60000)                                                       */
+  uint32_t reserved[7];          /* zero                                                                  */
+} infr_cuda_config;
+int32_t infr_cuda_get_config(const infr_cuda_ctx* ctx, infr_cuda_config* out);
+int32_t infr_cuda_set_config(infr_cuda_ctx* ctx, const infr_cuda_config* cfg);
+
 /* ---- buffers: Backend::alloc / alloc_uninit / upload / download / sync ------------------------ */
 
 /* Backend::alloc (backend.rs:652; zero-initialised, the calloc contract of :647-651) when
@@ -98,10 +127,11 @@ int32_t infr_cuda_sync(infr_cuda_ctx* ctx);
 
 /* ---- Op::MoeFfn ------------------------------------------------------------------------------ */
 
-/* Mirrors Op::MoeFfn (crates/infr-core/src/graph.rs:1259-1352) for the forms on the hot path:
- * split gate/up banks, SiLU, output-side weighting (`weight_before` = false), no `down_scale`,
- * no hash-routed `expert_ids`, no SwiGLU clamp.  Banks are `[n_expert, out_f, in_f]` row-major,
- * expert e = the e-th equal byte slice (graph.rs:1257-1258).
+/* Mirrors Op::MoeFfn (crates/infr-core/src/graph.rs:1259-1352), every field of it: split or fused
+ * gate/up banks, SiLU / GELU / Sigmoid, routing weight on the output or on the input
+ * (`weight_before`), `down_scale`, caller-selected `expert_ids`, SwiGLU clamp, `ep_band`.  Banks are
+ * `[n_expert, out_f, in_f]` row-major, expert e = the e-th equal byte slice (graph.rs:1257-1258);
+ * a bank buffer needs exactly that many bytes - no kernel reads past a bank's last block.
  *
  * The shared expert of qwen35moe / DeepSeek (graph builder: crates/infr-llama/src/seam/runner.rs:
  * 8088-8175) can ride in the same call: when `sh_gate` is non-NULL the result is
@@ -196,18 +226,23 @@ int32_t infr_cuda_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* de
  * memory to its own pool (a late cudaMalloc there simply fails), or a latency-critical loop that
  * cannot afford the device-wide synchronisation an allocation implies.  `infr_cuda_moe_route`
  * grows per-context scratch on demand; this variant does the same computation (router logits in
- * the CPU's accumulation order, gating, top-k, routing weights) with its scratch in a fixed array
- * inside the library image: 8 rows x 1024 experts of f32 logits plus a counter, 33 KB, held by
- * every GPU that loads the library until the process exits.  Larger calls are rejected with
- * INFR_CUDA_ERR_INVALID_ARG and a message; nothing here calls cudaMalloc, cudaFree or any
- * allocating routine.  All arguments are plain device pointers (inputs and outputs stay the
- * caller's); `cuda_stream` is a cudaStream_t (NULL = the legacy default stream); `err`/`err_cap`
- * optionally receive the error text.
+ * the CPU's accumulation order, softmax / sigmoid / sqrt-softplus gating, bias, expert groups,
+ * top-k, routing weights) with its scratch in a fixed array inside the library image: 8 rows x
+ * 1024 experts of f32 logits, 32 KB, held by every GPU that loads the library until the process
+ * exits.  Larger calls are rejected with INFR_CUDA_ERR_INVALID_ARG and a message; nothing here
+ * calls cudaMalloc, cudaFree or any allocating routine.  All arguments are plain device pointers
+ * (inputs and outputs stay the caller's); `cuda_stream` is a cudaStream_t (NULL = the legacy
+ * default stream); `err`/`err_cap` optionally receive the error text.
  *
  * The first call on a device looks up the device address of the array (cudaGetSymbolAddress) with
- * that device current.  Every call shares the one array (each call first resets the part it uses,
- * two small memsets queued on the stream), and two calls that overlap on the GPU race on it - keep
- * calls on one device ordered on one stream. */
+ * that device current; make that first call before any stream capture.  Every call shares the one
+ * array (each call first resets the part it uses with a memset queued on the stream), and two calls
+ * that overlap on the GPU race on it - keep calls on one device ordered on one stream.
+ *
+ * There is no context whose next sync could report a device-side failure, so the outputs carry it:
+ * the call queues a fill of `ids_out` with -1 ahead of the kernel.  The kernel's only wait (for the
+ * logits of its own grid) is bounded; if it ever gives up, the ids are still -1 when the stream has
+ * drained and `wts_out` is unchanged.  An id of -1 therefore means "this call produced nothing". */
 int32_t infr_cuda_moe_route_noalloc(int32_t device, void* cuda_stream, const float* router_x, const float* router,
                                     const float* exp_probs_b, int32_t* ids_out, float* wts_out, uint32_t rows,
                                     uint32_t ne, uint32_t n_expert, uint32_t n_used, float scale, uint32_t gating,
@@ -235,7 +270,49 @@ int32_t infr_cuda_rmsnorm(infr_cuda_ctx* ctx, const infr_cuda_buf* x, const infr
 int32_t infr_cuda_add(infr_cuda_ctx* ctx, const infr_cuda_buf* a, const infr_cuda_buf* b, infr_cuda_buf* dst,
                       size_t n);
 
-/* ---- expert-parallel building blocks (crates/infr-vulkan/src/ep.rs:454-493) ------------------- */
+/* ---- expert parallelism (crates/infr-vulkan/src/ep.rs:1-53, 156-505) ---------------------------- */
+
+/* The reference's ExpertParallelBackend gives rank r the contiguous expert band
+ * [r*E/W, (r+1)*E/W) (ep.rs:12-14, 171-176), runs every band's partial per MoE layer and sums the
+ * partials in fixed rank order (ep.rs:454-493).  Here the ranks are processes, one per GPU, joined by
+ * an NCCL communicator that the library owns; the tokens are sharded over the ranks as well.
+ *
+ *   rank 0:      infr_cuda_ep_unique_id(id)          (ncclGetUniqueId; 128 bytes, passed to the other
+ *                                                    ranks by the host's own means)
+ *   every rank:  infr_cuda_ep_init(ctx, id, rank, world)
+ *
+ * After that, a call of infr_cuda_moe_ffn whose descriptor carries this rank's band
+ * (ep_lo == rank * n_expert / world, ep_n_local == n_expert / world) is a COLLECTIVE call: every
+ * rank makes it, in the same order, with the same `rows`, ne, n_expert, n_used and n_ff_exp.  `x`,
+ * `dst` (and residual, ids_out, wts_out) are this rank's `rows` token rows; router, exp_probs_b and
+ * the shared expert are replicated; gate_exps / up_exps / down_exps hold ONLY the band's
+ * ep_n_local experts.  Inside the call: routing of the rank's own rows, dispatch of rows, ids and
+ * weights to the ranks (fixed-capacity slots of `rows` rows per pair of ranks, so that no count has to
+ * come back to the host), the band's experts over everything received, the partial sums back to the
+ * tokens' home ranks, and there the sum over ranks in rank order, then the shared expert (computed
+ * on a side stream while the exchanges run) and the residual.  Results equal the single-device op
+ * up to the association of that sum.  A descriptor without a band, or with another rank's band,
+ * runs locally as before (the reference's replicated form: full banks, ids global).
+ *
+ * Failures: a rank that passes a different shape is detected before anything is exchanged (the
+ * first call with a new shape compares the shapes of all ranks) and every rank gets
+ * INFR_CUDA_ERR_NCCL; an NCCL call that fails, or a stream that does not drain within
+ * `sync_timeout_ms` (a peer never arrived), aborts the communicator (ncclCommAbort) and returns
+ * INFR_CUDA_ERR_NCCL from that call or from infr_cuda_sync.  After an abort the context runs
+ * local calls only.  NCCL is loaded at run time (libnccl.so.2); without it ep_init returns
+ * INFR_CUDA_ERR_UNSUPPORTED and everything else works. */
+#define INFR_CUDA_EP_ID_BYTES 128
+int32_t infr_cuda_ep_unique_id(uint8_t id[INFR_CUDA_EP_ID_BYTES]);
+int32_t infr_cuda_ep_init(infr_cuda_ctx* ctx, const uint8_t id[INFR_CUDA_EP_ID_BYTES], int32_t rank, int32_t world);
+/* Leaves the communicator (ncclCommDestroy after the stream has drained); collective like init. */
+int32_t infr_cuda_ep_finalize(infr_cuda_ctx* ctx);
+/* Time stamps of the last expert-parallel call's phases on this rank, in milliseconds from the
+ * call's first kernel: [0] routing done, [1] dispatch received, [2] band experts done, [3] partials
+ * received, [4] result written.  Waits for the stream.  The reference's analogue is the `[prof-moe]`
+ * breakdown of crates/infr-cpu/src/lib.rs:4267-4285. */
+int32_t infr_cuda_ep_last_phases(infr_cuda_ctx* ctx, float ms_out[5]);
+
+/* ---- expert-parallel building blocks for hosts that run the exchange themselves ---------------- */
 
 /* Expert FFN over rows that are already grouped by expert: rows [seg_off[e], seg_off[e+1]) of
  * `x_rows` go through local expert e (gate/up → SwiGLU → down) and land in the same rows of

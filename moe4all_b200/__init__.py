@@ -8,5 +8,5 @@ interface for that path: `CudaBackend` follows `infr_core::backend::Backend`
 every call raises.
 """
 from .backend import (  # noqa: F401
-    Activation, BackendError, Buffer, CudaBackend, DType, MoeFfn, MoeGating, Unsupported, load_library,
+    Activation, BackendError, Buffer, Config, CudaBackend, DType, MoeFfn, MoeGating, Unsupported, load_library,
 )

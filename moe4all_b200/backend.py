@@ -32,6 +32,8 @@ EXPORTS = [
     "infr_cuda_gated_act", "infr_cuda_moe_shared_add", "infr_cuda_rmsnorm", "infr_cuda_add",
     "infr_cuda_moe_expert_rows", "infr_cuda_launch_count",
     "infr_cuda_graph_begin", "infr_cuda_graph_end", "infr_cuda_graph_launch", "infr_cuda_graph_free", "infr_cuda_set_trace", "infr_cuda_moe_route_noalloc", "infr_cuda_moe_combine", "infr_cuda_umma_selftest",
+    "infr_cuda_get_config", "infr_cuda_set_config",
+    "infr_cuda_ep_unique_id", "infr_cuda_ep_init", "infr_cuda_ep_finalize", "infr_cuda_ep_last_phases",
 ]
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_OOM, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6
@@ -98,6 +100,18 @@ class _Desc(C.Structure):
     ]
 
 
+class Config(C.Structure):
+    """`infr_cuda_config`: the context's tuning switches (the reference's typed kernel config,
+    crates/infr-core/src/config/mod.rs:1-29)."""
+    _fields_ = [
+        ("gu_warps", C.c_uint32), ("gu_chunks", C.c_uint32), ("dn_warps", C.c_uint32), ("upload_by_copy", C.c_uint32),
+        ("trace_tile", C.c_uint32), ("expert_major", C.c_uint32), ("topk_cta", C.c_uint32), ("dense_min_tiles", C.c_uint32),
+        ("sync_timeout_ms", C.c_uint32), ("reserved", C.c_uint32 * 7),
+    ]
+
+
+EP_ID_BYTES = 128
+
 _lib = None
 
 
@@ -153,6 +167,12 @@ def load_library(path: Optional[str] = None):
     L.infr_cuda_moe_combine.argtypes = [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32]
     L.infr_cuda_moe_route_noalloc.argtypes = [i32, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, C.c_float, u32, u32, u32, u32,
                                               C.c_char_p, sz]
+    L.infr_cuda_get_config.argtypes = [vp, C.POINTER(Config)]
+    L.infr_cuda_set_config.argtypes = [vp, C.POINTER(Config)]
+    L.infr_cuda_ep_unique_id.argtypes = [C.c_char_p]
+    L.infr_cuda_ep_init.argtypes = [vp, C.c_char_p, i32, i32]
+    L.infr_cuda_ep_finalize.argtypes = [vp]
+    L.infr_cuda_ep_last_phases.argtypes = [vp, C.POINTER(C.c_float)]
     L.infr_cuda_launch_count.argtypes = [vp]
     L.infr_cuda_launch_count.restype = C.c_uint64
     for name in EXPORTS:
@@ -382,6 +402,48 @@ class CudaBackend:
         b._n = a.nbytes
         self.upload(b, a)
         return b
+
+    # -- tuning switches ------------------------------------------------------------------------
+    def get_config(self) -> Config:
+        c = Config()
+        self._check(self._lib.infr_cuda_get_config(self._ctx, C.byref(c)))
+        return c
+
+    def set_config(self, **fields) -> Config:
+        """Change the named fields of the context's config; returns the config now in force."""
+        c = self.get_config()
+        for k, v in fields.items():
+            if not hasattr(c, k) or k == "reserved":
+                raise ValueError(f"no such config field: {k}")
+            setattr(c, k, int(v))
+        self._check(self._lib.infr_cuda_set_config(self._ctx, C.byref(c)))
+        return c
+
+    # -- expert parallelism (crates/infr-vulkan/src/ep.rs) ------------------------------------------
+    def ep_unique_id(self) -> bytes:
+        """Rank 0 makes the communicator id; the host hands it to the other ranks."""
+        buf = C.create_string_buffer(EP_ID_BYTES)
+        rc = self._lib.infr_cuda_ep_unique_id(buf)
+        if rc != OK:
+            raise (Unsupported if rc == ERR_UNSUPPORTED else BackendError)(rc, "ep_unique_id failed (is libnccl.so.2 loadable?)")
+        return buf.raw
+
+    def ep_init(self, unique_id: bytes, rank: int, world: int) -> None:
+        """Joins the communicator (collective).  After it, a `MoeFfn` whose `ep_band` is this rank's
+        band runs expert-parallel inside the library."""
+        if len(unique_id) != EP_ID_BYTES:
+            raise ValueError("unique_id must be 128 bytes")
+        self._check(self._lib.infr_cuda_ep_init(self._ctx, unique_id, rank, world))
+        self.ep_rank, self.ep_world = rank, world
+
+    def ep_finalize(self) -> None:
+        self._check(self._lib.infr_cuda_ep_finalize(self._ctx))
+
+    def ep_last_phases(self):
+        """ms from the call's start: routed, dispatched, band done, partials back, result written."""
+        out = (C.c_float * 5)()
+        self._check(self._lib.infr_cuda_ep_last_phases(self._ctx, out))
+        return [float(v) for v in out]
 
     def set_trace(self, buf: Optional[Buffer]) -> None:
         self._check(self._lib.infr_cuda_set_trace(self._ctx, _h(buf)))

@@ -73,12 +73,28 @@ struct DeviceGuard {
 
 bool fits(const infr_cuda_buf* b, size_t need) { return b && b->ptr && b->bytes >= need; }
 
+infr_cuda_config default_config() {
+  infr_cuda_config c = {};
+  c.gu_warps = 4;
+  c.gu_chunks = 4;
+  c.dn_warps = 12;
+  c.dense_min_tiles = 2;
+  c.sync_timeout_ms = 60000;
+  return c;
+}
+
 // Drains the context's stream and reports what kernels flagged: a bounded wait that ran out, or an
 // expert id outside [0, n_expert).  The status words live in pinned host memory that the device
 // writes directly (and only in those cases), so polling them costs nothing beyond the one wait.
 int32_t drain_and_poll(infr_cuda_ctx* ctx, const char* what) {
-  const cudaError_t e = cudaStreamSynchronize(ctx->stream);
-  if (e != cudaSuccess) return check_cuda(ctx, e, what);
+  if (ctx->ep) {
+    // collectives may be queued: a peer that never arrives must not block the host for ever
+    const int32_t rc = ep_wait_stream(ctx, what);
+    if (rc) return rc;
+  } else {
+    const cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return check_cuda(ctx, e, what);
+  }
   volatile DeviceStatus* st = ctx->status_host;
   const int tag = st->timeout, bad = st->bad_index;
   if (tag || bad) {
@@ -123,8 +139,6 @@ int32_t infr_cuda_create(int32_t device, infr_cuda_ctx** out) {
   if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaHostAlloc(reinterpret_cast<void**>(&ctx->status_host), sizeof(DeviceStatus), cudaHostAllocMapped) != cudaSuccess ||
       cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->status), ctx->status_host, 0) != cudaSuccess ||
-      cudaMalloc(&ctx->counters, 64 * sizeof(unsigned int)) != cudaSuccess ||
-      cudaMemset(ctx->counters, 0, 64 * sizeof(unsigned int)) != cudaSuccess ||
       cudaMalloc(&ctx->route_logits, ROUTE_LOGIT_BYTES) != cudaSuccess ||
       cudaMemset(ctx->route_logits, 0xFF, ROUTE_LOGIT_BYTES) != cudaSuccess) {
     infr_cuda_destroy(ctx);
@@ -132,6 +146,7 @@ int32_t infr_cuda_create(int32_t device, infr_cuda_ctx** out) {
   }
   std::memset(ctx->status_host, 0, sizeof(DeviceStatus));
   ctx->stream = ctx->own_stream;
+  ctx->cfg = default_config();
   *out = ctx;
   return INFR_CUDA_OK;
 }
@@ -139,10 +154,10 @@ int32_t infr_cuda_create(int32_t device, infr_cuda_ctx** out) {
 void infr_cuda_destroy(infr_cuda_ctx* ctx) {
   if (!ctx) return;
   DeviceGuard g(ctx->device);
+  if (ctx->ep) ep_release(ctx, false);
   if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
-  if (ctx->counters) cudaFree(ctx->counters);
   if (ctx->route_logits) cudaFree(ctx->route_logits);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
@@ -156,13 +171,29 @@ int32_t infr_cuda_set_stream(infr_cuda_ctx* ctx, void* cuda_stream) {
   return INFR_CUDA_OK;
 }
 
+int32_t infr_cuda_get_config(const infr_cuda_ctx* ctx, infr_cuda_config* out) {
+  if (!ctx || !out) return INFR_CUDA_ERR_INVALID_ARG;
+  *out = ctx->cfg;
+  return INFR_CUDA_OK;
+}
+
+int32_t infr_cuda_set_config(infr_cuda_ctx* ctx, const infr_cuda_config* cfg) {
+  if (!ctx || !cfg) return INFR_CUDA_ERR_INVALID_ARG;
+  if (cfg->gu_chunks > 4 || cfg->gu_warps > 16 || cfg->dn_warps > 24 || cfg->expert_major > 2 || cfg->topk_cta > 2)
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_config: a field is outside its range");
+  for (uint32_t r : cfg->reserved)
+    if (r) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_config: reserved fields must be zero");
+  ctx->cfg = *cfg;
+  return INFR_CUDA_OK;
+}
+
 int32_t infr_cuda_alloc(infr_cuda_ctx* ctx, size_t bytes, int32_t zero, infr_cuda_buf** out) {
   if (!ctx || !out) return INFR_CUDA_ERR_INVALID_ARG;
   *out = nullptr;
   DeviceGuard g(ctx->device);
   infr_cuda_buf* b = new (std::nothrow) infr_cuda_buf();
   if (!b) return fail(ctx, INFR_CUDA_ERR_OOM, "alloc: host out of memory");
-  // 16 spare bytes so block decoders may read a word pair at the very end of a bank
+  // (16 spare bytes; no kernel needs them - none reads past a bank's last block)
   cudaError_t e = cudaMalloc(&b->ptr, bytes + 16);
   if (e != cudaSuccess) {
     delete b;
@@ -241,8 +272,7 @@ int32_t infr_cuda_upload_async(infr_cuda_ctx* ctx, infr_cuda_buf* dst, size_t ds
   DeviceGuard g(ctx->device);
   char* d = static_cast<char*>(dst->ptr) + dst_off;
   // a few rows from pinned memory: fetched by a kernel, which the next kernel can overlap
-  static const bool by_kernel = !(getenv("INFR_UPLOAD_BY_COPY") && atoi(getenv("INFR_UPLOAD_BY_COPY")));
-  if (by_kernel && n <= (256u << 10) && n % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(d) % 16 == 0) {
+  if (!ctx->cfg.upload_by_copy && n <= (256u << 10) && n % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(d) % 16 == 0) {
     cudaPointerAttributes at = {};
     if (cudaPointerGetAttributes(&at, src) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer != nullptr)
       return launch_fetch_host(ctx, at.devicePointer, d, n);
@@ -257,8 +287,7 @@ int32_t infr_cuda_download_async(infr_cuda_ctx* ctx, const infr_cuda_buf* src, s
   if (!n) return INFR_CUDA_OK;
   DeviceGuard g(ctx->device);
   const char* sp = static_cast<const char*>(src->ptr) + src_off;
-  static const bool by_kernel = !(getenv("INFR_UPLOAD_BY_COPY") && atoi(getenv("INFR_UPLOAD_BY_COPY")));
-  if (by_kernel && n <= (256u << 10) && n % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 && reinterpret_cast<uintptr_t>(sp) % 16 == 0) {
+  if (!ctx->cfg.upload_by_copy && n <= (256u << 10) && n % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0 && reinterpret_cast<uintptr_t>(sp) % 16 == 0) {
     cudaPointerAttributes at = {};
     if (cudaPointerGetAttributes(&at, dst) == cudaSuccess && at.type == cudaMemoryTypeHost && at.devicePointer != nullptr)
       return launch_store_host(ctx, sp, at.devicePointer, n);
@@ -343,10 +372,16 @@ void infr_cuda_graph_free(infr_cuda_ctx* ctx, infr_cuda_graph* graph) {
 
 // ---- Op::MoeFfn ---------------------------------------------------------------------------------
 
-static int32_t validate_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
+}  // extern "C"
+
+namespace infr {
+
+int32_t validate_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   if (!d) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: null descriptor");
   if (!d->rows || !d->ne || !d->n_expert || !d->n_used) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: zero dimension");
-  if (d->n_used > d->n_expert) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: n_used exceeds n_expert");
+  // (a call that takes its routing as an input may hold fewer experts than a token uses: an expert-parallel band)
+  if (d->n_used > d->n_expert && (d->stages == 0 || (d->stages & 1u)))
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: n_used exceeds n_expert");
   if (d->n_used > 32) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: n_used > 32 is not covered");
   if (d->n_expert > 1024) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: more than 1024 experts is not covered");
   if (d->ne % 64) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: ne must be a multiple of 64");
@@ -373,8 +408,10 @@ static int32_t validate_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* 
   return INFR_CUDA_OK;
 }
 
-static int32_t validate_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
-  int32_t rc = validate_route(ctx, d);
+// `bank_experts`: experts held by gate_exps / up_exps / down_exps (n_expert, or the band of an
+// expert-parallel rank).
+int32_t validate_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, uint32_t bank_experts) {
+  int32_t rc = validate_moe_route(ctx, d);
   if (rc) return rc;
   if (!d->n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: zero n_ff_exp");
   if (d->gate_dtype != INFR_CUDA_DT_Q4K || d->up_dtype != INFR_CUDA_DT_Q4K ||
@@ -384,8 +421,8 @@ static int32_t validate_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d)
   const size_t xb = (size_t)d->rows * d->ne * 4;
   if (!fits(d->x, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: x missing or too small");
   if (!fits(d->dst, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: dst missing or too small");
-  const size_t gb = (size_t)d->n_expert * d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
-  const size_t db = (size_t)d->n_expert * d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
+  const size_t gb = (size_t)bank_experts * d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
+  const size_t db = (size_t)bank_experts * d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
   if (d->fused_gate_up ? !fits(d->gate_exps, 2 * gb) : (!fits(d->gate_exps, gb) || !fits(d->up_exps, gb)))
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: gate/up bank missing or too small");
   if (!fits(d->down_exps, db)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: down bank missing or too small");
@@ -417,6 +454,10 @@ static int32_t validate_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d)
   }
   return INFR_CUDA_OK;
 }
+
+}  // namespace infr
+
+extern "C" {
 
 namespace {
 // Scratch carve-up for one call.
@@ -464,7 +505,6 @@ RouteParams route_params(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, co
   rp.sh_logit = s.sh_logit;
   rp.ids = d->ids_out ? static_cast<int32_t*>(d->ids_out->ptr) : s.ids;
   rp.wts = d->wts_out ? static_cast<float*>(d->wts_out->ptr) : s.wts;
-  rp.counter = ctx->counters;
   rp.trace = ctx->trace;
   rp.rows = d->rows;
   rp.ne = d->ne;
@@ -481,7 +521,7 @@ RouteParams route_params(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, co
 
 int32_t infr_cuda_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
-  int32_t rc = validate_route(ctx, d);
+  int32_t rc = validate_moe_route(ctx, d);
   if (rc) return rc;
   if (!d->ids_out || !d->wts_out) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_route: ids_out and wts_out are required");
   DeviceGuard g(ctx->device);
@@ -494,7 +534,8 @@ int32_t infr_cuda_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d)
 
 int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
-  int32_t rc = validate_ffn(ctx, d);
+  if (d && ep_call_is_collective(ctx, d)) return ep_moe_ffn(ctx, d);
+  int32_t rc = validate_moe_ffn(ctx, d, d->n_expert);
   if (rc) return rc;
   DeviceGuard g(ctx->device);
   const bool has_sh = d->sh_gate != nullptr;
@@ -529,7 +570,13 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
       rp.xscale = s.xscale;
       rp.rms_w = d->norm_weight ? static_cast<const float*>(d->norm_weight->ptr) : nullptr;
       rp.rms_eps = d->norm_eps;
-      if ((stages & 1u) && (rc = launch_route(ctx, rp, true))) return rc;
+      if (stages & 1u) {
+        if ((rc = launch_route(ctx, rp, true))) return rc;
+      } else if (stages & 8u) {
+        // routing came from elsewhere: the router kernel, which would have made the fixed-point copy, does not run
+        if (d->norm_weight) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: stages without the router cannot apply norm_weight");
+        if ((rc = launch_quantize_rows(ctx, static_cast<const float*>(d->x->ptr), s.xq_lo, s.xq_hi, s.xscale, (int)d->rows, (int)d->ne))) return rc;
+      }
     } else if (stages & 1u) {
       const float* x_eff = static_cast<const float*>(d->x->ptr);
       if (d->norm_weight) {

@@ -29,6 +29,10 @@ struct DeviceStatus {
 
 }  // namespace infr
 
+namespace infr {
+struct EpState;  // ep.cu
+}
+
 struct infr_cuda_buf {
   void* ptr = nullptr;
   size_t bytes = 0;
@@ -55,10 +59,11 @@ struct infr_cuda_ctx {
   size_t scratch_bytes = 0;
   infr::DeviceStatus* status = nullptr;       // the device's address of the status words below
   infr::DeviceStatus* status_host = nullptr;  // pinned, mapped host memory: kernels write it directly when they flag something
-  unsigned int* counters = nullptr;           // device memory: completion counters (zeroed by users)
   float* route_logits = nullptr;              // device memory: the whole-row router kernel's logit buffer, all words
                                               // "not written yet" between launches (see ROUTE_LOGIT_EMPTY)
   unsigned long long* trace = nullptr;        // optional phase stamps (see trace_stamp)
+  infr_cuda_config cfg = {};                  // tuning switches (infr_cuda_set_config)
+  infr::EpState* ep = nullptr;                // expert-parallel communicator and buffers, or null
 };
 
 namespace infr {

@@ -12,9 +12,10 @@
 //
 // Data movement: only the routed experts' rows are touched, once.  Each CTA pulls its contiguous
 // slab of rows with 1-D bulk async copies (TMA, never multicast) into shared memory, all issued
-// up front so every SM has its whole share in flight, and lanes unpack blocks in registers:
-// a 4-bit (6-bit) code becomes the float 1 + n/16 (1 + q/64) with one byte-permute, products
-// are packed f32x2 fmas, and row sums finish with warp shuffles.
+// up front so every SM has its whole share in flight, and lanes unpack blocks in registers: the
+// activations arrive as 16-bit fixed point in two signed 8-bit limbs, the 4-bit (6-bit) codes are
+// masked in place and multiplied with integer dot-product instructions (exact integer sums), block
+// scales are applied per 32 (16) elements in f32, and row sums finish with warp shuffles.
 #include "kernels.cuh"
 
 namespace infr {
@@ -523,8 +524,7 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, u
     // Grids of more than four waves: four warps taking four chunks of four rows each (same tile per role
     // as 16 x 1, half the default tile).  The smaller CTAs put more independent chains of
     // (ids -> copies -> unpack) on an SM: 69 us against 78 us for 32 tokens.
-    static const int ew = getenv("INFR_GU_WARPS") ? atoi(getenv("INFR_GU_WARPS")) : 4;
-    static const int ec = getenv("INFR_GU_CHUNKS") ? atoi(getenv("INFR_GU_CHUNKS")) : 4;
+    const int ew = (int)ctx->cfg.gu_warps, ec = (int)ctx->cfg.gu_chunks;
     if (ew > 0 && ec > 0 && ec <= GU_MAX_CHUNKS && jobs > 4 * ctx->sm_count && p.ne / 16 <= ew * 32 && p.nff % (ew * ec) == 0 &&
         (!has_sh || sh_ff % (ew * ec) == 0)) {
       gw = ew;
@@ -574,7 +574,7 @@ int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, u
   {
     // Grids of more than four waves: at most 12 warps, so that three CTAs share an SM's registers and
     // their latency chains overlap (83 us against 98 us for 32 tokens).
-    static const int cap = getenv("INFR_DN_WARPS") ? atoi(getenv("INFR_DN_WARPS")) : 12;
+    const int cap = (int)ctx->cfg.dn_warps;
     if (cap > 0 && p.rows * (p.ne / TI) > 4 * ctx->sm_count)
       for (int c = cap; c >= 1; --c)
         if (n_tasks % c == 0) { nw = c; break; }

@@ -48,11 +48,12 @@ __device__ __forceinline__ int kperm(int k) {  // position of element k inside i
 // ---- permute -------------------------------------------------------------------------------------
 
 __global__ void k_pair_count(const int32_t* __restrict__ ids, int n_pairs, int n_expert, uint32_t ep_lo, uint32_t ep_n,
-                             int* __restrict__ counts) {
+                             int* __restrict__ counts, DeviceStatus* status) {
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   if (p >= n_pairs) return;
   int e = ids[p];
   if (e < 0) return;  // a negative id marks a pair another rank serves
+  if (e >= n_expert) status->bad_index = 1;  // served as the last expert, reported at the next sync
   e = min(e, n_expert - 1);
   if (ep_n && ((uint32_t)e < ep_lo || (uint32_t)e >= ep_lo + ep_n)) return;
   atomicAdd(&counts[e], 1);
@@ -158,8 +159,9 @@ __global__ void __launch_bounds__(1024) k_segment_scan(const int* __restrict__ c
 
 // Calls of up to a few hundred thousand pairs: count, scan and scatter by one CTA with the
 // histogram and the cursors in shared memory - one launch instead of a memset and three kernels.
-__device__ __forceinline__ int bucket_of(int e, int n_expert, uint32_t ep_lo, uint32_t ep_n) {
+__device__ __forceinline__ int bucket_of(int e, int n_expert, uint32_t ep_lo, uint32_t ep_n, DeviceStatus* status) {
   if (e < 0) return -1;  // a negative id marks a pair another rank serves
+  if (e >= n_expert) status->bad_index = 1;  // served as the last expert, reported at the next sync
   e = min(e, n_expert - 1);
   if (ep_n && ((uint32_t)e < ep_lo || (uint32_t)e >= ep_lo + ep_n)) return -1;
   return e;
@@ -168,7 +170,8 @@ __global__ void __launch_bounds__(1024) k_bucket_fused(const int32_t* __restrict
                                                        uint32_t ep_n, int shared_rows, int tn, int* __restrict__ seg_off,
                                                        int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                                        int* __restrict__ tile_rows, int* __restrict__ n_tiles,
-                                                       int* __restrict__ pos_of_pair, int* __restrict__ pair_of_pos) {
+                                                       int* __restrict__ pos_of_pair, int* __restrict__ pair_of_pos,
+                                                       DeviceStatus* status) {
   __shared__ int s_cnt[1025], s_off[1026], s_toff[1026], s_ws[66], s_hist[1024];
   const int tid = threadIdx.x;
   s_hist[tid] = 0;
@@ -180,7 +183,7 @@ __global__ void __launch_bounds__(1024) k_bucket_fused(const int32_t* __restrict
     for (int u = 0; u < 8; ++u) idv[u] = p0 + u * 1024 < n_pairs ? ids[p0 + u * 1024] : -1;
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      const int e = bucket_of(idv[u], n_expert, ep_lo, ep_n);
+      const int e = bucket_of(idv[u], n_expert, ep_lo, ep_n, status);
       if (e >= 0) atomicAdd(&s_hist[e], 1);
     }
   }
@@ -199,7 +202,7 @@ __global__ void __launch_bounds__(1024) k_bucket_fused(const int32_t* __restrict
     for (int u = 0; u < 8; ++u) {
       const int p = p0 + u * 1024;
       if (p >= n_pairs) break;
-      const int e = bucket_of(idv[u], n_expert, ep_lo, ep_n);
+      const int e = bucket_of(idv[u], n_expert, ep_lo, ep_n, status);
       if (e < 0) {
         pos_of_pair[p] = -1;
       } else {
@@ -439,10 +442,13 @@ __global__ void __launch_bounds__(GG_THREADS) k_grouped_gateup(GroupedParams p) 
 
 // ---- down -------------------------------------------------------------------------------------------
 
+// Four bytes at a 2-byte-aligned offset.  The upper word is only fetched when the offset is off a
+// word boundary: the last such read of a Q6_K block (scales at byte 204) then ends inside the block,
+// so nothing past a bank's last block is touched.
 __device__ __forceinline__ uint32_t ldg_u32_unaligned(const uint8_t* base, size_t off) {
   const size_t a = off & ~(size_t)3;
   const uint32_t lo = __ldg(reinterpret_cast<const uint32_t*>(base + a));
-  const uint32_t hi = __ldg(reinterpret_cast<const uint32_t*>(base + a + 4));
+  const uint32_t hi = (off & 3) ? __ldg(reinterpret_cast<const uint32_t*>(base + a + 4)) : 0u;
   return __funnelshift_r(lo, hi, (uint32_t)(off & 3) * 8);
 }
 
@@ -538,23 +544,24 @@ __global__ void __launch_bounds__(256) k_unpermute_combine(const float* __restri
                                                            const float* __restrict__ wts, const float* __restrict__ sh_logit,
                                                            const float* __restrict__ sh_y, int rows, int n_used, int ne,
                                                            float* __restrict__ dst) {
-  const int t = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
   if (c >= ne) return;
-  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s = 0; s < n_used; ++s) {
-    const int pos = pos_of_pair[t * n_used + s];
-    if (pos < 0) continue;
-    const float w = wts[t * n_used + s];
-    const float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * ne + c);
-    o.x += w * v.x; o.y += w * v.y; o.z += w * v.z; o.w += w * v.w;
+  for (int t = blockIdx.y; t < rows; t += gridDim.y) {  // the grid's y extent stops at 65535
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n_used; ++s) {
+      const int pos = pos_of_pair[(size_t)t * n_used + s];
+      if (pos < 0) continue;
+      const float w = wts[(size_t)t * n_used + s];
+      const float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * ne + c);
+      o.x += w * v.x; o.y += w * v.y; o.z += w * v.z; o.w += w * v.w;
+    }
+    if (sh_y) {
+      const float gsh = sh_logit ? 1.0f / (1.0f + __expf(-sh_logit[t])) : 1.0f;
+      const float4 v = *reinterpret_cast<const float4*>(sh_y + (size_t)t * ne + c);
+      o.x += gsh * v.x; o.y += gsh * v.y; o.z += gsh * v.z; o.w += gsh * v.w;
+    }
+    *reinterpret_cast<float4*>(dst + (size_t)t * ne + c) = o;
   }
-  if (sh_y) {
-    const float gsh = sh_logit ? 1.0f / (1.0f + __expf(-sh_logit[t])) : 1.0f;
-    const float4 v = *reinterpret_cast<const float4*>(sh_y + (size_t)t * ne + c);
-    o.x += gsh * v.x; o.y += gsh * v.y; o.z += gsh * v.z; o.w += gsh * v.w;
-  }
-  *reinterpret_cast<float4*>(dst + (size_t)t * ne + c) = o;
 }
 
 // The shared segment starts right after the routed rows: its address is only known on the device.
@@ -564,31 +571,33 @@ __global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __re
                                                                int rows, int n_used, int ne, const float* residual,
                                                                const int32_t* __restrict__ ids, const float* __restrict__ down_scale,
                                                                int weight_before, float* dst) {
-  const int t = blockIdx.y;
   const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
   if (c >= ne) return;
-  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s = 0; s < n_used; ++s) {
-    const int pos = pos_of_pair[t * n_used + s];
-    if (pos < 0) continue;
-    const float w = weight_before ? 1.0f : wts[t * n_used + s];
-    float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * ne + c);
-    if (down_scale != nullptr) {  // y = raw * scale[e], then the weighted sum (Op::MoeFfn::down_scale)
-      const float sc = down_scale[ids[t * n_used + s]];
-      v.x *= sc; v.y *= sc; v.z *= sc; v.w *= sc;
+  for (int t = blockIdx.y; t < rows; t += gridDim.y) {  // the grid's y extent stops at 65535
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n_used; ++s) {
+      const int pos = pos_of_pair[(size_t)t * n_used + s];
+      if (pos < 0) continue;
+      const float w = weight_before ? 1.0f : wts[(size_t)t * n_used + s];
+      float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * ne + c);
+      if (down_scale != nullptr) {  // y = raw * scale[e], then the weighted sum (Op::MoeFfn::down_scale)
+        // ids may be the caller's: same clamp as the bucketing, which also reported the bad id
+        const float sc = down_scale[min(max(ids[(size_t)t * n_used + s], 0), n_seg_routed - 1)];
+        v.x *= sc; v.y *= sc; v.z *= sc; v.w *= sc;
+      }
+      o.x += w * v.x; o.y += w * v.y; o.z += w * v.z; o.w += w * v.w;
     }
-    o.x += w * v.x; o.y += w * v.y; o.z += w * v.z; o.w += w * v.w;
+    if (has_shared) {
+      const float gsh = sh_logit ? 1.0f / (1.0f + __expf(-sh_logit[t])) : 1.0f;
+      const float4 v = *reinterpret_cast<const float4*>(y + (size_t)(seg_off[n_seg_routed] + t) * ne + c);
+      o.x += gsh * v.x; o.y += gsh * v.y; o.z += gsh * v.z; o.w += gsh * v.w;
+    }
+    if (residual != nullptr) {  // MoeFfn -> Add; may alias dst: each element is read, then written, by this thread
+      const float4 h = *reinterpret_cast<const float4*>(residual + (size_t)t * ne + c);
+      o.x += h.x; o.y += h.y; o.z += h.z; o.w += h.w;
+    }
+    *reinterpret_cast<float4*>(dst + (size_t)t * ne + c) = o;
   }
-  if (has_shared) {
-    const float gsh = sh_logit ? 1.0f / (1.0f + __expf(-sh_logit[t])) : 1.0f;
-    const float4 v = *reinterpret_cast<const float4*>(y + (size_t)(seg_off[n_seg_routed] + t) * ne + c);
-    o.x += gsh * v.x; o.y += gsh * v.y; o.z += gsh * v.z; o.w += gsh * v.w;
-  }
-  if (residual != nullptr) {  // MoeFfn -> Add; may alias dst: each element is read, then written, by this thread
-    const float4 h = *reinterpret_cast<const float4*>(residual + (size_t)t * ne + c);
-    o.x += h.x; o.y += h.y; o.z += h.z; o.w += h.w;
-  }
-  *reinterpret_cast<float4*>(dst + (size_t)t * ne + c) = o;
 }
 
 // Tile table straight from caller-provided segment offsets (rows already grouped by expert).
@@ -675,12 +684,12 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
     // routed call: bucket the pairs
     if (c.n_pairs <= (1 << 16)) {
       k_bucket_fused<<<1, 1024, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, c.shared_rows, tn, seg_off, tile_expert, tile_row0,
-                                         tile_rows, n_tiles, pos_of_pair, pair_of_pos);
+                                         tile_rows, n_tiles, pos_of_pair, pair_of_pos, ctx->status);
       ctx->launches += 1;
     } else {
       cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)(n_seg + 2) * 4, st);
       if (e != cudaSuccess) return check_cuda(ctx, e, "grouped: memset");
-      k_pair_count<<<(c.n_pairs + 255) / 256, 256, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, counts);
+      k_pair_count<<<(c.n_pairs + 255) / 256, 256, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, counts, ctx->status);
       k_segment_scan<<<1, 1024, 0, st>>>(counts, c.n_expert, c.shared_rows, tn, seg_off, fill, tile_expert, tile_row0, tile_rows, n_tiles);
       k_pair_scatter<<<(c.n_pairs + 255) / 256, 256, 0, st>>>(c.ids, c.n_pairs, c.n_expert, c.ep_lo, c.ep_n, seg_off, fill,
                                                                pos_of_pair, pair_of_pos);
@@ -734,7 +743,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   p.clamp = c.clamp;
   p.status = ctx->status;
   p.trace = ctx->trace;
-  p.trace_tile = getenv("INFR_TRACE_TILE") ? atoi(getenv("INFR_TRACE_TILE")) : 0;
+  p.trace_tile = (int)ctx->cfg.trace_tile;
   if (use_umma) {
     const int32_t rc = launch_umma_grouped(ctx, p, max_tiles);
     if (rc) return rc;
@@ -744,7 +753,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
     ctx->launches += 2;
   }
   if (c.dst) {
-    k_unpermute_combine_seg<<<dim3((c.ne / 4 + 255) / 256, c.rows), 256, 0, st>>>(y, pos_of_pair, c.wts, c.sh_logit, seg_off, n_seg_routed,
+    k_unpermute_combine_seg<<<dim3((c.ne / 4 + 255) / 256, std::min(c.rows, 65535)), 256, 0, st>>>(y, pos_of_pair, c.wts, c.sh_logit, seg_off, n_seg_routed,
                                                                                    c.shared_rows > 0 ? 1 : 0, c.rows, c.n_used, c.ne, c.residual, c.ids, c.down_scale,
                                                                                    c.weight_before, c.dst);
     ctx->launches += 1;
@@ -754,7 +763,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
 
 int32_t launch_combine(infr_cuda_ctx* ctx, const float* y, const int* pos_of_pair, const float* wts, const float* sh_logit,
                        const float* sh_y, int rows, int n_used, int ne, float* dst) {
-  k_unpermute_combine<<<dim3((ne / 4 + 255) / 256, rows), 256, 0, ctx->stream>>>(y, pos_of_pair, wts, sh_logit, sh_y, rows, n_used, ne, dst);
+  k_unpermute_combine<<<dim3((ne / 4 + 255) / 256, std::min(rows, 65535)), 256, 0, ctx->stream>>>(y, pos_of_pair, wts, sh_logit, sh_y, rows, n_used, ne, dst);
   ctx->launches += 1;
   return check_cuda(ctx, cudaGetLastError(), "combine launch");
 }

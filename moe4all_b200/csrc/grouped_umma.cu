@@ -463,16 +463,20 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p, con
     const int n_pairs = p.nff / 128;
     auto fetch_pair = [&](int pair) {
       const int blk = pair >> 1, h = pair & 1;
-      // lane's spare word: scales (3 words), d, ql word 16 of this half, qh word 8 of this half
-      const int spare = w == 0 ? 192 + 8 * h : w == 1 ? 196 + 8 * h : w == 2 ? 200 + 8 * h : w == 3 ? 208 : w == 4 ? 64 * h + 64 : 160 + 32 * h;
   #pragma unroll
       for (int ps = 0; ps < PS; ++ps) {
         const size_t bo = (size_t)(i0 + ps * (U_PRODUCERS / 8) + g8) * drb + (size_t)blk * Q6K_BLOCK_BYTES;
         const uint8_t* ab = wbase + (bo & ~(size_t)3);
+        const bool aligned = (bo & 3) == 0;
+        // lane's spare word: scales (3 words), d, ql word 16 of this half, qh word 8 of this half.
+        // Nothing past the block's 210 bytes is read (the bank may end with it): a block on a word
+        // boundary needs no third scale word (lane 2 repeats the second), and d comes as 16 bits.
+        const int spare = w == 0 ? 192 + 8 * h : w == 1 ? 196 + 8 * h : w == 2 ? (aligned ? 196 : 200) + 8 * h : w == 4 ? 64 * h + 64 : 160 + 32 * h;
         nxt[ps][0] = __ldg(reinterpret_cast<const uint32_t*>(ab + 64 * h + 4 * w));
         nxt[ps][1] = __ldg(reinterpret_cast<const uint32_t*>(ab + 64 * h + 32 + 4 * w));
         nxt[ps][2] = __ldg(reinterpret_cast<const uint32_t*>(ab + 128 + 32 * h + 4 * w));
-        nxt[ps][3] = w < 6 ? __ldg(reinterpret_cast<const uint32_t*>(ab + spare)) : 0u;
+        nxt[ps][3] = w == 3 ? (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(wbase + bo + 208))
+                            : (w < 6 ? __ldg(reinterpret_cast<const uint32_t*>(ab + spare)) : 0u);
       }
     };
     // the CTA's 256 weight rows are one contiguous range: ask for it in L2 up front, so that the
@@ -506,7 +510,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p, con
           cur[ps][2] = __funnelshift_r(h0, w == 7 ? h_8 : h_r, sh);
           cur[ps][3] = __funnelshift_r(s0, s1, sh);
           cur[ps][4] = __funnelshift_r(s1, s2, sh);
-          cur[ps][5] = (dw >> sh) & 0xFFFFu;
+          cur[ps][5] = dw;  // the block's f16 d, fetched as 16 bits
         }
         if ((step >> 1) + 1 < n_pairs) fetch_pair((step >> 1) + 1);
       }

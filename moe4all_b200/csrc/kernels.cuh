@@ -5,8 +5,8 @@
 namespace infr {
 
 // The whole-row router kernel (fused norm, fixed-point copy and top-k) takes up to this many rows per
-// CTA group, up to ROUTE_SMALL_MAX_GROUPS groups (one completion counter each) and
-// ROUTE_SMALL_LIMIT rows per call.
+// CTA group, up to ROUTE_SMALL_MAX_GROUPS groups (one selecting CTA each) and ROUTE_SMALL_LIMIT rows
+// per call.
 constexpr int ROUTE_SMALL_MAX_ROWS = 8;
 constexpr int ROUTE_SMALL_MAX_GROUPS = 64;
 constexpr int ROUTE_SMALL_LIMIT = 64;
@@ -28,7 +28,6 @@ struct RouteParams {
   float* sh_logit;           // [rows] scratch
   int32_t* ids;              // [rows, n_used]
   float* wts;                // [rows, n_used]
-  unsigned int* counter;     // zero on entry, zero on exit
   DeviceStatus* status;      // bounded waits that ran out are recorded here
   int8_t *xq_lo, *xq_hi;     // [rows, ne] fixed-point limbs of x for the small-m expert kernels, or null
   float* xscale;             // [rows] value of one fixed-point unit
@@ -115,6 +114,17 @@ size_t grouped_scratch_bytes(int rows_total, int n_pairs, int n_seg, int ne, int
 int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c);
 int32_t launch_combine(infr_cuda_ctx* ctx, const float* y, const int* pos_of_pair, const float* wts, const float* sh_logit,
                        const float* sh_y, int rows, int n_used, int ne, float* dst);
+
+// Descriptor checks shared by the local and the expert-parallel entry (api.cu).
+int32_t validate_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d);
+int32_t validate_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, uint32_t bank_experts);
+
+// Expert parallelism (ep.cu).  A descriptor is a collective call when the context has joined a
+// communicator of more than one rank and the descriptor names this rank's band.
+bool ep_call_is_collective(const infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d);
+int32_t ep_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d);
+int32_t ep_wait_stream(infr_cuda_ctx* ctx, const char* what);  // bounded wait; aborts the communicator when it runs out
+void ep_release(infr_cuda_ctx* ctx, bool orderly);
 
 int32_t launch_umma_selftest(infr_cuda_ctx* ctx, const __half* a, const __half* b, float* c, int n);
 int32_t launch_route(infr_cuda_ctx* ctx, const RouteParams& p, bool pdl);

@@ -237,3 +237,50 @@ class CudaExpertParallelLayer:
         out = self.ep.forward(x, rows_equal=rows_equal)
         del keep
         return out
+
+
+# -------------------------------------------------------------------------------------------------
+# Expert parallelism inside the library (infr_cuda_ep_init + the collective form of infr_cuda_moe_ffn)
+# -------------------------------------------------------------------------------------------------
+
+def join_communicator(be, group: Optional[dist.ProcessGroup] = None) -> None:
+    """Brings the backend's context into an NCCL communicator of its own, spanning the ranks of the
+    (already initialised) torch process group: rank 0 makes the id, the group carries it to the others
+    (the role `ncclGetUniqueId` + an out-of-band channel plays for a host without torch)."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    box = [be.ep_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0, group=group)
+    be.ep_init(box[0], rank, world)
+
+
+class LibraryExpertParallelLayer:
+    """One MoE layer sharded over the ranks, every step of it inside the C-ABI library: the call
+    below is `Backend::execute` of an `Op::MoeFfn` whose `ep_band` is this rank's band, on a context
+    that has joined a communicator (`ExpertParallelBackend`, crates/infr-vulkan/src/ep.rs:454-493).
+
+    `layer` holds the full router and shared expert and the banks of THIS rank's experts only
+    (devgen.DeviceLayer(..., band=(rank * E / W, E / W)))."""
+
+    def __init__(self, be, layer, n_expert: int, n_used: int, n_ff: int, ne: int, sh_ff: int = 0, **route_kw):
+        from .backend import MoeFfn
+        self.be, self.L, self._MoeFfn = be, layer, MoeFfn
+        world, rank = getattr(be, "ep_world", 1), getattr(be, "ep_rank", 0)
+        if n_expert % world:
+            raise ValueError(f"n_expert {n_expert} is not a multiple of the world size {world}")  # ep.rs:171-176
+        self.band = (rank * (n_expert // world), n_expert // world)
+        self.dims = dict(ne=ne, n_expert=n_expert, n_used=n_used, n_ff_exp=n_ff)
+        self.sh_ff = sh_ff if "sh_gate" in layer.b else 0
+        self.route_kw = route_kw
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, ids_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x: this rank's token rows [R, ne] f32 (the same R on every rank).  Collective."""
+        be, b = self.be, self.L.b
+        out = torch.empty_like(x) if out is None else out
+        op = self._MoeFfn(x=be.wrap_tensor(x), dst=be.wrap_tensor(out), rows=x.shape[0], router=b["router"], gate_exps=b["gate"],
+                          up_exps=b["up"], down_exps=b["down"], exp_probs_b=b.get("bias"), ep_band=self.band,
+                          ids_out=be.wrap_tensor(ids_out) if ids_out is not None else None,
+                          sh_gate=b.get("sh_gate") if self.sh_ff else None, sh_up=b.get("sh_up") if self.sh_ff else None,
+                          sh_down=b.get("sh_down") if self.sh_ff else None,
+                          sh_gate_inp=b.get("sh_gate_inp") if self.sh_ff else None, sh_ff=self.sh_ff, **self.dims, **self.route_kw)
+        be.moe_ffn(op)
+        return out

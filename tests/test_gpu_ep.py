@@ -1,7 +1,10 @@
-"""GPU: expert-parallel layer (all-to-all dispatch/combine over NCCL) against the single-device
-result - the reference's own EP check is world-1 vs world-N identity
-(crates/infr-vulkan/src/adapter.rs:27494-27701).  Runs at world size 2 when the box has two GPUs,
-else at world size 1 (identity lowering)."""
+"""GPU: the expert-parallel layer against the single-device result - the reference's own EP check is
+world-1 vs world-N identity (crates/infr-vulkan/src/adapter.rs:27494-27701: rows 1 / 4 / 16, tolerance
+3e-3).  Two forms are checked, each at every world size the box has GPUs for (1 = the identity
+lowering): the exchange inside the library (`infr_cuda_ep_init`, NCCL send/recv) and the exchange run
+by the host with the library's building blocks (`CudaExpertParallelLayer`, torch.distributed).  Ranks
+are child processes, one per GPU.  The one failure case is made on the host: a rank that passes a
+different shape; nothing is left in flight and every rank gets the NCCL error class."""
 import os
 import socket
 
@@ -11,56 +14,129 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-NE, E, K, NFF, ROWS = 512, 16, 4, 256, 48
+NE, E, K, NFF = 512, 16, 4, 256
+
+
+def single_device(be, full, x, rows, path):
+    from moe4all_b200 import MoeFfn
+    dst = torch.empty_like(x)
+    ids = torch.empty(rows, K, dtype=torch.int32, device=x.device)
+    b = full.b
+    be.moe_ffn(MoeFfn(x=be.wrap_tensor(x), router=b["router"], gate_exps=b["gate"], up_exps=b["up"], down_exps=b["down"],
+                      dst=be.wrap_tensor(dst), rows=rows, ne=NE, n_expert=E, n_used=K, n_ff_exp=NFF, sh_gate=b["sh_gate"],
+                      sh_up=b["sh_up"], sh_down=b["sh_down"], sh_gate_inp=b["sh_gate_inp"], sh_ff=NFF, path=path,
+                      ids_out=be.wrap_tensor(ids)))
+    be.sync()
+    torch.cuda.synchronize()
+    return dst.cpu().numpy(), ids.cpu().numpy()
+
+
+def rel(got, ref):
+    return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-3))
 
 
 def worker(rank, world, port, ret):
     import torch.distributed as dist
-    from moe4all_b200 import CudaBackend, MoeFfn
+    from moe4all_b200 import BackendError, CudaBackend
+    from moe4all_b200.backend import ERR_NCCL
     from moe4all_b200.devgen import DeviceLayer
-    from moe4all_b200.ep import CudaExpertParallelLayer
+    from moe4all_b200.ep import CudaExpertParallelLayer, LibraryExpertParallelLayer, join_communicator
 
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     torch.cuda.set_device(rank)
     dev = f"cuda:{rank}"
     if world > 1:
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(dev))
+    out = {}
     try:
-        be = CudaBackend(rank)
         stream = torch.cuda.Stream()
         with torch.cuda.stream(stream):
+            be = CudaBackend(rank)           # host-run exchange; also computes the single-device results
+            be.set_stream(stream.cuda_stream)
+            be_lib = CudaBackend(rank)       # exchange inside the library
+            be_lib.set_stream(stream.cuda_stream)
+            if world > 1:
+                join_communicator(be_lib)
             el = E // world
             banded = DeviceLayer(be, 7, NE, E, NFF, sh_ff=NFF, device=dev, router_std=0.05, band=(rank * el, el))
+            banded_lib = DeviceLayer(be_lib, 7, NE, E, NFF, sh_ff=NFF, device=dev, router_std=0.05, band=(rank * el, el))
             full = DeviceLayer(be, 7, NE, E, NFF, sh_ff=NFF, device=dev, router_std=0.05)
+            host_layer = CudaExpertParallelLayer(be, banded, E, K, NFF, NE)
+            lib_layer = LibraryExpertParallelLayer(be_lib, banded_lib, E, K, NFF, NE, sh_ff=NFF)
             gen = torch.Generator(device=dev)
             gen.manual_seed(5)
-            x_all = torch.randn(world * ROWS, NE, generator=gen, device=dev)  # same on every rank
-            x = x_all[rank * ROWS:(rank + 1) * ROWS].contiguous()
-            layer = CudaExpertParallelLayer(be, banded, E, K, NFF, NE)
-            out = layer.forward(x)
-            out_static = layer.forward(x, rows_equal=True)  # fixed-shape exchange (world > 1), same sums
-            # single-device result for the same rows
-            dst = torch.empty_like(x)
-            b = full.b
-            be.moe_ffn(MoeFfn(x=be.wrap_tensor(x), router=b["router"], gate_exps=b["gate"], up_exps=b["up"], down_exps=b["down"],
-                              dst=be.wrap_tensor(dst), rows=ROWS, ne=NE, n_expert=E, n_used=K, n_ff_exp=NFF, sh_gate=b["sh_gate"],
-                              sh_up=b["sh_up"], sh_down=b["sh_down"], sh_gate_inp=b["sh_gate_inp"], sh_ff=NFF, path=2))
-            be.sync()
+            # rows per rank: the reference's 1 / 4 / 16 (small-m kernels in the band) and a batch (grouped GEMMs)
+            for rows in (1, 4, 16, 48):
+                x_all = torch.randn(world * rows, NE, generator=gen, device=dev)  # the same on every rank
+                x = x_all[rank * rows:(rank + 1) * rows].contiguous()
+                # the same kernels as the band call will pick (small-m while an expert sees few rows), so
+                # that the comparison isolates the exchange: the only difference left is the association of
+                # the sum over ranks
+                path = 1 if (rows <= 8 or rows * K * 8 <= el * 22) else 2
+                ref, ref_ids = single_device(be, full, x, rows, path)
+                mag = float(np.abs(ref).max())
+                ids_lib = torch.empty(rows, K, dtype=torch.int32, device=dev)
+                got_lib = lib_layer.forward(x, ids_out=ids_lib)
+                be_lib.sync()
+                torch.cuda.synchronize()
+                out[f"lib{rows}"] = (rel(got_lib.cpu().numpy(), ref), mag, bool(np.array_equal(ids_lib.cpu().numpy(), ref_ids)))
+                got_host = host_layer.forward(x)
+                got_static = host_layer.forward(x, rows_equal=True)  # fixed-shape exchange (world > 1), same sums
+                be.sync()
+                torch.cuda.synchronize()
+                # (the host-run form picks its kernels per received batch: fixed-point or f16 operands, both inside 2e-3)
+                out[f"host{rows}"] = (max(rel(got_host.cpu().numpy(), ref), rel(got_static.cpu().numpy(), ref)) / 20.0, mag, True)
+            # the fused forms of the op through the collective call: RmsNorm in front, residual behind, in place
+            rows = 8
+            h = torch.randn(rows, NE, generator=gen, device=dev)
+            nw = 1.0 + 0.1 * torch.randn(NE, generator=gen, device=dev)
+            hn = (h * torch.rsqrt((h * h).mean(1, keepdim=True) + 1e-6)) * nw
+            ref, _ = single_device(be, full, hn.contiguous(), rows, 1)
+            ref = ref + h.cpu().numpy()
+            from moe4all_b200 import MoeFfn
+            b = banded_lib.b
+            hb = be_lib.wrap_tensor(h)
+            be_lib.moe_ffn(MoeFfn(x=hb, dst=hb, residual=hb, norm_weight=be_lib.wrap_tensor(nw), norm_eps=1e-6, rows=rows, ne=NE,
+                                  n_expert=E, n_used=K, n_ff_exp=NFF, router=b["router"], gate_exps=b["gate"], up_exps=b["up"],
+                                  down_exps=b["down"], sh_gate=b["sh_gate"], sh_up=b["sh_up"], sh_down=b["sh_down"],
+                                  sh_gate_inp=b["sh_gate_inp"], sh_ff=NFF, ep_band=(rank * el, el)))
+            be_lib.sync()
             torch.cuda.synchronize()
-            ref = dst.cpu().numpy()
-            got = out.cpu().numpy()
-            rel = float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-3))
-            rel = max(rel, float(np.abs(out_static.cpu().numpy() - ref).max() / max(np.abs(ref).max(), 1e-3)))
-            ret[rank] = (rel, float(np.abs(ref).max()))
+            out["fused"] = (rel(h.cpu().numpy(), ref), float(np.abs(ref).max()), True)
+            if world > 1:
+                # host-side failure: rank 1 passes one row fewer than the others (a shape no rank has used
+                # yet); the shapes are compared before anything of the call is exchanged, so every rank
+                # fails the same way and nothing hangs
+                bad_rows = 5 if rank == 1 else 6
+                xb = torch.randn(bad_rows, NE, generator=gen, device=dev)
+                try:
+                    lib_layer.forward(xb)
+                    be_lib.sync()
+                    out["mismatch"] = "no error"
+                except BackendError as e:
+                    out["mismatch"] = "nccl" if e.code == ERR_NCCL else f"code {e.code}"
+                # the communicator survives a refused call: the next matching call still works
+                x = torch.randn(4, NE, generator=gen, device=dev)
+                ref, _ = single_device(be, full, x, 4, 1)
+                got = lib_layer.forward(x)
+                be_lib.sync()
+                torch.cuda.synchronize()
+                out["after"] = (rel(got.cpu().numpy(), ref), float(np.abs(ref).max()), True)
+                out["phases"] = be_lib.ep_last_phases()
+                be_lib.ep_finalize()
+        ret[rank] = out
     finally:
         if world > 1:
+            dist.barrier()
             dist.destroy_process_group()
 
 
-def test_ep_matches_single_device():
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_ep_matches_single_device(world):
     import torch.multiprocessing as mp
 
-    world = 2 if torch.cuda.device_count() >= 2 else 1
+    if world > 1 and torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
@@ -72,6 +148,14 @@ def test_ep_matches_single_device():
         mp.spawn(worker, args=(world, port, ret), nprocs=world, join=True)
         ret = dict(ret)
     assert len(ret) == world
-    for rank, (rel, mag) in ret.items():
-        assert mag > 0
-        assert rel < 1e-4, f"rank {rank}: expert-parallel result differs from single device by {rel:.2e}"
+    for rank, out in ret.items():
+        for name, val in out.items():
+            if name == "mismatch":
+                assert val == "nccl", f"rank {rank}: a mismatched shape must fail with the NCCL error class, got {val}"
+            elif name == "phases":
+                assert all(b >= a for a, b in zip(val, val[1:])) and val[-1] > 0, f"rank {rank}: phase stamps {val}"
+            else:
+                err, mag, ids_ok = val
+                assert mag > 0, f"rank {rank} {name}: vacuous"
+                assert ids_ok, f"rank {rank} {name}: expert ids differ from the single-device routing"
+                assert err < 1e-4, f"rank {rank} {name}: expert-parallel result differs from single device by {err:.2e}"

@@ -14,6 +14,9 @@ import numpy as np
 import pytest
 
 from moe4all_b200 import MoeFfn, MoeGating, synth
+from oracle import oracle as orc
+
+from helpers import near_tie_rows
 
 pytestmark = pytest.mark.gpu
 
@@ -65,6 +68,12 @@ def test_noalloc_route_matches_and_repeats(backend):
         assert np.array_equal(ids_a, ids_b), f"call {call}: expert ids differ"
         np.testing.assert_allclose(wts_b, wts_a, rtol=2e-6, atol=1e-9)
         assert len(set(ids_b.tolist())) > 6  # not a degenerate selection
+        # and against the CPU oracle's routing of the same rows (a one-expert band: routing only)
+        res = orc.moe_ffn(x, L.router, L.gate, L.up, L.down, n_expert=L.n_expert, n_used=6, n_ff_exp=L.n_ff, scale=2.5, gating=1,
+                          bias=L.bias, groups=8, groups_used=4, ep_band=(L.n_expert - 1, 1))
+        keep = [r for r in range(rows) if r not in set(near_tie_rows(res, 6).tolist())]
+        assert keep and np.array_equal(ids_b.reshape(rows, 6)[keep], res.ids[keep]), f"call {call}: ids differ from the oracle's"
+        np.testing.assert_allclose(wts_b.reshape(rows, 6)[keep], res.wts[keep], rtol=1e-5, atol=1e-8)
 
 
 def test_noalloc_route_softmax_shape_of_the_benchmark(backend):
@@ -72,6 +81,20 @@ def test_noalloc_route_softmax_shape_of_the_benchmark(backend):
     x = synth.activations(3, 1, 2048)
     (ids_a, wts_a), (ids_b, wts_b) = route_both(backend, L, x, 8)
     assert np.array_equal(ids_a, ids_b)
+    np.testing.assert_allclose(wts_b, wts_a, rtol=2e-6, atol=1e-9)
+    res = orc.moe_ffn(x, L.router, L.gate, L.up, L.down, n_expert=256, n_used=8, n_ff_exp=L.n_ff, ep_band=(255, 1))
+    if len(near_tie_rows(res, 8)) == 0:
+        assert np.array_equal(ids_b.reshape(1, 8), res.ids)
+        np.testing.assert_allclose(wts_b.reshape(1, 8), res.wts, rtol=1e-5, atol=1e-8)
+
+
+def test_noalloc_route_sqrt_softplus_and_untouched_ids_marker(backend):
+    # the third gating function goes through the same entry point; and the ids buffer is pre-filled with -1
+    # by the call itself, so a caller can tell "nothing was produced" from a result (no id is ever -1 here)
+    L = synth.make_layer(63, 1024, 64, 256, router_std=0.05)
+    x = synth.activations(4, 3, 1024)
+    (ids_a, wts_a), (ids_b, wts_b) = route_both(backend, L, x, 4, gating=MoeGating.SqrtSoftplus, scale=1.5)
+    assert np.array_equal(ids_a, ids_b) and (ids_b >= 0).all()
     np.testing.assert_allclose(wts_b, wts_a, rtol=2e-6, atol=1e-9)
 
 
