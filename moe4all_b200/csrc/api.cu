@@ -455,6 +455,30 @@ int32_t validate_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, ui
   return INFR_CUDA_OK;
 }
 
+// Which kernels serve a call of `rows` rows (measured on B200, 256 experts top-8, experts of 2 MB and of
+// 28 MB; pp = one CTA per pair, em = expert-major integer tensor-core tiles, gg = grouped GEMM on tcgen05):
+//   experts of 2 MB:   32 rows pp 174 / em 168 / gg 313 us; 64: 330 / 227 / 420; 256: 1206 / 363 / 488
+//   experts of 28 MB:  2 rows pp 290 / em 196 / gg 385 us; 64: 8190 / 2247 / 4083; 256: 32770 / 3785 / 4649
+// The expert-major form's time grows with the rows per expert, the grouped GEMM's hardly at all: they cross
+// near 11 (token, expert) pairs per expert.
+bool em_preferred(uint32_t rows, uint32_t n_used, uint32_t n_expert, uint32_t ne, uint32_t nff) {
+  const bool big = (uint64_t)ne * nff >= (1ull << 23);  // experts of tens of megabytes
+  return big ? rows >= 2 : (uint64_t)rows * n_used >= n_expert;
+}
+
+uint32_t choose_moe_path(const infr_cuda_ctx* ctx, uint32_t rows, uint32_t n_used, uint32_t n_expert, uint32_t ne, uint32_t nff,
+                         uint32_t sh_ff, bool down_q4k) {
+  const bool small_ok = decode_ffn_supported(ctx, (int)ne, (int)nff, (int)sh_ff, (int)n_used, down_q4k, nullptr);
+  const bool em_ok = ctx->cfg.expert_major != 1 && em_supported((int)ne, (int)nff, (int)sh_ff, (int)n_expert, down_q4k);
+  const uint64_t pairs8 = (uint64_t)rows * n_used * 8;
+  if (em_ok && pairs8 < (uint64_t)n_expert * 88) return 1;  // fewer than 11 pairs per expert
+  // without the expert-major kernels: per-pair kernels while an expert sees fewer than 2.75 rows (not for
+  // experts of tens of megabytes, where they hold one chunk of rows per CTA)
+  const bool big = (uint64_t)ne * nff >= (1ull << 23);
+  const bool few_per_expert = pairs8 <= (uint64_t)n_expert * 22;
+  return (small_ok && (big ? rows < 8 : (rows <= 8 || few_per_expert))) ? 1 : 2;
+}
+
 }  // namespace infr
 
 extern "C" {
@@ -541,26 +565,26 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   const bool has_sh = d->sh_gate != nullptr;
   std::string why;
   const bool down_q4k = d->down_dtype == INFR_CUDA_DT_Q4K;
-  const bool small_ok = decode_ffn_supported(ctx, d->ne, d->n_ff_exp, has_sh ? d->sh_ff : 0, d->n_used, down_q4k, &why);
+  const int sh_ff_eff = has_sh ? (int)d->sh_ff : 0;
+  const bool small_ok = decode_ffn_supported(ctx, d->ne, d->n_ff_exp, sh_ff_eff, d->n_used, down_q4k, &why);
+  const bool em_ok = em_supported((int)d->ne, (int)d->n_ff_exp, sh_ff_eff, (int)d->n_expert, down_q4k);
   uint32_t path = d->path;
-  // Per (token, expert) pair the small-m kernels are cheaper than a grouped-GEMM tile until an
-  // expert sees several tokens of the call on average; measured cross-over near 90 rows for
-  // 256 experts, top-8.
-  if (path == 0) {
-    const bool few_per_expert = (uint64_t)d->rows * d->n_used * 8 <= (uint64_t)d->n_expert * 22;  // <= 2.75 tokens per expert
-    // experts of tens of megabytes (hidden 7168 x intermediate 2048): the small-m kernels hold one
-    // chunk of rows per CTA there and the grouped GEMMs are ahead from eight rows on
-    const bool big = (uint64_t)d->ne * d->n_ff_exp >= (1ull << 23);
-    path = (small_ok && (big ? d->rows < 8 : (d->rows <= 8 || few_per_expert))) ? 1 : 2;
-  }
+  if (path == 0) path = choose_moe_path(ctx, d->rows, d->n_used, d->n_expert, d->ne, d->n_ff_exp, sh_ff_eff, down_q4k);
+  // One CTA per (token, expert) pair, or one per expert with all its tokens: the second form reads and
+  // unpacks an expert's blocks once however many rows of the call it serves, at the price of two more
+  // (small) launches.
+  const bool use_em = path == 1 && em_ok &&
+                      (ctx->cfg.expert_major == 2 || !small_ok ||
+                       (ctx->cfg.expert_major == 0 && em_preferred(d->rows, d->n_used, d->n_expert, d->ne, d->n_ff_exp)));
   if (path == 1) {
-    if (!small_ok) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, why);
+    if (!small_ok && !use_em) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, why);
     // Where the whole-row router kernel covers the call it also normalises x and makes its
     // fixed-point copy; otherwise the batched router runs and two small kernels do those jobs.
     const bool few = route_small_group(ctx, (int)d->rows, (int)d->ne, (int)d->n_expert) > 0;
     Scratch sz = carve(nullptr, d, true);
     const size_t hn_bytes = (!few && d->norm_weight) ? align_up((size_t)d->rows * d->ne * 4, 256) : 0;
-    if ((rc = ensure_scratch(ctx, sz.total + hn_bytes))) return rc;
+    const size_t em_bytes = use_em ? em_scratch_bytes((int)d->rows, (int)d->n_used, (int)d->ne, (int)d->n_ff_exp, sh_ff_eff) : 0;
+    if ((rc = ensure_scratch(ctx, sz.total + hn_bytes + em_bytes))) return rc;
     Scratch s = carve(ctx->scratch, d, true);
     RouteParams rp = route_params(ctx, d, s, true);
     const uint32_t stages = d->stages ? d->stages : 7u;
@@ -628,6 +652,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.act_kind = (int)d->act;
     dp.weight_before = d->weight_before ? 1 : 0;
     dp.clamp = d->swiglu_clamp;
+    if (use_em) return launch_em_ffn(ctx, dp, static_cast<char*>(ctx->scratch) + sz.total + hn_bytes, stages);
     return launch_decode_ffn(ctx, dp, true, stages);
   }
   // batched path: router GEMM + top-k, permute, grouped GEMMs, un-permute combine

@@ -412,13 +412,11 @@ int32_t ep_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     f.residual = nullptr;
     f.down_scale = d->down_scale ? &b_ds : nullptr;
     f.stages = 2u | 4u | 8u;  // routing is an input
-    // the path is chosen for what the band serves - about a W-th of the pairs - not for all T rows
+    // the path is chosen for what the band serves - about a W-th of the T rows' pairs over n_expert / W
+    // experts, i.e. R rows over El experts - not for all T rows
     if (f.path == 0) {
-      const bool few_per_expert = (uint64_t)R * k * 8 <= (uint64_t)El * 22;
-      const bool big = (uint64_t)ne * d->n_ff_exp >= (1ull << 23);
-      std::string why;
-      const bool small_ok = decode_ffn_supported(ctx, (int)ne, (int)d->n_ff_exp, 0, (int)k, d->down_dtype == INFR_CUDA_DT_Q4K, &why) && T <= 4096;
-      f.path = (small_ok && (big ? R < 8 : (R <= 8 || few_per_expert))) ? 1 : 2;
+      f.path = choose_moe_path(ctx, R, k, El, ne, d->n_ff_exp, 0, d->down_dtype == INFR_CUDA_DT_Q4K);
+      if (f.path == 1 && T > 4096) f.path = 2;  // the small-m kernels' grids and scratch grow with all T rows
     }
     if ((rc = infr_cuda_moe_ffn(ctx, &f))) return rc;
   }

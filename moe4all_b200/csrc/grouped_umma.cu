@@ -24,6 +24,7 @@
 
 #include "kernels.cuh"
 #include "umma.cuh"
+#include "tma.cuh"
 
 namespace infr {
 namespace {
@@ -61,16 +62,6 @@ __device__ __forceinline__ void q6_word_to_h2(uint32_t c, __half2 s, uint32_t& o
 // [tile][K step][256 rows][128 bytes].
 __device__ __forceinline__ size_t tile_step_offset(int tile, int k_steps, int step) {
   return ((size_t)tile * k_steps + step) * (size_t)(UN * 128);
-}
-
-// One tiled copy: a box of the 2-D tensor behind `tm` at (x = bytes inside the row, y = row) into
-// shared memory, completion counted in bytes on `bar`.  x * element size must be a multiple of 16.
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tm, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
-          smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
 }
 
 struct PipeBars {
@@ -581,33 +572,6 @@ bool umma_grouped_supported(int ne, int nff) { return ne % 256 == 0 && nff % 256
 int umma_tile_rows() { return UN; }
 
 namespace {
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-      f = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(f);
-  }();
-  return fn;
-}
-
-// A Q4_K bank as a 2-D byte tensor [rows][row_bytes]; box = one block (144 B) of `box_rows` rows.
-bool q4k_rows_map(CUtensorMap* tm, const uint8_t* base, size_t n_rows, size_t row_bytes, int box_rows) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)n_rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-  const cuuint32_t box[2] = {(cuuint32_t)Q4K_BLOCK_BYTES, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  return enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 }  // namespace
 

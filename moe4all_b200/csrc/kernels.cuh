@@ -61,6 +61,27 @@ struct DecodeParams {
   float clamp;           // > 0: routed experts clamp gate (one-sided) and up (both sides) first
 };
 
+// Expert-major small-m kernels (expert_major.cu): every (token, rank) pair of the call, grouped by
+// expert into segments of a few token rows; pair ids P + r stand for the shared expert's copy of row r.
+struct EmParams {
+  const int8_t *xq_lo, *xq_hi;   // [rows, ne] fixed-point limbs of x
+  const float* xscale;           // [rows]
+  int* xsum;                     // [rows, ne/32] integer sums of x per 32-element sub-block
+  const int32_t* ids;            // [rows, n_used]
+  const float* wts;              // [rows, n_used]
+  int *n_seg, *seg_expert, *seg_off, *seg_cnt, *seg_pairs;  // segment table, built on the device
+  const uint8_t *gate, *up, *down, *sh_gate, *sh_up, *sh_down;
+  size_t gate_stride, up_stride, down_stride;
+  float* act;                    // [pairs, nffmax] activations
+  float* y;                      // [pairs, ne] raw expert outputs
+  const float* down_scale;       // [n_expert] or null
+  DeviceStatus* status;
+  int rows, ne, n_used, nff, sh_ff, n_expert, nffmax;
+  uint32_t ep_lo, ep_n;
+  int act_kind, weight_before;
+  float clamp;
+};
+
 // Device-side view of one grouped-GEMM launch (see grouped_ffn.cu).
 struct GroupedParams {
   const int *tile_expert, *tile_row0, *tile_rows, *n_tiles;  // tile table built on the device
@@ -119,6 +140,12 @@ int32_t launch_combine(infr_cuda_ctx* ctx, const float* y, const int* pos_of_pai
 int32_t validate_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d);
 int32_t validate_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, uint32_t bank_experts);
 
+// Path choice for a call (api.cu): 1 = small-m kernels, 2 = grouped GEMMs; and, inside path 1, whether the
+// expert-major kernels are ahead of the per-pair ones.
+uint32_t choose_moe_path(const infr_cuda_ctx* ctx, uint32_t rows, uint32_t n_used, uint32_t n_expert, uint32_t ne, uint32_t nff,
+                         uint32_t sh_ff, bool down_q4k);
+bool em_preferred(uint32_t rows, uint32_t n_used, uint32_t n_expert, uint32_t ne, uint32_t nff);
+
 // Expert parallelism (ep.cu).  A descriptor is a collective call when the context has joined a
 // communicator of more than one rank and the descriptor names this rank's band.
 bool ep_call_is_collective(const infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d);
@@ -131,6 +158,10 @@ int32_t launch_route(infr_cuda_ctx* ctx, const RouteParams& p, bool pdl);
 // Rows per group the whole-row router kernel would use for this shape; 0 = the call takes the batched router.
 int route_small_group(const infr_cuda_ctx* ctx, int rows, int ne, int n_expert);
 int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages);
+// The expert-major form of the same stages (2: bucket + gate/up, 4: down + combine); `scratch` holds em_scratch_bytes(...).
+bool em_supported(int ne, int nff, int sh_ff, int n_expert, bool down_q4k);
+size_t em_scratch_bytes(int rows, int n_used, int ne, int nff, int sh_ff);
+int32_t launch_em_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, void* scratch, uint32_t stages);
 // Whether the small-m kernels cover this shape (dims, shared-memory budget).
 bool decode_ffn_supported(const infr_cuda_ctx* ctx, int ne, int nff, int sh_ff, int n_used, bool down_q4k, std::string* why);
 

@@ -95,8 +95,8 @@ class ExpertParallel:
         dest = torch.div(ids.clamp(0, self.n_expert - 1), self.e_local, rounding_mode="floor")                # [R, k]
         ranks = torch.arange(W, device=x.device, dtype=dest.dtype).view(W, 1, 1)
         ids_w = torch.where(dest.unsqueeze(0) == ranks, ids.unsqueeze(0), torch.full_like(ids, -1).unsqueeze(0))  # [W, R, k]
-        send_m = torch.cat([ids_w.contiguous().view(torch.float32), wts.unsqueeze(0).expand(W, R, k)], 2).reshape(W * R, 2 * k)
-        send_x = x.unsqueeze(0).expand(W, R, ne).reshape(W * R, ne)
+        send_m = torch.cat([ids_w.contiguous().view(torch.float32), wts.unsqueeze(0).expand(W, R, k)], 2).reshape(W * R, 2 * k).contiguous()
+        send_x = x.unsqueeze(0).expand(W, R, ne).reshape(W * R, ne).contiguous()  # (a one-row expand reshapes to a stride-0 view)
         recv_x = torch.empty_like(send_x)
         recv_m = torch.empty_like(send_m)
         self._a2a(recv_x, send_x)

@@ -55,6 +55,10 @@ def worker(rank, world, port, ret):
             be.set_stream(stream.cuda_stream)
             be_lib = CudaBackend(rank)       # exchange inside the library
             be_lib.set_stream(stream.cuda_stream)
+            # one form of the small-m kernels on both sides (left alone, a band call over all ranks' rows and a
+            # single-device call over one rank's rows may choose differently; both forms are oracle-checked elsewhere)
+            be.set_config(expert_major=2)
+            be_lib.set_config(expert_major=2)
             if world > 1:
                 join_communicator(be_lib)
             el = E // world
@@ -69,10 +73,10 @@ def worker(rank, world, port, ret):
             for rows in (1, 4, 16, 48):
                 x_all = torch.randn(world * rows, NE, generator=gen, device=dev)  # the same on every rank
                 x = x_all[rank * rows:(rank + 1) * rows].contiguous()
-                # the same kernels as the band call will pick (small-m while an expert sees few rows), so
-                # that the comparison isolates the exchange: the only difference left is the association of
-                # the sum over ranks
-                path = 1 if (rows <= 8 or rows * K * 8 <= el * 22) else 2
+                # the same kernels as the band call will pick (small-m while an expert sees fewer than 11
+                # rows), so that the comparison isolates the exchange: the only difference left is the
+                # association of the sum over ranks
+                path = 1 if rows * K * 8 < el * 88 else 2
                 ref, ref_ids = single_device(be, full, x, rows, path)
                 mag = float(np.abs(ref).max())
                 ids_lib = torch.empty(rows, K, dtype=torch.int32, device=dev)
@@ -91,7 +95,7 @@ def worker(rank, world, port, ret):
             h = torch.randn(rows, NE, generator=gen, device=dev)
             nw = 1.0 + 0.1 * torch.randn(NE, generator=gen, device=dev)
             hn = (h * torch.rsqrt((h * h).mean(1, keepdim=True) + 1e-6)) * nw
-            ref, _ = single_device(be, full, hn.contiguous(), rows, 1)
+            ref, _ = single_device(be, full, hn.contiguous(), rows, 1 if rows * K * 8 < el * 88 else 2)
             ref = ref + h.cpu().numpy()
             from moe4all_b200 import MoeFfn
             b = banded_lib.b
@@ -117,7 +121,7 @@ def worker(rank, world, port, ret):
                     out["mismatch"] = "nccl" if e.code == ERR_NCCL else f"code {e.code}"
                 # the communicator survives a refused call: the next matching call still works
                 x = torch.randn(4, NE, generator=gen, device=dev)
-                ref, _ = single_device(be, full, x, 4, 1)
+                ref, _ = single_device(be, full, x, 4, 1 if 4 * K * 8 < el * 88 else 2)
                 got = lib_layer.forward(x)
                 be_lib.sync()
                 torch.cuda.synchronize()
