@@ -22,6 +22,8 @@ int32_t check_cuda(infr_cuda_ctx* ctx, cudaError_t e, const char* what) {
 
 int32_t ensure_scratch(infr_cuda_ctx* ctx, size_t bytes) {
   if (bytes <= ctx->scratch_bytes) return INFR_CUDA_OK;
+  if (ctx->scratch_borrowed)
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "internal: a nested call needs more scratch than was set aside for it");
   if (ctx->capturing)
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "scratch would have to grow while recording: run the call once un-recorded first");
   // growing is a synchronising operation: earlier launches may still use the old block
@@ -179,7 +181,7 @@ int32_t infr_cuda_get_config(const infr_cuda_ctx* ctx, infr_cuda_config* out) {
 
 int32_t infr_cuda_set_config(infr_cuda_ctx* ctx, const infr_cuda_config* cfg) {
   if (!ctx || !cfg) return INFR_CUDA_ERR_INVALID_ARG;
-  if (cfg->gu_chunks > 4 || cfg->gu_warps > 16 || cfg->dn_warps > 24 || cfg->expert_major > 2 || cfg->topk_cta > 2)
+  if (cfg->gu_chunks > 4 || cfg->gu_warps > 16 || cfg->dn_warps > 24 || cfg->expert_major > 2)
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_config: a field is outside its range");
   for (uint32_t r : cfg->reserved)
     if (r) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_config: reserved fields must be zero");
@@ -542,6 +544,19 @@ RouteParams route_params(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, co
   return rp;
 }
 }  // namespace
+
+}  // extern "C"
+
+namespace infr {
+// Upper bound on the context scratch a small-m (path 1) call of this descriptor uses, whichever form serves it.
+size_t small_path_scratch_need(const infr_cuda_moe_ffn_desc* d) {
+  const int sh_ff = d->sh_gate ? (int)d->sh_ff : 0;
+  return carve(nullptr, d, true).total + align_up((size_t)d->rows * d->ne * 4, 256) +
+         em_scratch_bytes((int)d->rows, (int)d->n_used, (int)d->ne, (int)d->n_ff_exp, sh_ff) + 4096;
+}
+}  // namespace infr
+
+extern "C" {
 
 int32_t infr_cuda_moe_route(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;

@@ -57,6 +57,7 @@ struct infr_cuda_ctx {
   // scratch grown on demand (never inside a launch sequence that could be captured)
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  bool scratch_borrowed = false;  // `scratch` points into someone else's block for one nested call: never grown or freed
   infr::DeviceStatus* status = nullptr;       // the device's address of the status words below
   infr::DeviceStatus* status_host = nullptr;  // pinned, mapped host memory: kernels write it directly when they flag something
   float* route_logits = nullptr;              // device memory: the whole-row router kernel's logit buffer, all words

@@ -304,8 +304,20 @@ int32_t ep_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   const size_t o_x_all = take(x_all_b), o_ids_all = take(kk_all_b), o_wts_all = take(kk_all_b), o_loc_all = take(kk_all_b);
   const size_t o_part = take(x_all_b), o_back = take(x_all_b);
   const size_t o_sh_rows = has_sh ? take(x_local_b) : 0, o_sh_logit = has_sh ? take((size_t)R * 4) : 0, o_seg = take(256);
-  const size_t sh_scratch_b = has_sh ? grouped_scratch_bytes((int)R, 1, 2, (int)ne, (int)d->sh_ff) : 0;
-  const size_t o_sh_scratch = take(sh_scratch_b);
+  // The shared expert over this rank's own rows: a few rows go through the small-m kernels (a call with no
+  // routed pair: every id negative), a batch through the grouped GEMMs.  Either runs on the side stream with
+  // scratch of its own, next to the exchange buffers.
+  // the kernels are chosen for what the band serves - about a W-th of the T rows' pairs over n_expert / W
+  // experts, i.e. R rows over El experts - not for all T rows; the shared expert goes the same way
+  uint32_t band_path = d->path ? d->path : choose_moe_path(ctx, R, k, El, ne, d->n_ff_exp, 0, d->down_dtype == INFR_CUDA_DT_Q4K);
+  if (band_path == 1 && T > 4096) band_path = 2;  // the small-m kernels' grids and scratch grow with all T rows
+  const bool sh_small = has_sh && band_path == 1;
+  infr_cuda_moe_ffn_desc shd = *d;  // the nested small-m call (filled in below)
+  shd.rows = R;
+  shd.n_expert = El;
+  shd.stages = 2u | 4u | 8u;
+  const size_t sh_scratch_b = !has_sh ? 0 : (sh_small ? small_path_scratch_need(&shd) : grouped_scratch_bytes((int)R, 1, 2, (int)ne, (int)d->sh_ff));
+  const size_t o_sh_scratch = take(sh_scratch_b), o_neg = sh_small ? take(kk_local_b) : 0;
   if ((rc = ep_ensure_buf(ctx, off))) return rc;
   char* B = static_cast<char*>(ep->buf);
   cudaStream_t main = ctx->stream;
@@ -327,29 +339,57 @@ int32_t ep_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     if (e == cudaSuccess) e = cudaStreamWaitEvent(ep->side, ep->ev_fork, 0);
     if (e != cudaSuccess) return check_cuda(ctx, e, "expert parallel: fork");
     ctx->stream = ep->side;
-    k_ep_set_pair<<<1, 1, 0, ep->side>>>(reinterpret_cast<int*>(B + o_seg), 0, (int)R);  // segment offsets of the one "expert"
-    ctx->launches += 1;
-    GroupedCall c = {};
-    c.scratch = B + o_sh_scratch;
-    c.x = x_eff;
-    c.seg_off_in = reinterpret_cast<const int*>(B + o_seg);
-    c.y_out = reinterpret_cast<float*>(B + o_sh_rows);
-    c.gate = static_cast<const uint8_t*>(d->sh_gate->ptr);
-    c.up = static_cast<const uint8_t*>(d->sh_up->ptr);
-    c.down = static_cast<const uint8_t*>(d->sh_down->ptr);
-    c.gate_stride = (size_t)d->sh_ff * row_bytes(d->gate_dtype, ne);
-    c.up_stride = c.gate_stride;
-    c.down_stride = (size_t)ne * row_bytes(d->down_dtype, d->sh_ff);
-    c.rows = (int)R;
-    c.n_used = 1;
-    c.n_pairs = 1;
-    c.ne = (int)ne;
-    c.nff = (int)d->sh_ff;
-    c.n_expert = 1;
-    c.rows_bound = (int)R;
-    c.down_q4k = d->down_dtype == INFR_CUDA_DT_Q4K ? 1 : 0;
-    c.act_kind = (int)d->act;
-    rc = e == cudaSuccess ? launch_grouped_ffn(ctx, c) : check_cuda(ctx, e, "expert parallel: shared expert set-up");
+    if (sh_small) {
+      e = cudaMemsetAsync(B + o_neg, 0xFF, kk_local_b, ep->side);  // every (token, rank) pair "not this call's"
+      infr_cuda_buf b_neg = view(B + o_neg, kk_local_b), b_w = view(B + o_wts, kk_local_b), b_sh = view(B + o_sh_rows, x_local_b);
+      shd.x = &b_x;
+      shd.router_x = &b_x;
+      shd.dst = &b_sh;
+      shd.ids_out = &b_neg;
+      shd.wts_out = &b_w;  // never used: no pair is served
+      shd.ep_lo = shd.ep_n_local = 0;
+      shd.exp_probs_b = nullptr;
+      shd.expert_ids = nullptr;
+      shd.down_scale = nullptr;
+      shd.n_expert_groups = shd.n_expert_groups_used = 0;
+      shd.sh_gate_inp = nullptr;  // the plain sum 0 + shexp(x); the gate is applied with the final sum
+      shd.norm_weight = nullptr;
+      shd.residual = nullptr;
+      shd.path = 1;
+      void* keep_s = ctx->scratch;
+      const size_t keep_b = ctx->scratch_bytes;
+      ctx->scratch = B + o_sh_scratch;
+      ctx->scratch_bytes = sh_scratch_b;
+      ctx->scratch_borrowed = true;
+      rc = e == cudaSuccess ? infr_cuda_moe_ffn(ctx, &shd) : check_cuda(ctx, e, "expert parallel: shared expert set-up");
+      ctx->scratch = keep_s;
+      ctx->scratch_bytes = keep_b;
+      ctx->scratch_borrowed = false;
+    } else {
+      k_ep_set_pair<<<1, 1, 0, ep->side>>>(reinterpret_cast<int*>(B + o_seg), 0, (int)R);  // segment offsets of the one "expert"
+      ctx->launches += 1;
+      GroupedCall c = {};
+      c.scratch = B + o_sh_scratch;
+      c.x = x_eff;
+      c.seg_off_in = reinterpret_cast<const int*>(B + o_seg);
+      c.y_out = reinterpret_cast<float*>(B + o_sh_rows);
+      c.gate = static_cast<const uint8_t*>(d->sh_gate->ptr);
+      c.up = static_cast<const uint8_t*>(d->sh_up->ptr);
+      c.down = static_cast<const uint8_t*>(d->sh_down->ptr);
+      c.gate_stride = (size_t)d->sh_ff * row_bytes(d->gate_dtype, ne);
+      c.up_stride = c.gate_stride;
+      c.down_stride = (size_t)ne * row_bytes(d->down_dtype, d->sh_ff);
+      c.rows = (int)R;
+      c.n_used = 1;
+      c.n_pairs = 1;
+      c.ne = (int)ne;
+      c.nff = (int)d->sh_ff;
+      c.n_expert = 1;
+      c.rows_bound = (int)R;
+      c.down_q4k = d->down_dtype == INFR_CUDA_DT_Q4K ? 1 : 0;
+      c.act_kind = (int)d->act;
+      rc = launch_grouped_ffn(ctx, c);
+    }
     if (rc == INFR_CUDA_OK && d->sh_gate_inp)
       rc = launch_linear(ctx, INFR_CUDA_DT_F32, static_cast<const uint8_t*>(d->sh_gate_inp->ptr), x_eff,
                          reinterpret_cast<float*>(B + o_sh_logit), (int)R, (int)ne, 1);
@@ -412,12 +452,7 @@ int32_t ep_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     f.residual = nullptr;
     f.down_scale = d->down_scale ? &b_ds : nullptr;
     f.stages = 2u | 4u | 8u;  // routing is an input
-    // the path is chosen for what the band serves - about a W-th of the T rows' pairs over n_expert / W
-    // experts, i.e. R rows over El experts - not for all T rows
-    if (f.path == 0) {
-      f.path = choose_moe_path(ctx, R, k, El, ne, d->n_ff_exp, 0, d->down_dtype == INFR_CUDA_DT_Q4K);
-      if (f.path == 1 && T > 4096) f.path = 2;  // the small-m kernels' grids and scratch grow with all T rows
-    }
+    f.path = band_path;
     if ((rc = infr_cuda_moe_ffn(ctx, &f))) return rc;
   }
   phase(ctx, 3);

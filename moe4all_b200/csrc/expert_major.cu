@@ -577,16 +577,29 @@ __global__ void __launch_bounds__(256) k_em_combine(EmParams p, const float* sh_
   const int P = p.rows * p.n_used;
   for (int r = blockIdx.y; r < p.rows; r += gridDim.y) {
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < p.n_used; ++s) {
-      const int pr = r * p.n_used + s;
-      int e = __ldcg(p.ids + pr);
-      if (e < 0) continue;
-      e = min(e, p.n_expert - 1);
-      if (p.ep_n != 0 && ((uint32_t)e < p.ep_lo || (uint32_t)e >= p.ep_lo + p.ep_n)) continue;
-      const float w = p.weight_before ? 1.0f : __ldcg(p.wts + pr);
-      const float ds = p.down_scale ? __ldg(p.down_scale + e) : 1.0f;
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(p.y + (size_t)pr * p.ne + c));
-      o.x += w * (v.x * ds); o.y += w * (v.y * ds); o.z += w * (v.z * ds); o.w += w * (v.w * ds);
+    for (int s0 = 0; s0 < p.n_used; s0 += 8) {
+      // eight ranks at a time: ids, weights and rows are requested together, then added in rank order
+      float w[8];
+      float4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int pr = r * p.n_used + s0 + j;
+        w[j] = 0.f;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (s0 + j >= p.n_used) continue;
+        int e = __ldcg(p.ids + pr);
+        if (e < 0) continue;
+        e = min(e, p.n_expert - 1);
+        if (p.ep_n != 0 && ((uint32_t)e < p.ep_lo || (uint32_t)e >= p.ep_lo + p.ep_n)) continue;
+        const float ds = p.down_scale ? __ldg(p.down_scale + e) : 1.0f;
+        w[j] = p.weight_before ? 1.0f : __ldcg(p.wts + pr);
+        v[j] = __ldcg(reinterpret_cast<const float4*>(p.y + (size_t)pr * p.ne + c));
+        v[j].x *= ds; v[j].y *= ds; v[j].z *= ds; v[j].w *= ds;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {  // a skipped rank adds 0 * 0: the sum is the one over the served ranks, in order
+        o.x += w[j] * v[j].x; o.y += w[j] * v[j].y; o.z += w[j] * v[j].z; o.w += w[j] * v[j].w;
+      }
     }
     if (p.sh_ff) {
       const float gsh = sh_logit ? 1.0f / (1.0f + __expf(-__ldcg(sh_logit + r))) : 1.0f;

@@ -146,6 +146,8 @@ uint32_t choose_moe_path(const infr_cuda_ctx* ctx, uint32_t rows, uint32_t n_use
                          uint32_t sh_ff, bool down_q4k);
 bool em_preferred(uint32_t rows, uint32_t n_used, uint32_t n_expert, uint32_t ne, uint32_t nff);
 
+size_t small_path_scratch_need(const infr_cuda_moe_ffn_desc* d);
+
 // Expert parallelism (ep.cu).  A descriptor is a collective call when the context has joined a
 // communicator of more than one rank and the descriptor names this rank's band.
 bool ep_call_is_collective(const infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d);
