@@ -284,6 +284,29 @@ class Backend {
   Status add(const Buffer& a, const Buffer& b, Buffer& dst, size_t n) { return st(infr_cuda_add(ctx_, a.handle(), b.handle(), dst.handle(), n)); }
 
   // backend.rs:907-908: ops issued between begin_record and end_record are compiled into a plan
+  // ---- tuning switches (the reference's typed kernel config, crates/infr-core/src/config/mod.rs:1-29) ----
+  Result<infr_cuda_config> config() const {
+    Result<infr_cuda_config> r;
+    r.status = st(infr_cuda_get_config(ctx_, &r.value));
+    return r;
+  }
+  Status set_config(const infr_cuda_config& cfg) { return st(infr_cuda_set_config(ctx_, &cfg)); }
+
+  // ---- expert parallelism (ExpertParallelBackend, crates/infr-vulkan/src/ep.rs) ----
+  // Rank 0 makes the id and hands it to the other ranks; `join` is collective.  Afterwards a MoeFfn
+  // whose band is this rank's runs as the collective form of the op (banks hold the band only).
+  static Result<std::vector<uint8_t>> ep_unique_id() {
+    Result<std::vector<uint8_t>> r;
+    r.value.resize(INFR_CUDA_EP_ID_BYTES);
+    r.status = make_status(nullptr, infr_cuda_ep_unique_id(r.value.data()), "ncclGetUniqueId failed (is libnccl.so.2 loadable?)");
+    return r;
+  }
+  Status join(const std::vector<uint8_t>& id, int32_t rank, int32_t world) {
+    if (id.size() != INFR_CUDA_EP_ID_BYTES) return make_status(nullptr, INFR_CUDA_ERR_INVALID_ARG, "the communicator id must be 128 bytes");
+    return st(infr_cuda_ep_init(ctx_, id.data(), rank, world));
+  }
+  Status leave() { return st(infr_cuda_ep_finalize(ctx_)); }
+
   Status begin_record() { return st(infr_cuda_graph_begin(ctx_)); }
   Result<Plan> end_record() {
     Result<Plan> r;
