@@ -583,7 +583,11 @@ def run_ours(args):
     # ---- the step's three kernels, each replayed alone (stage masks: 1 router + top-k, 2 gate/up, 4 down) ----
     kernel_us = {}
     n_k = 200
-    for name, mask in (("k_router_small", 1), ("k_decode_gateup", 2), ("k_decode_down", 4)):
+    # from n_expert / n_used rows on, the small-m path runs its expert-major kernels (the library's own rule)
+    em = N_EXPERT <= R * N_USED and R * N_USED * 8 < N_EXPERT * 88
+    names = ("k_router_small", "k_em_bucket + k_em_gateup", "k_em_down + k_em_combine") if em else \
+            ("k_router_small", "k_decode_gateup", "k_decode_down")
+    for name, mask in zip(names, (1, 2, 4)):
         for s in range(SETS):
             be.moe_ffn(op_for(s, stages=mask))
         be.sync()
@@ -652,8 +656,7 @@ def run_ours(args):
         step_us = ms * 1e3 / K
         active_bytes = (mean_u + 1) * EXPERT_BYTES  # routed experts actually touched + the shared expert
         layer_gbs = active_bytes / (step_us * 1e-6) / 1e9
-        kbytes = {"k_router_small": N_EXPERT * NE * 4 + R * NE * 4, "k_decode_gateup": (mean_u + 1) * 2 * N_FF * Q4K_ROW,
-                  "k_decode_down": (mean_u + 1) * NE * Q6K_ROW}
+        kbytes = dict(zip(names, (N_EXPERT * NE * 4 + R * NE * 4, (mean_u + 1) * 2 * N_FF * Q4K_ROW, (mean_u + 1) * NE * Q6K_ROW)))
         kernels = [{"name": n, "us_alone": kernel_us[n], "algorithmic_bytes": kbytes[n],
                     "gbs_alone": kbytes[n] / (kernel_us[n] * 1e-6) / 1e9, "hbm_frac_alone": kbytes[n] / (kernel_us[n] * 1e-6) / 1e9 / peaks["hbm_gbs"],
                     "traffic": NCU_TRAFFIC_R1[n] if R == 1 else None} for n in kernel_us]

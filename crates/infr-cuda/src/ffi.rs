@@ -94,9 +94,8 @@ pub struct infr_cuda_config {
     pub upload_by_copy: u32,
     pub trace_tile: u32,
     pub expert_major: u32,
-    pub dense_min_tiles: u32,
     pub sync_timeout_ms: u32,
-    pub reserved: [u32; 8],
+    pub reserved: [u32; 9],
 }
 
 extern "C" {

@@ -82,13 +82,10 @@ typedef struct infr_cuda_config {
   uint32_t expert_major;         /* small-m path, who owns a CTA: 0 = choose by rows (default), 1 = always
                                     one (token, expert) pair per CTA, 2 = always one expert with all of
                                     its tokens per CTA (int8 tensor-core tiles)                           */
-  uint32_t dense_min_tiles;      /* batched path: experts with at least this many 256-token tiles are
-                                    unpacked to f16 once per call and fed to the tensor cores by tiled
-                                    copies; 0 = never (default 2)                                         */
   uint32_t sync_timeout_ms;      /* expert-parallel contexts: how long infr_cuda_sync waits for the stream
                                     before it aborts the communicator and returns INFR_CUDA_ERR_NCCL
                                     (default 60000)                                                       */
-  uint32_t reserved[8];          /* zero                                                                  */
+  uint32_t reserved[9];          /* zero                                                                  */
 } infr_cuda_config;
 int32_t infr_cuda_get_config(const infr_cuda_ctx* ctx, infr_cuda_config* out);
 int32_t infr_cuda_set_config(infr_cuda_ctx* ctx, const infr_cuda_config* cfg);

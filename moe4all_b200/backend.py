@@ -105,8 +105,8 @@ class Config(C.Structure):
     crates/infr-core/src/config/mod.rs:1-29)."""
     _fields_ = [
         ("gu_warps", C.c_uint32), ("gu_chunks", C.c_uint32), ("dn_warps", C.c_uint32), ("upload_by_copy", C.c_uint32),
-        ("trace_tile", C.c_uint32), ("expert_major", C.c_uint32), ("dense_min_tiles", C.c_uint32),
-        ("sync_timeout_ms", C.c_uint32), ("reserved", C.c_uint32 * 8),
+        ("trace_tile", C.c_uint32), ("expert_major", C.c_uint32),
+        ("sync_timeout_ms", C.c_uint32), ("reserved", C.c_uint32 * 9),
     ]
 
 

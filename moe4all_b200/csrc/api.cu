@@ -80,7 +80,6 @@ infr_cuda_config default_config() {
   c.gu_warps = 4;
   c.gu_chunks = 4;
   c.dn_warps = 12;
-  c.dense_min_tiles = 2;
   c.sync_timeout_ms = 60000;
   return c;
 }
