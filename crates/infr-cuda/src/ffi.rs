@@ -28,6 +28,8 @@ pub const ERR_TIMEOUT: i32 = -6;
 pub const DT_F32: i32 = 0;
 pub const DT_Q4K: i32 = 12;
 pub const DT_Q6K: i32 = 14;
+pub const DT_Q8_0: i32 = 8;
+pub const DT_Q5K: i32 = 13;
 
 pub const EP_ID_BYTES: usize = 128;
 

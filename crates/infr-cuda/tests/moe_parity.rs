@@ -49,14 +49,16 @@ struct Case {
     groups: (u32, u32),
     bias: bool,
     down: DType,
+    /// format of the gate and up banks
+    gu: DType,
 }
 
 fn moe_case(c: &Case) -> (Graph, Vec<(TensorId, Vec<u8>)>, TensorId) {
     let mut g = Graph::new();
     let x = g.input(f32d(c.rows * c.ne));
     let router = g.weight(f32d(c.n_expert * c.ne));
-    let gate = g.weight(qd(c.n_expert * c.n_ff * c.ne, DType::Q4K));
-    let up = g.weight(qd(c.n_expert * c.n_ff * c.ne, DType::Q4K));
+    let gate = g.weight(qd(c.n_expert * c.n_ff * c.ne, c.gu));
+    let up = g.weight(qd(c.n_expert * c.n_ff * c.ne, c.gu));
     let down = g.weight(qd(c.n_expert * c.ne * c.n_ff, c.down));
     let bias = if c.bias { Some(g.weight(f32d(c.n_expert))) } else { None };
     let dst = g.output(f32d(c.rows * c.ne));
@@ -95,8 +97,8 @@ fn moe_case(c: &Case) -> (Graph, Vec<(TensorId, Vec<u8>)>, TensorId) {
     let mut bound = vec![
         (x, bytes_of(&gen_f32(c.rows * c.ne, 1))),
         (router, bytes_of(&r)),
-        (gate, synth_weight(DType::Q4K, c.n_expert * c.n_ff * c.ne, 11)),
-        (up, synth_weight(DType::Q4K, c.n_expert * c.n_ff * c.ne, 12)),
+        (gate, synth_weight(c.gu, c.n_expert * c.n_ff * c.ne, 11)),
+        (up, synth_weight(c.gu, c.n_expert * c.n_ff * c.ne, 12)),
         (down, synth_weight(c.down, c.n_expert * c.ne * c.n_ff, 13)),
     ];
     if let Some(b) = bias {
@@ -123,7 +125,7 @@ fn check(c: Case, what: &str) {
 fn moe_decode_rows_1_and_4() {
     for rows in [1usize, 4] {
         check(
-            Case { rows, ne: 512, n_expert: 16, n_used: 4, n_ff: 256, gating: MoeGating::Softmax, groups: (0, 0), bias: false, down: DType::Q6K },
+            Case { rows, ne: 512, n_expert: 16, n_used: 4, n_ff: 256, gating: MoeGating::Softmax, groups: (0, 0), bias: false, down: DType::Q6K, gu: DType::Q4K },
             &format!("MoeFfn decode rows={rows}"),
         );
     }
@@ -132,7 +134,7 @@ fn moe_decode_rows_1_and_4() {
 #[test]
 fn moe_batched_rows_96() {
     check(
-        Case { rows: 96, ne: 512, n_expert: 16, n_used: 4, n_ff: 256, gating: MoeGating::Softmax, groups: (0, 0), bias: false, down: DType::Q6K },
+        Case { rows: 96, ne: 512, n_expert: 16, n_used: 4, n_ff: 256, gating: MoeGating::Softmax, groups: (0, 0), bias: false, down: DType::Q6K, gu: DType::Q4K },
         "MoeFfn batched rows=96 (grouped GEMM on tcgen05)",
     );
 }
@@ -140,7 +142,7 @@ fn moe_batched_rows_96() {
 #[test]
 fn moe_sigmoid_groups_bias() {
     check(
-        Case { rows: 3, ne: 512, n_expert: 32, n_used: 4, n_ff: 256, gating: MoeGating::Sigmoid, groups: (4, 2), bias: true, down: DType::Q6K },
+        Case { rows: 3, ne: 512, n_expert: 32, n_used: 4, n_ff: 256, gating: MoeGating::Sigmoid, groups: (4, 2), bias: true, down: DType::Q6K, gu: DType::Q4K },
         "MoeFfn sigmoid gating, 4 groups / 2 used, selection bias",
     );
 }
@@ -148,9 +150,23 @@ fn moe_sigmoid_groups_bias() {
 #[test]
 fn moe_sqrt_softplus_and_q4k_down() {
     check(
-        Case { rows: 2, ne: 512, n_expert: 16, n_used: 2, n_ff: 256, gating: MoeGating::SqrtSoftplus, groups: (0, 0), bias: false, down: DType::Q4K },
+        Case { rows: 2, ne: 512, n_expert: 16, n_used: 2, n_ff: 256, gating: MoeGating::SqrtSoftplus, groups: (0, 0), bias: false, down: DType::Q4K, gu: DType::Q4K },
         "MoeFfn sqrt-softplus gating, Q4_K down bank",
     );
+}
+
+/// Other bank formats real files mix in (`crates/infr-core/src/tensor.rs:172-196`): Q5_K gate/up with a
+/// Q6_K down bank, and Q8_0 throughout, on the small-m kernels and on the grouped GEMM tiles.
+#[test]
+fn moe_q5k_and_q8_0_banks() {
+    for (gu, down, name) in [(DType::Q5K, DType::Q6K, "Q5_K / Q6_K"), (DType::Q8_0, DType::Q8_0, "Q8_0")] {
+        for rows in [1usize, 4, 96] {
+            check(
+                Case { rows, ne: 512, n_expert: 16, n_used: 4, n_ff: 256, gating: MoeGating::Softmax, groups: (0, 0), bias: false, down, gu },
+                &format!("MoeFfn {name} banks rows={rows}"),
+            );
+        }
+    }
 }
 
 /// The whole FFN sub-layer as the graph builder emits it for qwen35moe

@@ -38,6 +38,8 @@ extern "C" {
 #define INFR_CUDA_DT_F32 0
 #define INFR_CUDA_DT_Q4K 12 /* 256 weights / 144 B, crates/infr-core/src/decode_spec.rs:327 */
 #define INFR_CUDA_DT_Q6K 14 /* 256 weights / 210 B, crates/infr-core/src/decode_spec.rs:331 */
+#define INFR_CUDA_DT_Q8_0 8 /* 32 weights / 34 B, crates/infr-core/src/decode_spec.rs:320   */
+#define INFR_CUDA_DT_Q5K 13 /* 256 weights / 176 B, crates/infr-core/src/decode_spec.rs:329 */
 
 /* MoeGating (crates/infr-core/src/graph.rs:73-85). */
 #define INFR_CUDA_GATING_SOFTMAX 0
@@ -139,7 +141,7 @@ typedef struct infr_cuda_moe_ffn_desc {
   const infr_cuda_buf* router;      /* [n_expert, ne] router_dtype                                 */
   const infr_cuda_buf* gate_exps;   /* [n_expert, n_ff_exp, ne] gate_dtype                         */
   const infr_cuda_buf* up_exps;     /* [n_expert, n_ff_exp, ne] up_dtype                           */
-  const infr_cuda_buf* down_exps;   /* [n_expert, ne, n_ff_exp] down_dtype (Q6_K or Q4_K)          */
+  const infr_cuda_buf* down_exps;   /* [n_expert, ne, n_ff_exp] down_dtype                         */
   const infr_cuda_buf* exp_probs_b; /* [n_expert] f32 selection-only bias, or NULL                 */
   infr_cuda_buf* dst;               /* [rows, ne] f32                                              */
   infr_cuda_buf* ids_out;           /* [rows, n_used] i32 selected experts, rank order; or NULL    */
@@ -247,7 +249,7 @@ int32_t infr_cuda_moe_route_noalloc(int32_t device, void* cuda_stream, const flo
 /* ---- the ops around it (shared expert and the 40-layer stack) --------------------------------- */
 
 /* Op::Linear (crates/infr-cpu/src/lib.rs:1275-1328): y[m, out_f] = x[m, in_f] · Wᵀ, W row-major
- * [out_f, in_f] of `dtype` (F32, Q4_K, Q6_K). */
+ * [out_f, in_f] of `dtype` (F32, Q4_K, Q5_K, Q6_K, Q8_0). */
 int32_t infr_cuda_linear(infr_cuda_ctx* ctx, int32_t dtype, const infr_cuda_buf* w, const infr_cuda_buf* x,
                          infr_cuda_buf* y, uint32_t m, uint32_t in_f, uint32_t out_f);
 /* Op::GatedAct with Activation::Silu, contiguous operands (crates/infr-cpu/src/lib.rs:2973-3027):

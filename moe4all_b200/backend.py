@@ -54,15 +54,19 @@ class Unsupported(BackendError):
 class DType(enum.IntEnum):
     """crates/infr-core/src/tensor.rs:7-57, numbered as in the GGUF file format."""
     F32 = 0
+    Q8_0 = 8
     Q4K = 12
+    Q5K = 13
     Q6K = 14
 
     def row_bytes(self, n_elem: int) -> int:
+        """crates/infr-core/src/decode_spec.rs:315-335: elements and bytes per block."""
         if self is DType.F32:
             return n_elem * 4
-        if n_elem % 256:
-            raise ValueError(f"{self.name}: {n_elem} elements is not a whole number of 256-element blocks")
-        return n_elem // 256 * (144 if self is DType.Q4K else 210)
+        elems, nbytes = {DType.Q8_0: (32, 34), DType.Q4K: (256, 144), DType.Q5K: (256, 176), DType.Q6K: (256, 210)}[self]
+        if n_elem % elems:
+            raise ValueError(f"{self.name}: {n_elem} elements is not a whole number of {elems}-element blocks")
+        return n_elem // elems * nbytes
 
 
 class MoeGating(enum.IntEnum):

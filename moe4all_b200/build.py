@@ -12,7 +12,7 @@ OUT_DIR = os.path.join(HERE, "_lib")
 LIB = os.path.join(OUT_DIR, "libinfr_cuda.so")
 
 SOURCES = ["api.cu", "router_topk.cu", "decode_ffn.cu", "dense_ops.cu", "grouped_ffn.cu", "grouped_umma.cu", "umma_selftest.cu",
-           "gguf_ingest.cu", "ep.cu", "expert_major.cu"]
+           "gguf_ingest.cu", "ep.cu", "expert_major.cu", "anyfmt_ffn.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -5,6 +5,7 @@
 #include <mutex>
 #include <new>
 
+#include "formats.cuh"
 #include "kernels.cuh"
 
 namespace infr {
@@ -415,16 +416,18 @@ int32_t validate_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, ui
   int32_t rc = validate_moe_route(ctx, d);
   if (rc) return rc;
   if (!d->n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: zero n_ff_exp");
-  if (d->gate_dtype != INFR_CUDA_DT_Q4K || d->up_dtype != INFR_CUDA_DT_Q4K ||
-      (d->down_dtype != INFR_CUDA_DT_Q6K && d->down_dtype != INFR_CUDA_DT_Q4K))
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be gate/up Q4_K and down Q6_K or Q4_K");
+  if (!bank_dtype_ok(d->gate_dtype) || !bank_dtype_ok(d->up_dtype) || !bank_dtype_ok(d->down_dtype))
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be Q4_K, Q5_K, Q6_K or Q8_0");
+  if (d->fused_gate_up && d->gate_dtype != d->up_dtype)
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: a fused gate/up bank has one dtype");
   if (d->ne % 256 || d->n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ne and n_ff_exp must be multiples of the 256-weight block");
   const size_t xb = (size_t)d->rows * d->ne * 4;
   if (!fits(d->x, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: x missing or too small");
   if (!fits(d->dst, xb)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: dst missing or too small");
   const size_t gb = (size_t)bank_experts * d->n_ff_exp * row_bytes(d->gate_dtype, d->ne);
+  const size_t ub = (size_t)bank_experts * d->n_ff_exp * row_bytes(d->up_dtype, d->ne);
   const size_t db = (size_t)bank_experts * d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
-  if (d->fused_gate_up ? !fits(d->gate_exps, 2 * gb) : (!fits(d->gate_exps, gb) || !fits(d->up_exps, gb)))
+  if (d->fused_gate_up ? !fits(d->gate_exps, 2 * gb) : (!fits(d->gate_exps, gb) || !fits(d->up_exps, ub)))
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: gate/up bank missing or too small");
   if (!fits(d->down_exps, db)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: down bank missing or too small");
   if (d->norm_weight) {
@@ -444,9 +447,9 @@ int32_t validate_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, ui
   if (d->sh_gate || d->sh_up || d->sh_down) {
     if (!d->sh_gate || !d->sh_up || !d->sh_down || !d->sh_ff || d->sh_ff % 256)
       return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: shared expert needs gate, up, down and sh_ff (multiple of 256)");
-    const size_t sgb = (size_t)d->sh_ff * row_bytes(d->gate_dtype, d->ne);
+    const size_t sgb = (size_t)d->sh_ff * row_bytes(d->gate_dtype, d->ne), sub = (size_t)d->sh_ff * row_bytes(d->up_dtype, d->ne);
     const size_t sdb = (size_t)d->ne * row_bytes(d->down_dtype, d->sh_ff);
-    if (!fits(d->sh_gate, sgb) || !fits(d->sh_up, sgb) || !fits(d->sh_down, sdb))
+    if (!fits(d->sh_gate, sgb) || !fits(d->sh_up, sub) || !fits(d->sh_down, sdb))
       return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: shared expert tensor too small");
     if (d->sh_gate_inp && !fits(d->sh_gate_inp, (size_t)d->ne * 4))
       return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: sh_gate_inp too small");
@@ -468,9 +471,9 @@ bool em_preferred(uint32_t rows, uint32_t n_used, uint32_t n_expert, uint32_t ne
 }
 
 uint32_t choose_moe_path(const infr_cuda_ctx* ctx, uint32_t rows, uint32_t n_used, uint32_t n_expert, uint32_t ne, uint32_t nff,
-                         uint32_t sh_ff, bool down_q4k) {
-  const bool small_ok = decode_ffn_supported(ctx, (int)ne, (int)nff, (int)sh_ff, (int)n_used, down_q4k, nullptr);
-  const bool em_ok = ctx->cfg.expert_major != 1 && em_supported((int)ne, (int)nff, (int)sh_ff, (int)n_expert, down_q4k);
+                         uint32_t sh_ff, BankTypes bt) {
+  const bool small_ok = decode_ffn_supported(ctx, (int)ne, (int)nff, (int)sh_ff, (int)n_used, bt, nullptr);
+  const bool em_ok = ctx->cfg.expert_major != 1 && em_supported((int)ne, (int)nff, (int)sh_ff, (int)n_expert, bt);
   const uint64_t pairs8 = (uint64_t)rows * n_used * 8;
   if (em_ok && pairs8 < (uint64_t)n_expert * 88) return 1;  // fewer than 11 pairs per expert
   // without the expert-major kernels: per-pair kernels while an expert sees fewer than 2.75 rows (not for
@@ -578,12 +581,13 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   DeviceGuard g(ctx->device);
   const bool has_sh = d->sh_gate != nullptr;
   std::string why;
-  const bool down_q4k = d->down_dtype == INFR_CUDA_DT_Q4K;
+  const BankTypes bt = {d->gate_dtype, d->up_dtype, d->down_dtype};
+  const bool down_q4k = bt.down_q4k();
   const int sh_ff_eff = has_sh ? (int)d->sh_ff : 0;
-  const bool small_ok = decode_ffn_supported(ctx, d->ne, d->n_ff_exp, sh_ff_eff, d->n_used, down_q4k, &why);
-  const bool em_ok = em_supported((int)d->ne, (int)d->n_ff_exp, sh_ff_eff, (int)d->n_expert, down_q4k);
+  const bool small_ok = decode_ffn_supported(ctx, d->ne, d->n_ff_exp, sh_ff_eff, d->n_used, bt, &why);
+  const bool em_ok = em_supported((int)d->ne, (int)d->n_ff_exp, sh_ff_eff, (int)d->n_expert, bt);
   uint32_t path = d->path;
-  if (path == 0) path = choose_moe_path(ctx, d->rows, d->n_used, d->n_expert, d->ne, d->n_ff_exp, sh_ff_eff, down_q4k);
+  if (path == 0) path = choose_moe_path(ctx, d->rows, d->n_used, d->n_expert, d->ne, d->n_ff_exp, sh_ff_eff, bt);
   // One CTA per (token, expert) pair, or one per expert with all its tokens: the second form reads and
   // unpacks an expert's blocks once however many rows of the call it serves, at the price of two more
   // (small) launches.
@@ -651,7 +655,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.status = ctx->status;
     dp.trace = ctx->trace;
     dp.gate_stride = (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne) * (d->fused_gate_up ? 2 : 1);
-    dp.up_stride = dp.gate_stride;
+    dp.up_stride = d->fused_gate_up ? dp.gate_stride : (size_t)d->n_ff_exp * row_bytes(d->up_dtype, d->ne);
     dp.down_stride = (size_t)d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
     dp.rows = d->rows;
     dp.ne = d->ne;
@@ -662,6 +666,9 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.ep_lo = d->ep_lo;
     dp.ep_n = d->ep_n_local;
     dp.down_q4k = down_q4k ? 1 : 0;
+    dp.gate_dt = d->gate_dtype;
+    dp.up_dt = d->up_dtype;
+    dp.down_dt = d->down_dtype;
     dp.down_scale = d->down_scale ? static_cast<const float*>(d->down_scale->ptr) : nullptr;
     dp.act_kind = (int)d->act;
     dp.weight_before = d->weight_before ? 1 : 0;
@@ -711,7 +718,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     c.sh_up = has_sh ? static_cast<const uint8_t*>(d->sh_up->ptr) : nullptr;
     c.sh_down = has_sh ? static_cast<const uint8_t*>(d->sh_down->ptr) : nullptr;
     c.gate_stride = (size_t)d->n_ff_exp * row_bytes(d->gate_dtype, d->ne) * (d->fused_gate_up ? 2 : 1);
-    c.up_stride = c.gate_stride;
+    c.up_stride = d->fused_gate_up ? c.gate_stride : (size_t)d->n_ff_exp * row_bytes(d->up_dtype, d->ne);
     c.down_stride = (size_t)d->ne * row_bytes(d->down_dtype, d->n_ff_exp);
     c.rows = (int)d->rows;
     c.n_used = (int)d->n_used;
@@ -725,6 +732,9 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     c.ep_n = d->ep_n_local;
     c.legacy = (path == 3) ? 1 : 0;
     c.down_q4k = down_q4k ? 1 : 0;
+    c.gate_dt = d->gate_dtype;
+    c.up_dt = d->up_dtype;
+    c.down_dt = d->down_dtype;
     c.act_kind = (int)d->act;
     c.clamp = d->swiglu_clamp;
     c.weight_before = d->weight_before ? 1 : 0;
@@ -740,7 +750,7 @@ int32_t infr_cuda_linear(infr_cuda_ctx* ctx, int32_t dtype, const infr_cuda_buf*
   if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
   if (!m || !in_f || !out_f) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: zero dimension");
   const size_t rb = row_bytes(dtype, in_f);
-  if (!rb) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32, Q4_K, Q6_K only)");
+  if (!rb) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32, Q4_K, Q5_K, Q6_K, Q8_0)");
   if (dtype != INFR_CUDA_DT_F32 && in_f % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: in_f must be a multiple of the 256-weight block");
   if (!fits(w, rb * out_f) || !fits(x, (size_t)m * in_f * 4) || !fits(y, (size_t)m * out_f * 4))
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: buffer missing or too small");
@@ -795,13 +805,14 @@ int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_row
   if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
   if (!n_local || !ne || !n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: zero dimension");
   if (n_local > 1024) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: more than 1024 local experts");
-  if (gate_dtype != INFR_CUDA_DT_Q4K || up_dtype != INFR_CUDA_DT_Q4K || (down_dtype != INFR_CUDA_DT_Q6K && down_dtype != INFR_CUDA_DT_Q4K))
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be gate/up Q4_K and down Q6_K or Q4_K");
+  if (!bank_dtype_ok(gate_dtype) || !bank_dtype_ok(up_dtype) || !bank_dtype_ok(down_dtype))
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be Q4_K, Q5_K, Q6_K or Q8_0");
   if (ne % 256 || n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: ne and n_ff_exp must be multiples of 256");
   if (!n_rows) return INFR_CUDA_OK;
-  const size_t gb = (size_t)n_local * n_ff_exp * row_bytes(gate_dtype, ne), db = (size_t)n_local * ne * row_bytes(down_dtype, n_ff_exp);
+  const size_t gb = (size_t)n_local * n_ff_exp * row_bytes(gate_dtype, ne), ub = (size_t)n_local * n_ff_exp * row_bytes(up_dtype, ne),
+               db = (size_t)n_local * ne * row_bytes(down_dtype, n_ff_exp);
   if (!fits(x_rows, (size_t)n_rows * ne * 4) || !fits(y_rows, (size_t)n_rows * ne * 4) || !fits(seg_off, (size_t)(n_local + 1) * 4) ||
-      !fits(gate_exps, gb) || !fits(up_exps, gb) || !fits(down_exps, db))
+      !fits(gate_exps, gb) || !fits(up_exps, ub) || !fits(down_exps, db))
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: buffer missing or too small");
   DeviceGuard g(ctx->device);
   const size_t gbytes = grouped_scratch_bytes((int)n_rows, 1, (int)n_local + 1, (int)ne, (int)n_ff_exp);
@@ -816,8 +827,11 @@ int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_row
   c.up = static_cast<const uint8_t*>(up_exps->ptr);
   c.down = static_cast<const uint8_t*>(down_exps->ptr);
   c.gate_stride = (size_t)n_ff_exp * row_bytes(gate_dtype, ne);
-  c.up_stride = c.gate_stride;
+  c.up_stride = (size_t)n_ff_exp * row_bytes(up_dtype, ne);
   c.down_stride = (size_t)ne * row_bytes(down_dtype, n_ff_exp);
+  c.gate_dt = gate_dtype;
+  c.up_dt = up_dtype;
+  c.down_dt = down_dtype;
   c.rows = (int)n_rows;
   c.n_used = 1;
   c.n_pairs = 1;

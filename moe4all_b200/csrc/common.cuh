@@ -76,20 +76,22 @@ int32_t ensure_scratch(infr_cuda_ctx* ctx, size_t bytes);
 // Raise a kernel's dynamic shared-memory limit once per (device, kernel) instead of on every launch.
 cudaError_t ensure_smem(const void* kernel, size_t bytes);
 
-inline size_t row_bytes(int32_t dtype, size_t n_elem) {
-  switch (dtype) {
-    case INFR_CUDA_DT_F32: return n_elem * 4;
-    case INFR_CUDA_DT_Q4K: return n_elem / QK * Q4K_BLOCK_BYTES;
-    case INFR_CUDA_DT_Q6K: return n_elem / QK * Q6K_BLOCK_BYTES;
-    default: return 0;
-  }
-}
-
 #ifdef __CUDACC__
 #define INFR_HD __host__ __device__
 #else
 #define INFR_HD
 #endif
+// Bytes of a row of n_elem weights (crates/infr-core/src/decode_spec.rs:315-335: elements and bytes per block).
+INFR_HD inline size_t row_bytes(int32_t dtype, size_t n_elem) {
+  switch (dtype) {
+    case INFR_CUDA_DT_F32: return n_elem * 4;
+    case INFR_CUDA_DT_Q4K: return n_elem / 256 * 144;
+    case INFR_CUDA_DT_Q5K: return n_elem / 256 * 176;
+    case INFR_CUDA_DT_Q6K: return n_elem / 256 * 210;
+    case INFR_CUDA_DT_Q8_0: return n_elem / 32 * 34;
+    default: return 0;
+  }
+}
 INFR_HD inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // ---------------------------------------------------------------------------------------------

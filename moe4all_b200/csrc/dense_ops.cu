@@ -1,8 +1,9 @@
 // The ops around Op::MoeFfn that the graph builder emits for a MoE layer
-// (crates/infr-llama/src/seam/runner.rs:7999-8176): Linear on F32 / Q4_K / Q6_K weights, GatedAct,
+// (crates/infr-llama/src/seam/runner.rs:7999-8176): Linear on F32 / Q4_K / Q5_K / Q6_K / Q8_0 weights, GatedAct,
 // MoeSharedExpertAdd, RmsNorm, Add.  CPU arms: crates/infr-cpu/src/lib.rs:1275-1328, 2973-3027,
 // 3336-3356, 1046-1069, 3055-3070.  These are the un-fused forms; the hot path folds the shared
 // expert into the MoE kernels instead (see decode_ffn.cu).
+#include "formats.cuh"
 #include "kernels.cuh"
 
 namespace infr {
@@ -102,6 +103,37 @@ __global__ void __launch_bounds__(256) k_linear(const unsigned char* __restrict_
     acc = warp_sum(acc);
     if (lane == 0) y[(size_t)r * out_f + o] = acc;
   }
+}
+
+// The same op on any block format through the code view of formats.cuh: one warp per (input row, output
+// feature), a lane per 16 weights: w . x = A * (sum code x - off * sum x) + B * sum x.
+__global__ void __launch_bounds__(256) k_linear_anyfmt(int dt, const unsigned char* __restrict__ w, const float* __restrict__ x,
+                                                       float* __restrict__ y, int in_f, int out_f, size_t rb) {
+  const int o = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (o >= out_f) return;
+  const float* xr = x + (size_t)blockIdx.y * in_f;
+  const unsigned char* wr = w + (size_t)o * rb;
+  float acc = 0.f;
+  for (int h = lane; h < in_f / 16; h += 32) {
+    uint32_t c[4];
+    float A, B;
+    int off;
+    fmt_codes16(dt, wr, h, c, A, B, off);
+    float f = 0.f, S = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(xr + 16 * h) + i);
+      f = fmaf((float)(c[i] & 0xFFu), v.x, f);
+      f = fmaf((float)((c[i] >> 8) & 0xFFu), v.y, f);
+      f = fmaf((float)((c[i] >> 16) & 0xFFu), v.z, f);
+      f = fmaf((float)(c[i] >> 24), v.w, f);
+      S += (v.x + v.y) + (v.z + v.w);
+    }
+    acc += fmaf(A, f - (float)off * S, B * S);
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) y[(size_t)blockIdx.y * out_f + o] = acc;
 }
 
 __global__ void k_gated_act(const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ dst, size_t n) {
@@ -204,7 +236,11 @@ int32_t launch_linear(infr_cuda_ctx* ctx, int32_t dtype, const uint8_t* w, const
     case INFR_CUDA_DT_F32: k_linear<INFR_CUDA_DT_F32><<<grid, block, 0, ctx->stream>>>(w, x, y, m, in_f, out_f, wb); break;
     case INFR_CUDA_DT_Q4K: k_linear<INFR_CUDA_DT_Q4K><<<grid, block, 0, ctx->stream>>>(w, x, y, m, in_f, out_f, wb); break;
     case INFR_CUDA_DT_Q6K: k_linear<INFR_CUDA_DT_Q6K><<<grid, block, 0, ctx->stream>>>(w, x, y, m, in_f, out_f, wb); break;
-    default: return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32, Q4_K, Q6_K only)");
+    case INFR_CUDA_DT_Q5K:
+    case INFR_CUDA_DT_Q8_0:
+      k_linear_anyfmt<<<grid, block, 0, ctx->stream>>>(dtype, w, x, y, in_f, out_f, row_bytes(dtype, in_f));
+      break;
+    default: return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32, Q4_K, Q5_K, Q6_K, Q8_0)");
   }
   ctx->launches += 1;
   return check_cuda(ctx, cudaGetLastError(), "k_linear launch");

@@ -249,7 +249,7 @@ static int32_t ep_check_shape(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* 
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "expert parallel: the first call of a shape cannot be recorded: run it once un-recorded first");
   const int W = ep->world;
   int32_t mine[8] = {(int32_t)d->rows, (int32_t)d->ne, (int32_t)d->n_expert, (int32_t)d->n_used, (int32_t)d->n_ff_exp,
-                     (int32_t)(d->sh_gate ? d->sh_ff : 0u), (int32_t)d->gate_dtype * 256 + (int32_t)d->down_dtype, W};
+                     (int32_t)(d->sh_gate ? d->sh_ff : 0u), (int32_t)d->gate_dtype * 65536 + (int32_t)d->up_dtype * 256 + (int32_t)d->down_dtype, W};
   cudaError_t e = cudaMemcpyAsync(ep->shape_dev + (size_t)ep->rank * 8, mine, sizeof mine, cudaMemcpyHostToDevice, ctx->stream);
   if (e != cudaSuccess) return check_cuda(ctx, e, "expert parallel: shape upload");
   NCCL_TRY(ep->api->AllGather(ep->shape_dev + (size_t)ep->rank * 8, ep->shape_dev, 8, ncclInt32, ep->comm, ctx->stream), "shape exchange");
@@ -309,7 +309,7 @@ int32_t ep_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   // scratch of its own, next to the exchange buffers.
   // the kernels are chosen for what the band serves - about a W-th of the T rows' pairs over n_expert / W
   // experts, i.e. R rows over El experts - not for all T rows; the shared expert goes the same way
-  uint32_t band_path = d->path ? d->path : choose_moe_path(ctx, R, k, El, ne, d->n_ff_exp, 0, d->down_dtype == INFR_CUDA_DT_Q4K);
+  uint32_t band_path = d->path ? d->path : choose_moe_path(ctx, R, k, El, ne, d->n_ff_exp, 0, BankTypes{d->gate_dtype, d->up_dtype, d->down_dtype});
   if (band_path == 1 && T > 4096) band_path = 2;  // the small-m kernels' grids and scratch grow with all T rows
   const bool sh_small = has_sh && band_path == 1;
   infr_cuda_moe_ffn_desc shd = *d;  // the nested small-m call (filled in below)
@@ -377,7 +377,7 @@ int32_t ep_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
       c.up = static_cast<const uint8_t*>(d->sh_up->ptr);
       c.down = static_cast<const uint8_t*>(d->sh_down->ptr);
       c.gate_stride = (size_t)d->sh_ff * row_bytes(d->gate_dtype, ne);
-      c.up_stride = c.gate_stride;
+      c.up_stride = (size_t)d->sh_ff * row_bytes(d->up_dtype, ne);
       c.down_stride = (size_t)ne * row_bytes(d->down_dtype, d->sh_ff);
       c.rows = (int)R;
       c.n_used = 1;
@@ -387,6 +387,9 @@ int32_t ep_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
       c.n_expert = 1;
       c.rows_bound = (int)R;
       c.down_q4k = d->down_dtype == INFR_CUDA_DT_Q4K ? 1 : 0;
+      c.gate_dt = d->gate_dtype;
+      c.up_dt = d->up_dtype;
+      c.down_dt = d->down_dtype;
       c.act_kind = (int)d->act;
       rc = launch_grouped_ffn(ctx, c);
     }

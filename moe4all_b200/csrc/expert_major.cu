@@ -660,8 +660,8 @@ size_t em_scratch_bytes(int rows, int n_used, int ne, int nff, int sh_ff) {
   return b;
 }
 
-bool em_supported(int ne, int nff, int sh_ff, int n_expert, bool down_q4k) {
-  if (down_q4k || ne % 256 || nff % 256 || sh_ff % 256 || n_expert > 1024) return false;
+bool em_supported(int ne, int nff, int sh_ff, int n_expert, BankTypes bt) {
+  if (!bt.tuned() || bt.down_q4k() || ne % 256 || nff % 256 || sh_ff % 256 || n_expert > 1024) return false;
   int apitch;
   size_t slab_pitch, smem;
   return down_rows(ne, std::max(nff, sh_ff), &apitch, &slab_pitch, &smem) != 0;

@@ -1,0 +1,103 @@
+// One view of the GGUF block formats the expert banks may hold beyond the Q4_K / Q6_K pair the tuned
+// kernels are written for: 16 consecutive weights of a row as sixteen unsigned 8-bit codes and the
+// affine map of their scale group,
+//
+//     w = A * (code - off) + B .
+//
+// It is the factored form of the reference's host decoder (crates/infr-gguf/src/dequant.rs:119-400:
+// `codes`, per-16 `(sc, m)`, per-block `(d, dmin)`; values `(d*sc)*code + (dmin*m)`, :35-51):
+//
+//   Q4_K  144 B / 256   code = 4-bit nibble,            A = d*sc6,  B = -dmin*m6,  off = 0    (:315-335)
+//   Q5_K  176 B / 256   code = nibble | high bit << 4,  A = d*sc6,  B = -dmin*m6,  off = 0    (:337-362)
+//   Q6_K  210 B / 256   code = 6 bits (ql | qh << 4),   A = d*sc8,  B = 0,         off = 32   (:365-400)
+//   Q8_0   34 B / 32    code = q + 128,                 A = d,      B = 0,         off = 128  (:214-223)
+//
+// The generic small-m kernels (anyfmt_ffn.cu) feed the codes to integer dot products against the
+// fixed-point activations; the generic grouped GEMM (grouped_ffn.cu) turns them into f16 operands.
+#pragma once
+#include "common.cuh"
+
+namespace infr {
+
+constexpr uint32_t Q5K_BLOCK_BYTES = 176;  // 256 weights: f16 d, f16 dmin, 12 B scales, 32 B high bits, 128 B nibbles
+constexpr uint32_t Q80_BLOCK_BYTES = 34;   // 32 weights: f16 d, 32 int8
+
+// The formats an expert bank may have.
+inline bool bank_dtype_ok(int32_t dt) {
+  return dt == INFR_CUDA_DT_Q4K || dt == INFR_CUDA_DT_Q5K || dt == INFR_CUDA_DT_Q6K || dt == INFR_CUDA_DT_Q8_0;
+}
+// The combination the tuned kernels (per-pair, expert-major, tcgen05) are written for.
+inline bool bank_dtypes_tuned(int32_t gate, int32_t up, int32_t down) {
+  return gate == INFR_CUDA_DT_Q4K && up == INFR_CUDA_DT_Q4K && (down == INFR_CUDA_DT_Q6K || down == INFR_CUDA_DT_Q4K);
+}
+
+#ifdef __CUDACC__
+
+// Four bytes at a 2-byte-aligned address: one word load when the address is word aligned, else two
+// 16-bit loads, so nothing outside the four bytes is touched.
+__device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t* p) {
+  if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) return __ldg(reinterpret_cast<const uint32_t*>(p));
+  const uint32_t lo = __ldg(reinterpret_cast<const unsigned short*>(p));
+  const uint32_t hi = __ldg(reinterpret_cast<const unsigned short*>(p + 2));
+  return lo | (hi << 16);
+}
+
+// Codes and affine map of weights 16h .. 16h+15 of the row starting at `row` (global memory).
+__device__ __forceinline__ void fmt_codes16(int dt, const uint8_t* __restrict__ row, int h, uint32_t (&c)[4], float& A, float& B,
+                                            int& off) {
+  if (dt == INFR_CUDA_DT_Q4K || dt == INFR_CUDA_DT_Q5K) {
+    const bool q5 = dt == INFR_CUDA_DT_Q5K;
+    const uint8_t* blk = row + (size_t)(h >> 4) * (q5 ? Q5K_BLOCK_BYTES : Q4K_BLOCK_BYTES);
+    const int e = (h & 15) * 16, j = e >> 6, sub = (e >> 5) & 1, l0 = e & 31;
+    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(blk + (q5 ? 48 : 16) + 32 * j + l0));
+    const int sh = 4 * sub;
+    c[0] = (q.x >> sh) & 0x0F0F0F0Fu;
+    c[1] = (q.y >> sh) & 0x0F0F0F0Fu;
+    c[2] = (q.z >> sh) & 0x0F0F0F0Fu;
+    c[3] = (q.w >> sh) & 0x0F0F0F0Fu;
+    if (q5) {
+      // bit 2j + sub of qh[l] is the fifth code bit of element 64j + 32 sub + l
+      const uint4 qh = __ldg(reinterpret_cast<const uint4*>(blk + 16 + l0));
+      const int sb = 2 * j + sub;
+      c[0] |= ((qh.x >> sb) & 0x01010101u) << 4;
+      c[1] |= ((qh.y >> sb) & 0x01010101u) << 4;
+      c[2] |= ((qh.z >> sb) & 0x01010101u) << 4;
+      c[3] |= ((qh.w >> sb) & 0x01010101u) << 4;
+    }
+    uint32_t scp, mp;
+    q4k_scale_min_pair(hdr.y, hdr.z, hdr.w, j, scp, mp);
+    A = f16_bits_to_f32(hdr.x) * (float)((scp >> (8 * sub)) & 0xFFu);
+    B = -(f16_bits_to_f32(hdr.x >> 16) * (float)((mp >> (8 * sub)) & 0xFFu));
+    off = 0;
+  } else if (dt == INFR_CUDA_DT_Q6K) {
+    // element 128 hh + 32 qd + l: low nibble source ql[64 hh + 32 (qd & 1) + l] (high nibble for qd >= 2),
+    // bits 2 qd .. 2 qd + 1 of qh[32 hh + l]; one int8 scale per 16 elements.  Blocks are 2-byte aligned.
+    const uint8_t* blk = row + (size_t)(h >> 4) * Q6K_BLOCK_BYTES;
+    const int e = (h & 15) * 16, hh = e >> 7, qd = (e >> 5) & 3, l0 = e & 31;
+    const uint8_t* ql = blk + 64 * hh + 32 * (qd & 1) + l0;
+    const uint8_t* qh = blk + 128 + 32 * hh + l0;
+    const int nsh = 4 * (qd >> 1), hsh = 2 * qd;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t lo = ldg_u32_a2(ql + 4 * i), hi = ldg_u32_a2(qh + 4 * i);
+      c[i] = ((lo >> nsh) & 0x0F0F0F0Fu) | (((hi >> hsh) & 0x03030303u) << 4);
+    }
+    const float d = f16_bits_to_f32(__ldg(reinterpret_cast<const unsigned short*>(blk + 208)));
+    A = d * (float)(int)(signed char)__ldg(blk + 192 + 8 * hh + 2 * qd + (l0 >> 4));
+    B = 0.f;
+    off = 32;
+  } else {  // Q8_0
+    const uint8_t* blk = row + (size_t)(h >> 1) * Q80_BLOCK_BYTES;
+    const uint8_t* q = blk + 2 + 16 * (h & 1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[i] = ldg_u32_a2(q + 4 * i) ^ 0x80808080u;
+    A = f16_bits_to_f32(__ldg(reinterpret_cast<const unsigned short*>(blk)));
+    B = 0.f;
+    off = 128;
+  }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace infr

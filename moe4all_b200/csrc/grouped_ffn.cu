@@ -26,6 +26,7 @@
 #include <algorithm>
 #include <cstdlib>
 
+#include "formats.cuh"
 #include "kernels.cuh"
 
 namespace infr {
@@ -536,6 +537,113 @@ __global__ void __launch_bounds__(GG_THREADS) k_grouped_down(GroupedParams p) {
   }
 }
 
+// ---- any bank format (formats.cuh): the same 64 x 64 tiles, weights unpacked through the code view ----
+
+// Sixteen codes -> sixteen f16 weights (code - off) * s + m, every four in the order 0,2,1,3.
+__device__ __forceinline__ void codes16_to_h(const uint32_t (&c)[4], float A, float B, int off, uint4& o0, uint4& o1) {
+  const __half2 s = __float2half2_rn(A * W_PRESCALE), m = __float2half2_rn(B * W_PRESCALE);
+  const __half2 koff = __float2half2_rn(1024.f + (float)off);  // 1024 + code is exact in f16 for 8-bit codes
+  uint32_t o[8];
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const __half2 a = __hsub2(u32_as_h2((c[w] & 0x00FF00FFu) | 0x64006400u), koff);
+    const __half2 b = __hsub2(u32_as_h2(((c[w] >> 8) & 0x00FF00FFu) | 0x64006400u), koff);
+    o[2 * w] = h2_as_u32(__hfma2(a, s, m));
+    o[2 * w + 1] = h2_as_u32(__hfma2(b, s, m));
+  }
+  o0 = make_uint4(o[0], o[1], o[2], o[3]);
+  o1 = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// NR = 2: gate and up rows of 64 features with the gated activation as epilogue (act, f16).
+// NR = 1: 64 rows of the down matrix, raw outputs y (f32).
+template <int NR>
+__global__ void __launch_bounds__(GG_THREADS) k_anyfmt_grouped(GroupedParams p) {
+  __shared__ __align__(16) __half As[2 * TM * PITCH];
+  __shared__ __align__(16) __half Bs[TN * PITCH];
+  const int tile = blockIdx.y;
+  if (tile >= *p.n_tiles) return;
+  const int e = p.tile_expert[tile], row0 = p.tile_row0[tile], rows_valid = p.tile_rows[tile];
+  const int f0 = blockIdx.x * TM;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warp_m = warp & 3, warp_n = warp >> 2;
+  const bool shared_seg = e >= p.n_expert;
+  const int K = NR == 2 ? p.ne : p.nff;
+  const int dt0 = NR == 2 ? p.gate_dt : p.down_dt, dt1 = p.up_dt;
+  const size_t rb0 = row_bytes(dt0, K), rb1 = row_bytes(dt1, K);
+  const uint8_t* base0 = NR == 2 ? (shared_seg ? p.sh_gate : p.gate + (size_t)e * p.gate_stride)
+                                 : (shared_seg ? p.sh_down : p.down + (size_t)e * p.down_stride);
+  const uint8_t* base1 = shared_seg ? p.sh_up : p.up + (size_t)e * p.up_stride;
+  const int urow = tid >> 2, uq = tid & 3;  // unpack role: (weight row, 16 of the step's 64 elements)
+  const uint8_t* wrow0 = base0 + (size_t)(f0 + urow) * rb0;
+  const uint8_t* wrow1 = base1 + (size_t)(f0 + urow) * rb1;
+  const __half* tok = (NR == 2 ? p.xg : p.act) + (size_t)row0 * K;
+
+  float acc[NR][4][4];
+#pragma unroll
+  for (int r = 0; r < NR; ++r)
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[r][nt][i] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += TK) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      uint32_t c[4];
+      float A, B;
+      int off;
+      fmt_codes16(r == 0 ? dt0 : dt1, r == 0 ? wrow0 : wrow1, (k0 >> 4) + uq, c, A, B, off);
+      uint4 o0, o1;
+      codes16_to_h(c, A, B, off, o0, o1);
+      __half* arow = As + (size_t)r * TM * PITCH + urow * PITCH + 16 * uq;
+      *reinterpret_cast<uint4*>(arow) = o0;
+      *reinterpret_cast<uint4*>(arow + 8) = o1;
+    }
+    stage_tokens(tok, K, k0, rows_valid, Bs, tid);
+    __syncthreads();
+    mma_step<NR>(As, Bs, warp_m, warp_n, lane, acc);
+    __syncthreads();
+  }
+
+  const int g = lane >> 2, t = lane & 3;
+  if (NR == 2) {
+    __half* T = As;  // [TN][PITCH] token-major f16 rows
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int f = warp_m * 16 + g + (i >> 1) * 8;
+        const int n = warp_n * 32 + nt * 8 + 2 * t + (i & 1);
+        const float gv = acc[0][nt][i] * W_POSTSCALE, uv = acc[NR - 1][nt][i] * W_POSTSCALE;
+        const float a = gated_act(p.act_kind, e < p.n_expert ? p.clamp : 0.f, gv, uv);
+        T[n * PITCH + kperm(f)] = __float2half_rn(fminf(fmaxf(a, -65504.f), 65504.f));
+      }
+    __syncthreads();
+    for (int i = tid; i < TN * 8; i += GG_THREADS) {
+      const int n = i >> 3, c = i & 7;
+      if (n < rows_valid)
+        *reinterpret_cast<uint4*>(p.act + (size_t)(row0 + n) * p.nff + f0 + c * 8) = *reinterpret_cast<const uint4*>(T + n * PITCH + c * 8);
+    }
+  } else {
+    float* T = reinterpret_cast<float*>(As);  // [TN][TM + 4] floats
+    constexpr int TP = TM + 4;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int f = warp_m * 16 + g + (i >> 1) * 8;
+        const int n = warp_n * 32 + nt * 8 + 2 * t + (i & 1);
+        T[n * TP + f] = acc[0][nt][i] * W_POSTSCALE;
+      }
+    __syncthreads();
+    for (int i = tid; i < TN * (TM / 4); i += GG_THREADS) {
+      const int n = i / (TM / 4), c = i % (TM / 4);
+      if (n < rows_valid)
+        *reinterpret_cast<float4*>(p.y + (size_t)(row0 + n) * p.ne + f0 + c * 4) = *reinterpret_cast<const float4*>(T + n * TP + c * 4);
+    }
+  }
+}
+
 // ---- un-permute + combine -----------------------------------------------------------------------------
 
 // dst[t, :] = sum over ranks (in rank order) of w * y[pos(t, rank), :], then the shared expert
@@ -657,8 +765,9 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   const int n_seg_routed = c.n_expert;
   const int n_seg = c.n_expert + (c.shared_rows > 0 ? 1 : 0);
   const int rows_total = c.rows_bound;  // upper bound on sorted rows + shared rows
-  const bool use_umma = !c.legacy && umma_grouped_supported(c.ne, c.nff);
-  if (c.down_q4k && !use_umma)
+  const bool tuned = BankTypes{c.gate_dt, c.up_dt, c.down_dt}.tuned();
+  const bool use_umma = tuned && !c.legacy && umma_grouped_supported(c.ne, c.nff);
+  if (tuned && c.down_q4k && !use_umma)
     return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "grouped GEMM: Q4_K down banks need the tcgen05 tiles (ne, n_ff_exp multiples of 256, not path 3)");
   const int tn = use_umma ? umma_tile_rows() : TN;
   const int max_tiles = rows_total / tn + n_seg + 1;
@@ -738,6 +847,9 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   p.nff = c.nff;
   p.n_expert = c.n_expert;
   p.down_q4k = c.down_q4k;
+  p.gate_dt = c.gate_dt;
+  p.up_dt = c.up_dt;
+  p.down_dt = c.down_dt;
   p.act_kind = c.act_kind;
   p.gu_rows = (int)(c.gate_stride / ((size_t)c.ne / 256 * Q4K_BLOCK_BYTES));
   p.clamp = c.clamp;
@@ -747,6 +859,12 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   if (use_umma) {
     const int32_t rc = launch_umma_grouped(ctx, p, max_tiles);
     if (rc) return rc;
+  } else if (!tuned) {
+    // banks in another format mix: the same tiles, weights unpacked through the generic code view
+    if (c.ne % 256 || c.nff % 256) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "grouped GEMM: ne and n_ff_exp must be multiples of 256 for these bank formats");
+    k_anyfmt_grouped<2><<<dim3(c.nff / TM, max_tiles), GG_THREADS, 0, st>>>(p);
+    k_anyfmt_grouped<1><<<dim3(c.ne / TM, max_tiles), GG_THREADS, 0, st>>>(p);
+    ctx->launches += 2;
   } else {
     k_grouped_gateup<<<dim3(c.nff / TM, max_tiles), GG_THREADS, 0, st>>>(p);
     k_grouped_down<<<dim3(c.ne / TM, max_tiles), GG_THREADS, 0, st>>>(p);

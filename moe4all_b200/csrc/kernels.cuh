@@ -37,6 +37,15 @@ struct RouteParams {
   int gating, norm_w, n_groups, n_groups_used;
 };
 
+// Formats of a call's expert banks (INFR_CUDA_DT_*); the shared expert's tensors follow the same three.
+struct BankTypes {
+  int32_t gate, up, down;
+  bool tuned() const {  // the combination the per-pair, expert-major and tcgen05 kernels are written for
+    return gate == INFR_CUDA_DT_Q4K && up == INFR_CUDA_DT_Q4K && (down == INFR_CUDA_DT_Q6K || down == INFR_CUDA_DT_Q4K);
+  }
+  bool down_q4k() const { return down == INFR_CUDA_DT_Q4K; }
+};
+
 struct DecodeParams {
   const float* x;        // [rows, ne]
   const int32_t* ids;    // [rows, n_used]
@@ -55,6 +64,7 @@ struct DecodeParams {
   int rows, ne, n_used, nff, sh_ff, n_expert;
   uint32_t ep_lo, ep_n;  // band (ep_n == 0: off)
   int down_q4k;          // the down banks (routed and shared) are Q4_K instead of Q6_K
+  int gate_dt, up_dt, down_dt;  // INFR_CUDA_DT_* of the banks (the generic-format kernels read these)
   const float* down_scale;  // [n_expert] scale on a routed expert's down output, or null
   int act_kind;          // INFR_CUDA_ACT_*
   int weight_before;     // routing weight on gate and up before the activation, none on the output
@@ -98,6 +108,7 @@ struct GroupedParams {
   int trace_tile;             // tile whose first CTA writes them
   int ne, nff, n_expert;
   int down_q4k;               // the down banks are Q4_K instead of Q6_K (tcgen05 kernels only)
+  int gate_dt, up_dt, down_dt;  // INFR_CUDA_DT_* of the banks (the generic-format tiles read these)
   int act_kind;               // INFR_CUDA_ACT_*
   int gu_rows;                // rows of one expert in the gate bank: nff, or 2 nff where gate and up share a bank
   float clamp;                // > 0: routed tiles clamp gate (from above) and up (both sides) first
@@ -122,6 +133,7 @@ struct GroupedCall {
   uint32_t ep_lo, ep_n;
   int legacy;              // 1: use the mma.sync tiles even where the tcgen05 kernels apply
   int down_q4k;            // the down banks are Q4_K instead of Q6_K
+  int gate_dt, up_dt, down_dt;  // INFR_CUDA_DT_* of the banks
   int act_kind;            // INFR_CUDA_ACT_*
   float clamp;             // Op::MoeFfn::swiglu_clamp, 0 = none
   int weight_before;       // routing weight on the expert's input rows, none on its output
@@ -143,7 +155,7 @@ int32_t validate_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, ui
 // Path choice for a call (api.cu): 1 = small-m kernels, 2 = grouped GEMMs; and, inside path 1, whether the
 // expert-major kernels are ahead of the per-pair ones.
 uint32_t choose_moe_path(const infr_cuda_ctx* ctx, uint32_t rows, uint32_t n_used, uint32_t n_expert, uint32_t ne, uint32_t nff,
-                         uint32_t sh_ff, bool down_q4k);
+                         uint32_t sh_ff, BankTypes bt);
 bool em_preferred(uint32_t rows, uint32_t n_used, uint32_t n_expert, uint32_t ne, uint32_t nff);
 
 size_t small_path_scratch_need(const infr_cuda_moe_ffn_desc* d);
@@ -161,11 +173,15 @@ int32_t launch_route(infr_cuda_ctx* ctx, const RouteParams& p, bool pdl);
 int route_small_group(const infr_cuda_ctx* ctx, int rows, int ne, int n_expert);
 int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages);
 // The expert-major form of the same stages (2: bucket + gate/up, 4: down + combine); `scratch` holds em_scratch_bytes(...).
-bool em_supported(int ne, int nff, int sh_ff, int n_expert, bool down_q4k);
+bool em_supported(int ne, int nff, int sh_ff, int n_expert, BankTypes bt);
 size_t em_scratch_bytes(int rows, int n_used, int ne, int nff, int sh_ff);
 int32_t launch_em_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, void* scratch, uint32_t stages);
 // Whether the small-m kernels cover this shape (dims, shared-memory budget).
-bool decode_ffn_supported(const infr_cuda_ctx* ctx, int ne, int nff, int sh_ff, int n_used, bool down_q4k, std::string* why);
+bool decode_ffn_supported(const infr_cuda_ctx* ctx, int ne, int nff, int sh_ff, int n_used, BankTypes bt, std::string* why);
+// Small-m kernels for banks in any mix of Q4_K / Q5_K / Q6_K / Q8_0 (anyfmt_ffn.cu): the tuned kernels'
+// arithmetic with the blocks read straight from global memory.
+bool anyfmt_decode_supported(int ne, int nff, int sh_ff, int n_used, std::string* why);
+int32_t launch_anyfmt_decode(infr_cuda_ctx* ctx, const DecodeParams& p, uint32_t stages);
 
 // y[m, out_f] = x[m, in_f] · Wᵀ for W of dtype F32 / Q4_K / Q6_K.
 int32_t launch_linear(infr_cuda_ctx* ctx, int32_t dtype, const uint8_t* w, const float* x, float* y, int m, int in_f,

@@ -23,30 +23,52 @@ def q6k_bank(n_blocks: int, gen, device) -> torch.Tensor:
     return t.reshape(-1)
 
 
+# GGUF type number -> (elements per block, bytes per block, offsets of the f16 scale slots, scale factor)
+BLOCKS = {12: (256, 144, (0, 2), 1.0), 13: (256, 176, (0, 2), 1.0), 14: (256, 210, (208,), 1.0), 8: (32, 34, (0,), 2.0)}
+
+
+def bank(dtype: int, n_elem: int, gen, device) -> torch.Tensor:
+    """Random blocks of GGUF type `dtype` (12 Q4_K, 13 Q5_K, 14 Q6_K, 8 Q8_0) holding n_elem weights."""
+    if dtype == 12:
+        return q4k_bank(n_elem // 256, gen, device)
+    if dtype == 14:
+        return q6k_bank(n_elem // 256, gen, device)
+    elems, nbytes, slots, k = BLOCKS[dtype]
+    n = n_elem // elems
+    t = torch.randint(0, 256, (n, nbytes), dtype=torch.uint8, generator=gen, device=device)
+    for o in slots:
+        t[:, o:o + 2] = ((torch.rand(n, generator=gen, device=device) * 9e-4 + 1e-4) * k).to(torch.float16).view(torch.uint8).reshape(n, 2)
+    return t.reshape(-1)
+
+
 class DeviceLayer:
     """One MoE layer's tensors as torch CUDA tensors plus Buffer handles on them."""
 
     def __init__(self, be, seed, ne, n_expert, n_ff, sh_ff=0, gated_shared=True, device="cuda:0", router_std=0.02,
-                 band=None):
+                 band=None, dtypes=(12, 12, 14)):
         """band = (lo, n_local): keep only that slice of the expert banks (an expert-parallel rank);
-        the bytes equal the same slice of the un-banded layer with the same seed."""
+        the bytes equal the same slice of the un-banded layer with the same seed.
+        dtypes = GGUF type numbers of the gate, up and down banks."""
         gen = torch.Generator(device=device)
         gen.manual_seed(seed)
         self.ne, self.n_expert, self.n_ff, self.sh_ff = ne, n_expert, n_ff, sh_ff
         self.t = {}
         self.t["router"] = torch.randn(n_expert, ne, generator=gen, device=device) * router_std
-        self.t["gate"] = q4k_bank(n_expert * n_ff * ne // 256, gen, device)
-        self.t["up"] = q4k_bank(n_expert * n_ff * ne // 256, gen, device)
-        self.t["down"] = q6k_bank(n_expert * ne * n_ff // 256, gen, device)
+        self.dtypes = tuple(dtypes)
+        gd, ud, dd = self.dtypes
+        self.t["gate"] = bank(gd, n_expert * n_ff * ne, gen, device)
+        self.t["up"] = bank(ud, n_expert * n_ff * ne, gen, device)
+        self.t["down"] = bank(dd, n_expert * ne * n_ff, gen, device)
         if sh_ff:
-            self.t["sh_gate"] = q4k_bank(sh_ff * ne // 256, gen, device)
-            self.t["sh_up"] = q4k_bank(sh_ff * ne // 256, gen, device)
-            self.t["sh_down"] = q6k_bank(ne * sh_ff // 256, gen, device)
+            self.t["sh_gate"] = bank(gd, sh_ff * ne, gen, device)
+            self.t["sh_up"] = bank(ud, sh_ff * ne, gen, device)
+            self.t["sh_down"] = bank(dd, ne * sh_ff, gen, device)
             if gated_shared:
                 self.t["sh_gate_inp"] = torch.randn(ne, generator=gen, device=device) * router_std
         if band is not None:
             lo, n_local = band
-            for k, per in (("gate", n_ff * ne // 256 * 144), ("up", n_ff * ne // 256 * 144), ("down", ne * n_ff // 256 * 210)):
+            per_elem = lambda dt: BLOCKS[dt][1] / BLOCKS[dt][0]
+            for k, per in (("gate", int(n_ff * ne * per_elem(gd))), ("up", int(n_ff * ne * per_elem(ud))), ("down", int(ne * n_ff * per_elem(dd)))):
                 self.t[k] = self.t[k][lo * per:(lo + n_local) * per].clone()
         # 16 spare bytes after each bank: block decoders may read a word pair at the very end
         for k in list(self.t):
@@ -64,6 +86,7 @@ class DeviceLayer:
         get = lambda k: self.t[k][:-16].cpu().numpy() if k in self.t else None
         L.router = get("router").view(np.float32).reshape(self.n_expert, self.ne)
         L.gate, L.up, L.down = get("gate"), get("up"), get("down")
+        L.gate_dtype, L.up_dtype, L.down_dtype = self.dtypes
         L.sh_gate, L.sh_up, L.sh_down = get("sh_gate"), get("sh_up"), get("sh_down")
         gi = get("sh_gate_inp")
         L.sh_gate_inp = gi.view(np.float32) if gi is not None else None

@@ -1,6 +1,6 @@
 """Seeded synthetic inputs in the shapes and value distributions of the benchmark configs.
 
-Block generators write valid GGUF Q4_K / Q6_K super-blocks: every payload bit pattern decodes to
+Block generators write valid GGUF Q4_K / Q5_K / Q6_K / Q8_0 blocks: every payload bit pattern decodes to
 a finite value, only the f16 scale slots need sane magnitudes.  Two families:
   * `random_q4k` / `random_q6k`: random payload, f16 d (and dmin) drawn from U[1e-4, 1e-3]
     (the benchmark configs);
@@ -12,6 +12,9 @@ from __future__ import annotations
 import numpy as np
 
 Q4K_BYTES, Q6K_BYTES, QK = 144, 210, 256
+Q5K_BYTES, Q80_BYTES = 176, 34
+# GGUF type number -> (elements per block, bytes per block, offsets of the f16 scale slots)
+BLOCKS = {12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,)), 8: (32, 34, (0,))}
 
 
 def _f16_bytes(vals: np.ndarray) -> np.ndarray:
@@ -33,6 +36,17 @@ def random_q6k(rng: np.random.Generator, n_blocks: int, lo: float = 1e-4, hi: fl
     return blk
 
 
+def random_blocks(rng: np.random.Generator, dtype: int, n_elem: int, lo: float = 1e-4, hi: float = 1e-3) -> np.ndarray:
+    """[n_blocks, block bytes] u8 of GGUF type `dtype` (12 Q4_K, 13 Q5_K, 14 Q6_K, 8 Q8_0): random payload,
+    every f16 scale slot ~ U[lo, hi]."""
+    elems, nbytes, slots = BLOCKS[dtype]
+    n_blocks = n_elem // elems
+    blk = rng.integers(0, 256, size=(n_blocks, nbytes), dtype=np.uint8)
+    for o in slots:
+        blk[:, o:o + 2] = _f16_bytes(rng.uniform(lo, hi, n_blocks))
+    return blk
+
+
 def lcg_bytes(seed: int, n: int) -> np.ndarray:
     """crates/infr-testkit/src/lib.rs:49-56: seed = seed*1664525 + 1013904223 (mod 2^32); byte = seed >> 16."""
     out = np.empty(n, dtype=np.uint8)
@@ -50,7 +64,18 @@ def gen_f32(n: int, salt: int) -> np.ndarray:
 
 
 def testkit_weight(dtype_name: str, n_elem: int, seed: int) -> np.ndarray:
-    """crates/infr-testkit/src/lib.rs:106-123 for Q4_K (d 0.05, dmin 0.10) and Q6_K (d 0.03)."""
+    """crates/infr-testkit/src/lib.rs:74-123 for Q4_K and Q5_K (d 0.05, dmin 0.10), Q6_K (d 0.03) and
+    Q8_0 (d 0.01)."""
+    if dtype_name in ("Q5K", "Q8_0"):
+        elems, nbytes, slots = BLOCKS[13 if dtype_name == "Q5K" else 8]
+        assert n_elem % elems == 0
+        nblk = n_elem // elems
+        out = np.empty((nblk, nbytes), np.uint8)
+        for b in range(nblk):
+            out[b] = lcg_bytes(seed ^ b, nbytes)
+        for o, v in zip(slots, (0.05, 0.10) if dtype_name == "Q5K" else (0.01,)):
+            out[:, o:o + 2] = _f16_bytes(np.full(nblk, v))
+        return out
     assert n_elem % QK == 0
     nblk = n_elem // QK
     if dtype_name == "Q4K":
@@ -77,16 +102,32 @@ class LayerWeights:
         self.router = self.gate = self.up = self.down = None
         self.sh_gate = self.sh_up = self.sh_down = self.sh_gate_inp = None
         self.bias = None
+        self.gate_dtype = self.up_dtype = 12
         self.down_dtype = 14
 
 
 def make_layer(seed: int, ne: int, n_expert: int, n_ff: int, sh_ff: int = 0, gated_shared: bool = True,
-               router_std: float = 0.02, bias_std: float = 0.0, down_q4k: bool = False) -> LayerWeights:
+               router_std: float = 0.02, bias_std: float = 0.0, down_q4k: bool = False, dtypes=None) -> LayerWeights:
     """One layer in the benchmark configs' distributions: router f32 N(0, 0.02); gate/up Q4_K and
-    down Q6_K with random payload and U[1e-4, 1e-3] scales; optional shared expert."""
+    down Q6_K with random payload and U[1e-4, 1e-3] scales; optional shared expert.
+    dtypes = (gate, up, down) GGUF type numbers for another mix of bank formats."""
     rng = np.random.default_rng(seed)
     L = LayerWeights(ne, n_expert, n_ff, sh_ff, gated_shared)
     L.router = rng.normal(0.0, router_std, size=(n_expert, ne)).astype(np.float32)
+    if dtypes is not None:
+        L.gate_dtype, L.up_dtype, L.down_dtype = dtypes
+
+        def bank(dt, n_elem):
+            k = 2.0 if dt == 8 else 1.0
+            return random_blocks(rng, dt, n_elem, 1e-4 * k, 1e-3 * k).reshape(-1)
+        L.gate, L.up, L.down = bank(dtypes[0], n_expert * n_ff * ne), bank(dtypes[1], n_expert * n_ff * ne), bank(dtypes[2], n_expert * ne * n_ff)
+        if sh_ff:
+            L.sh_gate, L.sh_up, L.sh_down = bank(dtypes[0], sh_ff * ne), bank(dtypes[1], sh_ff * ne), bank(dtypes[2], ne * sh_ff)
+            if gated_shared:
+                L.sh_gate_inp = rng.normal(0.0, router_std, size=ne).astype(np.float32)
+        if bias_std > 0:
+            L.bias = rng.normal(0.0, bias_std, size=n_expert).astype(np.float32)
+        return L
     L.gate = random_q4k(rng, n_expert * n_ff * ne // QK).reshape(-1)
     L.up = random_q4k(rng, n_expert * n_ff * ne // QK).reshape(-1)
     L.down_dtype = 12 if down_q4k else 14  # GGUF type numbers: Q4_K, Q6_K (a Q4_K_M file mixes both over its layers)

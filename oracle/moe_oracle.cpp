@@ -39,7 +39,7 @@
 namespace {
 
 // dtype ids follow the public GGUF/ggml numbering.
-enum : int { DT_F32 = 0, DT_Q4K = 12, DT_Q6K = 14 };
+enum : int { DT_F32 = 0, DT_Q8_0 = 8, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14 };
 
 // IEEE binary16 → binary32, exact (what `half::f16::to_f32` does; dequant.rs:72-74).
 inline float f16_to_f32(uint16_t h) {
@@ -135,10 +135,53 @@ void dequant_q6k_block(const uint8_t* blk, float* out) {
   }
 }
 
+// One Q5_K super-block (176 B -> 256 f32).  Factored form dequant.rs:337-362: Q4_K's scales and
+// mins, nibbles at byte 48, and bit 2j (low nibble) / 2j+1 (high nibble) of qh[l] (byte 16 + l) as
+// the fifth code bit; expansion dequant.rs:35-51 as for Q4_K.
+void dequant_q5k_block(const uint8_t* blk, float* out) {
+  const float d = f16_to_f32(rd16(blk));
+  const float dmin = f16_to_f32(rd16(blk + 2));
+  const uint8_t* scales = blk + 4;
+  const uint8_t* qh = blk + 16;
+  const uint8_t* qs = blk + 48;
+  uint8_t u1 = 1, u2 = 2;
+  for (int j = 0; j < 4; ++j) {
+    uint32_t sc1, m1, sc2, m2;
+    k4(2 * j, scales, sc1, m1);
+    k4(2 * j + 1, scales, sc2, m2);
+    const float s1 = d * (float)(int16_t)sc1;
+    const float n1 = dmin * (float)(int16_t)(-(int)m1);
+    const float s2 = d * (float)(int16_t)sc2;
+    const float n2 = dmin * (float)(int16_t)(-(int)m2);
+    for (int l = 0; l < 32; ++l) {
+      const uint8_t v = qs[j * 32 + l];
+      const uint8_t c1 = (uint8_t)((v & 0xF) + ((qh[l] & u1) ? 16 : 0));
+      const uint8_t c2 = (uint8_t)((v >> 4) + ((qh[l] & u2) ? 16 : 0));
+      out[j * 64 + l] = s1 * (float)c1 + n1;
+      out[j * 64 + 32 + l] = s2 * (float)c2 + n2;
+    }
+    u1 = (uint8_t)(u1 << 2);
+    u2 = (uint8_t)(u2 << 2);
+  }
+}
+
+// One Q8_0 block (34 B -> 32 f32).  Factored form dequant.rs:214-223: code = q + 128, scale pair
+// (1, -128) on (d, d); expansion dequant.rs:35-51: sc = d*1 ; mn = d*(-128) ; out = sc*code + mn.
+void dequant_q80_block(const uint8_t* blk, float* out) {
+  const float d = f16_to_f32(rd16(blk));
+  const float sc = d * 1.0f, mn = d * -128.0f;
+  for (int i = 0; i < 32; ++i) {
+    const uint8_t code = (uint8_t)((int)(int8_t)blk[2 + i] + 128);
+    out[i] = sc * (float)code + mn;
+  }
+}
+
 size_t row_bytes(int dtype, size_t n_elem) {
   switch (dtype) {
     case DT_F32: return n_elem * 4;
+    case DT_Q8_0: return n_elem / 32 * 34;
     case DT_Q4K: return n_elem / 256 * 144;
+    case DT_Q5K: return n_elem / 256 * 176;
     case DT_Q6K: return n_elem / 256 * 210;
     default: return 0;
   }
@@ -157,6 +200,14 @@ bool dequant_row(int dtype, const uint8_t* bytes, size_t n_elem, float* out) {
     case DT_Q6K:
       if (n_elem % 256) return false;
       for (size_t b = 0; b < n_elem / 256; ++b) dequant_q6k_block(bytes + b * 210, out + b * 256);
+      return true;
+    case DT_Q5K:
+      if (n_elem % 256) return false;
+      for (size_t b = 0; b < n_elem / 256; ++b) dequant_q5k_block(bytes + b * 176, out + b * 256);
+      return true;
+    case DT_Q8_0:
+      if (n_elem % 32) return false;
+      for (size_t b = 0; b < n_elem / 32; ++b) dequant_q80_block(bytes + b * 34, out + b * 32);
       return true;
     default:
       return false;

@@ -16,6 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_build", "libmoe_oracle.so")
 
 DT_F32, DT_Q4K, DT_Q6K = 0, 12, 14
+DT_Q8_0, DT_Q5K = 8, 13
 GATING_SOFTMAX, GATING_SIGMOID, GATING_SQRT_SOFTPLUS = 0, 1, 2
 
 

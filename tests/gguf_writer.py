@@ -54,15 +54,16 @@ def layer_to_gguf(path, L, layer=0, arch="qwen35moe", n_used=8, alignment=32, ex
     meta = [("general.architecture", T_STR, arch), (f"{arch}.expert_count", T_U32, L.n_expert), (f"{arch}.expert_used_count", T_U32, n_used),
             (f"{arch}.expert_feed_forward_length", T_U32, L.n_ff), ("tokenizer.ggml.tokens", T_ARR, (T_STR, ["a", "b", "c"])),
             ("some.nested", T_ARR, (T_ARR, [(T_I32, [1, 2]), (T_I32, [3])]))] + list(extra_meta)
+    gd, ud, dd = getattr(L, "gate_dtype", 12), getattr(L, "up_dtype", 12), getattr(L, "down_dtype", 14)
     t = [("token_embd.weight", (L.ne, 4), 0, np.zeros((4, L.ne), np.float32).tobytes()),
          (p + "ffn_gate_inp.weight", (L.ne, L.n_expert), 0, np.ascontiguousarray(L.router, np.float32).tobytes()),
-         (p + "ffn_gate_exps.weight", (L.ne, L.n_ff, L.n_expert), 12, L.gate.tobytes()),
-         (p + "ffn_up_exps.weight", (L.ne, L.n_ff, L.n_expert), 12, L.up.tobytes()),
-         (p + "ffn_down_exps.weight", (L.n_ff, L.ne, L.n_expert), getattr(L, "down_dtype", 14), L.down.tobytes())]
+         (p + "ffn_gate_exps.weight", (L.ne, L.n_ff, L.n_expert), gd, L.gate.tobytes()),
+         (p + "ffn_up_exps.weight", (L.ne, L.n_ff, L.n_expert), ud, L.up.tobytes()),
+         (p + "ffn_down_exps.weight", (L.n_ff, L.ne, L.n_expert), dd, L.down.tobytes())]
     if L.sh_gate is not None:
-        t += [(p + "ffn_gate_shexp.weight", (L.ne, L.sh_ff), 12, L.sh_gate.tobytes()),
-              (p + "ffn_up_shexp.weight", (L.ne, L.sh_ff), 12, L.sh_up.tobytes()),
-              (p + "ffn_down_shexp.weight", (L.sh_ff, L.ne), getattr(L, "down_dtype", 14), L.sh_down.tobytes())]
+        t += [(p + "ffn_gate_shexp.weight", (L.ne, L.sh_ff), gd, L.sh_gate.tobytes()),
+              (p + "ffn_up_shexp.weight", (L.ne, L.sh_ff), ud, L.sh_up.tobytes()),
+              (p + "ffn_down_shexp.weight", (L.sh_ff, L.ne), dd, L.sh_down.tobytes())]
         if L.sh_gate_inp is not None:
             t.append((p + "ffn_gate_inp_shexp.weight", (L.ne,), 0, np.ascontiguousarray(L.sh_gate_inp, np.float32).tobytes()))
     if L.bias is not None:

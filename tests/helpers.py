@@ -75,6 +75,7 @@ class GpuLayer:
                     sh_down=self.sh_down if use_sh else None,
                     sh_gate_inp=self.sh_gate_inp if use_sh else None,
                     sh_ff=L.sh_ff if use_sh else 0, path=path, down_dtype=DType(getattr(L, "down_dtype", 14)),
+                    gate_dtype=DType(getattr(L, "gate_dtype", 12)), up_dtype=DType(getattr(L, "up_dtype", 12)),
                     expert_ids=given, down_scale=dsc, act=act, weight_before=weight_before, swiglu_clamp=swiglu_clamp,
                     fused_gate_up=fused_gate_up)
         be.moe_ffn(op)
@@ -88,7 +89,8 @@ def oracle_layer(L, x, n_used, *, router_x=None, scale=1.0, gating=0, norm_w=Tru
                  weight_before=False, swiglu_clamp=0.0, fused_gate_up=False):
     kw = dict(n_expert=L.n_expert, n_used=n_used, n_ff_exp=L.n_ff, scale=scale, gating=int(gating),
               norm_w=norm_w, bias=L.bias, groups=groups, groups_used=groups_used, ep_band=ep_band,
-              threads=threads, router_x=router_x, down_dtype=getattr(L, "down_dtype", 14), expert_ids=expert_ids,
+              threads=threads, router_x=router_x, down_dtype=getattr(L, "down_dtype", 14), gate_dtype=getattr(L, "gate_dtype", 12),
+              up_dtype=getattr(L, "up_dtype", 12), expert_ids=expert_ids,
               down_scale=down_scale, act=int(act), weight_before=weight_before, swiglu_clamp=swiglu_clamp,
               fused_gate_up=fused_gate_up)
     gate = fused_bank(L) if fused_gate_up else L.gate

@@ -78,14 +78,18 @@ def test_malformed_files_are_refused(tmp_path, case):
 
 
 @pytest.mark.gpu
-def test_layer_from_file_matches_oracle(backend, tmp_path):
+@pytest.mark.parametrize("dtypes", [None, (13, 13, 14), (8, 8, 8)])
+def test_layer_from_file_matches_oracle(backend, tmp_path, dtypes):
     from helpers import assert_close, near_tie_rows, oracle_layer
-    L = small_layer()
+    # the file's tensor types (Q4_K / Q6_K, a Q5_K_M-like mix, Q8_0 throughout) travel into the op
+    L = small_layer() if dtypes is None else synth.make_layer(4, 256, 8, 256, sh_ff=256, router_std=0.05, dtypes=dtypes)
     path = str(tmp_path / "layer.gguf")
     gw.layer_to_gguf(path, L, layer=0, n_used=2)
     g = GgufFile(path)
     op, bufs = moe_layer_op(backend, g, 0)
     assert (op.ne, op.n_expert, op.n_used, op.n_ff_exp, op.sh_ff) == (256, 8, 2, 256, 256)
+    if dtypes is not None:
+        assert (int(op.gate_dtype), int(op.up_dtype), int(op.down_dtype)) == dtypes
     # bytes on the device are the file's bytes
     got = backend.download(bufs["down"], np.uint8, count=L.down.size)
     assert np.array_equal(got, L.down.reshape(-1))

@@ -1,0 +1,90 @@
+"""Expert banks in other GGUF formats than the Q4_K / Q6_K pair: Q5_K, Q8_0 and mixes, through the
+C ABI against the CPU oracle, on the small-m kernels, the grouped GEMM tiles, the un-fused Linear op and
+the expert-parallel band form (the reference takes gate, up and down formats independently:
+crates/infr-core/src/tensor.rs:172-196; op parity per dtype in the style of
+crates/infr-llama/tests/seam_op_parity.rs)."""
+import numpy as np
+import pytest
+
+from moe4all_b200 import BackendError, DType, synth
+from oracle import oracle as orc
+
+from helpers import GpuLayer, assert_close, near_tie_rows, oracle_layer
+
+pytestmark = pytest.mark.gpu
+
+Q8_0, Q4K, Q5K, Q6K = 8, 12, 13, 14
+MIXES = [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0), (Q5K, Q5K, Q5K), (Q4K, Q5K, Q8_0), (Q6K, Q6K, Q4K), (Q8_0, Q4K, Q6K)]
+
+
+def check(out, ids, ref, n_used):
+    ties = set(near_tie_rows(ref, n_used).tolist())
+    for r in range(ids.shape[0]):
+        if r not in ties:
+            assert ids[r].tolist() == ref.ids[r].tolist()
+    return assert_close(out, ref.dst)
+
+
+@pytest.mark.parametrize("mix", MIXES)
+@pytest.mark.parametrize("rows,path", [(1, 0), (5, 1), (40, 1), (40, 2), (300, 0)])
+def test_format_mix_matches_oracle(backend, mix, rows, path):
+    L = synth.make_layer(31 + mix[0], 512, 16, 256, sh_ff=256, router_std=0.05, dtypes=mix)
+    x = synth.activations(200 + rows, rows, 512)
+    g = GpuLayer(backend, L)
+    n0 = backend.launch_count()
+    out, ids, _ = g.run(x, 4, path=path)
+    assert backend.launch_count() > n0
+    check(out, ids, oracle_layer(L, x, 4), 4)
+
+
+@pytest.mark.parametrize("mix", [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0)])
+def test_config1_shape(backend, mix):
+    # hidden 2048, 256 experts top-8, intermediate 512, gated shared expert: decode rows and a batched call
+    L = synth.make_layer(5, 2048, 256, 512, sh_ff=512, dtypes=mix)
+    g = GpuLayer(backend, L)
+    for rows in (1, 4, 400):
+        x = synth.activations(50 + rows, rows, 2048)
+        out, ids, _ = g.run(x, 8)
+        sel = np.arange(rows) if rows <= 4 else np.random.default_rng(1).choice(rows, 6, replace=False)
+        ref = oracle_layer(L, x[sel], 8)
+        check(out[sel], ids[sel], ref, 8)
+
+
+@pytest.mark.parametrize("mix", [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0)])
+def test_variants_and_bands(backend, mix):
+    L = synth.make_layer(77, 512, 16, 256, sh_ff=256, router_std=0.05, dtypes=mix)
+    g = GpuLayer(backend, L)
+    x = synth.activations(9, 6, 512)
+    ds = np.linspace(0.5, 1.5, 16).astype(np.float32)
+    for path in (1, 2):
+        # weight on the expert's input, GELU, clamp, a per-expert output scale, a fused gate/up bank
+        for kw in (dict(weight_before=True), dict(act=1), dict(swiglu_clamp=0.02), dict(down_scale=ds), dict(fused_gate_up=True)):
+            out, ids, _ = g.run(x, 4, path=path, **kw)
+            check(out, ids, oracle_layer(L, x, 4, **kw), 4)
+        # two expert-parallel bands sum to the whole layer's routed part
+        full = oracle_layer(L, x, 4, shared=False).dst
+        parts = [g.run(x, 4, path=path, shared=False, ep_band=(lo, 8))[0] for lo in (0, 8)]
+        assert_close(parts[0] + parts[1], full)
+
+
+@pytest.mark.parametrize("dt,name", [(Q5K, "Q5K"), (Q8_0, "Q8_0")])
+def test_linear_op(backend, dt, name):
+    # Op::Linear on the reference's synthesised weights (crates/infr-testkit/src/lib.rs:74-123)
+    w = synth.testkit_weight(name, 64 * 512, seed=0x77).reshape(-1)
+    x = synth.gen_f32(3 * 512, 5).reshape(3, 512)
+    be = backend
+    wb, xb, yb = be.from_host(w), be.from_host(x), be.alloc(3 * 64 * 4)
+    be.linear(DType(dt), wb, xb, yb, 3, 512, 64)
+    be.sync()
+    got = be.download(yb, np.float32).reshape(3, 64)
+    assert_close(got, orc.linear(dt, w, x, 64), tol=1e-4)
+
+
+def test_unknown_format_refused(backend):
+    L = synth.make_layer(3, 256, 8, 256)
+    g = GpuLayer(backend, L)
+    L.gate_dtype = 0  # F32 banks: not covered
+    with pytest.raises(BackendError) as e:
+        g.run(synth.activations(1, 1, 256), 2)
+    assert "Q4_K, Q5_K, Q6_K or Q8_0" in str(e.value)
+    L.gate_dtype = 12

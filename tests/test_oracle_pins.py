@@ -73,6 +73,39 @@ def np_q6k(raw, glsl_form=False):
     return out.reshape(-1)
 
 
+def np_q5k(raw):
+    """Factored form (dequant.rs:35-51, 337-362): Q4_K's scales; code = nibble + 16 * bit (2j | 2j+1) of qh[l]."""
+    raw = np.asarray(raw, np.uint8).reshape(-1, 176)
+    out = np.empty((raw.shape[0], 256), F32)
+    for bi, blk in enumerate(raw):
+        d, dmin = f16(int(blk[0]), int(blk[1])), f16(int(blk[2]), int(blk[3]))
+        sc_b, qh, qs = blk[4:16].astype(np.int64), blk[16:48].astype(np.int64), blk[48:176].astype(np.int64)
+        for s in range(8):
+            if s < 4:
+                sc, m = sc_b[s] & 63, sc_b[s + 4] & 63
+            else:
+                sc = (sc_b[s + 4] & 0xF) | ((sc_b[s - 4] >> 6) << 4)
+                m = (sc_b[s + 4] >> 4) | ((sc_b[s] >> 6) << 4)
+            S = F32(d * F32(sc))
+            M = F32(dmin * F32(-m))
+            byts = qs[32 * (s // 2): 32 * (s // 2) + 32]
+            q = ((byts & 0xF) if s % 2 == 0 else (byts >> 4)) + 16 * ((qh >> s) & 1)
+            out[bi, 32 * s: 32 * s + 32] = (S * q.astype(F32)).astype(F32) + M
+    return out.reshape(-1)
+
+
+def np_q80(raw):
+    """Factored form (dequant.rs:35-51, 214-223): (f32(d)*1)*(q+128) + f32(d)*(-128)."""
+    raw = np.asarray(raw, np.uint8).reshape(-1, 34)
+    out = np.empty((raw.shape[0], 32), F32)
+    for bi, blk in enumerate(raw):
+        d = f16(int(blk[0]), int(blk[1]))
+        code = blk[2:34].view(np.int8).astype(np.int64) + 128
+        with np.errstate(all="ignore"):
+            out[bi] = (F32(d * F32(1)) * code.astype(F32)).astype(F32) + F32(d * F32(-128))
+    return out.reshape(-1)
+
+
 def pattern_q4k():
     # crates/infr-gguf/src/dequant.rs:1174-1187: bytes ((i*37+11)&0xFF), d = 0.375, dmin = -0.125
     b = ((np.arange(288) * 37 + 11) & 0xFF).astype(np.uint8)
@@ -131,6 +164,38 @@ def test_random_blocks_match_numpy_decoder():
     q4, q6 = synth.random_q4k(rng, 16), synth.random_q6k(rng, 16)
     assert np.array_equal(orc.dequant(orc.DT_Q4K, q4, 4096).view(np.uint32), np_q4k(q4).view(np.uint32))
     assert np.array_equal(orc.dequant(orc.DT_Q6K, q6, 4096).view(np.uint32), np_q6k(q6).view(np.uint32))
+
+
+@pytest.mark.parametrize("dt,nbytes,elems,ref", [(orc.DT_Q5K, 176, 256, np_q5k), (orc.DT_Q8_0, 34, 32, np_q80)])
+def test_q5k_q80_patterns(dt, nbytes, elems, ref):
+    # crates/infr-gguf/src/dequant.rs:1206-1229: two blocks of bytes ((i*29+3)&0xFF), scale slots included
+    # (a block whose patterned scale is not finite decodes to the same non-finite bit patterns)
+    raw = ((np.arange(2 * nbytes) * 29 + 3) & 0xFF).astype(np.uint8)
+    with np.errstate(all="ignore"):
+        want = ref(raw)
+    got = orc.dequant(dt, raw, 2 * elems)
+    fin = np.isfinite(want)
+    assert np.array_equal(got[fin].view(np.uint32), want[fin].view(np.uint32))
+    assert np.array_equal(np.isnan(got), np.isnan(want)) and np.array_equal(np.isinf(got), np.isinf(want))
+    # the reference's synthesis recipe (crates/infr-testkit/src/lib.rs:74-123): LCG payload, scale slots set
+    name = "Q5K" if dt == orc.DT_Q5K else "Q8_0"
+    raw = synth.testkit_weight(name, 1024, seed=0x4321)
+    got = orc.dequant(dt, raw, 1024)
+    assert np.array_equal(got.view(np.uint32), ref(raw).view(np.uint32))
+    assert np.all(np.isfinite(got)) and np.ptp(got) > 0
+    # random payloads
+    rb = synth.random_blocks(np.random.default_rng(9), dt, 4096)
+    assert np.array_equal(orc.dequant(dt, rb, 4096).view(np.uint32), ref(rb).view(np.uint32))
+
+
+def test_q80_by_hand():
+    # d = 0.5, q = [-128, -1, 0, 127, ...]: value = d * q exactly
+    blk = np.zeros(34, np.uint8)
+    blk[0:2] = np.array([0.5], np.float16).view(np.uint8)
+    blk[2:6] = np.array([-128, -1, 0, 127], np.int8).view(np.uint8)
+    got = orc.dequant(orc.DT_Q8_0, blk, 32)
+    assert list(got[:4]) == [-64.0, -0.5, 0.0, 63.5]
+    assert orc.row_bytes(orc.DT_Q8_0, 2048) == 2176 and orc.row_bytes(orc.DT_Q5K, 2048) == 1408
 
 
 def test_ragged_block_count_rejected():
