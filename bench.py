@@ -44,6 +44,36 @@ X_POOL = 64
 Q4K_ROW = NE // 256 * 144      # bytes of one gate/up row
 Q6K_ROW = N_FF // 256 * 210    # bytes of one down row
 EXPERT_BYTES = 2 * N_FF * Q4K_ROW + NE * Q6K_ROW  # 2 039 808
+# --banks: GGUF type numbers and (elements, bytes) per block of the formats an expert bank may have
+BANK_TYPES = {"q8_0": 8, "q4k": 12, "q5k": 13, "q6k": 14}
+BANK_BLOCK = {8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210)}
+BANKS = (12, 12, 14)           # gate, up, down of the layer workload (set from --banks)
+
+
+def set_banks(spec):
+    """--banks gate,up,down: the layer workload's bank formats; the byte counts follow."""
+    global BANKS, Q4K_ROW, Q6K_ROW, EXPERT_BYTES
+    names = spec.lower().split(",")
+    if len(names) != 3 or any(n not in BANK_TYPES for n in names):
+        raise SystemExit(f"--banks wants gate,up,down out of {sorted(BANK_TYPES)}")
+    BANKS = tuple(BANK_TYPES[n] for n in names)
+    row = lambda dt, n: n // BANK_BLOCK[dt][0] * BANK_BLOCK[dt][1]
+    Q4K_ROW, Q6K_ROW = (row(BANKS[0], NE) + row(BANKS[1], NE)) / 2, row(BANKS[2], N_FF)  # mean gate/up row, down row
+    EXPERT_BYTES = int(2 * N_FF * Q4K_ROW + NE * Q6K_ROW)
+    if BANKS != (12, 12, 14):
+        global DTYPE
+        DTYPE = DTYPE.replace("Q4_K / Q6_K codes", banks_name() + " codes")
+
+
+def banks_tuned():
+    return BANKS[0] == 12 and BANKS[1] == 12 and BANKS[2] in (12, 14)
+
+
+def banks_name():
+    inv = {v: k for k, v in BANK_TYPES.items()}
+    pretty = {"q8_0": "Q8_0", "q4k": "Q4_K", "q5k": "Q5_K", "q6k": "Q6_K"}
+    g, u, d = (pretty[inv[b]] for b in BANKS)
+    return f"gate/up {g}, down {d}" if g == u else f"gate {g}, up {u}, down {d}"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each kernel of the step at
 # 1 stream, from an ncu capture of this workload: router, gate/up, down
 NCU_TRAFFIC_R1 = {"k_router_small": 2_196_736, "k_decode_gateup": 10_651_392, "k_decode_down": 7_798_528}
@@ -67,6 +97,8 @@ def parse_args():
     ap.add_argument("--shape", default="qwen", choices=["qwen", "deepseek"],
                     help="prefill workload only: the 256-expert Qwen3.6-35B-A3B layer, or the DeepSeek-V3-shaped one "
                          "(hidden 7168, intermediate 2048, sigmoid gating in 8 groups / 4 used, ungated shared expert)")
+    ap.add_argument("--banks", default="q4k,q4k,q6k", help="layer workload: formats of the gate, up and down banks "
+                    "(q4k, q5k, q6k, q8_0); the default is the configuration the metric is quoted on")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-subrecords", action="store_true", help="layer workload: skip the prefill and stack sub-records")
@@ -136,12 +168,14 @@ def distinct_experts(ids):
 
 def cpu_layers(n_sets):
     from moe4all_b200 import synth
-    return [synth.make_layer(1000 + i, NE, N_EXPERT, N_FF, sh_ff=SH_FF) for i in range(n_sets)]
+    return [synth.make_layer(1000 + i, NE, N_EXPERT, N_FF, sh_ff=SH_FF, dtypes=None if BANKS == (12, 12, 14) else BANKS)
+            for i in range(n_sets)]
 
 
 def cpu_step(orc, L, x, router_x=None):
     return orc.moe_layer(x, L.router, L.gate, L.up, L.down, L.sh_gate, L.sh_up, L.sh_down, L.sh_gate_inp, SH_FF,
-                         n_expert=N_EXPERT, n_used=N_USED, n_ff_exp=N_FF, threads=0, router_x=router_x)
+                         n_expert=N_EXPERT, n_used=N_USED, n_ff_exp=N_FF, threads=0, router_x=router_x,
+                         gate_dtype=L.gate_dtype, up_dtype=L.up_dtype, down_dtype=L.down_dtype)
 
 
 def time_cpu(streams, steps, warmup, n_sets=2):
@@ -242,7 +276,7 @@ def run_reference(args):
 
 def workload_config(streams, layer_sets):
     return {"workload": f"Qwen3.6-35B-A3B-shaped MoE layer decode, {streams} stream(s): hidden 2048, 256 experts top-8, "
-                        f"intermediate 512, gated shared expert, gate/up Q4_K, down Q6_K",
+                        f"intermediate 512, gated shared expert, {banks_name()}",
             "streams": streams, "layer_sets": layer_sets,
             "l2": f"steps rotate over {layer_sets} weight sets of {N_EXPERT * EXPERT_BYTES >> 20} MiB each (inputs larger than L2)"}
 
@@ -510,16 +544,16 @@ def measure_prefill(env, T, deepseek, steps, warmup, with_e2e=True):
 
 def run_ours(args):
     import torch
-    from moe4all_b200 import MoeFfn
+    from moe4all_b200 import DType, MoeFfn
     from moe4all_b200.devgen import DeviceLayer
 
     env = Env()
     be, world, rank, dev = env.be, env.world, env.rank, env.dev
     R, K, W, SETS = args.streams, args.steps, max(args.warmup, 3), max(args.layer_sets, 1)
-    subrecords = not args.no_subrecords
+    subrecords = not args.no_subrecords and BANKS == (12, 12, 14)  # the sub-records are the default formats' configs
     # the stack sub-record needs 40 layers; the layer workload rotates over the first SETS of them
     n_layers = max(SETS, 40) if subrecords else SETS
-    layers = [DeviceLayer(be, 1000 * (rank + 1) + i, NE, N_EXPERT, N_FF, sh_ff=SH_FF, device=dev) for i in range(n_layers)]
+    layers = [DeviceLayer(be, 1000 * (rank + 1) + i, NE, N_EXPERT, N_FF, sh_ff=SH_FF, device=dev, dtypes=BANKS) for i in range(n_layers)]
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
     x_dev = torch.randn(X_POOL, R, NE, generator=gen, device=dev)
@@ -534,7 +568,8 @@ def run_ours(args):
         return MoeFfn(x=xbuf if xbuf is not None else xb[step % X_POOL], router=b["router"], gate_exps=b["gate"],
                       up_exps=b["up"], down_exps=b["down"], dst=dst, rows=R, ne=NE, n_expert=N_EXPERT,
                       n_used=N_USED, n_ff_exp=N_FF, ids_out=ids, wts_out=wts, sh_gate=b["sh_gate"],
-                      sh_up=b["sh_up"], sh_down=b["sh_down"], sh_gate_inp=b["sh_gate_inp"], sh_ff=SH_FF, stages=stages)
+                      sh_up=b["sh_up"], sh_down=b["sh_down"], sh_gate_inp=b["sh_gate_inp"], sh_ff=SH_FF, stages=stages,
+                      gate_dtype=DType(BANKS[0]), up_dtype=DType(BANKS[1]), down_dtype=DType(BANKS[2]))
 
     # ---- device-resident timing: K steps recorded once, replayed (the reference replays a recorded decode
     # step the same way); warm-up runs the same steps un-recorded -----------------------------------
@@ -584,9 +619,10 @@ def run_ours(args):
     kernel_us = {}
     n_k = 200
     # from n_expert / n_used rows on, the small-m path runs its expert-major kernels (the library's own rule)
-    em = N_EXPERT <= R * N_USED and R * N_USED * 8 < N_EXPERT * 88
+    em = banks_tuned() and BANKS[2] == 14 and N_EXPERT <= R * N_USED and R * N_USED * 8 < N_EXPERT * 88
     names = ("k_router_small", "k_em_bucket + k_em_gateup", "k_em_down + k_em_combine") if em else \
-            ("k_router_small", "k_decode_gateup", "k_decode_down")
+            ("k_router_small", "k_decode_gateup", "k_decode_down") if banks_tuned() else \
+            ("k_router_small", "k_anyfmt_gateup", "k_anyfmt_down")
     for name, mask in zip(names, (1, 2, 4)):
         for s in range(SETS):
             be.moe_ffn(op_for(s, stages=mask))
@@ -659,7 +695,7 @@ def run_ours(args):
         kbytes = dict(zip(names, (N_EXPERT * NE * 4 + R * NE * 4, (mean_u + 1) * 2 * N_FF * Q4K_ROW, (mean_u + 1) * NE * Q6K_ROW)))
         kernels = [{"name": n, "us_alone": kernel_us[n], "algorithmic_bytes": kbytes[n],
                     "gbs_alone": kbytes[n] / (kernel_us[n] * 1e-6) / 1e9, "hbm_frac_alone": kbytes[n] / (kernel_us[n] * 1e-6) / 1e9 / peaks["hbm_gbs"],
-                    "traffic": NCU_TRAFFIC_R1[n] if R == 1 else None} for n in kernel_us]
+                    "traffic": NCU_TRAFFIC_R1[n] if R == 1 and BANKS == (12, 12, 14) else None} for n in kernel_us]
         line = {
             "metric": "moe_layer_decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K,
             "warmup": W, "repeats": repeats, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -670,7 +706,7 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "layer step (router + gate/up + down)", "achieved": layer_gbs, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": layer_gbs / peaks["hbm_gbs"], "peak_kind": peak_kind, "us_per_step": step_us,
                          "algorithmic_bytes": active_bytes, "distinct_routed_experts": mean_u,
-                         "traffic": sum(NCU_TRAFFIC_R1.values()) if R == 1 else None, "kernels": kernels},
+                         "traffic": sum(NCU_TRAFFIC_R1.values()) if R == 1 and BANKS == (12, 12, 14) else None, "kernels": kernels},
             "e2e": {"value": world * R * e2e_steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": nbytes,
                     "d2h_bytes_per_step": nbytes, "steps": e2e_steps},
             "gpu_launches": launches, "clocks": clocks, **sub,
@@ -728,6 +764,7 @@ def run_prefill(args):
 
 def main():
     args = parse_args()
+    set_banks(args.banks)
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "stack":

@@ -490,7 +490,7 @@ int pick_down_tile(int ne, int nff, int sh_ff, int n_used, size_t dbb) {
 }  // namespace
 
 bool decode_ffn_supported(const infr_cuda_ctx*, int ne, int nff, int sh_ff, int n_used, BankTypes bt, std::string* why) {
-  if (!bt.tuned()) return anyfmt_decode_supported(ne, nff, sh_ff, n_used, why);
+  if (!bt.tuned()) return anyfmt_decode_supported(ne, nff, sh_ff, n_used, bt, why);
   const bool down_q4k = bt.down_q4k();
   if (ne % 256 || nff % 256 || (sh_ff % 256)) {
     if (why) *why = "small-m path: ne, n_ff_exp and sh_ff must be multiples of 256";
@@ -512,7 +512,7 @@ bool decode_ffn_supported(const infr_cuda_ctx*, int ne, int nff, int sh_ff, int 
 }
 
 int32_t launch_decode_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages) {
-  if (!BankTypes{p.gate_dt, p.up_dt, p.down_dt}.tuned()) return launch_anyfmt_decode(ctx, p, stages);
+  if (!BankTypes{p.gate_dt, p.up_dt, p.down_dt}.tuned()) return launch_anyfmt_decode(ctx, p, pdl, stages);
   const bool has_sh = p.sh_gate != nullptr;
   const int sh_ff = has_sh ? p.sh_ff : 0;
   const int n_chunks = pick_chunks(p.ne, p.nff, sh_ff);

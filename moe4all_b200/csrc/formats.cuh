@@ -33,24 +33,35 @@ inline bool bank_dtypes_tuned(int32_t gate, int32_t up, int32_t down) {
 
 #ifdef __CUDACC__
 
+// A load through the read-only path when the blocks sit in global memory (G), a plain load when a
+// kernel has staged them in shared memory.
+template <bool G, typename T>
+__device__ __forceinline__ T fmt_ld(const void* p) {
+  if (G) return __ldg(reinterpret_cast<const T*>(p));
+  return *reinterpret_cast<const T*>(p);
+}
+
 // Four bytes at a 2-byte-aligned address: one word load when the address is word aligned, else two
 // 16-bit loads, so nothing outside the four bytes is touched.
-__device__ __forceinline__ uint32_t ldg_u32_a2(const uint8_t* p) {
-  if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) return __ldg(reinterpret_cast<const uint32_t*>(p));
-  const uint32_t lo = __ldg(reinterpret_cast<const unsigned short*>(p));
-  const uint32_t hi = __ldg(reinterpret_cast<const unsigned short*>(p + 2));
+template <bool G>
+__device__ __forceinline__ uint32_t ld_u32_a2(const uint8_t* p) {
+  if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) return fmt_ld<G, uint32_t>(p);
+  const uint32_t lo = fmt_ld<G, unsigned short>(p);
+  const uint32_t hi = fmt_ld<G, unsigned short>(p + 2);
   return lo | (hi << 16);
 }
 
-// Codes and affine map of weights 16h .. 16h+15 of the row starting at `row` (global memory).
+// Codes and affine map of weights 16h .. 16h+15 of the row starting at `row` (G: in global memory;
+// else a copy in shared memory with the same alignment modulo 16).
+template <bool G = true>
 __device__ __forceinline__ void fmt_codes16(int dt, const uint8_t* __restrict__ row, int h, uint32_t (&c)[4], float& A, float& B,
                                             int& off) {
   if (dt == INFR_CUDA_DT_Q4K || dt == INFR_CUDA_DT_Q5K) {
     const bool q5 = dt == INFR_CUDA_DT_Q5K;
     const uint8_t* blk = row + (size_t)(h >> 4) * (q5 ? Q5K_BLOCK_BYTES : Q4K_BLOCK_BYTES);
     const int e = (h & 15) * 16, j = e >> 6, sub = (e >> 5) & 1, l0 = e & 31;
-    const uint4 hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-    const uint4 q = __ldg(reinterpret_cast<const uint4*>(blk + (q5 ? 48 : 16) + 32 * j + l0));
+    const uint4 hdr = fmt_ld<G, uint4>(blk);
+    const uint4 q = fmt_ld<G, uint4>(blk + (q5 ? 48 : 16) + 32 * j + l0);
     const int sh = 4 * sub;
     c[0] = (q.x >> sh) & 0x0F0F0F0Fu;
     c[1] = (q.y >> sh) & 0x0F0F0F0Fu;
@@ -58,7 +69,7 @@ __device__ __forceinline__ void fmt_codes16(int dt, const uint8_t* __restrict__ 
     c[3] = (q.w >> sh) & 0x0F0F0F0Fu;
     if (q5) {
       // bit 2j + sub of qh[l] is the fifth code bit of element 64j + 32 sub + l
-      const uint4 qh = __ldg(reinterpret_cast<const uint4*>(blk + 16 + l0));
+      const uint4 qh = fmt_ld<G, uint4>(blk + 16 + l0);
       const int sb = 2 * j + sub;
       c[0] |= ((qh.x >> sb) & 0x01010101u) << 4;
       c[1] |= ((qh.y >> sb) & 0x01010101u) << 4;
@@ -80,19 +91,19 @@ __device__ __forceinline__ void fmt_codes16(int dt, const uint8_t* __restrict__ 
     const int nsh = 4 * (qd >> 1), hsh = 2 * qd;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint32_t lo = ldg_u32_a2(ql + 4 * i), hi = ldg_u32_a2(qh + 4 * i);
+      const uint32_t lo = ld_u32_a2<G>(ql + 4 * i), hi = ld_u32_a2<G>(qh + 4 * i);
       c[i] = ((lo >> nsh) & 0x0F0F0F0Fu) | (((hi >> hsh) & 0x03030303u) << 4);
     }
-    const float d = f16_bits_to_f32(__ldg(reinterpret_cast<const unsigned short*>(blk + 208)));
-    A = d * (float)(int)(signed char)__ldg(blk + 192 + 8 * hh + 2 * qd + (l0 >> 4));
+    const float d = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk + 208));
+    A = d * (float)(int)(signed char)fmt_ld<G, uint8_t>(blk + 192 + 8 * hh + 2 * qd + (l0 >> 4));
     B = 0.f;
     off = 32;
   } else {  // Q8_0
     const uint8_t* blk = row + (size_t)(h >> 1) * Q80_BLOCK_BYTES;
     const uint8_t* q = blk + 2 + 16 * (h & 1);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) c[i] = ldg_u32_a2(q + 4 * i) ^ 0x80808080u;
-    A = f16_bits_to_f32(__ldg(reinterpret_cast<const unsigned short*>(blk)));
+    for (int i = 0; i < 4; ++i) c[i] = ld_u32_a2<G>(q + 4 * i) ^ 0x80808080u;
+    A = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk));
     B = 0.f;
     off = 128;
   }

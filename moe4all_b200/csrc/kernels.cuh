@@ -180,8 +180,8 @@ int32_t launch_em_ffn(infr_cuda_ctx* ctx, const DecodeParams& p, void* scratch, 
 bool decode_ffn_supported(const infr_cuda_ctx* ctx, int ne, int nff, int sh_ff, int n_used, BankTypes bt, std::string* why);
 // Small-m kernels for banks in any mix of Q4_K / Q5_K / Q6_K / Q8_0 (anyfmt_ffn.cu): the tuned kernels'
 // arithmetic with the blocks read straight from global memory.
-bool anyfmt_decode_supported(int ne, int nff, int sh_ff, int n_used, std::string* why);
-int32_t launch_anyfmt_decode(infr_cuda_ctx* ctx, const DecodeParams& p, uint32_t stages);
+bool anyfmt_decode_supported(int ne, int nff, int sh_ff, int n_used, BankTypes bt, std::string* why);
+int32_t launch_anyfmt_decode(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl, uint32_t stages);
 
 // y[m, out_f] = x[m, in_f] · Wᵀ for W of dtype F32 / Q4_K / Q6_K.
 int32_t launch_linear(infr_cuda_ctx* ctx, int32_t dtype, const uint8_t* w, const float* x, float* y, int m, int in_f,

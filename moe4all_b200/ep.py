@@ -270,7 +270,10 @@ class LibraryExpertParallelLayer:
         self.band = (rank * (n_expert // world), n_expert // world)
         self.dims = dict(ne=ne, n_expert=n_expert, n_used=n_used, n_ff_exp=n_ff)
         self.sh_ff = sh_ff if "sh_gate" in layer.b else 0
-        self.route_kw = route_kw
+        # formats of the banks (devgen.DeviceLayer.dtypes; Q4_K / Q4_K / Q6_K when the layer does not say)
+        from .backend import DType
+        gd, ud, dd = getattr(layer, "dtypes", (12, 12, 14))
+        self.route_kw = dict(route_kw, gate_dtype=DType(gd), up_dtype=DType(ud), down_dtype=DType(dd))
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, ids_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: this rank's token rows [R, ne] f32 (the same R on every rank).  Collective."""

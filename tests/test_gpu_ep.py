@@ -18,14 +18,15 @@ NE, E, K, NFF = 512, 16, 4, 256
 
 
 def single_device(be, full, x, rows, path):
-    from moe4all_b200 import MoeFfn
+    from moe4all_b200 import DType, MoeFfn
     dst = torch.empty_like(x)
     ids = torch.empty(rows, K, dtype=torch.int32, device=x.device)
     b = full.b
+    gd, ud, dd = full.dtypes
     be.moe_ffn(MoeFfn(x=be.wrap_tensor(x), router=b["router"], gate_exps=b["gate"], up_exps=b["up"], down_exps=b["down"],
                       dst=be.wrap_tensor(dst), rows=rows, ne=NE, n_expert=E, n_used=K, n_ff_exp=NFF, sh_gate=b["sh_gate"],
                       sh_up=b["sh_up"], sh_down=b["sh_down"], sh_gate_inp=b["sh_gate_inp"], sh_ff=NFF, path=path,
-                      ids_out=be.wrap_tensor(ids)))
+                      ids_out=be.wrap_tensor(ids), gate_dtype=DType(gd), up_dtype=DType(ud), down_dtype=DType(dd)))
     be.sync()
     torch.cuda.synchronize()
     return dst.cpu().numpy(), ids.cpu().numpy()
@@ -133,6 +134,79 @@ def worker(rank, world, port, ret):
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
+
+
+def formats_worker(rank, world, port, ret):
+    """Banks in other formats through the collective call: Q5_K gate/up with Q6_K down, and Q8_0 throughout."""
+    import torch.distributed as dist
+    from moe4all_b200 import CudaBackend
+    from moe4all_b200.devgen import DeviceLayer
+    from moe4all_b200.ep import LibraryExpertParallelLayer, join_communicator
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(dev))
+    out = {}
+    try:
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            be, be_lib = CudaBackend(rank), CudaBackend(rank)
+            be.set_stream(stream.cuda_stream)
+            be_lib.set_stream(stream.cuda_stream)
+            if world > 1:
+                join_communicator(be_lib)
+            el = E // world
+            gen = torch.Generator(device=dev)
+            gen.manual_seed(11)
+            for mix in ((13, 13, 14), (8, 8, 8)):
+                banded = DeviceLayer(be_lib, 9, NE, E, NFF, sh_ff=NFF, device=dev, router_std=0.05, band=(rank * el, el), dtypes=mix)
+                full = DeviceLayer(be, 9, NE, E, NFF, sh_ff=NFF, device=dev, router_std=0.05, dtypes=mix)
+                lib_layer = LibraryExpertParallelLayer(be_lib, banded, E, K, NFF, NE, sh_ff=NFF)
+                for rows in (2, 48):
+                    x_all = torch.randn(world * rows, NE, generator=gen, device=dev)
+                    x = x_all[rank * rows:(rank + 1) * rows].contiguous()
+                    # small-m kernels (fixed-point activations) or grouped tiles (f16) on both sides alike
+                    path = 1 if rows * K * 8 <= el * 22 or rows <= 8 else 2
+                    ref, ref_ids = single_device(be, full, x, rows, path)
+                    ids_lib = torch.empty(rows, K, dtype=torch.int32, device=dev)
+                    got = lib_layer.forward(x, ids_out=ids_lib)
+                    be_lib.sync()
+                    torch.cuda.synchronize()
+                    out[f"{mix}-{rows}"] = (rel(got.cpu().numpy(), ref), float(np.abs(ref).max()), bool(np.array_equal(ids_lib.cpu().numpy(), ref_ids)))
+            if world > 1:
+                be_lib.ep_finalize()
+        ret[rank] = out
+    finally:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_ep_other_bank_formats(world):
+    import torch.multiprocessing as mp
+
+    if world > 1 and torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    if world == 1:
+        ret = {}
+        formats_worker(0, 1, port, ret)
+    else:
+        ret = mp.Manager().dict()
+        mp.spawn(formats_worker, args=(world, port, ret), nprocs=world, join=True)
+        ret = dict(ret)
+    assert len(ret) == world
+    for rank, out in ret.items():
+        assert len(out) == 4
+        for name, (err, mag, ids_ok) in out.items():
+            assert mag > 0 and ids_ok, f"rank {rank} {name}"
+            # the two sides may round the activations differently (fixed point against f16 tiles): the layer bound
+            assert err < 2e-3, f"rank {rank} {name}: expert-parallel result differs from single device by {err:.2e}"
 
 
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
