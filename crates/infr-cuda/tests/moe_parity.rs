@@ -243,7 +243,7 @@ fn unsupported_is_an_error() {
     let Some(gpu) = gpu() else { return };
     let mut g = Graph::new();
     let x = g.input(f32d(64));
-    let w = g.weight(qd(64 * 256, DType::Q8_0));
+    let w = g.weight(qd(64 * 256, DType::Q4_0));
     let y = g.output(f32d(256));
     g.push(Op::Linear { x, weight: w, dst: y, m: 1, in_f: 64, out_f: 256, w_off: 0 });
     let plan = gpu.compile(&g).expect("compile");

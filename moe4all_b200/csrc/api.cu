@@ -751,7 +751,8 @@ int32_t infr_cuda_linear(infr_cuda_ctx* ctx, int32_t dtype, const infr_cuda_buf*
   if (!m || !in_f || !out_f) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: zero dimension");
   const size_t rb = row_bytes(dtype, in_f);
   if (!rb) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32, Q4_K, Q5_K, Q6_K, Q8_0)");
-  if (dtype != INFR_CUDA_DT_F32 && in_f % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: in_f must be a multiple of the 256-weight block");
+  if (dtype != INFR_CUDA_DT_F32 && in_f % (dtype == INFR_CUDA_DT_Q8_0 ? 32 : 256))
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: in_f must be a whole number of weight blocks (256, or 32 for Q8_0)");
   if (!fits(w, rb * out_f) || !fits(x, (size_t)m * in_f * 4) || !fits(y, (size_t)m * out_f * 4))
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: buffer missing or too small");
   DeviceGuard g(ctx->device);

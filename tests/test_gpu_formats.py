@@ -67,17 +67,21 @@ def test_variants_and_bands(backend, mix):
         assert_close(parts[0] + parts[1], full)
 
 
-@pytest.mark.parametrize("dt,name", [(Q5K, "Q5K"), (Q8_0, "Q8_0")])
-def test_linear_op(backend, dt, name):
-    # Op::Linear on the reference's synthesised weights (crates/infr-testkit/src/lib.rs:74-123)
-    w = synth.testkit_weight(name, 64 * 512, seed=0x77).reshape(-1)
-    x = synth.gen_f32(3 * 512, 5).reshape(3, 512)
+@pytest.mark.parametrize("dt,name,in_f,out_f", [(Q5K, "Q5K", 512, 64), (Q8_0, "Q8_0", 512, 64), (Q8_0, "Q8_0", 96, 40)])
+def test_linear_op(backend, dt, name, in_f, out_f):
+    # Op::Linear on the reference's synthesised weights (crates/infr-testkit/src/lib.rs:74-123); Q8_0 rows
+    # need whole 32-weight blocks only
+    w = synth.testkit_weight(name, out_f * in_f, seed=0x77).reshape(-1)
+    x = synth.gen_f32(3 * in_f, 5).reshape(3, in_f)
     be = backend
-    wb, xb, yb = be.from_host(w), be.from_host(x), be.alloc(3 * 64 * 4)
-    be.linear(DType(dt), wb, xb, yb, 3, 512, 64)
+    wb, xb, yb = be.from_host(w), be.from_host(x), be.alloc(3 * out_f * 4)
+    be.linear(DType(dt), wb, xb, yb, 3, in_f, out_f)
     be.sync()
-    got = be.download(yb, np.float32).reshape(3, 64)
-    assert_close(got, orc.linear(dt, w, x, 64), tol=1e-4)
+    got = be.download(yb, np.float32).reshape(3, out_f)
+    assert_close(got, orc.linear(dt, w, x, out_f), tol=1e-4)
+    if dt == Q5K:
+        with pytest.raises(BackendError):
+            be.linear(DType(dt), wb, xb, yb, 3, 96, 8)  # not a whole number of 256-weight blocks
 
 
 def test_unknown_format_refused(backend):
