@@ -102,7 +102,9 @@ def test_descriptor_validation(backend):
     be.moe_ffn(op())
     be.sync()
     with pytest.raises(Unsupported):
-        be.moe_ffn(op(gate_dtype=DType.Q6K))      # gate bank dtype without a kernel
+        be.moe_ffn(op(gate_dtype=DType.F32))      # gate bank dtype without a kernel
+    with pytest.raises(BackendError):
+        be.moe_ffn(op(gate_dtype=DType.Q6K))      # a covered format, but the bank holds Q4_K's bytes: too small
     with pytest.raises(Unsupported):
         be.moe_ffn(op(router_dtype=DType.Q4K))
     with pytest.raises(BackendError):
