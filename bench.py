@@ -620,9 +620,10 @@ def run_ours(args):
     n_k = 200
     # from n_expert / n_used rows on, the small-m path runs its expert-major kernels (the library's own rule)
     em = banks_tuned() and BANKS[2] == 14 and N_EXPERT <= R * N_USED and R * N_USED * 8 < N_EXPERT * 88
-    names = ("k_router_small", "k_em_bucket + k_em_gateup", "k_em_down + k_em_combine") if em else \
-            ("k_router_small", "k_decode_gateup", "k_decode_down") if banks_tuned() else \
-            ("k_router_small", "k_anyfmt_gateup", "k_anyfmt_down")
+    router = "k_router_mid" if 8 < R <= 64 else "k_router_small"  # (beyond 64 rows: the batched router's three kernels)
+    names = (router, "k_em_bucket + k_em_gateup", "k_em_down + k_em_combine") if em else \
+            (router, "k_decode_gateup", "k_decode_down") if banks_tuned() else \
+            (router, "k_anyfmt_gateup", "k_anyfmt_down")
     for name, mask in zip(names, (1, 2, 4)):
         for s in range(SETS):
             be.moe_ffn(op_for(s, stages=mask))
@@ -695,7 +696,7 @@ def run_ours(args):
         kbytes = dict(zip(names, (N_EXPERT * NE * 4 + R * NE * 4, (mean_u + 1) * 2 * N_FF * Q4K_ROW, (mean_u + 1) * NE * Q6K_ROW)))
         kernels = [{"name": n, "us_alone": kernel_us[n], "algorithmic_bytes": kbytes[n],
                     "gbs_alone": kbytes[n] / (kernel_us[n] * 1e-6) / 1e9, "hbm_frac_alone": kbytes[n] / (kernel_us[n] * 1e-6) / 1e9 / peaks["hbm_gbs"],
-                    "traffic": NCU_TRAFFIC_R1[n] if R == 1 and BANKS == (12, 12, 14) else None} for n in kernel_us]
+                    "traffic": NCU_TRAFFIC_R1.get(n) if R == 1 and BANKS == (12, 12, 14) else None} for n in kernel_us]
         line = {
             "metric": "moe_layer_decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": K,
             "warmup": W, "repeats": repeats, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
