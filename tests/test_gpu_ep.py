@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 NE, E, K, NFF = 512, 16, 4, 256
 
 
-def single_device(be, full, x, rows, path):
+def single_device(be, full, x, rows, path, E=E):
     from moe4all_b200 import DType, MoeFfn
     dst = torch.empty_like(x)
     ids = torch.empty(rows, K, dtype=torch.int32, device=x.device)
@@ -36,7 +36,7 @@ def rel(got, ref):
     return float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-3))
 
 
-def worker(rank, world, port, ret):
+def worker(rank, world, port, ret, E=E):
     import torch.distributed as dist
     from moe4all_b200 import BackendError, CudaBackend
     from moe4all_b200.backend import ERR_NCCL
@@ -67,18 +67,22 @@ def worker(rank, world, port, ret):
             banded_lib = DeviceLayer(be_lib, 7, NE, E, NFF, sh_ff=NFF, device=dev, router_std=0.05, band=(rank * el, el))
             full = DeviceLayer(be, 7, NE, E, NFF, sh_ff=NFF, device=dev, router_std=0.05)
             host_layer = CudaExpertParallelLayer(be, banded, E, K, NFF, NE)
-            lib_layer = LibraryExpertParallelLayer(be_lib, banded_lib, E, K, NFF, NE, sh_ff=NFF)
             gen = torch.Generator(device=dev)
             gen.manual_seed(5)
+
+            def band_path(rows):
+                # The kernels a band call of `rows` rows per rank picks when left alone (small-m while an expert
+                # sees fewer than 11 rows, or the call has at most 8 rows); both sides are then told to use them,
+                # so that the comparison isolates the exchange: the only difference left is the association of
+                # the sum over ranks.
+                return 1 if rows * K * 8 < el * 88 or rows <= 8 else 2
             # rows per rank: the reference's 1 / 4 / 16 (small-m kernels in the band) and a batch (grouped GEMMs)
             for rows in (1, 4, 16, 48):
                 x_all = torch.randn(world * rows, NE, generator=gen, device=dev)  # the same on every rank
                 x = x_all[rank * rows:(rank + 1) * rows].contiguous()
-                # the same kernels as the band call will pick (small-m while an expert sees fewer than 11
-                # rows), so that the comparison isolates the exchange: the only difference left is the
-                # association of the sum over ranks
-                path = 1 if rows * K * 8 < el * 88 else 2
-                ref, ref_ids = single_device(be, full, x, rows, path)
+                path = band_path(rows)
+                lib_layer = LibraryExpertParallelLayer(be_lib, banded_lib, E, K, NFF, NE, sh_ff=NFF, path=path)
+                ref, ref_ids = single_device(be, full, x, rows, path, E)
                 mag = float(np.abs(ref).max())
                 ids_lib = torch.empty(rows, K, dtype=torch.int32, device=dev)
                 got_lib = lib_layer.forward(x, ids_out=ids_lib)
@@ -96,7 +100,7 @@ def worker(rank, world, port, ret):
             h = torch.randn(rows, NE, generator=gen, device=dev)
             nw = 1.0 + 0.1 * torch.randn(NE, generator=gen, device=dev)
             hn = (h * torch.rsqrt((h * h).mean(1, keepdim=True) + 1e-6)) * nw
-            ref, _ = single_device(be, full, hn.contiguous(), rows, 1 if rows * K * 8 < el * 88 else 2)
+            ref, _ = single_device(be, full, hn.contiguous(), rows, band_path(rows), E)
             ref = ref + h.cpu().numpy()
             from moe4all_b200 import MoeFfn
             b = banded_lib.b
@@ -104,7 +108,7 @@ def worker(rank, world, port, ret):
             be_lib.moe_ffn(MoeFfn(x=hb, dst=hb, residual=hb, norm_weight=be_lib.wrap_tensor(nw), norm_eps=1e-6, rows=rows, ne=NE,
                                   n_expert=E, n_used=K, n_ff_exp=NFF, router=b["router"], gate_exps=b["gate"], up_exps=b["up"],
                                   down_exps=b["down"], sh_gate=b["sh_gate"], sh_up=b["sh_up"], sh_down=b["sh_down"],
-                                  sh_gate_inp=b["sh_gate_inp"], sh_ff=NFF, ep_band=(rank * el, el)))
+                                  sh_gate_inp=b["sh_gate_inp"], sh_ff=NFF, ep_band=(rank * el, el), path=band_path(rows)))
             be_lib.sync()
             torch.cuda.synchronize()
             out["fused"] = (rel(h.cpu().numpy(), ref), float(np.abs(ref).max()), True)
@@ -122,7 +126,8 @@ def worker(rank, world, port, ret):
                     out["mismatch"] = "nccl" if e.code == ERR_NCCL else f"code {e.code}"
                 # the communicator survives a refused call: the next matching call still works
                 x = torch.randn(4, NE, generator=gen, device=dev)
-                ref, _ = single_device(be, full, x, 4, 1 if 4 * K * 8 < el * 88 else 2)
+                lib_layer = LibraryExpertParallelLayer(be_lib, banded_lib, E, K, NFF, NE, sh_ff=NFF, path=band_path(4))
+                ref, _ = single_device(be, full, x, 4, band_path(4), E)
                 got = lib_layer.forward(x)
                 be_lib.sync()
                 torch.cuda.synchronize()
@@ -209,8 +214,10 @@ def test_ep_other_bank_formats(world):
             assert err < 2e-3, f"rank {rank} {name}: expert-parallel result differs from single device by {err:.2e}"
 
 
-@pytest.mark.parametrize("world", [1, 2, 4, 8])
-def test_ep_matches_single_device(world):
+# (world, experts): 16 experts over 1 / 2 / 4 / 8 ranks, and bands of two experts - fewer than a token uses -
+# as they are at 8 ranks, on 2 ranks
+@pytest.mark.parametrize("world,n_expert", [(1, 16), (2, 16), (4, 16), (8, 16), (2, 4)])
+def test_ep_matches_single_device(world, n_expert):
     import torch.multiprocessing as mp
 
     if world > 1 and torch.cuda.device_count() < world:
@@ -220,10 +227,10 @@ def test_ep_matches_single_device(world):
         port = s.getsockname()[1]
     if world == 1:
         ret = {}
-        worker(0, 1, port, ret)
+        worker(0, 1, port, ret, n_expert)
     else:
         ret = mp.Manager().dict()
-        mp.spawn(worker, args=(world, port, ret), nprocs=world, join=True)
+        mp.spawn(worker, args=(world, port, ret, n_expert), nprocs=world, join=True)
         ret = dict(ret)
     assert len(ret) == world
     for rank, out in ret.items():
