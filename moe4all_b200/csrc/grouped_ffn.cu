@@ -673,7 +673,9 @@ __global__ void __launch_bounds__(256) k_unpermute_combine(const float* __restri
 }
 
 // The shared segment starts right after the routed rows: its address is only known on the device.
-__global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
+template <bool Y16>
+__global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __restrict__ y, const float* __restrict__ y_scale,
+                                                               const int* __restrict__ pos_of_pair,
                                                                const float* __restrict__ wts, const float* __restrict__ sh_logit,
                                                                const int* __restrict__ seg_off, int n_seg_routed, int has_shared,
                                                                int rows, int n_used, int ne, const float* residual,
@@ -681,13 +683,21 @@ __global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __re
                                                                int weight_before, float* dst) {
   const int c = (blockIdx.x * 256 + threadIdx.x) * 4;
   if (c >= ne) return;
+  // four outputs of row `pos` of y (f32 rows; or the tcgen05 down kernel's f16 rows with one scale per 32)
+  auto y4 = [&](size_t pos) {
+    if (!Y16) return *reinterpret_cast<const float4*>(y + pos * ne + c);
+    const uint2 h = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(y) + pos * ne + c);
+    const float sc = y_scale[pos * (ne / 32) + (c >> 5)];
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&h.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&h.y));
+    return make_float4(a.x * sc, a.y * sc, b.x * sc, b.y * sc);
+  };
   for (int t = blockIdx.y; t < rows; t += gridDim.y) {  // the grid's y extent stops at 65535
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < n_used; ++s) {
       const int pos = pos_of_pair[(size_t)t * n_used + s];
       if (pos < 0) continue;
       const float w = weight_before ? 1.0f : wts[(size_t)t * n_used + s];
-      float4 v = *reinterpret_cast<const float4*>(y + (size_t)pos * ne + c);
+      float4 v = y4((size_t)pos);
       if (down_scale != nullptr) {  // y = raw * scale[e], then the weighted sum (Op::MoeFfn::down_scale)
         // ids may be the caller's: same clamp as the bucketing, which also reported the bad id
         const float sc = down_scale[min(max(ids[(size_t)t * n_used + s], 0), n_seg_routed - 1)];
@@ -697,7 +707,7 @@ __global__ void __launch_bounds__(256) k_unpermute_combine_seg(const float* __re
     }
     if (has_shared) {
       const float gsh = sh_logit ? 1.0f / (1.0f + __expf(-sh_logit[t])) : 1.0f;
-      const float4 v = *reinterpret_cast<const float4*>(y + (size_t)(seg_off[n_seg_routed] + t) * ne + c);
+      const float4 v = y4((size_t)(seg_off[n_seg_routed] + t));
       o.x += gsh * v.x; o.y += gsh * v.y; o.z += gsh * v.z; o.w += gsh * v.w;
     }
     if (residual != nullptr) {  // MoeFfn -> Add; may alias dst: each element is read, then written, by this thread
@@ -847,6 +857,10 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   p.nff = c.nff;
   p.n_expert = c.n_expert;
   p.down_q4k = c.down_q4k;
+  // tcgen05 tiles with the combine behind them: the raw rows cross memory as f16 (half the bytes out of the
+  // down kernel and into the combine); rows handed to the caller stay f32
+  p.y_f16 = (use_umma && c.dst != nullptr && c.y_out == nullptr && c.ne % 32 == 0) ? 1 : 0;
+  p.y_scale = reinterpret_cast<float*>(reinterpret_cast<char*>(y) + ((size_t)rows_total + 256) * c.ne * 2);  // behind the f16 rows
   p.gate_dt = c.gate_dt;
   p.up_dt = c.up_dt;
   p.down_dt = c.down_dt;
@@ -871,9 +885,10 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
     ctx->launches += 2;
   }
   if (c.dst) {
-    k_unpermute_combine_seg<<<dim3((c.ne / 4 + 255) / 256, std::min(c.rows, 65535)), 256, 0, st>>>(y, pos_of_pair, c.wts, c.sh_logit, seg_off, n_seg_routed,
-                                                                                   c.shared_rows > 0 ? 1 : 0, c.rows, c.n_used, c.ne, c.residual, c.ids, c.down_scale,
-                                                                                   c.weight_before, c.dst);
+    auto comb = p.y_f16 ? k_unpermute_combine_seg<true> : k_unpermute_combine_seg<false>;
+    comb<<<dim3((c.ne / 4 + 255) / 256, std::min(c.rows, 65535)), 256, 0, st>>>(y, p.y_scale, pos_of_pair, c.wts, c.sh_logit, seg_off, n_seg_routed,
+                                                                                 c.shared_rows > 0 ? 1 : 0, c.rows, c.n_used, c.ne, c.residual, c.ids, c.down_scale,
+                                                                                 c.weight_before, c.dst);
     ctx->launches += 1;
   }
   return check_cuda(ctx, cudaGetLastError(), "grouped ffn launch");

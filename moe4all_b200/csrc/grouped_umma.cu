@@ -540,13 +540,39 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p, con
     if (ok && m < n_m) {
       const int n0 = m * 128 + lq * 32;
       const uint32_t trow = tmem + ((uint32_t)(lq * 32) << 16) + (uint32_t)(m * 256 + ch * 128);
-      unsigned char* out = reinterpret_cast<unsigned char*>(p.y + (size_t)(row0 + n0) * p.ne + i0 + ch * 128);
-      const size_t out_pitch = (size_t)p.ne * 4;
+      const size_t esz = p.y_f16 ? 2 : 4;
+      unsigned char* out = reinterpret_cast<unsigned char*>(p.y) + ((size_t)(row0 + n0) * p.ne + i0 + ch * 128) * esz;
+      const size_t out_pitch = (size_t)p.ne * esz;
       unsigned char* patch = a_stages + (size_t)warp * (32 * 144);  // the weight stages are idle by now
+      float row_scale[4] = {0.f, 0.f, 0.f, 0.f};  // f16 rows: the scales of this thread's four passes
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         float v[32];
         umma::ld_32x32(trow + c * 32, v);
+        if (p.y_f16) {
+          // the combine kernel is the only reader: f16 rows, the 32 outputs of this pass sharing a
+          // power-of-two scale that brings their largest magnitude to [2^14, 2^15) (any range of
+          // outputs keeps 11 bits against its neighbours' maximum; the sum over slots is taken in f32)
+          float m = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) m = fmaxf(m, fabsf(v[i]));
+          const int ex = (__float_as_int(m) >> 23) & 0xFF;  // biased exponent of the maximum
+          const bool live = ex >= 32;                       // below 2^-95: stored as zeros
+          const bool fin = ex < 255;                        // an infinite or NaN output goes through as it is
+          const float inv = !live ? 0.f : fin ? __int_as_float((268 - ex) << 23) : 1.0f;  // 2^(14 - exponent)
+          row_scale[c] = !live ? 0.f : fin ? __int_as_float((ex - 22) << 23) : W_POSTSCALE;  // 2^-8 / inv
+          uint4 h[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float* q = v + 8 * t;
+            h[t] = make_uint4(h2_as_u32(__floats2half2_rn(q[0] * inv, q[1] * inv)), h2_as_u32(__floats2half2_rn(q[2] * inv, q[3] * inv)),
+                              h2_as_u32(__floats2half2_rn(q[4] * inv, q[5] * inv)), h2_as_u32(__floats2half2_rn(q[6] * inv, q[7] * inv)));
+          }
+          warp_store_rows<4>(patch, h, lane, rows_valid - n0, [&](int row, int piece) {
+            return out + (size_t)row * out_pitch + (size_t)c * 64 + piece * 16;
+          });
+          continue;
+        }
         uint4 o[8];
 #pragma unroll
         for (int t = 0; t < 8; ++t)
@@ -556,6 +582,9 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_down(GroupedParams p, con
           return out + (size_t)row * out_pitch + (size_t)c * 128 + piece * 16;
         });
       }
+      if (p.y_f16 && lane < rows_valid - n0)  // the four scales of this row's 128 outputs: one 16-byte store
+        *reinterpret_cast<float4*>(p.y_scale + (size_t)(row0 + n0 + lane) * (p.ne / 32) + (i0 + ch * 128) / 32) =
+            make_float4(row_scale[0], row_scale[1], row_scale[2], row_scale[3]);
     }
   }
   trace_stamp(trc, 47);

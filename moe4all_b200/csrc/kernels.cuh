@@ -99,7 +99,10 @@ struct GroupedParams {
   // [rows, nff] row-major.  tcgen05 tiles: [tile][K step][256 rows][64] with swizzled 128-byte lines.
   const __half* xg;
   __half* act;
-  float* y;          // [rows, ne]
+  float* y;          // [rows, ne] raw down outputs: f32, or f16 in the same buffer when y_f16 is set
+  int y_f16;         // the combine kernel is the only reader (tcgen05 tiles): rows as f16 with one power-of-two
+                     // scale per 32 outputs of a row (y_scale), half the bytes both ways
+  float* y_scale;    // [rows, ne / 32]: in the unused half of the y buffer
   const uint8_t *gate, *up, *down;
   const uint8_t *sh_gate, *sh_up, *sh_down;  // segment index n_expert = the shared expert
   size_t gate_stride, up_stride, down_stride;
