@@ -306,6 +306,7 @@ class MoeFfn:
         d.down_scale, d.act = _h(self.down_scale), int(self.act)
         d.weight_before, d.swiglu_clamp = int(bool(self.weight_before)), float(self.swiglu_clamp)
         d.fused_gate_up = int(bool(self.fused_gate_up))
+        d._op = self  # the descriptor holds raw handle pointers: the op (and its Buffer objects) must outlive it
         return d
 
 
