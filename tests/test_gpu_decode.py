@@ -258,3 +258,23 @@ def test_many_experts(backend, rows, n_expert):
     ref = oracle_layer(L, x, 8)
     check_ids(ids, wts, ref, 8)
     assert_close(out, ref.dst)
+
+
+@pytest.mark.parametrize("rows,n_expert,ne", [(20, 20, 512), (9, 44, 768), (40, 100, 256)])
+def test_streamed_router_ragged_experts(backend, rows, n_expert, ne):
+    # 9 .. 64 rows take the streamed router; an expert count that is no multiple of a CTA's eight router
+    # rows leaves the last CTA a partial share, a row count that is no multiple of eight a partial group
+    L = synth.make_layer(91, ne, n_expert, 256, sh_ff=256, router_std=0.05)
+    x = synth.activations(93, rows, ne)
+    g = GpuLayer(backend, L)
+    out, ids, wts = g.run(x, 3, path=1)
+    ref = oracle_layer(L, x, 3)
+    check_ids(ids, wts, ref, 3)
+    assert_close(out, ref.dst)
+    # the caller's selection through the same kernel: weights of the given experts
+    given = ref.ids[:, ::-1].copy()
+    out2, ids2, wts2 = g.run(x, 3, path=1, expert_ids=given)
+    ref2 = oracle_layer(L, x, 3, expert_ids=given)
+    assert np.array_equal(ids2, given)
+    np.testing.assert_allclose(wts2, ref2.wts, rtol=2e-6, atol=1e-9)
+    assert_close(out2, ref2.dst)
