@@ -499,12 +499,21 @@ def measure_prefill(env, T, deepseek, steps, warmup, with_e2e=True):
         env.dist.all_gather(all_band, band_ms)
         extra["band_experts_ms_per_rank"] = [float(v) for v in all_band]
         if full is not None:
+            # The comparison isolates the exchange: both sides keep the experts' raw rows in f32 for it (the
+            # single-device call rounds the shared expert's rows to f16 with the routed ones, the band call
+            # computes them apart), so what is left is the association of the sum over ranks.
+            be.set_config(raw_rows_f32=1)
+            sync_be.set_config(raw_rows_f32=1)
+            step(0)
+            sync_be.sync()
             ref = torch.empty_like(x)
             be.moe_ffn(single_op(x, ref, rows))
             be.sync()
             torch.cuda.synchronize()
             mag = float(ref.abs().max())
             extra["ep_parity_rel"] = env.max_over_ranks(float((dst - ref).abs().max()) / max(mag, 1e-3))[0]
+            be.set_config(raw_rows_f32=0)
+            sync_be.set_config(raw_rows_f32=0)
     flops = 3 * 2 * T * n_used * ne * n_ff  # routed experts only (2*pairs*K*N per GEMM)
     tfl = flops / (ms / steps * 1e-3) / 1e12
     peaks, kind = measured_peaks()

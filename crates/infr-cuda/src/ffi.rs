@@ -97,7 +97,8 @@ pub struct infr_cuda_config {
     pub trace_tile: u32,
     pub expert_major: u32,
     pub sync_timeout_ms: u32,
-    pub reserved: [u32; 9],
+    pub raw_rows_f32: u32,
+    pub reserved: [u32; 8],
 }
 
 extern "C" {

@@ -87,7 +87,11 @@ typedef struct infr_cuda_config {
   uint32_t sync_timeout_ms;      /* expert-parallel contexts: how long infr_cuda_sync waits for the stream
                                     before it aborts the communicator and returns INFR_CUDA_ERR_NCCL
                                     (default 60000)                                                       */
-  uint32_t reserved[9];          /* zero                                                                  */
+  uint32_t raw_rows_f32;         /* batched path on the tcgen05 tiles: 1 = the experts' raw output rows cross memory
+                                    as f32 between the down and the combine kernel instead of f16 with a scale
+                                    per 32 outputs (twice the bytes, no rounding before the sum over a token's
+                                    experts; default 0)                                                    */
+  uint32_t reserved[8];          /* zero                                                                  */
 } infr_cuda_config;
 int32_t infr_cuda_get_config(const infr_cuda_ctx* ctx, infr_cuda_config* out);
 int32_t infr_cuda_set_config(infr_cuda_ctx* ctx, const infr_cuda_config* cfg);

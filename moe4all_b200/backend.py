@@ -110,7 +110,7 @@ class Config(C.Structure):
     _fields_ = [
         ("gu_warps", C.c_uint32), ("gu_chunks", C.c_uint32), ("dn_warps", C.c_uint32), ("upload_by_copy", C.c_uint32),
         ("trace_tile", C.c_uint32), ("expert_major", C.c_uint32),
-        ("sync_timeout_ms", C.c_uint32), ("reserved", C.c_uint32 * 9),
+        ("sync_timeout_ms", C.c_uint32), ("raw_rows_f32", C.c_uint32), ("reserved", C.c_uint32 * 8),
     ]
 
 

@@ -181,7 +181,7 @@ int32_t infr_cuda_get_config(const infr_cuda_ctx* ctx, infr_cuda_config* out) {
 
 int32_t infr_cuda_set_config(infr_cuda_ctx* ctx, const infr_cuda_config* cfg) {
   if (!ctx || !cfg) return INFR_CUDA_ERR_INVALID_ARG;
-  if (cfg->gu_chunks > 4 || cfg->gu_warps > 16 || cfg->dn_warps > 24 || cfg->expert_major > 2)
+  if (cfg->gu_chunks > 4 || cfg->gu_warps > 16 || cfg->dn_warps > 24 || cfg->expert_major > 2 || cfg->raw_rows_f32 > 1)
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_config: a field is outside its range");
   for (uint32_t r : cfg->reserved)
     if (r) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_config: reserved fields must be zero");

@@ -81,6 +81,8 @@ struct EpState {
   bool dead = false;             // the communicator was aborted: local calls only from now on
   cudaStream_t side = nullptr;   // the shared expert runs here while the exchanges are in flight
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  cudaStream_t xfer = nullptr;   // the token rows' all-gather runs here while the router works on the main stream
+  cudaEvent_t ev_x = nullptr, ev_xg = nullptr;
   cudaEvent_t ev_phase[EP_PHASES] = {};
   bool phases_valid = false;
   void* buf = nullptr;           // exchange buffers, grown on demand (never while recording)
@@ -117,6 +119,7 @@ int32_t ep_ensure_buf(infr_cuda_ctx* ctx, size_t bytes) {
   int32_t rc = ep_wait_stream(ctx, "expert parallel: buffer grow");
   if (rc) return rc;
   cudaStreamSynchronize(ep->side);
+  cudaStreamSynchronize(ep->xfer);
   if (ep->buf) cudaFree(ep->buf);
   ep->buf = nullptr;
   ep->buf_bytes = 0;
@@ -228,8 +231,14 @@ void ep_release(infr_cuda_ctx* ctx, bool orderly) {
     cudaStreamSynchronize(ep->side);
     cudaStreamDestroy(ep->side);
   }
+  if (ep->xfer) {
+    cudaStreamSynchronize(ep->xfer);
+    cudaStreamDestroy(ep->xfer);
+  }
   if (ep->ev_fork) cudaEventDestroy(ep->ev_fork);
   if (ep->ev_join) cudaEventDestroy(ep->ev_join);
+  if (ep->ev_x) cudaEventDestroy(ep->ev_x);
+  if (ep->ev_xg) cudaEventDestroy(ep->ev_xg);
   for (cudaEvent_t e : ep->ev_phase)
     if (e) cudaEventDestroy(e);
   if (ep->buf) cudaFree(ep->buf);
@@ -333,6 +342,18 @@ int32_t ep_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   }
   infr_cuda_buf b_x = view(const_cast<float*>(x_eff), x_local_b), b_rx = view(const_cast<float*>(rx_eff), x_local_b);
 
+  // dispatch, first half: the rows of every rank to every rank (slot p of the receive array = rank p's rows).
+  // Nothing of the routing goes into them, so their all-gather - the bulk of the dispatch - runs on a stream of
+  // its own beside the router; the main stream joins it before the band's experts start.
+  {
+    cudaError_t e = cudaEventRecord(ep->ev_x, main);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ep->xfer, ep->ev_x, 0);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "expert parallel: rows fork");
+    NCCL_TRY(ep->api->AllGather(x_eff, B + o_x_all, (size_t)R * ne, ncclFloat32, ep->comm, ep->xfer), "dispatch (rows)");
+    e = cudaEventRecord(ep->ev_xg, ep->xfer);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "expert parallel: rows record");
+  }
+
   // the shared expert needs nothing from the other ranks: side stream, joined before the final sum
   if (has_sh) {
     cudaError_t e = cudaEventRecord(ep->ev_fork, main);
@@ -419,13 +440,18 @@ int32_t ep_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
   }
   phase(ctx, 1);
 
-  // dispatch: rows, ids and weights of every rank to every rank (slot p of the receive arrays = rank p's rows)
+  // dispatch, second half: the rows' arrival first - two collectives of one communicator are never in flight
+  // together (on different streams they would share its channels) -, then ids and weights of every rank to
+  // every rank
+  {
+    const cudaError_t e = cudaStreamWaitEvent(main, ep->ev_xg, 0);
+    if (e != cudaSuccess) return check_cuda(ctx, e, "expert parallel: rows join");
+  }
   NCCL_TRY(ep->api->GroupStart(), "dispatch");
-  ncclResult_t r1 = ep->api->AllGather(x_eff, B + o_x_all, (size_t)R * ne, ncclFloat32, ep->comm, main);
   ncclResult_t r2 = ep->api->AllGather(b_ids.ptr, B + o_ids_all, (size_t)R * k, ncclInt32, ep->comm, main);
   ncclResult_t r3 = ep->api->AllGather(b_wts.ptr, B + o_wts_all, (size_t)R * k, ncclFloat32, ep->comm, main);
   ncclResult_t r4 = ep->api->GroupEnd();
-  for (ncclResult_t r : {r1, r2, r3, r4})
+  for (ncclResult_t r : {r2, r3, r4})
     if (r != ncclSuccess) return ep_fail(ctx, "dispatch", r);
   phase(ctx, 2);
 
@@ -522,6 +548,9 @@ int32_t infr_cuda_ep_init(infr_cuda_ctx* ctx, const uint8_t id[INFR_CUDA_EP_ID_B
   ctx->ep = ep;
   int32_t rc = INFR_CUDA_OK;
   if (cudaStreamCreateWithFlags(&ep->side, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&ep->xfer, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ep->ev_x, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ep->ev_xg, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&ep->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&ep->ev_join, cudaEventDisableTiming) != cudaSuccess ||
       cudaMalloc(reinterpret_cast<void**>(&ep->shape_dev), (size_t)world * 8 * sizeof(int32_t)) != cudaSuccess)

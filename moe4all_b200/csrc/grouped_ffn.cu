@@ -859,7 +859,7 @@ int32_t launch_grouped_ffn(infr_cuda_ctx* ctx, const GroupedCall& c) {
   p.down_q4k = c.down_q4k;
   // tcgen05 tiles with the combine behind them: the raw rows cross memory as f16 (half the bytes out of the
   // down kernel and into the combine); rows handed to the caller stay f32
-  p.y_f16 = (use_umma && c.dst != nullptr && c.y_out == nullptr && c.ne % 32 == 0) ? 1 : 0;
+  p.y_f16 = (use_umma && c.dst != nullptr && c.y_out == nullptr && c.ne % 32 == 0 && !ctx->cfg.raw_rows_f32) ? 1 : 0;
   p.y_scale = reinterpret_cast<float*>(reinterpret_cast<char*>(y) + ((size_t)rows_total + 256) * c.ne * 2);  // behind the f16 rows
   p.gate_dt = c.gate_dt;
   p.up_dt = c.up_dt;

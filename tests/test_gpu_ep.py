@@ -58,8 +58,10 @@ def worker(rank, world, port, ret, E=E):
             be_lib.set_stream(stream.cuda_stream)
             # one form of the small-m kernels on both sides (left alone, a band call over all ranks' rows and a
             # single-device call over one rank's rows may choose differently; both forms are oracle-checked elsewhere)
-            be.set_config(expert_major=2)
-            be_lib.set_config(expert_major=2)
+            # and the experts' raw rows in f32 on both (the single-device call rounds the shared expert's rows to
+            # f16 together with the routed ones, the band call computes them apart)
+            be.set_config(expert_major=2, raw_rows_f32=1)
+            be_lib.set_config(expert_major=2, raw_rows_f32=1)
             if world > 1:
                 join_communicator(be_lib)
             el = E // world
