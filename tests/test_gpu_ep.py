@@ -44,6 +44,7 @@ def worker(rank, world, port, ret, E=E):
     from moe4all_b200.ep import CudaExpertParallelLayer, LibraryExpertParallelLayer, join_communicator
 
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # a test that ends a collective early keeps off NVLink multicast
     torch.cuda.set_device(rank)
     dev = f"cuda:{rank}"
     if world > 1:
@@ -151,6 +152,7 @@ def formats_worker(rank, world, port, ret):
     from moe4all_b200.ep import LibraryExpertParallelLayer, join_communicator
 
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # a test that ends a collective early keeps off NVLink multicast
     torch.cuda.set_device(rank)
     dev = f"cuda:{rank}"
     if world > 1:
