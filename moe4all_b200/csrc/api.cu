@@ -606,10 +606,16 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     Scratch s = carve(ctx->scratch, d, true);
     RouteParams rp = route_params(ctx, d, s, true);
     const uint32_t stages = d->stages ? d->stages : 7u;
+    bool xsum_ready = false;
     if (few) {
       rp.xq_lo = s.xq_lo;
       rp.xq_hi = s.xq_hi;
       rp.xscale = s.xscale;
+      if (use_em && (stages & 1u)) {
+        // the expert-major kernels' sums of x (the first array of their scratch) come out of the same pass
+        rp.xsum = reinterpret_cast<int*>(static_cast<char*>(ctx->scratch) + sz.total + hn_bytes);
+        xsum_ready = true;
+      }
       rp.rms_w = d->norm_weight ? static_cast<const float*>(d->norm_weight->ptr) : nullptr;
       rp.rms_eps = d->norm_eps;
       if (stages & 1u) {
@@ -669,6 +675,7 @@ int32_t infr_cuda_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d) {
     dp.gate_dt = d->gate_dtype;
     dp.up_dt = d->up_dtype;
     dp.down_dt = d->down_dtype;
+    dp.xsum_ready = xsum_ready ? 1 : 0;
     dp.down_scale = d->down_scale ? static_cast<const float*>(d->down_scale->ptr) : nullptr;
     dp.act_kind = (int)d->act;
     dp.weight_before = d->weight_before ? 1 : 0;

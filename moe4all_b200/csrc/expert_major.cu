@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(1024) k_em_bucket(EmParams p, int seg_cap) {
   // sums of the fixed-point activations per 32-element sub-block (the Q4_K `min` term needs them).
   // xq_* come from the kernel before this one in the stream.
   pdl_wait();
-  {
+  if (!p.xsum_ready) {  // (the whole-row router kernels make them with the fixed-point copy)
     const int nsb = p.ne / 32, total = p.rows * nsb;
     for (int i = tid; i < total; i += 1024) {
       const int r = i / nsb, sb = i - r * nsb;
@@ -686,6 +686,7 @@ int32_t launch_em_ffn(infr_cuda_ctx* ctx, const DecodeParams& dp, void* scratch,
   p.seg_pairs = reinterpret_cast<int*>(take((PT + 8) * 4));
   p.act = reinterpret_cast<float*>(take(PT * nffmax * 4));
   p.y = reinterpret_cast<float*>(take(PT * (size_t)dp.ne * 4));
+  p.xsum_ready = dp.xsum_ready;
   p.xq_lo = dp.xq_lo;
   p.xq_hi = dp.xq_hi;
   p.xscale = dp.xscale;

@@ -31,6 +31,7 @@ struct RouteParams {
   DeviceStatus* status;      // bounded waits that ran out are recorded here
   int8_t *xq_lo, *xq_hi;     // [rows, ne] fixed-point limbs of x for the small-m expert kernels, or null
   float* xscale;             // [rows] value of one fixed-point unit
+  int* xsum;                 // [rows, ne / 32] sums of the fixed-point x per 32 elements (expert-major kernels), or null
   unsigned long long* trace; // optional phase stamps
   int rows, ne, n_expert, n_used;
   float scale;
@@ -65,6 +66,7 @@ struct DecodeParams {
   uint32_t ep_lo, ep_n;  // band (ep_n == 0: off)
   int down_q4k;          // the down banks (routed and shared) are Q4_K instead of Q6_K
   int gate_dt, up_dt, down_dt;  // INFR_CUDA_DT_* of the banks (the generic-format kernels read these)
+  int xsum_ready;        // the router kernel already made the expert-major kernels' sums of x (first array of their scratch)
   const float* down_scale;  // [n_expert] scale on a routed expert's down output, or null
   int act_kind;          // INFR_CUDA_ACT_*
   int weight_before;     // routing weight on gate and up before the activation, none on the output
@@ -77,6 +79,7 @@ struct EmParams {
   const int8_t *xq_lo, *xq_hi;   // [rows, ne] fixed-point limbs of x
   const float* xscale;           // [rows]
   int* xsum;                     // [rows, ne/32] integer sums of x per 32-element sub-block
+  int xsum_ready;                // made by the router kernel with the fixed-point copy: the bucket kernel skips them
   const int32_t* ids;            // [rows, n_used]
   const float* wts;              // [rows, n_used]
   int *n_seg, *seg_expert, *seg_off, *seg_cnt, *seg_pairs;  // segment table, built on the device
