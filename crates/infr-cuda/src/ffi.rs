@@ -30,6 +30,8 @@ pub const DT_Q4K: i32 = 12;
 pub const DT_Q6K: i32 = 14;
 pub const DT_Q8_0: i32 = 8;
 pub const DT_Q5K: i32 = 13;
+pub const DT_IQ4NL: i32 = 20;
+pub const DT_IQ4XS: i32 = 23;
 
 pub const EP_ID_BYTES: usize = 128;
 

@@ -58,12 +58,15 @@ class DType(enum.IntEnum):
     Q4K = 12
     Q5K = 13
     Q6K = 14
+    IQ4NL = 20
+    IQ4XS = 23
 
     def row_bytes(self, n_elem: int) -> int:
         """crates/infr-core/src/decode_spec.rs:315-335: elements and bytes per block."""
         if self is DType.F32:
             return n_elem * 4
-        elems, nbytes = {DType.Q8_0: (32, 34), DType.Q4K: (256, 144), DType.Q5K: (256, 176), DType.Q6K: (256, 210)}[self]
+        elems, nbytes = {DType.Q8_0: (32, 34), DType.Q4K: (256, 144), DType.Q5K: (256, 176), DType.Q6K: (256, 210),
+                         DType.IQ4NL: (32, 18), DType.IQ4XS: (256, 136)}[self]
         if n_elem % elems:
             raise ValueError(f"{self.name}: {n_elem} elements is not a whole number of {elems}-element blocks")
         return n_elem // elems * nbytes

@@ -12,6 +12,11 @@
 //   Q6_K  210 B / 256   code = 6 bits (ql | qh << 4),   A = d*sc8,  B = 0,         off = 32   (:365-400)
 //   Q8_0   34 B / 32    code = q + 128,                 A = d,      B = 0,         off = 128  (:214-223)
 //
+// and of its codebook decoder for the two 4-bit non-linear formats (dequant.rs:443-445, 499-553):
+//
+//   IQ4_NL  18 B / 32   code = kvalues[nibble] + 128,   A = d,            B = 0,   off = 128
+//   IQ4_XS 136 B / 256  code = kvalues[nibble] + 128,   A = d * (ls6 - 32), B = 0, off = 128
+//
 // The generic small-m kernels (anyfmt_ffn.cu) feed the codes to integer dot products against the
 // fixed-point activations; the generic grouped GEMM (grouped_ffn.cu) turns them into f16 operands.
 #pragma once
@@ -21,10 +26,13 @@ namespace infr {
 
 constexpr uint32_t Q5K_BLOCK_BYTES = 176;  // 256 weights: f16 d, f16 dmin, 12 B scales, 32 B high bits, 128 B nibbles
 constexpr uint32_t Q80_BLOCK_BYTES = 34;   // 32 weights: f16 d, 32 int8
+constexpr uint32_t IQ4NL_BLOCK_BYTES = 18;   // 32 weights: f16 d, 16 B nibbles (elements j and j + 16 share a byte)
+constexpr uint32_t IQ4XS_BLOCK_BYTES = 136;  // 256 weights: f16 d, u16 scale high bits, 4 B scale low nibbles, 128 B nibbles
 
 // The formats an expert bank may have.
 inline bool bank_dtype_ok(int32_t dt) {
-  return dt == INFR_CUDA_DT_Q4K || dt == INFR_CUDA_DT_Q5K || dt == INFR_CUDA_DT_Q6K || dt == INFR_CUDA_DT_Q8_0;
+  return dt == INFR_CUDA_DT_Q4K || dt == INFR_CUDA_DT_Q5K || dt == INFR_CUDA_DT_Q6K || dt == INFR_CUDA_DT_Q8_0 ||
+         dt == INFR_CUDA_DT_IQ4NL || dt == INFR_CUDA_DT_IQ4XS;
 }
 // The combination the tuned kernels (per-pair, expert-major, tcgen05) are written for.
 inline bool bank_dtypes_tuned(int32_t gate, int32_t up, int32_t down) {
@@ -49,6 +57,19 @@ __device__ __forceinline__ uint32_t ld_u32_a2(const uint8_t* p) {
   const uint32_t lo = fmt_ld<G, unsigned short>(p);
   const uint32_t hi = fmt_ld<G, unsigned short>(p + 2);
   return lo | (hi << 16);
+}
+
+// Four 4-bit indices (one per byte of n) -> the bytes kvalues_iq4nl[index] + 128 of the IQ4 codebook
+// {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113}: two byte permutes over the
+// table's halves (index bits 0-2 as the selector), the half chosen by index bit 3.
+__device__ __forceinline__ uint32_t iq4_codes(uint32_t n) {
+  const uint32_t n7 = n & 0x07070707u;
+  const uint32_t t = n7 | (n7 >> 4);                                         // nibbles: b0 b1 b1 b2 b2 b3 b3 0
+  const uint32_t sel = (t & 0xFFu) | ((t >> 4) & 0xF00u) | ((t >> 8) & 0xF000u);  // b0 b1 b2 b3
+  const uint32_t lo = __byte_perm(0x3F2D1801u, 0x766A5D4Fu, sel);            // entries 0-7  (+128)
+  const uint32_t hi = __byte_perm(0xA6998D81u, 0xF1D9C5B5u, sel);            // entries 8-15 (+128)
+  const uint32_t m = ((n >> 3) & 0x01010101u) * 0xFFu;                       // 0xFF where the index is 8-15
+  return (lo & ~m) | (hi & m);
 }
 
 // Codes and affine map of weights 16h .. 16h+15 of the row starting at `row` (G: in global memory;
@@ -98,6 +119,27 @@ __device__ __forceinline__ void fmt_codes16(int dt, const uint8_t* __restrict__ 
     A = d * (float)(int)(signed char)fmt_ld<G, uint8_t>(blk + 192 + 8 * hh + 2 * qd + (l0 >> 4));
     B = 0.f;
     off = 32;
+  } else if (dt == INFR_CUDA_DT_IQ4NL) {
+    // elements 0-15 of a block are the low nibbles of its 16 code bytes, elements 16-31 the high nibbles
+    const uint8_t* blk = row + (size_t)(h >> 1) * IQ4NL_BLOCK_BYTES;
+    const int sh = 4 * (h & 1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[i] = iq4_codes((ld_u32_a2<G>(blk + 2 + 4 * i) >> sh) & 0x0F0F0F0Fu);
+    A = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk));
+    B = 0.f;
+    off = 128;
+  } else if (dt == INFR_CUDA_DT_IQ4XS) {
+    // sub-block ib (32 elements) = 16 code bytes at 8 + 16 ib, low nibbles first; its 6-bit scale: low
+    // four bits in scales_l (a nibble per sub-block), high two in scales_h
+    const uint8_t* blk = row + (size_t)(h >> 4) * IQ4XS_BLOCK_BYTES;  // 8-byte aligned
+    const int e = (h & 15) * 16, ib = e >> 5, sh = 4 * ((e >> 4) & 1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[i] = iq4_codes((fmt_ld<G, uint32_t>(blk + 8 + 16 * ib + 4 * i) >> sh) & 0x0F0F0F0Fu);
+    const uint32_t hdr = fmt_ld<G, uint32_t>(blk), sl = fmt_ld<G, uint32_t>(blk + 4);  // d | scales_h << 16, scales_l
+    const int ls = (int)(((sl >> (4 * ib)) & 0xFu) | ((((hdr >> 16) >> (2 * ib)) & 3u) << 4));
+    A = f16_bits_to_f32(hdr) * (float)(ls - 32);
+    B = 0.f;
+    off = 128;
   } else {  // Q8_0
     const uint8_t* blk = row + (size_t)(h >> 1) * Q80_BLOCK_BYTES;
     const uint8_t* q = blk + 2 + 16 * (h & 1);

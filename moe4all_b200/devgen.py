@@ -24,11 +24,12 @@ def q6k_bank(n_blocks: int, gen, device) -> torch.Tensor:
 
 
 # GGUF type number -> (elements per block, bytes per block, offsets of the f16 scale slots, scale factor)
-BLOCKS = {12: (256, 144, (0, 2), 1.0), 13: (256, 176, (0, 2), 1.0), 14: (256, 210, (208,), 1.0), 8: (32, 34, (0,), 2.0)}
+BLOCKS = {12: (256, 144, (0, 2), 1.0), 13: (256, 176, (0, 2), 1.0), 14: (256, 210, (208,), 1.0), 8: (32, 34, (0,), 2.0),
+          20: (32, 18, (0,), 2.0), 23: (256, 136, (0,), 1.0)}
 
 
 def bank(dtype: int, n_elem: int, gen, device) -> torch.Tensor:
-    """Random blocks of GGUF type `dtype` (12 Q4_K, 13 Q5_K, 14 Q6_K, 8 Q8_0) holding n_elem weights."""
+    """Random blocks of GGUF type `dtype` (12 Q4_K, 13 Q5_K, 14 Q6_K, 8 Q8_0, 20 IQ4_NL, 23 IQ4_XS) holding n_elem weights."""
     if dtype == 12:
         return q4k_bank(n_elem // 256, gen, device)
     if dtype == 14:

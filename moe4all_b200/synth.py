@@ -14,7 +14,8 @@ import numpy as np
 Q4K_BYTES, Q6K_BYTES, QK = 144, 210, 256
 Q5K_BYTES, Q80_BYTES = 176, 34
 # GGUF type number -> (elements per block, bytes per block, offsets of the f16 scale slots)
-BLOCKS = {12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,)), 8: (32, 34, (0,))}
+BLOCKS = {12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,)), 8: (32, 34, (0,)),
+          20: (32, 18, (0,)), 23: (256, 136, (0,))}
 
 
 def _f16_bytes(vals: np.ndarray) -> np.ndarray:
@@ -37,7 +38,7 @@ def random_q6k(rng: np.random.Generator, n_blocks: int, lo: float = 1e-4, hi: fl
 
 
 def random_blocks(rng: np.random.Generator, dtype: int, n_elem: int, lo: float = 1e-4, hi: float = 1e-3) -> np.ndarray:
-    """[n_blocks, block bytes] u8 of GGUF type `dtype` (12 Q4_K, 13 Q5_K, 14 Q6_K, 8 Q8_0): random payload,
+    """[n_blocks, block bytes] u8 of GGUF type `dtype` (12 Q4_K, 13 Q5_K, 14 Q6_K, 8 Q8_0, 20 IQ4_NL, 23 IQ4_XS): random payload,
     every f16 scale slot ~ U[lo, hi]."""
     elems, nbytes, slots = BLOCKS[dtype]
     n_blocks = n_elem // elems
@@ -64,16 +65,16 @@ def gen_f32(n: int, salt: int) -> np.ndarray:
 
 
 def testkit_weight(dtype_name: str, n_elem: int, seed: int) -> np.ndarray:
-    """crates/infr-testkit/src/lib.rs:74-123 for Q4_K and Q5_K (d 0.05, dmin 0.10), Q6_K (d 0.03) and
-    Q8_0 (d 0.01)."""
-    if dtype_name in ("Q5K", "Q8_0"):
-        elems, nbytes, slots = BLOCKS[13 if dtype_name == "Q5K" else 8]
+    """crates/infr-testkit/src/lib.rs:74-123 for Q4_K and Q5_K (d 0.05, dmin 0.10), Q6_K (d 0.03),
+    Q8_0 (d 0.01), IQ4_NL (d 0.004) and IQ4_XS (d 0.06)."""
+    if dtype_name in ("Q5K", "Q8_0", "IQ4NL", "IQ4XS"):
+        elems, nbytes, slots = BLOCKS[{"Q5K": 13, "Q8_0": 8, "IQ4NL": 20, "IQ4XS": 23}[dtype_name]]
         assert n_elem % elems == 0
         nblk = n_elem // elems
         out = np.empty((nblk, nbytes), np.uint8)
         for b in range(nblk):
             out[b] = lcg_bytes(seed ^ b, nbytes)
-        for o, v in zip(slots, (0.05, 0.10) if dtype_name == "Q5K" else (0.01,)):
+        for o, v in zip(slots, {"Q5K": (0.05, 0.10), "Q8_0": (0.01,), "IQ4NL": (0.004,), "IQ4XS": (0.06,)}[dtype_name]):
             out[:, o:o + 2] = _f16_bytes(np.full(nblk, v))
         return out
     assert n_elem % QK == 0
@@ -118,7 +119,7 @@ def make_layer(seed: int, ne: int, n_expert: int, n_ff: int, sh_ff: int = 0, gat
         L.gate_dtype, L.up_dtype, L.down_dtype = dtypes
 
         def bank(dt, n_elem):
-            k = 2.0 if dt == 8 else 1.0
+            k = 2.0 if dt in (8, 20) else 1.0
             return random_blocks(rng, dt, n_elem, 1e-4 * k, 1e-3 * k).reshape(-1)
         L.gate, L.up, L.down = bank(dtypes[0], n_expert * n_ff * ne), bank(dtypes[1], n_expert * n_ff * ne), bank(dtypes[2], n_expert * ne * n_ff)
         if sh_ff:

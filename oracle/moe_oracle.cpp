@@ -39,7 +39,7 @@
 namespace {
 
 // dtype ids follow the public GGUF/ggml numbering.
-enum : int { DT_F32 = 0, DT_Q8_0 = 8, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14 };
+enum : int { DT_F32 = 0, DT_Q8_0 = 8, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14, DT_IQ4NL = 20, DT_IQ4XS = 23 };
 
 // IEEE binary16 → binary32, exact (what `half::f16::to_f32` does; dequant.rs:72-74).
 inline float f16_to_f32(uint16_t h) {
@@ -176,9 +176,42 @@ void dequant_q80_block(const uint8_t* blk, float* out) {
   }
 }
 
+// The 16-entry signed codebook of the two non-linear 4-bit formats (dequant.rs:443-445).
+const int8_t KV_IQ4NL[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+// One IQ4_NL block (18 B -> 32 f32), dequant.rs:499-517: y[j] = d * kv[qs[j] & 0xF], y[j + 16] = d * kv[qs[j] >> 4].
+void dequant_iq4nl_block(const uint8_t* blk, float* out) {
+  const float d = f16_to_f32(rd16(blk));
+  const uint8_t* qs = blk + 2;
+  for (int j = 0; j < 16; ++j) {
+    out[j] = d * (float)KV_IQ4NL[qs[j] & 0xF];
+    out[j + 16] = d * (float)KV_IQ4NL[qs[j] >> 4];
+  }
+}
+
+// One IQ4_XS block (136 B -> 256 f32), dequant.rs:521-553: eight sub-blocks of 32 with a 6-bit scale
+// ls (low four bits in scales_l, high two in scales_h); dl = d * (ls - 32); codes as in IQ4_NL.
+void dequant_iq4xs_block(const uint8_t* blk, float* out) {
+  const float d = f16_to_f32(rd16(blk));
+  const uint32_t scales_h = rd16(blk + 2);
+  const uint8_t* scales_l = blk + 4;
+  const uint8_t* qs = blk + 8;
+  for (int ib = 0; ib < 8; ++ib) {
+    const uint32_t lo = (uint32_t)(scales_l[ib / 2] >> (4 * (ib % 2))) & 0xFu;
+    const uint32_t hi = (scales_h >> (2 * ib)) & 3u;
+    const float dl = d * (float)((int)(lo | (hi << 4)) - 32);
+    for (int j = 0; j < 16; ++j) {
+      out[ib * 32 + j] = dl * (float)KV_IQ4NL[qs[ib * 16 + j] & 0xF];
+      out[ib * 32 + j + 16] = dl * (float)KV_IQ4NL[qs[ib * 16 + j] >> 4];
+    }
+  }
+}
+
 size_t row_bytes(int dtype, size_t n_elem) {
   switch (dtype) {
     case DT_F32: return n_elem * 4;
+    case DT_IQ4NL: return n_elem / 32 * 18;
+    case DT_IQ4XS: return n_elem / 256 * 136;
     case DT_Q8_0: return n_elem / 32 * 34;
     case DT_Q4K: return n_elem / 256 * 144;
     case DT_Q5K: return n_elem / 256 * 176;
@@ -208,6 +241,14 @@ bool dequant_row(int dtype, const uint8_t* bytes, size_t n_elem, float* out) {
     case DT_Q8_0:
       if (n_elem % 32) return false;
       for (size_t b = 0; b < n_elem / 32; ++b) dequant_q80_block(bytes + b * 34, out + b * 32);
+      return true;
+    case DT_IQ4NL:
+      if (n_elem % 32) return false;
+      for (size_t b = 0; b < n_elem / 32; ++b) dequant_iq4nl_block(bytes + b * 18, out + b * 32);
+      return true;
+    case DT_IQ4XS:
+      if (n_elem % 256) return false;
+      for (size_t b = 0; b < n_elem / 256; ++b) dequant_iq4xs_block(bytes + b * 136, out + b * 256);
       return true;
     default:
       return false;

@@ -13,8 +13,9 @@ from helpers import GpuLayer, assert_close, near_tie_rows, oracle_layer
 
 pytestmark = pytest.mark.gpu
 
-Q8_0, Q4K, Q5K, Q6K = 8, 12, 13, 14
-MIXES = [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0), (Q5K, Q5K, Q5K), (Q4K, Q5K, Q8_0), (Q6K, Q6K, Q4K), (Q8_0, Q4K, Q6K)]
+Q8_0, Q4K, Q5K, Q6K, IQ4NL, IQ4XS = 8, 12, 13, 14, 20, 23
+MIXES = [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0), (Q5K, Q5K, Q5K), (Q4K, Q5K, Q8_0), (Q6K, Q6K, Q4K), (Q8_0, Q4K, Q6K),
+         (IQ4XS, IQ4XS, Q6K), (IQ4NL, IQ4NL, IQ4NL), (IQ4XS, IQ4NL, IQ4XS)]
 
 
 def check(out, ids, ref, n_used):
@@ -37,7 +38,7 @@ def test_format_mix_matches_oracle(backend, mix, rows, path):
     check(out, ids, oracle_layer(L, x, 4), 4)
 
 
-@pytest.mark.parametrize("mix", [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0)])
+@pytest.mark.parametrize("mix", [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0), (IQ4XS, IQ4XS, Q6K)])
 def test_config1_shape(backend, mix):
     # hidden 2048, 256 experts top-8, intermediate 512, gated shared expert: decode rows and a batched call
     L = synth.make_layer(5, 2048, 256, 512, sh_ff=512, dtypes=mix)
@@ -50,7 +51,7 @@ def test_config1_shape(backend, mix):
         check(out[sel], ids[sel], ref, 8)
 
 
-@pytest.mark.parametrize("mix", [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0)])
+@pytest.mark.parametrize("mix", [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0), (IQ4XS, IQ4XS, IQ4NL)])
 def test_variants_and_bands(backend, mix):
     L = synth.make_layer(77, 512, 16, 256, sh_ff=256, router_std=0.05, dtypes=mix)
     g = GpuLayer(backend, L)
@@ -67,7 +68,8 @@ def test_variants_and_bands(backend, mix):
         assert_close(parts[0] + parts[1], full)
 
 
-@pytest.mark.parametrize("dt,name,in_f,out_f", [(Q5K, "Q5K", 512, 64), (Q8_0, "Q8_0", 512, 64), (Q8_0, "Q8_0", 96, 40)])
+@pytest.mark.parametrize("dt,name,in_f,out_f", [(Q5K, "Q5K", 512, 64), (Q8_0, "Q8_0", 512, 64), (Q8_0, "Q8_0", 96, 40),
+                                                (IQ4XS, "IQ4XS", 512, 64), (IQ4NL, "IQ4NL", 160, 24)])
 def test_linear_op(backend, dt, name, in_f, out_f):
     # Op::Linear on the reference's synthesised weights (crates/infr-testkit/src/lib.rs:74-123); Q8_0 rows
     # need whole 32-weight blocks only
@@ -90,5 +92,5 @@ def test_unknown_format_refused(backend):
     L.gate_dtype = 0  # F32 banks: not covered
     with pytest.raises(BackendError) as e:
         g.run(synth.activations(1, 1, 256), 2)
-    assert "Q4_K, Q5_K, Q6_K or Q8_0" in str(e.value)
+    assert "Q4_K, Q5_K, Q6_K, Q8_0, IQ4_NL or IQ4_XS" in str(e.value)
     L.gate_dtype = 12

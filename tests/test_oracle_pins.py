@@ -198,6 +198,64 @@ def test_q80_by_hand():
     assert orc.row_bytes(orc.DT_Q8_0, 2048) == 2176 and orc.row_bytes(orc.DT_Q5K, 2048) == 1408
 
 
+KV_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.float32)  # dequant.rs:443-445
+
+
+def np_iq4nl(raw):
+    """dequant.rs:499-517: y[j] = d * kv[qs[j] & 0xF], y[j + 16] = d * kv[qs[j] >> 4]."""
+    raw = np.asarray(raw, np.uint8).reshape(-1, 18)
+    out = np.empty((raw.shape[0], 32), F32)
+    for bi, blk in enumerate(raw):
+        d = f16(int(blk[0]), int(blk[1]))
+        qs = blk[2:18].astype(np.int64)
+        out[bi, :16] = F32(d) * KV_IQ4NL[qs & 0xF]
+        out[bi, 16:] = F32(d) * KV_IQ4NL[qs >> 4]
+    return out.reshape(-1)
+
+
+def np_iq4xs(raw):
+    """dequant.rs:521-553: sub-block scale ls = scales_l nibble | scales_h two bits << 4; dl = d * (ls - 32)."""
+    raw = np.asarray(raw, np.uint8).reshape(-1, 136)
+    out = np.empty((raw.shape[0], 256), F32)
+    for bi, blk in enumerate(raw):
+        d = f16(int(blk[0]), int(blk[1]))
+        sh = int(blk[2]) | (int(blk[3]) << 8)
+        for ib in range(8):
+            ls = ((int(blk[4 + ib // 2]) >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)
+            dl = F32(F32(d) * F32(ls - 32))
+            qs = blk[8 + 16 * ib: 24 + 16 * ib].astype(np.int64)
+            out[bi, 32 * ib: 32 * ib + 16] = dl * KV_IQ4NL[qs & 0xF]
+            out[bi, 32 * ib + 16: 32 * ib + 32] = dl * KV_IQ4NL[qs >> 4]
+    return out.reshape(-1)
+
+
+def test_iq4_reference_vectors():
+    # crates/infr-gguf/src/dequant.rs `iq4nl_single_block`: d = 1, qs[0] = 0x80 -> y[0] = kv[0] = -127, y[16] = kv[8] = 1
+    blk = np.zeros(18, np.uint8)
+    blk[0:2] = np.array([1.0], np.float16).view(np.uint8)
+    blk[2] = 0x80
+    y = orc.dequant(orc.DT_IQ4NL, blk, 32)
+    assert y[0] == -127.0 and y[16] == 1.0
+    assert np.all(y[1:16] == -127.0) and np.all(y[17:] == -127.0)  # the other code bytes are 0: kv[0] both ways
+    # `iq4xs` single block: d = 1, everything else 0 -> ls = 0, dl = -32, every code kv[0] = -127: all 4064
+    blk = np.zeros(136, np.uint8)
+    blk[0:2] = np.array([1.0], np.float16).view(np.uint8)
+    y = orc.dequant(orc.DT_IQ4XS, blk, 256)
+    assert np.all(y == 4064.0)
+    assert orc.row_bytes(orc.DT_IQ4NL, 2048) == 1152 and orc.row_bytes(orc.DT_IQ4XS, 2048) == 1088
+
+
+@pytest.mark.parametrize("dt,name,elems,ref", [(orc.DT_IQ4NL, "IQ4NL", 32, np_iq4nl), (orc.DT_IQ4XS, "IQ4XS", 256, np_iq4xs)])
+def test_iq4_blocks_match_numpy_decoder(dt, name, elems, ref):
+    # the reference's synthesis recipe (LCG payload, d slot set: crates/infr-testkit/src/lib.rs:74-123) and random payloads
+    raw = synth.testkit_weight(name, 1024, seed=0x9876)
+    got = orc.dequant(dt, raw, 1024)
+    assert np.array_equal(got.view(np.uint32), ref(raw).view(np.uint32))
+    assert np.all(np.isfinite(got)) and np.ptp(got) > 0
+    rb = synth.random_blocks(np.random.default_rng(11), dt, 4096)
+    assert np.array_equal(orc.dequant(dt, rb, 4096).view(np.uint32), ref(rb).view(np.uint32))
+
+
 def test_ragged_block_count_rejected():
     with pytest.raises(ValueError):
         orc.dequant(orc.DT_Q4K, np.zeros(144, np.uint8), 100)
