@@ -156,10 +156,15 @@ fn moe_sqrt_softplus_and_q4k_down() {
 }
 
 /// Other bank formats real files mix in (`crates/infr-core/src/tensor.rs:172-196`): Q5_K gate/up with a
-/// Q6_K down bank, and Q8_0 throughout, on the small-m kernels and on the grouped GEMM tiles.
+/// Q6_K down bank, Q8_0 throughout, and the two non-linear 4-bit formats, on the small-m kernels and on the
+/// grouped GEMM tiles.
 #[test]
 fn moe_q5k_and_q8_0_banks() {
-    for (gu, down, name) in [(DType::Q5K, DType::Q6K, "Q5_K / Q6_K"), (DType::Q8_0, DType::Q8_0, "Q8_0")] {
+    for (gu, down, name) in [
+        (DType::Q5K, DType::Q6K, "Q5_K / Q6_K"),
+        (DType::Q8_0, DType::Q8_0, "Q8_0"),
+        (DType::Iq4Xs, DType::Iq4Nl, "IQ4_XS / IQ4_NL"),
+    ] {
         for rows in [1usize, 4, 96] {
             check(
                 Case { rows, ne: 512, n_expert: 16, n_used: 4, n_ff: 256, gating: MoeGating::Softmax, groups: (0, 0), bias: false, down, gu },
