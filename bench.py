@@ -45,8 +45,9 @@ Q4K_ROW = NE // 256 * 144      # bytes of one gate/up row
 Q6K_ROW = N_FF // 256 * 210    # bytes of one down row
 EXPERT_BYTES = 2 * N_FF * Q4K_ROW + NE * Q6K_ROW  # 2 039 808
 # --banks: GGUF type numbers and (elements, bytes) per block of the formats an expert bank may have
-BANK_TYPES = {"q8_0": 8, "q4k": 12, "q5k": 13, "q6k": 14, "iq4_nl": 20, "iq4_xs": 23}
-BANK_BLOCK = {8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210), 20: (32, 18), 23: (256, 136)}
+BANK_TYPES = {"q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8, "q2k": 10, "q3k": 11, "q4k": 12, "q5k": 13, "q6k": 14, "iq4_nl": 20, "iq4_xs": 23}
+BANK_BLOCK = {2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176),
+              14: (256, 210), 20: (32, 18), 23: (256, 136)}
 BANKS = (12, 12, 14)           # gate, up, down of the layer workload (set from --banks)
 
 
@@ -71,7 +72,7 @@ def banks_tuned():
 
 def banks_name():
     inv = {v: k for k, v in BANK_TYPES.items()}
-    pretty = {"q8_0": "Q8_0", "q4k": "Q4_K", "q5k": "Q5_K", "q6k": "Q6_K", "iq4_nl": "IQ4_NL", "iq4_xs": "IQ4_XS"}
+    pretty = {k: k.upper().replace("K", "_K") if k.endswith("k") else k.upper() for k in BANK_TYPES}
     g, u, d = (pretty[inv[b]] for b in BANKS)
     return f"gate/up {g}, down {d}" if g == u else f"gate {g}, up {u}, down {d}"
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each kernel of the step at
@@ -98,7 +99,7 @@ def parse_args():
                     help="prefill workload only: the 256-expert Qwen3.6-35B-A3B layer, or the DeepSeek-V3-shaped one "
                          "(hidden 7168, intermediate 2048, sigmoid gating in 8 groups / 4 used, ungated shared expert)")
     ap.add_argument("--banks", default="q4k,q4k,q6k", help="layer workload: formats of the gate, up and down banks "
-                    "(q4k, q5k, q6k, q8_0, iq4_nl, iq4_xs); the default is the configuration the metric is quoted on")
+                    "(q4_0, q4_1, q5_0, q5_1, q8_0, q2k ... q6k, iq4_nl, iq4_xs); the default is the configuration the metric is quoted on")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-subrecords", action="store_true", help="layer workload: skip the prefill and stack sub-records")

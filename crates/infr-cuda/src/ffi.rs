@@ -30,6 +30,12 @@ pub const DT_Q4K: i32 = 12;
 pub const DT_Q6K: i32 = 14;
 pub const DT_Q8_0: i32 = 8;
 pub const DT_Q5K: i32 = 13;
+pub const DT_Q4_0: i32 = 2;
+pub const DT_Q4_1: i32 = 3;
+pub const DT_Q5_0: i32 = 6;
+pub const DT_Q5_1: i32 = 7;
+pub const DT_Q2K: i32 = 10;
+pub const DT_Q3K: i32 = 11;
 pub const DT_IQ4NL: i32 = 20;
 pub const DT_IQ4XS: i32 = 23;
 

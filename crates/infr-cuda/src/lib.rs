@@ -205,6 +205,12 @@ fn dt_code(dt: DType) -> Result<i32> {
         DType::Q6K => Ok(ffi::DT_Q6K),
         DType::Q5K => Ok(ffi::DT_Q5K),
         DType::Q8_0 => Ok(ffi::DT_Q8_0),
+        DType::Q4_0 => Ok(ffi::DT_Q4_0),
+        DType::Q4_1 => Ok(ffi::DT_Q4_1),
+        DType::Q5_0 => Ok(ffi::DT_Q5_0),
+        DType::Q5_1 => Ok(ffi::DT_Q5_1),
+        DType::Q2K => Ok(ffi::DT_Q2K),
+        DType::Q3K => Ok(ffi::DT_Q3K),
         DType::Iq4Nl => Ok(ffi::DT_IQ4NL),
         DType::Iq4Xs => Ok(ffi::DT_IQ4XS),
         other => Err(Error::Unsupported(format!("infr-cuda: weight dtype {other:?} has no sm_100a kernel (F32, Q4_K, Q6_K only)"))),

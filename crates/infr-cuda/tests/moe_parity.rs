@@ -247,13 +247,13 @@ fn moe_sublayer_with_shared_expert() {
 fn unsupported_is_an_error() {
     let Some(gpu) = gpu() else { return };
     let mut g = Graph::new();
-    let x = g.input(f32d(64));
-    let w = g.weight(qd(64 * 256, DType::Q4_0));
+    let x = g.input(f32d(256));
+    let w = g.weight(qd(256 * 256, DType::Iq2S));
     let y = g.output(f32d(256));
-    g.push(Op::Linear { x, weight: w, dst: y, m: 1, in_f: 64, out_f: 256, w_off: 0 });
+    g.push(Op::Linear { x, weight: w, dst: y, m: 1, in_f: 256, out_f: 256, w_off: 0 });
     let plan = gpu.compile(&g).expect("compile");
-    let xb = gpu.alloc(256, infr_core::backend::BufferUsage::Activations).unwrap();
-    let wb = gpu.alloc(64 * 256, infr_core::backend::BufferUsage::Weights).unwrap();
+    let xb = gpu.alloc(1024, infr_core::backend::BufferUsage::Activations).unwrap();
+    let wb = gpu.alloc(256 * 82, infr_core::backend::BufferUsage::Weights).unwrap();  // 256 rows of one 82-byte IQ2_S block
     let yb = gpu.alloc(1024, infr_core::backend::BufferUsage::Readback).unwrap();
     let mut b = infr_core::backend::Bindings::new();
     b.bind(x, xb.as_ref()).bind(w, wb.as_ref()).bind(y, yb.as_ref());

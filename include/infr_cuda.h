@@ -40,6 +40,12 @@ extern "C" {
 #define INFR_CUDA_DT_Q6K 14 /* 256 weights / 210 B, crates/infr-core/src/decode_spec.rs:331 */
 #define INFR_CUDA_DT_Q8_0 8 /* 32 weights / 34 B, crates/infr-core/src/decode_spec.rs:320   */
 #define INFR_CUDA_DT_Q5K 13 /* 256 weights / 176 B, crates/infr-core/src/decode_spec.rs:329 */
+#define INFR_CUDA_DT_Q4_0 2 /* 32 weights / 18 B, crates/infr-core/src/decode_spec.rs:312   */
+#define INFR_CUDA_DT_Q4_1 3 /* 32 weights / 20 B, crates/infr-core/src/decode_spec.rs:314   */
+#define INFR_CUDA_DT_Q5_0 6 /* 32 weights / 22 B, crates/infr-core/src/decode_spec.rs:316   */
+#define INFR_CUDA_DT_Q5_1 7 /* 32 weights / 24 B, crates/infr-core/src/decode_spec.rs:318   */
+#define INFR_CUDA_DT_Q2K 10 /* 256 weights / 84 B, crates/infr-core/src/decode_spec.rs:323  */
+#define INFR_CUDA_DT_Q3K 11 /* 256 weights / 110 B, crates/infr-core/src/decode_spec.rs:325 */
 #define INFR_CUDA_DT_IQ4NL 20 /* 32 weights / 18 B, crates/infr-core/src/decode_spec.rs:349  */
 #define INFR_CUDA_DT_IQ4XS 23 /* 256 weights / 136 B, crates/infr-core/src/decode_spec.rs:351 */
 
@@ -255,7 +261,7 @@ int32_t infr_cuda_moe_route_noalloc(int32_t device, void* cuda_stream, const flo
 /* ---- the ops around it (shared expert and the 40-layer stack) --------------------------------- */
 
 /* Op::Linear (crates/infr-cpu/src/lib.rs:1275-1328): y[m, out_f] = x[m, in_f] · Wᵀ, W row-major
- * [out_f, in_f] of `dtype` (F32, Q4_K, Q5_K, Q6_K, Q8_0, IQ4_NL, IQ4_XS). */
+ * [out_f, in_f] of `dtype` (F32 or any of the block formats above). */
 int32_t infr_cuda_linear(infr_cuda_ctx* ctx, int32_t dtype, const infr_cuda_buf* w, const infr_cuda_buf* x,
                          infr_cuda_buf* y, uint32_t m, uint32_t in_f, uint32_t out_f);
 /* Op::GatedAct with Activation::Silu, contiguous operands (crates/infr-cpu/src/lib.rs:2973-3027):

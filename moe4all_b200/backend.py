@@ -54,7 +54,13 @@ class Unsupported(BackendError):
 class DType(enum.IntEnum):
     """crates/infr-core/src/tensor.rs:7-57, numbered as in the GGUF file format."""
     F32 = 0
+    Q4_0 = 2
+    Q4_1 = 3
+    Q5_0 = 6
+    Q5_1 = 7
     Q8_0 = 8
+    Q2K = 10
+    Q3K = 11
     Q4K = 12
     Q5K = 13
     Q6K = 14
@@ -66,7 +72,8 @@ class DType(enum.IntEnum):
         if self is DType.F32:
             return n_elem * 4
         elems, nbytes = {DType.Q8_0: (32, 34), DType.Q4K: (256, 144), DType.Q5K: (256, 176), DType.Q6K: (256, 210),
-                         DType.IQ4NL: (32, 18), DType.IQ4XS: (256, 136)}[self]
+                         DType.IQ4NL: (32, 18), DType.IQ4XS: (256, 136), DType.Q4_0: (32, 18), DType.Q4_1: (32, 20),
+                         DType.Q5_0: (32, 22), DType.Q5_1: (32, 24), DType.Q2K: (256, 84), DType.Q3K: (256, 110)}[self]
         if n_elem % elems:
             raise ValueError(f"{self.name}: {n_elem} elements is not a whole number of {elems}-element blocks")
         return n_elem // elems * nbytes

@@ -1,4 +1,4 @@
-// Small-m expert FFN for banks in any mix of Q4_K, Q5_K, Q6_K, Q8_0, IQ4_NL and IQ4_XS (the reference's batched and
+// Small-m expert FFN for banks in any mix of the formats formats.cuh covers (the reference's batched and
 // decode MoE kernels take gate, up and down formats independently: crates/infr-core/src/tensor.rs:172-196;
 // real files mix them, e.g. Q5_K gate/up with Q6_K down, or Q8_0 throughout).
 //

@@ -89,6 +89,12 @@ INFR_HD inline size_t row_bytes(int32_t dtype, size_t n_elem) {
     case INFR_CUDA_DT_Q5K: return n_elem / 256 * 176;
     case INFR_CUDA_DT_Q6K: return n_elem / 256 * 210;
     case INFR_CUDA_DT_Q8_0: return n_elem / 32 * 34;
+    case INFR_CUDA_DT_Q4_0: return n_elem / 32 * 18;
+    case INFR_CUDA_DT_Q4_1: return n_elem / 32 * 20;
+    case INFR_CUDA_DT_Q5_0: return n_elem / 32 * 22;
+    case INFR_CUDA_DT_Q5_1: return n_elem / 32 * 24;
+    case INFR_CUDA_DT_Q2K: return n_elem / 256 * 84;
+    case INFR_CUDA_DT_Q3K: return n_elem / 256 * 110;
     case INFR_CUDA_DT_IQ4NL: return n_elem / 32 * 18;
     case INFR_CUDA_DT_IQ4XS: return n_elem / 256 * 136;
     default: return 0;

@@ -238,11 +238,17 @@ int32_t launch_linear(infr_cuda_ctx* ctx, int32_t dtype, const uint8_t* w, const
     case INFR_CUDA_DT_Q6K: k_linear<INFR_CUDA_DT_Q6K><<<grid, block, 0, ctx->stream>>>(w, x, y, m, in_f, out_f, wb); break;
     case INFR_CUDA_DT_Q5K:
     case INFR_CUDA_DT_Q8_0:
+    case INFR_CUDA_DT_Q4_0:
+    case INFR_CUDA_DT_Q4_1:
+    case INFR_CUDA_DT_Q5_0:
+    case INFR_CUDA_DT_Q5_1:
+    case INFR_CUDA_DT_Q2K:
+    case INFR_CUDA_DT_Q3K:
     case INFR_CUDA_DT_IQ4NL:
     case INFR_CUDA_DT_IQ4XS:
       k_linear_anyfmt<<<grid, block, 0, ctx->stream>>>(dtype, w, x, y, in_f, out_f, row_bytes(dtype, in_f));
       break;
-    default: return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32, Q4_K, Q5_K, Q6_K, Q8_0, IQ4_NL, IQ4_XS)");
+    default: return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32 and the block formats an expert bank may have)");
   }
   ctx->launches += 1;
   return check_cuda(ctx, cudaGetLastError(), "k_linear launch");

@@ -11,6 +11,12 @@
 //   Q5_K  176 B / 256   code = nibble | high bit << 4,  A = d*sc6,  B = -dmin*m6,  off = 0    (:337-362)
 //   Q6_K  210 B / 256   code = 6 bits (ql | qh << 4),   A = d*sc8,  B = 0,         off = 32   (:365-400)
 //   Q8_0   34 B / 32    code = q + 128,                 A = d,      B = 0,         off = 128  (:214-223)
+//   Q4_0   18 B / 32    code = nibble,                  A = d,      B = 0,         off = 8    (:142-158)
+//   Q4_1   20 B / 32    code = nibble,                  A = d,      B = m,         off = 0    (:159-175)
+//   Q5_0   22 B / 32    code = nibble | high bit << 4,  A = d,      B = 0,         off = 16   (:176-194)
+//   Q5_1   24 B / 32    code = nibble | high bit << 4,  A = d,      B = m,         off = 0    (:195-212)
+//   Q2_K   84 B / 256   code = 2 bits,                  A = d*sc4,  B = -dmin*m4,  off = 0    (:224-252; per 16)
+//   Q3_K  110 B / 256   code = 2 bits | high bit << 2,  A = d*(sc6 - 32), B = 0,   off = 4    (:253-314; per 16)
 //
 // and of its codebook decoder for the two 4-bit non-linear formats (dequant.rs:443-445, 499-553):
 //
@@ -31,8 +37,14 @@ constexpr uint32_t IQ4XS_BLOCK_BYTES = 136;  // 256 weights: f16 d, u16 scale hi
 
 // The formats an expert bank may have.
 inline bool bank_dtype_ok(int32_t dt) {
-  return dt == INFR_CUDA_DT_Q4K || dt == INFR_CUDA_DT_Q5K || dt == INFR_CUDA_DT_Q6K || dt == INFR_CUDA_DT_Q8_0 ||
-         dt == INFR_CUDA_DT_IQ4NL || dt == INFR_CUDA_DT_IQ4XS;
+  switch (dt) {
+    case INFR_CUDA_DT_Q4_0: case INFR_CUDA_DT_Q4_1: case INFR_CUDA_DT_Q5_0: case INFR_CUDA_DT_Q5_1: case INFR_CUDA_DT_Q8_0:
+    case INFR_CUDA_DT_Q2K: case INFR_CUDA_DT_Q3K: case INFR_CUDA_DT_Q4K: case INFR_CUDA_DT_Q5K: case INFR_CUDA_DT_Q6K:
+    case INFR_CUDA_DT_IQ4NL: case INFR_CUDA_DT_IQ4XS:
+      return true;
+    default:
+      return false;
+  }
 }
 // The combination the tuned kernels (per-pair, expert-major, tcgen05) are written for.
 inline bool bank_dtypes_tuned(int32_t gate, int32_t up, int32_t down) {
@@ -119,6 +131,53 @@ __device__ __forceinline__ void fmt_codes16(int dt, const uint8_t* __restrict__ 
     A = d * (float)(int)(signed char)fmt_ld<G, uint8_t>(blk + 192 + 8 * hh + 2 * qd + (l0 >> 4));
     B = 0.f;
     off = 32;
+  } else if (dt == INFR_CUDA_DT_Q4_0 || dt == INFR_CUDA_DT_Q4_1 || dt == INFR_CUDA_DT_Q5_0 || dt == INFR_CUDA_DT_Q5_1) {
+    // 32-weight blocks: f16 d (and f16 m for the _1 forms), for the 5-bit forms 32 high bits, then 16 code
+    // bytes whose low nibbles are elements 0-15 and high nibbles elements 16-31
+    const bool has_m = dt == INFR_CUDA_DT_Q4_1 || dt == INFR_CUDA_DT_Q5_1, five = dt == INFR_CUDA_DT_Q5_0 || dt == INFR_CUDA_DT_Q5_1;
+    const int hdr = has_m ? 4 : 2, bb = 16 + hdr + (five ? 4 : 0), half = h & 1;
+    const uint8_t* blk = row + (size_t)(h >> 1) * bb;
+    const uint8_t* qs = blk + hdr + (five ? 4 : 0);
+    const uint32_t qh = five ? (ld_u32_a2<G>(blk + hdr) >> (16 * half)) : 0u;  // bit j: element 16 half + j
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      c[i] = (ld_u32_a2<G>(qs + 4 * i) >> (4 * half)) & 0x0F0F0F0Fu;
+      if (five) {
+        const uint32_t b4 = (qh >> (4 * i)) & 0xFu;  // the high bits of elements 4 i .. 4 i + 3
+        c[i] |= ((b4 & 1u) << 4) | ((b4 & 2u) << 11) | ((b4 & 4u) << 18) | ((b4 & 8u) << 25);
+      }
+    }
+    A = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk));
+    B = has_m ? f16_bits_to_f32(fmt_ld<G, unsigned short>(blk + 2)) : 0.f;
+    off = has_m ? 0 : (five ? 16 : 8);
+  } else if (dt == INFR_CUDA_DT_Q2K || dt == INFR_CUDA_DT_Q3K) {
+    // 16 elements = group (n, j, half) of the block: 16 code bytes at 32 n + 16 half, two bits each at bit 2 j;
+    // Q3_K adds bit 4 n + j of hmask[16 half + l]; one scale (and min) per 16 elements
+    const bool q3 = dt == INFR_CUDA_DT_Q3K;
+    const uint8_t* blk = row + (size_t)(h >> 4) * (q3 ? 110 : 84);
+    const int h16 = h & 15, n = h16 >> 3, j = (h16 >> 1) & 3, half = h16 & 1;
+    const uint8_t* qs = blk + (q3 ? 32 : 16) + 32 * n + 16 * half;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      c[i] = (ld_u32_a2<G>(qs + 4 * i) >> (2 * j)) & 0x03030303u;
+      if (q3) c[i] |= ((ld_u32_a2<G>(blk + 16 * half + 4 * i) >> (4 * n + j)) & 0x01010101u) << 2;
+    }
+    if (q3) {
+      // sixteen 6-bit scales in 12 bytes: low nibbles of bytes 0-7 (scales 0-7: low, 8-15: high nibble),
+      // two more bits each in bytes 8-11
+      const uint32_t a = ld_u32_a2<G>(blk + 96 + 4 * ((h16 >> 2) & 1)), tmp = ld_u32_a2<G>(blk + 104);
+      const uint32_t lo4 = (h16 < 8 ? a : (a >> 4)) & 0x0F0F0F0Fu;
+      const uint32_t hi2 = ((tmp >> (2 * (h16 >> 2))) & 0x03030303u) << 4;
+      const int sc = (int)(((lo4 | hi2) >> (8 * (h16 & 3))) & 0xFFu) - 32;
+      A = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk + 108)) * (float)sc;
+      B = 0.f;
+      off = 4;
+    } else {
+      const uint32_t sc = fmt_ld<G, uint8_t>(blk + h16);
+      A = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk + 80)) * (float)(sc & 0xFu);
+      B = -(f16_bits_to_f32(fmt_ld<G, unsigned short>(blk + 82)) * (float)(sc >> 4));
+      off = 0;
+    }
   } else if (dt == INFR_CUDA_DT_IQ4NL) {
     // elements 0-15 of a block are the low nibbles of its 16 code bytes, elements 16-31 the high nibbles
     const uint8_t* blk = row + (size_t)(h >> 1) * IQ4NL_BLOCK_BYTES;

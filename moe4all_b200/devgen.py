@@ -25,7 +25,8 @@ def q6k_bank(n_blocks: int, gen, device) -> torch.Tensor:
 
 # GGUF type number -> (elements per block, bytes per block, offsets of the f16 scale slots, scale factor)
 BLOCKS = {12: (256, 144, (0, 2), 1.0), 13: (256, 176, (0, 2), 1.0), 14: (256, 210, (208,), 1.0), 8: (32, 34, (0,), 2.0),
-          20: (32, 18, (0,), 2.0), 23: (256, 136, (0,), 1.0)}
+          20: (32, 18, (0,), 2.0), 23: (256, 136, (0,), 1.0), 2: (32, 18, (0,), 32.0), 3: (32, 20, (0, 2), 32.0), 6: (32, 22, (0,), 16.0),
+          7: (32, 24, (0, 2), 16.0), 10: (256, 84, (80, 82), 64.0), 11: (256, 110, (108,), 8.0)}
 
 
 def bank(dtype: int, n_elem: int, gen, device) -> torch.Tensor:

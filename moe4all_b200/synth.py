@@ -15,7 +15,8 @@ Q4K_BYTES, Q6K_BYTES, QK = 144, 210, 256
 Q5K_BYTES, Q80_BYTES = 176, 34
 # GGUF type number -> (elements per block, bytes per block, offsets of the f16 scale slots)
 BLOCKS = {12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,)), 8: (32, 34, (0,)),
-          20: (32, 18, (0,)), 23: (256, 136, (0,))}
+          20: (32, 18, (0,)), 23: (256, 136, (0,)), 2: (32, 18, (0,)), 3: (32, 20, (0, 2)), 6: (32, 22, (0,)), 7: (32, 24, (0, 2)),
+          10: (256, 84, (80, 82)), 11: (256, 110, (108,))}
 
 
 def _f16_bytes(vals: np.ndarray) -> np.ndarray:
@@ -66,15 +67,18 @@ def gen_f32(n: int, salt: int) -> np.ndarray:
 
 def testkit_weight(dtype_name: str, n_elem: int, seed: int) -> np.ndarray:
     """crates/infr-testkit/src/lib.rs:74-123 for Q4_K and Q5_K (d 0.05, dmin 0.10), Q6_K (d 0.03),
-    Q8_0 (d 0.01), IQ4_NL (d 0.004) and IQ4_XS (d 0.06)."""
-    if dtype_name in ("Q5K", "Q8_0", "IQ4NL", "IQ4XS"):
-        elems, nbytes, slots = BLOCKS[{"Q5K": 13, "Q8_0": 8, "IQ4NL": 20, "IQ4XS": 23}[dtype_name]]
+    Q8_0 (d 0.01), IQ4_NL (d 0.004), IQ4_XS (d 0.06), Q4_0 / Q5_0 (d 0.04), Q4_1 / Q5_1 (d 0.04, m -0.30),
+    Q2_K (d 0.05, dmin 0.10) and Q3_K (d 0.03)."""
+    TK = {"Q5K": (13, (0.05, 0.10)), "Q8_0": (8, (0.01,)), "IQ4NL": (20, (0.004,)), "IQ4XS": (23, (0.06,)), "Q4_0": (2, (0.04,)),
+          "Q4_1": (3, (0.04, -0.30)), "Q5_0": (6, (0.04,)), "Q5_1": (7, (0.04, -0.30)), "Q2K": (10, (0.05, 0.10)), "Q3K": (11, (0.03,))}
+    if dtype_name in TK:
+        elems, nbytes, slots = BLOCKS[TK[dtype_name][0]]
         assert n_elem % elems == 0
         nblk = n_elem // elems
         out = np.empty((nblk, nbytes), np.uint8)
         for b in range(nblk):
             out[b] = lcg_bytes(seed ^ b, nbytes)
-        for o, v in zip(slots, {"Q5K": (0.05, 0.10), "Q8_0": (0.01,), "IQ4NL": (0.004,), "IQ4XS": (0.06,)}[dtype_name]):
+        for o, v in zip(slots, TK[dtype_name][1]):
             out[:, o:o + 2] = _f16_bytes(np.full(nblk, v))
         return out
     assert n_elem % QK == 0
@@ -119,7 +123,7 @@ def make_layer(seed: int, ne: int, n_expert: int, n_ff: int, sh_ff: int = 0, gat
         L.gate_dtype, L.up_dtype, L.down_dtype = dtypes
 
         def bank(dt, n_elem):
-            k = 2.0 if dt in (8, 20) else 1.0
+            k = {8: 2.0, 20: 2.0, 2: 32.0, 3: 32.0, 6: 16.0, 7: 16.0, 10: 64.0, 11: 8.0}.get(dt, 1.0)  # similar weight magnitudes
             return random_blocks(rng, dt, n_elem, 1e-4 * k, 1e-3 * k).reshape(-1)
         L.gate, L.up, L.down = bank(dtypes[0], n_expert * n_ff * ne), bank(dtypes[1], n_expert * n_ff * ne), bank(dtypes[2], n_expert * ne * n_ff)
         if sh_ff:

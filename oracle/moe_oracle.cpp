@@ -39,7 +39,7 @@
 namespace {
 
 // dtype ids follow the public GGUF/ggml numbering.
-enum : int { DT_F32 = 0, DT_Q8_0 = 8, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14, DT_IQ4NL = 20, DT_IQ4XS = 23 };
+enum : int { DT_F32 = 0, DT_Q4_0 = 2, DT_Q4_1 = 3, DT_Q5_0 = 6, DT_Q5_1 = 7, DT_Q8_0 = 8, DT_Q2K = 10, DT_Q3K = 11, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14, DT_IQ4NL = 20, DT_IQ4XS = 23 };
 
 // IEEE binary16 → binary32, exact (what `half::f16::to_f32` does; dequant.rs:72-74).
 inline float f16_to_f32(uint16_t h) {
@@ -176,6 +176,75 @@ void dequant_q80_block(const uint8_t* blk, float* out) {
   }
 }
 
+// The legacy 32-weight formats (dequant.rs:142-212), factored as code, (sc, m) = (1, k) on (d, d or m), expanded
+// as everywhere (dequant.rs:35-51): out = (f32(d) * sc) * code + (f32(d or m) * m).
+//   Q4_0: d, 16 code bytes; m = -8.     Q4_1: d, m, 16 code bytes; m-factor 1 on the block's own m.
+//   Q5_0: d, 32 high bits, 16 code bytes; m = -16.   Q5_1: d, m, 32 high bits, 16 code bytes.
+// Code j = low nibble of byte j (| bit j of the high bits << 4), code j + 16 = high nibble (| bit j + 16).
+void dequant_legacy32_block(int dtype, const uint8_t* blk, float* out) {
+  const bool has_m = dtype == DT_Q4_1 || dtype == DT_Q5_1, five = dtype == DT_Q5_0 || dtype == DT_Q5_1;
+  const float d = f16_to_f32(rd16(blk));
+  const float sc = d * 1.0f;
+  const float mn = has_m ? f16_to_f32(rd16(blk + 2)) * 1.0f : d * (five ? -16.0f : -8.0f);
+  const int hdr = has_m ? 4 : 2;
+  uint32_t qh = 0;
+  if (five) qh = (uint32_t)blk[hdr] | ((uint32_t)blk[hdr + 1] << 8) | ((uint32_t)blk[hdr + 2] << 16) | ((uint32_t)blk[hdr + 3] << 24);
+  const uint8_t* qs = blk + hdr + (five ? 4 : 0);
+  for (int j = 0; j < 16; ++j) {
+    uint32_t c0 = qs[j] & 0x0Fu, c1 = qs[j] >> 4;
+    if (five) {
+      c0 |= ((qh >> j) << 4) & 0x10u;
+      c1 |= (qh >> (j + 12)) & 0x10u;
+    }
+    out[j] = sc * (float)c0 + mn;
+    out[j + 16] = sc * (float)c1 + mn;
+  }
+}
+
+// One Q2_K block (84 B -> 256 f32), dequant.rs:224-252: 16 scale bytes (scale low nibble, min high nibble, one
+// per 16 elements), 64 code bytes (2 bits per element), d, dmin: out = (d * sc) * code + (dmin * -m).
+void dequant_q2k_block(const uint8_t* blk, float* out) {
+  const uint8_t* scales = blk;
+  const uint8_t* qs = blk + 16;
+  const float d = f16_to_f32(rd16(blk + 80)), dmin = f16_to_f32(rd16(blk + 82));
+  int o = 0, is = 0;
+  for (int n = 0; n < 2; ++n)
+    for (int j = 0; j < 4; ++j)
+      for (int half = 0; half < 2; ++half) {
+        const uint8_t s = scales[is++];
+        const float sc = d * (float)(int16_t)(s & 0xF), mn = dmin * (float)(int16_t)(-(int)(s >> 4));
+        for (int l = 0; l < 16; ++l) out[o++] = sc * (float)((qs[32 * n + 16 * half + l] >> (2 * j)) & 3) + mn;
+      }
+}
+
+// One Q3_K block (110 B -> 256 f32), dequant.rs:253-314: 32 high-bit bytes, 64 code bytes, 12 bytes holding
+// sixteen 6-bit scales, d: s = sc6 - 32 per 16 elements, out = (d * s) * code + (d * (-4 s)), code = low2 | high << 2.
+void dequant_q3k_block(const uint8_t* blk, float* out) {
+  const uint8_t* hmask = blk;
+  const uint8_t* qs = blk + 32;
+  const uint8_t* sr = blk + 96;
+  const float d = f16_to_f32(rd16(blk + 108));
+  auto rd32 = [](const uint8_t* p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24); };
+  const uint32_t a0 = rd32(sr), a1 = rd32(sr + 4), tmp = rd32(sr + 8), k1 = 0x03030303u, k2 = 0x0f0f0f0fu;
+  const uint32_t aux[4] = {(a0 & k2) | ((tmp & k1) << 4), (a1 & k2) | (((tmp >> 2) & k1) << 4), ((a0 >> 4) & k2) | (((tmp >> 4) & k1) << 4),
+                           ((a1 >> 4) & k2) | (((tmp >> 6) & k1) << 4)};
+  int o = 0, is = 0;
+  uint8_t m = 1;
+  for (int n = 0; n < 2; ++n)
+    for (int j = 0; j < 4; ++j) {
+      for (int half = 0; half < 2; ++half) {
+        const int16_t s = (int16_t)((int8_t)(uint8_t)((aux[is / 4] >> ((is % 4) * 8)) & 0xFF)) - 32;
+        ++is;
+        const float sc = d * (float)s, mn = d * (float)(int16_t)(-4 * s);
+        for (int l = 0; l < 16; ++l) {
+          const uint8_t low2 = (qs[32 * n + 16 * half + l] >> (2 * j)) & 3, high = (hmask[16 * half + l] & m) ? 1 : 0;
+          out[o++] = sc * (float)(uint8_t)(low2 | (high << 2)) + mn;
+        }
+      }
+      m = (uint8_t)(m << 1);
+    }
+}
+
 // The 16-entry signed codebook of the two non-linear 4-bit formats (dequant.rs:443-445).
 const int8_t KV_IQ4NL[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 
@@ -210,6 +279,12 @@ void dequant_iq4xs_block(const uint8_t* blk, float* out) {
 size_t row_bytes(int dtype, size_t n_elem) {
   switch (dtype) {
     case DT_F32: return n_elem * 4;
+    case DT_Q4_0: return n_elem / 32 * 18;
+    case DT_Q4_1: return n_elem / 32 * 20;
+    case DT_Q5_0: return n_elem / 32 * 22;
+    case DT_Q5_1: return n_elem / 32 * 24;
+    case DT_Q2K: return n_elem / 256 * 84;
+    case DT_Q3K: return n_elem / 256 * 110;
     case DT_IQ4NL: return n_elem / 32 * 18;
     case DT_IQ4XS: return n_elem / 256 * 136;
     case DT_Q8_0: return n_elem / 32 * 34;
@@ -241,6 +316,23 @@ bool dequant_row(int dtype, const uint8_t* bytes, size_t n_elem, float* out) {
     case DT_Q8_0:
       if (n_elem % 32) return false;
       for (size_t b = 0; b < n_elem / 32; ++b) dequant_q80_block(bytes + b * 34, out + b * 32);
+      return true;
+    case DT_Q4_0:
+    case DT_Q4_1:
+    case DT_Q5_0:
+    case DT_Q5_1: {
+      if (n_elem % 32) return false;
+      const size_t bb = row_bytes(dtype, 32);
+      for (size_t b = 0; b < n_elem / 32; ++b) dequant_legacy32_block(dtype, bytes + b * bb, out + b * 32);
+      return true;
+    }
+    case DT_Q2K:
+      if (n_elem % 256) return false;
+      for (size_t b = 0; b < n_elem / 256; ++b) dequant_q2k_block(bytes + b * 84, out + b * 256);
+      return true;
+    case DT_Q3K:
+      if (n_elem % 256) return false;
+      for (size_t b = 0; b < n_elem / 256; ++b) dequant_q3k_block(bytes + b * 110, out + b * 256);
       return true;
     case DT_IQ4NL:
       if (n_elem % 32) return false;

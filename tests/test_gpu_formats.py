@@ -14,8 +14,10 @@ from helpers import GpuLayer, assert_close, near_tie_rows, oracle_layer
 pytestmark = pytest.mark.gpu
 
 Q8_0, Q4K, Q5K, Q6K, IQ4NL, IQ4XS = 8, 12, 13, 14, 20, 23
+Q4_0, Q4_1, Q5_0, Q5_1, Q2K, Q3K = 2, 3, 6, 7, 10, 11
 MIXES = [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0), (Q5K, Q5K, Q5K), (Q4K, Q5K, Q8_0), (Q6K, Q6K, Q4K), (Q8_0, Q4K, Q6K),
-         (IQ4XS, IQ4XS, Q6K), (IQ4NL, IQ4NL, IQ4NL), (IQ4XS, IQ4NL, IQ4XS)]
+         (IQ4XS, IQ4XS, Q6K), (IQ4NL, IQ4NL, IQ4NL), (IQ4XS, IQ4NL, IQ4XS),
+         (Q4_0, Q4_0, Q4_0), (Q4_1, Q4_1, Q5_1), (Q5_0, Q5_1, Q5_0), (Q2K, Q2K, Q3K), (Q3K, Q3K, Q6K), (Q3K, Q2K, Q2K)]
 
 
 def check(out, ids, ref, n_used):
@@ -69,7 +71,9 @@ def test_variants_and_bands(backend, mix):
 
 
 @pytest.mark.parametrize("dt,name,in_f,out_f", [(Q5K, "Q5K", 512, 64), (Q8_0, "Q8_0", 512, 64), (Q8_0, "Q8_0", 96, 40),
-                                                (IQ4XS, "IQ4XS", 512, 64), (IQ4NL, "IQ4NL", 160, 24)])
+                                                (IQ4XS, "IQ4XS", 512, 64), (IQ4NL, "IQ4NL", 160, 24), (Q4_0, "Q4_0", 96, 16),
+                                                (Q4_1, "Q4_1", 512, 16), (Q5_0, "Q5_0", 512, 16), (Q5_1, "Q5_1", 64, 16),
+                                                (Q2K, "Q2K", 512, 32), (Q3K, "Q3K", 768, 32)])
 def test_linear_op(backend, dt, name, in_f, out_f):
     # Op::Linear on the reference's synthesised weights (crates/infr-testkit/src/lib.rs:74-123); Q8_0 rows
     # need whole 32-weight blocks only
@@ -92,5 +96,5 @@ def test_unknown_format_refused(backend):
     L.gate_dtype = 0  # F32 banks: not covered
     with pytest.raises(BackendError) as e:
         g.run(synth.activations(1, 1, 256), 2)
-    assert "Q4_K, Q5_K, Q6_K, Q8_0, IQ4_NL or IQ4_XS" in str(e.value)
+    assert "expert banks must be one of" in str(e.value)
     L.gate_dtype = 12

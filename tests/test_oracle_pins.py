@@ -256,6 +256,99 @@ def test_iq4_blocks_match_numpy_decoder(dt, name, elems, ref):
     assert np.array_equal(orc.dequant(dt, rb, 4096).view(np.uint32), ref(rb).view(np.uint32))
 
 
+def np_legacy32(raw, dt):
+    """dequant.rs:142-212, 35-51: Q4_0 / Q4_1 / Q5_0 / Q5_1 = (f32(d)*1)*code + (f32(d)*-8 | f32(m)*1 | f32(d)*-16 | f32(m)*1)."""
+    has_m, five = dt in (3, 7), dt in (6, 7)
+    hdr = 4 if has_m else 2
+    bb = hdr + (4 if five else 0) + 16
+    raw = np.asarray(raw, np.uint8).reshape(-1, bb)
+    out = np.empty((raw.shape[0], 32), F32)
+    for bi, blk in enumerate(raw):
+        with np.errstate(all="ignore"):
+            d = f16(int(blk[0]), int(blk[1]))
+            mn = F32(f16(int(blk[2]), int(blk[3])) * F32(1)) if has_m else F32(d * F32(-16 if five else -8))
+            qh = int.from_bytes(bytes(blk[hdr:hdr + 4]), "little") if five else 0
+            qs = blk[hdr + (4 if five else 0):].astype(np.int64)
+            j = np.arange(16)
+            c0 = (qs & 0xF) | ((((qh >> j) & 1) << 4) if five else 0)
+            c1 = (qs >> 4) | ((((qh >> (j + 16)) & 1) << 4) if five else 0)
+            sc = F32(d * F32(1))
+            out[bi, :16] = (sc * c0.astype(F32)).astype(F32) + mn
+            out[bi, 16:] = (sc * c1.astype(F32)).astype(F32) + mn
+    return out.reshape(-1)
+
+
+def np_q2k(raw):
+    """dequant.rs:224-252: per 16 elements (f32(d)*(s & 15))*code + (f32(dmin)*-(s >> 4)), 2-bit codes."""
+    raw = np.asarray(raw, np.uint8).reshape(-1, 84)
+    out = np.empty((raw.shape[0], 256), F32)
+    for bi, blk in enumerate(raw):
+        with np.errstate(all="ignore"):
+            d, dmin = f16(int(blk[80]), int(blk[81])), f16(int(blk[82]), int(blk[83]))
+            qs = blk[16:80].astype(np.int64)
+            for g in range(16):
+                n, j, half = g >> 3, (g >> 1) & 3, g & 1
+                s = int(blk[g])
+                code = (qs[32 * n + 16 * half: 32 * n + 16 * half + 16] >> (2 * j)) & 3
+                out[bi, 16 * g: 16 * g + 16] = (F32(d * F32(s & 15)) * code.astype(F32)).astype(F32) + F32(dmin * F32(-(s >> 4)))
+    return out.reshape(-1)
+
+
+def np_q3k(raw):
+    """dequant.rs:253-314: sixteen 6-bit scales (s = sc6 - 32), codes low2 | hmask bit << 2: (f32(d)*s)*code + f32(d)*(-4 s)."""
+    raw = np.asarray(raw, np.uint8).reshape(-1, 110)
+    out = np.empty((raw.shape[0], 256), F32)
+    for bi, blk in enumerate(raw):
+        with np.errstate(all="ignore"):
+            d = f16(int(blk[108]), int(blk[109]))
+            hm, qs, sr = blk[0:32].astype(np.int64), blk[32:96].astype(np.int64), blk[96:108].astype(np.int64)
+            for g in range(16):
+                n, j, half = g >> 3, (g >> 1) & 3, g & 1
+                # scale g: low four bits = low (g < 8) or high nibble of byte g % 8, two more bits from byte 8 + g % 4 at bit 2 (g / 4)
+                lo4 = (sr[g % 8] >> (0 if g < 8 else 4)) & 0xF
+                hi2 = (sr[8 + g % 4] >> (2 * (g // 4))) & 3
+                s = int(lo4 | (hi2 << 4)) - 32
+                low2 = (qs[32 * n + 16 * half: 32 * n + 16 * half + 16] >> (2 * j)) & 3
+                high = (hm[16 * half: 16 * half + 16] >> (4 * n + j)) & 1
+                code = low2 | (high << 2)
+                out[bi, 16 * g: 16 * g + 16] = (F32(d * F32(s)) * code.astype(F32)).astype(F32) + F32(d * F32(-4 * s))
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("dt,name,nbytes,elems", [(2, "Q4_0", 18, 32), (3, "Q4_1", 20, 32), (6, "Q5_0", 22, 32), (7, "Q5_1", 24, 32),
+                                                   (10, "Q2K", 84, 256), (11, "Q3K", 110, 256)])
+def test_legacy_and_small_k_formats(dt, name, nbytes, elems):
+    ref = np_q2k if dt == 10 else np_q3k if dt == 11 else (lambda raw: np_legacy32(raw, dt))
+    # crates/infr-gguf/src/dequant.rs:1206-1229: two blocks of bytes ((i*29+3)&0xFF), scale slots included
+    raw = ((np.arange(2 * nbytes) * 29 + 3) & 0xFF).astype(np.uint8)
+    want, got = ref(raw), orc.dequant(dt, raw, 2 * elems)
+    fin = np.isfinite(want)
+    assert np.array_equal(got[fin].view(np.uint32), want[fin].view(np.uint32))
+    assert np.array_equal(np.isnan(got), np.isnan(want)) and np.array_equal(np.isinf(got), np.isinf(want))
+    # the reference's synthesis recipe (crates/infr-testkit/src/lib.rs:74-123) and random payloads
+    raw = synth.testkit_weight(name, 1024, seed=0x2468)
+    got = orc.dequant(dt, raw, 1024)
+    assert np.array_equal(got.view(np.uint32), ref(raw).view(np.uint32))
+    assert np.all(np.isfinite(got)) and np.ptp(got) > 0
+    rb = synth.random_blocks(np.random.default_rng(13), dt, 4096)
+    assert np.array_equal(orc.dequant(dt, rb, 4096).view(np.uint32), ref(rb).view(np.uint32))
+
+
+def test_q4_0_by_hand():
+    # d = 2, code byte 0x1F: element 0 = 2 * (15 - 8) = 14, element 16 = 2 * (1 - 8) = -14; Q4_1 with m = 0.5: 2 * 15 + 0.5, 2 * 1 + 0.5
+    blk = np.zeros(18, np.uint8)
+    blk[0:2] = np.array([2.0], np.float16).view(np.uint8)
+    blk[2] = 0x1F
+    y = orc.dequant(2, blk, 32)
+    assert y[0] == 14.0 and y[16] == -14.0 and y[1] == -16.0
+    blk = np.zeros(20, np.uint8)
+    blk[0:2] = np.array([2.0], np.float16).view(np.uint8)
+    blk[2:4] = np.array([0.5], np.float16).view(np.uint8)
+    blk[4] = 0x1F
+    y = orc.dequant(3, blk, 32)
+    assert y[0] == 30.5 and y[16] == 2.5 and y[1] == 0.5
+
+
 def test_ragged_block_count_rejected():
     with pytest.raises(ValueError):
         orc.dequant(orc.DT_Q4K, np.zeros(144, np.uint8), 100)
