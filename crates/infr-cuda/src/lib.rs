@@ -213,6 +213,7 @@ fn dt_code(dt: DType) -> Result<i32> {
         DType::Q3K => Ok(ffi::DT_Q3K),
         DType::Iq4Nl => Ok(ffi::DT_IQ4NL),
         DType::Iq4Xs => Ok(ffi::DT_IQ4XS),
+        DType::Mxfp4 => Ok(ffi::DT_MXFP4),
         other => Err(Error::Unsupported(format!("infr-cuda: weight dtype {other:?} has no sm_100a kernel (F32, Q4_K, Q6_K only)"))),
     }
 }

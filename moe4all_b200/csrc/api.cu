@@ -417,7 +417,7 @@ int32_t validate_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, ui
   if (rc) return rc;
   if (!d->n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: zero n_ff_exp");
   if (!bank_dtype_ok(d->gate_dtype) || !bank_dtype_ok(d->up_dtype) || !bank_dtype_ok(d->down_dtype))
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS");
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS MXFP4");
   if (d->fused_gate_up && d->gate_dtype != d->up_dtype)
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: a fused gate/up bank has one dtype");
   if (d->ne % 256 || d->n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ne and n_ff_exp must be multiples of the 256-weight block");
@@ -815,7 +815,7 @@ int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_row
   if (!n_local || !ne || !n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: zero dimension");
   if (n_local > 1024) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: more than 1024 local experts");
   if (!bank_dtype_ok(gate_dtype) || !bank_dtype_ok(up_dtype) || !bank_dtype_ok(down_dtype))
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS");
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS MXFP4");
   if (ne % 256 || n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: ne and n_ff_exp must be multiples of 256");
   if (!n_rows) return INFR_CUDA_OK;
   const size_t gb = (size_t)n_local * n_ff_exp * row_bytes(gate_dtype, ne), ub = (size_t)n_local * n_ff_exp * row_bytes(up_dtype, ne),

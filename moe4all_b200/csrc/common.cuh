@@ -97,6 +97,7 @@ INFR_HD inline size_t row_bytes(int32_t dtype, size_t n_elem) {
     case INFR_CUDA_DT_Q3K: return n_elem / 256 * 110;
     case INFR_CUDA_DT_IQ4NL: return n_elem / 32 * 18;
     case INFR_CUDA_DT_IQ4XS: return n_elem / 256 * 136;
+    case INFR_CUDA_DT_MXFP4: return n_elem / 32 * 17;
     default: return 0;
   }
 }

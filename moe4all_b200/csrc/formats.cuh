@@ -22,6 +22,7 @@
 //
 //   IQ4_NL  18 B / 32   code = kvalues[nibble] + 128,   A = d,            B = 0,   off = 128
 //   IQ4_XS 136 B / 256  code = kvalues[nibble] + 128,   A = d * (ls6 - 32), B = 0, off = 128
+//   MXFP4   17 B / 32   code = e2m1x2[nibble] + 128,    A = 2^(e - 128),  B = 0,   off = 128  (:409-421, 1029-1046)
 //
 // The generic small-m kernels (anyfmt_ffn.cu) feed the codes to integer dot products against the
 // fixed-point activations; the generic grouped GEMM (grouped_ffn.cu) turns them into f16 operands.
@@ -40,7 +41,7 @@ inline bool bank_dtype_ok(int32_t dt) {
   switch (dt) {
     case INFR_CUDA_DT_Q4_0: case INFR_CUDA_DT_Q4_1: case INFR_CUDA_DT_Q5_0: case INFR_CUDA_DT_Q5_1: case INFR_CUDA_DT_Q8_0:
     case INFR_CUDA_DT_Q2K: case INFR_CUDA_DT_Q3K: case INFR_CUDA_DT_Q4K: case INFR_CUDA_DT_Q5K: case INFR_CUDA_DT_Q6K:
-    case INFR_CUDA_DT_IQ4NL: case INFR_CUDA_DT_IQ4XS:
+    case INFR_CUDA_DT_IQ4NL: case INFR_CUDA_DT_IQ4XS: case INFR_CUDA_DT_MXFP4:
       return true;
     default:
       return false;
@@ -71,17 +72,28 @@ __device__ __forceinline__ uint32_t ld_u32_a2(const uint8_t* p) {
   return lo | (hi << 16);
 }
 
-// Four 4-bit indices (one per byte of n) -> the bytes kvalues_iq4nl[index] + 128 of the IQ4 codebook
-// {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113}: two byte permutes over the
-// table's halves (index bits 0-2 as the selector), the half chosen by index bit 3.
-__device__ __forceinline__ uint32_t iq4_codes(uint32_t n) {
+// Four 4-bit indices (one per byte of n) -> the bytes table[index] of a 16-entry byte table given as four
+// words: two byte permutes over the table's halves (index bits 0-2 as the selector), the half chosen by
+// index bit 3.
+__device__ __forceinline__ uint32_t lut16_bytes(uint32_t n, uint32_t t0, uint32_t t1, uint32_t t2, uint32_t t3) {
   const uint32_t n7 = n & 0x07070707u;
   const uint32_t t = n7 | (n7 >> 4);                                         // nibbles: b0 b1 b1 b2 b2 b3 b3 0
   const uint32_t sel = (t & 0xFFu) | ((t >> 4) & 0xF00u) | ((t >> 8) & 0xF000u);  // b0 b1 b2 b3
-  const uint32_t lo = __byte_perm(0x3F2D1801u, 0x766A5D4Fu, sel);            // entries 0-7  (+128)
-  const uint32_t hi = __byte_perm(0xA6998D81u, 0xF1D9C5B5u, sel);            // entries 8-15 (+128)
+  const uint32_t lo = __byte_perm(t0, t1, sel), hi = __byte_perm(t2, t3, sel);
   const uint32_t m = ((n >> 3) & 0x01010101u) * 0xFFu;                       // 0xFF where the index is 8-15
   return (lo & ~m) | (hi & m);
+}
+// kvalues_iq4nl + 128: {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113}
+__device__ __forceinline__ uint32_t iq4_codes(uint32_t n) { return lut16_bytes(n, 0x3F2D1801u, 0x766A5D4Fu, 0xA6998D81u, 0xF1D9C5B5u); }
+// kvalues_mxfp4 (E2M1 values x 2) + 128: {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12}
+__device__ __forceinline__ uint32_t mxfp4_codes(uint32_t n) { return lut16_bytes(n, 0x83828180u, 0x8C888684u, 0x7D7E7F80u, 0x74787A7Cu); }
+
+// Four bytes at any address (MXFP4 blocks are 17 bytes).
+template <bool G>
+__device__ __forceinline__ uint32_t ld_u32_a1(const uint8_t* p) {
+  if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) return fmt_ld<G, uint32_t>(p);
+  return (uint32_t)fmt_ld<G, uint8_t>(p) | ((uint32_t)fmt_ld<G, uint8_t>(p + 1) << 8) | ((uint32_t)fmt_ld<G, uint8_t>(p + 2) << 16) |
+         ((uint32_t)fmt_ld<G, uint8_t>(p + 3) << 24);
 }
 
 // Codes and affine map of weights 16h .. 16h+15 of the row starting at `row` (G: in global memory;
@@ -185,6 +197,16 @@ __device__ __forceinline__ void fmt_codes16(int dt, const uint8_t* __restrict__ 
 #pragma unroll
     for (int i = 0; i < 4; ++i) c[i] = iq4_codes((ld_u32_a2<G>(blk + 2 + 4 * i) >> sh) & 0x0F0F0F0Fu);
     A = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk));
+    B = 0.f;
+    off = 128;
+  } else if (dt == INFR_CUDA_DT_MXFP4) {
+    // one E8M0 exponent byte (the scale is 2^(e - 128): `e8m0_to_fp32_half`), 16 code bytes as in IQ4_NL
+    const uint8_t* blk = row + (size_t)(h >> 1) * 17;
+    const int sh = 4 * (h & 1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[i] = mxfp4_codes((ld_u32_a1<G>(blk + 1 + 4 * i) >> sh) & 0x0F0F0F0Fu);
+    const uint32_t e = fmt_ld<G, uint8_t>(blk);
+    A = __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1) << 23));
     B = 0.f;
     off = 128;
   } else if (dt == INFR_CUDA_DT_IQ4XS) {

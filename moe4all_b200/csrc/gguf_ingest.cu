@@ -61,6 +61,7 @@ bool block_layout(int32_t type, uint64_t* elems, uint64_t* bytes) {
     case 27: *elems = 1; *bytes = 8; return true;     // I64
     case 28: *elems = 1; *bytes = 8; return true;     // F64
     case 30: *elems = 1; *bytes = 2; return true;     // BF16
+    case 39: *elems = 32; *bytes = 17; return true;   // MXFP4
     default: return false;
   }
 }

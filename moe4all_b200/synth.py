@@ -16,7 +16,7 @@ Q5K_BYTES, Q80_BYTES = 176, 34
 # GGUF type number -> (elements per block, bytes per block, offsets of the f16 scale slots)
 BLOCKS = {12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,)), 8: (32, 34, (0,)),
           20: (32, 18, (0,)), 23: (256, 136, (0,)), 2: (32, 18, (0,)), 3: (32, 20, (0, 2)), 6: (32, 22, (0,)), 7: (32, 24, (0, 2)),
-          10: (256, 84, (80, 82)), 11: (256, 110, (108,))}
+          10: (256, 84, (80, 82)), 11: (256, 110, (108,)), 39: (32, 17, ())}  # (MXFP4's scale is one exponent byte, set apart)
 
 
 def _f16_bytes(vals: np.ndarray) -> np.ndarray:
@@ -46,6 +46,8 @@ def random_blocks(rng: np.random.Generator, dtype: int, n_elem: int, lo: float =
     blk = rng.integers(0, 256, size=(n_blocks, nbytes), dtype=np.uint8)
     for o in slots:
         blk[:, o:o + 2] = _f16_bytes(rng.uniform(lo, hi, n_blocks))
+    if dtype == 39:  # E8M0 exponent: 2^-14 .. 2^-9, the magnitude of hi
+        blk[:, 0] = rng.integers(114, 120, size=n_blocks, dtype=np.uint8)
     return blk
 
 
@@ -70,7 +72,8 @@ def testkit_weight(dtype_name: str, n_elem: int, seed: int) -> np.ndarray:
     Q8_0 (d 0.01), IQ4_NL (d 0.004), IQ4_XS (d 0.06), Q4_0 / Q5_0 (d 0.04), Q4_1 / Q5_1 (d 0.04, m -0.30),
     Q2_K (d 0.05, dmin 0.10) and Q3_K (d 0.03)."""
     TK = {"Q5K": (13, (0.05, 0.10)), "Q8_0": (8, (0.01,)), "IQ4NL": (20, (0.004,)), "IQ4XS": (23, (0.06,)), "Q4_0": (2, (0.04,)),
-          "Q4_1": (3, (0.04, -0.30)), "Q5_0": (6, (0.04,)), "Q5_1": (7, (0.04, -0.30)), "Q2K": (10, (0.05, 0.10)), "Q3K": (11, (0.03,))}
+          "Q4_1": (3, (0.04, -0.30)), "Q5_0": (6, (0.04,)), "Q5_1": (7, (0.04, -0.30)), "Q2K": (10, (0.05, 0.10)), "Q3K": (11, (0.03,)),
+          "MXFP4": (39, ())}
     if dtype_name in TK:
         elems, nbytes, slots = BLOCKS[TK[dtype_name][0]]
         assert n_elem % elems == 0
@@ -80,6 +83,8 @@ def testkit_weight(dtype_name: str, n_elem: int, seed: int) -> np.ndarray:
             out[b] = lcg_bytes(seed ^ b, nbytes)
         for o, v in zip(slots, TK[dtype_name][1]):
             out[:, o:o + 2] = _f16_bytes(np.full(nblk, v))
+        if dtype_name == "MXFP4":
+            out[:, 0] = 126  # E8M0 of the recipe's d = 0.25 = 2^(126 - 128)
         return out
     assert n_elem % QK == 0
     nblk = n_elem // QK

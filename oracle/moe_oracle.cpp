@@ -39,7 +39,7 @@
 namespace {
 
 // dtype ids follow the public GGUF/ggml numbering.
-enum : int { DT_F32 = 0, DT_Q4_0 = 2, DT_Q4_1 = 3, DT_Q5_0 = 6, DT_Q5_1 = 7, DT_Q8_0 = 8, DT_Q2K = 10, DT_Q3K = 11, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14, DT_IQ4NL = 20, DT_IQ4XS = 23 };
+enum : int { DT_F32 = 0, DT_Q4_0 = 2, DT_Q4_1 = 3, DT_Q5_0 = 6, DT_Q5_1 = 7, DT_Q8_0 = 8, DT_Q2K = 10, DT_Q3K = 11, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14, DT_IQ4NL = 20, DT_IQ4XS = 23, DT_MXFP4 = 39 };
 
 // IEEE binary16 → binary32, exact (what `half::f16::to_f32` does; dequant.rs:72-74).
 inline float f16_to_f32(uint16_t h) {
@@ -258,6 +258,20 @@ void dequant_iq4nl_block(const uint8_t* blk, float* out) {
   }
 }
 
+// One MXFP4 block (17 B -> 32 f32), dequant.rs:409-421, 1029-1046: an E8M0 exponent byte e (d = 2^(e - 128), built
+// from bits as `e8m0_to_fp32_half` does), 16 code bytes indexing the E2M1 x 2 table; y = kv * d.
+void dequant_mxfp4_block(const uint8_t* blk, float* out) {
+  static const int8_t KV[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
+  const uint32_t e = blk[0], bits = e < 2 ? (0x00200000u << e) : ((e - 1) << 23);
+  float d;
+  std::memcpy(&d, &bits, 4);
+  const uint8_t* qs = blk + 1;
+  for (int j = 0; j < 16; ++j) {
+    out[j] = (float)KV[qs[j] & 0xF] * d;
+    out[j + 16] = (float)KV[qs[j] >> 4] * d;
+  }
+}
+
 // One IQ4_XS block (136 B -> 256 f32), dequant.rs:521-553: eight sub-blocks of 32 with a 6-bit scale
 // ls (low four bits in scales_l, high two in scales_h); dl = d * (ls - 32); codes as in IQ4_NL.
 void dequant_iq4xs_block(const uint8_t* blk, float* out) {
@@ -287,6 +301,7 @@ size_t row_bytes(int dtype, size_t n_elem) {
     case DT_Q3K: return n_elem / 256 * 110;
     case DT_IQ4NL: return n_elem / 32 * 18;
     case DT_IQ4XS: return n_elem / 256 * 136;
+    case DT_MXFP4: return n_elem / 32 * 17;
     case DT_Q8_0: return n_elem / 32 * 34;
     case DT_Q4K: return n_elem / 256 * 144;
     case DT_Q5K: return n_elem / 256 * 176;
@@ -337,6 +352,10 @@ bool dequant_row(int dtype, const uint8_t* bytes, size_t n_elem, float* out) {
     case DT_IQ4NL:
       if (n_elem % 32) return false;
       for (size_t b = 0; b < n_elem / 32; ++b) dequant_iq4nl_block(bytes + b * 18, out + b * 32);
+      return true;
+    case DT_MXFP4:
+      if (n_elem % 32) return false;
+      for (size_t b = 0; b < n_elem / 32; ++b) dequant_mxfp4_block(bytes + b * 17, out + b * 32);
       return true;
     case DT_IQ4XS:
       if (n_elem % 256) return false;

@@ -349,6 +349,35 @@ def test_q4_0_by_hand():
     assert y[0] == 30.5 and y[16] == 2.5 and y[1] == 0.5
 
 
+def np_mxfp4(raw):
+    """dequant.rs:409-421, 1029-1046: d = 2^(e - 128) (e < 2: the two subnormals), y = kv[nibble] * d."""
+    kv = np.array([0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12], np.float32)
+    raw = np.asarray(raw, np.uint8).reshape(-1, 17)
+    out = np.empty((raw.shape[0], 32), F32)
+    for bi, blk in enumerate(raw):
+        e = int(blk[0])
+        d = np.float32(np.ldexp(1.0, e - 128))  # exact in f32 down to 2^-128 = the subnormal the reference builds for e = 0
+        qs = blk[1:17].astype(np.int64)
+        out[bi, :16] = kv[qs & 0xF] * d
+        out[bi, 16:] = kv[qs >> 4] * d
+    return out.reshape(-1)
+
+
+def test_mxfp4_reference_vector_and_blocks():
+    # crates/infr-gguf/src/dequant.rs `mxfp4_single_block`: e = 128 -> d = 1; qs[0] = 0x21 -> y[0] = 1, y[16] = 2, the rest 0
+    blk = np.zeros(17, np.uint8)
+    blk[0], blk[1] = 128, 0x21
+    y = orc.dequant(orc.DT_MXFP4, blk, 32)
+    assert y[0] == 1.0 and y[16] == 2.0 and np.all(y[1:16] == 0.0) and np.all(y[17:] == 0.0)
+    assert orc.row_bytes(orc.DT_MXFP4, 2048) == 1088
+    raw = synth.testkit_weight("MXFP4", 1024, seed=0x1357)  # the reference's recipe: d = 0.25
+    got = orc.dequant(orc.DT_MXFP4, raw, 1024)
+    assert np.array_equal(got.view(np.uint32), np_mxfp4(raw).view(np.uint32)) and np.abs(got).max() == 3.0
+    rb = ((np.arange(4 * 17) * 29 + 3) & 0xFF).astype(np.uint8)  # every exponent byte, the two smallest included, decodes alike
+    rb[0], rb[17] = 0, 1
+    assert np.array_equal(orc.dequant(orc.DT_MXFP4, rb, 128).view(np.uint32), np_mxfp4(rb).view(np.uint32))
+
+
 def test_ragged_block_count_rejected():
     with pytest.raises(ValueError):
         orc.dequant(orc.DT_Q4K, np.zeros(144, np.uint8), 100)
