@@ -45,9 +45,9 @@ Q4K_ROW = NE // 256 * 144      # bytes of one gate/up row
 Q6K_ROW = N_FF // 256 * 210    # bytes of one down row
 EXPERT_BYTES = 2 * N_FF * Q4K_ROW + NE * Q6K_ROW  # 2 039 808
 # --banks: GGUF type numbers and (elements, bytes) per block of the formats an expert bank may have
-BANK_TYPES = {"q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8, "q2k": 10, "q3k": 11, "q4k": 12, "q5k": 13, "q6k": 14, "iq4_nl": 20, "iq4_xs": 23, "mxfp4": 39}
+BANK_TYPES = {"q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8, "q2k": 10, "q3k": 11, "q4k": 12, "q5k": 13, "q6k": 14, "iq4_nl": 20, "iq4_xs": 23, "mxfp4": 39, "nvfp4": 40, "q2_0": 42}
 BANK_BLOCK = {2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176),
-              14: (256, 210), 20: (32, 18), 23: (256, 136), 39: (32, 17)}
+              14: (256, 210), 20: (32, 18), 23: (256, 136), 39: (32, 17), 40: (64, 36), 42: (64, 18)}
 BANKS = (12, 12, 14)           # gate, up, down of the layer workload (set from --banks)
 
 

@@ -39,6 +39,8 @@ pub const DT_Q3K: i32 = 11;
 pub const DT_IQ4NL: i32 = 20;
 pub const DT_IQ4XS: i32 = 23;
 pub const DT_MXFP4: i32 = 39;
+pub const DT_NVFP4: i32 = 40;
+pub const DT_Q2_0: i32 = 42;
 
 pub const EP_ID_BYTES: usize = 128;
 

@@ -214,7 +214,9 @@ fn dt_code(dt: DType) -> Result<i32> {
         DType::Iq4Nl => Ok(ffi::DT_IQ4NL),
         DType::Iq4Xs => Ok(ffi::DT_IQ4XS),
         DType::Mxfp4 => Ok(ffi::DT_MXFP4),
-        other => Err(Error::Unsupported(format!("infr-cuda: weight dtype {other:?} has no sm_100a kernel (F32, Q4_K, Q6_K only)"))),
+        DType::Nvfp4 => Ok(ffi::DT_NVFP4),
+        DType::Q2_0 => Ok(ffi::DT_Q2_0),
+        other => Err(Error::Unsupported(format!("infr-cuda: weight dtype {other:?} has no sm_100a kernel"))),
     }
 }
 

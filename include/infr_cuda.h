@@ -49,6 +49,8 @@ extern "C" {
 #define INFR_CUDA_DT_IQ4NL 20 /* 32 weights / 18 B, crates/infr-core/src/decode_spec.rs:349  */
 #define INFR_CUDA_DT_IQ4XS 23 /* 256 weights / 136 B, crates/infr-core/src/decode_spec.rs:351 */
 #define INFR_CUDA_DT_MXFP4 39 /* 32 weights / 17 B, crates/infr-core/src/decode_spec.rs:361  */
+#define INFR_CUDA_DT_NVFP4 40 /* 64 weights / 36 B, crates/infr-core/src/decode_spec.rs:363  */
+#define INFR_CUDA_DT_Q2_0 42 /* 64 weights / 18 B, crates/infr-core/src/decode_spec.rs:358   */
 
 /* MoeGating (crates/infr-core/src/graph.rs:73-85). */
 #define INFR_CUDA_GATING_SOFTMAX 0

@@ -40,7 +40,7 @@ struct Result {
 
 // crates/infr-core/src/tensor.rs:7-57, numbered as in the GGUF file format.
 enum class DType : int32_t { F32 = INFR_CUDA_DT_F32, Q4_0 = INFR_CUDA_DT_Q4_0, Q4_1 = INFR_CUDA_DT_Q4_1, Q5_0 = INFR_CUDA_DT_Q5_0,
-                             Q5_1 = INFR_CUDA_DT_Q5_1, Q2K = INFR_CUDA_DT_Q2K, Q3K = INFR_CUDA_DT_Q3K, Q8_0 = INFR_CUDA_DT_Q8_0, Q4K = INFR_CUDA_DT_Q4K, Q5K = INFR_CUDA_DT_Q5K, Q6K = INFR_CUDA_DT_Q6K, IQ4NL = INFR_CUDA_DT_IQ4NL, IQ4XS = INFR_CUDA_DT_IQ4XS, MXFP4 = INFR_CUDA_DT_MXFP4 };
+                             Q5_1 = INFR_CUDA_DT_Q5_1, Q2K = INFR_CUDA_DT_Q2K, Q3K = INFR_CUDA_DT_Q3K, Q8_0 = INFR_CUDA_DT_Q8_0, Q4K = INFR_CUDA_DT_Q4K, Q5K = INFR_CUDA_DT_Q5K, Q6K = INFR_CUDA_DT_Q6K, IQ4NL = INFR_CUDA_DT_IQ4NL, IQ4XS = INFR_CUDA_DT_IQ4XS, MXFP4 = INFR_CUDA_DT_MXFP4, NVFP4 = INFR_CUDA_DT_NVFP4, Q2_0 = INFR_CUDA_DT_Q2_0 };
 // crates/infr-core/src/graph.rs:73-85
 enum class MoeGating : uint32_t {
   Softmax = INFR_CUDA_GATING_SOFTMAX,

@@ -67,6 +67,8 @@ class DType(enum.IntEnum):
     IQ4NL = 20
     IQ4XS = 23
     MXFP4 = 39
+    NVFP4 = 40
+    Q2_0 = 42
 
     def row_bytes(self, n_elem: int) -> int:
         """crates/infr-core/src/decode_spec.rs:315-335: elements and bytes per block."""
@@ -74,7 +76,8 @@ class DType(enum.IntEnum):
             return n_elem * 4
         elems, nbytes = {DType.Q8_0: (32, 34), DType.Q4K: (256, 144), DType.Q5K: (256, 176), DType.Q6K: (256, 210),
                          DType.IQ4NL: (32, 18), DType.IQ4XS: (256, 136), DType.Q4_0: (32, 18), DType.Q4_1: (32, 20),
-                         DType.Q5_0: (32, 22), DType.Q5_1: (32, 24), DType.Q2K: (256, 84), DType.Q3K: (256, 110), DType.MXFP4: (32, 17)}[self]
+                         DType.Q5_0: (32, 22), DType.Q5_1: (32, 24), DType.Q2K: (256, 84), DType.Q3K: (256, 110), DType.MXFP4: (32, 17),
+                         DType.NVFP4: (64, 36), DType.Q2_0: (64, 18)}[self]
         if n_elem % elems:
             raise ValueError(f"{self.name}: {n_elem} elements is not a whole number of {elems}-element blocks")
         return n_elem // elems * nbytes

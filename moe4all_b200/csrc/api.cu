@@ -417,7 +417,7 @@ int32_t validate_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, ui
   if (rc) return rc;
   if (!d->n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: zero n_ff_exp");
   if (!bank_dtype_ok(d->gate_dtype) || !bank_dtype_ok(d->up_dtype) || !bank_dtype_ok(d->down_dtype))
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS MXFP4");
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS MXFP4 NVFP4 Q2_0");
   if (d->fused_gate_up && d->gate_dtype != d->up_dtype)
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: a fused gate/up bank has one dtype");
   if (d->ne % 256 || d->n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ne and n_ff_exp must be multiples of the 256-weight block");
@@ -756,11 +756,11 @@ int32_t infr_cuda_linear(infr_cuda_ctx* ctx, int32_t dtype, const infr_cuda_buf*
                          infr_cuda_buf* y, uint32_t m, uint32_t in_f, uint32_t out_f) {
   if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
   if (!m || !in_f || !out_f) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: zero dimension");
+  if (dtype != INFR_CUDA_DT_F32 && !block_elems(dtype))
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32 and the block formats an expert bank may have)");
+  if (dtype != INFR_CUDA_DT_F32 && in_f % block_elems(dtype))
+    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: in_f must be a whole number of weight blocks (32, 64 or 256 weights)");
   const size_t rb = row_bytes(dtype, in_f);
-  if (!rb) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32 and the block formats an expert bank may have)");
-  // (formats with 32-weight blocks give bytes for 32 elements, the 256-weight ones do not)
-  if (dtype != INFR_CUDA_DT_F32 && in_f % (row_bytes(dtype, 32) ? 32 : 256))
-    return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: in_f must be a whole number of weight blocks (32 or 256 weights)");
   if (!fits(w, rb * out_f) || !fits(x, (size_t)m * in_f * 4) || !fits(y, (size_t)m * out_f * 4))
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: buffer missing or too small");
   DeviceGuard g(ctx->device);
@@ -815,7 +815,7 @@ int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_row
   if (!n_local || !ne || !n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: zero dimension");
   if (n_local > 1024) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: more than 1024 local experts");
   if (!bank_dtype_ok(gate_dtype) || !bank_dtype_ok(up_dtype) || !bank_dtype_ok(down_dtype))
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS MXFP4");
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS MXFP4 NVFP4 Q2_0");
   if (ne % 256 || n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: ne and n_ff_exp must be multiples of 256");
   if (!n_rows) return INFR_CUDA_OK;
   const size_t gb = (size_t)n_local * n_ff_exp * row_bytes(gate_dtype, ne), ub = (size_t)n_local * n_ff_exp * row_bytes(up_dtype, ne),

@@ -98,8 +98,16 @@ INFR_HD inline size_t row_bytes(int32_t dtype, size_t n_elem) {
     case INFR_CUDA_DT_IQ4NL: return n_elem / 32 * 18;
     case INFR_CUDA_DT_IQ4XS: return n_elem / 256 * 136;
     case INFR_CUDA_DT_MXFP4: return n_elem / 32 * 17;
+    case INFR_CUDA_DT_NVFP4: return n_elem / 64 * 36;
+    case INFR_CUDA_DT_Q2_0: return n_elem / 64 * 18;
     default: return 0;
   }
+}
+// Weights per block of a block format (0: not one).
+INFR_HD inline int block_elems(int32_t dtype) {
+  if (dtype == INFR_CUDA_DT_NVFP4 || dtype == INFR_CUDA_DT_Q2_0) return 64;
+  if (dtype == INFR_CUDA_DT_F32 || !row_bytes(dtype, 256)) return 0;
+  return row_bytes(dtype, 32) ? 32 : 256;
 }
 INFR_HD inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 

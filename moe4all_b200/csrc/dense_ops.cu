@@ -247,6 +247,8 @@ int32_t launch_linear(infr_cuda_ctx* ctx, int32_t dtype, const uint8_t* w, const
     case INFR_CUDA_DT_IQ4NL:
     case INFR_CUDA_DT_IQ4XS:
     case INFR_CUDA_DT_MXFP4:
+    case INFR_CUDA_DT_NVFP4:
+    case INFR_CUDA_DT_Q2_0:
       k_linear_anyfmt<<<grid, block, 0, ctx->stream>>>(dtype, w, x, y, in_f, out_f, row_bytes(dtype, in_f));
       break;
     default: return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32 and the block formats an expert bank may have)");

@@ -23,6 +23,11 @@
 //   IQ4_NL  18 B / 32   code = kvalues[nibble] + 128,   A = d,            B = 0,   off = 128
 //   IQ4_XS 136 B / 256  code = kvalues[nibble] + 128,   A = d * (ls6 - 32), B = 0, off = 128
 //   MXFP4   17 B / 32   code = e2m1x2[nibble] + 128,    A = 2^(e - 128),  B = 0,   off = 128  (:409-421, 1029-1046)
+//   NVFP4   36 B / 64   code = e2m1x2[nibble] + 128,    A = ue4m3(scale of the 16) / 2, B = 0, off = 128  (:423-439, 1053-1073)
+//
+// and the ternary-plus-one 2-bit form (:1007-1022):
+//
+//   Q2_0    18 B / 64   code = 2 bits,                  A = d,      B = 0,         off = 1
 //
 // The generic small-m kernels (anyfmt_ffn.cu) feed the codes to integer dot products against the
 // fixed-point activations; the generic grouped GEMM (grouped_ffn.cu) turns them into f16 operands.
@@ -42,6 +47,7 @@ inline bool bank_dtype_ok(int32_t dt) {
     case INFR_CUDA_DT_Q4_0: case INFR_CUDA_DT_Q4_1: case INFR_CUDA_DT_Q5_0: case INFR_CUDA_DT_Q5_1: case INFR_CUDA_DT_Q8_0:
     case INFR_CUDA_DT_Q2K: case INFR_CUDA_DT_Q3K: case INFR_CUDA_DT_Q4K: case INFR_CUDA_DT_Q5K: case INFR_CUDA_DT_Q6K:
     case INFR_CUDA_DT_IQ4NL: case INFR_CUDA_DT_IQ4XS: case INFR_CUDA_DT_MXFP4:
+    case INFR_CUDA_DT_NVFP4: case INFR_CUDA_DT_Q2_0:
       return true;
     default:
       return false;
@@ -209,6 +215,34 @@ __device__ __forceinline__ void fmt_codes16(int dt, const uint8_t* __restrict__ 
     A = __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1) << 23));
     B = 0.f;
     off = 128;
+  } else if (dt == INFR_CUDA_DT_NVFP4) {
+    // 64-weight blocks (4-byte aligned): four UE4M3 scale bytes, one per 16 weights, then 8 code bytes per 16
+    // weights whose low nibbles are weights 0-7 and high nibbles weights 8-15
+    const uint8_t* blk = row + (size_t)(h >> 2) * 36;
+    const int s = h & 3;
+    const uint32_t a = fmt_ld<G, uint32_t>(blk + 4 + 8 * s), b = fmt_ld<G, uint32_t>(blk + 8 + 8 * s);
+    c[0] = mxfp4_codes(a & 0x0F0F0F0Fu);
+    c[1] = mxfp4_codes(b & 0x0F0F0F0Fu);
+    c[2] = mxfp4_codes((a >> 4) & 0x0F0F0F0Fu);
+    c[3] = mxfp4_codes((b >> 4) & 0x0F0F0F0Fu);
+    // UE4M3 (bias 7, 3 mantissa bits; bit 7 unused), halved: man * 2^-10 for exponent 0, else (8 + man) * 2^(exp - 11);
+    // bytes 0x00 and 0x7F decode to 0
+    const uint32_t x = (fmt_ld<G, uint32_t>(blk) >> (8 * s)) & 0xFFu, ex = (x >> 3) & 0xFu, man = x & 7u;
+    A = (x == 0u || x == 0x7Fu) ? 0.f : (ex == 0u ? (float)man * 0x1p-10f : (float)(8u + man) * __uint_as_float((ex + 116u) << 23));
+    B = 0.f;
+    off = 128;
+  } else if (dt == INFR_CUDA_DT_Q2_0) {
+    // 64-weight blocks (2-byte aligned): f16 d, 16 code bytes of four 2-bit fields, weight j in byte j / 4 at bit 2 (j % 4)
+    const uint8_t* blk = row + (size_t)(h >> 2) * 18;
+    const uint32_t w = ld_u32_a2<G>(blk + 2 + 4 * (h & 3));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t v = (w >> (8 * i)) & 0xFFu;
+      c[i] = (v & 3u) | ((v & 0x0Cu) << 6) | ((v & 0x30u) << 12) | ((v & 0xC0u) << 18);
+    }
+    A = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk));
+    B = 0.f;
+    off = 1;
   } else if (dt == INFR_CUDA_DT_IQ4XS) {
     // sub-block ib (32 elements) = 16 code bytes at 8 + 16 ib, low nibbles first; its 6-bit scale: low
     // four bits in scales_l (a nibble per sub-block), high two in scales_h

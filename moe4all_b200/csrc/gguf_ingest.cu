@@ -62,6 +62,8 @@ bool block_layout(int32_t type, uint64_t* elems, uint64_t* bytes) {
     case 28: *elems = 1; *bytes = 8; return true;     // F64
     case 30: *elems = 1; *bytes = 2; return true;     // BF16
     case 39: *elems = 32; *bytes = 17; return true;   // MXFP4
+    case 40: *elems = 64; *bytes = 36; return true;   // NVFP4
+    case 42: *elems = 64; *bytes = 18; return true;   // Q2_0
     default: return false;
   }
 }

@@ -26,7 +26,8 @@ def q6k_bank(n_blocks: int, gen, device) -> torch.Tensor:
 # GGUF type number -> (elements per block, bytes per block, offsets of the f16 scale slots, scale factor)
 BLOCKS = {12: (256, 144, (0, 2), 1.0), 13: (256, 176, (0, 2), 1.0), 14: (256, 210, (208,), 1.0), 8: (32, 34, (0,), 2.0),
           20: (32, 18, (0,), 2.0), 23: (256, 136, (0,), 1.0), 2: (32, 18, (0,), 32.0), 3: (32, 20, (0, 2), 32.0), 6: (32, 22, (0,), 16.0),
-          7: (32, 24, (0, 2), 16.0), 10: (256, 84, (80, 82), 64.0), 11: (256, 110, (108,), 8.0), 39: (32, 17, (), 1.0)}
+          7: (32, 24, (0, 2), 16.0), 10: (256, 84, (80, 82), 64.0), 11: (256, 110, (108,), 8.0), 39: (32, 17, (), 1.0),
+          40: (64, 36, (), 1.0), 42: (64, 18, (0,), 64.0)}
 
 
 def bank(dtype: int, n_elem: int, gen, device) -> torch.Tensor:
@@ -42,6 +43,8 @@ def bank(dtype: int, n_elem: int, gen, device) -> torch.Tensor:
         t[:, o:o + 2] = ((torch.rand(n, generator=gen, device=device) * 9e-4 + 1e-4) * k).to(torch.float16).view(torch.uint8).reshape(n, 2)
     if dtype == 39:  # MXFP4: one E8M0 exponent byte per block, 2^-14 .. 2^-9
         t[:, 0] = torch.randint(114, 120, (n,), dtype=torch.uint8, generator=gen, device=device)
+    if dtype == 40:  # NVFP4: four UE4M3 sub-scale bytes per block with exponent field 0 or 1
+        t[:, 0:4] = torch.randint(1, 16, (n, 4), dtype=torch.uint8, generator=gen, device=device)
     return t.reshape(-1)
 
 

@@ -16,7 +16,8 @@ Q5K_BYTES, Q80_BYTES = 176, 34
 # GGUF type number -> (elements per block, bytes per block, offsets of the f16 scale slots)
 BLOCKS = {12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,)), 8: (32, 34, (0,)),
           20: (32, 18, (0,)), 23: (256, 136, (0,)), 2: (32, 18, (0,)), 3: (32, 20, (0, 2)), 6: (32, 22, (0,)), 7: (32, 24, (0, 2)),
-          10: (256, 84, (80, 82)), 11: (256, 110, (108,)), 39: (32, 17, ())}  # (MXFP4's scale is one exponent byte, set apart)
+          10: (256, 84, (80, 82)), 11: (256, 110, (108,)), 39: (32, 17, ()),
+          40: (64, 36, ()), 42: (64, 18, (0,))}  # (MXFP4's exponent byte and NVFP4's four UE4M3 bytes are set apart)
 
 
 def _f16_bytes(vals: np.ndarray) -> np.ndarray:
@@ -48,6 +49,8 @@ def random_blocks(rng: np.random.Generator, dtype: int, n_elem: int, lo: float =
         blk[:, o:o + 2] = _f16_bytes(rng.uniform(lo, hi, n_blocks))
     if dtype == 39:  # E8M0 exponent: 2^-14 .. 2^-9, the magnitude of hi
         blk[:, 0] = rng.integers(114, 120, size=n_blocks, dtype=np.uint8)
+    if dtype == 40:  # UE4M3 sub-scales with exponent field 0 or 1: at most 15 * 2^-10 / 8, times codes up to 12
+        blk[:, 0:4] = rng.integers(1, 16, size=(n_blocks, 4), dtype=np.uint8)
     return blk
 
 
@@ -70,10 +73,10 @@ def gen_f32(n: int, salt: int) -> np.ndarray:
 def testkit_weight(dtype_name: str, n_elem: int, seed: int) -> np.ndarray:
     """crates/infr-testkit/src/lib.rs:74-123 for Q4_K and Q5_K (d 0.05, dmin 0.10), Q6_K (d 0.03),
     Q8_0 (d 0.01), IQ4_NL (d 0.004), IQ4_XS (d 0.06), Q4_0 / Q5_0 (d 0.04), Q4_1 / Q5_1 (d 0.04, m -0.30),
-    Q2_K (d 0.05, dmin 0.10) and Q3_K (d 0.03)."""
+    Q2_K (d 0.05, dmin 0.10), Q3_K (d 0.03), MXFP4 (d 0.25), NVFP4 (d 0.5) and Q2_0 (d 0.05)."""
     TK = {"Q5K": (13, (0.05, 0.10)), "Q8_0": (8, (0.01,)), "IQ4NL": (20, (0.004,)), "IQ4XS": (23, (0.06,)), "Q4_0": (2, (0.04,)),
           "Q4_1": (3, (0.04, -0.30)), "Q5_0": (6, (0.04,)), "Q5_1": (7, (0.04, -0.30)), "Q2K": (10, (0.05, 0.10)), "Q3K": (11, (0.03,)),
-          "MXFP4": (39, ())}
+          "MXFP4": (39, ()), "NVFP4": (40, ()), "Q2_0": (42, (0.05,))}
     if dtype_name in TK:
         elems, nbytes, slots = BLOCKS[TK[dtype_name][0]]
         assert n_elem % elems == 0
@@ -85,6 +88,10 @@ def testkit_weight(dtype_name: str, n_elem: int, seed: int) -> np.ndarray:
             out[:, o:o + 2] = _f16_bytes(np.full(nblk, v))
         if dtype_name == "MXFP4":
             out[:, 0] = 126  # E8M0 of the recipe's d = 0.25 = 2^(126 - 128)
+        if dtype_name == "NVFP4":
+            # the recipe's d = 0.5 spread as d * (0.625 + 0.125 i) over the four sub-scales
+            # (crates/infr-core/src/decode_spec.rs:192-198): 0.3125, 0.375, 0.4375, 0.5, all exact in UE4M3
+            out[:, 0:4] = np.array([0x2A, 0x2C, 0x2E, 0x30], np.uint8)
         return out
     assert n_elem % QK == 0
     nblk = n_elem // QK
@@ -128,7 +135,7 @@ def make_layer(seed: int, ne: int, n_expert: int, n_ff: int, sh_ff: int = 0, gat
         L.gate_dtype, L.up_dtype, L.down_dtype = dtypes
 
         def bank(dt, n_elem):
-            k = {8: 2.0, 20: 2.0, 2: 32.0, 3: 32.0, 6: 16.0, 7: 16.0, 10: 64.0, 11: 8.0}.get(dt, 1.0)  # similar weight magnitudes
+            k = {8: 2.0, 20: 2.0, 2: 32.0, 3: 32.0, 6: 16.0, 7: 16.0, 10: 64.0, 11: 8.0, 42: 64.0}.get(dt, 1.0)  # similar weight magnitudes
             return random_blocks(rng, dt, n_elem, 1e-4 * k, 1e-3 * k).reshape(-1)
         L.gate, L.up, L.down = bank(dtypes[0], n_expert * n_ff * ne), bank(dtypes[1], n_expert * n_ff * ne), bank(dtypes[2], n_expert * ne * n_ff)
         if sh_ff:

@@ -39,7 +39,7 @@
 namespace {
 
 // dtype ids follow the public GGUF/ggml numbering.
-enum : int { DT_F32 = 0, DT_Q4_0 = 2, DT_Q4_1 = 3, DT_Q5_0 = 6, DT_Q5_1 = 7, DT_Q8_0 = 8, DT_Q2K = 10, DT_Q3K = 11, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14, DT_IQ4NL = 20, DT_IQ4XS = 23, DT_MXFP4 = 39 };
+enum : int { DT_F32 = 0, DT_Q4_0 = 2, DT_Q4_1 = 3, DT_Q5_0 = 6, DT_Q5_1 = 7, DT_Q8_0 = 8, DT_Q2K = 10, DT_Q3K = 11, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14, DT_IQ4NL = 20, DT_IQ4XS = 23, DT_MXFP4 = 39, DT_NVFP4 = 40, DT_Q2_0 = 42 };
 
 // IEEE binary16 → binary32, exact (what `half::f16::to_f32` does; dequant.rs:72-74).
 inline float f16_to_f32(uint16_t h) {
@@ -272,6 +272,35 @@ void dequant_mxfp4_block(const uint8_t* blk, float* out) {
   }
 }
 
+// One NVFP4 block (36 B -> 64 f32), dequant.rs:423-439, 1053-1073: four UE4M3 scale bytes (4 exponent bits with
+// bias 7, 3 mantissa bits, the value halved; 0x00 and 0x7F decode to 0), one per 16 weights; 8 code bytes per 16
+// weights index the E2M1 x 2 table, low nibbles weights 0-7, high nibbles weights 8-15; y = kv * d.
+float ue4m3_half(uint8_t x) {
+  if (x == 0 || x == 0x7F) return 0.0f;
+  const int ex = (x >> 3) & 0xF;
+  const float man = (float)(x & 7);
+  const float raw = ex == 0 ? man * std::ldexp(1.0f, -9) : (1.0f + man / 8.0f) * std::ldexp(1.0f, ex - 7);
+  return raw * 0.5f;
+}
+void dequant_nvfp4_block(const uint8_t* blk, float* out) {
+  static const int8_t KV[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
+  const uint8_t* qs = blk + 4;
+  for (int s = 0; s < 4; ++s) {
+    const float d = ue4m3_half(blk[s]);
+    for (int j = 0; j < 8; ++j) {
+      out[16 * s + j] = (float)KV[qs[8 * s + j] & 0xF] * d;
+      out[16 * s + j + 8] = (float)KV[qs[8 * s + j] >> 4] * d;
+    }
+  }
+}
+
+// One Q2_0 block (18 B -> 64 f32), dequant.rs:1007-1022: f16 d, 2-bit codes (weight j in byte j / 4 at bit
+// 2 (j % 4)); y = (q - 1) * d.
+void dequant_q2_0_block(const uint8_t* blk, float* out) {
+  const float d = f16_to_f32(rd16(blk));
+  for (int j = 0; j < 64; ++j) out[j] = (float)((int)((blk[2 + j / 4] >> ((j % 4) * 2)) & 3) - 1) * d;
+}
+
 // One IQ4_XS block (136 B -> 256 f32), dequant.rs:521-553: eight sub-blocks of 32 with a 6-bit scale
 // ls (low four bits in scales_l, high two in scales_h); dl = d * (ls - 32); codes as in IQ4_NL.
 void dequant_iq4xs_block(const uint8_t* blk, float* out) {
@@ -302,6 +331,8 @@ size_t row_bytes(int dtype, size_t n_elem) {
     case DT_IQ4NL: return n_elem / 32 * 18;
     case DT_IQ4XS: return n_elem / 256 * 136;
     case DT_MXFP4: return n_elem / 32 * 17;
+    case DT_NVFP4: return n_elem / 64 * 36;
+    case DT_Q2_0: return n_elem / 64 * 18;
     case DT_Q8_0: return n_elem / 32 * 34;
     case DT_Q4K: return n_elem / 256 * 144;
     case DT_Q5K: return n_elem / 256 * 176;
@@ -356,6 +387,14 @@ bool dequant_row(int dtype, const uint8_t* bytes, size_t n_elem, float* out) {
     case DT_MXFP4:
       if (n_elem % 32) return false;
       for (size_t b = 0; b < n_elem / 32; ++b) dequant_mxfp4_block(bytes + b * 17, out + b * 32);
+      return true;
+    case DT_NVFP4:
+      if (n_elem % 64) return false;
+      for (size_t b = 0; b < n_elem / 64; ++b) dequant_nvfp4_block(bytes + b * 36, out + b * 64);
+      return true;
+    case DT_Q2_0:
+      if (n_elem % 64) return false;
+      for (size_t b = 0; b < n_elem / 64; ++b) dequant_q2_0_block(bytes + b * 18, out + b * 64);
       return true;
     case DT_IQ4XS:
       if (n_elem % 256) return false;

@@ -17,7 +17,7 @@ _SO = os.path.join(_HERE, "_build", "libmoe_oracle.so")
 
 DT_F32, DT_Q4K, DT_Q6K = 0, 12, 14
 DT_Q8_0, DT_Q5K = 8, 13
-DT_IQ4NL, DT_IQ4XS, DT_MXFP4 = 20, 23, 39
+DT_IQ4NL, DT_IQ4XS, DT_MXFP4, DT_NVFP4, DT_Q2_0 = 20, 23, 39, 40, 42
 DT_Q4_0, DT_Q4_1, DT_Q5_0, DT_Q5_1, DT_Q2K, DT_Q3K = 2, 3, 6, 7, 10, 11
 GATING_SOFTMAX, GATING_SIGMOID, GATING_SQRT_SOFTPLUS = 0, 1, 2
 

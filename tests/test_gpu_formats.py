@@ -14,11 +14,12 @@ from helpers import GpuLayer, assert_close, near_tie_rows, oracle_layer
 pytestmark = pytest.mark.gpu
 
 Q8_0, Q4K, Q5K, Q6K, IQ4NL, IQ4XS = 8, 12, 13, 14, 20, 23
-Q4_0, Q4_1, Q5_0, Q5_1, Q2K, Q3K, MXFP4 = 2, 3, 6, 7, 10, 11, 39
+Q4_0, Q4_1, Q5_0, Q5_1, Q2K, Q3K, MXFP4, NVFP4, Q2_0 = 2, 3, 6, 7, 10, 11, 39, 40, 42
 MIXES = [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0), (Q5K, Q5K, Q5K), (Q4K, Q5K, Q8_0), (Q6K, Q6K, Q4K), (Q8_0, Q4K, Q6K),
          (IQ4XS, IQ4XS, Q6K), (IQ4NL, IQ4NL, IQ4NL), (IQ4XS, IQ4NL, IQ4XS),
          (Q4_0, Q4_0, Q4_0), (Q4_1, Q4_1, Q5_1), (Q5_0, Q5_1, Q5_0), (Q2K, Q2K, Q3K), (Q3K, Q3K, Q6K), (Q3K, Q2K, Q2K),
-         (MXFP4, MXFP4, MXFP4), (MXFP4, MXFP4, Q6K)]
+         (MXFP4, MXFP4, MXFP4), (MXFP4, MXFP4, Q6K),
+         (NVFP4, NVFP4, NVFP4), (Q2_0, Q2_0, Q2_0), (Q2_0, NVFP4, Q4K)]
 
 
 def check(out, ids, ref, n_used):
@@ -74,7 +75,8 @@ def test_variants_and_bands(backend, mix):
 @pytest.mark.parametrize("dt,name,in_f,out_f", [(Q5K, "Q5K", 512, 64), (Q8_0, "Q8_0", 512, 64), (Q8_0, "Q8_0", 96, 40),
                                                 (IQ4XS, "IQ4XS", 512, 64), (IQ4NL, "IQ4NL", 160, 24), (Q4_0, "Q4_0", 96, 16),
                                                 (Q4_1, "Q4_1", 512, 16), (Q5_0, "Q5_0", 512, 16), (Q5_1, "Q5_1", 64, 16),
-                                                (Q2K, "Q2K", 512, 32), (Q3K, "Q3K", 768, 32), (MXFP4, "MXFP4", 96, 24)])
+                                                (Q2K, "Q2K", 512, 32), (Q3K, "Q3K", 768, 32), (MXFP4, "MXFP4", 96, 24),
+                                                (NVFP4, "NVFP4", 192, 24), (Q2_0, "Q2_0", 320, 16)])
 def test_linear_op(backend, dt, name, in_f, out_f):
     # Op::Linear on the reference's synthesised weights (crates/infr-testkit/src/lib.rs:74-123); Q8_0 rows
     # need whole 32-weight blocks only

@@ -378,6 +378,55 @@ def test_mxfp4_reference_vector_and_blocks():
     assert np.array_equal(orc.dequant(orc.DT_MXFP4, rb, 128).view(np.uint32), np_mxfp4(rb).view(np.uint32))
 
 
+def np_nvfp4(raw):
+    """dequant.rs:423-439, 1053-1073: per 16 weights a UE4M3 byte (halved; 0x00 and 0x7F give 0) and 8 code bytes,
+    low nibbles weights 0-7, high nibbles weights 8-15; y = kv[nibble] * d."""
+    kv = np.array([0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12], np.float32)
+    raw = np.asarray(raw, np.uint8).reshape(-1, 36)
+    out = np.empty((raw.shape[0], 64), F32)
+    for bi, blk in enumerate(raw):
+        for s in range(4):
+            x = int(blk[s])
+            ex, man = (x >> 3) & 0xF, x & 7
+            d = 0.0 if x in (0, 0x7F) else (man * 2.0 ** -9 if ex == 0 else (1 + man / 8) * 2.0 ** (ex - 7)) * 0.5  # exact in f64 and f32
+            qs = blk[4 + 8 * s:12 + 8 * s].astype(np.int64)
+            out[bi, 16 * s:16 * s + 8] = kv[qs & 0xF] * np.float32(d)
+            out[bi, 16 * s + 8:16 * s + 16] = kv[qs >> 4] * np.float32(d)
+    return out.reshape(-1)
+
+
+def test_nvfp4_reference_vector_and_blocks():
+    # crates/infr-gguf/src/dequant.rs `nvfp4_single_block`: the all-zero block decodes to zeros
+    assert np.all(orc.dequant(orc.DT_NVFP4, np.zeros(36, np.uint8), 64) == 0.0)
+    assert orc.row_bytes(orc.DT_NVFP4, 2048) == 1152
+    # the reference's recipe (d = 0.5 spread over the four sub-scales, crates/infr-core/src/decode_spec.rs:192-198):
+    # four distinct non-zero scale bytes, as its `write_scales_round_trips_each_encoding` asks
+    raw = synth.testkit_weight("NVFP4", 1024, seed=0x2468)
+    assert len(set(raw.reshape(-1, 36)[0, :4].tolist())) == 4 and raw.reshape(-1, 36)[:, :4].min() > 0
+    got = orc.dequant(orc.DT_NVFP4, raw, 1024)
+    assert np.array_equal(got.view(np.uint32), np_nvfp4(raw).view(np.uint32))
+    assert np.abs(got).max() == 12 * 0.25  # code 12 under the largest sub-scale 0.5, halved
+    # every scale byte, 0x00, 0x7F, the exponent-0 forms and bit 7 set included
+    rb = ((np.arange(64 * 36) * 37 + 11) & 0xFF).astype(np.uint8).reshape(64, 36)
+    rb[:, :4] = np.arange(256, dtype=np.uint8).reshape(64, 4)
+    assert np.array_equal(orc.dequant(orc.DT_NVFP4, rb.reshape(-1), 64 * 64).view(np.uint32), np_nvfp4(rb).view(np.uint32))
+
+
+def test_q2_0_reference_vector_and_blocks():
+    # crates/infr-gguf/src/dequant.rs `q2_0_single_block`: d = 0.5, qs[0] = 0b11100100 -> -0.5, 0, 0.5, 1.0, then -0.5
+    blk = np.zeros(18, np.uint8)
+    blk[0:2] = np.array([0.5], np.float16).view(np.uint8)
+    blk[2] = 0b11100100
+    y = orc.dequant(orc.DT_Q2_0, blk, 64)
+    assert y[:4].tolist() == [-0.5, 0.0, 0.5, 1.0] and np.all(y[4:] == -0.5)
+    assert orc.row_bytes(orc.DT_Q2_0, 2048) == 576
+    raw = synth.testkit_weight("Q2_0", 1024, seed=0x99).reshape(-1, 18)
+    d = raw[:, 0:2].copy().view(np.float16).astype(np.float32)  # [blocks, 1]
+    q = (raw[:, 2 + np.arange(64) // 4].astype(np.int64) >> ((np.arange(64) % 4) * 2)) & 3
+    want = ((q - 1).astype(np.float32) * d).reshape(-1)
+    assert np.array_equal(orc.dequant(orc.DT_Q2_0, raw.reshape(-1), 1024).view(np.uint32), want.view(np.uint32))
+
+
 def test_ragged_block_count_rejected():
     with pytest.raises(ValueError):
         orc.dequant(orc.DT_Q4K, np.zeros(144, np.uint8), 100)
