@@ -106,41 +106,57 @@ __device__ __forceinline__ void block_scan2(int& a, int& b, int& ta, int& tb, in
 // Exclusive scan of the per-expert counts (thread e holds the count of segment e), the tile table
 // (one entry per `tn` rows of a segment, the shared expert's rows appended as segment n_expert) and
 // the segment offsets, by the 1024 threads of one CTA.  Offsets stay in s_off for the caller.
+// Tiles are listed heaviest first - the full tiles of all segments, then the segments' last, partial
+// tiles by falling row count - so that the GEMM kernels' last wave of CTAs is made of the light ones
+// (a tile's index only names its slot in the token and activation arrays).  tn is a power of two.
 __device__ __forceinline__ void segment_tables(int cnt, int n_expert, int shared_rows, int tn, int* __restrict__ seg_off,
                                                int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                                int* __restrict__ tile_rows, int* __restrict__ n_tiles, int* s_cnt, int* s_off,
                                                int* s_toff, int* s_ws) {
   const int tid = threadIdx.x;
   const int n_seg = n_expert + (shared_rows > 0 ? 1 : 0);
-  int off = cnt, toff = (cnt + tn - 1) / tn, total = 0, total_t = 0;
-  block_scan2(off, toff, total, total_t, s_ws);
+  int off = cnt, foff = cnt / tn, total = 0, total_f = 0;  // rows and full tiles ahead of this segment
+  block_scan2(off, foff, total, total_f, s_ws);
   if (tid < n_seg) {
     s_cnt[tid] = cnt;
     s_off[tid] = off;
-    s_toff[tid] = toff;
+    s_toff[tid] = foff;
   }
-  if (tid == 0) {
-    // segment 1024 (only with 1024 experts and a shared segment) is appended here
-    if (n_seg > 1024) {
+  // partial tiles: the count over the CTA; segment 1024 (only with 1024 experts and a shared segment) is added below
+  int n_part = __syncthreads_count(tid < n_seg && (cnt & (tn - 1)) != 0);
+  if (n_seg > 1024) {
+    if (tid == 0) {
       s_cnt[1024] = shared_rows;
       s_off[1024] = total;
-      s_toff[1024] = total_t;
-      total += shared_rows;
-      total_t += (shared_rows + tn - 1) / tn;
+      s_toff[1024] = total_f;
     }
+    total += shared_rows;
+    total_f += shared_rows / tn;
+    n_part += (shared_rows & (tn - 1)) != 0;
+  }
+  if (tid == 0) {
     s_off[n_seg] = total;
-    s_toff[n_seg] = total_t;
-    *n_tiles = total_t;
+    *n_tiles = total_f + n_part;
     seg_off[n_expert + 1] = total;  // total grouped rows, with or without a shared segment
   }
   __syncthreads();
   for (int e = tid; e <= n_seg; e += 1024) seg_off[e] = s_off[e];
   for (int e = tid; e < n_seg; e += 1024) {
-    const int nt = (s_cnt[e] + tn - 1) / tn;
-    for (int t = 0; t < nt; ++t) {
+    const int nf = s_cnt[e] / tn, part = s_cnt[e] & (tn - 1);
+    for (int t = 0; t < nf; ++t) {
       tile_expert[s_toff[e] + t] = e;
       tile_row0[s_toff[e] + t] = s_off[e] + t * tn;
-      tile_rows[s_toff[e] + t] = min(tn, s_cnt[e] - t * tn);
+      tile_rows[s_toff[e] + t] = tn;
+    }
+    if (part) {
+      int rank = 0;  // partial tiles with more rows, or as many in an earlier segment
+      for (int o = 0; o < n_seg; ++o) {
+        const int po = s_cnt[o] & (tn - 1);
+        rank += (po > part) || (po == part && o < e);
+      }
+      tile_expert[total_f + rank] = e;
+      tile_row0[total_f + rank] = s_off[e] + nf * tn;
+      tile_rows[total_f + rank] = part;
     }
   }
 }
