@@ -109,7 +109,8 @@ pub struct infr_cuda_config {
     pub expert_major: u32,
     pub sync_timeout_ms: u32,
     pub raw_rows_f32: u32,
-    pub reserved: [u32; 8],
+    pub gate_timeout_ms: u32,
+    pub reserved: [u32; 7],
 }
 
 extern "C" {
@@ -130,6 +131,12 @@ extern "C" {
     pub fn infr_cuda_download(ctx: *mut infr_cuda_ctx, src: *const infr_cuda_buf, src_off: usize, dst: *mut c_void, n: usize) -> i32;
     pub fn infr_cuda_upload_async(ctx: *mut infr_cuda_ctx, dst: *mut infr_cuda_buf, dst_off: usize, src: *const c_void, n: usize) -> i32;
     pub fn infr_cuda_download_async(ctx: *mut infr_cuda_ctx, src: *const infr_cuda_buf, src_off: usize, dst: *mut c_void, n: usize) -> i32;
+    pub fn infr_cuda_upload_gated(ctx: *mut infr_cuda_ctx, dst: *mut infr_cuda_buf, dst_off: usize, src: *const c_void, n: usize, ticket: u64) -> i32;
+    pub fn infr_cuda_host_signal(ctx: *mut infr_cuda_ctx, ticket: u64) -> i32;
+    pub fn infr_cuda_host_ring(ctx: *mut infr_cuda_ctx, ticket: u64) -> i32;
+    pub fn infr_cuda_host_await(ctx: *mut infr_cuda_ctx, ticket: u64) -> i32;
+    pub fn infr_cuda_host_reset(ctx: *mut infr_cuda_ctx) -> i32;
+    pub fn infr_cuda_host_step(ctx: *mut infr_cuda_ctx, ticket: u64, stage: *mut c_void, rows: *const c_void, n: usize) -> i32;
     pub fn infr_cuda_sync(ctx: *mut infr_cuda_ctx) -> i32;
 
     pub fn infr_cuda_moe_ffn(ctx: *mut infr_cuda_ctx, desc: *const infr_cuda_moe_ffn_desc) -> i32;

@@ -102,7 +102,10 @@ typedef struct infr_cuda_config {
                                     as f32 between the down and the combine kernel instead of f16 with a scale
                                     per 32 outputs (twice the bytes, no rounding before the sum over a token's
                                     experts; default 0)                                                    */
-  uint32_t reserved[8];          /* zero                                                                  */
+  uint32_t gate_timeout_ms;      /* host-paced plans: how long a gated fetch waits for its ticket, and
+                                    infr_cuda_host_await for its own, before giving up with
+                                    INFR_CUDA_ERR_TIMEOUT (default 2000)                                  */
+  uint32_t reserved[7];          /* zero                                                                  */
 } infr_cuda_config;
 int32_t infr_cuda_get_config(const infr_cuda_ctx* ctx, infr_cuda_config* out);
 int32_t infr_cuda_set_config(infr_cuda_ctx* ctx, const infr_cuda_config* cfg);
@@ -134,6 +137,31 @@ int32_t infr_cuda_download(infr_cuda_ctx* ctx, const infr_cuda_buf* src, size_t 
  * and a recorded plan holds kernel nodes only. */
 int32_t infr_cuda_upload_async(infr_cuda_ctx* ctx, infr_cuda_buf* dst, size_t dst_off, const void* src, size_t n);
 int32_t infr_cuda_download_async(infr_cuda_ctx* ctx, const infr_cuda_buf* src, size_t src_off, void* dst, size_t n);
+
+/* Host-paced plans: many decode steps recorded once (infr_cuda_graph_begin / end), launched once, and
+ * then paced by the host through two words in pinned memory instead of one launch and one stream wait
+ * per step.  A step is recorded as
+ *     infr_cuda_upload_gated(ctx, x, 0, x_pinned, n, t);  ...ops...;  infr_cuda_host_signal(ctx, t);
+ * with tickets t = 1, 2, ... in stream order, and run as
+ *     write the step's rows into x_pinned;  infr_cuda_host_ring(ctx, t);  infr_cuda_host_await(ctx, t);
+ * after which everything queued before the signal has finished (results written into pinned host memory,
+ * directly by a kernel or by infr_cuda_download_async, are there).  The gated upload is the fetch kernel
+ * of infr_cuda_upload_async (src: pinned host memory, 16-byte aligned, at most 256 KB, else
+ * INFR_CUDA_ERR_UNSUPPORTED) whose CTAs first poll the bell word until it reaches the ticket; kernels
+ * queued behind it may take their places and do their input-independent prologues meanwhile.  The wait is
+ * bounded by `gate_timeout_ms`: a ticket that never comes is recorded like any other bounded wait
+ * (INFR_CUDA_ERR_TIMEOUT from infr_cuda_host_await / infr_cuda_sync), and once anything has been recorded
+ * later gates no longer wait, so a plan always drains.  infr_cuda_host_reset drains the stream and sets
+ * both words back to zero: call it before launching a plan whose tickets start again at 1.
+ * One pacing host thread per context. */
+int32_t infr_cuda_upload_gated(infr_cuda_ctx* ctx, infr_cuda_buf* dst, size_t dst_off, const void* src, size_t n, uint64_t ticket);
+int32_t infr_cuda_host_signal(infr_cuda_ctx* ctx, uint64_t ticket);
+int32_t infr_cuda_host_ring(infr_cuda_ctx* ctx, uint64_t ticket);
+int32_t infr_cuda_host_await(infr_cuda_ctx* ctx, uint64_t ticket);
+int32_t infr_cuda_host_reset(infr_cuda_ctx* ctx);
+/* One step in one call: copy `n` bytes of `rows` into the pinned staging range `stage` (skipped when `rows`
+ * is NULL), ring `ticket`, await `ticket`. */
+int32_t infr_cuda_host_step(infr_cuda_ctx* ctx, uint64_t ticket, void* stage, const void* rows, size_t n);
 /* Backend::sync (backend.rs:1006). */
 int32_t infr_cuda_sync(infr_cuda_ctx* ctx);
 

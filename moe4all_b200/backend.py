@@ -26,6 +26,7 @@ EXPORTS = [
     "infr_cuda_set_stream", "infr_cuda_alloc", "infr_cuda_wrap", "infr_cuda_free",
     "infr_cuda_buf_len", "infr_cuda_buf_ptr", "infr_cuda_upload", "infr_cuda_download",
     "infr_cuda_upload_async", "infr_cuda_download_async",
+    "infr_cuda_upload_gated", "infr_cuda_host_signal", "infr_cuda_host_ring", "infr_cuda_host_await", "infr_cuda_host_reset", "infr_cuda_host_step",
     "infr_cuda_gguf_open", "infr_cuda_gguf_close", "infr_cuda_gguf_tensor_count", "infr_cuda_gguf_find",
     "infr_cuda_gguf_meta_u64", "infr_cuda_gguf_meta_f64", "infr_cuda_gguf_meta_str", "infr_cuda_gguf_upload",
     "infr_cuda_sync", "infr_cuda_moe_ffn", "infr_cuda_moe_route", "infr_cuda_linear",
@@ -124,7 +125,8 @@ class Config(C.Structure):
     _fields_ = [
         ("gu_warps", C.c_uint32), ("gu_chunks", C.c_uint32), ("dn_warps", C.c_uint32), ("upload_by_copy", C.c_uint32),
         ("trace_tile", C.c_uint32), ("expert_major", C.c_uint32),
-        ("sync_timeout_ms", C.c_uint32), ("raw_rows_f32", C.c_uint32), ("reserved", C.c_uint32 * 8),
+        ("sync_timeout_ms", C.c_uint32), ("raw_rows_f32", C.c_uint32), ("gate_timeout_ms", C.c_uint32),
+        ("reserved", C.c_uint32 * 7),
     ]
 
 
@@ -166,6 +168,12 @@ def load_library(path: Optional[str] = None):
     L.infr_cuda_download.argtypes = [vp, vp, sz, vp, sz]
     L.infr_cuda_upload_async.argtypes = [vp, vp, sz, vp, sz]
     L.infr_cuda_download_async.argtypes = [vp, vp, sz, vp, sz]
+    L.infr_cuda_upload_gated.argtypes = [vp, vp, sz, vp, sz, C.c_uint64]
+    L.infr_cuda_host_signal.argtypes = [vp, C.c_uint64]
+    L.infr_cuda_host_ring.argtypes = [vp, C.c_uint64]
+    L.infr_cuda_host_await.argtypes = [vp, C.c_uint64]
+    L.infr_cuda_host_reset.argtypes = [vp]
+    L.infr_cuda_host_step.argtypes = [vp, C.c_uint64, vp, vp, sz]
     L.infr_cuda_sync.argtypes = [vp]
     L.infr_cuda_moe_ffn.argtypes = [vp, C.POINTER(_Desc)]
     L.infr_cuda_moe_route.argtypes = [vp, C.POINTER(_Desc)]
@@ -397,6 +405,31 @@ class CudaBackend:
     def upload_ptr_async(self, dst: Buffer, host_ptr: int, nbytes: int, offset: int = 0) -> None:
         """Queued copy: the host range must stay untouched until `sync()`."""
         self._check(self._lib.infr_cuda_upload_async(self._ctx, dst.handle, offset, host_ptr, nbytes))
+
+    # -- host-paced plans: steps recorded once, launched once, paced through two words in pinned memory --
+    def upload_ptr_gated(self, dst: Buffer, host_ptr: int, nbytes: int, ticket: int, offset: int = 0) -> None:
+        """Queued fetch of pinned host rows that first waits (bounded) until the host has rung `ticket`."""
+        self._check(self._lib.infr_cuda_upload_gated(self._ctx, dst.handle, offset, host_ptr, nbytes, ticket))
+
+    def host_signal(self, ticket: int) -> None:
+        """Queued: publish `ticket` to the host once everything queued before it has finished."""
+        self._check(self._lib.infr_cuda_host_signal(self._ctx, ticket))
+
+    def host_ring(self, ticket: int) -> None:
+        """Host side: the rows of step `ticket` are in pinned memory, let its gated fetch go."""
+        self._check(self._lib.infr_cuda_host_ring(self._ctx, ticket))
+
+    def host_await(self, ticket: int) -> None:
+        """Host side: spin until `ticket` has been signalled (bounded; raises on a recorded device status)."""
+        self._check(self._lib.infr_cuda_host_await(self._ctx, ticket))
+
+    def host_step(self, ticket: int, stage_ptr: int, rows_ptr: int, nbytes: int) -> None:
+        """One step in one call: rows -> pinned staging range, ring, await."""
+        self._check(self._lib.infr_cuda_host_step(self._ctx, ticket, stage_ptr, rows_ptr, nbytes))
+
+    def host_reset(self) -> None:
+        """Drain the stream and set both pacing words back to zero (before a plan whose tickets restart at 1)."""
+        self._check(self._lib.infr_cuda_host_reset(self._ctx))
 
     def download_ptr_async(self, src: Buffer, host_ptr: int, nbytes: int, offset: int = 0) -> None:
         """Queued copy: the host range holds the data after `sync()`."""

@@ -1,5 +1,6 @@
 // C ABI: context, buffers, descriptor validation and dispatch (see include/infr_cuda.h).
 #include <cstdio>
+#include <chrono>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -76,12 +77,15 @@ struct DeviceGuard {
 
 bool fits(const infr_cuda_buf* b, size_t need) { return b && b->ptr && b->bytes >= need; }
 
+constexpr size_t HOST_WORDS_BYTES = 192;  // status words, bell word, done word: one 64-byte line each
+
 infr_cuda_config default_config() {
   infr_cuda_config c = {};
   c.gu_warps = 4;
   c.gu_chunks = 4;
   c.dn_warps = 12;
   c.sync_timeout_ms = 60000;
+  c.gate_timeout_ms = 2000;
   return c;
 }
 
@@ -139,14 +143,19 @@ int32_t infr_cuda_create(int32_t device, infr_cuda_ctx** out) {
   ctx->sm_count = prop.multiProcessorCount;
   DeviceGuard g(device);
   if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
-      cudaHostAlloc(reinterpret_cast<void**>(&ctx->status_host), sizeof(DeviceStatus), cudaHostAllocMapped) != cudaSuccess ||
+      cudaHostAlloc(reinterpret_cast<void**>(&ctx->status_host), HOST_WORDS_BYTES, cudaHostAllocMapped) != cudaSuccess ||
       cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->status), ctx->status_host, 0) != cudaSuccess ||
       cudaMalloc(&ctx->route_logits, ROUTE_LOGIT_BYTES) != cudaSuccess ||
       cudaMemset(ctx->route_logits, 0xFF, ROUTE_LOGIT_BYTES) != cudaSuccess) {
     infr_cuda_destroy(ctx);
     return INFR_CUDA_ERR_CUDA;
   }
-  std::memset(ctx->status_host, 0, sizeof(DeviceStatus));
+  std::memset(ctx->status_host, 0, HOST_WORDS_BYTES);
+  // the pacing words of host-paced plans: each on a cache line of its own behind the status words
+  ctx->bell_host = reinterpret_cast<volatile unsigned long long*>(reinterpret_cast<char*>(ctx->status_host) + 64);
+  ctx->done_host = reinterpret_cast<volatile unsigned long long*>(reinterpret_cast<char*>(ctx->status_host) + 128);
+  ctx->bell_dev = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(ctx->status) + 64);
+  ctx->done_dev = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(ctx->status) + 128);
   ctx->stream = ctx->own_stream;
   ctx->cfg = default_config();
   *out = ctx;
@@ -296,6 +305,78 @@ int32_t infr_cuda_download_async(infr_cuda_ctx* ctx, const infr_cuda_buf* src, s
     (void)cudaGetLastError();
   }
   return check_cuda(ctx, cudaMemcpyAsync(dst, sp, n, cudaMemcpyDeviceToHost, ctx->stream), "download (queued)");
+}
+
+int32_t infr_cuda_upload_gated(infr_cuda_ctx* ctx, infr_cuda_buf* dst, size_t dst_off, const void* src, size_t n, uint64_t ticket) {
+  if (!ctx || !dst || !src) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "upload_gated: null argument");
+  if (dst_off > dst->bytes || n > dst->bytes - dst_off) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "upload_gated: range exceeds the buffer");
+  if (!n || !ticket) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "upload_gated: nothing to copy, or ticket 0");
+  DeviceGuard g(ctx->device);
+  char* d = static_cast<char*>(dst->ptr) + dst_off;
+  cudaPointerAttributes at = {};
+  const bool shape_ok = n <= (256u << 10) && n % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(d) % 16 == 0;
+  if (!shape_ok || cudaPointerGetAttributes(&at, src) != cudaSuccess || at.type != cudaMemoryTypeHost || at.devicePointer == nullptr) {
+    (void)cudaGetLastError();
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "upload_gated: the source must be pinned host memory, 16-byte aligned, a multiple of 16 bytes and at most 256 KB");
+  }
+  const unsigned long long limit_ns = (unsigned long long)(ctx->cfg.gate_timeout_ms ? ctx->cfg.gate_timeout_ms : 2000u) * 1000000ull;
+  return launch_fetch_host_gated(ctx, at.devicePointer, d, n, ctx->bell_dev, ticket, limit_ns);
+}
+
+int32_t infr_cuda_host_signal(infr_cuda_ctx* ctx, uint64_t ticket) {
+  if (!ctx || !ticket) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "host_signal: null context or ticket 0");
+  DeviceGuard g(ctx->device);
+  return launch_host_signal(ctx, ctx->done_dev, ticket);
+}
+
+int32_t infr_cuda_host_ring(infr_cuda_ctx* ctx, uint64_t ticket) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  // release: the rows the host wrote into pinned memory before this call are in memory before the ticket
+  __atomic_store_n(const_cast<unsigned long long*>(ctx->bell_host), (unsigned long long)ticket, __ATOMIC_RELEASE);
+  return INFR_CUDA_OK;
+}
+
+int32_t infr_cuda_host_await(infr_cuda_ctx* ctx, uint64_t ticket) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  const auto t0 = std::chrono::steady_clock::now();
+  const auto limit = std::chrono::milliseconds(ctx->cfg.gate_timeout_ms ? ctx->cfg.gate_timeout_ms : 2000u);
+  volatile DeviceStatus* st = ctx->status_host;
+  for (unsigned spin = 0;; ++spin) {
+    if (__atomic_load_n(const_cast<unsigned long long*>(ctx->done_host), __ATOMIC_ACQUIRE) >= ticket) {
+      if (st->timeout || st->bad_index) break;  // reported below, once the stream has drained
+      return INFR_CUDA_OK;
+    }
+    if (st->timeout || st->bad_index) break;
+    if ((spin & 1023u) == 1023u && std::chrono::steady_clock::now() - t0 > limit) {
+      // nothing answered: let the gates still queued run out (they stop waiting once a status is recorded)
+      st->timeout = 10;
+      break;
+    }
+#if defined(__x86_64__) || defined(__i386__)
+    __builtin_ia32_pause();
+#endif
+  }
+  DeviceGuard g(ctx->device);
+  const int32_t rc = drain_and_poll(ctx, "host_await");
+  return rc ? rc : fail(ctx, INFR_CUDA_ERR_TIMEOUT, "host_await: the ticket was not signalled in time");
+}
+
+int32_t infr_cuda_host_step(infr_cuda_ctx* ctx, uint64_t ticket, void* stage, const void* rows, size_t n) {
+  if (!ctx || (rows && !stage)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "host_step: null argument");
+  if (rows && n) std::memcpy(stage, rows, n);
+  infr_cuda_host_ring(ctx, ticket);
+  return infr_cuda_host_await(ctx, ticket);
+}
+
+int32_t infr_cuda_host_reset(infr_cuda_ctx* ctx) {
+  if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
+  if (ctx->capturing) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "host_reset: not while recording");
+  DeviceGuard g(ctx->device);
+  const int32_t rc = drain_and_poll(ctx, "host_reset");
+  *ctx->bell_host = 0;
+  *ctx->done_host = 0;
+  __atomic_thread_fence(__ATOMIC_SEQ_CST);
+  return rc;
 }
 
 int32_t infr_cuda_sync(infr_cuda_ctx* ctx) {

@@ -60,6 +60,12 @@ struct infr_cuda_ctx {
   bool scratch_borrowed = false;  // `scratch` points into someone else's block for one nested call: never grown or freed
   infr::DeviceStatus* status = nullptr;       // the device's address of the status words below
   infr::DeviceStatus* status_host = nullptr;  // pinned, mapped host memory: kernels write it directly when they flag something
+  // host-paced plans: two 64-bit words in the same pinned block, `bell` written by the host and polled by
+  // gated fetch kernels, `done` written by signal kernels and polled by the host (infr_cuda_host_*)
+  volatile unsigned long long* bell_host = nullptr;
+  volatile unsigned long long* done_host = nullptr;
+  unsigned long long* bell_dev = nullptr;
+  unsigned long long* done_dev = nullptr;
   float* route_logits = nullptr;              // device memory: the whole-row router kernel's logit buffer, all words
                                               // "not written yet" between launches (see ROUTE_LOGIT_EMPTY)
   unsigned long long* trace = nullptr;        // optional phase stamps (see trace_stamp)

@@ -293,7 +293,68 @@ __global__ void __launch_bounds__(256) k_fetch_host(const uint4* __restrict__ sr
   const int i = blockIdx.x * 256 + threadIdx.x;
   if (i < n16) dst[i] = __ldcv(src + i);  // never a cached copy of host memory
 }
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// The same fetch behind a gate: thread 0 of every CTA polls the bell word (pinned host memory, so every
+// poll is a read across PCIe) until the host has rung `ticket`.  Bounded: after `limit_ns` the status word
+// is set and the copy goes ahead with whatever is there; a status already set (by this or any other
+// bounded wait) ends the wait at once, so the gates of a recorded plan never add up.
+__global__ void __launch_bounds__(256) k_fetch_host_gated(const uint4* __restrict__ src, uint4* __restrict__ dst, int n16,
+                                                          const unsigned long long* bell, unsigned long long ticket,
+                                                          unsigned long long limit_ns, DeviceStatus* status) {
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    const unsigned long long t0 = global_ns();
+    while (*reinterpret_cast<const volatile unsigned long long*>(bell) < ticket) {
+      if (*reinterpret_cast<volatile int*>(&status->timeout) != 0) break;
+      if (global_ns() - t0 > limit_ns) {
+        atomicExch(&status->timeout, 9);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n16) dst[i] = __ldcv(src + i);
+}
+
+// Publishes `ticket` in the done word (pinned host memory) once every kernel queued before this one has
+// finished: a programmatic dependent of the kernel ahead, so its thread is in place when that one ends.
+__global__ void k_host_signal(unsigned long long* done, unsigned long long ticket) {
+  pdl_wait();
+  __threadfence_system();
+  *reinterpret_cast<volatile unsigned long long*>(done) = ticket;
+  __threadfence_system();
+}
 }  // namespace
+
+int32_t launch_fetch_host_gated(infr_cuda_ctx* ctx, const void* src_dev_view, void* dst, size_t bytes, const unsigned long long* bell,
+                                unsigned long long ticket, unsigned long long limit_ns) {
+  const int n16 = (int)(bytes / 16);
+  if (n16 > 512) {
+    // many CTAs: one thread of a kernel of its own polls (every poll crosses PCIe, where the host is writing
+    // the rows), the plain fetch follows it in the stream
+    k_fetch_host_gated<<<1, 32, 0, ctx->stream>>>(nullptr, nullptr, 0, bell, ticket, limit_ns, ctx->status);
+    k_fetch_host<<<(n16 + 255) / 256, 256, 0, ctx->stream>>>(static_cast<const uint4*>(src_dev_view), static_cast<uint4*>(dst), n16);
+    ctx->launches += 2;
+    return check_cuda(ctx, cudaGetLastError(), "gate + k_fetch_host launch");
+  }
+  k_fetch_host_gated<<<(n16 + 255) / 256, 256, 0, ctx->stream>>>(static_cast<const uint4*>(src_dev_view), static_cast<uint4*>(dst), n16, bell,
+                                                                  ticket, limit_ns, ctx->status);
+  ctx->launches += 1;
+  return check_cuda(ctx, cudaGetLastError(), "k_fetch_host_gated launch");
+}
+
+int32_t launch_host_signal(infr_cuda_ctx* ctx, unsigned long long* done, unsigned long long ticket) {
+  const cudaError_t e = launch_ex(k_host_signal, dim3(1), dim3(1), 0, ctx->stream, true, done, ticket);
+  ctx->launches += 1;
+  return check_cuda(ctx, e, "k_host_signal launch");
+}
 
 int32_t launch_store_host(infr_cuda_ctx* ctx, const void* src, void* dst_dev_view, size_t bytes) {
   // the same kernel the other way round: device rows written into mapped pinned host memory
