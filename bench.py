@@ -21,7 +21,10 @@ The line printed by rank 0 follows the driver's contract.  `roofline` is the who
 active-expert bytes, with the three kernels' own times beside it; `prefill` and `stack` are the
 other two halves of the metric (4096-token prefill chunk, TFLOP/s; 40-layer stack, tok/s);
 `cpu_baseline` is the CPU oracle (a restatement of the reference's infr-cpu reference-mode
-arithmetic) timed on the host cores on a bounded sample.
+arithmetic) timed on the host cores on a bounded sample.  `e2e` is the same step with host buffers
+through the C ABI: the rows start in pinned host memory and the result ends there, step after step,
+as a host-paced plan (steps recorded and launched once, each released by a ticket the host writes);
+`e2e.launch_per_step` is the same with one plan launch and one stream wait per step.
 """
 from __future__ import annotations
 
