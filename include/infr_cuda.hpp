@@ -321,6 +321,15 @@ class Backend {
   }
   Status execute(const Plan& plan) { return st(infr_cuda_graph_launch(ctx_, plan.g_)); }
 
+  // Host-paced plans: steps recorded and launched once, each released by a ticket the host writes into
+  // pinned memory and reported back the same way (no launch and no stream wait per step).
+  Status upload_gated(Buffer& dst, const void* pinned_src, size_t n, uint64_t ticket, size_t offset = 0) {
+    return st(infr_cuda_upload_gated(ctx_, dst.handle(), offset, pinned_src, n, ticket));
+  }
+  Status host_signal(uint64_t ticket) { return st(infr_cuda_host_signal(ctx_, ticket)); }
+  Status host_step(uint64_t ticket, void* stage, const void* rows, size_t n) { return st(infr_cuda_host_step(ctx_, ticket, stage, rows, n)); }
+  Status host_reset() { return st(infr_cuda_host_reset(ctx_)); }
+
   infr_cuda_ctx* raw() const { return ctx_; }
 
  private:
