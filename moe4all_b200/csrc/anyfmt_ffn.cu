@@ -222,13 +222,8 @@ __global__ void __launch_bounds__(256, 3) k_anyfmt_down(DecodeParams p) {
         const float m = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
         const float inv = m > 0.f ? 32639.f / m : 0.f;
         const int X[4] = {__float2int_rn(v.x * inv), __float2int_rn(v.y * inv), __float2int_rn(v.z * inv), __float2int_rn(v.w * inv)};
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const int hh = (X[t] + 128) >> 8, ll = X[t] - (hh << 8);
-          lo |= (uint32_t)(ll & 0xFF) << (8 * t);
-          hi |= (uint32_t)(hh & 0xFF) << (8 * t);
-        }
+        uint32_t lo, hi;
+        pack_limbs4(X, lo, hi);
         s_lo[c * 32 + lane] = lo;
         s_hi[c * 32 + lane] = hi;
         int sx = (X[0] + X[1]) + (X[2] + X[3]);  // 16 elements sit in four neighbouring lanes

@@ -131,6 +131,16 @@ __device__ __forceinline__ float f16_bits_to_f32(uint32_t h) {
   return __half2float(__ushort_as_half(static_cast<unsigned short>(h & 0xFFFFu)));
 }
 
+// Four 16-bit fixed-point values X (|X| <= 32639) as signed 8-bit limbs, X = 256 hi + lo with lo in [-128, 127]:
+// hi = (X + 128) >> 8 and lo = X - 256 hi, i.e. with Y = X + 128 the second byte of Y and the first byte of Y
+// with its top bit flipped.  Byte t of `lo` / `hi` belongs to X[t].
+__device__ __forceinline__ void pack_limbs4(const int (&X)[4], uint32_t& lo, uint32_t& hi) {
+  const uint32_t p01 = __byte_perm((uint32_t)(X[0] + 128), (uint32_t)(X[1] + 128), 0x5140);  // Y0.b0 Y1.b0 Y0.b1 Y1.b1
+  const uint32_t p23 = __byte_perm((uint32_t)(X[2] + 128), (uint32_t)(X[3] + 128), 0x5140);
+  lo = __byte_perm(p01, p23, 0x5410) ^ 0x80808080u;
+  hi = __byte_perm(p01, p23, 0x7632);
+}
+
 // ---- mbarrier + bulk async copy (TMA, untiled form; never multicast) --------------------------
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

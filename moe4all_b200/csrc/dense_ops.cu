@@ -208,13 +208,8 @@ __global__ void __launch_bounds__(256) k_quantize_rows(const float* __restrict__
     const float4 v = xr[i];
     const int X[4] = {__float2int_rn(v.x * q_inv), __float2int_rn(v.y * q_inv), __float2int_rn(v.z * q_inv),
                       __float2int_rn(v.w * q_inv)};
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const int h = (X[t] + 128) >> 8, l = X[t] - (h << 8);
-      lo |= (uint32_t)(l & 0xFF) << (8 * t);
-      hi |= (uint32_t)(h & 0xFF) << (8 * t);
-    }
+    uint32_t lo, hi;
+    pack_limbs4(X, lo, hi);
     lo_row[i] = lo;
     hi_row[i] = hi;
   }

@@ -452,13 +452,8 @@ __global__ void __launch_bounds__(EM_DN_WARPS * 32) k_em_down(EmParams p, int ro
         for (int i = tid; i < n4; i += EM_DN_WARPS * 32) {
           const float4 v = __ldcg(arow + i);
           const int X[4] = {__float2int_rn(v.x * inv), __float2int_rn(v.y * inv), __float2int_rn(v.z * inv), __float2int_rn(v.w * inv)};
-          uint32_t lo = 0, hi = 0;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int hh = (X[q] + 128) >> 8, ll = X[q] - (hh << 8);
-            lo |= (uint32_t)(ll & 0xFF) << (8 * q);
-            hi |= (uint32_t)(hh & 0xFF) << (8 * q);
-          }
+          uint32_t lo, hi;
+          pack_limbs4(X, lo, hi);
           *reinterpret_cast<uint32_t*>(s_act + (size_t)tk * apitch + 4 * i) = lo;
           *reinterpret_cast<uint32_t*>(s_act + (size_t)(8 + tk) * apitch + 4 * i) = hi;
           int sx = (X[0] + X[1]) + (X[2] + X[3]);  // 16 elements = four neighbouring threads (n4 is a multiple of 64: whole warps)
