@@ -165,6 +165,32 @@ impl CudaBackend {
         self.ctx.check(unsafe { ffi::infr_cuda_ep_finalize(self.ctx.raw) })
     }
 
+    /// Host-paced plans: the steps of a decode loop are recorded once (`gated_upload`, the ops,
+    /// `host_signal` per step, tickets 1, 2, ...) and launched once; per token the host then only writes the
+    /// step's rows into the pinned staging range and calls `host_step` - no launch and no stream wait.
+    /// `src` must be pinned host memory, 16-byte aligned, at most 256 KB.
+    pub fn gated_upload(&self, dst: &CudaBuffer, src: *const u8, n: usize, ticket: u64) -> Result<()> {
+        let _g = self.lock();
+        self.ctx.check(unsafe { ffi::infr_cuda_upload_gated(self.ctx.raw, dst.raw, 0, src as *const _, n, ticket) })
+    }
+
+    pub fn host_signal(&self, ticket: u64) -> Result<()> {
+        let _g = self.lock();
+        self.ctx.check(unsafe { ffi::infr_cuda_host_signal(self.ctx.raw, ticket) })
+    }
+
+    /// Copy `rows` into the pinned staging range, ring `ticket`, wait (bounded) for its signal.  Not under the
+    /// backend's lock: the pacing thread spins here while the recorded plan runs.
+    pub fn host_step(&self, ticket: u64, stage: *mut u8, rows: &[u8]) -> Result<()> {
+        self.ctx.check(unsafe { ffi::infr_cuda_host_step(self.ctx.raw, ticket, stage as *mut _, rows.as_ptr() as *const _, rows.len()) })
+    }
+
+    /// Drain the stream and set the pacing words back to zero (before a plan whose tickets start again at 1).
+    pub fn host_reset(&self) -> Result<()> {
+        let _g = self.lock();
+        self.ctx.check(unsafe { ffi::infr_cuda_host_reset(self.ctx.raw) })
+    }
+
     /// Tuning switches (`infr_cuda_config`), read - modify - write.
     pub fn configure(&self, f: impl FnOnce(&mut ffi::infr_cuda_config)) -> Result<()> {
         let _g = self.lock();
