@@ -136,6 +136,7 @@ extern "C" {
     pub fn infr_cuda_host_ring(ctx: *mut infr_cuda_ctx, ticket: u64) -> i32;
     pub fn infr_cuda_host_await(ctx: *mut infr_cuda_ctx, ticket: u64) -> i32;
     pub fn infr_cuda_host_reset(ctx: *mut infr_cuda_ctx) -> i32;
+    pub fn infr_cuda_host_steps(ctx: *mut infr_cuda_ctx, first_ticket: u64, count: u32, stage: *mut c_void, rows: *const *const c_void, n_in: usize, result: *const c_void, results_out: *const *mut c_void, n_out: usize) -> i32;
     pub fn infr_cuda_host_step(ctx: *mut infr_cuda_ctx, ticket: u64, stage: *mut c_void, rows: *const c_void, n: usize) -> i32;
     pub fn infr_cuda_sync(ctx: *mut infr_cuda_ctx) -> i32;
 

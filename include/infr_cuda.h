@@ -162,6 +162,12 @@ int32_t infr_cuda_host_reset(infr_cuda_ctx* ctx);
 /* One step in one call: copy `n` bytes of `rows` into the pinned staging range `stage` (skipped when `rows`
  * is NULL), ring `ticket`, await `ticket`. */
 int32_t infr_cuda_host_step(infr_cuda_ctx* ctx, uint64_t ticket, void* stage, const void* rows, size_t n);
+/* `count` consecutive steps in one call, tickets first_ticket, first_ticket + 1, ...: step i copies `n_in` bytes
+ * of rows[i] into `stage`, rings and awaits its ticket, then (results_out not NULL) copies the step's `n_out`
+ * result bytes from `result` (the pinned range the recorded step writes) to results_out[i].  For hosts that know
+ * a run of inputs in advance (teacher-forced evaluation, benchmarks); stops at the first error. */
+int32_t infr_cuda_host_steps(infr_cuda_ctx* ctx, uint64_t first_ticket, uint32_t count, void* stage, const void* const* rows, size_t n_in,
+                             const void* result, void* const* results_out, size_t n_out);
 /* Backend::sync (backend.rs:1006). */
 int32_t infr_cuda_sync(infr_cuda_ctx* ctx);
 

@@ -328,6 +328,10 @@ class Backend {
   }
   Status host_signal(uint64_t ticket) { return st(infr_cuda_host_signal(ctx_, ticket)); }
   Status host_step(uint64_t ticket, void* stage, const void* rows, size_t n) { return st(infr_cuda_host_step(ctx_, ticket, stage, rows, n)); }
+  Status host_steps(uint64_t first_ticket, uint32_t count, void* stage, const void* const* rows, size_t n_in, const void* result = nullptr,
+                    void* const* results_out = nullptr, size_t n_out = 0) {
+    return st(infr_cuda_host_steps(ctx_, first_ticket, count, stage, rows, n_in, result, results_out, n_out));
+  }
   Status host_reset() { return st(infr_cuda_host_reset(ctx_)); }
 
   infr_cuda_ctx* raw() const { return ctx_; }

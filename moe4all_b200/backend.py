@@ -26,7 +26,7 @@ EXPORTS = [
     "infr_cuda_set_stream", "infr_cuda_alloc", "infr_cuda_wrap", "infr_cuda_free",
     "infr_cuda_buf_len", "infr_cuda_buf_ptr", "infr_cuda_upload", "infr_cuda_download",
     "infr_cuda_upload_async", "infr_cuda_download_async",
-    "infr_cuda_upload_gated", "infr_cuda_host_signal", "infr_cuda_host_ring", "infr_cuda_host_await", "infr_cuda_host_reset", "infr_cuda_host_step",
+    "infr_cuda_upload_gated", "infr_cuda_host_signal", "infr_cuda_host_ring", "infr_cuda_host_await", "infr_cuda_host_reset", "infr_cuda_host_step", "infr_cuda_host_steps",
     "infr_cuda_gguf_open", "infr_cuda_gguf_close", "infr_cuda_gguf_tensor_count", "infr_cuda_gguf_find",
     "infr_cuda_gguf_meta_u64", "infr_cuda_gguf_meta_f64", "infr_cuda_gguf_meta_str", "infr_cuda_gguf_upload",
     "infr_cuda_sync", "infr_cuda_moe_ffn", "infr_cuda_moe_route", "infr_cuda_linear",
@@ -174,6 +174,7 @@ def load_library(path: Optional[str] = None):
     L.infr_cuda_host_await.argtypes = [vp, C.c_uint64]
     L.infr_cuda_host_reset.argtypes = [vp]
     L.infr_cuda_host_step.argtypes = [vp, C.c_uint64, vp, vp, sz]
+    L.infr_cuda_host_steps.argtypes = [vp, C.c_uint64, C.c_uint32, vp, C.POINTER(C.c_void_p), sz, vp, C.POINTER(C.c_void_p), sz]
     L.infr_cuda_sync.argtypes = [vp]
     L.infr_cuda_moe_ffn.argtypes = [vp, C.POINTER(_Desc)]
     L.infr_cuda_moe_route.argtypes = [vp, C.POINTER(_Desc)]
@@ -426,6 +427,15 @@ class CudaBackend:
     def host_step(self, ticket: int, stage_ptr: int, rows_ptr: int, nbytes: int) -> None:
         """One step in one call: rows -> pinned staging range, ring, await."""
         self._check(self._lib.infr_cuda_host_step(self._ctx, ticket, stage_ptr, rows_ptr, nbytes))
+
+    def host_steps(self, first_ticket: int, stage_ptr: int, row_ptrs, nbytes_in: int, result_ptr: int = 0, result_out_ptrs=None,
+                   nbytes_out: int = 0) -> None:
+        """`len(row_ptrs)` consecutive steps in one call (inputs known in advance); each step's result is copied
+        from the pinned range `result_ptr` to `result_out_ptrs[i]` when given."""
+        n = len(row_ptrs)
+        rows = (C.c_void_p * n)(*row_ptrs)
+        outs = (C.c_void_p * n)(*result_out_ptrs) if result_out_ptrs is not None else None
+        self._check(self._lib.infr_cuda_host_steps(self._ctx, first_ticket, n, stage_ptr, rows, nbytes_in, result_ptr or None, outs, nbytes_out))
 
     def host_reset(self) -> None:
         """Drain the stream and set both pacing words back to zero (before a plan whose tickets restart at 1)."""

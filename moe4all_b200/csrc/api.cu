@@ -368,6 +368,17 @@ int32_t infr_cuda_host_step(infr_cuda_ctx* ctx, uint64_t ticket, void* stage, co
   return infr_cuda_host_await(ctx, ticket);
 }
 
+int32_t infr_cuda_host_steps(infr_cuda_ctx* ctx, uint64_t first_ticket, uint32_t count, void* stage, const void* const* rows, size_t n_in,
+                             const void* result, void* const* results_out, size_t n_out) {
+  if (!ctx || !stage || !rows || (results_out && !result)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "host_steps: null argument");
+  for (uint32_t i = 0; i < count; ++i) {
+    const int32_t rc = infr_cuda_host_step(ctx, first_ticket + i, stage, rows[i], n_in);
+    if (rc) return rc;
+    if (results_out && results_out[i] && n_out) std::memcpy(results_out[i], result, n_out);
+  }
+  return INFR_CUDA_OK;
+}
+
 int32_t infr_cuda_host_reset(infr_cuda_ctx* ctx) {
   if (!ctx) return INFR_CUDA_ERR_INVALID_ARG;
   if (ctx->capturing) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "host_reset: not while recording");

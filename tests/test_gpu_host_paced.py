@@ -53,6 +53,14 @@ def test_paced_steps_match_oracle(backend, rows, host_dst):
     plan = be.graph_end()
     xs = [synth.activations(300 + s, rows, L.ne) for s in range(steps)]
     want = [oracle_layer(L, x, 4).dst for x in xs]
+    # a run of steps in one call, every step's result copied out
+    outs = [np.empty(n, np.float32) for _ in range(steps)]
+    be.host_reset()
+    be.execute(plan)
+    be.host_steps(1, stage_ptr, [x.ctypes.data for x in xs], n * 4, out_ptr, [o.ctypes.data for o in outs], n * 4)
+    be.sync()
+    for s in range(steps):
+        assert_close(outs[s].reshape(rows, L.ne), want[s])
     for rep in range(2):  # the second replay checks that the words were set back
         be.host_reset()
         be.execute(plan)
