@@ -632,7 +632,7 @@ def run_ours(args):
     kernel_us = {}
     n_k = 200
     # from n_expert / n_used rows on, the small-m path runs its expert-major kernels (the library's own rule)
-    em = banks_tuned() and BANKS[2] == 14 and N_EXPERT <= R * N_USED and R * N_USED * 8 < N_EXPERT * 88
+    em = banks_tuned() and N_EXPERT <= R * N_USED and R * N_USED * 8 < N_EXPERT * 88
     router = "k_router_mid" if 8 < R <= 64 else "k_router_small"  # (beyond 64 rows: the batched router's three kernels)
     names = (router, "k_em_bucket + k_em_gateup", "k_em_down + k_em_combine") if em else \
             (router, "k_decode_gateup", "k_decode_down") if banks_tuned() else \

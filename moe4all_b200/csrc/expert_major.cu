@@ -369,7 +369,12 @@ __global__ void __launch_bounds__((EM_GU_WARPS + 1) * 32) k_em_gateup(EmParams p
 // word boundary: fragment words are two aligned loads and a funnel shift.  A 16-element scale group is one
 // m16n8k16 MMA per limb; scales are applied in integers and converted once per block (bounded: 16 groups x
 // 128 x 16 x 63 x 128 < 2^31).
+// Q4 = the down banks are Q4_K (the other half of the layers of a Q4_K_M file): 144-byte blocks on 16-byte
+// boundaries, so fragment words are plain loads; a 32-element scale group is one m16n8k32 MMA per limb, its
+// 6-bit scale and min applied in integers (8 groups x 32 x 15 x 63 x 128 and 8 x 63 x 32 x 32639, both < 2^31).
+template <bool Q4>
 __global__ void __launch_bounds__(EM_DN_WARPS * 32) k_em_down(EmParams p, int rows_cta, int apitch, uint32_t slab_pitch) {
+  constexpr uint32_t DBB = Q4 ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t s_bar[2];
   __shared__ int s_pair[8];
@@ -403,13 +408,13 @@ __global__ void __launch_bounds__(EM_DN_WARPS * 32) k_em_down(EmParams p, int ro
     const int e = __ldcg(p.seg_expert + seg);
     const bool shared_seg = e >= p.n_expert;
     nff_e = shared_seg ? p.sh_ff : p.nff;
-    return (shared_seg ? p.sh_down : p.down + (size_t)e * p.down_stride) + (size_t)tile * rows_cta * (nff_e / 256 * (int)Q6K_BLOCK_BYTES);
+    return (shared_seg ? p.sh_down : p.down + (size_t)e * p.down_stride) + (size_t)tile * rows_cta * (nff_e / 256 * (int)DBB);
   };
   // a slab lands at its source's offset inside a 128-byte line
   auto request = [&](int job, int buf) {
     int nff_e;
     const uint8_t* src = job_src(job, nff_e);
-    const uint32_t bytes = (uint32_t)rows_cta * (nff_e / 256 * Q6K_BLOCK_BYTES);
+    const uint32_t bytes = (uint32_t)rows_cta * (nff_e / 256 * DBB);
     mbar_arrive_expect_tx(&s_bar[buf], bytes);
     bulk_g2s(slab_area + (size_t)buf * slab_pitch + (uint32_t)(reinterpret_cast<uintptr_t>(src) & 127u), src, bytes, &s_bar[buf]);
   };
@@ -423,7 +428,7 @@ __global__ void __launch_bounds__(EM_DN_WARPS * 32) k_em_down(EmParams p, int ro
     int nff_e;
     const uint8_t* src = job_src(job, nff_e);
     const unsigned char* slab = slab_area + (size_t)buf * slab_pitch + (uint32_t)(reinterpret_cast<uintptr_t>(src) & 127u);
-    const int drb = nff_e / 256 * (int)Q6K_BLOCK_BYTES;
+    const int drb = nff_e / 256 * (int)DBB;
     __syncthreads();  // every warp is done with the previous job: its slab buffer (the other one) and the limbs may be reused
     if (tid == 0 && job + 1 < job1) request(job + 1, buf ^ 1);
     if (seg != cur_seg) {
@@ -479,7 +484,50 @@ __global__ void __launch_bounds__(EM_DN_WARPS * 32) k_em_down(EmParams p, int ro
     const int rt = warp % n_rt, ks = warp / n_rt;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const uint32_t rofs[2] = {(uint32_t)(rt * 16 + g) * drb, (uint32_t)(rt * 16 + g + 8) * drb};
-    for (int b = ks; b < nb; b += ksplit) {
+    for (int b = ks; Q4 && b < nb; b += ksplit) {
+      // rows g and g + 8 of the tile: header (d, dmin, 12 scale bytes), then per 64 weights 32 code bytes whose
+      // low nibbles are the first 32-element group and high nibbles the second
+      const unsigned char* blk[2] = {slab + rofs[0] + (uint32_t)b * Q4K_BLOCK_BYTES, slab + rofs[1] + (uint32_t)b * Q4K_BLOCK_BYTES};
+      const uint4 hdr[2] = {*reinterpret_cast<const uint4*>(blk[0]), *reinterpret_cast<const uint4*>(blk[1])};
+      int svl[4] = {0, 0, 0, 0}, svh[4] = {0, 0, 0, 0}, mv[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t scp[2], mp[2], w0[2], w1[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          q4k_scale_min_pair(hdr[r].y, hdr[r].z, hdr[r].w, j, scp[r], mp[r]);
+          w0[r] = *reinterpret_cast<const uint32_t*>(blk[r] + 16 + 32 * j + 4 * t);       // k = 4 t .. 4 t + 3 of a group
+          w1[r] = *reinterpret_cast<const uint32_t*>(blk[r] + 32 + 32 * j + 4 * t);       // k = 16 + 4 t ..
+        }
+#pragma unroll
+        for (int hn = 0; hn < 2; ++hn) {
+          const int k0 = b * 256 + j * 64 + hn * 32, grp = k0 >> 4;
+          const uint32_t a00 = (w0[0] >> (4 * hn)) & 0x0F0F0F0Fu, a10 = (w0[1] >> (4 * hn)) & 0x0F0F0F0Fu,
+                         a01 = (w1[0] >> (4 * hn)) & 0x0F0F0F0Fu, a11 = (w1[1] >> (4 * hn)) & 0x0F0F0F0Fu;
+          const uint32_t b0l = *reinterpret_cast<const uint32_t*>(alo + k0), b1l = *reinterpret_cast<const uint32_t*>(alo + k0 + 16);
+          const uint32_t b0h = *reinterpret_cast<const uint32_t*>(ahi + k0), b1h = *reinterpret_cast<const uint32_t*>(ahi + k0 + 16);
+          int cl[4] = {0, 0, 0, 0}, ch[4] = {0, 0, 0, 0};
+          mma_u8s8_k32(cl, a00, a10, a01, a11, b0l, b1l);
+          mma_u8s8_k32(ch, a00, a10, a01, a11, b0h, b1h);
+          const int m0 = sum0[grp] + sum0[grp + 1], m1 = sum1[grp] + sum1[grp + 1];
+          const int scv[2] = {(int)((scp[0] >> (8 * hn)) & 0xFFu), (int)((scp[1] >> (8 * hn)) & 0xFFu)};
+          const int mnv[2] = {(int)((mp[0] >> (8 * hn)) & 0xFFu), (int)((mp[1] >> (8 * hn)) & 0xFFu)};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            svl[i] += scv[i >> 1] * cl[i];
+            svh[i] += scv[i >> 1] * ch[i];
+            mv[i] += mnv[i >> 1] * ((i & 1) ? m1 : m0);
+          }
+        }
+      }
+      // sum over the block of d sc sum(q X) - dmin m sum(X), X = 256 hi + lo
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float d = f16_bits_to_f32(hdr[i >> 1].x), dmin = f16_bits_to_f32(hdr[i >> 1].x >> 16);
+        acc[i] = fmaf(d, fmaf(256.f, (float)svh[i], (float)svl[i]), fmaf(-dmin, (float)mv[i], acc[i]));
+      }
+    }
+    for (int b = ks; !Q4 && b < nb; b += ksplit) {
       // per row: aligned view of the block, the shift that realigns it, d and the 16 scales
       const uint32_t* wq[2];
       uint32_t sh[2];
@@ -624,10 +672,10 @@ void gateup_shape(int ne, int* KB, int* S, int* xpitch, size_t* stage_bytes) {
 
 // Rows of the down matrix per job: 64 (one 16-row tile per warp) while two slab buffers and the activation
 // limbs leave room for two CTAs per SM, else 32 or 16 with the blocks split over the warps.
-int down_rows(int ne, int nffmax, int* apitch, size_t* slab_pitch, size_t* smem) {
+int down_rows(int ne, int nffmax, size_t dbb, int* apitch, size_t* slab_pitch, size_t* smem) {
   *apitch = nffmax + 16;  // 4 (mod 32) words
   const size_t fixed = (size_t)16 * *apitch + (size_t)8 * (nffmax / 16 + 4) * 4 + 256;
-  const size_t drb = (size_t)nffmax / 256 * Q6K_BLOCK_BYTES;
+  const size_t drb = (size_t)nffmax / 256 * dbb;
   const int nb = nffmax / 256;
   for (int rows : {64, 32, 16}) {
     if (ne % rows) continue;
@@ -656,10 +704,10 @@ size_t em_scratch_bytes(int rows, int n_used, int ne, int nff, int sh_ff) {
 }
 
 bool em_supported(int ne, int nff, int sh_ff, int n_expert, BankTypes bt) {
-  if (!bt.tuned() || bt.down_q4k() || ne % 256 || nff % 256 || sh_ff % 256 || n_expert > 1024) return false;
+  if (!bt.tuned() || ne % 256 || nff % 256 || sh_ff % 256 || n_expert > 1024) return false;
   int apitch;
   size_t slab_pitch, smem;
-  return down_rows(ne, std::max(nff, sh_ff), &apitch, &slab_pitch, &smem) != 0;
+  return down_rows(ne, std::max(nff, sh_ff), bt.down_q4k() ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES, &apitch, &slab_pitch, &smem) != 0;
 }
 
 int32_t launch_em_ffn(infr_cuda_ctx* ctx, const DecodeParams& dp, void* scratch, uint32_t stages) {
@@ -733,14 +781,18 @@ int32_t launch_em_ffn(infr_cuda_ctx* ctx, const DecodeParams& dp, void* scratch,
   {
     int apitch;
     size_t slab_pitch, smem;
-    const int rows_cta = down_rows(dp.ne, (int)nffmax, &apitch, &slab_pitch, &smem);
+    const int rows_cta = down_rows(dp.ne, (int)nffmax, dp.down_q4k ? Q4K_BLOCK_BYTES : Q6K_BLOCK_BYTES, &apitch, &slab_pitch, &smem);
     if (!rows_cta) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "expert-major down kernel: tile does not fit shared memory");
     const unsigned jobs_bound = (unsigned)n_seg_bound * (unsigned)(dp.ne / rows_cta);
     const unsigned per_sm = (unsigned)std::max<size_t>(1, std::min<size_t>(4, (200 * 1024) / smem));
-    e = ensure_smem(reinterpret_cast<const void*>(k_em_down), smem);
-    if (e == cudaSuccess)
-      e = launch_ex(k_em_down, dim3(std::min(jobs_bound, per_sm * (unsigned)ctx->sm_count)), dim3(EM_DN_WARPS * 32), smem, ctx->stream, true, p,
-                    rows_cta, apitch, (uint32_t)slab_pitch);
+    auto run_dn = [&](auto kern) {
+      cudaError_t ee = ensure_smem(reinterpret_cast<const void*>(kern), smem);
+      if (ee == cudaSuccess)
+        ee = launch_ex(kern, dim3(std::min(jobs_bound, per_sm * (unsigned)ctx->sm_count)), dim3(EM_DN_WARPS * 32), smem, ctx->stream, true, p,
+                       rows_cta, apitch, (uint32_t)slab_pitch);
+      return ee;
+    };
+    e = dp.down_q4k ? run_dn(k_em_down<true>) : run_dn(k_em_down<false>);
     ctx->launches += 1;
     if (e != cudaSuccess) return check_cuda(ctx, e, "k_em_down launch");
   }

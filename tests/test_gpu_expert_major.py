@@ -54,6 +54,22 @@ def test_config1_shape(em, rows):
     assert_close(out2[keep], oracle_layer(L, x, 8, shared=False).dst[keep])
 
 
+@pytest.mark.parametrize("rows", [1, 5, 24, 64])
+@pytest.mark.parametrize("dims", [(512, 16, 256, 256, 4), (2048, 32, 512, 512, 8), (1024, 16, 768, 256, 4)])
+def test_q4k_down_banks(em, rows, dims):
+    # the other half of a Q4_K_M file's layers: down banks in Q4_K (144-byte blocks, scale and min per 32 weights);
+    # one, two and three blocks per row, shared expert narrower than the routed ones in the last case
+    ne, n_expert, nff, sh_ff, n_used = dims
+    L = synth.make_layer(71, ne, n_expert, nff, sh_ff=sh_ff, down_q4k=True, router_std=0.05)
+    x = synth.activations(400 + rows, rows, ne)
+    n0 = em.launch_count()
+    out, ids, wts = GpuLayer(em, L).run(x, n_used, path=1)
+    assert em.launch_count() - n0 == 5  # router, bucket, gate/up, down, combine: the expert-major kernels ran
+    ref = oracle_layer(L, x, n_used)
+    keep = check_ids(ids, ref, n_used)
+    assert_close(out[keep], ref.dst[keep])
+
+
 def test_matches_per_pair_kernels_closely(backend):
     # both forms use the same fixed-point activations for gate/up; they differ in the granularity of the
     # down kernel's activation scales (one per row against one per 128 elements), so they agree far inside the oracle bound
