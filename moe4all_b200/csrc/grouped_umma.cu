@@ -169,8 +169,9 @@ __device__ __forceinline__ void warp_store_rows(unsigned char* patch, const uint
 constexpr int GU_SA = 3, GU_SB = 2;                          // weight stages, token stages
 constexpr uint32_t GU_A_STAGE_BYTES = 2 * A_TILE_BYTES;      // gate tile + up tile, 32 KB
 
-// GENERAL = false is the common form (SiLU, no clamp): its epilogue has no other arm.
-template <bool GENERAL>
+// GENERAL = false is the common form (SiLU, no clamp): its epilogue has no other arm.  TRACED = false leaves
+// the phase stamps out of the K loop altogether (they are only wanted while a trace buffer is set).
+template <bool GENERAL, bool TRACED>
 __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, const __grid_constant__ CUtensorMap tm_gate,
                                                              const __grid_constant__ CUtensorMap tm_up,
                                                              const __grid_constant__ CUtensorMap tm_sh_gate,
@@ -181,7 +182,7 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
   __shared__ uint32_t s_tmem;
   const int tile = blockIdx.y;
   if (tile >= *p.n_tiles) return;
-  trace_stamp((blockIdx.x == 0 && blockIdx.y == p.trace_tile) ? p.trace : nullptr, 40);
+  if (TRACED) trace_stamp((blockIdx.x == 0 && blockIdx.y == p.trace_tile) ? p.trace : nullptr, 40);
   unsigned char* a_stages = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* b_stages = a_stages + GU_SA * GU_A_STAGE_BYTES;
   const int e = p.tile_expert[tile], rows_valid = p.tile_rows[tile];
@@ -275,12 +276,12 @@ __global__ void __launch_bounds__(U_THREADS, 1) k_umma_gateup(GroupedParams p, c
     }
   };
   const int k_steps = p.ne / UK;
-  unsigned long long* trc = (blockIdx.x == 0 && blockIdx.y == p.trace_tile) ? p.trace : nullptr;
+  unsigned long long* trc = (TRACED && blockIdx.x == 0 && blockIdx.y == p.trace_tile) ? p.trace : nullptr;
   trace_stamp(trc, 41);
   bool ok = run_pipeline<GU_SA, GU_SB>(bars, a_stages, GU_A_STAGE_BYTES, b_stages,
                                        reinterpret_cast<const unsigned char*>(p.xg) + tile_step_offset(tile, k_steps, 0),
                                        (size_t)UN * 128, (uint32_t)n_eff * 128u, k_steps, unpack, issue,
-                                       trc);
+                                       TRACED ? trc : nullptr);
   trace_stamp(trc, 42);
 
   // epilogue: a thread's accumulator row is a token; its 64 gate and 64 up values per feature half
@@ -609,8 +610,10 @@ int32_t launch_umma_grouped(infr_cuda_ctx* ctx, const GroupedParams& p, int max_
   const size_t smem_dn = 1024 + (size_t)DN_SA * DN_W_STAGE_BYTES +
                          (p.down_q4k ? (size_t)2 * B_TILE_BYTES + (size_t)DM * Q4K_BLOCK_BYTES : (size_t)DN_SB * B_TILE_BYTES);
   const bool general = p.act_kind != INFR_CUDA_ACT_SILU || p.clamp > 0.f;
-  cudaError_t e = general ? ensure_smem(reinterpret_cast<const void*>(k_umma_gateup<true>), smem_gu)
-                          : ensure_smem(reinterpret_cast<const void*>(k_umma_gateup<false>), smem_gu);
+  const bool traced = p.trace != nullptr;
+  auto gu_kernel = general ? (traced ? k_umma_gateup<true, true> : k_umma_gateup<true, false>)
+                           : (traced ? k_umma_gateup<false, true> : k_umma_gateup<false, false>);
+  cudaError_t e = ensure_smem(reinterpret_cast<const void*>(gu_kernel), smem_gu);
   if (e == cudaSuccess)
     e = p.down_q4k ? ensure_smem(reinterpret_cast<const void*>(k_umma_down<true>), smem_dn)
                    : ensure_smem(reinterpret_cast<const void*>(k_umma_down<false>), smem_dn);
@@ -637,10 +640,7 @@ int32_t launch_umma_grouped(infr_cuda_ctx* ctx, const GroupedParams& p, int max_
     if (ok && p.sh_down) ok = q4k_rows_map(&tm_sh_down, p.sh_down, (size_t)p.ne, drb, DM);
   }
   if (!ok) return fail(ctx, INFR_CUDA_ERR_CUDA, "grouped GEMM: the driver refused a tensor map for the expert banks");
-  if (general)
-    k_umma_gateup<true><<<dim3(p.nff / UM, max_tiles), U_THREADS, smem_gu, ctx->stream>>>(p, tm_gate, tm_up, tm_sh_gate, tm_sh_up);
-  else
-    k_umma_gateup<false><<<dim3(p.nff / UM, max_tiles), U_THREADS, smem_gu, ctx->stream>>>(p, tm_gate, tm_up, tm_sh_gate, tm_sh_up);
+  gu_kernel<<<dim3(p.nff / UM, max_tiles), U_THREADS, smem_gu, ctx->stream>>>(p, tm_gate, tm_up, tm_sh_gate, tm_sh_up);
   if (p.down_q4k)
     k_umma_down<true><<<dim3(p.ne / DM, max_tiles), U_THREADS, smem_dn, ctx->stream>>>(p, tm_down, tm_sh_down);
   else
