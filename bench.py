@@ -48,9 +48,11 @@ Q4K_ROW = NE // 256 * 144      # bytes of one gate/up row
 Q6K_ROW = N_FF // 256 * 210    # bytes of one down row
 EXPERT_BYTES = 2 * N_FF * Q4K_ROW + NE * Q6K_ROW  # 2 039 808
 # --banks: GGUF type numbers and (elements, bytes) per block of the formats an expert bank may have
-BANK_TYPES = {"q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8, "q2k": 10, "q3k": 11, "q4k": 12, "q5k": 13, "q6k": 14, "iq4_nl": 20, "iq4_xs": 23, "mxfp4": 39, "nvfp4": 40, "q2_0": 42}
+BANK_TYPES = {"q4_0": 2, "q4_1": 3, "q5_0": 6, "q5_1": 7, "q8_0": 8, "q2k": 10, "q3k": 11, "q4k": 12, "q5k": 13, "q6k": 14, "iq4_nl": 20, "iq4_xs": 23, "mxfp4": 39, "nvfp4": 40, "q2_0": 42,
+              "iq2_xs": 17, "iq2_s": 22, "iq3_xxs": 18, "iq3_s": 21}
 BANK_BLOCK = {2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176),
-              14: (256, 210), 20: (32, 18), 23: (256, 136), 39: (32, 17), 40: (64, 36), 42: (64, 18)}
+              14: (256, 210), 20: (32, 18), 23: (256, 136), 39: (32, 17), 40: (64, 36), 42: (64, 18),
+              17: (256, 74), 22: (256, 82), 18: (256, 98), 21: (256, 110)}
 BANKS = (12, 12, 14)           # gate, up, down of the layer workload (set from --banks)
 
 
@@ -186,6 +188,8 @@ def time_cpu(streams, steps, warmup, n_sets=2):
     """tok/s of the CPU oracle on `steps` steps of the layer workload (all host threads)."""
     from moe4all_b200 import synth
     from oracle import oracle as orc
+    for dt in sorted(set(BANKS) & set(synth.CODEBOOKS)):
+        orc.set_codebook(dt, synth.codebook(dt))
     layers = cpu_layers(n_sets)
     xs = [synth.activations(50 + i, streams, NE) for i in range(8)]
     for i in range(warmup):
@@ -309,7 +313,7 @@ class Env:
     def __init__(self):
         import torch
         import torch.distributed as dist
-        from moe4all_b200 import CudaBackend, build
+        from moe4all_b200 import CudaBackend, DType, build
         self.torch, self.dist = torch, dist
         self.world = int(os.environ.get("WORLD_SIZE", "1"))
         self.rank = int(os.environ.get("RANK", "0"))
@@ -320,6 +324,11 @@ class Env:
         self.dev = f"cuda:{self.local}"
         build.build()
         self.be = CudaBackend(self.local)
+        # --banks with a grid codebook format: the stand-in tables of synth.codebook (same shape and alphabet as
+        # the real ones, which a host of the reference would hand over)
+        from moe4all_b200 import synth as _synth
+        for dt in sorted(set(BANKS) & set(_synth.CODEBOOKS)):
+            self.be.set_codebook(DType(dt), _synth.codebook(dt))
         self.stream = torch.cuda.Stream()
         torch.cuda.set_stream(self.stream)
         self.be.set_stream(self.stream.cuda_stream)

@@ -51,6 +51,12 @@ extern "C" {
 #define INFR_CUDA_DT_MXFP4 39 /* 32 weights / 17 B, crates/infr-core/src/decode_spec.rs:361  */
 #define INFR_CUDA_DT_NVFP4 40 /* 64 weights / 36 B, crates/infr-core/src/decode_spec.rs:363  */
 #define INFR_CUDA_DT_Q2_0 42 /* 64 weights / 18 B, crates/infr-core/src/decode_spec.rs:358   */
+/* grid codebook formats (256 weights per block): usable once the format's grid table has been handed over
+ * with infr_cuda_set_codebook */
+#define INFR_CUDA_DT_IQ2XS 17  /* 74 B  */
+#define INFR_CUDA_DT_IQ3XXS 18 /* 98 B  */
+#define INFR_CUDA_DT_IQ3S 21   /* 110 B */
+#define INFR_CUDA_DT_IQ2S 22   /* 82 B  */
 
 /* MoeGating (crates/infr-core/src/graph.rs:73-85). */
 #define INFR_CUDA_GATING_SOFTMAX 0
@@ -109,6 +115,12 @@ typedef struct infr_cuda_config {
 } infr_cuda_config;
 int32_t infr_cuda_get_config(const infr_cuda_ctx* ctx, infr_cuda_config* out);
 int32_t infr_cuda_set_config(infr_cuda_ctx* ctx, const infr_cuda_config* cfg);
+/* The grid table of a codebook format (crates/infr-core/src/iquant_grids.rs: IQ2XS_GRID 512 x u64, IQ2S_GRID
+ * 1024 x u64, IQ3XXS_GRID 256 x u32, IQ3S_GRID 512 x u32; little-endian entries, one byte per weight, every
+ * byte below 128), copied to the device once.  `bytes` must be the table's exact size.  Banks and Linear
+ * weights of that dtype are INFR_CUDA_ERR_UNSUPPORTED until the table is there.  The tables are constants of
+ * the formats: every context of a device sees the last one set. */
+int32_t infr_cuda_set_codebook(infr_cuda_ctx* ctx, int32_t dtype, const void* table, size_t bytes);
 
 /* ---- buffers: Backend::alloc / alloc_uninit / upload / download / sync ------------------------ */
 

@@ -26,7 +26,7 @@ EXPORTS = [
     "infr_cuda_set_stream", "infr_cuda_alloc", "infr_cuda_wrap", "infr_cuda_free",
     "infr_cuda_buf_len", "infr_cuda_buf_ptr", "infr_cuda_upload", "infr_cuda_download",
     "infr_cuda_upload_async", "infr_cuda_download_async",
-    "infr_cuda_upload_gated", "infr_cuda_host_signal", "infr_cuda_host_ring", "infr_cuda_host_await", "infr_cuda_host_reset", "infr_cuda_host_step", "infr_cuda_host_steps",
+    "infr_cuda_upload_gated", "infr_cuda_host_signal", "infr_cuda_host_ring", "infr_cuda_host_await", "infr_cuda_host_reset", "infr_cuda_host_step", "infr_cuda_host_steps", "infr_cuda_set_codebook",
     "infr_cuda_gguf_open", "infr_cuda_gguf_close", "infr_cuda_gguf_tensor_count", "infr_cuda_gguf_find",
     "infr_cuda_gguf_meta_u64", "infr_cuda_gguf_meta_f64", "infr_cuda_gguf_meta_str", "infr_cuda_gguf_upload",
     "infr_cuda_sync", "infr_cuda_moe_ffn", "infr_cuda_moe_route", "infr_cuda_linear",
@@ -70,6 +70,10 @@ class DType(enum.IntEnum):
     MXFP4 = 39
     NVFP4 = 40
     Q2_0 = 42
+    IQ2XS = 17
+    IQ3XXS = 18
+    IQ3S = 21
+    IQ2S = 22
 
     def row_bytes(self, n_elem: int) -> int:
         """crates/infr-core/src/decode_spec.rs:315-335: elements and bytes per block."""
@@ -78,7 +82,8 @@ class DType(enum.IntEnum):
         elems, nbytes = {DType.Q8_0: (32, 34), DType.Q4K: (256, 144), DType.Q5K: (256, 176), DType.Q6K: (256, 210),
                          DType.IQ4NL: (32, 18), DType.IQ4XS: (256, 136), DType.Q4_0: (32, 18), DType.Q4_1: (32, 20),
                          DType.Q5_0: (32, 22), DType.Q5_1: (32, 24), DType.Q2K: (256, 84), DType.Q3K: (256, 110), DType.MXFP4: (32, 17),
-                         DType.NVFP4: (64, 36), DType.Q2_0: (64, 18)}[self]
+                         DType.NVFP4: (64, 36), DType.Q2_0: (64, 18), DType.IQ2XS: (256, 74), DType.IQ2S: (256, 82),
+                         DType.IQ3XXS: (256, 98), DType.IQ3S: (256, 110)}[self]
         if n_elem % elems:
             raise ValueError(f"{self.name}: {n_elem} elements is not a whole number of {elems}-element blocks")
         return n_elem // elems * nbytes
@@ -173,6 +178,7 @@ def load_library(path: Optional[str] = None):
     L.infr_cuda_host_ring.argtypes = [vp, C.c_uint64]
     L.infr_cuda_host_await.argtypes = [vp, C.c_uint64]
     L.infr_cuda_host_reset.argtypes = [vp]
+    L.infr_cuda_set_codebook.argtypes = [vp, C.c_int32, vp, sz]
     L.infr_cuda_host_step.argtypes = [vp, C.c_uint64, vp, vp, sz]
     L.infr_cuda_host_steps.argtypes = [vp, C.c_uint64, C.c_uint32, vp, C.POINTER(C.c_void_p), sz, vp, C.POINTER(C.c_void_p), sz]
     L.infr_cuda_sync.argtypes = [vp]
@@ -466,6 +472,11 @@ class CudaBackend:
         return b
 
     # -- tuning switches ------------------------------------------------------------------------
+    def set_codebook(self, dtype: "DType", table: np.ndarray) -> None:
+        """Hand over the grid table of a codebook format (IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S) as its little-endian bytes."""
+        t = np.ascontiguousarray(table).view(np.uint8).reshape(-1)
+        self._check(self._lib.infr_cuda_set_codebook(self._ctx, int(dtype), t.ctypes.data_as(C.c_void_p), t.nbytes))
+
     def get_config(self) -> Config:
         c = Config()
         self._check(self._lib.infr_cuda_get_config(self._ctx, C.byref(c)))

@@ -339,4 +339,6 @@ int32_t launch_anyfmt_decode(infr_cuda_ctx* ctx, const DecodeParams& p, bool pdl
   return check_cuda(ctx, cudaGetLastError(), "generic-format small-m launch");
 }
 
+cudaError_t publish_codebooks_anyfmt(const unsigned char* const* tables) { return publish_codebooks(tables); }
+
 }  // namespace infr

@@ -77,6 +77,12 @@ struct DeviceGuard {
 
 bool fits(const infr_cuda_buf* b, size_t need) { return b && b->ptr && b->bytes >= need; }
 
+// A grid codebook format whose table the host has not handed over yet.
+bool codebook_missing(const infr_cuda_ctx* ctx, int32_t dt) {
+  const int slot = codebook_slot(dt);
+  return slot >= 0 && ctx->codebook[slot] == nullptr;
+}
+
 constexpr size_t HOST_WORDS_BYTES = 192;  // status words, bell word, done word: one 64-byte line each
 
 infr_cuda_config default_config() {
@@ -169,6 +175,8 @@ void infr_cuda_destroy(infr_cuda_ctx* ctx) {
   if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
+  for (unsigned char* t : ctx->codebook)
+    if (t) cudaFree(t);
   if (ctx->route_logits) cudaFree(ctx->route_logits);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
@@ -305,6 +313,25 @@ int32_t infr_cuda_download_async(infr_cuda_ctx* ctx, const infr_cuda_buf* src, s
     (void)cudaGetLastError();
   }
   return check_cuda(ctx, cudaMemcpyAsync(dst, sp, n, cudaMemcpyDeviceToHost, ctx->stream), "download (queued)");
+}
+
+int32_t infr_cuda_set_codebook(infr_cuda_ctx* ctx, int32_t dtype, const void* table, size_t bytes) {
+  if (!ctx || !table) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_codebook: null argument");
+  const int slot = codebook_slot(dtype);
+  if (slot < 0) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_codebook: not a grid codebook format (IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S)");
+  if (bytes != codebook_bytes(slot)) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_codebook: wrong table size for this format");
+  const unsigned char* tb = static_cast<const unsigned char*>(table);
+  for (size_t i = 0; i < bytes; ++i)
+    if (tb[i] >= 128) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_codebook: grid bytes must be below 128");
+  if (ctx->capturing) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_codebook: not while recording");
+  DeviceGuard g(ctx->device);
+  cudaError_t e = cudaStreamSynchronize(ctx->stream);  // no kernel reads a table while it changes
+  if (e == cudaSuccess && !ctx->codebook[slot]) e = cudaMalloc(reinterpret_cast<void**>(&ctx->codebook[slot]), bytes);
+  if (e == cudaSuccess) e = cudaMemcpy(ctx->codebook[slot], table, bytes, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = publish_codebooks_dense(ctx->codebook);
+  if (e == cudaSuccess) e = publish_codebooks_anyfmt(ctx->codebook);
+  if (e == cudaSuccess) e = publish_codebooks_grouped(ctx->codebook);
+  return check_cuda(ctx, e, "set_codebook");
 }
 
 int32_t infr_cuda_upload_gated(infr_cuda_ctx* ctx, infr_cuda_buf* dst, size_t dst_off, const void* src, size_t n, uint64_t ticket) {
@@ -509,7 +536,9 @@ int32_t validate_moe_ffn(infr_cuda_ctx* ctx, const infr_cuda_moe_ffn_desc* d, ui
   if (rc) return rc;
   if (!d->n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: zero n_ff_exp");
   if (!bank_dtype_ok(d->gate_dtype) || !bank_dtype_ok(d->up_dtype) || !bank_dtype_ok(d->down_dtype))
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS MXFP4 NVFP4 Q2_0");
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS MXFP4 NVFP4 Q2_0 IQ2_XS IQ2_S IQ3_XXS IQ3_S");
+  if (codebook_missing(ctx, d->gate_dtype) || codebook_missing(ctx, d->up_dtype) || codebook_missing(ctx, d->down_dtype))
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_ffn: a bank is in a grid codebook format whose table has not been set (infr_cuda_set_codebook)");
   if (d->fused_gate_up && d->gate_dtype != d->up_dtype)
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: a fused gate/up bank has one dtype");
   if (d->ne % 256 || d->n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_ffn: ne and n_ff_exp must be multiples of the 256-weight block");
@@ -850,6 +879,8 @@ int32_t infr_cuda_linear(infr_cuda_ctx* ctx, int32_t dtype, const infr_cuda_buf*
   if (!m || !in_f || !out_f) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: zero dimension");
   if (dtype != INFR_CUDA_DT_F32 && !block_elems(dtype))
     return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32 and the block formats an expert bank may have)");
+  if (codebook_missing(ctx, dtype))
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: the weight is in a grid codebook format whose table has not been set (infr_cuda_set_codebook)");
   if (dtype != INFR_CUDA_DT_F32 && in_f % block_elems(dtype))
     return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "linear: in_f must be a whole number of weight blocks (32, 64 or 256 weights)");
   const size_t rb = row_bytes(dtype, in_f);
@@ -907,9 +938,11 @@ int32_t infr_cuda_moe_expert_rows(infr_cuda_ctx* ctx, const infr_cuda_buf* x_row
   if (!n_local || !ne || !n_ff_exp) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: zero dimension");
   if (n_local > 1024) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: more than 1024 local experts");
   if (!bank_dtype_ok(gate_dtype) || !bank_dtype_ok(up_dtype) || !bank_dtype_ok(down_dtype))
-    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS MXFP4 NVFP4 Q2_0");
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: expert banks must be one of Q4_0 Q4_1 Q5_0 Q5_1 Q8_0 Q2_K Q3_K Q4_K Q5_K Q6_K IQ4_NL IQ4_XS MXFP4 NVFP4 Q2_0 IQ2_XS IQ2_S IQ3_XXS IQ3_S");
   if (ne % 256 || n_ff_exp % 256) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "moe_expert_rows: ne and n_ff_exp must be multiples of 256");
   if (!n_rows) return INFR_CUDA_OK;
+  if (codebook_missing(ctx, gate_dtype) || codebook_missing(ctx, up_dtype) || codebook_missing(ctx, down_dtype))
+    return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "moe_expert_rows: a bank is in a grid codebook format whose table has not been set (infr_cuda_set_codebook)");
   const size_t gb = (size_t)n_local * n_ff_exp * row_bytes(gate_dtype, ne), ub = (size_t)n_local * n_ff_exp * row_bytes(up_dtype, ne),
                db = (size_t)n_local * ne * row_bytes(down_dtype, n_ff_exp);
   if (!fits(x_rows, (size_t)n_rows * ne * 4) || !fits(y_rows, (size_t)n_rows * ne * 4) || !fits(seg_off, (size_t)(n_local + 1) * 4) ||

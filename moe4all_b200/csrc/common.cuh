@@ -71,6 +71,7 @@ struct infr_cuda_ctx {
   unsigned long long* trace = nullptr;        // optional phase stamps (see trace_stamp)
   infr_cuda_config cfg = {};                  // tuning switches (infr_cuda_set_config)
   infr::EpState* ep = nullptr;                // expert-parallel communicator and buffers, or null
+  unsigned char* codebook[4] = {nullptr, nullptr, nullptr, nullptr};  // device copies of the grid tables (formats.cuh slots)
 };
 
 namespace infr {
@@ -106,6 +107,10 @@ INFR_HD inline size_t row_bytes(int32_t dtype, size_t n_elem) {
     case INFR_CUDA_DT_MXFP4: return n_elem / 32 * 17;
     case INFR_CUDA_DT_NVFP4: return n_elem / 64 * 36;
     case INFR_CUDA_DT_Q2_0: return n_elem / 64 * 18;
+    case INFR_CUDA_DT_IQ2XS: return n_elem / 256 * 74;
+    case INFR_CUDA_DT_IQ2S: return n_elem / 256 * 82;
+    case INFR_CUDA_DT_IQ3XXS: return n_elem / 256 * 98;
+    case INFR_CUDA_DT_IQ3S: return n_elem / 256 * 110;
     default: return 0;
   }
 }

@@ -244,6 +244,10 @@ int32_t launch_linear(infr_cuda_ctx* ctx, int32_t dtype, const uint8_t* w, const
     case INFR_CUDA_DT_MXFP4:
     case INFR_CUDA_DT_NVFP4:
     case INFR_CUDA_DT_Q2_0:
+    case INFR_CUDA_DT_IQ2XS:
+    case INFR_CUDA_DT_IQ2S:
+    case INFR_CUDA_DT_IQ3XXS:
+    case INFR_CUDA_DT_IQ3S:
       k_linear_anyfmt<<<grid, block, 0, ctx->stream>>>(dtype, w, x, y, in_f, out_f, row_bytes(dtype, in_f));
       break;
     default: return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "linear: weight dtype not covered (F32 and the block formats an expert bank may have)");
@@ -368,6 +372,8 @@ int32_t launch_fetch_host(infr_cuda_ctx* ctx, const void* src_dev_view, void* ds
   ctx->launches += 1;
   return check_cuda(ctx, cudaGetLastError(), "k_fetch_host launch");
 }
+
+cudaError_t publish_codebooks_dense(const unsigned char* const* tables) { return publish_codebooks(tables); }
 
 int32_t launch_add(infr_cuda_ctx* ctx, const float* a, const float* b, float* dst, size_t n) {
   k_add<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(a, b, dst, n);

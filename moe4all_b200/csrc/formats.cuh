@@ -29,6 +29,17 @@
 //
 //   Q2_0    18 B / 64   code = 2 bits,                  A = d,      B = 0,         off = 1
 //
+// and the grid codebook formats (dequant.rs:477-488, 605-770): a group of 8 (IQ2) or 4 (IQ3) weights is one entry of
+// a grid table - eight or four small positive bytes - with a sign bit per weight, times the scale of its 16 or 32
+//
+//   IQ2_XS   74 B / 256  code = 128 +- grid2xs[9 bits][k],  A = d (0.5 + ls4) / 4,  signs = 7-bit index with its parity on top
+//   IQ2_S    82 B / 256  code = 128 +- grid2s[10 bits][k],  A = d (0.5 + ls4) / 4,  a sign byte per 8 weights
+//   IQ3_XXS  98 B / 256  code = 128 +- grid3xxs[8 bits][k], A = d (0.5 + ls4) / 2,  signs as IQ2_XS, scale per 32
+//   IQ3_S   110 B / 256  code = 128 +- grid3s[9 bits][k],   A = d (1 + 2 ls4),      a sign byte per 8 weights
+//
+// (B = 0, off = 128).  The grid tables are constants of the formats that this library does not carry: the host
+// hands them over once (infr_cuda_set_codebook) and the kernels read them through pointers in constant memory.
+//
 // The generic small-m kernels (anyfmt_ffn.cu) feed the codes to integer dot products against the
 // fixed-point activations; the generic grouped GEMM (grouped_ffn.cu) turns them into f16 operands.
 #pragma once
@@ -48,17 +59,39 @@ inline bool bank_dtype_ok(int32_t dt) {
     case INFR_CUDA_DT_Q2K: case INFR_CUDA_DT_Q3K: case INFR_CUDA_DT_Q4K: case INFR_CUDA_DT_Q5K: case INFR_CUDA_DT_Q6K:
     case INFR_CUDA_DT_IQ4NL: case INFR_CUDA_DT_IQ4XS: case INFR_CUDA_DT_MXFP4:
     case INFR_CUDA_DT_NVFP4: case INFR_CUDA_DT_Q2_0:
+    case INFR_CUDA_DT_IQ2XS: case INFR_CUDA_DT_IQ2S: case INFR_CUDA_DT_IQ3XXS: case INFR_CUDA_DT_IQ3S:
       return true;
     default:
       return false;
   }
 }
+// Grid codebook formats: the slot of the format's table, or -1; the table's size (entries x bytes per entry).
+constexpr int N_CODEBOOKS = 4;
+inline int codebook_slot(int32_t dt) {
+  return dt == INFR_CUDA_DT_IQ2XS ? 0 : dt == INFR_CUDA_DT_IQ3XXS ? 1 : dt == INFR_CUDA_DT_IQ3S ? 2 : dt == INFR_CUDA_DT_IQ2S ? 3 : -1;
+}
+inline size_t codebook_bytes(int slot) { return slot == 0 ? 512 * 8 : slot == 1 ? 256 * 4 : slot == 2 ? 512 * 4 : slot == 3 ? 1024 * 8 : 0; }
 // The combination the tuned kernels (per-pair, expert-major, tcgen05) are written for.
 inline bool bank_dtypes_tuned(int32_t gate, int32_t up, int32_t down) {
   return gate == INFR_CUDA_DT_Q4K && up == INFR_CUDA_DT_Q4K && (down == INFR_CUDA_DT_Q6K || down == INFR_CUDA_DT_Q4K);
 }
 
 #ifdef __CUDACC__
+
+// Device addresses of the grid tables, one copy per translation unit that unpacks weights (each publishes its
+// own through publish_codebooks): slots as codebook_slot().
+static __constant__ const unsigned char* c_codebook[N_CODEBOOKS];
+static inline cudaError_t publish_codebooks(const unsigned char* const* tables) {
+  return cudaMemcpyToSymbol(c_codebook, tables, sizeof(const unsigned char*) * N_CODEBOOKS);
+}
+
+// The sign byte of a 7-bit sign index: the index with its parity as the eighth bit (an even number of negations).
+__device__ __forceinline__ uint32_t iq_signs7(uint32_t i) { return i | ((uint32_t)(__popc(i) & 1) << 7); }
+// Four grid bytes v (each < 128) and four sign bits (bit j set: weight j is negative) -> the bytes 128 +- v.
+__device__ __forceinline__ uint32_t iq_signed_codes(uint32_t v, uint32_t s4) {
+  const uint32_t m = (((s4 & 0xFu) * 0x00204081u) & 0x01010101u) * 0xFFu;  // 0xFF in the bytes to negate
+  return 0x80808080u + (v & ~m) - (v & m);
+}
 
 // A load through the read-only path when the blocks sit in global memory (G), a plain load when a
 // kernel has staged them in shared memory.
@@ -243,6 +276,65 @@ __device__ __forceinline__ void fmt_codes16(int dt, const uint8_t* __restrict__ 
     A = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk));
     B = 0.f;
     off = 1;
+  } else if (dt == INFR_CUDA_DT_IQ2XS || dt == INFR_CUDA_DT_IQ2S) {
+    // 16 weights = two groups of 8 (l = 2 half, 2 half + 1) of the 32-weight group ib32; a 4-bit scale per 16
+    const bool s2 = dt == INFR_CUDA_DT_IQ2S;
+    const uint8_t* blk = row + (size_t)(h >> 4) * (s2 ? 82 : 74);
+    const int ib32 = (h & 15) >> 1, half = h & 1;
+    const uint32_t sc = fmt_ld<G, uint8_t>(blk + (s2 ? 74 : 66) + ib32);
+    A = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk)) * (0.5f + (float)(half ? sc >> 4 : sc & 15u)) * 0.25f;
+    const uint32_t qh = s2 ? fmt_ld<G, uint8_t>(blk + 66 + ib32) : 0u;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int l = 2 * half + s;
+      uint32_t idx, sg;
+      if (s2) {
+        idx = fmt_ld<G, uint8_t>(blk + 2 + 4 * ib32 + l) | ((qh << (8 - 2 * l)) & 0x300u);
+        sg = fmt_ld<G, uint8_t>(blk + 34 + 4 * ib32 + l);
+      } else {
+        const uint32_t q16 = fmt_ld<G, unsigned short>(blk + 2 + 2 * (4 * ib32 + l));
+        idx = q16 & 511u;
+        sg = iq_signs7(q16 >> 9);
+      }
+      const uint2 g = __ldg(reinterpret_cast<const uint2*>(c_codebook[s2 ? 3 : 0]) + idx);
+      c[2 * s] = iq_signed_codes(g.x, sg);
+      c[2 * s + 1] = iq_signed_codes(g.y, sg >> 4);
+    }
+    B = 0.f;
+    off = 128;
+  } else if (dt == INFR_CUDA_DT_IQ3XXS || dt == INFR_CUDA_DT_IQ3S) {
+    // 16 weights = two groups of 8, each two grid entries of 4; IQ3_XXS: one word per 32 weights holds four 7-bit
+    // sign indices and the scale; IQ3_S: a sign byte per 8 weights, a ninth index bit in qh, a 4-bit scale per 32
+    const bool s3 = dt == INFR_CUDA_DT_IQ3S;
+    const uint8_t* blk = row + (size_t)(h >> 4) * (s3 ? 110 : 98);
+    const int ib32 = (h & 15) >> 1, half = h & 1;
+    const float d = f16_bits_to_f32(fmt_ld<G, unsigned short>(blk));
+    uint32_t aux = 0, qh = 0;
+    if (s3) {
+      const uint32_t sb = fmt_ld<G, uint8_t>(blk + 106 + (ib32 >> 1));
+      A = d * (1.0f + 2.0f * (float)((ib32 & 1) ? sb >> 4 : sb & 15u));
+      qh = fmt_ld<G, uint8_t>(blk + 66 + ib32);
+    } else {
+      aux = ld_u32_a2<G>(blk + 66 + 4 * ib32);
+      A = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+    }
+    const uint32_t* grid = reinterpret_cast<const uint32_t*>(c_codebook[s3 ? 2 : 1]);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int l = 2 * half + s;
+      uint32_t i1 = fmt_ld<G, uint8_t>(blk + 2 + 8 * ib32 + 2 * l), i2 = fmt_ld<G, uint8_t>(blk + 3 + 8 * ib32 + 2 * l), sg;
+      if (s3) {
+        i1 |= (qh << (8 - 2 * l)) & 256u;
+        i2 |= (qh << (7 - 2 * l)) & 256u;
+        sg = fmt_ld<G, uint8_t>(blk + 74 + 4 * ib32 + l);
+      } else {
+        sg = iq_signs7((aux >> (7 * l)) & 127u);
+      }
+      c[2 * s] = iq_signed_codes(__ldg(grid + i1), sg);
+      c[2 * s + 1] = iq_signed_codes(__ldg(grid + i2), sg >> 4);
+    }
+    B = 0.f;
+    off = 128;
   } else if (dt == INFR_CUDA_DT_IQ4XS) {
     // sub-block ib (32 elements) = 16 code bytes at 8 + 16 ib, low nibbles first; its 6-bit scale: low
     // four bits in scales_l (a nibble per sub-block), high two in scales_h

@@ -53,6 +53,10 @@ bool block_layout(int32_t type, uint64_t* elems, uint64_t* bytes) {
     case 12: *elems = 256; *bytes = 144; return true; // Q4_K
     case 13: *elems = 256; *bytes = 176; return true; // Q5_K
     case 14: *elems = 256; *bytes = 210; return true; // Q6_K
+    case 17: *elems = 256; *bytes = 74; return true;  // IQ2_XS
+    case 18: *elems = 256; *bytes = 98; return true;  // IQ3_XXS
+    case 21: *elems = 256; *bytes = 110; return true; // IQ3_S
+    case 22: *elems = 256; *bytes = 82; return true;  // IQ2_S
     case 20: *elems = 32; *bytes = 18; return true;   // IQ4_NL
     case 23: *elems = 256; *bytes = 136; return true; // IQ4_XS
     case 24: *elems = 1; *bytes = 1; return true;     // I8

@@ -917,4 +917,6 @@ int32_t launch_combine(infr_cuda_ctx* ctx, const float* y, const int* pos_of_pai
   return check_cuda(ctx, cudaGetLastError(), "combine launch");
 }
 
+cudaError_t publish_codebooks_grouped(const unsigned char* const* tables) { return publish_codebooks(tables); }
+
 }  // namespace infr

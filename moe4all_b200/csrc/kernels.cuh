@@ -201,6 +201,10 @@ int32_t launch_add(infr_cuda_ctx* ctx, const float* a, const float* b, float* ds
 // dst[0, bytes) = the pinned host range whose device view is src_dev_view (16-byte aligned, bytes % 16 == 0).
 int32_t launch_fetch_host(infr_cuda_ctx* ctx, const void* src_dev_view, void* dst, size_t bytes);
 int32_t launch_store_host(infr_cuda_ctx* ctx, const void* src, void* dst_dev_view, size_t bytes);
+// The grid tables' device addresses into the constant memory of each translation unit that unpacks weights.
+cudaError_t publish_codebooks_dense(const unsigned char* const* tables);
+cudaError_t publish_codebooks_anyfmt(const unsigned char* const* tables);
+cudaError_t publish_codebooks_grouped(const unsigned char* const* tables);
 int32_t launch_fetch_host_gated(infr_cuda_ctx* ctx, const void* src_dev_view, void* dst, size_t bytes, const unsigned long long* bell,
                                 unsigned long long ticket, unsigned long long limit_ns);
 int32_t launch_host_signal(infr_cuda_ctx* ctx, unsigned long long* done, unsigned long long ticket);

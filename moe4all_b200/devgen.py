@@ -27,7 +27,8 @@ def q6k_bank(n_blocks: int, gen, device) -> torch.Tensor:
 BLOCKS = {12: (256, 144, (0, 2), 1.0), 13: (256, 176, (0, 2), 1.0), 14: (256, 210, (208,), 1.0), 8: (32, 34, (0,), 2.0),
           20: (32, 18, (0,), 2.0), 23: (256, 136, (0,), 1.0), 2: (32, 18, (0,), 32.0), 3: (32, 20, (0, 2), 32.0), 6: (32, 22, (0,), 16.0),
           7: (32, 24, (0, 2), 16.0), 10: (256, 84, (80, 82), 64.0), 11: (256, 110, (108,), 8.0), 39: (32, 17, (), 1.0),
-          40: (64, 36, (), 1.0), 42: (64, 18, (0,), 64.0)}
+          40: (64, 36, (), 1.0), 42: (64, 18, (0,), 64.0),
+          17: (256, 74, (0,), 0.5), 22: (256, 82, (0,), 0.5), 18: (256, 98, (0,), 0.2), 21: (256, 110, (0,), 0.2)}
 
 
 def bank(dtype: int, n_elem: int, gen, device) -> torch.Tensor:

@@ -17,7 +17,8 @@ Q5K_BYTES, Q80_BYTES = 176, 34
 BLOCKS = {12: (256, 144, (0, 2)), 13: (256, 176, (0, 2)), 14: (256, 210, (208,)), 8: (32, 34, (0,)),
           20: (32, 18, (0,)), 23: (256, 136, (0,)), 2: (32, 18, (0,)), 3: (32, 20, (0, 2)), 6: (32, 22, (0,)), 7: (32, 24, (0, 2)),
           10: (256, 84, (80, 82)), 11: (256, 110, (108,)), 39: (32, 17, ()),
-          40: (64, 36, ()), 42: (64, 18, (0,))}  # (MXFP4's exponent byte and NVFP4's four UE4M3 bytes are set apart)
+          40: (64, 36, ()), 42: (64, 18, (0,)),
+          17: (256, 74, (0,)), 22: (256, 82, (0,)), 18: (256, 98, (0,)), 21: (256, 110, (0,))}  # (MXFP4's exponent byte and NVFP4's four UE4M3 bytes are set apart)
 
 
 def _f16_bytes(vals: np.ndarray) -> np.ndarray:
@@ -54,6 +55,23 @@ def random_blocks(rng: np.random.Generator, dtype: int, n_elem: int, lo: float =
     return blk
 
 
+# Grid codebook formats: GGUF type -> (entries, bytes per entry, the byte values an entry is made of, entry 0)
+CODEBOOKS = {17: (512, 8, (0x08, 0x19, 0x2B), 0x08), 22: (1024, 8, (0x08, 0x19, 0x2B), 0x08),
+             18: (256, 4, (4, 12, 20, 28, 36, 44, 52, 62), 4), 21: (512, 4, (1, 3, 5, 7, 9, 11, 13, 15), 1)}
+
+
+def codebook(dtype: int) -> np.ndarray:
+    """A stand-in for the grid table of a codebook format, [entries, bytes per entry] u8, seeded: the real tables
+    are constants the reference keeps (crates/infr-core/src/iquant_grids.rs) and a host hands to the library; the
+    stand-in has their shape, their alphabet of byte values and their first entry (all 0x08 for the IQ2 grids,
+    0x04040404 for IQ3_XXS, 0x01010101 for IQ3_S: the reference's own single-block tests rest on those)."""
+    entries, width, alphabet, first = CODEBOOKS[dtype]
+    rng = np.random.default_rng(0xC0DE + dtype)
+    t = np.asarray(alphabet, np.uint8)[rng.integers(0, len(alphabet), size=(entries, width))]
+    t[0, :] = first
+    return t
+
+
 def lcg_bytes(seed: int, n: int) -> np.ndarray:
     """crates/infr-testkit/src/lib.rs:49-56: seed = seed*1664525 + 1013904223 (mod 2^32); byte = seed >> 16."""
     out = np.empty(n, dtype=np.uint8)
@@ -73,10 +91,12 @@ def gen_f32(n: int, salt: int) -> np.ndarray:
 def testkit_weight(dtype_name: str, n_elem: int, seed: int) -> np.ndarray:
     """crates/infr-testkit/src/lib.rs:74-123 for Q4_K and Q5_K (d 0.05, dmin 0.10), Q6_K (d 0.03),
     Q8_0 (d 0.01), IQ4_NL (d 0.004), IQ4_XS (d 0.06), Q4_0 / Q5_0 (d 0.04), Q4_1 / Q5_1 (d 0.04, m -0.30),
-    Q2_K (d 0.05, dmin 0.10), Q3_K (d 0.03), MXFP4 (d 0.25), NVFP4 (d 0.5) and Q2_0 (d 0.05)."""
+    Q2_K (d 0.05, dmin 0.10), Q3_K (d 0.03), MXFP4 (d 0.25), NVFP4 (d 0.5), Q2_0 (d 0.05), IQ2_XS / IQ2_S (d 0.015),
+    IQ3_XXS (d 0.008) and IQ3_S (d 0.002)."""
     TK = {"Q5K": (13, (0.05, 0.10)), "Q8_0": (8, (0.01,)), "IQ4NL": (20, (0.004,)), "IQ4XS": (23, (0.06,)), "Q4_0": (2, (0.04,)),
           "Q4_1": (3, (0.04, -0.30)), "Q5_0": (6, (0.04,)), "Q5_1": (7, (0.04, -0.30)), "Q2K": (10, (0.05, 0.10)), "Q3K": (11, (0.03,)),
-          "MXFP4": (39, ()), "NVFP4": (40, ()), "Q2_0": (42, (0.05,))}
+          "MXFP4": (39, ()), "NVFP4": (40, ()), "Q2_0": (42, (0.05,)),
+          "IQ2XS": (17, (0.015,)), "IQ2S": (22, (0.015,)), "IQ3XXS": (18, (0.008,)), "IQ3S": (21, (0.002,))}
     if dtype_name in TK:
         elems, nbytes, slots = BLOCKS[TK[dtype_name][0]]
         assert n_elem % elems == 0
@@ -135,7 +155,7 @@ def make_layer(seed: int, ne: int, n_expert: int, n_ff: int, sh_ff: int = 0, gat
         L.gate_dtype, L.up_dtype, L.down_dtype = dtypes
 
         def bank(dt, n_elem):
-            k = {8: 2.0, 20: 2.0, 2: 32.0, 3: 32.0, 6: 16.0, 7: 16.0, 10: 64.0, 11: 8.0, 42: 64.0}.get(dt, 1.0)  # similar weight magnitudes
+            k = {8: 2.0, 20: 2.0, 2: 32.0, 3: 32.0, 6: 16.0, 7: 16.0, 10: 64.0, 11: 8.0, 42: 64.0, 17: 0.5, 22: 0.5, 18: 0.2, 21: 0.2}.get(dt, 1.0)  # similar weight magnitudes
             return random_blocks(rng, dt, n_elem, 1e-4 * k, 1e-3 * k).reshape(-1)
         L.gate, L.up, L.down = bank(dtypes[0], n_expert * n_ff * ne), bank(dtypes[1], n_expert * n_ff * ne), bank(dtypes[2], n_expert * ne * n_ff)
         if sh_ff:

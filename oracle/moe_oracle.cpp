@@ -39,7 +39,7 @@
 namespace {
 
 // dtype ids follow the public GGUF/ggml numbering.
-enum : int { DT_F32 = 0, DT_Q4_0 = 2, DT_Q4_1 = 3, DT_Q5_0 = 6, DT_Q5_1 = 7, DT_Q8_0 = 8, DT_Q2K = 10, DT_Q3K = 11, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14, DT_IQ4NL = 20, DT_IQ4XS = 23, DT_MXFP4 = 39, DT_NVFP4 = 40, DT_Q2_0 = 42 };
+enum : int { DT_F32 = 0, DT_Q4_0 = 2, DT_Q4_1 = 3, DT_Q5_0 = 6, DT_Q5_1 = 7, DT_Q8_0 = 8, DT_Q2K = 10, DT_Q3K = 11, DT_Q4K = 12, DT_Q5K = 13, DT_Q6K = 14, DT_IQ4NL = 20, DT_IQ4XS = 23, DT_MXFP4 = 39, DT_NVFP4 = 40, DT_Q2_0 = 42, DT_IQ2XS = 17, DT_IQ3XXS = 18, DT_IQ3S = 21, DT_IQ2S = 22 };
 
 // IEEE binary16 → binary32, exact (what `half::f16::to_f32` does; dequant.rs:72-74).
 inline float f16_to_f32(uint16_t h) {
@@ -301,6 +301,77 @@ void dequant_q2_0_block(const uint8_t* blk, float* out) {
   for (int j = 0; j < 64; ++j) out[j] = (float)((int)((blk[2 + j / 4] >> ((j % 4) * 2)) & 3) - 1) * d;
 }
 
+// ---- grid codebook formats (dequant.rs:477-488, 605-770) ------------------------------------------------
+// A group of 8 (IQ2) or 4 (IQ3) weights is one entry of the format's grid table (one byte per weight) with a
+// sign bit per weight; out = db * grid byte * (+-1), db the group's scale.  The tables are constants of the
+// formats kept by the reference (crates/infr-core/src/iquant_grids.rs); this restatement does not carry them:
+// the tests hand them in (orc_set_codebook).  Slots: 0 IQ2_XS (512 x 8), 1 IQ3_XXS (256 x 4), 2 IQ3_S (512 x 4),
+// 3 IQ2_S (1024 x 8).
+std::vector<uint8_t> g_codebook[4];
+int codebook_slot(int dt) { return dt == DT_IQ2XS ? 0 : dt == DT_IQ3XXS ? 1 : dt == DT_IQ3S ? 2 : dt == DT_IQ2S ? 3 : -1; }
+size_t codebook_bytes(int slot) { return slot == 0 ? 4096 : slot == 1 ? 1024 : slot == 2 ? 2048 : slot == 3 ? 8192 : 0; }
+// The sign byte of a 7-bit index: the index with its parity on top (KSIGNS_IQ2XS, iquant_grids.rs:6-16).
+uint8_t ksigns(uint32_t i) { return (uint8_t)(i | ((uint32_t)(__builtin_popcount(i) & 1) << 7)); }
+// n weights from grid bytes `g`, sign bits sign_off .. sign_off + n - 1 of `signs` (apply_signs, dequant.rs:477-488)
+void put_signed(float* out, const uint8_t* g, uint8_t signs, int sign_off, int n, float db) {
+  for (int j = 0; j < n; ++j) {
+    const float gv = (float)(int8_t)g[j];
+    out[j] = db * gv * ((signs >> (sign_off + j)) & 1 ? -1.0f : 1.0f);
+  }
+}
+void dequant_iq2xs_block(const uint8_t* blk, float* out) {  // 74 B: d, 32 x u16 (9-bit grid index, 7-bit sign index), 8 scale bytes
+  const float d = f16_to_f32(rd16(blk));
+  const uint8_t* grid = g_codebook[0].data();
+  for (int ib32 = 0; ib32 < 8; ++ib32) {
+    const uint8_t sc = blk[66 + ib32];
+    const float db0 = d * (0.5f + (float)(sc & 0xF)) * 0.25f, db1 = d * (0.5f + (float)(sc >> 4)) * 0.25f;
+    for (int l = 0; l < 4; ++l) {
+      const uint32_t q = rd16(blk + 2 + 2 * (ib32 * 4 + l));
+      put_signed(out + ib32 * 32 + l * 8, grid + 8 * (q & 511), ksigns(q >> 9), 0, 8, l < 2 ? db0 : db1);
+    }
+  }
+}
+void dequant_iq2s_block(const uint8_t* blk, float* out) {  // 82 B: d, 32 grid bytes, 32 sign bytes, 8 high-bit bytes, 8 scale bytes
+  const float d = f16_to_f32(rd16(blk));
+  const uint8_t* grid = g_codebook[3].data();
+  for (int ib32 = 0; ib32 < 8; ++ib32) {
+    const uint8_t sc = blk[74 + ib32], qh = blk[66 + ib32];
+    const float db0 = d * (0.5f + (float)(sc & 0xF)) * 0.25f, db1 = d * (0.5f + (float)(sc >> 4)) * 0.25f;
+    for (int l = 0; l < 4; ++l) {
+      const uint32_t idx = (uint32_t)blk[2 + ib32 * 4 + l] | (((uint32_t)qh << (8 - 2 * l)) & 0x300u);
+      put_signed(out + ib32 * 32 + l * 8, grid + 8 * idx, blk[34 + ib32 * 4 + l], 0, 8, l < 2 ? db0 : db1);
+    }
+  }
+}
+void dequant_iq3xxs_block(const uint8_t* blk, float* out) {  // 98 B: d, 64 grid bytes, 8 words of 4 x 7 sign-index bits + 4 scale bits
+  const float d = f16_to_f32(rd16(blk));
+  const uint8_t* grid = g_codebook[1].data();
+  for (int ib32 = 0; ib32 < 8; ++ib32) {
+    const uint32_t aux = (uint32_t)rd16(blk + 66 + 4 * ib32) | ((uint32_t)rd16(blk + 68 + 4 * ib32) << 16);
+    const float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+    for (int l = 0; l < 4; ++l) {
+      const uint8_t sg = ksigns((aux >> (7 * l)) & 127);
+      put_signed(out + ib32 * 32 + l * 8, grid + 4 * blk[2 + 8 * ib32 + 2 * l], sg, 0, 4, db);
+      put_signed(out + ib32 * 32 + l * 8 + 4, grid + 4 * blk[3 + 8 * ib32 + 2 * l], sg, 4, 4, db);
+    }
+  }
+}
+void dequant_iq3s_block(const uint8_t* blk, float* out) {  // 110 B: d, 64 grid bytes, 8 ninth-bit bytes, 32 sign bytes, 4 scale bytes
+  const float d = f16_to_f32(rd16(blk));
+  const uint8_t* grid = g_codebook[2].data();
+  for (int ib32 = 0; ib32 < 8; ++ib32) {
+    const uint8_t sb = blk[106 + ib32 / 2], qh = blk[66 + ib32];
+    const float db = d * (1.0f + 2.0f * (float)((ib32 & 1) ? sb >> 4 : sb & 0xF));
+    for (int l = 0; l < 4; ++l) {
+      const uint32_t i1 = (uint32_t)blk[2 + 8 * ib32 + 2 * l] | (((uint32_t)qh << (8 - 2 * l)) & 256u);
+      const uint32_t i2 = (uint32_t)blk[3 + 8 * ib32 + 2 * l] | (((uint32_t)qh << (7 - 2 * l)) & 256u);
+      const uint8_t sg = blk[74 + 4 * ib32 + l];
+      put_signed(out + ib32 * 32 + l * 8, grid + 4 * i1, sg, 0, 4, db);
+      put_signed(out + ib32 * 32 + l * 8 + 4, grid + 4 * i2, sg, 4, 4, db);
+    }
+  }
+}
+
 // One IQ4_XS block (136 B -> 256 f32), dequant.rs:521-553: eight sub-blocks of 32 with a 6-bit scale
 // ls (low four bits in scales_l, high two in scales_h); dl = d * (ls - 32); codes as in IQ4_NL.
 void dequant_iq4xs_block(const uint8_t* blk, float* out) {
@@ -333,6 +404,10 @@ size_t row_bytes(int dtype, size_t n_elem) {
     case DT_MXFP4: return n_elem / 32 * 17;
     case DT_NVFP4: return n_elem / 64 * 36;
     case DT_Q2_0: return n_elem / 64 * 18;
+    case DT_IQ2XS: return n_elem / 256 * 74;
+    case DT_IQ2S: return n_elem / 256 * 82;
+    case DT_IQ3XXS: return n_elem / 256 * 98;
+    case DT_IQ3S: return n_elem / 256 * 110;
     case DT_Q8_0: return n_elem / 32 * 34;
     case DT_Q4K: return n_elem / 256 * 144;
     case DT_Q5K: return n_elem / 256 * 176;
@@ -396,6 +471,22 @@ bool dequant_row(int dtype, const uint8_t* bytes, size_t n_elem, float* out) {
       if (n_elem % 64) return false;
       for (size_t b = 0; b < n_elem / 64; ++b) dequant_q2_0_block(bytes + b * 18, out + b * 64);
       return true;
+    case DT_IQ2XS:
+    case DT_IQ2S:
+    case DT_IQ3XXS:
+    case DT_IQ3S: {
+      if (n_elem % 256 || g_codebook[codebook_slot(dtype)].empty()) return false;  // (no table handed in: not decodable)
+      const size_t bb = row_bytes(dtype, 256);
+      for (size_t b = 0; b < n_elem / 256; ++b) {
+        const uint8_t* blk = bytes + b * bb;
+        float* o = out + b * 256;
+        if (dtype == DT_IQ2XS) dequant_iq2xs_block(blk, o);
+        else if (dtype == DT_IQ2S) dequant_iq2s_block(blk, o);
+        else if (dtype == DT_IQ3XXS) dequant_iq3xxs_block(blk, o);
+        else dequant_iq3s_block(blk, o);
+      }
+      return true;
+    }
     case DT_IQ4XS:
       if (n_elem % 256) return false;
       for (size_t b = 0; b < n_elem / 256; ++b) dequant_iq4xs_block(bytes + b * 136, out + b * 256);
@@ -511,6 +602,14 @@ int orc_hw_threads(void) {
 }
 
 size_t orc_row_bytes(int dtype, size_t n_elem) { return row_bytes(dtype, n_elem); }
+
+// The grid table of a codebook format (see above); 0 on success.
+int orc_set_codebook(int dtype, const uint8_t* table, size_t bytes) {
+  const int slot = codebook_slot(dtype);
+  if (slot < 0 || bytes != codebook_bytes(slot)) return 1;
+  g_codebook[slot].assign(table, table + bytes);
+  return 0;
+}
 
 int orc_dequant(int dtype, const uint8_t* bytes, size_t n_elem, float* out) {
   return dequant_row(dtype, bytes, n_elem, out) ? 0 : -1;

@@ -18,6 +18,7 @@ _SO = os.path.join(_HERE, "_build", "libmoe_oracle.so")
 DT_F32, DT_Q4K, DT_Q6K = 0, 12, 14
 DT_Q8_0, DT_Q5K = 8, 13
 DT_IQ4NL, DT_IQ4XS, DT_MXFP4, DT_NVFP4, DT_Q2_0 = 20, 23, 39, 40, 42
+DT_IQ2XS, DT_IQ3XXS, DT_IQ3S, DT_IQ2S = 17, 18, 21, 22
 DT_Q4_0, DT_Q4_1, DT_Q5_0, DT_Q5_1, DT_Q2K, DT_Q3K = 2, 3, 6, 7, 10, 11
 GATING_SOFTMAX, GATING_SIGMOID, GATING_SQRT_SOFTPLUS = 0, 1, 2
 
@@ -58,6 +59,7 @@ def lib():
         L.orc_row_bytes.restype = C.c_size_t
         L.orc_row_bytes.argtypes = [C.c_int, C.c_size_t]
         L.orc_dequant.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.orc_set_codebook.argtypes = [C.c_int, C.c_void_p, C.c_size_t]
         L.orc_dot.restype = C.c_float
         L.orc_dot.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
         L.orc_dot_scalar.restype = C.c_float
@@ -92,6 +94,13 @@ def _u8(a):
 
 def hw_threads() -> int:
     return int(lib().orc_hw_threads())
+
+
+def set_codebook(dtype: int, table: np.ndarray) -> None:
+    """Hand in the grid table of a codebook format (IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S) as its little-endian bytes."""
+    t = np.ascontiguousarray(table).view(np.uint8).reshape(-1)
+    if lib().orc_set_codebook(dtype, _p(t), t.nbytes) != 0:
+        raise ValueError(f"dtype {dtype}: not a grid codebook format, or a table of the wrong size")
 
 
 def row_bytes(dtype: int, n_elem: int) -> int:

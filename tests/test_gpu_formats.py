@@ -15,11 +15,22 @@ pytestmark = pytest.mark.gpu
 
 Q8_0, Q4K, Q5K, Q6K, IQ4NL, IQ4XS = 8, 12, 13, 14, 20, 23
 Q4_0, Q4_1, Q5_0, Q5_1, Q2K, Q3K, MXFP4, NVFP4, Q2_0 = 2, 3, 6, 7, 10, 11, 39, 40, 42
+IQ2XS, IQ3XXS, IQ3S, IQ2S = 17, 18, 21, 22
 MIXES = [(Q5K, Q5K, Q6K), (Q8_0, Q8_0, Q8_0), (Q5K, Q5K, Q5K), (Q4K, Q5K, Q8_0), (Q6K, Q6K, Q4K), (Q8_0, Q4K, Q6K),
          (IQ4XS, IQ4XS, Q6K), (IQ4NL, IQ4NL, IQ4NL), (IQ4XS, IQ4NL, IQ4XS),
          (Q4_0, Q4_0, Q4_0), (Q4_1, Q4_1, Q5_1), (Q5_0, Q5_1, Q5_0), (Q2K, Q2K, Q3K), (Q3K, Q3K, Q6K), (Q3K, Q2K, Q2K),
          (MXFP4, MXFP4, MXFP4), (MXFP4, MXFP4, Q6K),
-         (NVFP4, NVFP4, NVFP4), (Q2_0, Q2_0, Q2_0), (Q2_0, NVFP4, Q4K)]
+         (NVFP4, NVFP4, NVFP4), (Q2_0, Q2_0, Q2_0), (Q2_0, NVFP4, Q4K),
+         (IQ2XS, IQ2XS, IQ3S), (IQ3XXS, IQ3XXS, IQ2S), (IQ3S, IQ2S, Q6K), (IQ2S, IQ3XXS, IQ2XS)]
+
+
+@pytest.fixture(autouse=True)
+def grid_tables(backend):
+    # the grid codebook formats need their tables: stand-ins with the real ones' shape, alphabet and first entry,
+    # the same on both sides
+    for dt in synth.CODEBOOKS:
+        backend.set_codebook(DType(dt), synth.codebook(dt))
+        orc.set_codebook(dt, synth.codebook(dt))
 
 
 def check(out, ids, ref, n_used):
@@ -76,7 +87,9 @@ def test_variants_and_bands(backend, mix):
                                                 (IQ4XS, "IQ4XS", 512, 64), (IQ4NL, "IQ4NL", 160, 24), (Q4_0, "Q4_0", 96, 16),
                                                 (Q4_1, "Q4_1", 512, 16), (Q5_0, "Q5_0", 512, 16), (Q5_1, "Q5_1", 64, 16),
                                                 (Q2K, "Q2K", 512, 32), (Q3K, "Q3K", 768, 32), (MXFP4, "MXFP4", 96, 24),
-                                                (NVFP4, "NVFP4", 192, 24), (Q2_0, "Q2_0", 320, 16)])
+                                                (NVFP4, "NVFP4", 192, 24), (Q2_0, "Q2_0", 320, 16),
+                                                (IQ2XS, "IQ2XS", 512, 24), (IQ2S, "IQ2S", 256, 16), (IQ3XXS, "IQ3XXS", 768, 16),
+                                                (IQ3S, "IQ3S", 512, 24)])
 def test_linear_op(backend, dt, name, in_f, out_f):
     # Op::Linear on the reference's synthesised weights (crates/infr-testkit/src/lib.rs:74-123); Q8_0 rows
     # need whole 32-weight blocks only
@@ -91,6 +104,30 @@ def test_linear_op(backend, dt, name, in_f, out_f):
     if dt == Q5K:
         with pytest.raises(BackendError):
             be.linear(DType(dt), wb, xb, yb, 3, 96, 8)  # not a whole number of 256-weight blocks
+
+
+def test_codebook_format_needs_its_table():
+    # a context that was never given the table refuses the format (and says how to fix it); wrong tables are refused too
+    from moe4all_b200 import CudaBackend, Unsupported
+
+    be = CudaBackend(0)
+    try:
+        w = be.from_host(synth.testkit_weight("IQ3S", 512 * 8, seed=1).reshape(-1))
+        x, y = be.from_host(synth.gen_f32(512, 2)), be.alloc(8 * 4)
+        with pytest.raises(Unsupported) as e:
+            be.linear(DType(IQ3S), w, x, y, 1, 512, 8)
+        assert "infr_cuda_set_codebook" in str(e.value)
+        with pytest.raises(BackendError):
+            be.set_codebook(DType(IQ3S), synth.codebook(IQ3S)[:-1])  # wrong size
+        with pytest.raises(BackendError):
+            be.set_codebook(DType(IQ3S), synth.codebook(IQ3S) | 0x80)  # grid bytes must stay below 128
+        with pytest.raises(BackendError):
+            be.set_codebook(DType(Q4K), synth.codebook(IQ3S))  # not a codebook format
+        be.set_codebook(DType(IQ3S), synth.codebook(IQ3S))
+        be.linear(DType(IQ3S), w, x, y, 1, 512, 8)
+        be.sync()
+    finally:
+        be.close()
 
 
 def test_unknown_format_refused(backend):

@@ -427,6 +427,73 @@ def test_q2_0_reference_vector_and_blocks():
     assert np.array_equal(orc.dequant(orc.DT_Q2_0, raw.reshape(-1), 1024).view(np.uint32), want.view(np.uint32))
 
 
+def _ksigns(i):
+    return i | ((bin(i).count("1") & 1) << 7)
+
+
+def np_grid_formats(dt, raw, table):
+    """dequant.rs:477-488, 605-770 for IQ2_XS (17), IQ2_S (22), IQ3_XXS (18), IQ3_S (21): grid entry bytes x sign x the
+    group's scale, with f32 products in the reference's order (db first, then db * byte, then the sign)."""
+    bb = {17: 74, 22: 82, 18: 98, 21: 110}[dt]
+    raw = np.asarray(raw, np.uint8).reshape(-1, bb)
+    t = np.asarray(table, np.uint8)
+    out = np.empty((raw.shape[0], 256), F32)
+    for bi, blk in enumerate(raw):
+        d = F32(blk[0:2].copy().view(np.float16)[0])
+        for ib in range(8):
+            for l in range(4):
+                if dt in (17, 22):
+                    sc = int(blk[(66 if dt == 17 else 74) + ib])
+                    ls = (sc & 15) if l < 2 else (sc >> 4)
+                    db = F32(F32(d * F32(0.5 + ls)) * F32(0.25))
+                    if dt == 17:
+                        q = int(blk[2 + 2 * (4 * ib + l)]) | (int(blk[3 + 2 * (4 * ib + l)]) << 8)
+                        vals, sg = t[q & 511], _ksigns(q >> 9)
+                    else:
+                        idx = int(blk[2 + 4 * ib + l]) | ((int(blk[66 + ib]) << (8 - 2 * l)) & 0x300)
+                        vals, sg = t[idx], int(blk[34 + 4 * ib + l])
+                else:
+                    if dt == 18:
+                        aux = int.from_bytes(bytes(blk[66 + 4 * ib:70 + 4 * ib]), "little")
+                        db = F32(F32(d * F32(0.5 + (aux >> 28))) * F32(0.5))
+                        sg = _ksigns((aux >> (7 * l)) & 127)
+                        i1, i2 = int(blk[2 + 8 * ib + 2 * l]), int(blk[3 + 8 * ib + 2 * l])
+                    else:
+                        sb, qh = int(blk[106 + ib // 2]), int(blk[66 + ib])
+                        db = F32(d * F32(1.0 + 2.0 * ((sb >> 4) if ib & 1 else (sb & 15))))
+                        sg = int(blk[74 + 4 * ib + l])
+                        i1 = int(blk[2 + 8 * ib + 2 * l]) | ((qh << (8 - 2 * l)) & 256)
+                        i2 = int(blk[3 + 8 * ib + 2 * l]) | ((qh << (7 - 2 * l)) & 256)
+                    vals = np.concatenate([t[i1], t[i2]])
+                for j in range(8):
+                    v = F32(db * F32(int(vals[j])))
+                    out[bi, 32 * ib + 8 * l + j] = -v if (sg >> j) & 1 else v
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("dt,name,bb", [(17, "IQ2XS", 74), (22, "IQ2S", 82), (18, "IQ3XXS", 98), (21, "IQ3S", 110)])
+def test_grid_codebook_formats(dt, name, bb):
+    # The grid tables are handed in (the real ones are the reference's constants); the stand-ins keep the first
+    # entry of the real tables, on which the reference's own single-block tests rest
+    # (crates/infr-gguf/src/dequant.rs `iq2xs_single_block`, `iq2s_single_block`, `iq3xxs_single_block`,
+    # `iq3s_single_block`: d = 1 and an otherwise all-zero block decode to 1.0 everywhere).
+    table = synth.codebook(dt)
+    orc.set_codebook(dt, table)
+    blk = np.zeros(bb, np.uint8)
+    blk[0:2] = np.array([1.0], np.float16).view(np.uint8)
+    assert np.all(orc.dequant(dt, blk, 256) == 1.0)
+    assert orc.row_bytes(dt, 2048) == 8 * bb
+    raw = synth.testkit_weight(name, 1024, seed=0x5150 + dt)  # the reference's recipe: LCG payload, d from synth_scales
+    got = orc.dequant(dt, raw, 1024)
+    want = np_grid_formats(dt, raw, table)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32)) and np.abs(got).max() > 0
+    assert (got < 0).any() and (got > 0).any()
+    with pytest.raises(ValueError):
+        orc.set_codebook(dt, table[:-1])  # a table of the wrong size
+    with pytest.raises(ValueError):
+        orc.set_codebook(12, table)  # not a codebook format
+
+
 def test_ragged_block_count_rejected():
     with pytest.raises(ValueError):
         orc.dequant(orc.DT_Q4K, np.zeros(144, np.uint8), 100)
