@@ -41,6 +41,10 @@ pub const DT_IQ4XS: i32 = 23;
 pub const DT_MXFP4: i32 = 39;
 pub const DT_NVFP4: i32 = 40;
 pub const DT_Q2_0: i32 = 42;
+pub const DT_IQ2XS: i32 = 17;
+pub const DT_IQ3XXS: i32 = 18;
+pub const DT_IQ3S: i32 = 21;
+pub const DT_IQ2S: i32 = 22;
 
 pub const EP_ID_BYTES: usize = 128;
 
@@ -121,6 +125,7 @@ extern "C" {
     pub fn infr_cuda_set_stream(ctx: *mut infr_cuda_ctx, cuda_stream: *mut c_void) -> i32;
     pub fn infr_cuda_get_config(ctx: *const infr_cuda_ctx, out: *mut infr_cuda_config) -> i32;
     pub fn infr_cuda_set_config(ctx: *mut infr_cuda_ctx, cfg: *const infr_cuda_config) -> i32;
+    pub fn infr_cuda_set_codebook(ctx: *mut infr_cuda_ctx, dtype: i32, table: *const c_void, bytes: usize) -> i32;
 
     pub fn infr_cuda_alloc(ctx: *mut infr_cuda_ctx, bytes: usize, zero: i32, out: *mut *mut infr_cuda_buf) -> i32;
     pub fn infr_cuda_wrap(ctx: *mut infr_cuda_ctx, device_ptr: *mut c_void, bytes: usize, out: *mut *mut infr_cuda_buf) -> i32;

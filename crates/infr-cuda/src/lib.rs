@@ -135,6 +135,24 @@ impl CudaBackend {
             });
         }
         let name = unsafe { CStr::from_ptr(ffi::infr_cuda_name()).to_string_lossy().into_owned() };
+        // The grid tables of the codebook formats are this workspace's constants (`infr_core::iquant_grids`); the
+        // library carries none and unpacks IQ2_XS / IQ2_S / IQ3_XXS / IQ3_S weights only after it has been given them.
+        {
+            use infr_core::iquant_grids::{IQ2S_GRID, IQ2XS_GRID, IQ3S_GRID, IQ3XXS_GRID};
+            let tables: [(i32, &[u8]); 4] = [
+                (ffi::DT_IQ2XS, bytemuck::cast_slice(&IQ2XS_GRID[..])),
+                (ffi::DT_IQ2S, bytemuck::cast_slice(&IQ2S_GRID[..])),
+                (ffi::DT_IQ3XXS, bytemuck::cast_slice(&IQ3XXS_GRID[..])),
+                (ffi::DT_IQ3S, bytemuck::cast_slice(&IQ3S_GRID[..])),
+            ];
+            for (dt, bytes) in tables {
+                let rc = unsafe { ffi::infr_cuda_set_codebook(raw, dt, bytes.as_ptr() as *const _, bytes.len()) };
+                if rc != ffi::OK {
+                    unsafe { ffi::infr_cuda_destroy(raw) };
+                    return Err(Error::backend(format!("infr-cuda: infr_cuda_set_codebook(dtype {dt}) failed with status {rc}")));
+                }
+            }
+        }
         Ok(Self { ctx: Arc::new(Ctx { raw, gate: Mutex::new(()) }), name, scratch: Mutex::new(HashMap::new()), ep: Mutex::new(None) })
     }
 
@@ -242,6 +260,10 @@ fn dt_code(dt: DType) -> Result<i32> {
         DType::Mxfp4 => Ok(ffi::DT_MXFP4),
         DType::Nvfp4 => Ok(ffi::DT_NVFP4),
         DType::Q2_0 => Ok(ffi::DT_Q2_0),
+        DType::Iq2Xs => Ok(ffi::DT_IQ2XS),
+        DType::Iq2S => Ok(ffi::DT_IQ2S),
+        DType::Iq3Xxs => Ok(ffi::DT_IQ3XXS),
+        DType::Iq3S => Ok(ffi::DT_IQ3S),
         other => Err(Error::Unsupported(format!("infr-cuda: weight dtype {other:?} has no sm_100a kernel"))),
     }
 }

@@ -164,6 +164,9 @@ fn moe_q5k_and_q8_0_banks() {
         (DType::Q5K, DType::Q6K, "Q5_K / Q6_K"),
         (DType::Q8_0, DType::Q8_0, "Q8_0"),
         (DType::Iq4Xs, DType::Iq4Nl, "IQ4_XS / IQ4_NL"),
+        // grid codebook formats: the backend was given this workspace's grid tables when it was created
+        (DType::Iq2Xs, DType::Iq3S, "IQ2_XS / IQ3_S"),
+        (DType::Iq3Xxs, DType::Iq2S, "IQ3_XXS / IQ2_S"),
     ] {
         for rows in [1usize, 4, 96] {
             check(
@@ -248,12 +251,12 @@ fn unsupported_is_an_error() {
     let Some(gpu) = gpu() else { return };
     let mut g = Graph::new();
     let x = g.input(f32d(256));
-    let w = g.weight(qd(256 * 256, DType::Iq2S));
+    let w = g.weight(qd(256 * 256, DType::Iq1S));
     let y = g.output(f32d(256));
     g.push(Op::Linear { x, weight: w, dst: y, m: 1, in_f: 256, out_f: 256, w_off: 0 });
     let plan = gpu.compile(&g).expect("compile");
     let xb = gpu.alloc(1024, infr_core::backend::BufferUsage::Activations).unwrap();
-    let wb = gpu.alloc(256 * 82, infr_core::backend::BufferUsage::Weights).unwrap();  // 256 rows of one 82-byte IQ2_S block
+    let wb = gpu.alloc(256 * 50, infr_core::backend::BufferUsage::Weights).unwrap();  // 256 rows of one 50-byte IQ1_S block
     let yb = gpu.alloc(1024, infr_core::backend::BufferUsage::Readback).unwrap();
     let mut b = infr_core::backend::Bindings::new();
     b.bind(x, xb.as_ref()).bind(w, wb.as_ref()).bind(y, yb.as_ref());
