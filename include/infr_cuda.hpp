@@ -40,7 +40,8 @@ struct Result {
 
 // crates/infr-core/src/tensor.rs:7-57, numbered as in the GGUF file format.
 enum class DType : int32_t { F32 = INFR_CUDA_DT_F32, Q4_0 = INFR_CUDA_DT_Q4_0, Q4_1 = INFR_CUDA_DT_Q4_1, Q5_0 = INFR_CUDA_DT_Q5_0,
-                             Q5_1 = INFR_CUDA_DT_Q5_1, Q2K = INFR_CUDA_DT_Q2K, Q3K = INFR_CUDA_DT_Q3K, Q8_0 = INFR_CUDA_DT_Q8_0, Q4K = INFR_CUDA_DT_Q4K, Q5K = INFR_CUDA_DT_Q5K, Q6K = INFR_CUDA_DT_Q6K, IQ4NL = INFR_CUDA_DT_IQ4NL, IQ4XS = INFR_CUDA_DT_IQ4XS, MXFP4 = INFR_CUDA_DT_MXFP4, NVFP4 = INFR_CUDA_DT_NVFP4, Q2_0 = INFR_CUDA_DT_Q2_0 };
+                             Q5_1 = INFR_CUDA_DT_Q5_1, Q2K = INFR_CUDA_DT_Q2K, Q3K = INFR_CUDA_DT_Q3K, Q8_0 = INFR_CUDA_DT_Q8_0, Q4K = INFR_CUDA_DT_Q4K, Q5K = INFR_CUDA_DT_Q5K, Q6K = INFR_CUDA_DT_Q6K, IQ4NL = INFR_CUDA_DT_IQ4NL, IQ4XS = INFR_CUDA_DT_IQ4XS, MXFP4 = INFR_CUDA_DT_MXFP4, NVFP4 = INFR_CUDA_DT_NVFP4, Q2_0 = INFR_CUDA_DT_Q2_0,
+                             IQ2XS = INFR_CUDA_DT_IQ2XS, IQ2S = INFR_CUDA_DT_IQ2S, IQ3XXS = INFR_CUDA_DT_IQ3XXS, IQ3S = INFR_CUDA_DT_IQ3S };
 // crates/infr-core/src/graph.rs:73-85
 enum class MoeGating : uint32_t {
   Softmax = INFR_CUDA_GATING_SOFTMAX,
@@ -307,6 +308,9 @@ class Backend {
     return st(infr_cuda_ep_init(ctx_, id.data(), rank, world));
   }
   Status leave() { return st(infr_cuda_ep_finalize(ctx_)); }
+
+  // The grid table of a codebook format (IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S), handed over once per format.
+  Status set_codebook(DType dtype, const void* table, size_t bytes) { return st(infr_cuda_set_codebook(ctx_, (int32_t)dtype, table, bytes)); }
 
   Status begin_record() { return st(infr_cuda_graph_begin(ctx_)); }
   Result<Plan> end_record() {
