@@ -119,7 +119,8 @@ int32_t infr_cuda_set_config(infr_cuda_ctx* ctx, const infr_cuda_config* cfg);
  * 1024 x u64, IQ3XXS_GRID 256 x u32, IQ3S_GRID 512 x u32; little-endian entries, one byte per weight, every
  * byte below 128), copied to the device once.  `bytes` must be the table's exact size.  Banks and Linear
  * weights of that dtype are INFR_CUDA_ERR_UNSUPPORTED until the table is there.  The tables are constants of
- * the formats: every context of a device sees the last one set. */
+ * the formats and the device copies belong to the device: every context of a device that has set a format's
+ * table reads the last one set for it, and the copies (a few KB) stay allocated until the process ends. */
 int32_t infr_cuda_set_codebook(infr_cuda_ctx* ctx, int32_t dtype, const void* table, size_t bytes);
 
 /* ---- buffers: Backend::alloc / alloc_uninit / upload / download / sync ------------------------ */

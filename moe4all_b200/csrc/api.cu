@@ -77,6 +77,11 @@ struct DeviceGuard {
 
 bool fits(const infr_cuda_buf* b, size_t need) { return b && b->ptr && b->bytes >= need; }
 
+// Device copies of the grid tables, per device (see infr_cuda_set_codebook).
+constexpr int MAX_CODEBOOK_DEVICES = 64;
+unsigned char* g_codebook_dev[MAX_CODEBOOK_DEVICES][N_CODEBOOKS] = {};
+std::mutex g_codebook_mu;
+
 // A grid codebook format whose table the host has not handed over yet.
 bool codebook_missing(const infr_cuda_ctx* ctx, int32_t dt) {
   const int slot = codebook_slot(dt);
@@ -175,8 +180,6 @@ void infr_cuda_destroy(infr_cuda_ctx* ctx) {
   if (ctx->own_stream) cudaStreamSynchronize(ctx->own_stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
-  for (unsigned char* t : ctx->codebook)
-    if (t) cudaFree(t);
   if (ctx->route_logits) cudaFree(ctx->route_logits);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   delete ctx;
@@ -324,13 +327,20 @@ int32_t infr_cuda_set_codebook(infr_cuda_ctx* ctx, int32_t dtype, const void* ta
   for (size_t i = 0; i < bytes; ++i)
     if (tb[i] >= 128) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_codebook: grid bytes must be below 128");
   if (ctx->capturing) return fail(ctx, INFR_CUDA_ERR_INVALID_ARG, "set_codebook: not while recording");
+  if (ctx->device < 0 || ctx->device >= MAX_CODEBOOK_DEVICES) return fail(ctx, INFR_CUDA_ERR_UNSUPPORTED, "set_codebook: device index beyond 63");
   DeviceGuard g(ctx->device);
-  cudaError_t e = cudaStreamSynchronize(ctx->stream);  // no kernel reads a table while it changes
-  if (e == cudaSuccess && !ctx->codebook[slot]) e = cudaMalloc(reinterpret_cast<void**>(&ctx->codebook[slot]), bytes);
-  if (e == cudaSuccess) e = cudaMemcpy(ctx->codebook[slot], table, bytes, cudaMemcpyHostToDevice);
-  if (e == cudaSuccess) e = publish_codebooks_dense(ctx->codebook);
-  if (e == cudaSuccess) e = publish_codebooks_anyfmt(ctx->codebook);
-  if (e == cudaSuccess) e = publish_codebooks_grouped(ctx->codebook);
+  // The device copies belong to the device, not to the context: the kernels find them through constant memory,
+  // which every context of the device shares, so a table stays where it is (and allocated, a few KB) until the
+  // process ends; a context only remembers that it has been given one.
+  std::lock_guard<std::mutex> lk(g_codebook_mu);
+  unsigned char** dev = g_codebook_dev[ctx->device];
+  cudaError_t e = cudaDeviceSynchronize();  // no kernel of any context reads a table while it changes
+  if (e == cudaSuccess && !dev[slot]) e = cudaMalloc(reinterpret_cast<void**>(&dev[slot]), bytes);
+  if (e == cudaSuccess) e = cudaMemcpy(dev[slot], table, bytes, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = publish_codebooks_dense(dev);
+  if (e == cudaSuccess) e = publish_codebooks_anyfmt(dev);
+  if (e == cudaSuccess) e = publish_codebooks_grouped(dev);
+  if (e == cudaSuccess) ctx->codebook[slot] = dev[slot];
   return check_cuda(ctx, e, "set_codebook");
 }
 

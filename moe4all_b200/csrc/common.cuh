@@ -71,7 +71,8 @@ struct infr_cuda_ctx {
   unsigned long long* trace = nullptr;        // optional phase stamps (see trace_stamp)
   infr_cuda_config cfg = {};                  // tuning switches (infr_cuda_set_config)
   infr::EpState* ep = nullptr;                // expert-parallel communicator and buffers, or null
-  unsigned char* codebook[4] = {nullptr, nullptr, nullptr, nullptr};  // device copies of the grid tables (formats.cuh slots)
+  unsigned char* codebook[4] = {nullptr, nullptr, nullptr, nullptr};  // grid tables this context has been given (formats.cuh
+                                                                      // slots): the device-wide copies, not owned
 };
 
 namespace infr {

@@ -126,8 +126,23 @@ def test_codebook_format_needs_its_table():
         be.set_codebook(DType(IQ3S), synth.codebook(IQ3S))
         be.linear(DType(IQ3S), w, x, y, 1, 512, 8)
         be.sync()
+        want = orc.linear(IQ3S, be.download(w, np.uint8), synth.gen_f32(512, 2).reshape(1, 512), 8)
+        assert_close(be.download(y, np.float32).reshape(1, 8), want, tol=1e-4)
     finally:
         be.close()
+    # the table outlives the context that set it: another context of the device that was given it keeps working
+    be2 = CudaBackend(0)
+    try:
+        be2.set_codebook(DType(IQ3S), synth.codebook(IQ3S))
+        be3 = CudaBackend(0)
+        be3.set_codebook(DType(IQ3S), synth.codebook(IQ3S))
+        be3.close()
+        w2, x2, y2 = be2.from_host(synth.testkit_weight("IQ3S", 512 * 8, seed=1).reshape(-1)), be2.from_host(synth.gen_f32(512, 2)), be2.alloc(32)
+        be2.linear(DType(IQ3S), w2, x2, y2, 1, 512, 8)
+        be2.sync()
+        assert_close(be2.download(y2, np.float32).reshape(1, 8), want, tol=1e-4)
+    finally:
+        be2.close()
 
 
 def test_unknown_format_refused(backend):
