@@ -494,6 +494,25 @@ def test_grid_codebook_formats(dt, name, bb):
         orc.set_codebook(12, table)  # not a codebook format
 
 
+def test_block_size_tables_agree():
+    # the block sizes are written down in five places (the library's header via backend.DType, the oracle, the two
+    # generators, the benchmark): one disagreement would make a bank the wrong size
+    import importlib.util
+    import os
+
+    from moe4all_b200 import DType, devgen
+
+    spec = importlib.util.spec_from_file_location("bench_for_tables", os.path.join(os.path.dirname(os.path.dirname(__file__)), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert set(synth.BLOCKS) == set(devgen.BLOCKS) == set(bench.BANK_BLOCK) == set(bench.BANK_TYPES.values())
+    for dt, (elems, nbytes, _slots) in synth.BLOCKS.items():
+        assert devgen.BLOCKS[dt][:2] == (elems, nbytes) and bench.BANK_BLOCK[dt] == (elems, nbytes)
+        assert DType(dt).row_bytes(8 * elems) == 8 * nbytes == orc.row_bytes(dt, 8 * elems)
+        with pytest.raises(ValueError):
+            DType(dt).row_bytes(elems + 1)
+
+
 def test_ragged_block_count_rejected():
     with pytest.raises(ValueError):
         orc.dequant(orc.DT_Q4K, np.zeros(144, np.uint8), 100)
