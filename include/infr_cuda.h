@@ -415,6 +415,9 @@ typedef struct infr_cuda_gguf_tensor {
 int32_t infr_cuda_gguf_open(const char* path, infr_cuda_gguf** out, char* err, size_t err_cap);
 void infr_cuda_gguf_close(infr_cuda_gguf* g);
 uint64_t infr_cuda_gguf_tensor_count(const infr_cuda_gguf* g);
+/* The name of tensor `index` (names in sorted order): lets a host that opens the shards of a split model
+ * (`<base>-NNNNN-of-MMMMM.gguf`, crates/infr-core/src/gguf_split.rs) check that no name appears twice. */
+int32_t infr_cuda_gguf_tensor_name(const infr_cuda_gguf* g, uint64_t index, char* out, size_t cap);
 /* INFR_CUDA_ERR_INVALID_ARG when there is no such tensor / key (or the key has another type). */
 int32_t infr_cuda_gguf_find(const infr_cuda_gguf* g, const char* name, infr_cuda_gguf_tensor* out);
 int32_t infr_cuda_gguf_meta_u64(const infr_cuda_gguf* g, const char* key, uint64_t* out);

@@ -27,7 +27,7 @@ EXPORTS = [
     "infr_cuda_buf_len", "infr_cuda_buf_ptr", "infr_cuda_upload", "infr_cuda_download",
     "infr_cuda_upload_async", "infr_cuda_download_async",
     "infr_cuda_upload_gated", "infr_cuda_host_signal", "infr_cuda_host_ring", "infr_cuda_host_await", "infr_cuda_host_reset", "infr_cuda_host_step", "infr_cuda_host_steps", "infr_cuda_set_codebook",
-    "infr_cuda_gguf_open", "infr_cuda_gguf_close", "infr_cuda_gguf_tensor_count", "infr_cuda_gguf_find",
+    "infr_cuda_gguf_open", "infr_cuda_gguf_close", "infr_cuda_gguf_tensor_count", "infr_cuda_gguf_tensor_name", "infr_cuda_gguf_find",
     "infr_cuda_gguf_meta_u64", "infr_cuda_gguf_meta_f64", "infr_cuda_gguf_meta_str", "infr_cuda_gguf_upload",
     "infr_cuda_sync", "infr_cuda_moe_ffn", "infr_cuda_moe_route", "infr_cuda_linear",
     "infr_cuda_gated_act", "infr_cuda_moe_shared_add", "infr_cuda_rmsnorm", "infr_cuda_add",

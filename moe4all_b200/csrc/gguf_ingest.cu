@@ -265,6 +265,15 @@ void infr_cuda_gguf_close(infr_cuda_gguf* g) {
 
 uint64_t infr_cuda_gguf_tensor_count(const infr_cuda_gguf* g) { return g ? g->tensors.size() : 0; }
 
+int32_t infr_cuda_gguf_tensor_name(const infr_cuda_gguf* g, uint64_t index, char* out, size_t cap) {
+  if (!g || !out || !cap || index >= g->tensors.size()) return INFR_CUDA_ERR_INVALID_ARG;
+  auto it = g->tensors.begin();
+  std::advance(it, (ptrdiff_t)index);  // name order; a caller walking all names of a shard pays n^2 / 2 steps of a small map
+  if (it->first.size() + 1 > cap) return INFR_CUDA_ERR_INVALID_ARG;
+  std::snprintf(out, cap, "%s", it->first.c_str());
+  return INFR_CUDA_OK;
+}
+
 int32_t infr_cuda_gguf_find(const infr_cuda_gguf* g, const char* name, infr_cuda_gguf_tensor* out) {
   if (!g || !name || !out) return INFR_CUDA_ERR_INVALID_ARG;
   auto it = g->tensors.find(name);

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from moe4all_b200 import BackendError, synth
-from moe4all_b200.gguf import GgufFile, moe_layer_op
+from moe4all_b200.gguf import GgufFile, GgufModel, moe_layer_op, parse_shard, shard_set
 
 import gguf_writer as gw
 
@@ -75,6 +75,84 @@ def test_malformed_files_are_refused(tmp_path, case):
     with pytest.raises(BackendError) as e:
         GgufFile(path)
     assert str(e.value)
+
+
+def test_shard_names():
+    # the reference's own vectors (crates/infr-core/src/gguf_split.rs `parse_shard_pattern`,
+    # `an_over_wide_shard_total_is_not_a_shard`, and the set a shard name stands for)
+    assert parse_shard("model-Q4_K_M-00001-of-00003.gguf") == ("model-Q4_K_M", 1, 3, 5)
+    assert parse_shard("m-00003-of-00005.gguf")[1] == 3
+    assert parse_shard("model-Q4_K_M.gguf") is None
+    assert parse_shard("m-1-of-003.gguf") is None and parse_shard("m-000ab-of-00003.gguf") is None
+    assert parse_shard("m-Q4_K_M-0000000001-of-4294967295.gguf") is None and parse_shard("m-000001-of-999999.gguf") is None
+    assert shard_set("/d/m-00002-of-00003.gguf") == [f"/d/m-0000{i}-of-00003.gguf" for i in (1, 2, 3)]
+    assert shard_set("/d/plain.gguf") == ["/d/plain.gguf"]
+
+
+def write_split(tmp_path, L, parts=3, count=None, numbers=None, tensors_count=None, dup=False, base="m"):
+    """One layer's tensors dealt over `parts` shard files the way gguf-split writes them: the model's metadata in
+    the first shard, only the three split keys in the others (crates/infr-gguf/src/lib.rs:69-90)."""
+    ref_path = str(tmp_path / "whole.gguf")
+    tensors = gw.layer_to_gguf(ref_path, L, layer=0, n_used=2)
+    groups = [tensors[i::parts] for i in range(parts)]
+    if dup:
+        groups[1] = groups[1] + [groups[0][0]]
+    total = sum(len(g_) for g_ in groups) if tensors_count is None else tensors_count
+    paths = []
+    for i, grp in enumerate(groups):
+        split = [("split.no", gw.T_U16, i if numbers is None else numbers[i]), ("split.count", gw.T_U16, parts if count is None else count),
+                 ("split.tensors.count", gw.T_I32, total)]
+        meta = split if i else [("general.architecture", gw.T_STR, "qwen35moe"), ("qwen35moe.expert_used_count", gw.T_U32, 2)] + split
+        path = str(tmp_path / f"{base}-{i + 1:05d}-of-{parts:05d}.gguf")
+        gw.write_gguf(path, meta, grp)
+        paths.append(path)
+    return paths, tensors
+
+
+def test_split_model_opens_through_any_shard(tmp_path):
+    L = small_layer()
+    paths, tensors = write_split(tmp_path, L)
+    for chosen in (paths[0], paths[2]):
+        m = GgufModel(chosen)
+        assert len(m.shards) == 3 and m.tensor_count() == len(tensors)
+        assert m.meta_str("general.architecture") == "qwen35moe" and m.meta_u64("qwen35moe.expert_used_count") == 2
+        for name, dims, gtype, payload in tensors:
+            t = m.find(name)
+            assert t is not None and t.dtype == gtype and t.dims == tuple(dims) and t.nbytes == len(payload)
+        assert m.find("blk.0.nope") is None
+        m.close()
+    whole = GgufModel(str(tmp_path / "whole.gguf"))  # a single file is a model of one shard
+    assert len(whole.shards) == 1 and whole.tensor_count() == len(tensors)
+    whole.close()
+
+
+@pytest.mark.parametrize("case", ["missing", "count", "number", "tensors", "duplicate"])
+def test_broken_split_sets_are_refused(tmp_path, case):
+    import os
+    L = small_layer()
+    kw = {"count": dict(count=4), "number": dict(numbers=[0, 2, 1]), "tensors": dict(tensors_count=99), "duplicate": dict(dup=True)}.get(case, {})
+    paths, _ = write_split(tmp_path, L, **kw)
+    if case == "missing":
+        os.remove(paths[1])
+    with pytest.raises(BackendError) as e:
+        GgufModel(paths[0])
+    assert {"missing": "is missing", "count": "split.count", "number": "split.no", "tensors": "split.tensors.count", "duplicate": "appears in shards"}[case] in str(e.value)
+
+
+@pytest.mark.gpu
+def test_layer_from_split_model_matches_oracle(backend, tmp_path):
+    from helpers import assert_close, oracle_layer
+    L = small_layer()
+    paths, _ = write_split(tmp_path, L)
+    m = GgufModel(paths[1])
+    op, bufs = moe_layer_op(backend, m, 0)
+    assert np.array_equal(backend.download(bufs["gate"], np.uint8, count=L.gate.size), L.gate.reshape(-1))
+    x = synth.activations(78, 3, 256)
+    op.x, op.dst, op.rows = backend.from_host(x), backend.alloc(3 * 256 * 4), 3
+    backend.moe_ffn(op)
+    backend.sync()
+    assert_close(backend.download(op.dst, np.float32).reshape(3, 256), oracle_layer(L, x, 2).dst)
+    m.close()
 
 
 @pytest.mark.gpu
