@@ -74,3 +74,22 @@ def test_dtype_geometry():
     assert DType.F32.row_bytes(7) == 28
     with pytest.raises(ValueError):
         DType.Q4K.row_bytes(100)
+
+
+def test_reference_arm_prints_the_contract_line():
+    # `bench.py --impl reference` runs the CPU restatement only (no GPU, no CUDA library): one JSON line with the
+    # keys the driver reads; the prefill workload's bounded sample keeps this to a second or two
+    import json
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--workload", "prefill", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=300, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["metric"] == "moe_prefill_routed_tflops" and line["unit"] == "TFLOP/s"
+    assert line["value"] > 0 and line["higher_is_better"] is True and line["vs_baseline"] is None and line["data"] == "synthetic"
+    cb = line["cpu_baseline"]
+    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == line["value"] and cb["sample"]
+    assert line["e2e"] == {"value": line["value"], "unit": line["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
