@@ -494,6 +494,32 @@ def test_grid_codebook_formats(dt, name, bb):
         orc.set_codebook(12, table)  # not a codebook format
 
 
+@pytest.mark.parametrize("dt", sorted(synth.BLOCKS))
+def test_random_blocks_decode_like_the_independent_restatements(dt):
+    # every format, random payload bits (the generators of the GPU tests and the benchmark): the oracle's decoder and
+    # the numpy restatement above agree bit for bit, and nothing decodes to a non-finite value
+    for cb in synth.CODEBOOKS:
+        orc.set_codebook(cb, synth.codebook(cb))
+    elems = synth.BLOCKS[dt][0]
+    n = 24 * max(elems, 64)
+    raw = synth.random_blocks(np.random.default_rng(700 + dt), dt, n, 1e-3, 1e-1).reshape(-1)
+    got = orc.dequant(dt, raw, n)
+    if dt == 42:  # Q2_0: (code - 1) * d, codes two bits each
+        blk = raw.reshape(-1, 18)
+        d = blk[:, 0:2].copy().view(np.float16).astype(np.float32)
+        q = (blk[:, 2 + np.arange(64) // 4].astype(np.int64) >> ((np.arange(64) % 4) * 2)) & 3
+        want = ((q - 1).astype(np.float32) * d).reshape(-1)
+    else:
+        want = {12: np_q4k, 14: np_q6k, 13: np_q5k, 8: np_q80, 20: np_iq4nl, 23: np_iq4xs, 10: np_q2k, 11: np_q3k, 39: np_mxfp4,
+                40: np_nvfp4, 2: lambda r: np_legacy32(r, 2), 3: lambda r: np_legacy32(r, 3), 6: lambda r: np_legacy32(r, 6),
+                7: lambda r: np_legacy32(r, 7), 17: lambda r: np_grid_formats(17, r, synth.codebook(17)),
+                22: lambda r: np_grid_formats(22, r, synth.codebook(22)), 18: lambda r: np_grid_formats(18, r, synth.codebook(18)),
+                21: lambda r: np_grid_formats(21, r, synth.codebook(21))}[dt](raw)
+    want = np.asarray(want, np.float32).reshape(-1)
+    assert np.all(np.isfinite(got)) and np.abs(got).max() > 0
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
 def test_block_size_tables_agree():
     # the block sizes are written down in five places (the library's header via backend.DType, the oracle, the two
     # generators, the benchmark): one disagreement would make a bank the wrong size
